@@ -1,0 +1,167 @@
+/* mary_b200.h -- C ABI of the B200 (sm_100a) kernels behind maryml's quantized
+ * inference op surface.
+ *
+ * Every entry point takes plain device pointers, sizes and scalars, enqueues its
+ * work on the given CUDA stream and returns without synchronising (the one
+ * exception, the weight quantizer's amax readback, is the reference's own).
+ * Outputs and workspaces are allocated by the caller, so a Rust wrapper can hand
+ * out buffers of its own arena and keep ownership. Return value: 0, or a negative
+ * MB_ERR_* code with the text available from mb_last_error(). Preflight refusals
+ * (shape, alignment, extent) happen before any launch, as in the reference.
+ *
+ * Each declaration cites the reference interface it replaces (file:line, paths
+ * relative to the reference project root).
+ *
+ * Layouts
+ *   codes      [rows, K/2] bytes, E2M1, the lower K index in the LOW nibble
+ *   scales     [rows, K/16] E4M3 bytes, row-major             (MB_SF_ROWMAJOR)
+ *   scales     tiled for the tensor-core GEMM                 (MB_SF_TILED):
+ *              512-byte atoms of 128 rows x 4 scales, byte (row%32)*16 +
+ *              (row/32%4)*4 + kb%4 inside an atom, atoms ordered [row/128][kb/4],
+ *              K padded to a multiple of 256 elements, rows to 128
+ *   scale2     one f32 per tensor (per expert in a bank)
+ */
+#ifndef MARY_B200_H
+#define MARY_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct mb_ctx mb_ctx;
+typedef void* mb_stream; /* a cudaStream_t */
+
+enum {
+  MB_OK = 0,
+  MB_ERR_INVALID = -1, /* refused before launch: shape, alignment, extent, non-finite scale */
+  MB_ERR_CUDA = -2,    /* a CUDA runtime/driver call failed */
+  MB_ERR_NONFINITE = -3, /* the reference refuses a weight holding NaN/Inf */
+  MB_ERR_DEVICE_FLAG = -4, /* a kernel raised a status word (timeout, bad routing) */
+  MB_ERR_UNAVAILABLE = -5  /* an optional dependency (NCCL) could not be loaded */
+};
+
+enum { MB_DT_BF16 = 0, MB_DT_F32 = 1 };
+enum { MB_SF_ROWMAJOR = 0, MB_SF_TILED = 1 };
+
+/* Activation quantizer recipes. */
+enum {
+  /* quantize_block with a second-level scale `input_scale`: block byte =
+   * e4m3(min((amax/6)/input_scale, 448)), codes = cvt(x / (f32(byte)*input_scale)).
+   * src/nn/nvfp4_gemv.rs:140-172, used by src/nn/nvfp4_gemm.rs:644-669. */
+  MB_QUANT_SCALED = 0,
+  /* no second level, hoisted reciprocal: byte = e4m3(min(amax/6, 448)),
+   * codes = cvt(x * fl(1/f32(byte))). src/models/inkling/fp4quant.rs:199-238. */
+  MB_QUANT_RECIP = 1,
+  /* per-row second-level scale amax_row/2688 written to `rowscale`.
+   * src/nn/nvfp4_gemm.rs:757-813. */
+  MB_QUANT_ROWS = 2
+};
+
+/* GEMM epilogues. */
+enum {
+  MB_EPI_PLAIN = 0,            /* out = acc * alpha [* rowscale[m]] */
+  MB_EPI_SWIGLU_INTERLEAVED = 1 /* columns (2i, 2i+1) = (gate, up), each rounded to bf16, then
+                                  out[m, i] = bf16(silu(gate) * up); out has N/2 columns.
+                                  src/models/inkling/fp4gemm.rs:472-507 fused into the GEMM. */
+};
+
+/* ---- context ---------------------------------------------------------------- */
+/* Replaces the cubecl ComputeClient the reference's launch functions take
+ * (src/models/inkling/rawcuda.rs:31-80). One per device and host thread. */
+int mb_ctx_create(int device, mb_ctx** out);
+void mb_ctx_destroy(mb_ctx* ctx);
+const char* mb_last_error(mb_ctx* ctx);
+const char* mb_version(void);
+/* Reads and clears the device status words (bounded-wait timeouts, non-finite
+ * router logits, bad routing plans); synchronises `stream`. The reference reads
+ * such flags later on the host: src/models/inkling/routetopk.rs:39-45,
+ * src/models/inkling/devplan.rs:248-300. Returns MB_ERR_DEVICE_FLAG if any is set. */
+int mb_check_flags(mb_ctx* ctx, mb_stream stream, int32_t* flags_out8);
+
+/* ---- NVFP4 codec ---------------------------------------------------------------- */
+/* Nvfp4::quantize (src/nn/nvfp4_gemv.rs:284-351): amax over the tensor (one host
+ * round trip), scale2 = amax/(6*448) or 1.0, then one 16-block per thread.
+ * w: [n, k] bf16 contiguous, k % 32 == 0. Writes row-major codes and scales.
+ * Synchronises `stream` once. MB_ERR_NONFINITE for a NaN/Inf weight. */
+int mb_nvfp4_quantize_weight(mb_ctx* ctx, mb_stream stream, const void* w_bf16, size_t n, size_t k,
+                             uint8_t* codes, uint8_t* scales, float* scale2_host_out);
+
+/* quantize_kernel / quantize_nvfp4(_bf16) / quantize_rows_kernel
+ * (src/nn/nvfp4_gemv.rs:123-172, src/models/inkling/fp4quant.rs:199-238,
+ * src/nn/nvfp4_gemm.rs:757-813). x: [rows, k] bf16 or f32, k % 16 == 0 (k % 64
+ * for the tensor-core GEMM). sf_layout selects row-major or tiled scales; a tiled
+ * plane must hold mb_nvfp4_sf_bytes(rows, k) bytes. rowscale: [rows] f32 output for
+ * MB_QUANT_ROWS, else NULL. gather: optional [rows] int32 source-row map
+ * (src/models/inkling/moegroup.rs:313-331: out row r reads x row gather[r]; a
+ * negative entry is a zero row); src_rows = rows of x when gather is given. */
+int mb_nvfp4_quantize_act(mb_ctx* ctx, mb_stream stream, const void* x, int x_dtype, size_t rows, size_t k,
+                          int recipe, float input_scale, const int32_t* gather, size_t src_rows,
+                          uint8_t* codes, uint8_t* scales, int sf_layout, float* rowscale);
+
+/* dequantize_nvfp4(_bf16) (src/models/inkling/fp4quant.rs:437-459) and
+ * nvfp4::decode_payload (src/nvfp4.rs:170-182): out = E2M1[code]*(e4m3(scale)*scale2). */
+int mb_nvfp4_dequantize(mb_ctx* ctx, mb_stream stream, const uint8_t* codes, const uint8_t* scales_rowmajor,
+                        float scale2, size_t rows, size_t k, void* out, int out_dtype);
+
+/* Size of a tiled scale plane, and the re-layout of a row-major plane into it.
+ * The reference pre-permutes weights for its MMA the same way at load
+ * (src/models/inkling/fp4gemm.rs:1279-1367); `upload` still takes the canonical planes. */
+size_t mb_nvfp4_sf_bytes(size_t rows, size_t k);
+int mb_nvfp4_tile_scales(mb_ctx* ctx, mb_stream stream, const uint8_t* scales_rowmajor, size_t rows, size_t k,
+                         uint8_t* scales_tiled);
+int mb_nvfp4_untile_scales(mb_ctx* ctx, mb_stream stream, const uint8_t* scales_tiled, size_t rows, size_t k,
+                           uint8_t* scales_rowmajor);
+
+/* ---- linears ---------------------------------------------------------------------- */
+/* Nvfp4::gemv (src/nn/nvfp4_gemv.rs:202-250, 529-578): [rows<=8, k] x [n, k]^T,
+ * W4A16, one warp per output row, f32 carry, x scale2 once, one cast.
+ * x 16-byte aligned, k % 32 == 0. */
+int mb_nvfp4_gemv_w4a16(mb_ctx* ctx, mb_stream stream, const void* x_bf16, size_t rows, const uint8_t* codes,
+                        const uint8_t* scales_rowmajor, float scale2, size_t n, size_t k, void* out,
+                        int out_dtype);
+
+/* Nvfp4::project(W4a4) / project_w4a4_scaled / project_w4a4_rows and fp4_linear_launch
+ * (src/nn/nvfp4_gemm.rs:200-291, 644-694, 814-945; src/models/inkling/fp4gemm.rs:154-245):
+ * out[m, n] = (sum_k a[m,k] b[n,k]) * alpha [* rowscale[m]], both operands NVFP4
+ * planes with TILED scales; tcgen05 block-scaled MMA, f32 accumulation in TMEM.
+ * k % 64 == 0, n % 8 == 0. out: [m, n] bf16 or f32 ([m, n/2] bf16 for the SwiGLU epilogue). */
+int mb_nvfp4_gemm_w4a4(mb_ctx* ctx, mb_stream stream, const uint8_t* a_codes, const uint8_t* a_sf_tiled,
+                       const uint8_t* b_codes, const uint8_t* b_sf_tiled, const float* rowscale, float alpha,
+                       size_t m, size_t n, size_t k, void* out, int out_dtype, int epilogue);
+
+/* fp4_linear_grouped(_bf16)_launch (src/models/inkling/moegroup.rs:430-751): the
+ * stacked rows of all active experts against an expert bank. a: [m_cap, k] planes
+ * (each expert's rows padded to 128). bank: [experts, n, k] planes with tiled scales
+ * per expert. tile_expert: [m_cap/128] int32, the expert of each 128-row tile or -1;
+ * n_tiles_dev: device int32, tiles in use. alpha: [experts] f32 (the expert's scale2). */
+int mb_nvfp4_gemm_w4a4_grouped(mb_ctx* ctx, mb_stream stream, const uint8_t* a_codes, const uint8_t* a_sf_tiled,
+                               const uint8_t* bank_codes, const uint8_t* bank_sf_tiled, const float* alpha,
+                               const int32_t* tile_expert, const int32_t* n_tiles_dev, size_t m_cap,
+                               size_t experts, size_t n, size_t k, void* out, int out_dtype, int epilogue);
+
+/* bf16_linear_launch (src/models/inkling/bf16gemm.rs:64-152): [m, k] x [n, k]^T,
+ * bf16 operands, f32 accumulation (tcgen05 kind::f16), out = acc * alpha as bf16 or
+ * f32. k % 8 == 0. alpha carries the weight's scale2 when b is a decoded NVFP4 plane
+ * (the W4A16 lane, src/nn/nvfp4_gemm.rs:93-197: scale2 applied once to the accumulator). */
+int mb_bf16_gemm(mb_ctx* ctx, mb_stream stream, const void* a_bf16, const void* b_bf16, float alpha, size_t m,
+                 size_t n, size_t k, void* out, int out_dtype);
+
+/* ---- tensor parallel ---------------------------------------------------------------- */
+/* Tp::shard (src/models/inkling/tp.rs:540-555). Host arithmetic only. */
+int mb_tp_shard(size_t rank, size_t world, size_t extent, size_t* lo, size_t* hi);
+/* Group::form / warm / all_reduce_f32 (src/models/inkling/tpcomm.rs:271-310,
+ * 377-404, 415-429): rank 0 mints a 128-byte NCCL id, every rank joins with it;
+ * warm() all-reduces ones and requires the sum to equal world. */
+int mb_tp_unique_id(mb_ctx* ctx, uint8_t id_out[128]);
+int mb_tp_form(mb_ctx* ctx, const uint8_t id[128], int rank, int world);
+int mb_tp_warm(mb_ctx* ctx, mb_stream stream);
+int mb_tp_all_reduce(mb_ctx* ctx, mb_stream stream, void* buf, size_t count, int dtype);
+int mb_tp_close(mb_ctx* ctx);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* MARY_B200_H */

@@ -1,0 +1,57 @@
+// Context object and error reporting of the C ABI.
+#include "common.cuh"
+
+MB_API const char* mb_version(void) { return "mary-b200 0.1 (sm_100a)"; }
+
+MB_API int mb_ctx_create(int device, mb_ctx** out) {
+  if (!out) return MB_ERR_INVALID;
+  *out = nullptr;
+  int count = 0;
+  cudaError_t e = cudaGetDeviceCount(&count);
+  if (e != cudaSuccess || device < 0 || device >= count) return MB_ERR_CUDA;
+  if (cudaSetDevice(device) != cudaSuccess) return MB_ERR_CUDA;
+  cudaDeviceProp prop;
+  if (cudaGetDeviceProperties(&prop, device) != cudaSuccess) return MB_ERR_CUDA;
+  if (prop.major != 10) return MB_ERR_UNAVAILABLE;  // the kernels are sm_100a only; there is no fallback
+  mb_ctx* ctx = new mb_ctx();
+  ctx->device = device;
+  ctx->sm_count = prop.multiProcessorCount;
+  if (cudaMalloc(&ctx->flags_dev, (MB_FLAG_COUNT + 8) * sizeof(int)) != cudaSuccess ||
+      cudaMemset(ctx->flags_dev, 0, (MB_FLAG_COUNT + 8) * sizeof(int)) != cudaSuccess) {
+    delete ctx;
+    return MB_ERR_CUDA;
+  }
+  *out = ctx;
+  return MB_OK;
+}
+
+MB_API void mb_ctx_destroy(mb_ctx* ctx) {
+  if (!ctx) return;
+  mb_tp_close(ctx);
+  if (ctx->flags_dev) cudaFree(ctx->flags_dev);
+  delete ctx;
+}
+
+MB_API const char* mb_last_error(mb_ctx* ctx) {
+  if (!ctx) return "no context";
+  std::lock_guard<std::mutex> g(ctx->mu);
+  return ctx->last_error.c_str();
+}
+
+MB_API int mb_check_flags(mb_ctx* ctx, mb_stream stream_, int32_t* flags_out8) {
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  MB_REQUIRE(ctx, ctx != nullptr, "check_flags: null context");
+  int32_t host[MB_FLAG_COUNT];
+  MB_CUDA_OK(ctx, cudaMemcpyAsync(host, ctx->flags_dev, sizeof host, cudaMemcpyDeviceToHost, stream));
+  MB_CUDA_OK(ctx, cudaMemsetAsync(ctx->flags_dev, 0, sizeof host, stream));
+  MB_CUDA_OK(ctx, cudaStreamSynchronize(stream));
+  bool any = false;
+  for (int i = 0; i < MB_FLAG_COUNT; ++i) {
+    if (flags_out8) flags_out8[i] = host[i];
+    any |= host[i] != 0;
+  }
+  if (any)
+    return mb_fail(ctx, MB_ERR_DEVICE_FLAG, "device status: wait_timeout=%d router_nonfinite=%d plan_fault=%d",
+                   host[MB_FLAG_WAIT_TIMEOUT], host[MB_FLAG_ROUTER_NONFINITE], host[MB_FLAG_PLAN_FAULT]);
+  return MB_OK;
+}

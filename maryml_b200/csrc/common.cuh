@@ -1,0 +1,152 @@
+// Shared definitions of the library: the context object behind the C ABI, error
+// reporting, and the small device helpers every kernel file uses.
+#pragma once
+
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+
+#include <cstdarg>
+#include <cstdint>
+#include <cstdio>
+#include <cstring>
+#include <mutex>
+#include <string>
+
+#include "../../include/mary_b200.h"
+
+#define MB_API extern "C" __attribute__((visibility("default")))
+
+// Device-side status words of a context (one int each, in one small allocation).
+enum : int {
+  MB_FLAG_WAIT_TIMEOUT = 0,   // a bounded mbarrier wait ran out inside a kernel
+  MB_FLAG_ROUTER_NONFINITE,   // a router logit was NaN/Inf (token index + 1)
+  MB_FLAG_PLAN_FAULT,         // a routing plan held an out-of-range or duplicate expert
+  MB_FLAG_COUNT = 8
+};
+
+struct mb_ctx {
+  int device = 0;
+  int sm_count = 148;
+  int* flags_dev = nullptr;          // MB_FLAG_COUNT ints
+  std::string last_error;
+  std::mutex mu;
+  // Lazily resolved driver entry point for tensor-map encoding.
+  void* encode_tiled = nullptr;
+  // Tensor-parallel state (tp.cu).
+  void* nccl_lib = nullptr;
+  void* nccl_comm = nullptr;
+  int tp_rank = 0, tp_world = 1;
+};
+
+inline int mb_fail(mb_ctx* ctx, int code, const char* fmt, ...) {
+  char buf[512];
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(buf, sizeof buf, fmt, ap);
+  va_end(ap);
+  if (ctx) {
+    std::lock_guard<std::mutex> g(ctx->mu);
+    ctx->last_error = buf;
+  }
+  return code;
+}
+
+#define MB_CUDA_OK(ctx, expr)                                                                      \
+  do {                                                                                             \
+    cudaError_t e__ = (expr);                                                                      \
+    if (e__ != cudaSuccess)                                                                        \
+      return mb_fail(ctx, MB_ERR_CUDA, "%s failed: %s (%s:%d)", #expr, cudaGetErrorString(e__),    \
+                     __FILE__, __LINE__);                                                          \
+  } while (0)
+
+#define MB_REQUIRE(ctx, cond, ...)                                   \
+  do {                                                               \
+    if (!(cond)) return mb_fail(ctx, MB_ERR_INVALID, __VA_ARGS__);   \
+  } while (0)
+
+#define MB_LAUNCH_OK(ctx) MB_CUDA_OK(ctx, cudaGetLastError())
+
+inline bool mb_aligned(const void* p, size_t a) { return (reinterpret_cast<uintptr_t>(p) % a) == 0; }
+
+// ---------------------------------------------------------------------------
+// Device helpers
+// ---------------------------------------------------------------------------
+#if defined(__CUDACC__)
+
+__device__ __forceinline__ float mb_bf16_to_f32(__nv_bfloat16 v) { return __bfloat162float(v); }
+
+// E4M3 byte -> f32 (finite patterns; 0x7F/0xFF decode to NaN as the format says).
+__device__ __forceinline__ float mb_e4m3_to_f32(uint32_t b) {
+  uint32_t exp = (b >> 3) & 0xF, man = b & 7;
+  float mag;
+  if (exp == 0) {
+    mag = float(man) * 0.001953125f;  // 2^-9
+  } else if (exp == 15 && man == 7) {
+    mag = __int_as_float(0x7FC00000);
+  } else {
+    mag = __int_as_float(((exp + 120u) << 23) | (man << 20));
+  }
+  return (b & 0x80) ? -mag : mag;
+}
+
+// The E2M1 value of the low nibble of `code` by bit construction: for a
+// magnitude code m >= 2 the f32 bits are (m << 22) + bits(0.5); codes 0 and 1
+// are the subnormal pair; the sign bit moves to bit 31 (so code 8 is -0.0).
+__device__ __forceinline__ float mb_e2m1_to_f32(uint32_t code) {
+  uint32_t m = code & 7u;
+  uint32_t low = (m & 1u) * 0x3F000000u;
+  uint32_t high = (m << 22) + 0x3F000000u;
+  return __int_as_float((m >= 2u ? high : low) | ((code & 8u) << 28));
+}
+
+// f32 -> E4M3 byte for a non-negative finite value already clamped to [0, 448]:
+// round to nearest, ties to even significand. Arithmetic form: scaling by a
+// power of two is exact, so one rint is the conversion.
+__device__ __forceinline__ uint32_t mb_e4m3_from_f32(float v) {
+  if (!(v > 0.0f)) return 0;
+  if (v >= 448.0f) return 0x7E;
+  int e = int((__float_as_uint(v) >> 23) & 0xFF) - 127;
+  e = e < -6 ? -6 : e;
+  float scaled = v * __int_as_float(uint32_t(127 + 3 - e) << 23);
+  uint32_t steps = uint32_t(__float2int_rn(scaled));
+  uint32_t byte;
+  if (e == -6 && steps < 8) {
+    byte = steps;
+  } else {
+    uint32_t m;
+    if (steps == 16) { e += 1; m = 0; } else { m = steps - 8; }
+    byte = (uint32_t(e + 7) << 3) | m;
+  }
+  return byte > 0x7E ? 0x7E : byte;
+}
+
+// Two f32 -> one byte of E2M1 codes, `lo` in the LOW nibble: the hardware
+// cvt.rn.satfinite.e2m1x2.f32 (ties to the even code, saturating at 6, sign kept
+// on a zero result). PTX puts its first source operand in the HIGH nibble.
+__device__ __forceinline__ uint32_t mb_cvt_e2m1x2(float lo, float hi) {
+  uint16_t r;
+  asm volatile("{ .reg .b8 t; cvt.rn.satfinite.e2m1x2.f32 t, %1, %2; cvt.u16.u8 %0, t; }"
+               : "=h"(r) : "f"(hi), "f"(lo));
+  return uint32_t(r) & 0xFFu;
+}
+
+// Eight f32 -> one u32 of eight codes, element i at bits 4*i.
+__device__ __forceinline__ uint32_t mb_cvt_e2m1x8(const float* v) {
+  return mb_cvt_e2m1x2(v[0], v[1]) | (mb_cvt_e2m1x2(v[2], v[3]) << 8) | (mb_cvt_e2m1x2(v[4], v[5]) << 16) |
+         (mb_cvt_e2m1x2(v[6], v[7]) << 24);
+}
+
+// Byte offset of scale (row, kb) [kb = index of the 16-element block along K] in
+// the tiled scale-factor plane the tensor-core GEMM consumes: 512-byte atoms of
+// 128 rows x 4 scales, atom-internal offset (row%32)*16 + (row/32%4)*4 + kb%4,
+// atoms ordered [row/128][kb/4]. `kchunks` = atoms along K (padded to 4).
+__device__ __host__ __forceinline__ size_t mb_sf_offset(size_t row, size_t kb, size_t kchunks) {
+  return ((row >> 7) * kchunks + (kb >> 2)) * 512 + (row & 31) * 16 + ((row >> 5) & 3) * 4 + (kb & 3);
+}
+
+#endif  // __CUDACC__
+
+// Atoms along K of the tiled scale plane for a given K (4 per 256-element stage).
+inline size_t mb_sf_kchunks(size_t k) { return ((k + 255) / 256) * 4; }
+inline size_t mb_sf_plane_bytes(size_t rows, size_t k) { return ((rows + 127) / 128) * mb_sf_kchunks(k) * 512; }

@@ -1,0 +1,464 @@
+// Tensor-core GEMMs for sm_100a: out[m, n] = sum_k a[m, k] * b[n, k] (both operands
+// K-major), as one persistent, warp-specialised kernel:
+//
+//   warp 0   TMA producer: per 128-byte K step, the A tile (128 rows) and the B tile
+//            (BN rows) land in 128B-swizzled shared memory; for NVFP4 the tiled
+//            scale atoms of both operands come with them (plain bulk copies).
+//   warp 1   MMA issuer: tcgen05.mma (kind::mxf4nvf4 block-scaled, or kind::f16)
+//            with the accumulator in tensor memory; scale atoms are copied
+//            shared -> TMEM by tcgen05.cp right before the MMAs that read them.
+//   warps 2-5 epilogue: tcgen05.ld the finished accumulator, scale, convert, store.
+//
+// Two accumulators alternate so that the epilogue of tile i overlaps the MMAs of
+// tile i+1. TMEM has 512 columns; the NVFP4 kernel also keeps scale factors there,
+// so with BN = 256 the two accumulators share 64 columns: the epilogue drains those
+// first and releases them to the next tile's MMAs.
+//
+// NVFP4 algorithmic work per tile: 2*128*BN*K flop; bytes from L2: (128+BN)*K*(1/2+1/16).
+// Every mbarrier wait is bounded (tc5::mbar_wait).
+#include "common.cuh"
+#include "tc5.cuh"
+
+namespace {
+
+using namespace tc5;
+
+enum { KIND_NVF4 = 0, KIND_BF16 = 1 };
+
+struct GemmParams {
+  CUtensorMap tmap_a;
+  CUtensorMap tmap_b;
+  const uint8_t* sfa;         // tiled scale plane of A (NVFP4)
+  const uint8_t* sfb;         // tiled scale plane(s) of B
+  void* out;
+  const float* rowscale;      // [m] or null
+  const float* alpha_vec;     // [experts] or null
+  const int32_t* tile_expert; // grouped: expert of each 128-row tile
+  const int32_t* n_mtiles_dev;// grouped: tiles in use (device word)
+  int* flags;
+  float alpha;
+  uint32_t m, n, k_steps;     // k_steps: 128-byte K steps
+  uint32_t m_tiles, n_tiles;
+  uint32_t sf_kchunks;        // scale atoms along K per 128-row tile
+  uint32_t b_rows_per_expert; // grouped: n
+  uint64_t sfb_expert_stride; // grouped: bytes of one expert's tiled scale plane
+  uint32_t ldo;               // output row stride in elements
+  int out_dtype;
+  int epilogue;
+};
+
+template <int KIND, int BN>
+struct Cfg {
+  static constexpr int BM = 128;
+  static constexpr int A_BYTES = BM * 128;
+  static constexpr int B_BYTES = BN * 128;
+  static constexpr int SFA_BYTES = KIND == KIND_NVF4 ? 2048 : 0;
+  static constexpr int SFB_BYTES = KIND == KIND_NVF4 ? (BN / 128) * 2048 : 0;
+  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES + SFA_BYTES + SFB_BYTES;
+  static constexpr int STAGES = (KIND == KIND_NVF4) ? (BN == 256 ? 4 : 6) : (BN == 256 ? 4 : 6);
+  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*alignment*/ + 256 /*barriers*/;
+  // TMEM columns
+  static constexpr bool OVERLAP = (KIND == KIND_NVF4 && BN == 256);
+  static constexpr int ACC0 = 0;
+  static constexpr int ACC1 = OVERLAP ? 192 : BN;
+  static constexpr int SFA_COL = OVERLAP ? 448 : 2 * BN;   // 16 columns
+  static constexpr int SFB_COL = SFA_COL + 16;             // 4 * BN/32 columns
+  static constexpr int TMEM_COLS = 512;
+  static_assert(KIND == KIND_BF16 || SFB_COL + 4 * (BN / 32) <= 512, "TMEM budget");
+  static_assert(KIND == KIND_NVF4 || 2 * BN <= 512, "TMEM budget");
+};
+
+constexpr int NUM_THREADS = 192;
+constexpr int EPI_THREADS = 128;
+
+__device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+
+template <int KIND, int BN>
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+gemm_tc5_kernel(const __grid_constant__ GemmParams p) {
+  using C = Cfg<KIND, BN>;
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;   // swizzle atoms need 1024-byte alignment
+  uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
+  const uint32_t bar_base = smem_base + C::STAGES * C::STAGE_BYTES;
+  // barrier words: full[STAGES], empty[STAGES], acc_full[2], acc_empty[2], ovl_free, drain, then tmem ptr + abort
+  auto full_bar = [&](int s) { return bar_base + 8u * s; };
+  auto empty_bar = [&](int s) { return bar_base + 8u * (C::STAGES + s); };
+  auto acc_full_bar = [&](int b) { return bar_base + 8u * (2 * C::STAGES + b); };
+  auto acc_empty_bar = [&](int b) { return bar_base + 8u * (2 * C::STAGES + 2 + b); };
+  const uint32_t ovl_free_bar = bar_base + 8u * (2 * C::STAGES + 4);
+  const uint32_t drain_bar = bar_base + 8u * (2 * C::STAGES + 5);   // only used when a wait ran out
+  uint32_t* tmem_ptr_smem = reinterpret_cast<uint32_t*>(smem_gen + C::STAGES * C::STAGE_BYTES + 8 * (2 * C::STAGES + 6));
+  volatile int* abort_smem = reinterpret_cast<volatile int*>(tmem_ptr_smem + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  int* tflag = p.flags ? p.flags + MB_FLAG_WAIT_TIMEOUT : nullptr;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < C::STAGES; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
+    for (int b = 0; b < 2; ++b) { mbar_init(acc_full_bar(b), 1); mbar_init(acc_empty_bar(b), EPI_THREADS); }
+    mbar_init(ovl_free_bar, EPI_THREADS);
+    mbar_init(drain_bar, 1);
+    *abort_smem = 0;
+    fence_barrier_init();
+    tma_prefetch_desc(&p.tmap_a);
+    tma_prefetch_desc(&p.tmap_b);
+  }
+  if (warp == 1) {
+    tmem_alloc(smem_u32(tmem_ptr_smem), C::TMEM_COLS);
+    tmem_relinquish();
+  }
+  fence_before_sync();
+  __syncthreads();
+  fence_after_sync();
+  const uint32_t tmem_base = *tmem_ptr_smem;
+
+  const uint32_t m_tiles = p.n_mtiles_dev ? uint32_t(*p.n_mtiles_dev) : p.m_tiles;
+  const uint32_t total_tiles = m_tiles * p.n_tiles;
+
+  if (warp == 0) {
+    // ------------------------------ producer ------------------------------------
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      uint32_t armed = 0;   // bit s: stage s armed at least once; parity of its last arming in armed_par
+      uint32_t armed_par = 0;
+      bool ok = true;
+      for (uint32_t tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
+        const uint32_t mt = tile % m_tiles, nt = tile / m_tiles;
+        uint32_t brow = nt * BN;
+        const uint8_t* sfb = p.sfb;
+        if (p.tile_expert) {
+          int e = p.tile_expert[mt];
+          if (e < 0) e = 0;
+          brow += uint32_t(e) * p.b_rows_per_expert;
+          sfb += uint64_t(e) * p.sfb_expert_stride;
+        }
+        for (uint32_t ks = 0; ks < p.k_steps; ++ks) {
+          if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_smem, tflag, 1)) { ok = false; break; }
+          const uint32_t sa = smem_base + stage * C::STAGE_BYTES;
+          const uint32_t sb = sa + C::A_BYTES;
+          mbar_arrive_expect_tx(full_bar(stage), C::STAGE_BYTES);
+          armed |= 1u << stage;
+          armed_par = (armed_par & ~(1u << stage)) | (phase << stage);
+          const int x = KIND == KIND_NVF4 ? int(ks * 128) : int(ks * 64);   // element coordinate (bytes / bf16)
+          tma_load_2d(sa, &p.tmap_a, x, int(mt * C::BM), full_bar(stage));
+          tma_load_2d(sb, &p.tmap_b, x, int(brow), full_bar(stage));
+          if (KIND == KIND_NVF4) {
+            const uint32_t ssfa = sb + C::B_BYTES;
+            const uint32_t ssfb = ssfa + C::SFA_BYTES;
+            bulk_load(ssfa, p.sfa + (uint64_t(mt) * p.sf_kchunks + ks * 4u) * 512u, 2048u, full_bar(stage));
+#pragma unroll
+            for (int rt = 0; rt < BN / 128; ++rt)
+              bulk_load(ssfb + rt * 2048u,
+                        sfb + (uint64_t(nt * (BN / 128) + rt) * p.sf_kchunks + ks * 4u) * 512u, 2048u,
+                        full_bar(stage));
+          }
+          if (++stage == C::STAGES) { stage = 0; phase ^= 1u; }
+        }
+      }
+      if (!ok) {
+        // Leave no copy in flight: wait (bounded) for every stage this thread armed.
+        for (int s = 0; s < C::STAGES; ++s)
+          if (armed & (1u << s)) {
+            long long t0 = clock64();
+            while (!mbar_try_wait(full_bar(s), (armed_par >> s) & 1u) && clock64() - t0 < WAIT_LIMIT_CYCLES) {}
+          }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------ MMA issuer ----------------------------------
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      const uint32_t idesc = KIND == KIND_NVF4 ? idesc_nvf4(BN) : idesc_bf16(BN);
+      uint32_t it = 0;
+      bool ok = true;
+      for (uint32_t tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x, ++it) {
+        const uint32_t buf = it & 1u;
+        if (C::OVERLAP) {
+          // The previous tile's epilogue has drained the 64 shared columns.
+          if (it > 0 && !mbar_wait(ovl_free_bar, (it - 1u) & 1u, abort_smem, tflag, 2)) { ok = false; break; }
+        } else {
+          if (!mbar_wait(acc_empty_bar(buf), ((it >> 1) & 1u) ^ 1u, abort_smem, tflag, 2)) { ok = false; break; }
+        }
+        fence_after_sync();
+        const uint32_t d_tmem = tmem_base + (buf ? C::ACC1 : C::ACC0);
+        for (uint32_t ks = 0; ks < p.k_steps; ++ks) {
+          if (!mbar_wait(full_bar(stage), phase, abort_smem, tflag, 3)) { ok = false; break; }
+          fence_after_sync();
+          const uint32_t sa = smem_base + stage * C::STAGE_BYTES;
+          const uint32_t sb = sa + C::A_BYTES;
+          if (KIND == KIND_NVF4) {
+            const uint32_t ssfa = sb + C::B_BYTES;
+            const uint32_t ssfb = ssfa + C::SFA_BYTES;
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              utccp_32x128b_warpx4(tmem_base + C::SFA_COL + 4 * j, make_sf_desc(ssfa + 512 * j));
+#pragma unroll
+              for (int rt = 0; rt < BN / 128; ++rt)
+                utccp_32x128b_warpx4(tmem_base + C::SFB_COL + j * (BN / 32) + rt * 4,
+                                     make_sf_desc(ssfb + rt * 2048 + 512 * j));
+            }
+          }
+          const uint64_t adesc = make_kmajor_sw128_desc(sa);
+          const uint64_t bdesc = make_kmajor_sw128_desc(sb);
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const uint32_t acc = (ks | uint32_t(j)) != 0u;
+            // 32 bytes of K per instruction: the descriptor start address advances by 2 (16-byte units).
+            if (KIND == KIND_NVF4)
+              mma_nvf4(d_tmem, adesc + 2 * j, bdesc + 2 * j, idesc, tmem_base + C::SFA_COL + 4 * j,
+                       tmem_base + C::SFB_COL + j * (BN / 32), acc);
+            else
+              mma_f16(d_tmem, adesc + 2 * j, bdesc + 2 * j, idesc, acc);
+          }
+          umma_commit(empty_bar(stage));   // the stage is free once these MMAs have read it
+          if (++stage == C::STAGES) { stage = 0; phase ^= 1u; }
+        }
+        if (ok) umma_commit(acc_full_bar(buf));
+      }
+      if (!ok) {
+        // Let the issued MMAs retire before TMEM is freed: one more commit, bounded wait.
+        umma_commit(drain_bar);
+        long long t0 = clock64();
+        while (!mbar_try_wait(drain_bar, 0u) && clock64() - t0 < WAIT_LIMIT_CYCLES) {}
+      }
+    }
+  } else {
+    // ------------------------------ epilogue ------------------------------------
+    const uint32_t quad = warp & 3u;                  // TMEM lane quadrant this warp may read
+    const uint32_t row_in_tile = quad * 32u + lane;
+    uint32_t it = 0;
+    bool ok = true;
+    for (uint32_t tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x, ++it) {
+      const uint32_t mt = tile % m_tiles, nt = tile / m_tiles;
+      const uint32_t buf = it & 1u;
+      float alpha = p.alpha;
+      if (p.tile_expert) {
+        int e = p.tile_expert[mt];
+        alpha = e >= 0 ? p.alpha_vec[e] : 0.0f;
+      }
+      const uint32_t row = mt * C::BM + row_in_tile;
+      const bool row_ok = row < p.m;
+      float scale = alpha;
+      if (p.rowscale && row_ok) scale = p.rowscale[row] * alpha;
+      if (!mbar_wait(acc_full_bar(buf), (it >> 1) & 1u, abort_smem, tflag, 4)) { ok = false; break; }
+      fence_after_sync();
+      const uint32_t t_acc = tmem_base + ((quad * 32u) << 16) + (buf ? C::ACC1 : C::ACC0);
+      constexpr int CHUNKS = BN / 32;
+#pragma unroll 1
+      for (int ci = 0; ci < CHUNKS; ++ci) {
+        // Overlap scheme: buffer 0 drains its last two chunks (the shared columns) first.
+        int c = ci;
+        if (C::OVERLAP && buf == 0) c = (ci + CHUNKS - 2) % CHUNKS;
+        uint32_t r[32];
+        tmem_ld_x32(t_acc + c * 32, r);
+        tmem_ld_wait();
+        if (C::OVERLAP && ci == 1) {
+          fence_before_sync();
+          mbar_arrive(ovl_free_bar);
+        }
+        const uint32_t col0 = nt * BN + c * 32;
+        if (!row_ok) continue;
+        if (p.epilogue == MB_EPI_SWIGLU_INTERLEAVED) {
+          // (gate, up) pairs -> bf16(silu(bf16 gate) * bf16 up); 16 outputs per chunk.
+          __nv_bfloat16* o = static_cast<__nv_bfloat16*>(p.out) + size_t(row) * p.ldo + col0 / 2;
+          uint32_t w[8];
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            float v[2];
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+              float g = __bfloat162float(__float2bfloat16_rn(__uint_as_float(r[4 * i + 2 * h]) * scale));
+              float u = __bfloat162float(__float2bfloat16_rn(__uint_as_float(r[4 * i + 2 * h + 1]) * scale));
+              v[h] = __fdiv_rn(g, 1.0f + expf(-g)) * u;
+            }
+            w[i] = pack_bf16x2(v[0], v[1]);
+          }
+          if (col0 + 32 <= p.n) {
+            reinterpret_cast<uint4*>(o)[0] = make_uint4(w[0], w[1], w[2], w[3]);
+            reinterpret_cast<uint4*>(o)[1] = make_uint4(w[4], w[5], w[6], w[7]);
+          } else {
+            for (int i = 0; i < 8; ++i)
+              if (col0 + 4 * i + 4 <= p.n) reinterpret_cast<uint32_t*>(o)[i] = w[i];
+          }
+        } else if (p.out_dtype == MB_DT_BF16) {
+          __nv_bfloat16* o = static_cast<__nv_bfloat16*>(p.out) + size_t(row) * p.ldo + col0;
+#pragma unroll
+          for (int g = 0; g < 4; ++g) {
+            if (col0 + g * 8 + 8 <= p.n) {
+              uint4 w;
+              w.x = pack_bf16x2(__uint_as_float(r[8 * g + 0]) * scale, __uint_as_float(r[8 * g + 1]) * scale);
+              w.y = pack_bf16x2(__uint_as_float(r[8 * g + 2]) * scale, __uint_as_float(r[8 * g + 3]) * scale);
+              w.z = pack_bf16x2(__uint_as_float(r[8 * g + 4]) * scale, __uint_as_float(r[8 * g + 5]) * scale);
+              w.w = pack_bf16x2(__uint_as_float(r[8 * g + 6]) * scale, __uint_as_float(r[8 * g + 7]) * scale);
+              reinterpret_cast<uint4*>(o)[g] = w;
+            }
+          }
+        } else {
+          float* o = static_cast<float*>(p.out) + size_t(row) * p.ldo + col0;
+#pragma unroll
+          for (int g = 0; g < 8; ++g) {
+            if (col0 + g * 4 + 4 <= p.n) {
+              float4 w = make_float4(__uint_as_float(r[4 * g]) * scale, __uint_as_float(r[4 * g + 1]) * scale,
+                                     __uint_as_float(r[4 * g + 2]) * scale, __uint_as_float(r[4 * g + 3]) * scale);
+              reinterpret_cast<float4*>(o)[g] = w;
+            }
+          }
+        }
+      }
+      fence_before_sync();
+      mbar_arrive(acc_empty_bar(buf));
+    }
+  }
+
+  // ------------------------------ teardown ----------------------------------------
+  fence_before_sync();
+  __syncthreads();
+  if (warp == 1) {
+    fence_after_sync();
+    tmem_dealloc(tmem_base, C::TMEM_COLS);
+  }
+}
+
+// ---------------------------------------------------------------------------------
+// Host side
+// ---------------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+int get_encoder(mb_ctx* ctx, EncodeTiledFn* fn) {
+  if (!ctx->encode_tiled) {
+    void* sym = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    MB_CUDA_OK(ctx, cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &q));
+    if (!sym || q != cudaDriverEntryPointSuccess)
+      return mb_fail(ctx, MB_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
+    ctx->encode_tiled = sym;
+  }
+  *fn = reinterpret_cast<EncodeTiledFn>(ctx->encode_tiled);
+  return MB_OK;
+}
+
+// Row-major [rows, row_bytes] matrix, box of 128 bytes x box_rows, 128-byte swizzle.
+int make_tmap(mb_ctx* ctx, CUtensorMap* tm, const void* base, bool bf16, uint64_t rows, uint64_t row_bytes,
+              uint32_t box_rows) {
+  EncodeTiledFn enc;
+  int rc = get_encoder(ctx, &enc);
+  if (rc) return rc;
+  cuuint64_t dims[2] = {bf16 ? row_bytes / 2 : row_bytes, rows};
+  cuuint64_t strides[1] = {row_bytes};
+  cuuint32_t box[2] = {bf16 ? 64u : 128u, box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = enc(tm, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_UINT8, 2,
+                   const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                   CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return mb_fail(ctx, MB_ERR_CUDA, "cuTensorMapEncodeTiled failed with %d", int(r));
+  return MB_OK;
+}
+
+template <int KIND, int BN>
+int launch(mb_ctx* ctx, cudaStream_t stream, const GemmParams& p, uint32_t max_tiles) {
+  using C = Cfg<KIND, BN>;
+  static bool attr_set[16] = {};
+  auto kern = gemm_tc5_kernel<KIND, BN>;
+  if (!attr_set[ctx->device & 15]) {
+    MB_CUDA_OK(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES));
+    attr_set[ctx->device & 15] = true;
+  }
+  unsigned grid = std::min<uint32_t>(max_tiles, uint32_t(ctx->sm_count));
+  if (grid == 0) return MB_OK;
+  kern<<<grid, NUM_THREADS, C::SMEM_BYTES, stream>>>(p);
+  MB_LAUNCH_OK(ctx);
+  return MB_OK;
+}
+
+int gemm_w4a4_common(mb_ctx* ctx, cudaStream_t stream, const uint8_t* a_codes, const uint8_t* a_sf,
+                     const uint8_t* b_codes, const uint8_t* b_sf, const float* rowscale, float alpha,
+                     const float* alpha_vec, const int32_t* tile_expert, const int32_t* n_tiles_dev, size_t m,
+                     size_t experts, size_t n, size_t k, void* out, int out_dtype, int epilogue) {
+  MB_REQUIRE(ctx, ctx && a_codes && a_sf && b_codes && b_sf && out, "gemm_w4a4: null argument");
+  MB_REQUIRE(ctx, m > 0 && n > 0 && k > 0, "gemm_w4a4: empty extent");
+  MB_REQUIRE(ctx, k % 64 == 0, "W4A4 needs k a multiple of 64, got %zu", k);
+  MB_REQUIRE(ctx, n % 8 == 0, "NVFP4 prompt projection needs n a multiple of 8, got %zu", n);
+  MB_REQUIRE(ctx, m * k <= 0xFFFFFFFFull && n * k <= 0xFFFFFFFFull && experts * n < (1ull << 31),
+             "gemm_w4a4: exceeds u32 indexing");
+  MB_REQUIRE(ctx, out_dtype == MB_DT_BF16 || out_dtype == MB_DT_F32, "gemm_w4a4: output is bf16 or f32");
+  MB_REQUIRE(ctx, epilogue == MB_EPI_PLAIN || (epilogue == MB_EPI_SWIGLU_INTERLEAVED && out_dtype == MB_DT_BF16),
+             "gemm_w4a4: the SwiGLU epilogue writes bf16");
+  MB_REQUIRE(ctx, mb_aligned(a_codes, 16) && mb_aligned(b_codes, 16) && mb_aligned(a_sf, 16) && mb_aligned(b_sf, 16) &&
+                      mb_aligned(out, 16),
+             "gemm_w4a4: operands and output need 16-byte alignment");
+  if (tile_expert) MB_REQUIRE(ctx, n % 128 == 0 && m % 128 == 0, "grouped gemm: n and the stacked rows are multiples of 128");
+  GemmParams p;
+  memset(&p, 0, sizeof p);
+  const bool wide = (n % 256 == 0);
+  int rc = make_tmap(ctx, &p.tmap_a, a_codes, false, m, k / 2, 128);
+  if (rc) return rc;
+  rc = make_tmap(ctx, &p.tmap_b, b_codes, false, experts * n, k / 2, wide ? 256 : 128);
+  if (rc) return rc;
+  p.sfa = a_sf; p.sfb = b_sf; p.out = out; p.rowscale = rowscale; p.alpha_vec = alpha_vec;
+  p.tile_expert = tile_expert; p.n_mtiles_dev = n_tiles_dev; p.flags = ctx->flags_dev; p.alpha = alpha;
+  p.m = uint32_t(m); p.n = uint32_t(n); p.k_steps = uint32_t((k + 255) / 256);
+  p.m_tiles = uint32_t((m + 127) / 128);
+  p.n_tiles = uint32_t((n + (wide ? 255 : 127)) / (wide ? 256 : 128));
+  p.sf_kchunks = uint32_t(mb_sf_kchunks(k));
+  p.b_rows_per_expert = uint32_t(n);
+  p.sfb_expert_stride = mb_sf_plane_bytes(n, k);
+  p.ldo = uint32_t(epilogue == MB_EPI_SWIGLU_INTERLEAVED ? n / 2 : n);
+  p.out_dtype = out_dtype; p.epilogue = epilogue;
+  uint32_t tiles = p.m_tiles * p.n_tiles;
+  return wide ? launch<KIND_NVF4, 256>(ctx, stream, p, tiles) : launch<KIND_NVF4, 128>(ctx, stream, p, tiles);
+}
+
+}  // namespace
+
+MB_API int mb_nvfp4_gemm_w4a4(mb_ctx* ctx, mb_stream stream, const uint8_t* a_codes, const uint8_t* a_sf_tiled,
+                              const uint8_t* b_codes, const uint8_t* b_sf_tiled, const float* rowscale, float alpha,
+                              size_t m, size_t n, size_t k, void* out, int out_dtype, int epilogue) {
+  MB_REQUIRE(ctx, alpha == alpha && alpha > 0.0f && alpha <= 3.4e38f,
+             "W4A4 calibrated globals/product must be finite positive");
+  return gemm_w4a4_common(ctx, static_cast<cudaStream_t>(stream), a_codes, a_sf_tiled, b_codes, b_sf_tiled, rowscale,
+                          alpha, nullptr, nullptr, nullptr, m, 1, n, k, out, out_dtype, epilogue);
+}
+
+MB_API int mb_nvfp4_gemm_w4a4_grouped(mb_ctx* ctx, mb_stream stream, const uint8_t* a_codes,
+                                      const uint8_t* a_sf_tiled, const uint8_t* bank_codes,
+                                      const uint8_t* bank_sf_tiled, const float* alpha, const int32_t* tile_expert,
+                                      const int32_t* n_tiles_dev, size_t m_cap, size_t experts, size_t n, size_t k,
+                                      void* out, int out_dtype, int epilogue) {
+  MB_REQUIRE(ctx, alpha && tile_expert && n_tiles_dev && experts > 0, "grouped gemm: null argument");
+  return gemm_w4a4_common(ctx, static_cast<cudaStream_t>(stream), a_codes, a_sf_tiled, bank_codes, bank_sf_tiled,
+                          nullptr, 1.0f, alpha, tile_expert, n_tiles_dev, m_cap, experts, n, k, out, out_dtype,
+                          epilogue);
+}
+
+MB_API int mb_bf16_gemm(mb_ctx* ctx, mb_stream stream_, const void* a, const void* b, float alpha, size_t m, size_t n,
+                        size_t k, void* out, int out_dtype) {
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  MB_REQUIRE(ctx, ctx && a && b && out, "bf16_gemm: null argument");
+  MB_REQUIRE(ctx, m > 0 && n > 0 && k > 0 && k % 8 == 0 && n % 8 == 0, "bf16_gemm: k and n must be positive multiples of 8");
+  MB_REQUIRE(ctx, m * k <= 0xFFFFFFFFull && n * k <= 0xFFFFFFFFull, "bf16_gemm: exceeds u32 indexing");
+  MB_REQUIRE(ctx, out_dtype == MB_DT_BF16 || out_dtype == MB_DT_F32, "bf16_gemm: output is bf16 or f32");
+  MB_REQUIRE(ctx, mb_aligned(a, 16) && mb_aligned(b, 16) && mb_aligned(out, 16), "bf16_gemm: 16-byte alignment");
+  GemmParams p;
+  memset(&p, 0, sizeof p);
+  const bool wide = (n % 256 == 0);
+  int rc = make_tmap(ctx, &p.tmap_a, a, true, m, k * 2, 128);
+  if (rc) return rc;
+  rc = make_tmap(ctx, &p.tmap_b, b, true, n, k * 2, wide ? 256 : 128);
+  if (rc) return rc;
+  p.out = out; p.flags = ctx->flags_dev; p.alpha = alpha;
+  p.m = uint32_t(m); p.n = uint32_t(n); p.k_steps = uint32_t((k + 63) / 64);
+  p.m_tiles = uint32_t((m + 127) / 128);
+  p.n_tiles = uint32_t((n + (wide ? 255 : 127)) / (wide ? 256 : 128));
+  p.ldo = uint32_t(n); p.out_dtype = out_dtype; p.epilogue = MB_EPI_PLAIN;
+  uint32_t tiles = p.m_tiles * p.n_tiles;
+  return wide ? launch<KIND_BF16, 256>(ctx, stream, p, tiles) : launch<KIND_BF16, 128>(ctx, stream, p, tiles);
+}

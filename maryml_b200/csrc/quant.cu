@@ -1,0 +1,326 @@
+// NVFP4 quantizers, dequantizer and scale-plane re-layout.
+//
+// All of these are HBM-bound byte kernels: one thread owns one 16-element block
+// (32 B of bf16 or 64 B of f32 in, 8 B of codes + 1 scale byte out), loads are
+// 128-bit, four neighbouring lanes merge their scale bytes into one 32-bit store.
+// Algorithmic traffic per element: 2 (bf16) or 4 (f32) bytes read + 0.5625 written.
+#include "common.cuh"
+
+namespace {
+
+constexpr int QUANT_THREADS = 256;
+
+__device__ __forceinline__ void load16(const __nv_bfloat16* p, float* v) {
+  const uint4* q = reinterpret_cast<const uint4*>(p);
+  uint4 a = __ldg(q), b = __ldg(q + 1);
+  uint32_t w[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    v[2 * i] = __uint_as_float(w[i] << 16);
+    v[2 * i + 1] = __uint_as_float(w[i] & 0xFFFF0000u);
+  }
+}
+__device__ __forceinline__ void load16(const float* p, float* v) {
+  const float4* q = reinterpret_cast<const float4*>(p);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    float4 a = __ldg(q + i);
+    v[4 * i] = a.x; v[4 * i + 1] = a.y; v[4 * i + 2] = a.z; v[4 * i + 3] = a.w;
+  }
+}
+// Scalar fallback for sources that are only element-aligned.
+template <typename T>
+__device__ __forceinline__ void load16_scalar(const T* p, float* v) {
+#pragma unroll
+  for (int i = 0; i < 16; ++i) v[i] = float(p[i]);
+}
+
+__device__ __forceinline__ float amax16(const float* v) {
+  float m[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) m[i] = fmaxf(fabsf(v[i]), fabsf(v[i + 8]));
+  float a01 = fmaxf(fmaxf(m[0], m[1]), fmaxf(m[2], m[3]));
+  float a23 = fmaxf(fmaxf(m[4], m[5]), fmaxf(m[6], m[7]));
+  return fmaxf(a01, a23);
+}
+
+// One block under second-level scale `s2` with true divides: the weight recipe
+// and the mary::nn activation recipe.
+__device__ __forceinline__ void quant_block_scaled(const float* v, float s2, uint32_t& sbyte, uint2& codes) {
+  float bamax = amax16(v);
+  float t = __fdiv_rn(__fdiv_rn(bamax, 6.0f), s2);
+  sbyte = mb_e4m3_from_f32(fminf(t, 448.0f));
+  float d = __fmul_rn(mb_e4m3_to_f32(sbyte), s2);
+  float q[16];
+  if (d > 0.0f) {
+#pragma unroll
+    for (int i = 0; i < 16; ++i) q[i] = __fdiv_rn(v[i], d);
+    codes.x = mb_cvt_e2m1x8(q);
+    codes.y = mb_cvt_e2m1x8(q + 8);
+  } else {
+    codes.x = 0u;
+    codes.y = 0u;
+  }
+}
+
+// One block, no second level, hoisted reciprocal: the Inkling activation recipe.
+__device__ __forceinline__ void quant_block_recip(const float* v, uint32_t& sbyte, uint2& codes) {
+  float amax = amax16(v);
+  float sf = fminf(__fdiv_rn(amax, 6.0f), 448.0f);
+  sbyte = mb_e4m3_from_f32(sf);
+  float s = mb_e4m3_to_f32(sbyte);
+  float r = 0.0f;
+  if (s > 0.0f) r = __fdiv_rn(1.0f, s);
+  float q[16];
+#pragma unroll
+  for (int i = 0; i < 16; ++i) q[i] = __fmul_rn(v[i], r);
+  codes.x = mb_cvt_e2m1x8(q);
+  codes.y = mb_cvt_e2m1x8(q + 8);
+}
+
+template <typename T>
+__global__ void __launch_bounds__(QUANT_THREADS)
+quantize_kernel(const T* __restrict__ x, size_t rows, size_t k, int recipe, float input_scale,
+                const float* __restrict__ rowscale, const int32_t* __restrict__ gather, uint2* __restrict__ codes,
+                uint8_t* __restrict__ scales, int tiled, size_t kchunks, int vec_ok) {
+  size_t row_blocks = k / 16;
+  size_t blocks = rows * row_blocks;
+  size_t blk = size_t(blockIdx.x) * QUANT_THREADS + threadIdx.x;
+  bool live = blk < blocks;
+  size_t row = live ? blk / row_blocks : 0, kb = live ? blk % row_blocks : 0;
+  uint32_t sbyte = 0;
+  uint2 c = make_uint2(0u, 0u);
+  if (live) {
+    float v[16];
+    long long src = gather ? (long long)gather[row] : (long long)row;
+    if (src < 0) {
+#pragma unroll
+      for (int i = 0; i < 16; ++i) v[i] = 0.0f;
+    } else {
+      const T* p = x + size_t(src) * k + kb * 16;
+      if (vec_ok) load16(p, v); else load16_scalar(p, v);
+    }
+    if (recipe == MB_QUANT_RECIP) {
+      quant_block_recip(v, sbyte, c);
+    } else {
+      float s2 = recipe == MB_QUANT_ROWS ? rowscale[row] : input_scale;
+      quant_block_scaled(v, s2, sbyte, c);
+    }
+    codes[blk] = c;
+  }
+  // Four neighbouring lanes (same row, kb%4 = 0..3) merge their scale bytes.
+  if ((row_blocks & 3) == 0) {
+    uint32_t w = sbyte;
+    w |= __shfl_down_sync(0xFFFFFFFFu, sbyte, 1) << 8;
+    w |= __shfl_down_sync(0xFFFFFFFFu, sbyte, 2) << 16;
+    w |= __shfl_down_sync(0xFFFFFFFFu, sbyte, 3) << 24;
+    if (live && (threadIdx.x & 3) == 0) {
+      size_t off = tiled ? mb_sf_offset(row, kb, kchunks) : blk;
+      *reinterpret_cast<uint32_t*>(scales + off) = w;
+    }
+  } else if (live) {
+    size_t off = tiled ? mb_sf_offset(row, kb, kchunks) : blk;
+    scales[off] = uint8_t(sbyte);
+  }
+}
+
+// amax over a tensor with a separate NaN/Inf witness: max drops a NaN operand,
+// so non-finite values are recorded apart and the host refuses the tensor.
+__global__ void __launch_bounds__(256)
+amax_kernel(const __nv_bfloat16* __restrict__ w, size_t len, uint32_t* __restrict__ out2) {
+  float m = 0.0f;
+  uint32_t bad = 0;
+  size_t stride = size_t(gridDim.x) * blockDim.x;
+  for (size_t i = size_t(blockIdx.x) * blockDim.x + threadIdx.x; i < len; i += stride) {
+    float a = fabsf(__bfloat162float(w[i]));
+    if (!(a <= 3.4028234663852886e38f)) bad = 1;  // NaN or Inf
+    m = fmaxf(m, a);
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    m = fmaxf(m, __shfl_xor_sync(0xFFFFFFFFu, m, o));
+    bad |= __shfl_xor_sync(0xFFFFFFFFu, bad, o);
+  }
+  if ((threadIdx.x & 31) == 0) {
+    atomicMax(out2, __float_as_uint(m));  // non-negative floats order as their bit patterns
+    if (bad) atomicOr(out2 + 1, 1u);
+  }
+}
+
+// rowscale[r] = amax(|x[r,:]|)/2688, 1.0 for an all-zero row, NaN for a NaN row.
+template <typename T>
+__global__ void __launch_bounds__(256)
+row_scale_kernel(const T* __restrict__ x, size_t k, const int32_t* __restrict__ gather, float* __restrict__ rowscale) {
+  size_t r = blockIdx.x;
+  long long src = gather ? (long long)gather[r] : (long long)r;
+  float m = 0.0f;
+  uint32_t nan = 0;
+  if (src >= 0) {
+    for (size_t j = threadIdx.x; j < k; j += blockDim.x) {
+      float v = fabsf(float(x[size_t(src) * k + j]));
+      if (v != v) nan = 1;
+      m = fmaxf(m, v);
+    }
+  }
+  __shared__ float sm[8];
+  __shared__ uint32_t sn[8];
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    m = fmaxf(m, __shfl_xor_sync(0xFFFFFFFFu, m, o));
+    nan |= __shfl_xor_sync(0xFFFFFFFFu, nan, o);
+  }
+  if ((threadIdx.x & 31) == 0) { sm[threadIdx.x >> 5] = m; sn[threadIdx.x >> 5] = nan; }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float a = 0.0f;
+    uint32_t seen = 0;
+    for (int i = 0; i < 8; ++i) { a = fmaxf(a, sm[i]); seen |= sn[i]; }
+    float s = 1.0f;
+    if (a > 0.0f) s = __fdiv_rn(a, 2688.0f);
+    if (seen) s = __int_as_float(0x7FC00000);
+    rowscale[r] = s;
+  }
+}
+
+template <typename O>
+__global__ void __launch_bounds__(256)
+dequantize_kernel(const uint2* __restrict__ codes, const uint8_t* __restrict__ scales, float scale2, size_t blocks,
+                  O* __restrict__ out) {
+  size_t blk = size_t(blockIdx.x) * 256 + threadIdx.x;
+  if (blk >= blocks) return;
+  uint2 c = codes[blk];
+  float unit = __fmul_rn(mb_e4m3_to_f32(scales[blk]), scale2);
+  O* o = out + blk * 16;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    o[i] = O(__fmul_rn(mb_e2m1_to_f32(c.x >> (4 * i)), unit));
+    o[8 + i] = O(__fmul_rn(mb_e2m1_to_f32(c.y >> (4 * i)), unit));
+  }
+}
+
+__global__ void __launch_bounds__(256)
+tile_scales_kernel(const uint8_t* __restrict__ in, size_t rows, size_t row_blocks, size_t kchunks,
+                   uint8_t* __restrict__ out, int inverse) {
+  size_t i = size_t(blockIdx.x) * 256 + threadIdx.x;
+  if (i >= rows * row_blocks) return;
+  size_t row = i / row_blocks, kb = i % row_blocks;
+  size_t off = mb_sf_offset(row, kb, kchunks);
+  if (inverse) out[i] = in[off]; else out[off] = in[i];
+}
+
+}  // namespace
+
+MB_API size_t mb_nvfp4_sf_bytes(size_t rows, size_t k) { return mb_sf_plane_bytes(rows, k); }
+
+MB_API int mb_nvfp4_quantize_act(mb_ctx* ctx, mb_stream stream_, const void* x, int x_dtype, size_t rows, size_t k,
+                                 int recipe, float input_scale, const int32_t* gather, size_t src_rows,
+                                 uint8_t* codes, uint8_t* scales, int sf_layout, float* rowscale) {
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  MB_REQUIRE(ctx, ctx && x && codes && scales, "quantize_act: null argument");
+  MB_REQUIRE(ctx, rows > 0 && k > 0 && k % 16 == 0, "quantize_act: [%zu, %zu] needs k a positive multiple of 16", rows, k);
+  MB_REQUIRE(ctx, x_dtype == MB_DT_BF16 || x_dtype == MB_DT_F32, "quantize_act: activations are bf16 or f32");
+  MB_REQUIRE(ctx, recipe >= MB_QUANT_SCALED && recipe <= MB_QUANT_ROWS, "quantize_act: unknown recipe %d", recipe);
+  MB_REQUIRE(ctx, sf_layout == MB_SF_ROWMAJOR || sf_layout == MB_SF_TILED, "quantize_act: unknown scale layout");
+  MB_REQUIRE(ctx, rows * k <= 0xFFFFFFFFull * 16, "quantize_act: extent overflow");
+  MB_REQUIRE(ctx, mb_aligned(codes, 8) && mb_aligned(scales, 4), "quantize_act: outputs need 8/4-byte alignment");
+  size_t esz = x_dtype == MB_DT_BF16 ? 2 : 4;
+  MB_REQUIRE(ctx, mb_aligned(x, esz == 2 ? 4 : 4), "quantize_act: activation needs 4-byte alignment");
+  if (recipe == MB_QUANT_SCALED)
+    MB_REQUIRE(ctx, input_scale > 0.0f && input_scale <= 3.4e38f, "quantize_act: input_scale must be finite positive");
+  if (recipe == MB_QUANT_ROWS) MB_REQUIRE(ctx, rowscale != nullptr, "quantize_act: the rows recipe writes rowscale");
+  if (gather) MB_REQUIRE(ctx, src_rows > 0, "quantize_act: gather needs the source row count");
+  int vec_ok = mb_aligned(x, 16) && (k * esz) % 16 == 0;
+  size_t kchunks = mb_sf_kchunks(k);
+  if (sf_layout == MB_SF_TILED) {
+    // Pad rows and pad K-chunks of the tiled plane must not hold stale NaN patterns
+    // next to live rows of the same 128-row atom only cosmetically: those rows are
+    // never stored. They are zeroed so that the plane is deterministic.
+    MB_CUDA_OK(ctx, cudaMemsetAsync(scales, 0, mb_sf_plane_bytes(rows, k), stream));
+  }
+  if (recipe == MB_QUANT_ROWS) {
+    if (x_dtype == MB_DT_BF16)
+      row_scale_kernel<<<unsigned(rows), 256, 0, stream>>>(static_cast<const __nv_bfloat16*>(x), k, gather, rowscale);
+    else
+      row_scale_kernel<<<unsigned(rows), 256, 0, stream>>>(static_cast<const float*>(x), k, gather, rowscale);
+    MB_LAUNCH_OK(ctx);
+  }
+  size_t blocks = rows * (k / 16);
+  unsigned grid = unsigned((blocks + QUANT_THREADS - 1) / QUANT_THREADS);
+  if (x_dtype == MB_DT_BF16)
+    quantize_kernel<<<grid, QUANT_THREADS, 0, stream>>>(static_cast<const __nv_bfloat16*>(x), rows, k, recipe,
+                                                        input_scale, rowscale, gather,
+                                                        reinterpret_cast<uint2*>(codes), scales,
+                                                        sf_layout == MB_SF_TILED, kchunks, vec_ok);
+  else
+    quantize_kernel<<<grid, QUANT_THREADS, 0, stream>>>(static_cast<const float*>(x), rows, k, recipe, input_scale,
+                                                        rowscale, gather, reinterpret_cast<uint2*>(codes), scales,
+                                                        sf_layout == MB_SF_TILED, kchunks, vec_ok);
+  MB_LAUNCH_OK(ctx);
+  return MB_OK;
+}
+
+MB_API int mb_nvfp4_quantize_weight(mb_ctx* ctx, mb_stream stream_, const void* w_bf16, size_t n, size_t k,
+                                    uint8_t* codes, uint8_t* scales, float* scale2_host_out) {
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  MB_REQUIRE(ctx, ctx && w_bf16 && codes && scales && scale2_host_out, "quantize_weight: null argument");
+  MB_REQUIRE(ctx, n > 0 && k > 0 && k % 32 == 0, "NVFP4 needs contiguous [n, k] with k a multiple of 32, got [%zu, %zu]", n, k);
+  MB_REQUIRE(ctx, n * k <= 0xFFFFFFFFull, "NVFP4 weight exceeds u32 indexing");
+  uint32_t* scratch = reinterpret_cast<uint32_t*>(ctx->flags_dev + MB_FLAG_COUNT);  // two spare words
+  MB_CUDA_OK(ctx, cudaMemsetAsync(scratch, 0, 8, stream));
+  size_t len = n * k;
+  unsigned grid = unsigned(std::min<size_t>((len + 255) / 256, size_t(ctx->sm_count) * 8));
+  amax_kernel<<<grid, 256, 0, stream>>>(static_cast<const __nv_bfloat16*>(w_bf16), len, scratch);
+  MB_LAUNCH_OK(ctx);
+  uint32_t host[2];
+  MB_CUDA_OK(ctx, cudaMemcpyAsync(host, scratch, 8, cudaMemcpyDeviceToHost, stream));
+  MB_CUDA_OK(ctx, cudaStreamSynchronize(stream));
+  if (host[1]) return mb_fail(ctx, MB_ERR_NONFINITE, "NVFP4 source has a non-finite weight");
+  float amax;
+  memcpy(&amax, &host[0], 4);
+  float scale2 = amax > 0.0f ? amax / (6.0f * 448.0f) : 1.0f;
+  *scale2_host_out = scale2;
+  return mb_nvfp4_quantize_act(ctx, stream_, w_bf16, MB_DT_BF16, n, k, MB_QUANT_SCALED, scale2, nullptr, 0, codes,
+                               scales, MB_SF_ROWMAJOR, nullptr);
+}
+
+MB_API int mb_nvfp4_dequantize(mb_ctx* ctx, mb_stream stream_, const uint8_t* codes, const uint8_t* scales,
+                               float scale2, size_t rows, size_t k, void* out, int out_dtype) {
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  MB_REQUIRE(ctx, ctx && codes && scales && out, "dequantize: null argument");
+  MB_REQUIRE(ctx, rows > 0 && k > 0 && k % 16 == 0, "dequantize: k must be a positive multiple of 16");
+  MB_REQUIRE(ctx, mb_aligned(codes, 8), "dequantize: codes need 8-byte alignment");
+  size_t blocks = rows * k / 16;
+  unsigned grid = unsigned((blocks + 255) / 256);
+  if (out_dtype == MB_DT_F32)
+    dequantize_kernel<<<grid, 256, 0, stream>>>(reinterpret_cast<const uint2*>(codes), scales, scale2, blocks,
+                                                static_cast<float*>(out));
+  else if (out_dtype == MB_DT_BF16)
+    dequantize_kernel<<<grid, 256, 0, stream>>>(reinterpret_cast<const uint2*>(codes), scales, scale2, blocks,
+                                                static_cast<__nv_bfloat16*>(out));
+  else
+    return mb_fail(ctx, MB_ERR_INVALID, "dequantize: output is bf16 or f32");
+  MB_LAUNCH_OK(ctx);
+  return MB_OK;
+}
+
+static int tile_scales(mb_ctx* ctx, mb_stream stream_, const uint8_t* in, size_t rows, size_t k, uint8_t* out,
+                       int inverse) {
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  MB_REQUIRE(ctx, ctx && in && out, "tile_scales: null argument");
+  MB_REQUIRE(ctx, rows > 0 && k > 0 && k % 16 == 0, "tile_scales: k must be a positive multiple of 16");
+  if (!inverse) MB_CUDA_OK(ctx, cudaMemsetAsync(out, 0, mb_sf_plane_bytes(rows, k), stream));
+  size_t total = rows * (k / 16);
+  tile_scales_kernel<<<unsigned((total + 255) / 256), 256, 0, stream>>>(in, rows, k / 16, mb_sf_kchunks(k), out,
+                                                                        inverse);
+  MB_LAUNCH_OK(ctx);
+  return MB_OK;
+}
+
+MB_API int mb_nvfp4_tile_scales(mb_ctx* ctx, mb_stream stream, const uint8_t* scales_rowmajor, size_t rows, size_t k,
+                                uint8_t* scales_tiled) {
+  return tile_scales(ctx, stream, scales_rowmajor, rows, k, scales_tiled, 0);
+}
+MB_API int mb_nvfp4_untile_scales(mb_ctx* ctx, mb_stream stream, const uint8_t* scales_tiled, size_t rows, size_t k,
+                                  uint8_t* scales_rowmajor) {
+  return tile_scales(ctx, stream, scales_tiled, rows, k, scales_rowmajor, 1);
+}

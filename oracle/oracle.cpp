@@ -133,7 +133,7 @@ inline float block_amax(const float* b) {
 inline void quantize_block(const float* w, float scale2, uint8_t* codes8, uint8_t* scale_byte) {
   float bamax = block_amax(w);
   float t = (bamax / E2M1_MAX) / scale2;          // two correctly rounded divides, in this order
-  uint8_t se = e4m3_from_f32(std::min(t, E4M3_MAX));
+  uint8_t se = e4m3_from_f32(std::fmin(t, E4M3_MAX));  // f32::min / fminf: a NaN operand is dropped
   *scale_byte = se;
   float d = e4m3_to_f32(se) * scale2;
   for (int i = 0; i < BLOCK / 2; ++i) {
@@ -204,7 +204,7 @@ ORC_API int orc_scale2_of_tensor(const float* w, size_t len, float* scale2) {
 // src/nvfp4.rs:146-150
 ORC_API void orc_block_unit(const float* block, float scale2, uint8_t* byte, float* unit) {
   float bmax = block_amax(block);
-  uint8_t b = e4m3_from_f32(std::min((bmax / E2M1_MAX) / scale2, E4M3_MAX));
+  uint8_t b = e4m3_from_f32(std::fmin((bmax / E2M1_MAX) / scale2, E4M3_MAX));
   *byte = b;
   *unit = e4m3_to_f32(b) * scale2;
 }

@@ -1,0 +1,45 @@
+"""The C-ABI shared object loads without a GPU and exports every symbol the header declares."""
+import ctypes
+import os
+import re
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def declared_symbols():
+    text = open(os.path.join(ROOT, "include", "mary_b200.h")).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(mb_[a-z0-9_]+)\s*\(", text)))
+
+
+def test_library_loads_and_exports_every_declared_symbol():
+    from maryml_b200 import _lib
+    names = declared_symbols()
+    assert len(names) >= 20
+    lib = ctypes.CDLL(_lib.LIB_PATH)
+    missing = [n for n in names if not hasattr(lib, n)]
+    assert not missing, missing
+    # the Python binding covers the same set
+    assert sorted(_lib.SIGNATURES) == names
+    assert b"sm_100a" in _lib.lib.mb_version()
+
+
+def test_host_only_entry_points():
+    from maryml_b200 import _lib
+    lo, hi = ctypes.c_size_t(), ctypes.c_size_t()
+    assert _lib.lib.mb_tp_shard(1, 2, 32, ctypes.byref(lo), ctypes.byref(hi)) == 0
+    assert (lo.value, hi.value) == (16, 32)
+    assert _lib.lib.mb_tp_shard(0, 3, 32, ctypes.byref(lo), ctypes.byref(hi)) == _lib.ERR_INVALID
+    # tiled scale plane: 128-row x 4-scale atoms of 512 bytes, K padded to 256
+    assert _lib.lib.mb_nvfp4_sf_bytes(128, 256) == 4 * 512
+    assert _lib.lib.mb_nvfp4_sf_bytes(129, 320) == 2 * 8 * 512
+
+
+def test_no_gpu_means_a_loud_failure_not_a_fallback():
+    import pytest
+    import torch
+    from maryml_b200 import _lib
+    if torch.cuda.is_available():
+        pytest.skip("a GPU is present")
+    with pytest.raises(_lib.MaryError):
+        _lib.Context(0)

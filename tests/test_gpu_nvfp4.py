@@ -1,0 +1,349 @@
+"""GPU parity tests of the NVFP4 codec, GEMV and tensor-core GEMMs against the CPU oracle.
+
+Bit-exact for codes, scale bytes, scale2 and dequantised values; floating outputs
+within the stated tolerances. Every call goes through the C ABI (ctypes).
+"""
+import numpy as np
+import pytest
+
+torch = pytest.importorskip("torch")
+pytestmark = pytest.mark.gpu
+
+from oracle_lib import bf16_bits_to_f32, f32_to_bf16_bits  # noqa: E402
+
+
+@pytest.fixture(scope="module")
+def mb():
+    if not torch.cuda.is_available():
+        pytest.skip("no CUDA device")
+    import maryml_b200
+    from maryml_b200 import nvfp4
+    return nvfp4
+
+
+def dev_bf16(bits):
+    return torch.from_numpy(np.ascontiguousarray(bits, np.uint16).view(np.int16)).cuda().view(torch.bfloat16)
+
+
+def host_bits(t):
+    return t.contiguous().view(torch.int16).cpu().numpy().view(np.uint16)
+
+
+def adversarial(orc, n, k):
+    """The fixture of src/nn/nvfp4_gemv.rs:726-738 on bf16."""
+    w = orc.normal_f32(0xF160FF4, n * k, 0.5)
+    w[0] = 2688.0
+    ties = np.array([0.25, 0.75, 1.25, 1.75, 2.5, 3.5, 5.0, 6.0], np.float32)
+    small = orc.normal_f32(0x0F169E77, 2 * k, 1.0)
+    for i in range(k):
+        w[k + i] = (-1.0 if i % 3 == 0 else 1.0) * ties[i % 8]
+        w[2 * k + i] = small[i] * 1e-3
+        w[3 * k + i] = small[k + i] * 1e-6
+        w[4 * k + i] = -0.0 if i % 2 == 0 else 0.0
+    return f32_to_bf16_bits(w)
+
+
+def rel_check(got, ref, max_rel=1e-2, cos_min=0.9999):
+    """north_star tolerance: max relative error <= 1e-2 (relative to max(|ref|, 1/64 of the
+    reference rms, so that cancelled sums do not divide by ~0), cosine >= 0.9999."""
+    got = np.asarray(got, np.float64).ravel()
+    ref = np.asarray(ref, np.float64).ravel()
+    rms = np.sqrt(np.mean(ref ** 2)) + 1e-30
+    rel = np.abs(got - ref) / np.maximum(np.abs(ref), rms / 64 + 1e-30)
+    # bf16 outputs carry a 2^-9 rounding of their own
+    cos = float(np.dot(got, ref) / (np.linalg.norm(got) * np.linalg.norm(ref) + 1e-30))
+    return float(rel.max()), cos
+
+
+# --------------------------------------------------------------------------- codec
+@pytest.mark.parametrize("n,k", [(8, 128), (64, 4096), (33, 96)])
+def test_weight_quantizer_bit_exact(mb, orc, n, k):
+    bits = adversarial(orc, n, k) if n >= 8 and k >= 96 else f32_to_bf16_bits(orc.normal_f32(3, n * k, 0.02))
+    w = dev_bf16(bits).view(n, k)
+    q = mb.Nvfp4.quantize(w)
+    codes, scales = q.read_planes()
+    c_ref, s_ref, g_ref = orc.quantize_weight_bf16(bits, n, k)
+    assert np.float32(q.scale2).tobytes() == g_ref.tobytes()
+    assert np.array_equal(scales, s_ref)
+    assert np.array_equal(codes, c_ref)
+    # pack_matching (src/nn/nvfp4_gemv.rs:468-501): the host packing equals the device planes
+    c_host, s_host, g_host = orc.pack_nearest(bf16_bits_to_f32(bits), k)
+    assert np.array_equal(codes, c_host) and np.array_equal(scales, s_host) and g_host.tobytes() == g_ref.tobytes()
+    # dequantised values bit-exact
+    dq = mb.dequantize(q.codes, q.scales, q.scale2, n, k).cpu().numpy().ravel()
+    assert np.array_equal(dq.view(np.uint32), orc.dequantize(c_ref, s_ref, g_ref).view(np.uint32))
+
+
+def test_weight_quantizer_refuses_non_finite_and_zero_tensor(mb, orc):
+    from maryml_b200 import MaryError
+    w = torch.ones(4, 64, dtype=torch.bfloat16, device="cuda")
+    w[1, 3] = float("nan")
+    with pytest.raises(MaryError):
+        mb.Nvfp4.quantize(w)
+    w[1, 3] = float("inf")
+    with pytest.raises(MaryError):
+        mb.Nvfp4.quantize(w)
+    z = mb.Nvfp4.quantize(torch.zeros(4, 64, dtype=torch.bfloat16, device="cuda"))
+    assert z.scale2 == 1.0
+    codes, scales = z.read_planes()
+    assert not codes.any() and not scales.any()
+
+
+def test_upload_round_trip_and_refusals(mb, orc):
+    from maryml_b200 import MaryError
+    n, k = 16, 64
+    w = orc.normal_f32(5, n * k, 0.02)
+    codes, scales, s2 = orc.pack_nearest(w, k)
+    payload = orc.payload(codes, scales, s2)
+    q = mb.Nvfp4.upload(payload, [n, k], torch.bfloat16, torch.device("cuda", 0))
+    assert np.array_equal(q.payload(), payload)
+    with pytest.raises(MaryError):
+        mb.Nvfp4.upload(payload[:-1], [n, k], torch.bfloat16, torch.device("cuda", 0))
+    with pytest.raises(MaryError):
+        mb.Nvfp4.upload(payload, [n, k + 16], torch.bfloat16, torch.device("cuda", 0))
+    bad = payload.copy()
+    bad[-4:] = np.frombuffer(np.float32(-1.0).tobytes(), np.uint8)
+    with pytest.raises(MaryError):
+        mb.Nvfp4.upload(bad, [n, k], torch.bfloat16, torch.device("cuda", 0))
+
+
+@pytest.mark.parametrize("dtype", ["bf16", "f32"])
+@pytest.mark.parametrize("rows,k", [(1, 64), (37, 256), (130, 2048)])
+def test_activation_quantizers_bit_exact(mb, orc, dtype, rows, k):
+    from maryml_b200 import _lib
+    x32 = orc.normal_f32(100 + rows, rows * k, 1.0)
+    x32[: min(k, 16)] = 0.0  # a zero block
+    if rows > 2:
+        x32[k:2 * k] *= 1e-4  # a row deep in the subnormal scale range
+    if dtype == "bf16":
+        bits = f32_to_bf16_bits(x32)
+        x = dev_bf16(bits).view(rows, k)
+        wide = bf16_bits_to_f32(bits)
+    else:
+        x = torch.from_numpy(x32).cuda().view(rows, k)
+        wide = x32
+    for recipe, ref in [
+        (_lib.QUANT_SCALED, lambda: orc.quantize_act_scaled(wide, rows, k, 1.0)),
+        (_lib.QUANT_RECIP, lambda: orc.quantize_act_recip(wide, rows, k)),
+    ]:
+        c_ref, s_ref = ref()
+        for tiled in (False, True):
+            codes, scales, _ = mb.quantize_act(x, recipe, 1.0, tiled=tiled)
+            if tiled:
+                scales = mb.untile_scales(scales, rows, k)
+            assert np.array_equal(codes.cpu().numpy().ravel(), c_ref), (recipe, tiled)
+            assert np.array_equal(scales.cpu().numpy().ravel(), s_ref), (recipe, tiled)
+    # calibrated input scale
+    c_ref, s_ref = orc.quantize_act_scaled(wide, rows, k, 0.0123)
+    codes, scales, _ = mb.quantize_act(x, _lib.QUANT_SCALED, 0.0123, tiled=False)
+    assert np.array_equal(codes.cpu().numpy().ravel(), c_ref) and np.array_equal(scales.cpu().numpy().ravel(), s_ref)
+    # per-row scale
+    c_ref, s_ref, rs_ref = orc.quantize_act_rows(wide, rows, k)
+    codes, scales, rs = mb.quantize_act(x, _lib.QUANT_ROWS, 1.0, tiled=False)
+    assert np.array_equal(rs.cpu().numpy().view(np.uint32), rs_ref.view(np.uint32))
+    assert np.array_equal(codes.cpu().numpy().ravel(), c_ref) and np.array_equal(scales.cpu().numpy().ravel(), s_ref)
+
+
+def test_quantize_gather_and_nan_row(mb, orc):
+    from maryml_b200 import _lib
+    rows, k = 12, 128
+    x32 = orc.normal_f32(9, rows * k, 1.0).reshape(rows, k)
+    x32[5, 17] = np.nan
+    x = torch.from_numpy(x32).cuda()
+    gather = torch.tensor([3, -1, 0, 11, 5], dtype=torch.int32, device="cuda")
+    codes, scales, rs = mb.quantize_act(x, _lib.QUANT_ROWS, 1.0, tiled=False, gather=gather)
+    src = np.stack([x32[3], np.zeros(k, np.float32), x32[0], x32[11], x32[5]])
+    c_ref, s_ref, rs_ref = orc.quantize_act_rows(src, 5, k)
+    assert np.isnan(rs.cpu().numpy()[4]) and rs.cpu().numpy()[1] == 1.0
+    assert np.array_equal(rs.cpu().numpy()[:4].view(np.uint32), rs_ref[:4].view(np.uint32))
+    assert np.array_equal(codes.cpu().numpy().ravel(), c_ref) and np.array_equal(scales.cpu().numpy().ravel(), s_ref)
+
+
+def test_scale_tiling_is_a_bijection(mb, orc):
+    rows, k = 200, 576
+    s = torch.randint(0, 127, (rows, k // 16), dtype=torch.uint8, device="cuda")
+    t = mb.tile_scales(s, rows, k)
+    assert t.numel() == 2 * 3 * 4 * 512
+    assert torch.equal(mb.untile_scales(t, rows, k), s)
+    # atom-internal offset (row%32)*16 + (row/32%4)*4 + kb%4, atoms [row/128][kb/4]
+    th = t.cpu().numpy()
+    sh = s.cpu().numpy()
+    for (r, kb) in [(0, 0), (31, 3), (32, 0), (127, 35), (128, 4), (199, 35)]:
+        off = ((r // 128) * 12 + kb // 4) * 512 + (r % 32) * 16 + ((r // 32) % 4) * 4 + kb % 4
+        assert th[off] == sh[r, kb]
+
+
+# --------------------------------------------------------------------------- GEMV
+@pytest.mark.parametrize("rows", [1, 3, 8])
+def test_gemv_w4a16_against_f64(mb, orc, rows):
+    n, k = 512, 4096
+    wbits = f32_to_bf16_bits(orc.normal_f32(0x0F16CAFE, n * k, 0.02))
+    xbits = f32_to_bf16_bits(orc.normal_f32(21 + rows, rows * k, 1.0))
+    q = mb.Nvfp4.quantize(dev_bf16(wbits).view(n, k))
+    x = dev_bf16(xbits).view(1, rows, k)
+    assert q.takes(x) == rows
+    y = q.gemv(x, rows)
+    codes, scales = q.read_planes()
+    ref = orc.linear_w4a16(xbits, codes, scales, q.scale2, rows, n, k)
+    got = bf16_bits_to_f32(host_bits(y)).reshape(rows, n).astype(np.float64)
+    # the reference's own bound (src/nn/nvfp4_gemv.rs:890-905): f32 accumulation error below
+    # 64 eps * sum|x w|, and the output within half a bf16 ulp of that
+    dq = orc.dequantize(codes, scales, q.scale2).reshape(n, k).astype(np.float64)
+    xa = np.abs(bf16_bits_to_f32(xbits).reshape(rows, k).astype(np.float64))
+    bound = 64 * 2.0 ** -24 * (xa @ np.abs(dq).T) + np.abs(ref) * 2.0 ** -8 + 1e-30
+    assert np.all(np.abs(got - ref) <= bound)
+
+
+def test_takes_refuses_what_the_reference_refuses(mb, orc):
+    q = mb.Nvfp4.quantize(torch.randn(64, 128, device="cuda").to(torch.bfloat16))
+    assert q.takes(torch.zeros(1, 9, 128, dtype=torch.bfloat16, device="cuda")) is None
+    assert q.takes(torch.zeros(1, 2, 64, dtype=torch.bfloat16, device="cuda")) is None
+    assert q.takes(torch.zeros(1, 2, 128, dtype=torch.float32, device="cuda")) is None
+    assert q.takes(torch.zeros(2, 2, 128, dtype=torch.bfloat16, device="cuda")) is None
+    assert q.takes(torch.zeros(1, 2, 256, dtype=torch.bfloat16, device="cuda")[:, :, ::2]) is None
+
+
+# --------------------------------------------------------------------------- tensor-core GEMM
+def _pow2_planes(orc, rng, rows, k):
+    """Random codes with power-of-two block scales: every partial sum is exact in f32."""
+    codes = rng.integers(0, 256, size=rows * k // 2, dtype=np.uint8)
+    scales = rng.choice(np.array([0x30, 0x38, 0x40], np.uint8), size=rows * k // 16)
+    return codes, scales
+
+
+@pytest.mark.parametrize("m,n,k", [(128, 128, 256), (128, 256, 256), (128, 128, 1024), (256, 512, 1024),
+                                   (100, 136, 320), (300, 768, 448), (640, 1024, 1024)])
+def test_gemm_w4a4_exact_on_power_of_two_scales(mb, orc, m, n, k):
+    """One-hot/pow2 probe in the spirit of src/bin/nvfp4_mma_probe.rs:32-58: with exactly
+    representable partial sums the tensor-core result must equal the oracle to the bit, which
+    pins the operand, scale-factor and accumulator layouts."""
+    rng = np.random.default_rng(m * 131 + n * 17 + k)
+    a_codes, a_scales = _pow2_planes(orc, rng, m, k)
+    b_codes, b_scales = _pow2_planes(orc, rng, n, k)
+    ref = orc.linear_w4a4(a_codes, a_scales, b_codes, b_scales, 1.0, m, n, k)
+    ac = torch.from_numpy(a_codes).cuda()
+    bc = torch.from_numpy(b_codes).cuda()
+    asf = mb.tile_scales(torch.from_numpy(a_scales).cuda(), m, k)
+    bsf = mb.tile_scales(torch.from_numpy(b_scales).cuda(), n, k)
+    out = mb.gemm_w4a4(ac, asf, bc, bsf, 1.0, m, n, k, out_dtype=torch.float32)
+    got = out.cpu().numpy()
+    assert np.array_equal(got, ref), f"max abs err {np.abs(got - ref).max()}"
+
+
+@pytest.mark.parametrize("m,n,k", [(16, 4096, 4096), (128, 256, 4096), (1000, 1280, 2048)])
+def test_project_w4a4_against_same_operand_f64(mb, orc, m, n, k):
+    wbits = f32_to_bf16_bits(orc.normal_f32(2, n * k, 0.02))
+    xbits = f32_to_bf16_bits(orc.normal_f32(1, m * k, 1.0))
+    q = mb.Nvfp4.quantize(dev_bf16(wbits).view(n, k))
+    x = dev_bf16(xbits).view(1, m, k)
+    y = q.project(x, mb.PromptLane.W4A4)
+    assert tuple(y.shape) == (1, m, n)
+    # oracle: the same quantised operands, f64 accumulation, one rounding
+    a_codes, a_scales = orc.quantize_act_scaled(bf16_bits_to_f32(xbits), m, k, 1.0)
+    codes, scales = q.read_planes()
+    ref = orc.linear_w4a4(a_codes, a_scales, codes, scales, np.float32(q.scale2), m, n, k)
+    got = bf16_bits_to_f32(host_bits(y)).reshape(m, n)
+    rel, cos = rel_check(got, ref)
+    assert rel <= 1e-2 and cos >= 0.9999, (rel, cos)
+    # f32 output: the reference's own gate is 1e-4 relative vs f64 of the same operands
+    # (src/bin/inkling_fp4_expert_gate.rs:16-28)
+    a_c, a_sf, _ = mb.quantize_act(x.view(m, k), tiled=True)
+    out32 = mb.gemm_w4a4(a_c, a_sf, q.codes, q.sf_tiled(), q.scale2, m, n, k, out_dtype=torch.float32).cpu().numpy()
+    scale = np.sqrt(np.mean(ref.astype(np.float64) ** 2))
+    assert np.abs(out32 - ref).max() <= 1e-4 * scale * 8
+
+
+def test_project_w4a4_rows_and_scaled(mb, orc):
+    m, n, k = 150, 512, 1024
+    wbits = f32_to_bf16_bits(orc.normal_f32(12, n * k, 0.02))
+    x32 = orc.normal_f32(13, m * k, 1.0).reshape(m, k)
+    x32[7] *= 1e-3
+    x32[9] = 0.0
+    xbits = f32_to_bf16_bits(x32)
+    q = mb.Nvfp4.quantize(dev_bf16(wbits).view(n, k))
+    x = dev_bf16(xbits).view(1, m, k)
+    codes, scales = q.read_planes()
+    wide = bf16_bits_to_f32(xbits)
+    # rows lane
+    y = q.project_w4a4_rows(x)
+    a_codes, a_scales, rs = orc.quantize_act_rows(wide, m, k)
+    ref = orc.linear_w4a4(a_codes, a_scales, codes, scales, np.float32(q.scale2), m, n, k, rowscale=rs)
+    got = bf16_bits_to_f32(host_bits(y)).reshape(m, n)
+    rel, cos = rel_check(got, ref)
+    assert rel <= 1e-2 and cos >= 0.9999, (rel, cos)
+    assert not got[9].any()
+    # calibrated global
+    y = q.project_w4a4_scaled(x, 0.05)
+    a_codes, a_scales = orc.quantize_act_scaled(wide, m, k, 0.05)
+    alpha = np.float32(np.float32(q.scale2) * np.float32(0.05))
+    ref = orc.linear_w4a4(a_codes, a_scales, codes, scales, alpha, m, n, k)
+    rel, cos = rel_check(bf16_bits_to_f32(host_bits(y)).reshape(m, n), ref)
+    assert rel <= 1e-2 and cos >= 0.9999, (rel, cos)
+    from maryml_b200 import MaryError
+    with pytest.raises(MaryError):
+        q.project_w4a4_scaled(x, float("nan"))
+    with pytest.raises(MaryError):
+        q.project_w4a4_scaled(x, 0.0)
+
+
+def test_w4a4_rows_nan_row_poisons_only_itself(mb, orc):
+    # src/nn/nvfp4_gemm.rs:1123-1166
+    m, n, k = 40, 256, 256
+    w = torch.randn(n, k, device="cuda").to(torch.bfloat16) * 0.02
+    q = mb.Nvfp4.quantize(w)
+    x = torch.randn(1, m, k, device="cuda").to(torch.bfloat16)
+    clean = q.project_w4a4_rows(x).clone()
+    x2 = x.clone()
+    x2[0, 17, 5] = float("nan")
+    dirty = q.project_w4a4_rows(x2)
+    assert torch.isnan(dirty[0, 17]).all()
+    keep = [i for i in range(m) if i != 17]
+    assert torch.equal(dirty[0, keep].view(torch.int16), clean[0, keep].view(torch.int16))
+
+
+@pytest.mark.parametrize("m,n,k", [(128, 128, 64), (200, 264, 1032), (512, 1024, 2048)])
+def test_bf16_gemm_against_f64(mb, orc, m, n, k):
+    abits = f32_to_bf16_bits(orc.normal_f32(31, m * k, 1.0))
+    bbits = f32_to_bf16_bits(orc.normal_f32(32, n * k, 0.02))
+    ref = orc.linear_bf16(abits, bbits, m, n, k)
+    out = mb.bf16_gemm(dev_bf16(abits).view(m, k), dev_bf16(bbits).view(n, k), out_dtype=torch.float32).cpu().numpy()
+    scale = np.sqrt(np.mean(ref.astype(np.float64) ** 2))
+    assert np.abs(out - ref).max() <= 2e-5 * scale * np.sqrt(k / 64)
+    rel, cos = rel_check(out, ref)
+    assert rel <= 1e-2 and cos >= 0.9999
+
+
+def test_project_w4a16_and_linear_dispatch(mb, orc):
+    m, n, k = 41, 512, 1024
+    wbits = f32_to_bf16_bits(orc.normal_f32(41, n * k, 0.02))
+    xbits = f32_to_bf16_bits(orc.normal_f32(42, m * k, 1.0))
+    q = mb.Nvfp4.quantize(dev_bf16(wbits).view(n, k))
+    x = dev_bf16(xbits).view(1, m, k)
+    y = mb.linear(x, q)  # 41 rows -> prompt lane, default W4A16
+    codes, scales = q.read_planes()
+    ref = orc.linear_w4a16(xbits, codes, scales, q.scale2, m, n, k)
+    got = bf16_bits_to_f32(host_bits(y)).reshape(m, n)
+    # the reference's bound for this lane: relative rms below 4e-3 (src/models/breeze/nvfp4.rs:339-380)
+    assert np.sqrt(np.mean((got - ref) ** 2)) / np.sqrt(np.mean(ref ** 2)) < 4e-3
+    y8 = mb.linear(x[:, :8].contiguous(), q)  # 8 rows -> the GEMV
+    assert np.sqrt(np.mean((bf16_bits_to_f32(host_bits(y8)).reshape(8, n) - ref[:8]) ** 2)) / np.sqrt(np.mean(ref[:8] ** 2)) < 4e-3
+
+
+def test_full_size_linearity_property(mb, orc):
+    """At the benchmark's full shape the oracle is too slow; the size-independent property is
+    linearity in the weight's global scale and agreement of the W4A4 lane with the dequantised
+    bf16 tensor-core product of the same quantised operands."""
+    m, n, k = 1024, 4096, 4096
+    w = (torch.randn(n, k, device="cuda") * 0.02).to(torch.bfloat16)
+    x = torch.randn(m, k, device="cuda").to(torch.bfloat16)
+    q = mb.Nvfp4.quantize(w)
+    a_c, a_sf, _ = mb.quantize_act(x, tiled=True)
+    y1 = mb.gemm_w4a4(a_c, a_sf, q.codes, q.sf_tiled(), q.scale2, m, n, k, out_dtype=torch.float32)
+    y2 = mb.gemm_w4a4(a_c, a_sf, q.codes, q.sf_tiled(), 2.0 * q.scale2, m, n, k, out_dtype=torch.float32)
+    assert torch.equal(y2, 2.0 * y1)
+    a_sf_rm = mb.untile_scales(a_sf, m, k)
+    xa = mb.dequantize(a_c, a_sf_rm, 1.0, m, k, dtype=torch.bfloat16)
+    wb = mb.dequantize(q.codes, q.scales, 1.0, n, k, dtype=torch.bfloat16)
+    y3 = mb.bf16_gemm(xa, wb, out_dtype=torch.float32, alpha=q.scale2)
+    err = (y1 - y3).abs().max().item()
+    assert err <= 1e-4 * y3.abs().max().item() + 1e-6
