@@ -1,0 +1,333 @@
+#!/usr/bin/env python
+"""Benchmark of the NVFP4 linear hot path (BASELINE.json metric: NVFP4 GEMM TFLOPS).
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+One "step" is one pass of the W4A4 prompt projection (`Nvfp4.project(x, W4A4)`: device
+activation quantizer + tcgen05 block-scaled GEMM) over one batch of synthetic
+activations at M = 8192 for the three projection shapes of the sweep,
+(K, N) in {(4096, 4096), (4096, 14336), (14336, 4096)}. Inputs are seeded N(0, 1)
+activations and N(0, 0.02) weights quantised once to NVFP4; they stand in for real
+checkpoints (none exist offline) and are larger than L2 (126 MB) per step.
+
+`value` is TFLOP/s with inputs resident in HBM; `e2e` runs the same step from pinned
+host activations to pinned host outputs through the public API. `roofline` is the
+GEMM kernel alone (CUDA events around each launch); `cpu_baseline` is the CPU oracle's
+restatement of the reference's CPU lane timed on a bounded sample.
+
+With N > 1 (torchrun) every rank runs an independent replica of the step: the GEMM
+sweep does not shard (no collective on this path), so scaling is weak.
+"""
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+SHAPES = [(4096, 4096), (4096, 14336), (14336, 4096)]   # (K, N)
+M = 8192
+WORKLOAD = "nvfp4_w4a4_linear_prefill_M8192_KN{4096x4096,4096x14336,14336x4096}"
+NOMINAL_FP4_TFLOPS = 9000.0
+
+
+def step_flops(m=M):
+    return sum(2.0 * m * n * k for (k, n) in SHAPES)
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            p = json.load(f)
+        return {"hbm_gbs": p["hbm_gbs"], "bf16": p["bf16_tflops"], "bf16_sustained": p["bf16_tflops_sustained"],
+                "source": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16": 1590.0, "bf16_sustained": 1400.0, "source": "fallback"}
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi during the timed region."""
+
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+         "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index):
+        self.gpu = gpu_index
+        self.proc = None
+        self.lines = []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--id={self.gpu}", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "100"],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._pump, daemon=True).start()
+        except Exception:
+            self.proc = None
+
+    def _pump(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["unsampled"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=2)
+        except Exception:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for ln in self.lines:
+            f = [x.strip() for x in ln.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1]))
+                mx.append(float(f[2]))
+            except ValueError:
+                continue
+            for name, val in zip(names, f[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        if not sm:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["unsampled"]}
+        return {"sm_mhz": float(np.median(sm)), "sm_max_mhz": float(max(mx)), "reasons": sorted(reasons),
+                "samples": len(sm)}
+
+
+# --------------------------------------------------------------------------------------
+# CPU arm: the oracle's restatement of the reference's CPU lane (decode to dense f32,
+# f32 matmul, bf16 result) on a bounded sample of the same workload.
+# --------------------------------------------------------------------------------------
+def cpu_lane(sample_rows, threads=None, repeats=1):
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    from oracle_lib import oracle, f32_to_bf16_bits
+    orc = oracle()
+    if threads:
+        orc.set_threads(threads)
+    cores = orc.threads()
+    rng = np.random.default_rng(0)
+    planes = []
+    for (k, n) in SHAPES:
+        w = (rng.standard_normal(n * k, dtype=np.float32) * np.float32(0.02))
+        codes, scales, s2 = orc.pack_nearest(w, k)
+        t0 = time.perf_counter()
+        dense = orc.dequantize(codes, scales, s2)
+        planes.append((k, n, dense, time.perf_counter() - t0))
+    xs = {k: f32_to_bf16_bits(rng.standard_normal(sample_rows * k, dtype=np.float32)) for k in (4096, 14336)}
+    times = []
+    for _ in range(repeats):
+        t0 = time.perf_counter()
+        for (k, n, dense, _) in planes:
+            orc.linear_cpu_lane(xs[k], dense, sample_rows, n, k)
+        times.append(time.perf_counter() - t0)
+    flops = step_flops(sample_rows)
+    decode_s = sum(p[3] for p in planes)
+    return {"seconds": times, "flops": flops, "cores": cores, "decode_s": decode_s,
+            "sample": f"first {sample_rows} of {M} activation rows over the three (K,N) shapes; dense f32 decode of "
+                      f"the weights ({decode_s:.2f} s, once, untimed) then f32 matmul with bf16 result"}
+
+
+def run_reference(args, rank, world):
+    if rank != 0:
+        return
+    sample_rows = 64
+    for _ in range(args.warmup):
+        pass  # the CPU lane has no cold caches worth warming beyond its first repeat below
+    res = cpu_lane(sample_rows, repeats=max(1, args.steps))
+    secs = res["seconds"]
+    total = sum(secs)
+    tflops = res["flops"] * len(secs) / total / 1e12
+    line = {
+        "impl": "reference", "metric": "nvfp4_gemm_tflops", "value": tflops, "unit": "TFLOP/s", "n_gpus": args.gpus,
+        "steps": len(secs), "warmup": args.warmup, "ms_per_step": 1e3 * total / len(secs), "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "f32 (dequantised e2m1 x e4m3 weights, bf16 activations)",
+        "data": "synthetic", "config": {"workload": WORKLOAD, "sample_rows": sample_rows},
+        "cpu_baseline": {"value": tflops, "unit": "TFLOP/s", "cores": res["cores"], "kind": "port",
+                         "sample": res["sample"]},
+        "e2e": {"value": tflops, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+# --------------------------------------------------------------------------------------
+# GPU arm
+# --------------------------------------------------------------------------------------
+def run_ours(args, rank, world, local_rank):
+    import torch
+    import torch.distributed as dist
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py: no CUDA device; the library has no CPU fallback")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    import maryml_b200  # noqa: F401  (fails loudly if the CUDA library is missing)
+    from maryml_b200 import nvfp4 as mb, _lib
+    ctx = _lib.context(local_rank)
+
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    g = torch.Generator(device=dev)
+    g.manual_seed(1234 + rank)
+    weights, acts, outs = [], {}, []
+    for (k, n) in SHAPES:
+        w = (torch.randn(n, k, device=dev, generator=g) * 0.02).to(torch.bfloat16)
+        q = mb.Nvfp4.quantize(w)
+        q.sf_tiled()
+        weights.append(q)
+        del w
+        outs.append(torch.empty(M, n, dtype=torch.bfloat16, device=dev))
+    for k in (4096, 14336):
+        acts[k] = torch.randn(M, k, device=dev, generator=g).to(torch.bfloat16)
+    # preallocated activation planes: the step allocates nothing
+    a_codes = {k: torch.empty(M, k // 2, dtype=torch.uint8, device=dev) for k in acts}
+    a_sf = {k: torch.empty(mb.sf_bytes(M, k), dtype=torch.uint8, device=dev) for k in acts}
+    stream = torch.cuda.current_stream()
+    sp = lambda t: t.data_ptr()
+    lib = _lib.lib
+    gemm_events = []
+
+    def step(record=False):
+        for q, out in zip(weights, outs):
+            k, n = q.k(), q.n()
+            x = acts[k]
+            ctx.check(lib.mb_nvfp4_quantize_act(ctx.handle, stream.cuda_stream, sp(x), _lib.DT_BF16, M, k,
+                                                _lib.QUANT_SCALED, 1.0, None, 0, sp(a_codes[k]), sp(a_sf[k]),
+                                                _lib.SF_TILED, None))
+            if record:
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record(stream)
+            ctx.check(lib.mb_nvfp4_gemm_w4a4(ctx.handle, stream.cuda_stream, sp(a_codes[k]), sp(a_sf[k]), sp(q.codes),
+                                             sp(q.sf_tiled()), None, q.scale2, M, n, k, sp(out), _lib.DT_BF16,
+                                             _lib.EPI_PLAIN))
+            if record:
+                e1.record(stream)
+                gemm_events.append((e0, e1, 2.0 * M * n * k))
+
+    # launches per step: 3 x (memset of the scale plane is a driver memset, not ours) quantize + gemm
+    launches_per_step = 2 * len(SHAPES)
+
+    for _ in range(max(args.warmup, 3)):
+        step()
+    barrier()
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    t0 = torch.cuda.Event(enable_timing=True)
+    t1 = torch.cuda.Event(enable_timing=True)
+    t0.record(stream)
+    for _ in range(args.steps):
+        step(record=True)
+    t1.record(stream)
+    barrier()
+    clocks = sampler.stop() if rank == 0 else None
+    ms = t0.elapsed_time(t1)
+    if world > 1:
+        tms = torch.tensor([ms], device=dev)
+        dist.all_reduce(tms, op=dist.ReduceOp.MAX)
+        ms = float(tms.item())
+    rc, flags = ctx.check_flags(None)
+    if rc != 0:
+        raise SystemExit(f"bench.py: device status words set: {flags}")
+
+    # kernel-only roofline of the GEMM launches (CUDA events on the launching stream)
+    gemm_ms = sum(e0.elapsed_time(e1) for (e0, e1, _) in gemm_events)
+    gemm_fl = sum(f for (_, _, f) in gemm_events)
+    achieved = gemm_fl / (gemm_ms * 1e-3) / 1e12
+    peaks = measured_peaks()
+    fp4_peak = 4.0 * peaks["bf16"]
+
+    # end to end: pinned host activations in, pinned host outputs back, every step
+    h_x = {k: torch.empty(M, k, dtype=torch.bfloat16).pin_memory() for k in acts}
+    for k in acts:
+        h_x[k].copy_(acts[k])
+    h_y = [torch.empty(M, q.n(), dtype=torch.bfloat16).pin_memory() for q in weights]
+    d_x = {k: torch.empty_like(acts[k]) for k in acts}
+
+    def e2e_step():
+        for q, out, hy in zip(weights, outs, h_y):
+            k = q.k()
+            d_x[k].copy_(h_x[k], non_blocking=True)
+            y = q.project(d_x[k], mb.PromptLane.W4A4)
+            hy.copy_(y.view(M, q.n()), non_blocking=True)
+
+    e2e_steps = max(2, min(args.steps, 5))
+    e2e_step()
+    barrier()
+    s0 = torch.cuda.Event(enable_timing=True)
+    s1 = torch.cuda.Event(enable_timing=True)
+    s0.record(stream)
+    for _ in range(e2e_steps):
+        e2e_step()
+    s1.record(stream)
+    barrier()
+    e2e_ms = s0.elapsed_time(s1)
+    if world > 1:
+        tms = torch.tensor([e2e_ms], device=dev)
+        dist.all_reduce(tms, op=dist.ReduceOp.MAX)
+        e2e_ms = float(tms.item())
+    h2d = sum(M * q.k() * 2 for q in weights)
+    d2h = sum(M * q.n() * 2 for q in weights)
+
+    if rank == 0:
+        cpu = cpu_lane(32, repeats=1)
+        cpu_tflops = cpu["flops"] / cpu["seconds"][0] / 1e12
+        value = world * step_flops() * args.steps / (ms * 1e-3) / 1e12
+        line = {
+            "metric": "nvfp4_gemm_tflops", "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
+            "warmup": max(args.warmup, 3), "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "e2m1 x e2m1 (ue4m3 block scales), f32 accumulate, bf16 out",
+            "data": "synthetic",
+            "config": {"workload": WORKLOAD, "M": M, "KN": SHAPES, "lane": "W4A4 input_scale=1",
+                       "parallelism": f"replicas x{world}", "l2": "inputs+outputs per step exceed L2 (126 MB)"},
+            "clocks": clocks,
+            "e2e": {"value": world * step_flops() * e2e_steps / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s",
+                    "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
+            "gpu_launches": launches_per_step * args.steps,
+            "roofline": {"bound": "tensor", "kernel": "gemm_tc5_kernel<NVF4,256>", "achieved": achieved,
+                         "peak": fp4_peak, "unit": "TFLOP/s", "frac": achieved / fp4_peak,
+                         "peak_source": f"4 x {peaks['source']} bf16 burst ({peaks['bf16']} TFLOP/s): no FP4 figure "
+                                        f"in MEASURED_PEAKS.json",
+                         "frac_of_nominal_9pf": achieved / NOMINAL_FP4_TFLOPS, "traffic": None},
+            "cpu_baseline": {"value": cpu_tflops, "unit": "TFLOP/s", "cores": cpu["cores"], "kind": "port",
+                             "sample": cpu["sample"]},
+        }
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    args = ap.parse_args()
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.impl == "reference":
+        run_reference(args, rank, world)
+    else:
+        run_ours(args, rank, world, local_rank)
+
+
+if __name__ == "__main__":
+    main()

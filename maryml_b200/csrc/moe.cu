@@ -1,0 +1,328 @@
+// MoE routing: softmax top-k router, the stacked-row plan (token permutation) and
+// the ordered weighted un-permute. All HBM/latency-bound integer and f32 work:
+// warp-shuffle reductions, 128-bit accesses, no atomics on the data path (the
+// row order is deterministic: expert-ascending, then token-ascending).
+#include "common.cuh"
+
+namespace {
+
+// ---------------------------------------------------------------------------------
+// Router. One warp per token, expert e lives in lane e % 32, slot e / 32.
+// Scores follow the CPU rule exactly: m = max logit; e_i = exp(f64(x_i) - m);
+// v_i = f32(e_i); s = sum of e_i in index order (f64); score_i = f32(f64(v_i) / s).
+// Selection: descending score, ties to the lower index. Weights: gathered scores,
+// w / (sum + 1e-20) in selection order, times the scaling factor.
+// ---------------------------------------------------------------------------------
+template <int EPL>
+__global__ void __launch_bounds__(128)
+router_softmax_topk_kernel(const float* __restrict__ logits, uint32_t tokens, uint32_t n_experts, uint32_t k,
+                           int renormalize, float scaling, int32_t* __restrict__ idx, float* __restrict__ weight,
+                           int* __restrict__ flag) {
+  const uint32_t lane = threadIdx.x & 31;
+  const uint32_t t = blockIdx.x * 4 + (threadIdx.x >> 5);
+  if (t >= tokens) return;
+  const float* row = logits + size_t(t) * n_experts;
+  float x[EPL];
+  double e[EPL];
+  bool bad = false;
+  double m = -INFINITY;
+#pragma unroll
+  for (int j = 0; j < EPL; ++j) {
+    x[j] = row[lane + 32 * j];
+    if (!(fabsf(x[j]) <= 3.4028234663852886e38f)) bad = true;
+    m = fmax(m, double(x[j]));
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) m = fmax(m, __shfl_xor_sync(0xFFFFFFFFu, m, o));
+  if (__any_sync(0xFFFFFFFFu, bad)) {
+    if (lane == 0) atomicCAS(flag, 0, int(t) + 1);
+  }
+  float v[EPL];
+#pragma unroll
+  for (int j = 0; j < EPL; ++j) {
+    e[j] = exp(double(x[j]) - m);
+    v[j] = float(e[j]);
+  }
+  // Sum in expert-index order: expert i sits in lane i % 32, slot i / 32.
+  double s = 0.0;
+#pragma unroll
+  for (int j = 0; j < EPL; ++j) {
+#pragma unroll 8
+    for (int l = 0; l < 32; ++l) s += __shfl_sync(0xFFFFFFFFu, e[j], l);
+  }
+#pragma unroll
+  for (int j = 0; j < EPL; ++j) v[j] = float(double(v[j]) / s);
+
+  // k rounds of warp arg-max on (score desc, index asc).
+  uint32_t taken = 0;   // bit j: slot j of this lane already selected
+  float wsum = 0.0f;
+  float my_w = 0.0f;    // lane r keeps the weight of pick r (k <= 32)
+  int my_i = 0;
+  for (uint32_t r = 0; r < k; ++r) {
+    float best = -INFINITY;
+    uint32_t best_i = 0xFFFFFFFFu;
+#pragma unroll
+    for (int j = 0; j < EPL; ++j) {
+      uint32_t i = lane + 32 * j;
+      bool free_slot = !((taken >> j) & 1u);
+      if (free_slot && (v[j] > best || (v[j] == best && i < best_i) || best_i == 0xFFFFFFFFu)) {
+        best = v[j];
+        best_i = i;
+      }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      float ob = __shfl_xor_sync(0xFFFFFFFFu, best, o);
+      uint32_t oi = __shfl_xor_sync(0xFFFFFFFFu, best_i, o);
+      if (oi != 0xFFFFFFFFu && (best_i == 0xFFFFFFFFu || ob > best || (ob == best && oi < best_i))) {
+        best = ob;
+        best_i = oi;
+      }
+    }
+    if ((best_i & 31u) == lane) taken |= 1u << (best_i >> 5);
+    wsum += best;   // selection order, as the CPU rule sums
+    if (lane == r) { my_w = best; my_i = int(best_i); }
+  }
+  if (k > 1 && renormalize) my_w = __fdiv_rn(my_w, wsum + 1e-20f);
+  if (scaling != 1.0f) my_w *= scaling;
+  if (lane < k) {
+    idx[size_t(t) * k + lane] = my_i;
+    weight[size_t(t) * k + lane] = my_w;
+  }
+}
+
+// ---------------------------------------------------------------------------------
+// Row plan
+// ---------------------------------------------------------------------------------
+constexpr int PLAN_PAD = 128;   // rows per GEMM tile: each expert's rows are padded to this
+
+// counts[e] = picks of expert e; checks range and per-token duplicates.
+__global__ void __launch_bounds__(256)
+plan_count_kernel(const int32_t* __restrict__ idx, uint32_t tokens, uint32_t k, uint32_t n_experts,
+                  int32_t* __restrict__ counts, int* __restrict__ flag) {
+  uint32_t t = blockIdx.x * 256 + threadIdx.x;
+  if (t >= tokens) return;
+  const int32_t* p = idx + size_t(t) * k;
+  for (uint32_t j = 0; j < k; ++j) {
+    int32_t e = p[j];
+    bool ok = e >= 0 && uint32_t(e) < n_experts;
+    for (uint32_t i = 0; ok && i < j; ++i) ok = p[i] != e;
+    if (!ok) { atomicCAS(flag, 0, int(t) + 1); continue; }
+    atomicAdd(counts + e, 1);
+  }
+}
+
+// One block: exclusive scan of the padded counts -> first stacked row of each
+// expert, the expert of each 128-row tile, the number of tiles in use.
+__global__ void __launch_bounds__(1024)
+plan_scan_kernel(const int32_t* __restrict__ counts, uint32_t n_experts, int32_t* __restrict__ expert_rows,
+                 int32_t* __restrict__ expert_row0, int32_t* __restrict__ tile_expert, uint32_t tile_cap,
+                 int32_t* __restrict__ n_tiles) {
+  __shared__ int32_t s_pad[1024];
+  __shared__ int32_t s_off[1024];
+  uint32_t e = threadIdx.x;
+  int32_t c = e < n_experts ? counts[e] : 0;
+  s_pad[e] = (c + PLAN_PAD - 1) / PLAN_PAD;   // tiles of this expert
+  __syncthreads();
+  if (e == 0) {
+    int32_t run = 0;
+    for (uint32_t i = 0; i < n_experts; ++i) { s_off[i] = run; run += s_pad[i]; }
+    *n_tiles = run;
+  }
+  __syncthreads();
+  if (e < n_experts) {
+    expert_rows[e] = c;
+    expert_row0[e] = s_off[e] * PLAN_PAD;
+    for (int32_t i = 0; i < s_pad[e]; ++i)
+      if (uint32_t(s_off[e] + i) < tile_cap) tile_expert[s_off[e] + i] = int32_t(e);
+  }
+}
+
+// One block per expert walks the tokens in order; a token that picked the expert
+// takes the next stacked row. Deterministic: expert-ascending, token-ascending.
+__global__ void __launch_bounds__(256)
+plan_place_kernel(const int32_t* __restrict__ idx, const float* __restrict__ weight, uint32_t tokens, uint32_t k,
+                  const int32_t* __restrict__ expert_row0, int32_t* __restrict__ row_tok,
+                  float* __restrict__ row_wgt, int32_t* __restrict__ tok_rows) {
+  const int32_t e = blockIdx.x;
+  const uint32_t lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  __shared__ int32_t s_warp[8];
+  __shared__ int32_t s_base;
+  if (threadIdx.x == 0) s_base = expert_row0[e];
+  __syncthreads();
+  for (uint32_t t0 = 0; t0 < tokens; t0 += 256) {
+    uint32_t t = t0 + threadIdx.x;
+    int hit = -1;
+    if (t < tokens) {
+      const int32_t* p = idx + size_t(t) * k;
+      for (uint32_t j = 0; j < k; ++j)
+        if (p[j] == e) { hit = int(j); break; }
+    }
+    uint32_t ballot = __ballot_sync(0xFFFFFFFFu, hit >= 0);
+    if (lane == 0) s_warp[warp] = __popc(ballot);
+    __syncthreads();
+    int32_t before = 0, total = 0;
+    for (int w = 0; w < 8; ++w) {
+      if (w < int(warp)) before += s_warp[w];
+      total += s_warp[w];
+    }
+    if (hit >= 0) {
+      int32_t row = s_base + before + __popc(ballot & ((1u << lane) - 1u));
+      row_tok[row] = int32_t(t);
+      row_wgt[row] = weight[size_t(t) * k + hit];
+      tok_rows[size_t(t) * k + hit] = row;
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) s_base += total;
+    __syncthreads();
+  }
+}
+
+// Each token's k rows, ascending (the order its experts were stacked in).
+__global__ void __launch_bounds__(256)
+plan_sort_kernel(int32_t* __restrict__ tok_rows, uint32_t tokens, uint32_t k) {
+  uint32_t t = blockIdx.x * 256 + threadIdx.x;
+  if (t >= tokens) return;
+  int32_t* p = tok_rows + size_t(t) * k;
+  for (uint32_t i = 1; i < k; ++i) {
+    int32_t v = p[i];
+    int j = int(i) - 1;
+    while (j >= 0 && p[j] > v) { p[j + 1] = p[j]; --j; }
+    p[j + 1] = v;
+  }
+}
+
+// out[t, c..c+7] = sum_j fma(y[row_j, c..c+7], wgt[row_j], acc), rows ascending.
+template <typename Y>
+__global__ void __launch_bounds__(256)
+scatter_weighted_kernel(const Y* __restrict__ y, const float* __restrict__ row_wgt,
+                        const int32_t* __restrict__ tok_rows, uint32_t tokens, uint32_t k, uint32_t h,
+                        float* __restrict__ out) {
+  const uint32_t per_tok = h / 8;
+  size_t gid = size_t(blockIdx.x) * 256 + threadIdx.x;
+  if (gid >= size_t(tokens) * per_tok) return;
+  uint32_t t = uint32_t(gid / per_tok), c = uint32_t(gid % per_tok) * 8;
+  float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+  for (uint32_t j = 0; j < k; ++j) {
+    int32_t r = tok_rows[size_t(t) * k + j];
+    if (r < 0) continue;
+    float w = row_wgt[r];
+    float v[8];
+    if (sizeof(Y) == 2) {
+      uint4 q = __ldg(reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(y) + size_t(r) * h + c));
+      uint32_t ww[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        v[2 * i] = __uint_as_float(ww[i] << 16);
+        v[2 * i + 1] = __uint_as_float(ww[i] & 0xFFFF0000u);
+      }
+    } else {
+      const float4* q = reinterpret_cast<const float4*>(reinterpret_cast<const float*>(y) + size_t(r) * h + c);
+      float4 a = __ldg(q), b = __ldg(q + 1);
+      v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+    }
+#pragma unroll
+    for (int i = 0; i < 8; ++i) acc[i] = fmaf(v[i], w, acc[i]);
+  }
+  float4* o = reinterpret_cast<float4*>(out + size_t(t) * h + c);
+  o[0] = make_float4(acc[0], acc[1], acc[2], acc[3]);
+  o[1] = make_float4(acc[4], acc[5], acc[6], acc[7]);
+}
+
+}  // namespace
+
+MB_API int mb_router_topk_softmax(mb_ctx* ctx, mb_stream stream_, const float* logits, size_t tokens,
+                                  size_t n_experts, size_t k, int renormalize, float scaling, int32_t* idx,
+                                  float* weight) {
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  MB_REQUIRE(ctx, ctx && logits && idx && weight, "router: null argument");
+  MB_REQUIRE(ctx, tokens > 0, "router: select() on zero tokens");
+  MB_REQUIRE(ctx, n_experts >= 32 && n_experts % 32 == 0 && n_experts <= 512,
+             "router: n_experts must be a multiple of 32 up to 512, got %zu", n_experts);
+  MB_REQUIRE(ctx, k >= 1 && k <= 32 && k <= n_experts, "router: top_k must be 1..32, got %zu", k);
+  unsigned grid = unsigned((tokens + 3) / 4);
+  int* flag = ctx->flags_dev + MB_FLAG_ROUTER_NONFINITE;
+#define ROUTE(EPL)                                                                                            \
+  router_softmax_topk_kernel<EPL><<<grid, 128, 0, stream>>>(logits, uint32_t(tokens), uint32_t(n_experts),   \
+                                                            uint32_t(k), renormalize, scaling, idx, weight, flag)
+  switch (n_experts / 32) {
+    case 1: ROUTE(1); break;
+    case 2: ROUTE(2); break;
+    case 3: ROUTE(3); break;
+    case 4: ROUTE(4); break;
+    case 6: ROUTE(6); break;
+    case 8: ROUTE(8); break;
+    case 12: ROUTE(12); break;
+    case 16: ROUTE(16); break;
+    default: return mb_fail(ctx, MB_ERR_INVALID, "router: unsupported expert count %zu", n_experts);
+  }
+#undef ROUTE
+  MB_LAUNCH_OK(ctx);
+  return MB_OK;
+}
+
+MB_API size_t mb_moe_plan_rows(size_t tokens, size_t k, size_t n_experts) {
+  size_t active = n_experts < tokens * k ? n_experts : tokens * k;
+  size_t worst = tokens * k + active * (PLAN_PAD - 1);
+  return (worst + PLAN_PAD - 1) / PLAN_PAD * PLAN_PAD;
+}
+
+MB_API size_t mb_moe_plan_workspace(size_t tokens, size_t k, size_t n_experts) {
+  (void)tokens; (void)k;
+  return n_experts * sizeof(int32_t);
+}
+
+MB_API int mb_moe_plan(mb_ctx* ctx, mb_stream stream_, const int32_t* idx, const float* weight, size_t tokens,
+                       size_t k, size_t n_experts, int32_t* row_tok, float* row_wgt, int32_t* tok_rows,
+                       int32_t* expert_rows, int32_t* expert_row0, int32_t* tile_expert, int32_t* n_tiles,
+                       void* workspace, size_t workspace_bytes) {
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  MB_REQUIRE(ctx, ctx && idx && weight && row_tok && row_wgt && tok_rows && expert_rows && expert_row0 && tile_expert &&
+                      n_tiles && workspace,
+             "moe_plan: null argument");
+  MB_REQUIRE(ctx, tokens > 0 && k >= 1 && k <= 32 && n_experts >= 1 && n_experts <= 1024,
+             "moe_plan: tokens > 0, 1 <= k <= 32, experts <= 1024");
+  MB_REQUIRE(ctx, workspace_bytes >= mb_moe_plan_workspace(tokens, k, n_experts), "moe_plan: workspace too small");
+  MB_REQUIRE(ctx, tokens * k < (1ull << 31), "moe_plan: exceeds i32 indexing");
+  size_t m_cap = mb_moe_plan_rows(tokens, k, n_experts);
+  int32_t* counts = static_cast<int32_t*>(workspace);
+  MB_CUDA_OK(ctx, cudaMemsetAsync(counts, 0, n_experts * 4, stream));
+  MB_CUDA_OK(ctx, cudaMemsetAsync(row_tok, 0xFF, m_cap * 4, stream));   // -1: pad rows carry no token
+  MB_CUDA_OK(ctx, cudaMemsetAsync(row_wgt, 0, m_cap * 4, stream));
+  MB_CUDA_OK(ctx, cudaMemsetAsync(tile_expert, 0xFF, (m_cap / PLAN_PAD) * 4, stream));
+  MB_CUDA_OK(ctx, cudaMemsetAsync(tok_rows, 0xFF, tokens * k * 4, stream));
+  int* flag = ctx->flags_dev + MB_FLAG_PLAN_FAULT;
+  plan_count_kernel<<<unsigned((tokens + 255) / 256), 256, 0, stream>>>(idx, uint32_t(tokens), uint32_t(k),
+                                                                         uint32_t(n_experts), counts, flag);
+  MB_LAUNCH_OK(ctx);
+  plan_scan_kernel<<<1, 1024, 0, stream>>>(counts, uint32_t(n_experts), expert_rows, expert_row0, tile_expert,
+                                           uint32_t(m_cap / PLAN_PAD), n_tiles);
+  MB_LAUNCH_OK(ctx);
+  plan_place_kernel<<<unsigned(n_experts), 256, 0, stream>>>(idx, weight, uint32_t(tokens), uint32_t(k), expert_row0,
+                                                             row_tok, row_wgt, tok_rows);
+  MB_LAUNCH_OK(ctx);
+  plan_sort_kernel<<<unsigned((tokens + 255) / 256), 256, 0, stream>>>(tok_rows, uint32_t(tokens), uint32_t(k));
+  MB_LAUNCH_OK(ctx);
+  return MB_OK;
+}
+
+MB_API int mb_moe_scatter_weighted(mb_ctx* ctx, mb_stream stream_, const void* y, int y_dtype, const float* row_wgt,
+                                   const int32_t* tok_rows, size_t tokens, size_t k, size_t h, float* out) {
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  MB_REQUIRE(ctx, ctx && y && row_wgt && tok_rows && out, "scatter_weighted: null argument");
+  MB_REQUIRE(ctx, tokens > 0 && k >= 1 && h > 0 && h % 8 == 0, "scatter_weighted: h must be a positive multiple of 8");
+  MB_REQUIRE(ctx, mb_aligned(y, 16) && mb_aligned(out, 16), "scatter_weighted: 16-byte alignment");
+  size_t total = tokens * (h / 8);
+  unsigned grid = unsigned((total + 255) / 256);
+  if (y_dtype == MB_DT_BF16)
+    scatter_weighted_kernel<__nv_bfloat16><<<grid, 256, 0, stream>>>(static_cast<const __nv_bfloat16*>(y), row_wgt,
+                                                                      tok_rows, uint32_t(tokens), uint32_t(k),
+                                                                      uint32_t(h), out);
+  else if (y_dtype == MB_DT_F32)
+    scatter_weighted_kernel<float><<<grid, 256, 0, stream>>>(static_cast<const float*>(y), row_wgt, tok_rows,
+                                                             uint32_t(tokens), uint32_t(k), uint32_t(h), out);
+  else
+    return mb_fail(ctx, MB_ERR_INVALID, "scatter_weighted: y is bf16 or f32");
+  MB_LAUNCH_OK(ctx);
+  return MB_OK;
+}
