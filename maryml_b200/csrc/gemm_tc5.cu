@@ -56,7 +56,7 @@ struct Cfg {
   static constexpr int SFB_BYTES = KIND == KIND_NVF4 ? (BN / 128) * 2048 : 0;
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES + SFA_BYTES + SFB_BYTES;
   static constexpr int STAGES = (KIND == KIND_NVF4) ? (BN == 256 ? 4 : 6) : (BN == 256 ? 4 : 6);
-  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*alignment*/ + 256 /*barriers*/;
+  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*alignment*/ + 256 /*barriers*/ + 8192 /*store patches*/;
   // TMEM columns
   static constexpr bool OVERLAP = (KIND == KIND_NVF4 && BN == 256);
   static constexpr int ACC0 = 0;
@@ -74,6 +74,32 @@ constexpr int EPI_THREADS = 128;
 __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
   __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
   return *reinterpret_cast<uint32_t*>(&v);
+}
+
+
+// Warp-level transpose through a 2 KB shared-memory patch so that global stores
+// are coalesced: on entry lane l holds U 16-byte units of ITS row (32 rows, U*16
+// bytes each); on exit every store instruction writes 32/U rows x U*16 contiguous
+// bytes (full 32-byte sectors). The XOR on the unit index keeps both the 128-bit
+// shared stores and loads bank-conflict free.
+template <int U>
+__device__ __forceinline__ void stage_and_store(uint8_t* patch, uint32_t lane, const uint4* units, uint8_t* gbase,
+                                                size_t row_stride_bytes, uint32_t rows_valid, uint32_t units_valid) {
+  constexpr int RPI = 32 / U;                     // rows per store instruction
+  const uint32_t swz_w = U == 4 ? ((lane >> 1) & 3u) : ((lane >> 2) & 1u);
+#pragma unroll
+  for (int u = 0; u < U; ++u)
+    *reinterpret_cast<uint4*>(patch + lane * (U * 16) + ((uint32_t(u) ^ swz_w) * 16)) = units[u];
+  __syncwarp();
+#pragma unroll
+  for (int i = 0; i < U; ++i) {
+    const uint32_t r = i * RPI + lane / U, u = lane % U;
+    const uint32_t swz_r = U == 4 ? ((r >> 1) & 3u) : ((r >> 2) & 1u);
+    uint4 v = *reinterpret_cast<const uint4*>(patch + r * (U * 16) + ((u ^ swz_r) * 16));
+    if (r < rows_valid && u < units_valid)
+      *reinterpret_cast<uint4*>(gbase + size_t(r) * row_stride_bytes + u * 16) = v;
+  }
+  __syncwarp();
 }
 
 template <int KIND, int BN>
@@ -94,7 +120,8 @@ gemm_tc5_kernel(const __grid_constant__ GemmParams p) {
   uint32_t* tmem_ptr_smem = reinterpret_cast<uint32_t*>(smem_gen + C::STAGES * C::STAGE_BYTES + 8 * (2 * C::STAGES + 6));
   volatile int* abort_smem = reinterpret_cast<volatile int*>(tmem_ptr_smem + 1);
 
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int warp = __shfl_sync(0xFFFFFFFFu, int(threadIdx.x >> 5), 0);   // warp-uniform by construction
+  const int lane = threadIdx.x & 31;
   int* tflag = p.flags ? p.flags + MB_FLAG_WAIT_TIMEOUT : nullptr;
 
   if (threadIdx.x == 0) {
@@ -119,31 +146,34 @@ gemm_tc5_kernel(const __grid_constant__ GemmParams p) {
   const uint32_t m_tiles = p.n_mtiles_dev ? uint32_t(*p.n_mtiles_dev) : p.m_tiles;
   const uint32_t total_tiles = m_tiles * p.n_tiles;
 
+  // The two issuing roles run with all 32 lanes converged; every asynchronous
+  // instruction (TMA, tcgen05.cp/mma/commit) sits under elect_one() so that the
+  // compiler sees a single active thread with warp-uniform operands.
   if (warp == 0) {
     // ------------------------------ producer ------------------------------------
-    if (lane == 0) {
-      int stage = 0;
-      uint32_t phase = 0;
-      uint32_t armed = 0;   // bit s: stage s armed at least once; parity of its last arming in armed_par
-      uint32_t armed_par = 0;
-      bool ok = true;
-      for (uint32_t tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
-        const uint32_t mt = tile % m_tiles, nt = tile / m_tiles;
-        uint32_t brow = nt * BN;
-        const uint8_t* sfb = p.sfb;
-        if (p.tile_expert) {
-          int e = p.tile_expert[mt];
-          if (e < 0) e = 0;
-          brow += uint32_t(e) * p.b_rows_per_expert;
-          sfb += uint64_t(e) * p.sfb_expert_stride;
-        }
-        for (uint32_t ks = 0; ks < p.k_steps; ++ks) {
-          if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_smem, tflag, 1)) { ok = false; break; }
-          const uint32_t sa = smem_base + stage * C::STAGE_BYTES;
-          const uint32_t sb = sa + C::A_BYTES;
+    int stage = 0;
+    uint32_t phase = 0;
+    uint32_t armed = 0;   // bit s: stage s armed at least once; parity of its last arming in armed_par
+    uint32_t armed_par = 0;
+    bool ok = true;
+    for (uint32_t tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
+      const uint32_t mt = tile % m_tiles, nt = tile / m_tiles;
+      uint32_t brow = nt * BN;
+      const uint8_t* sfb = p.sfb;
+      if (p.tile_expert) {
+        int e = p.tile_expert[mt];
+        if (e < 0) e = 0;
+        brow += uint32_t(e) * p.b_rows_per_expert;
+        sfb += uint64_t(e) * p.sfb_expert_stride;
+      }
+      for (uint32_t ks = 0; ks < p.k_steps; ++ks) {
+        if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_smem, tflag, 1)) { ok = false; break; }
+        const uint32_t sa = smem_base + stage * C::STAGE_BYTES;
+        const uint32_t sb = sa + C::A_BYTES;
+        armed |= 1u << stage;
+        armed_par = (armed_par & ~(1u << stage)) | (phase << stage);
+        if (elect_one()) {
           mbar_arrive_expect_tx(full_bar(stage), C::STAGE_BYTES);
-          armed |= 1u << stage;
-          armed_par = (armed_par & ~(1u << stage)) | (phase << stage);
           const int x = KIND == KIND_NVF4 ? int(ks * 128) : int(ks * 64);   // element coordinate (bytes / bf16)
           tma_load_2d(sa, &p.tmap_a, x, int(mt * C::BM), full_bar(stage));
           tma_load_2d(sb, &p.tmap_b, x, int(brow), full_bar(stage));
@@ -157,41 +187,42 @@ gemm_tc5_kernel(const __grid_constant__ GemmParams p) {
                         sfb + (uint64_t(nt * (BN / 128) + rt) * p.sf_kchunks + ks * 4u) * 512u, 2048u,
                         full_bar(stage));
           }
-          if (++stage == C::STAGES) { stage = 0; phase ^= 1u; }
         }
+        __syncwarp();
+        if (++stage == C::STAGES) { stage = 0; phase ^= 1u; }
       }
-      if (!ok) {
-        // Leave no copy in flight: wait (bounded) for every stage this thread armed.
-        for (int s = 0; s < C::STAGES; ++s)
-          if (armed & (1u << s)) {
-            long long t0 = clock64();
-            while (!mbar_try_wait(full_bar(s), (armed_par >> s) & 1u) && clock64() - t0 < WAIT_LIMIT_CYCLES) {}
-          }
-      }
+    }
+    if (!ok) {
+      // Leave no copy in flight: wait (bounded) for every stage this warp armed.
+      for (int s = 0; s < C::STAGES; ++s)
+        if (armed & (1u << s)) {
+          long long t0 = clock64();
+          while (!mbar_try_wait(full_bar(s), (armed_par >> s) & 1u) && clock64() - t0 < WAIT_LIMIT_CYCLES) {}
+        }
     }
   } else if (warp == 1) {
     // ------------------------------ MMA issuer ----------------------------------
-    if (lane == 0) {
-      int stage = 0;
-      uint32_t phase = 0;
-      const uint32_t idesc = KIND == KIND_NVF4 ? idesc_nvf4(BN) : idesc_bf16(BN);
-      uint32_t it = 0;
-      bool ok = true;
-      for (uint32_t tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x, ++it) {
-        const uint32_t buf = it & 1u;
-        if (C::OVERLAP) {
-          // The previous tile's epilogue has drained the 64 shared columns.
-          if (it > 0 && !mbar_wait(ovl_free_bar, (it - 1u) & 1u, abort_smem, tflag, 2)) { ok = false; break; }
-        } else {
-          if (!mbar_wait(acc_empty_bar(buf), ((it >> 1) & 1u) ^ 1u, abort_smem, tflag, 2)) { ok = false; break; }
-        }
+    int stage = 0;
+    uint32_t phase = 0;
+    const uint32_t idesc = KIND == KIND_NVF4 ? idesc_nvf4(BN) : idesc_bf16(BN);
+    uint32_t it = 0;
+    bool ok = true;
+    for (uint32_t tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x, ++it) {
+      const uint32_t buf = it & 1u;
+      if (C::OVERLAP) {
+        // The previous tile's epilogue has drained the 64 shared columns.
+        if (it > 0 && !mbar_wait(ovl_free_bar, (it - 1u) & 1u, abort_smem, tflag, 2)) { ok = false; break; }
+      } else {
+        if (!mbar_wait(acc_empty_bar(buf), ((it >> 1) & 1u) ^ 1u, abort_smem, tflag, 2)) { ok = false; break; }
+      }
+      fence_after_sync();
+      const uint32_t d_tmem = tmem_base + (buf ? C::ACC1 : C::ACC0);
+      for (uint32_t ks = 0; ks < p.k_steps; ++ks) {
+        if (!mbar_wait(full_bar(stage), phase, abort_smem, tflag, 3)) { ok = false; break; }
         fence_after_sync();
-        const uint32_t d_tmem = tmem_base + (buf ? C::ACC1 : C::ACC0);
-        for (uint32_t ks = 0; ks < p.k_steps; ++ks) {
-          if (!mbar_wait(full_bar(stage), phase, abort_smem, tflag, 3)) { ok = false; break; }
-          fence_after_sync();
-          const uint32_t sa = smem_base + stage * C::STAGE_BYTES;
-          const uint32_t sb = sa + C::A_BYTES;
+        const uint32_t sa = smem_base + stage * C::STAGE_BYTES;
+        const uint32_t sb = sa + C::A_BYTES;
+        if (elect_one()) {
           if (KIND == KIND_NVF4) {
             const uint32_t ssfa = sb + C::B_BYTES;
             const uint32_t ssfb = ssfa + C::SFA_BYTES;
@@ -217,21 +248,23 @@ gemm_tc5_kernel(const __grid_constant__ GemmParams p) {
               mma_f16(d_tmem, adesc + 2 * j, bdesc + 2 * j, idesc, acc);
           }
           umma_commit(empty_bar(stage));   // the stage is free once these MMAs have read it
-          if (++stage == C::STAGES) { stage = 0; phase ^= 1u; }
+          if (ks + 1 == p.k_steps) umma_commit(acc_full_bar(buf));
         }
-        if (ok) umma_commit(acc_full_bar(buf));
+        __syncwarp();
+        if (++stage == C::STAGES) { stage = 0; phase ^= 1u; }
       }
-      if (!ok) {
-        // Let the issued MMAs retire before TMEM is freed: one more commit, bounded wait.
-        umma_commit(drain_bar);
-        long long t0 = clock64();
-        while (!mbar_try_wait(drain_bar, 0u) && clock64() - t0 < WAIT_LIMIT_CYCLES) {}
-      }
+    }
+    if (!ok) {
+      // Let the issued MMAs retire before TMEM is freed: one more commit, bounded wait.
+      if (elect_one()) umma_commit(drain_bar);
+      __syncwarp();
+      long long t0 = clock64();
+      while (!mbar_try_wait(drain_bar, 0u) && clock64() - t0 < WAIT_LIMIT_CYCLES) {}
     }
   } else {
     // ------------------------------ epilogue ------------------------------------
     const uint32_t quad = warp & 3u;                  // TMEM lane quadrant this warp may read
-    const uint32_t row_in_tile = quad * 32u + lane;
+    uint8_t* patch = smem_gen + C::STAGES * C::STAGE_BYTES + 256 + quad * 2048;
     uint32_t it = 0;
     bool ok = true;
     for (uint32_t tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x, ++it) {
@@ -242,31 +275,20 @@ gemm_tc5_kernel(const __grid_constant__ GemmParams p) {
         int e = p.tile_expert[mt];
         alpha = e >= 0 ? p.alpha_vec[e] : 0.0f;
       }
-      const uint32_t row = mt * C::BM + row_in_tile;
-      const bool row_ok = row < p.m;
+      const uint32_t row0 = mt * C::BM + quad * 32u;       // first row of this warp's 32
+      const uint32_t row = row0 + lane;
+      const uint32_t rows_valid = row0 < p.m ? min(32u, p.m - row0) : 0u;
       float scale = alpha;
-      if (p.rowscale && row_ok) scale = p.rowscale[row] * alpha;
+      if (p.rowscale && row < p.m) scale = p.rowscale[row] * alpha;
       if (!mbar_wait(acc_full_bar(buf), (it >> 1) & 1u, abort_smem, tflag, 4)) { ok = false; break; }
       fence_after_sync();
       const uint32_t t_acc = tmem_base + ((quad * 32u) << 16) + (buf ? C::ACC1 : C::ACC0);
       constexpr int CHUNKS = BN / 32;
-#pragma unroll 1
-      for (int ci = 0; ci < CHUNKS; ++ci) {
-        // Overlap scheme: buffer 0 drains its last two chunks (the shared columns) first.
-        int c = ci;
-        if (C::OVERLAP && buf == 0) c = (ci + CHUNKS - 2) % CHUNKS;
-        uint32_t r[32];
-        tmem_ld_x32(t_acc + c * 32, r);
-        tmem_ld_wait();
-        if (C::OVERLAP && ci == 1) {
-          fence_before_sync();
-          mbar_arrive(ovl_free_bar);
-        }
+      auto process = [&](int c, const uint32_t* r) {
         const uint32_t col0 = nt * BN + c * 32;
-        if (!row_ok) continue;
+        if (col0 >= p.n) return;       // warp-uniform
         if (p.epilogue == MB_EPI_SWIGLU_INTERLEAVED) {
-          // (gate, up) pairs -> bf16(silu(bf16 gate) * bf16 up); 16 outputs per chunk.
-          __nv_bfloat16* o = static_cast<__nv_bfloat16*>(p.out) + size_t(row) * p.ldo + col0 / 2;
+          // (gate, up) pairs -> bf16(silu(bf16 gate) * bf16 up); 16 outputs = 2 units per row.
           uint32_t w[8];
 #pragma unroll
           for (int i = 0; i < 8; ++i) {
@@ -279,37 +301,63 @@ gemm_tc5_kernel(const __grid_constant__ GemmParams p) {
             }
             w[i] = pack_bf16x2(v[0], v[1]);
           }
-          if (col0 + 32 <= p.n) {
-            reinterpret_cast<uint4*>(o)[0] = make_uint4(w[0], w[1], w[2], w[3]);
-            reinterpret_cast<uint4*>(o)[1] = make_uint4(w[4], w[5], w[6], w[7]);
-          } else {
-            for (int i = 0; i < 8; ++i)
-              if (col0 + 4 * i + 4 <= p.n) reinterpret_cast<uint32_t*>(o)[i] = w[i];
-          }
+          uint4 units[2] = {make_uint4(w[0], w[1], w[2], w[3]), make_uint4(w[4], w[5], w[6], w[7])};
+          uint8_t* g = static_cast<uint8_t*>(p.out) + (size_t(row0) * p.ldo + col0 / 2) * 2;
+          stage_and_store<2>(patch, lane, units, g, size_t(p.ldo) * 2, rows_valid, min(2u, (p.n - col0) / 16));
         } else if (p.out_dtype == MB_DT_BF16) {
-          __nv_bfloat16* o = static_cast<__nv_bfloat16*>(p.out) + size_t(row) * p.ldo + col0;
+          uint4 units[4];
 #pragma unroll
           for (int g = 0; g < 4; ++g) {
-            if (col0 + g * 8 + 8 <= p.n) {
-              uint4 w;
-              w.x = pack_bf16x2(__uint_as_float(r[8 * g + 0]) * scale, __uint_as_float(r[8 * g + 1]) * scale);
-              w.y = pack_bf16x2(__uint_as_float(r[8 * g + 2]) * scale, __uint_as_float(r[8 * g + 3]) * scale);
-              w.z = pack_bf16x2(__uint_as_float(r[8 * g + 4]) * scale, __uint_as_float(r[8 * g + 5]) * scale);
-              w.w = pack_bf16x2(__uint_as_float(r[8 * g + 6]) * scale, __uint_as_float(r[8 * g + 7]) * scale);
-              reinterpret_cast<uint4*>(o)[g] = w;
-            }
+            units[g].x = pack_bf16x2(__uint_as_float(r[8 * g + 0]) * scale, __uint_as_float(r[8 * g + 1]) * scale);
+            units[g].y = pack_bf16x2(__uint_as_float(r[8 * g + 2]) * scale, __uint_as_float(r[8 * g + 3]) * scale);
+            units[g].z = pack_bf16x2(__uint_as_float(r[8 * g + 4]) * scale, __uint_as_float(r[8 * g + 5]) * scale);
+            units[g].w = pack_bf16x2(__uint_as_float(r[8 * g + 6]) * scale, __uint_as_float(r[8 * g + 7]) * scale);
           }
+          uint8_t* g = static_cast<uint8_t*>(p.out) + (size_t(row0) * p.ldo + col0) * 2;
+          stage_and_store<4>(patch, lane, units, g, size_t(p.ldo) * 2, rows_valid, min(4u, (p.n - col0) / 8));
         } else {
-          float* o = static_cast<float*>(p.out) + size_t(row) * p.ldo + col0;
+          // f32: 32 columns = 128 bytes per row, in two passes of 16 columns through the patch
 #pragma unroll
-          for (int g = 0; g < 8; ++g) {
-            if (col0 + g * 4 + 4 <= p.n) {
-              float4 w = make_float4(__uint_as_float(r[4 * g]) * scale, __uint_as_float(r[4 * g + 1]) * scale,
-                                     __uint_as_float(r[4 * g + 2]) * scale, __uint_as_float(r[4 * g + 3]) * scale);
-              reinterpret_cast<float4*>(o)[g] = w;
+          for (int hh = 0; hh < 2; ++hh) {
+            uint4 units[4];
+#pragma unroll
+            for (int g = 0; g < 4; ++g) {
+              units[g].x = __float_as_uint(__uint_as_float(r[16 * hh + 4 * g + 0]) * scale);
+              units[g].y = __float_as_uint(__uint_as_float(r[16 * hh + 4 * g + 1]) * scale);
+              units[g].z = __float_as_uint(__uint_as_float(r[16 * hh + 4 * g + 2]) * scale);
+              units[g].w = __float_as_uint(__uint_as_float(r[16 * hh + 4 * g + 3]) * scale);
+            }
+            const uint32_t c0 = col0 + 16 * hh;
+            if (c0 < p.n) {
+              uint8_t* g = static_cast<uint8_t*>(p.out) + (size_t(row0) * p.ldo + c0) * 4;
+              stage_and_store<4>(patch, lane, units, g, size_t(p.ldo) * 4, rows_valid, min(4u, (p.n - c0) / 4));
             }
           }
         }
+      };
+      int first = 0;
+      if (C::OVERLAP) {
+        // The 64 columns shared with the other accumulator come out first, both chunks
+        // before any store work, so that the next tile's MMAs are released at once.
+        const int ca = buf == 0 ? CHUNKS - 2 : 0;
+        uint32_t ra[32], rb[32];
+        tmem_ld_x32(t_acc + ca * 32, ra);
+        tmem_ld_x32(t_acc + (ca + 1) * 32, rb);
+        tmem_ld_wait();
+        fence_before_sync();
+        mbar_arrive(ovl_free_bar);
+        process(ca, ra);
+        process(ca + 1, rb);
+        first = 2;
+      }
+#pragma unroll 1
+      for (int ci = first; ci < CHUNKS; ++ci) {
+        int c = ci;
+        if (C::OVERLAP && buf == 0) c = ci - 2;
+        uint32_t r[32];
+        tmem_ld_x32(t_acc + c * 32, r);
+        tmem_ld_wait();
+        process(c, r);
       }
       fence_before_sync();
       mbar_arrive(acc_empty_bar(buf));
