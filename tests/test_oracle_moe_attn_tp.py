@@ -1,0 +1,152 @@
+"""The oracle's router, row plan, attention and shard arithmetic against the reference's
+in-source known-answer tests (cited by file:line, paths relative to the reference root)."""
+import numpy as np
+import pytest
+
+MTILE = 16  # the reference's m16 MMA tile (src/models/inkling/moegroup.rs)
+
+
+def test_rows_are_stacked_in_expert_order_with_padding(orc):
+    # src/models/inkling/moegroup.rs:1947-1989: e0=[(1,.5)], e1=[(0,.25),(1,.125)], e2=[(0,.75)]
+    idx = np.array([[1, 2], [0, 1]], np.uint32)
+    wgt = np.array([[0.25, 0.75], [0.5, 0.125]], np.float32)
+    plan = orc.row_plan(idx, wgt, 3, MTILE)
+    assert plan["m_total"] == 3 * MTILE
+    assert list(plan["slot_expert"]) == [0, 1, 2]
+    assert list(plan["slot_row0"] // MTILE) == [0, 1, 2]          # blk_tile0, one tile each
+    rt = plan["row_tok"]
+    assert rt[0] == 1 and rt[1] == -1 and rt[MTILE] == 0 and rt[MTILE + 1] == 1 and rt[2 * MTILE] == 0
+    assert plan["kmax"] == 2 and list(plan["tok_cnt"]) == [2, 2]
+    assert list(plan["tok_rows"][0]) == [MTILE, 2 * MTILE]
+    assert list(plan["tok_rows"][1]) == [0, MTILE + 1]
+    rw = plan["row_wgt"]
+    assert rw[0] == 0.5 and rw[1] == 0.0 and rw[MTILE] == 0.25 and rw[MTILE + 1] == 0.125 and rw[2 * MTILE] == 0.75
+
+
+def test_every_tile_of_the_layer_is_served_once(orc):
+    # src/models/inkling/moegroup.rs:1991-2007: 65, 3 and 130 tokens -> 5 + 1 + 9 tiles of 16 rows
+    counts = [4 * MTILE + 1, 3, 8 * MTILE + 2]
+    n = counts[2]
+    idx = np.full((n, 3), 0, np.uint32)
+    # token t picks expert 0 if t < 65, expert 1 if t < 3, expert 2 always; unused picks go to a 4th expert
+    rows = []
+    for t in range(n):
+        picks = [e for e, c in enumerate(counts) if t < c]
+        picks += [3] * (3 - len(picks))
+        rows.append(picks)
+    idx = np.array(rows, np.uint32)
+    plan = orc.row_plan(idx, np.ones(idx.shape, np.float32), 4, MTILE)
+    tiles = [(int(c) + MTILE - 1) // MTILE for c in plan["slot_rows"][:3]]
+    assert tiles == [5, 1, 9]
+    assert list(plan["slot_row0"][:3] // MTILE) == [0, 5, 6]
+    # rows of one expert keep token order
+    rt = plan["row_tok"][: counts[0]]
+    assert list(rt) == list(range(counts[0]))
+
+
+def test_bias_moves_selection_not_weights_and_renormalise(orc):
+    # src/models/k3/router.rs:518-556 restated on the softmax branch the BASELINE config uses
+    w = np.array([[2.0, 0], [1.0, 0], [0.5, 0], [0.0, 0]], np.float32)
+    h = np.array([1.0, 0.0], np.float32)
+    logits = (w @ h).reshape(1, 4).astype(np.float32)
+    scores = orc.router_scores_softmax(logits)
+    idx0, w0 = orc.router_select(scores, 2)
+    assert list(idx0[0]) == [0, 1]
+    assert abs(float(w0.sum()) - 1.0) < 1e-6
+    idx1, w1 = orc.router_select(scores, 2, bias=[0, 0, 0, 1.0], renormalize=False)
+    assert list(idx1[0]) == [3, 0]
+    assert w1[0, 0] == scores[0, 3] and w1[0, 1] == scores[0, 0] and w1[0, 0] < 1.0
+    # ties go to the lower index (router.rs:410-419)
+    flat = np.zeros((1, 8), np.float32)
+    idx, wt = orc.router_select(orc.router_scores_softmax(flat), 3)
+    assert list(idx[0]) == [0, 1, 2]
+    with pytest.raises(ValueError):
+        orc.router_select(np.array([[np.nan, 1.0]], np.float32), 1)
+
+
+def test_softmax_scores_follow_the_f64_recipe(orc):
+    # router.rs:352-368: f64 exp, f32 store, f32(f64(v)/s)
+    rng = np.random.default_rng(0)
+    logits = rng.standard_normal((5, 128)).astype(np.float32) * 3
+    got = orc.router_scores_softmax(logits)
+    for t in range(5):
+        m = logits[t].astype(np.float64).max()
+        e = np.exp(logits[t].astype(np.float64) - m)
+        v = e.astype(np.float32)
+        s = 0.0
+        for x in e:
+            s += x
+        want = (v.astype(np.float64) / s).astype(np.float32)
+        assert np.array_equal(got[t], want)
+
+
+def test_bf16_widening_is_a_shift(orc):
+    # router.rs:567-572
+    from oracle_lib import bf16_bits_to_f32
+    assert list(bf16_bits_to_f32(np.array([0x3F80, 0xBF80], np.uint16))) == [1.0, -1.0]
+    assert orc.lib.orc_bf16_to_f32(0x3F80) == 1.0
+
+
+def test_cpu_attention_uses_absolute_positions_and_window_edges(orc):
+    # src/models/inkling/flash.rs:1989-2016 (scale plays the role of 1/head_dim there: zero logits anyway)
+    for window, expected in [(0, [5.5, 5.5, 37.0]), (3, [10.0, 10.0, 100.0])]:
+        out = orc.attention(np.zeros(3), np.zeros(4), np.array([1.0, 10.0, 100.0, 1000.0]), heads=1, kv_heads=1, D=1,
+                            q0=3, scale=1.0, key_pos=[0, 2, 5, 9], window=window)
+        assert np.allclose(out.ravel(), expected, atol=1e-12)
+
+
+def test_attention_gqa_and_causality(orc):
+    rng = np.random.default_rng(1)
+    heads, kvh, D, nq, keys = 4, 2, 8, 3, 6
+    q = rng.standard_normal((nq, heads * D)).astype(np.float32)
+    k = rng.standard_normal((keys, kvh * D)).astype(np.float32)
+    v = rng.standard_normal((keys, kvh * D)).astype(np.float32)
+    out = orc.attention(q, k, v, heads, kvh, D, q0=3, scale=1 / np.sqrt(D))
+    # numpy two-pass reference, kv head = h // (heads // kv_heads) (src/models/inkling/attn.rs:283-331)
+    for qi in range(nq):
+        for h in range(heads):
+            g = h // (heads // kvh)
+            vis = [j for j in range(keys) if j <= 3 + qi]
+            s = np.array([q[qi, h * D:(h + 1) * D].astype(np.float64) @ k[j, g * D:(g + 1) * D] / np.sqrt(D) for j in vis])
+            p = np.exp(s - s.max())
+            p /= p.sum()
+            want = sum(p[i] * v[j, g * D:(g + 1) * D].astype(np.float64) for i, j in enumerate(vis))
+            assert np.allclose(out[qi, h * D:(h + 1) * D], want, atol=1e-12)
+    # changing a masked (future) key must not move the answer
+    k2 = k.copy()
+    k2[5] += 100
+    out2 = orc.attention(q, k2, v, heads, kvh, D, q0=3, scale=1 / np.sqrt(D))
+    assert np.array_equal(out[:2], out2[:2])
+
+
+def test_shards_tile_the_axis_and_gqa_cut(orc):
+    # src/models/inkling/tp.rs:761-793
+    for world in (1, 2, 4, 8):
+        for extent in (32, 8, 256, 201024, 16384):
+            if extent % world:
+                continue
+            seen = np.zeros(extent, np.uint8)
+            for rank in range(world):
+                lo, hi = orc.tp_shard(rank, world, extent)
+                seen[lo:hi] += 1
+            assert (seen == 1).all()
+    assert orc.tp_shard(0, 2, 32) == (0, 16) and orc.tp_shard(1, 2, 32) == (16, 32)
+    assert orc.tp_shard(0, 2, 8) == (0, 4) and orc.tp_shard(1, 2, 8) == (4, 8)
+    assert orc.tp_shard(0, 1, 32) == (0, 32)          # the identity world shards nothing
+    with pytest.raises(ValueError):
+        orc.tp_shard(0, 3, 32)                        # Indivisible
+
+
+def test_gate_up_silu_readings_and_ordered_scatter(orc):
+    # src/models/inkling/fp4gemm.rs:472-507: interleaved vs halved; moegroup.rs:1690-1716: ascending fma
+    both = np.arange(8, dtype=np.float32).reshape(1, 8) / 4
+    inter = 4
+    silu = lambda g: g / (1 + np.exp(-g))
+    a = orc.gate_up_silu(both, 1, inter, halved=False)[0]
+    assert np.allclose(a, [silu(both[0, 2 * i]) * both[0, 2 * i + 1] for i in range(inter)], rtol=1e-6)
+    b = orc.gate_up_silu(both, 1, inter, halved=True)[0]
+    assert np.allclose(b, [silu(both[0, i]) * both[0, inter + i] for i in range(inter)], rtol=1e-6)
+    y = np.array([[1.0, 2.0], [10.0, 20.0], [100.0, 200.0]], np.float32)
+    wgt = np.array([0.5, 0.25, 0.125], np.float32)
+    out = orc.scatter_weighted(y, wgt, np.array([[0, 2], [1, 0]], np.uint32), np.array([2, 1], np.uint32), 2)
+    assert np.array_equal(out, np.array([[13.0, 26.0], [2.5, 5.0]], np.float32))
