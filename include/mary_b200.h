@@ -178,6 +178,35 @@ int mb_moe_plan(mb_ctx* ctx, mb_stream stream, const int32_t* idx, const float* 
 int mb_moe_scatter_weighted(mb_ctx* ctx, mb_stream stream, const void* y, int y_dtype, const float* row_wgt,
                             const int32_t* tok_rows, size_t tokens, size_t k, size_t h, float* out);
 
+/* ---- attention ---------------------------------------------------------------------- */
+/* flash_attention_launch (src/models/inkling/flash.rs:1140-1316) for the plain GQA
+ * case (no window, no relative bias, no eviction gaps): softmax(scale*QK^T + causal)V.
+ * q [batch, nq, heads*D] bf16, k/v [batch, keys, kv_heads*D] bf16 token-major,
+ * out [batch, nq, heads*D] bf16. Query i of a sequence sits at absolute position
+ * q0+i, key j at j; causal masks j > q0+i. D == 128. Decode (nq small) splits the
+ * key axis and combines partial (o, m, l) exactly as flash.rs:892-966; workspace
+ * from mb_attention_workspace(). */
+size_t mb_attention_workspace(size_t batch, size_t nq, size_t keys, size_t heads, size_t kv_heads, size_t d);
+int mb_attention(mb_ctx* ctx, mb_stream stream, const void* q, const void* k, const void* v, size_t batch,
+                 size_t nq, size_t keys, size_t heads, size_t kv_heads, size_t d, size_t q0, float scale,
+                 int causal, void* out, void* workspace, size_t workspace_bytes);
+
+/* ---- decoder-layer glue (Breeze rounding points) ------------------------------------ */
+/* norm_kernel (src/models/breeze/cuda_ops.rs:88-117): bf16(bf16(x*inv)*gain). */
+int mb_rmsnorm(mb_ctx* ctx, mb_stream stream, const void* x_bf16, const void* gain_bf16, size_t rows,
+               size_t width, float eps, void* out_bf16);
+/* element_kernel mode 0 / mode 2 (src/models/breeze/cuda_ops.rs:230-255). */
+int mb_add(mb_ctx* ctx, mb_stream stream, const void* a_bf16, const void* b_bf16, size_t n, void* out_bf16);
+int mb_swiglu(mb_ctx* ctx, mb_stream stream, const void* gate_bf16, const void* up_bf16, size_t n,
+              void* out_bf16);
+/* The residual add after a tensor-parallel reduction: out = bf16(a + bf16(partial_sum_f32)).
+ * The all-reduced partial is f32 (src/models/inkling/tpcomm.rs:1453-1467); rounding it to bf16
+ * first reproduces add(x, linear(..)) of src/models/breeze/backbone.rs:326-329 at world 1. */
+int mb_add_f32(mb_ctx* ctx, mb_stream stream, const void* a_bf16, const float* b_f32, size_t n, void* out_bf16);
+/* rope_kernel (src/models/breeze/cuda_ops.rs:286-320): x [tokens, heads, d], in place allowed. */
+int mb_rope(mb_ctx* ctx, mb_stream stream, const void* x_bf16, size_t tokens, size_t heads, size_t d,
+            size_t past, const float* inv_freq, void* out_bf16);
+
 /* ---- tensor parallel ---------------------------------------------------------------- */
 /* Tp::shard (src/models/inkling/tp.rs:540-555). Host arithmetic only. */
 int mb_tp_shard(size_t rank, size_t world, size_t extent, size_t* lo, size_t* hi);

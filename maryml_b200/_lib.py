@@ -11,7 +11,7 @@ LIB_PATH = os.path.join(_HERE, "libmary_b200.so")
 
 if not os.path.exists(LIB_PATH):
     raise ImportError(
-        f"{LIB_PATH} is missing: build the CUDA library first (python -m maryml_b200.build). "
+        f"{LIB_PATH} is missing: build the CUDA library first (python maryml_b200/build.py). "
         "maryml_b200 has no fallback path.")
 
 lib = C.CDLL(LIB_PATH)
@@ -45,6 +45,13 @@ SIGNATURES = {
     "mb_moe_plan_workspace": (_sz, [_sz, _sz, _sz]),
     "mb_moe_plan": (_i, [_vp, _vp, _vp, _vp, _sz, _sz, _sz, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _sz]),
     "mb_moe_scatter_weighted": (_i, [_vp, _vp, _vp, _i, _vp, _vp, _sz, _sz, _sz, _vp]),
+    "mb_attention_workspace": (_sz, [_sz, _sz, _sz, _sz, _sz, _sz]),
+    "mb_attention": (_i, [_vp, _vp, _vp, _vp, _vp, _sz, _sz, _sz, _sz, _sz, _sz, _sz, _f, _i, _vp, _vp, _sz]),
+    "mb_rmsnorm": (_i, [_vp, _vp, _vp, _vp, _sz, _sz, _f, _vp]),
+    "mb_add": (_i, [_vp, _vp, _vp, _vp, _sz, _vp]),
+    "mb_add_f32": (_i, [_vp, _vp, _vp, _vp, _sz, _vp]),
+    "mb_swiglu": (_i, [_vp, _vp, _vp, _vp, _sz, _vp]),
+    "mb_rope": (_i, [_vp, _vp, _vp, _sz, _sz, _sz, _sz, _vp, _vp]),
     "mb_tp_shard": (_i, [_sz, _sz, _sz, C.POINTER(_sz), C.POINTER(_sz)]),
     "mb_tp_unique_id": (_i, [_vp, C.POINTER(C.c_uint8)]),
     "mb_tp_form": (_i, [_vp, C.POINTER(C.c_uint8), _i, _i]),

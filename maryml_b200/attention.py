@@ -1,0 +1,44 @@
+"""Host-side mirror of the reference's attention entry points over the C ABI.
+
+`flash_attention` follows flash_attention_launch (src/models/inkling/flash.rs:1140-1316)
+for the plain GQA case (no window, no relative bias, no eviction gaps) with a batch axis
+of independent sequences; `attention_prefill` / `attention_step` are the op-surface names
+of src/models/inkling/burn.rs:1732, 2741.
+"""
+import math
+
+import torch
+
+from . import _lib
+from ._lib import lib, context
+from .nvfp4 import _p, _stream
+
+
+def flash_attention(q, k, v, q0=0, scale=None, causal=True, workspace=None):
+    """q [batch, nq, heads, D], k/v [batch, keys, kv_heads, D] bf16 -> out like q.
+    Query i sits at absolute position q0 + i, key j at j."""
+    assert q.dtype == k.dtype == v.dtype == torch.bfloat16
+    assert q.is_contiguous() and k.is_contiguous() and v.is_contiguous()
+    batch, nq, heads, d = q.shape
+    _, keys, kv_heads, _ = k.shape
+    ctx = context(q.device.index)
+    if scale is None:
+        scale = 1.0 / math.sqrt(d)
+    out = torch.empty_like(q)
+    need = int(lib.mb_attention_workspace(batch, nq, keys, heads, kv_heads, d))
+    if need and (workspace is None or workspace.numel() < need):
+        workspace = torch.empty(need, dtype=torch.uint8, device=q.device)
+    ctx.check(lib.mb_attention(ctx.handle, _stream(), _p(q), _p(k), _p(v), batch, nq, keys, heads, kv_heads, d, q0,
+                               float(scale), int(causal), _p(out), _p(workspace) if need else None, need))
+    return out
+
+
+def attention_prefill(q, k, v, scale=None):
+    """Causal self-attention over a fresh sequence (q0 = 0)."""
+    return flash_attention(q, k, v, 0, scale, True)
+
+
+def attention_step(q, k_cache, v_cache, scale=None):
+    """One decode step: the single query of each sequence sits after all cached keys."""
+    keys = k_cache.shape[1]
+    return flash_attention(q, k_cache, v_cache, keys - q.shape[1], scale, True)

@@ -1,6 +1,6 @@
 """Builds libmary_b200.so from maryml_b200/csrc/*.cu for sm_100a with nvcc.
 
-    python -m maryml_b200.build [--force]
+    python maryml_b200/build.py [--force]
 
 The shared object is written next to this file, in-tree, so that it travels with
 the source tree. nvcc cross-compiles without a GPU.

@@ -1,0 +1,579 @@
+// GQA flash attention, bf16 in / bf16 out, head_dim 128: softmax(scale * Q K^T + causal) V.
+//
+// Two kernels share one tile format. K and V tiles of 64 keys x 128 dims arrive by
+// TMA (4-D tensor maps over [batch, keys, kv_heads, D]) as two 64-dim halves, each a
+// 128-byte-row tile under the 128-byte swizzle, so that ldmatrix reads them without
+// bank conflicts; a dedicated producer warp keeps a ring of tiles in flight.
+//
+//  * decode  (nq * group <= 16): one CTA per (key split, kv head, sequence). All
+//    query heads of the kv head ride in one 16-row MMA tile, so every K/V byte is
+//    read once from HBM and shared by the whole group. The four compute warps take
+//    16 keys of each 64-key tile; partial (o, m, l) of the warps and of the key
+//    splits are merged at the end (flash-decoding). HBM-bound: algorithmic bytes =
+//    2 * keys * kv_heads * D * 2 per sequence.
+//  * prefill: one CTA per (128-query tile, head, sequence), eight compute warps of 16
+//    query rows each, online softmax, causal tiles beyond the diagonal skipped.
+//    Tensor-bound: 4 * nq * keys * D flop per head (half of it under the causal mask).
+//
+// The S = QK^T and O += PV products use warp-level mma.sync m16n8k16 (bf16, f32
+// accumulate). Every mbarrier wait is bounded.
+#include "common.cuh"
+#include "tc5.cuh"
+
+namespace {
+
+using namespace tc5;
+
+constexpr int D = 128;            // head dim
+constexpr int BC = 64;            // keys per tile
+constexpr int TILE_HALF_BYTES = BC * 128;       // one 64-dim half of a K or V tile
+constexpr int KV_STAGE_BYTES = 4 * TILE_HALF_BYTES;   // K lo, K hi, V lo, V hi = 32 KB
+
+struct AttnParams {
+  CUtensorMap tmap_q;   // [batch, nq, heads, D], box 64 x 1 x 128 x 1 (prefill only)
+  CUtensorMap tmap_k;   // [batch, keys, kv_heads, D], box 64 x 1 x 64 x 1
+  CUtensorMap tmap_v;
+  const __nv_bfloat16* q;
+  __nv_bfloat16* out;
+  float* part;          // decode partials [batch, kv_heads, splits, 16 rows, D + 2]
+  int* flags;
+  uint32_t batch, nq, keys, heads, kv_heads, q0, splits, keys_per_split;
+  float scale_log2;     // scale * log2(e)
+  int causal;
+};
+
+__device__ __forceinline__ void tma_load_4d(uint32_t dst, const void* tmap, int c0, int c1, int c2, int c3,
+                                            uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4, %5}], [%6];"
+      ::"r"(dst), "l"(tmap), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(bar)
+      : "memory");
+}
+
+__device__ __forceinline__ void ldsm_x4(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
+               : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
+}
+__device__ __forceinline__ void ldsm_x4_trans(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0, %1, %2, %3}, [%4];"
+               : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
+}
+__device__ __forceinline__ void mma_bf16(float* c, const uint32_t* a, uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, "
+      "{%0, %1, %2, %3};"
+      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t pack2(float lo, float hi) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+
+// Byte offset of (row, 16-byte chunk c of 16 chunks = 128 dims) in a [rows x 128 dims]
+// tile stored as two swizzled 64-dim halves of `half_bytes` each.
+__device__ __forceinline__ uint32_t tile_off(uint32_t row, uint32_t c, uint32_t half_bytes) {
+  return (c >> 3) * half_bytes + row * 128u + (((c & 7u) ^ (row & 7u)) << 4);
+}
+
+// S[16 x 8*NT] = Q[16 x 128] K^T for keys key0.. of a tile; Q fragments come from qf (8 k-steps x 4 regs).
+template <int NT>
+__device__ __forceinline__ void qk_tile(float (*s)[4], const uint32_t (*qf)[4], uint32_t k_base, uint32_t key0,
+                                        uint32_t lane) {
+#pragma unroll
+  for (int j = 0; j < NT; ++j) { s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.0f; }
+  const uint32_t mi = lane >> 3, l8 = lane & 7;
+#pragma unroll
+  for (int ks = 0; ks < 8; ++ks) {
+#pragma unroll
+    for (int jp = 0; jp < NT / 2; ++jp) {
+      uint32_t b0, b1, b2, b3;
+      const uint32_t row = key0 + jp * 16 + (mi >> 1) * 8 + l8;
+      ldsm_x4(k_base + tile_off(row, ks * 2 + (mi & 1), TILE_HALF_BYTES), b0, b1, b2, b3);
+      mma_bf16(s[2 * jp], qf[ks], b0, b1);
+      mma_bf16(s[2 * jp + 1], qf[ks], b2, b3);
+    }
+  }
+}
+
+// O[16 x 128] += P[16 x 16*KT] V for keys key0.. of a tile; P in C-fragment layout (bf16-rounded here).
+template <int KT>
+__device__ __forceinline__ void pv_tile(float (*o)[4], const float (*pfrag)[4], uint32_t v_base, uint32_t key0,
+                                        uint32_t lane) {
+  const uint32_t mi = lane >> 3, l8 = lane & 7;
+#pragma unroll
+  for (int kt = 0; kt < KT; ++kt) {
+    uint32_t a[4];
+    a[0] = pack2(pfrag[2 * kt][0], pfrag[2 * kt][1]);
+    a[1] = pack2(pfrag[2 * kt][2], pfrag[2 * kt][3]);
+    a[2] = pack2(pfrag[2 * kt + 1][0], pfrag[2 * kt + 1][1]);
+    a[3] = pack2(pfrag[2 * kt + 1][2], pfrag[2 * kt + 1][3]);
+    const uint32_t row = key0 + kt * 16 + (mi & 1) * 8 + l8;
+#pragma unroll
+    for (int np = 0; np < 8; ++np) {
+      uint32_t b0, b1, b2, b3;
+      ldsm_x4_trans(v_base + tile_off(row, np * 2 + (mi >> 1), TILE_HALF_BYTES), b0, b1, b2, b3);
+      mma_bf16(o[2 * np], a, b0, b1);
+      mma_bf16(o[2 * np + 1], a, b2, b3);
+    }
+  }
+}
+
+// One online-softmax step over NT key tiles of 8: masks, updates (m, l), rescales o, leaves p in s.
+// Rows g (regs 0, 1) and g + 8 (regs 2, 3); mask_lo/hi = number of visible keys from `kbase` for those rows.
+template <int NT>
+__device__ __forceinline__ void softmax_step(float (*s)[4], float (*o)[4], float* m, float* l, float scale_log2,
+                                             int vis_lo, int vis_hi, uint32_t lane) {
+  const int t2 = (lane & 3) * 2;
+  float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+  for (int j = 0; j < NT; ++j) {
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const int key = j * 8 + t2 + (e & 1);
+      const int vis = e < 2 ? vis_lo : vis_hi;
+      s[j][e] = key < vis ? s[j][e] * scale_log2 : -INFINITY;
+      mx[e >> 1] = fmaxf(mx[e >> 1], s[j][e]);
+    }
+  }
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xFFFFFFFFu, mx[h], 1));
+    mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xFFFFFFFFu, mx[h], 2));
+  }
+  float corr[2], sum[2] = {0.0f, 0.0f}, mnew[2];
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    mnew[h] = fmaxf(m[h], mx[h]);
+    // a fully masked row keeps m = -inf; exp2(-inf - (-inf)) is avoided by the guard
+    corr[h] = mnew[h] == -INFINITY ? 1.0f : exp2f(m[h] - mnew[h]);
+    m[h] = mnew[h];
+  }
+#pragma unroll
+  for (int j = 0; j < NT; ++j) {
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const float mm = mnew[e >> 1];
+      const float pv = mm == -INFINITY ? 0.0f : exp2f(s[j][e] - mm);
+      s[j][e] = pv;
+      sum[e >> 1] += pv;
+    }
+  }
+#pragma unroll
+  for (int h = 0; h < 2; ++h) l[h] = l[h] * corr[h] + sum[h];   // per-thread partial; quad-reduced at the end
+#pragma unroll
+  for (int n = 0; n < 16; ++n) {
+    o[n][0] *= corr[0]; o[n][1] *= corr[0];
+    o[n][2] *= corr[1]; o[n][3] *= corr[1];
+  }
+}
+
+// ---------------------------------------------------------------------------------
+// Decode: grid (splits, kv_heads, batch), 4 compute warps + 1 producer warp.
+// ---------------------------------------------------------------------------------
+constexpr int DEC_STAGES = 3;
+constexpr int DEC_THREADS = 160;
+constexpr int DEC_SMEM = DEC_STAGES * KV_STAGE_BYTES + 16 * D * 2 /*Q*/ + 1024 + 128;
+static_assert(4 * 16 * (D + 2) * 4 <= DEC_STAGES * KV_STAGE_BYTES, "the merge patch reuses the tile ring");
+
+__global__ void __launch_bounds__(DEC_THREADS, 2)
+attn_decode_kernel(const __grid_constant__ AttnParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* gen = smem_raw + (base - smem_u32(smem_raw));
+  const uint32_t q_smem = base + DEC_STAGES * KV_STAGE_BYTES;            // [16][128] bf16, swizzled halves of 16 rows
+  float* merge = reinterpret_cast<float*>(gen);   // reuses the tile ring once every compute warp is done with it
+  const uint32_t bar_base = base + DEC_STAGES * KV_STAGE_BYTES + 16 * D * 2;
+  auto full_bar = [&](int s) { return bar_base + 8u * s; };
+  auto empty_bar = [&](int s) { return bar_base + 8u * (DEC_STAGES + s); };
+  volatile int* abort_smem = reinterpret_cast<volatile int*>(gen + (bar_base - base) + 8 * 2 * DEC_STAGES);
+  int* tflag = p.flags ? p.flags + MB_FLAG_WAIT_TIMEOUT : nullptr;
+
+  const int warp = __shfl_sync(0xFFFFFFFFu, int(threadIdx.x >> 5), 0);
+  const uint32_t lane = threadIdx.x & 31;
+  const uint32_t split = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
+  const uint32_t group = p.heads / p.kv_heads;
+  const uint32_t rows = p.nq * group;                      // <= 16
+  // keys this query block can see at all, and this CTA's slice of them
+  const uint32_t visible = p.causal ? min(p.keys, p.q0 + p.nq) : p.keys;
+  const uint32_t k_begin = split * p.keys_per_split;
+  const uint32_t k_end = min(visible, k_begin + p.keys_per_split);
+  const uint32_t n_tiles = k_end > k_begin ? (k_end - k_begin + BC - 1) / BC : 0;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < DEC_STAGES; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 4); }
+    *abort_smem = 0;
+    fence_barrier_init();
+    tma_prefetch_desc(&p.tmap_k);
+    tma_prefetch_desc(&p.tmap_v);
+  }
+  // Q rows r = qi * group + hg, zero beyond `rows`; 16 chunks of 16 bytes per row.
+  for (uint32_t i = threadIdx.x; i < 16 * 16; i += DEC_THREADS) {
+    const uint32_t r = i >> 4, c = i & 15;
+    uint4 v = make_uint4(0, 0, 0, 0);
+    if (r < rows) {
+      const uint32_t qi = r / group, hg = r % group;
+      const __nv_bfloat16* src = p.q + ((size_t(b) * p.nq + qi) * p.heads + kvh * group + hg) * D + c * 8;
+      v = *reinterpret_cast<const uint4*>(src);
+    }
+    *reinterpret_cast<uint4*>(gen + (q_smem - base) + tile_off(r, c, 16 * 128)) = v;
+  }
+  __syncthreads();
+
+  if (warp == 4) {
+    // producer
+    int stage = 0;
+    uint32_t phase = 0;
+    for (uint32_t t = 0; t < n_tiles; ++t) {
+      if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_smem, tflag, 11)) break;
+      if (elect_one()) {
+        const uint32_t s0 = base + stage * KV_STAGE_BYTES;
+        const int key0 = int(k_begin + t * BC);
+        mbar_arrive_expect_tx(full_bar(stage), KV_STAGE_BYTES);
+        tma_load_4d(s0, &p.tmap_k, 0, int(kvh), key0, int(b), full_bar(stage));
+        tma_load_4d(s0 + TILE_HALF_BYTES, &p.tmap_k, 64, int(kvh), key0, int(b), full_bar(stage));
+        tma_load_4d(s0 + 2 * TILE_HALF_BYTES, &p.tmap_v, 0, int(kvh), key0, int(b), full_bar(stage));
+        tma_load_4d(s0 + 3 * TILE_HALF_BYTES, &p.tmap_v, 64, int(kvh), key0, int(b), full_bar(stage));
+      }
+      __syncwarp();
+      if (++stage == DEC_STAGES) { stage = 0; phase ^= 1u; }
+    }
+  } else {
+    // compute warp w takes keys [16 w, 16 w + 16) of every tile
+    uint32_t qf[8][4];
+#pragma unroll
+    for (int ks = 0; ks < 8; ++ks)
+      ldsm_x4(q_smem + tile_off(lane & 15, ks * 2 + (lane >> 4), 16 * 128), qf[ks][0], qf[ks][1], qf[ks][2], qf[ks][3]);
+    float o[16][4];
+#pragma unroll
+    for (int n = 0; n < 16; ++n) o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.0f;
+    float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.0f, 0.0f};
+    const uint32_t g = lane >> 2;
+    // query position of rows g and g + 8 (rows >= `rows` are padding; they see what row 0 sees)
+    const uint32_t qpos_lo = p.q0 + (g < rows ? g / group : 0);
+    const uint32_t qpos_hi = p.q0 + (g + 8 < rows ? (g + 8) / group : 0);
+    int stage = 0;
+    uint32_t phase = 0;
+    bool ok = true;
+    for (uint32_t t = 0; t < n_tiles; ++t) {
+      if (!mbar_wait(full_bar(stage), phase, abort_smem, tflag, 12)) { ok = false; break; }
+      const uint32_t s0 = base + stage * KV_STAGE_BYTES;
+      const uint32_t key0 = warp * 16;
+      const int kabs = int(k_begin + t * BC + key0);       // absolute index of this warp's first key
+      float s[2][4];
+      qk_tile<2>(s, qf, s0, key0, lane);
+      int vis_lo = int(k_end) - kabs, vis_hi = vis_lo;
+      if (p.causal) {
+        vis_lo = min(vis_lo, int(qpos_lo) + 1 - kabs);
+        vis_hi = min(vis_hi, int(qpos_hi) + 1 - kabs);
+      }
+      softmax_step<2>(s, o, m, l, p.scale_log2, vis_lo, vis_hi, lane);
+      pv_tile<1>(o, s, s0 + 2 * TILE_HALF_BYTES, key0, lane);
+      __syncwarp();
+      if (lane == 0) mbar_arrive(empty_bar(stage));
+      if (++stage == DEC_STAGES) { stage = 0; phase ^= 1u; }
+    }
+    (void)ok;
+    // quad-reduce l, then publish this warp's partial (o, m, l) for rows g and g + 8
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      l[h] += __shfl_xor_sync(0xFFFFFFFFu, l[h], 1);
+      l[h] += __shfl_xor_sync(0xFFFFFFFFu, l[h], 2);
+    }
+    asm volatile("bar.sync 1, 128;" ::: "memory");   // all four compute warps have read their last tile
+    float* mine = merge + warp * 16 * (D + 2);
+    const uint32_t t2 = (lane & 3) * 2;
+#pragma unroll
+    for (int n = 0; n < 16; ++n) {
+      mine[g * (D + 2) + n * 8 + t2] = o[n][0];
+      mine[g * (D + 2) + n * 8 + t2 + 1] = o[n][1];
+      mine[(g + 8) * (D + 2) + n * 8 + t2] = o[n][2];
+      mine[(g + 8) * (D + 2) + n * 8 + t2 + 1] = o[n][3];
+    }
+    if ((lane & 3) == 0) {
+      mine[g * (D + 2) + D] = m[0];
+      mine[g * (D + 2) + D + 1] = l[0];
+      mine[(g + 8) * (D + 2) + D] = m[1];
+      mine[(g + 8) * (D + 2) + D + 1] = l[1];
+    }
+  }
+  __syncthreads();
+  // merge the four warps: thread (r, d-group) handles row r, dims d..d+... ; 128 threads x 16 rows
+  if (threadIdx.x < 128) {
+    const uint32_t d = threadIdx.x;
+    for (uint32_t r = 0; r < rows; ++r) {
+      float mm = -INFINITY;
+      for (int w = 0; w < 4; ++w) mm = fmaxf(mm, merge[(w * 16 + r) * (D + 2) + D]);
+      float acc = 0.0f, ll = 0.0f;
+      for (int w = 0; w < 4; ++w) {
+        const float mw = merge[(w * 16 + r) * (D + 2) + D];
+        const float f = mw == -INFINITY ? 0.0f : exp2f(mw - mm);
+        acc += merge[(w * 16 + r) * (D + 2) + d] * f;
+        ll += merge[(w * 16 + r) * (D + 2) + D + 1] * f;
+      }
+      const uint32_t qi = r / group, hg = r % group;
+      if (p.splits == 1) {
+        const float v = ll > 0.0f ? acc / ll : 0.0f;
+        p.out[((size_t(b) * p.nq + qi) * p.heads + kvh * group + hg) * D + d] = __float2bfloat16_rn(v);
+      } else {
+        float* dst = p.part + (((size_t(b) * p.kv_heads + kvh) * p.splits + split) * 16 + r) * (D + 2);
+        dst[d] = acc;
+        if (d == 0) { dst[D] = mm; dst[D + 1] = ll; }
+      }
+    }
+  }
+}
+
+// Merge the key splits: out = sum_s o_s 2^(m_s - M) / sum_s l_s 2^(m_s - M).
+__global__ void __launch_bounds__(128)
+attn_combine_kernel(const float* __restrict__ part, __nv_bfloat16* __restrict__ out, uint32_t nq, uint32_t heads,
+                    uint32_t kv_heads, uint32_t splits) {
+  const uint32_t h = blockIdx.x % heads, qi = (blockIdx.x / heads) % nq, b = blockIdx.x / (heads * nq);
+  const uint32_t group = heads / kv_heads, kvh = h / group, r = qi * group + h % group, d = threadIdx.x;
+  const float* src = part + ((size_t(b) * kv_heads + kvh) * splits * 16 + r) * (D + 2);
+  const size_t split_stride = size_t(16) * (D + 2);
+  float mm = -INFINITY;
+  for (uint32_t s = 0; s < splits; ++s) mm = fmaxf(mm, src[s * split_stride + D]);
+  float acc = 0.0f, ll = 0.0f;
+  for (uint32_t s = 0; s < splits; ++s) {
+    const float ms = src[s * split_stride + D];
+    const float f = ms == -INFINITY ? 0.0f : exp2f(ms - mm);
+    acc += src[s * split_stride + d] * f;
+    ll += src[s * split_stride + D + 1] * f;
+  }
+  out[((size_t(b) * nq + qi) * heads + h) * D + d] = __float2bfloat16_rn(ll > 0.0f ? acc / ll : 0.0f);
+}
+
+// ---------------------------------------------------------------------------------
+// Prefill: grid (q tiles, heads, batch), 8 compute warps + 1 producer warp.
+// ---------------------------------------------------------------------------------
+constexpr int PRE_STAGES = 3;
+constexpr int PRE_THREADS = 288;
+constexpr int BR = 128;
+constexpr int PRE_SMEM = PRE_STAGES * KV_STAGE_BYTES + BR * D * 2 + 1024 + 128;
+
+__global__ void __launch_bounds__(PRE_THREADS, 1)
+attn_prefill_kernel(const __grid_constant__ AttnParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* gen = smem_raw + (base - smem_u32(smem_raw));
+  const uint32_t q_smem = base + PRE_STAGES * KV_STAGE_BYTES;      // two halves of [128][64]
+  const uint32_t bar_base = q_smem + BR * D * 2;
+  auto full_bar = [&](int s) { return bar_base + 8u * s; };
+  auto empty_bar = [&](int s) { return bar_base + 8u * (PRE_STAGES + s); };
+  const uint32_t q_bar = bar_base + 8u * 2 * PRE_STAGES;
+  volatile int* abort_smem = reinterpret_cast<volatile int*>(gen + (bar_base - base) + 8 * (2 * PRE_STAGES + 1));
+  int* tflag = p.flags ? p.flags + MB_FLAG_WAIT_TIMEOUT : nullptr;
+
+  const int warp = __shfl_sync(0xFFFFFFFFu, int(threadIdx.x >> 5), 0);
+  const uint32_t lane = threadIdx.x & 31;
+  // heavy (late) query tiles first
+  const uint32_t qt = gridDim.x - 1 - blockIdx.x, h = blockIdx.y, b = blockIdx.z;
+  const uint32_t kvh = h / (p.heads / p.kv_heads);
+  const uint32_t q_row0 = qt * BR;
+  const uint32_t q_rows = min(uint32_t(BR), p.nq - q_row0);
+  const uint32_t last_q = p.q0 + q_row0 + q_rows - 1;
+  const uint32_t k_end = p.causal ? min(p.keys, last_q + 1) : p.keys;
+  const uint32_t n_tiles = (k_end + BC - 1) / BC;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < PRE_STAGES; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 8); }
+    mbar_init(q_bar, 1);
+    *abort_smem = 0;
+    fence_barrier_init();
+    tma_prefetch_desc(&p.tmap_q);
+    tma_prefetch_desc(&p.tmap_k);
+    tma_prefetch_desc(&p.tmap_v);
+  }
+  __syncthreads();
+
+  if (warp == 8) {
+    if (elect_one()) {
+      mbar_arrive_expect_tx(q_bar, BR * D * 2);
+      tma_load_4d(q_smem, &p.tmap_q, 0, int(h), int(q_row0), int(b), q_bar);
+      tma_load_4d(q_smem + BR * 128, &p.tmap_q, 64, int(h), int(q_row0), int(b), q_bar);
+    }
+    __syncwarp();
+    int stage = 0;
+    uint32_t phase = 0;
+    for (uint32_t t = 0; t < n_tiles; ++t) {
+      if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_smem, tflag, 13)) break;
+      if (elect_one()) {
+        const uint32_t s0 = base + stage * KV_STAGE_BYTES;
+        const int key0 = int(t * BC);
+        mbar_arrive_expect_tx(full_bar(stage), KV_STAGE_BYTES);
+        tma_load_4d(s0, &p.tmap_k, 0, int(kvh), key0, int(b), full_bar(stage));
+        tma_load_4d(s0 + TILE_HALF_BYTES, &p.tmap_k, 64, int(kvh), key0, int(b), full_bar(stage));
+        tma_load_4d(s0 + 2 * TILE_HALF_BYTES, &p.tmap_v, 0, int(kvh), key0, int(b), full_bar(stage));
+        tma_load_4d(s0 + 3 * TILE_HALF_BYTES, &p.tmap_v, 64, int(kvh), key0, int(b), full_bar(stage));
+      }
+      __syncwarp();
+      if (++stage == PRE_STAGES) { stage = 0; phase ^= 1u; }
+    }
+  } else {
+    bool ok = mbar_wait(q_bar, 0u, abort_smem, tflag, 14);
+    uint32_t qf[8][4];
+    const uint32_t qr = warp * 16 + (lane & 15);
+#pragma unroll
+    for (int ks = 0; ks < 8; ++ks)
+      ldsm_x4(q_smem + tile_off(qr, ks * 2 + (lane >> 4), BR * 128), qf[ks][0], qf[ks][1], qf[ks][2], qf[ks][3]);
+    float o[16][4];
+#pragma unroll
+    for (int n = 0; n < 16; ++n) o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.0f;
+    float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.0f, 0.0f};
+    const uint32_t g = lane >> 2;
+    const int qpos_lo = int(p.q0 + q_row0 + warp * 16 + g), qpos_hi = qpos_lo + 8;
+    int stage = 0;
+    uint32_t phase = 0;
+    for (uint32_t t = 0; ok && t < n_tiles; ++t) {
+      if (!mbar_wait(full_bar(stage), phase, abort_smem, tflag, 15)) { ok = false; break; }
+      const uint32_t s0 = base + stage * KV_STAGE_BYTES;
+      const int kabs = int(t * BC);
+      // a warp whose rows all lie before this tile (causal) has nothing to add
+      const bool live = !p.causal || kabs <= qpos_lo + 8 + 7 - int(g);   // uniform: uses the warp's last row
+      if (live) {
+        float s[8][4];
+        qk_tile<8>(s, qf, s0, 0, lane);
+        int vis_lo = int(p.keys) - kabs, vis_hi = vis_lo;
+        if (p.causal) {
+          vis_lo = min(vis_lo, qpos_lo + 1 - kabs);
+          vis_hi = min(vis_hi, qpos_hi + 1 - kabs);
+        }
+        softmax_step<8>(s, o, m, l, p.scale_log2, vis_lo, vis_hi, lane);
+        pv_tile<4>(o, s, s0 + 2 * TILE_HALF_BYTES, 0, lane);
+      }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(empty_bar(stage));
+      if (++stage == PRE_STAGES) { stage = 0; phase ^= 1u; }
+    }
+#pragma unroll
+    for (int hh = 0; hh < 2; ++hh) {
+      l[hh] += __shfl_xor_sync(0xFFFFFFFFu, l[hh], 1);
+      l[hh] += __shfl_xor_sync(0xFFFFFFFFu, l[hh], 2);
+    }
+    const float inv0 = l[0] > 0.0f ? 1.0f / l[0] : 0.0f, inv1 = l[1] > 0.0f ? 1.0f / l[1] : 0.0f;
+    const uint32_t r_lo = warp * 16 + g, r_hi = r_lo + 8;
+    const uint32_t t2 = (lane & 3) * 2;
+#pragma unroll
+    for (int n = 0; n < 16; ++n) {
+      if (r_lo < q_rows)
+        *reinterpret_cast<uint32_t*>(p.out + ((size_t(b) * p.nq + q_row0 + r_lo) * p.heads + h) * D + n * 8 + t2) =
+            pack2(o[n][0] * inv0, o[n][1] * inv0);
+      if (r_hi < q_rows)
+        *reinterpret_cast<uint32_t*>(p.out + ((size_t(b) * p.nq + q_row0 + r_hi) * p.heads + h) * D + n * 8 + t2) =
+            pack2(o[n][2] * inv1, o[n][3] * inv1);
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------------
+// Host side
+// ---------------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+int make_tmap_4d(mb_ctx* ctx, CUtensorMap* tm, const void* basep, uint64_t batch, uint64_t rows, uint64_t hh,
+                 uint32_t box_rows) {
+  if (!ctx->encode_tiled) {
+    void* sym = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    MB_CUDA_OK(ctx, cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &q));
+    if (!sym || q != cudaDriverEntryPointSuccess)
+      return mb_fail(ctx, MB_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
+    ctx->encode_tiled = sym;
+  }
+  EncodeTiledFn enc = reinterpret_cast<EncodeTiledFn>(ctx->encode_tiled);
+  cuuint64_t dims[4] = {uint64_t(D), hh, rows, batch};
+  cuuint64_t strides[3] = {uint64_t(D) * 2, hh * D * 2, rows * hh * D * 2};
+  cuuint32_t box[4] = {64, 1, box_rows, 1};
+  cuuint32_t estr[4] = {1, 1, 1, 1};
+  CUresult r = enc(tm, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(basep), dims, strides, box, estr,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return mb_fail(ctx, MB_ERR_CUDA, "cuTensorMapEncodeTiled (attention) failed with %d", int(r));
+  return MB_OK;
+}
+
+uint32_t decode_splits(size_t batch, size_t kv_heads, size_t keys) {
+  // Fill a 148-SM part about eight CTAs deep; never split below 256 keys.
+  size_t base = batch * kv_heads;
+  size_t want = (size_t(148) * 8 + base - 1) / base;
+  size_t max_splits = (keys + 255) / 256;
+  size_t s = want < 1 ? 1 : want;
+  if (s > max_splits) s = max_splits;
+  if (s > 64) s = 64;
+  return uint32_t(s ? s : 1);
+}
+
+}  // namespace
+
+MB_API size_t mb_attention_workspace(size_t batch, size_t nq, size_t keys, size_t heads, size_t kv_heads, size_t d) {
+  (void)d;
+  if (kv_heads == 0 || heads % kv_heads != 0) return 0;
+  if (nq * (heads / kv_heads) > 16) return 0;   // prefill needs none
+  return batch * kv_heads * size_t(decode_splits(batch, kv_heads, keys)) * 16 * (D + 2) * sizeof(float);
+}
+
+MB_API int mb_attention(mb_ctx* ctx, mb_stream stream_, const void* q, const void* k, const void* v, size_t batch,
+                        size_t nq, size_t keys, size_t heads, size_t kv_heads, size_t d, size_t q0, float scale,
+                        int causal, void* out, void* workspace, size_t workspace_bytes) {
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  MB_REQUIRE(ctx, ctx && q && k && v && out, "attention: null argument");
+  MB_REQUIRE(ctx, d == D, "attention: head_dim must be 128, got %zu", d);
+  MB_REQUIRE(ctx, batch > 0 && nq > 0 && keys > 0 && heads > 0 && kv_heads > 0 && heads % kv_heads == 0,
+             "attention: bad extents (batch %zu, nq %zu, keys %zu, heads %zu, kv_heads %zu)", batch, nq, keys, heads, kv_heads);
+  MB_REQUIRE(ctx, scale == scale && scale > 0.0f, "attention: scale must be positive");
+  MB_REQUIRE(ctx, mb_aligned(q, 16) && mb_aligned(k, 16) && mb_aligned(v, 16) && mb_aligned(out, 16),
+             "attention: 16-byte alignment");
+  MB_REQUIRE(ctx, batch <= 65535 && heads <= 65535 && keys < (1ull << 31) && nq < (1ull << 31), "attention: extent overflow");
+  MB_REQUIRE(ctx, q0 < (1ull << 31), "attention: bad query offset");
+  AttnParams p;
+  memset(&p, 0, sizeof p);
+  int rc = make_tmap_4d(ctx, &p.tmap_k, k, batch, keys, kv_heads, BC);
+  if (rc) return rc;
+  rc = make_tmap_4d(ctx, &p.tmap_v, v, batch, keys, kv_heads, BC);
+  if (rc) return rc;
+  p.q = static_cast<const __nv_bfloat16*>(q);
+  p.out = static_cast<__nv_bfloat16*>(out);
+  p.flags = ctx->flags_dev;
+  p.batch = uint32_t(batch); p.nq = uint32_t(nq); p.keys = uint32_t(keys); p.heads = uint32_t(heads);
+  p.kv_heads = uint32_t(kv_heads); p.q0 = uint32_t(q0); p.causal = causal;
+  p.scale_log2 = scale * 1.4426950408889634f;
+  const size_t group = heads / kv_heads;
+  static bool attr_dec[16] = {}, attr_pre[16] = {};
+  if (nq * group <= 16) {
+    uint32_t splits = decode_splits(batch, kv_heads, keys);
+    size_t need = batch * kv_heads * splits * 16 * (D + 2) * sizeof(float);
+    if (splits > 1) {
+      MB_REQUIRE(ctx, workspace && workspace_bytes >= need, "attention: decode needs %zu workspace bytes", need);
+      MB_REQUIRE(ctx, mb_aligned(workspace, 16), "attention: workspace needs 16-byte alignment");
+    }
+    p.splits = splits;
+    p.keys_per_split = uint32_t(((keys + splits - 1) / splits + BC - 1) / BC * BC);
+    p.part = static_cast<float*>(workspace);
+    if (!attr_dec[ctx->device & 15]) {
+      MB_CUDA_OK(ctx, cudaFuncSetAttribute(attn_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, DEC_SMEM));
+      attr_dec[ctx->device & 15] = true;
+    }
+    dim3 grid(splits, unsigned(kv_heads), unsigned(batch));
+    attn_decode_kernel<<<grid, DEC_THREADS, DEC_SMEM, stream>>>(p);
+    MB_LAUNCH_OK(ctx);
+    if (splits > 1) {
+      attn_combine_kernel<<<unsigned(batch * nq * heads), 128, 0, stream>>>(p.part, p.out, p.nq, p.heads, p.kv_heads, splits);
+      MB_LAUNCH_OK(ctx);
+    }
+  } else {
+    rc = make_tmap_4d(ctx, &p.tmap_q, q, batch, nq, heads, BR);
+    if (rc) return rc;
+    p.splits = 1;
+    if (!attr_pre[ctx->device & 15]) {
+      MB_CUDA_OK(ctx, cudaFuncSetAttribute(attn_prefill_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, PRE_SMEM));
+      attr_pre[ctx->device & 15] = true;
+    }
+    dim3 grid(unsigned((nq + BR - 1) / BR), unsigned(heads), unsigned(batch));
+    attn_prefill_kernel<<<grid, PRE_THREADS, PRE_SMEM, stream>>>(p);
+    MB_LAUNCH_OK(ctx);
+  }
+  return MB_OK;
+}

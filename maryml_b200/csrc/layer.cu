@@ -1,0 +1,184 @@
+// Decoder-layer glue with the reference's bf16 rounding points: RMSNorm, residual
+// add, SwiGLU, RoPE. HBM-bound elementwise kernels with 128-bit accesses; the norm
+// keeps a row in registers between the sum-of-squares pass and the scaling pass.
+#include "common.cuh"
+
+namespace {
+
+__device__ __forceinline__ float bf16r(float v) { return __bfloat162float(__float2bfloat16_rn(v)); }
+__device__ __forceinline__ void unpack8(const uint4& q, float* v) {
+  const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    v[2 * i] = __uint_as_float(w[i] << 16);
+    v[2 * i + 1] = __uint_as_float(w[i] & 0xFFFF0000u);
+  }
+}
+__device__ __forceinline__ uint4 pack8(const float* v) {
+  uint32_t w[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    __nv_bfloat162 t = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
+    w[i] = *reinterpret_cast<uint32_t*>(&t);
+  }
+  return make_uint4(w[0], w[1], w[2], w[3]);
+}
+
+// One CTA of 256 threads per row; width <= 256 * 8 * VEC elements held in registers.
+// inv = 1/sqrt(mean(x^2) + eps); y = bf16(bf16(x * inv) * gain).
+template <int VEC>
+__global__ void __launch_bounds__(256)
+rmsnorm_kernel(const uint4* __restrict__ x, const uint4* __restrict__ gain, uint4* __restrict__ y, uint32_t width,
+               float eps) {
+  const uint32_t row = blockIdx.x, chunks = width / 8;
+  const uint4* xr = x + size_t(row) * chunks;
+  float v[VEC][8];
+  float sum = 0.0f;
+#pragma unroll
+  for (int i = 0; i < VEC; ++i) {
+    const uint32_t c = threadIdx.x + i * 256;
+    if (c < chunks) {
+      unpack8(__ldg(xr + c), v[i]);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) sum += v[i][j] * v[i][j];
+    }
+  }
+  __shared__ float red[8];
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xFFFFFFFFu, sum, o);
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = sum;
+  __syncthreads();
+  float total = 0.0f;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) total += red[i];
+  const float inv = 1.0f / sqrtf(total / float(width) + eps);
+#pragma unroll
+  for (int i = 0; i < VEC; ++i) {
+    const uint32_t c = threadIdx.x + i * 256;
+    if (c < chunks) {
+      float g[8], o[8];
+      unpack8(__ldg(gain + c), g);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) o[j] = bf16r(v[i][j] * inv) * g[j];
+      y[size_t(row) * chunks + c] = pack8(o);
+    }
+  }
+}
+
+// mode 0: a + b; mode 2: bf16(silu(a)) * b. n8 = elements / 8.
+template <int MODE>
+__global__ void __launch_bounds__(256)
+element_kernel(const uint4* __restrict__ a, const uint4* __restrict__ b, uint4* __restrict__ out, size_t n8) {
+  size_t i = size_t(blockIdx.x) * 256 + threadIdx.x;
+  if (i >= n8) return;
+  float x[8], y[8], o[8];
+  unpack8(__ldg(a + i), x);
+  unpack8(__ldg(b + i), y);
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    if (MODE == 0) o[j] = x[j] + y[j];
+    else o[j] = bf16r(__fdiv_rn(x[j], 1.0f + expf(-x[j]))) * y[j];
+  }
+  out[i] = pack8(o);
+}
+
+// out = bf16(a + bf16(b)) with b an f32 partial sum.
+__global__ void __launch_bounds__(256)
+add_f32_kernel(const uint4* __restrict__ a, const float4* __restrict__ b, uint4* __restrict__ out, size_t n8) {
+  size_t i = size_t(blockIdx.x) * 256 + threadIdx.x;
+  if (i >= n8) return;
+  float x[8], o[8];
+  unpack8(__ldg(a + i), x);
+  float4 p0 = __ldg(b + 2 * i), p1 = __ldg(b + 2 * i + 1);
+  const float y[8] = {p0.x, p0.y, p0.z, p0.w, p1.x, p1.y, p1.z, p1.w};
+#pragma unroll
+  for (int j = 0; j < 8; ++j) o[j] = x[j] + bf16r(y[j]);
+  out[i] = pack8(o);
+}
+
+// Half-split rotation; cos/sin rounded to bf16, each product rounded to bf16.
+// One thread per (row, f) pair: reads x[row, f] and x[row, half + f], writes both.
+__global__ void __launch_bounds__(256)
+rope_kernel(const __nv_bfloat16* __restrict__ x, __nv_bfloat16* __restrict__ out, size_t rows, uint32_t heads,
+            uint32_t d, uint32_t past, const float* __restrict__ inv_freq) {
+  const uint32_t half = d / 2;
+  size_t i = size_t(blockIdx.x) * 256 + threadIdx.x;
+  if (i >= rows * half) return;
+  const size_t row = i / half;
+  const uint32_t f = uint32_t(i % half);
+  const uint32_t position = past + uint32_t(row / heads);
+  const float angle = float(position) * inv_freq[f];
+  const float c = bf16r(cosf(angle)), s = bf16r(sinf(angle));
+  const float low = __bfloat162float(x[row * d + f]), high = __bfloat162float(x[row * d + half + f]);
+  out[row * d + f] = __float2bfloat16_rn(bf16r(low * c) - bf16r(high * s));
+  out[row * d + half + f] = __float2bfloat16_rn(bf16r(high * c) + bf16r(low * s));
+}
+
+}  // namespace
+
+MB_API int mb_rmsnorm(mb_ctx* ctx, mb_stream stream_, const void* x, const void* gain, size_t rows, size_t width,
+                      float eps, void* out) {
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  MB_REQUIRE(ctx, ctx && x && gain && out, "rmsnorm: null argument");
+  MB_REQUIRE(ctx, rows > 0 && width > 0 && width % 8 == 0 && width <= 256 * 8 * 4,
+             "rmsnorm: width must be a multiple of 8 up to 8192, got %zu", width);
+  MB_REQUIRE(ctx, mb_aligned(x, 16) && mb_aligned(gain, 16) && mb_aligned(out, 16), "rmsnorm: 16-byte alignment");
+  const uint4* xv = static_cast<const uint4*>(x);
+  const uint4* gv = static_cast<const uint4*>(gain);
+  uint4* ov = static_cast<uint4*>(out);
+  if (width <= 2048) rmsnorm_kernel<1><<<unsigned(rows), 256, 0, stream>>>(xv, gv, ov, uint32_t(width), eps);
+  else if (width <= 4096) rmsnorm_kernel<2><<<unsigned(rows), 256, 0, stream>>>(xv, gv, ov, uint32_t(width), eps);
+  else rmsnorm_kernel<4><<<unsigned(rows), 256, 0, stream>>>(xv, gv, ov, uint32_t(width), eps);
+  MB_LAUNCH_OK(ctx);
+  return MB_OK;
+}
+
+static int element(mb_ctx* ctx, mb_stream stream_, const void* a, const void* b, size_t n, void* out, int mode) {
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  MB_REQUIRE(ctx, ctx && a && b && out, "element: null argument");
+  MB_REQUIRE(ctx, n > 0 && n % 8 == 0, "element: the element count must be a positive multiple of 8");
+  MB_REQUIRE(ctx, mb_aligned(a, 16) && mb_aligned(b, 16) && mb_aligned(out, 16), "element: 16-byte alignment");
+  size_t n8 = n / 8;
+  unsigned grid = unsigned((n8 + 255) / 256);
+  if (mode == 0)
+    element_kernel<0><<<grid, 256, 0, stream>>>(static_cast<const uint4*>(a), static_cast<const uint4*>(b),
+                                                static_cast<uint4*>(out), n8);
+  else
+    element_kernel<2><<<grid, 256, 0, stream>>>(static_cast<const uint4*>(a), static_cast<const uint4*>(b),
+                                                static_cast<uint4*>(out), n8);
+  MB_LAUNCH_OK(ctx);
+  return MB_OK;
+}
+
+MB_API int mb_add(mb_ctx* ctx, mb_stream stream, const void* a, const void* b, size_t n, void* out) {
+  return element(ctx, stream, a, b, n, out, 0);
+}
+MB_API int mb_add_f32(mb_ctx* ctx, mb_stream stream_, const void* a, const float* b, size_t n, void* out) {
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  MB_REQUIRE(ctx, ctx && a && b && out, "add_f32: null argument");
+  MB_REQUIRE(ctx, n > 0 && n % 8 == 0, "add_f32: the element count must be a positive multiple of 8");
+  MB_REQUIRE(ctx, mb_aligned(a, 16) && mb_aligned(b, 16) && mb_aligned(out, 16), "add_f32: 16-byte alignment");
+  size_t n8 = n / 8;
+  add_f32_kernel<<<unsigned((n8 + 255) / 256), 256, 0, stream>>>(static_cast<const uint4*>(a),
+                                                                  reinterpret_cast<const float4*>(b),
+                                                                  static_cast<uint4*>(out), n8);
+  MB_LAUNCH_OK(ctx);
+  return MB_OK;
+}
+MB_API int mb_swiglu(mb_ctx* ctx, mb_stream stream, const void* gate, const void* up, size_t n, void* out) {
+  return element(ctx, stream, gate, up, n, out, 2);
+}
+
+MB_API int mb_rope(mb_ctx* ctx, mb_stream stream_, const void* x, size_t tokens, size_t heads, size_t d, size_t past,
+                   const float* inv_freq, void* out) {
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  MB_REQUIRE(ctx, ctx && x && inv_freq && out, "rope: null argument");
+  MB_REQUIRE(ctx, tokens > 0 && heads > 0 && d > 0 && d % 2 == 0, "rope: d must be even");
+  size_t rows = tokens * heads;
+  size_t total = rows * (d / 2);
+  rope_kernel<<<unsigned((total + 255) / 256), 256, 0, stream>>>(static_cast<const __nv_bfloat16*>(x),
+                                                                 static_cast<__nv_bfloat16*>(out), rows,
+                                                                 uint32_t(heads), uint32_t(d), uint32_t(past), inv_freq);
+  MB_LAUNCH_OK(ctx);
+  return MB_OK;
+}

@@ -1,0 +1,237 @@
+"""The NVFP4 decoder layer and its tensor-parallel placement, over the C ABI.
+
+The layer follows Breeze's `Decoder::forward` body (src/models/breeze/backbone.rs:287-333)
+with its bf16 rounding points (src/models/breeze/cuda_ops.rs:88-117, 230-255, 286-320);
+the placement follows the reference's TP path (src/models/inkling/tp.rs:283-325, 564-640;
+src/models/inkling/session.rs:2713-2717, 2843-2846): QKV / gate / up column-parallel (row
+ranges of the [out, in] planes), o / down row-parallel (column ranges, gathered at load),
+one SUM all-reduce of the f32 partial after o and after down, before the residual add.
+"""
+import ctypes as C
+import math
+
+import numpy as np
+import torch
+
+from . import _lib
+from ._lib import lib, context, MaryError
+from . import nvfp4 as nv
+from .attention import flash_attention
+
+_p = nv._p
+_stream = nv._stream
+
+
+# ---- elementwise glue ----------------------------------------------------------------
+def rmsnorm(x, gain, eps):
+    rows, width = x.shape
+    ctx = context(x.device.index)
+    out = torch.empty_like(x)
+    ctx.check(lib.mb_rmsnorm(ctx.handle, _stream(), _p(x), _p(gain), rows, width, float(eps), _p(out)))
+    return out
+
+
+def add(a, b):
+    ctx = context(a.device.index)
+    out = torch.empty_like(a)
+    ctx.check(lib.mb_add(ctx.handle, _stream(), _p(a), _p(b), a.numel(), _p(out)))
+    return out
+
+
+def add_f32(a, b_f32):
+    ctx = context(a.device.index)
+    out = torch.empty_like(a)
+    ctx.check(lib.mb_add_f32(ctx.handle, _stream(), _p(a), _p(b_f32), a.numel(), _p(out)))
+    return out
+
+
+def swiglu(gate, up):
+    ctx = context(gate.device.index)
+    out = torch.empty_like(gate)
+    ctx.check(lib.mb_swiglu(ctx.handle, _stream(), _p(gate), _p(up), gate.numel(), _p(out)))
+    return out
+
+
+def rope(x, tokens, heads, d, past, inv_freq):
+    """x viewed as [tokens, heads, d]; position of token t is past + t."""
+    ctx = context(x.device.index)
+    out = torch.empty_like(x)
+    ctx.check(lib.mb_rope(ctx.handle, _stream(), _p(x), tokens, heads, d, past, _p(inv_freq), _p(out)))
+    return out
+
+
+def inv_freq(d, theta):
+    """theta^(-2f/d) as f32 (the frequency table the rope kernel takes)."""
+    f = np.arange(d // 2, dtype=np.float64)
+    return (1.0 / (np.float64(theta) ** (2.0 * f / d))).astype(np.float32)
+
+
+# ---- tensor-parallel placement (host arithmetic; works on CPU tensors too) -----------
+class Indivisible(ValueError):
+    """A tensor axis that does not divide by the world size (src/models/inkling/tp.rs:461-470)."""
+
+    def __init__(self, axis, extent, world):
+        super().__init__(f"{axis} = {extent} does not divide by world {world}")
+        self.axis, self.extent, self.world = axis, extent, world
+
+
+class Tp:
+    """Which rank this process is and how many there are (src/models/inkling/tp.rs:449-555).
+    world == 1 is the identity: every cut returns the whole axis."""
+
+    def __init__(self, rank=0, world=1):
+        if world < 1 or not (0 <= rank < world):
+            raise ValueError(f"rank {rank} of world {world}")
+        self.rank, self.world = rank, world
+
+    def is_split(self):
+        return self.world > 1
+
+    def shard(self, axis, extent):
+        if extent % self.world != 0:
+            raise Indivisible(axis, extent, self.world)
+        per = extent // self.world
+        return range(self.rank * per, (self.rank + 1) * per)
+
+    def share(self, axis, extent):
+        return len(self.shard(axis, extent))
+
+    def q_heads(self, heads):
+        return self.shard("num_attention_heads", heads)
+
+    def kv_heads(self, kv_heads):
+        return self.shard("num_key_value_heads", kv_heads)
+
+    def dense_inter(self, inter):
+        return self.shard("intermediate_size", inter)
+
+
+def cut_rows(codes, scales, rows):
+    """Column-parallel cut of stored planes [n, k/2], [n, k/16]: a contiguous row range
+    (src/models/inkling/tpshard.rs:102-140). The global scale stays the whole tensor's."""
+    return codes[rows.start:rows.stop].contiguous(), scales[rows.start:rows.stop].contiguous()
+
+
+def cut_cols(codes, scales, cols):
+    """Row-parallel cut along K: the range must land on a 16-element block and a byte
+    (src/models/inkling/tpshard.rs:526-556 refuses a cut inside a byte)."""
+    if cols.start % 16 != 0 or cols.stop % 16 != 0:
+        raise ValueError(f"a K cut [{cols.start}, {cols.stop}) is not on 16-element block boundaries")
+    return (codes[:, cols.start // 2:cols.stop // 2].contiguous(),
+            scales[:, cols.start // 16:cols.stop // 16].contiguous())
+
+
+class Group:
+    """Group::form / warm / all_reduce_f32 (src/models/inkling/tpcomm.rs:217-429) over NCCL.
+    The 128-byte id minted on rank 0 travels through `exchange` (a callable that broadcasts bytes)."""
+
+    def __init__(self, tp, device, exchange=None):
+        self.tp = tp
+        self.ctx = context(device)
+        if tp.world > 1:
+            uid = (C.c_uint8 * 128)()
+            if tp.rank == 0:
+                self.ctx.check(lib.mb_tp_unique_id(self.ctx.handle, uid))
+            raw = exchange(bytes(uid))
+            uid = (C.c_uint8 * 128).from_buffer_copy(raw)
+            self.ctx.check(lib.mb_tp_form(self.ctx.handle, uid, tp.rank, tp.world))
+            self.warm()
+
+    def warm(self):
+        self.ctx.check(lib.mb_tp_warm(self.ctx.handle, _stream()))
+
+    def all_reduce_f32(self, t):
+        assert t.dtype == torch.float32 and t.is_contiguous()
+        self.ctx.check(lib.mb_tp_all_reduce(self.ctx.handle, _stream(), _p(t), t.numel(), _lib.DT_F32))
+        return t
+
+    def close(self):
+        lib.mb_tp_close(self.ctx.handle)
+
+
+# ---- the layer -----------------------------------------------------------------------
+class LayerConfig:
+    def __init__(self, hidden=4096, heads=32, kv_heads=8, head_dim=128, inter=14336, eps=1e-6, theta=1e6):
+        self.hidden, self.heads, self.kv_heads, self.head_dim = hidden, heads, kv_heads, head_dim
+        self.inter, self.eps, self.theta = inter, eps, theta
+
+
+class DecoderLayer:
+    """One Llama-style NVFP4 decoder layer, this rank's shard of it.
+
+    `full` maps names (q, k, v, o, gate, up, down) to whole-tensor planes
+    (codes [n, k/2], scales [n, k/16], scale2) quantised BEFORE the cut, so every rank
+    holds bytes of the same stored tensor (the reference cuts stored planes)."""
+
+    def __init__(self, cfg, full, input_gain, post_gain, tp=None, group=None, device=None):
+        self.cfg, self.tp, self.group = cfg, tp or Tp(), group
+        dev = device if device is not None else torch.device("cuda", torch.cuda.current_device())
+        D = cfg.head_dim
+        qh, kvh = self.tp.q_heads(cfg.heads), self.tp.kv_heads(cfg.kv_heads)
+        inter = self.tp.dense_inter(cfg.inter)
+        self.local_heads, self.local_kv_heads, self.local_inter = len(qh), len(kvh), len(inter)
+
+        def col_parallel(name, rows):
+            c, s, s2 = full[name]
+            cc, ss = cut_rows(c, s, rows)
+            return nv.Nvfp4.from_parts(cc.to(dev), ss.to(dev), s2, len(rows), c.shape[1] * 2, torch.bfloat16, dev)
+
+        def row_parallel(name, cols):
+            c, s, s2 = full[name]
+            cc, ss = cut_cols(c, s, cols)
+            return nv.Nvfp4.from_parts(cc.to(dev), ss.to(dev), s2, c.shape[0], len(cols), torch.bfloat16, dev)
+
+        self.wq = col_parallel("q", range(qh.start * D, qh.stop * D))
+        self.wk = col_parallel("k", range(kvh.start * D, kvh.stop * D))
+        self.wv = col_parallel("v", range(kvh.start * D, kvh.stop * D))
+        self.wo = row_parallel("o", range(qh.start * D, qh.stop * D))
+        self.wgate = col_parallel("gate", inter)
+        self.wup = col_parallel("up", inter)
+        self.wdown = row_parallel("down", inter)
+        self.input_gain, self.post_gain = input_gain.to(dev), post_gain.to(dev)
+        self.inv_freq = torch.from_numpy(inv_freq(D, cfg.theta)).to(dev)
+        for w in (self.wq, self.wk, self.wv, self.wo, self.wgate, self.wup, self.wdown):
+            w.sf_tiled()
+
+    def _linear(self, x, w, out_dtype=torch.bfloat16):
+        """W4A4 projection (activation quantised per 16 with unit global, src/nn/nvfp4_gemm.rs:644-694)."""
+        t = x.shape[0]
+        codes, sf, _ = nv.quantize_act(x, _lib.QUANT_SCALED, 1.0, tiled=True)
+        return nv.gemm_w4a4(codes, sf, w.codes, w.sf_tiled(), w.scale2, t, w.n(), w.k(), out_dtype=out_dtype)
+
+    def _reduced(self, x, w):
+        partial = self._linear(x, w, out_dtype=torch.float32)
+        if self.group is not None and self.tp.is_split():
+            self.group.all_reduce_f32(partial)
+        return partial
+
+    def forward(self, x, batch, past, k_cache, v_cache):
+        """x [batch * t, hidden] bf16 (t new tokens per sequence, sequence-major). Caches
+        [batch, capacity, local_kv_heads, D]; the new keys/values land at [past, past + t)."""
+        cfg = self.cfg
+        D = cfg.head_dim
+        t = x.shape[0] // batch
+        n = rmsnorm(x, self.input_gain, cfg.eps)
+        q = self._linear(n, self.wq)
+        k = self._linear(n, self.wk)
+        v = self._linear(n, self.wv)
+        # rope positions restart for every sequence: one call per sequence when t > 1, one call when t == 1
+        if t == 1:
+            q = rope(q, 1, batch * self.local_heads, D, past, self.inv_freq)
+            k = rope(k, 1, batch * self.local_kv_heads, D, past, self.inv_freq)
+        else:
+            qs, ks = q.view(batch, t * self.local_heads * D), k.view(batch, t * self.local_kv_heads * D)
+            q = torch.stack([rope(qs[b], t, self.local_heads, D, past, self.inv_freq) for b in range(batch)])
+            k = torch.stack([rope(ks[b], t, self.local_kv_heads, D, past, self.inv_freq) for b in range(batch)])
+        k_cache[:, past:past + t].copy_(k.view(batch, t, self.local_kv_heads, D))
+        v_cache[:, past:past + t].copy_(v.view(batch, t, self.local_kv_heads, D))
+        keys = past + t
+        a = flash_attention(q.view(batch, t, self.local_heads, D), k_cache[:, :keys].contiguous()
+                            if keys != k_cache.shape[1] else k_cache,
+                            v_cache[:, :keys].contiguous() if keys != v_cache.shape[1] else v_cache,
+                            q0=past, scale=1.0 / math.sqrt(D), causal=True)
+        residual = add_f32(x, self._reduced(a.view(batch * t, self.local_heads * D), self.wo))
+        n = rmsnorm(residual, self.post_gain, cfg.eps)
+        gate = self._linear(n, self.wgate)
+        up = self._linear(n, self.wup)
+        return add_f32(residual, self._reduced(swiglu(gate, up), self.wdown))
