@@ -191,6 +191,21 @@ int mb_attention(mb_ctx* ctx, mb_stream stream, const void* q, const void* k, co
                  size_t nq, size_t keys, size_t heads, size_t kv_heads, size_t d, size_t q0, float scale,
                  int causal, void* out, void* workspace, size_t workspace_bytes);
 
+/* Decode attention without any allocation; it has no counterpart in the reference.
+ * For hosts that gave all device memory to their own arena at start-up and may not
+ * call the driver's allocator afterwards (an allocation there stalls the token step
+ * and can fail under a full arena): the key-split scratch lives in a 16 MiB array
+ * built into the library, so the caller passes only q, k, v and out. Same arithmetic
+ * and argument meaning as mb_attention for decode shapes (nq * heads/kv_heads <= 16);
+ * shapes whose split scratch exceeds 16 MiB are refused with MB_ERR_INVALID. The first
+ * call on a device looks up the array's device address (the context's device must be
+ * current); make that call before any stream capture begins. All calls share the one
+ * array: the partials are fully rewritten by every call, nothing needs clearing, but two
+ * calls that overlap on the GPU (different streams) race on it. */
+int mb_attention_decode_static(mb_ctx* ctx, mb_stream stream, const void* q, const void* k, const void* v,
+                               size_t batch, size_t nq, size_t keys, size_t heads, size_t kv_heads, size_t d,
+                               size_t q0, float scale, int causal, void* out);
+
 /* ---- decoder-layer glue (Breeze rounding points) ------------------------------------ */
 /* norm_kernel (src/models/breeze/cuda_ops.rs:88-117): bf16(bf16(x*inv)*gain). */
 int mb_rmsnorm(mb_ctx* ctx, mb_stream stream, const void* x_bf16, const void* gain_bf16, size_t rows,

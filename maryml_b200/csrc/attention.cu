@@ -577,3 +577,80 @@ MB_API int mb_attention(mb_ctx* ctx, mb_stream stream_, const void* q, const voi
   }
   return MB_OK;
 }
+
+// ---------------------------------------------------------------------------------
+// Decode attention for hosts that must not allocate.
+//
+// Some hosts of this library hand their whole device-memory budget to an arena of
+// their own when they start (the compute client a Rust serving process keeps is one)
+// and, from then on, treat any driver allocation as a fault: it would synchronise the
+// device in the middle of a token step and can fail outright when the arena has left
+// nothing. Such a host can pass inputs and outputs it already owns, but it has nowhere
+// to get the scratch the key-split partials need. This entry point keeps that scratch
+// in a fixed array inside the library image instead.
+// ---------------------------------------------------------------------------------
+constexpr size_t STATIC_SCRATCH_BYTES = size_t(16) << 20;   // 16 MiB, held by every GPU that loads the library
+static __device__ __align__(256) unsigned char g_decode_scratch[STATIC_SCRATCH_BYTES];
+
+// Device address of the array, resolved once per device. In host code the array's
+// name is only a handle for the runtime; the kernel needs the address looked up here.
+static float* g_decode_scratch_ptr[64] = {};
+
+MB_API int mb_attention_decode_static(mb_ctx* ctx, mb_stream stream_, const void* q, const void* k, const void* v,
+                                      size_t batch, size_t nq, size_t keys, size_t heads, size_t kv_heads, size_t d,
+                                      size_t q0, float scale, int causal, void* out) {
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  MB_REQUIRE(ctx, ctx && q && k && v && out, "attention_decode_static: null argument");
+  MB_REQUIRE(ctx, d == D, "attention_decode_static: head_dim must be 128, got %zu", d);
+  MB_REQUIRE(ctx, batch > 0 && nq > 0 && keys > 0 && heads > 0 && kv_heads > 0 && heads % kv_heads == 0,
+             "attention_decode_static: bad extents");
+  MB_REQUIRE(ctx, nq * (heads / kv_heads) <= 16,
+             "attention_decode_static: takes decode shapes only (nq * heads/kv_heads <= 16)");
+  MB_REQUIRE(ctx, scale == scale && scale > 0.0f, "attention_decode_static: scale must be positive");
+  MB_REQUIRE(ctx, mb_aligned(q, 16) && mb_aligned(k, 16) && mb_aligned(v, 16) && mb_aligned(out, 16),
+             "attention_decode_static: 16-byte alignment");
+  MB_REQUIRE(ctx, batch <= 65535 && keys < (1ull << 31) && q0 < (1ull << 31), "attention_decode_static: extent overflow");
+  const uint32_t splits = decode_splits(batch, kv_heads, keys);
+  const size_t need = batch * kv_heads * size_t(splits) * 16 * (D + 2) * sizeof(float);
+  MB_REQUIRE(ctx, need <= STATIC_SCRATCH_BYTES,
+             "attention_decode_static: this shape needs %zu bytes of split scratch, the built-in array holds %zu; "
+             "use mb_attention with a caller workspace",
+             need, STATIC_SCRATCH_BYTES);
+  int current = -1;
+  MB_CUDA_OK(ctx, cudaGetDevice(&current));
+  MB_REQUIRE(ctx, current == ctx->device && current < 64,
+             "attention_decode_static: device %d must be current (it is %d)", ctx->device, current);
+  if (!g_decode_scratch_ptr[current]) {
+    void* ptr = nullptr;
+    MB_CUDA_OK(ctx, cudaGetSymbolAddress(&ptr, g_decode_scratch));
+    g_decode_scratch_ptr[current] = static_cast<float*>(ptr);
+  }
+  AttnParams p;
+  memset(&p, 0, sizeof p);
+  int rc = make_tmap_4d(ctx, &p.tmap_k, k, batch, keys, kv_heads, BC);
+  if (rc) return rc;
+  rc = make_tmap_4d(ctx, &p.tmap_v, v, batch, keys, kv_heads, BC);
+  if (rc) return rc;
+  p.q = static_cast<const __nv_bfloat16*>(q);
+  p.out = static_cast<__nv_bfloat16*>(out);
+  p.flags = ctx->flags_dev;
+  p.batch = uint32_t(batch); p.nq = uint32_t(nq); p.keys = uint32_t(keys); p.heads = uint32_t(heads);
+  p.kv_heads = uint32_t(kv_heads); p.q0 = uint32_t(q0); p.causal = causal;
+  p.scale_log2 = scale * 1.4426950408889634f;
+  p.splits = splits;
+  p.keys_per_split = uint32_t(((keys + splits - 1) / splits + BC - 1) / BC * BC);
+  p.part = g_decode_scratch_ptr[current];
+  static bool attr_set[64] = {};
+  if (!attr_set[current]) {
+    MB_CUDA_OK(ctx, cudaFuncSetAttribute(attn_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, DEC_SMEM));
+    attr_set[current] = true;
+  }
+  dim3 grid(splits, unsigned(kv_heads), unsigned(batch));
+  attn_decode_kernel<<<grid, DEC_THREADS, DEC_SMEM, stream>>>(p);
+  MB_LAUNCH_OK(ctx);
+  if (splits > 1) {
+    attn_combine_kernel<<<unsigned(batch * nq * heads), 128, 0, stream>>>(p.part, p.out, p.nq, p.heads, p.kv_heads, splits);
+    MB_LAUNCH_OK(ctx);
+  }
+  return MB_OK;
+}
