@@ -7,7 +7,8 @@
 //   warp 1   MMA issuer: tcgen05.mma (kind::mxf4nvf4 block-scaled, or kind::f16)
 //            with the accumulator in tensor memory; scale atoms are copied
 //            shared -> TMEM by tcgen05.cp right before the MMAs that read them.
-//   warps 2-5 epilogue: tcgen05.ld the finished accumulator, scale, convert, store.
+//   warps 2-9 epilogue: tcgen05.ld the finished accumulator, scale, convert, store;
+//            two warps per TMEM lane quadrant, each taking half of the columns.
 //
 // Two accumulators alternate so that the epilogue of tile i overlaps the MMAs of
 // tile i+1. TMEM has 512 columns; the NVFP4 kernel also keeps scale factors there,
@@ -56,7 +57,7 @@ struct Cfg {
   static constexpr int SFB_BYTES = KIND == KIND_NVF4 ? (BN / 128) * 2048 : 0;
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES + SFA_BYTES + SFB_BYTES;
   static constexpr int STAGES = (KIND == KIND_NVF4) ? (BN == 256 ? 4 : 6) : (BN == 256 ? 4 : 6);
-  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*alignment*/ + 256 /*barriers*/ + 8192 /*store patches*/;
+  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*alignment*/ + 256 /*barriers*/ + 8 * 1024 /*store patches*/;
   // TMEM columns
   static constexpr bool OVERLAP = (KIND == KIND_NVF4 && BN == 256);
   static constexpr int ACC0 = 0;
@@ -68,8 +69,8 @@ struct Cfg {
   static_assert(KIND == KIND_NVF4 || 2 * BN <= 512, "TMEM budget");
 };
 
-constexpr int NUM_THREADS = 192;
-constexpr int EPI_THREADS = 128;
+constexpr int NUM_THREADS = 320;   // producer warp, MMA warp, eight epilogue warps (two per TMEM lane quadrant)
+constexpr int EPI_THREADS = 256;
 
 __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
   __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
@@ -77,25 +78,22 @@ __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
 }
 
 
-// Warp-level transpose through a 2 KB shared-memory patch so that global stores
-// are coalesced: on entry lane l holds U 16-byte units of ITS row (32 rows, U*16
-// bytes each); on exit every store instruction writes 32/U rows x U*16 contiguous
-// bytes (full 32-byte sectors). The XOR on the unit index keeps both the 128-bit
-// shared stores and loads bank-conflict free.
-template <int U>
-__device__ __forceinline__ void stage_and_store(uint8_t* patch, uint32_t lane, const uint4* units, uint8_t* gbase,
-                                                size_t row_stride_bytes, uint32_t rows_valid, uint32_t units_valid) {
-  constexpr int RPI = 32 / U;                     // rows per store instruction
-  const uint32_t swz_w = U == 4 ? ((lane >> 1) & 3u) : ((lane >> 2) & 1u);
-#pragma unroll
-  for (int u = 0; u < U; ++u)
-    *reinterpret_cast<uint4*>(patch + lane * (U * 16) + ((uint32_t(u) ^ swz_w) * 16)) = units[u];
+// Warp-level transpose through a 1 KB shared-memory patch so that global stores are
+// coalesced: on entry lane l holds two 16-byte units of ITS row (32 rows x 32 bytes);
+// on exit each store instruction writes 16 rows x 32 contiguous bytes (whole sectors).
+// The XOR on the unit index keeps the 128-bit shared stores and loads conflict free.
+__device__ __forceinline__ void stage_and_store(uint8_t* patch, uint32_t lane, const uint4& u0, const uint4& u1,
+                                                uint8_t* gbase, size_t row_stride_bytes, uint32_t rows_valid,
+                                                uint32_t units_valid) {
+  const uint32_t swz_w = (lane >> 2) & 1u;
+  *reinterpret_cast<uint4*>(patch + lane * 32 + ((0u ^ swz_w) * 16)) = u0;
+  *reinterpret_cast<uint4*>(patch + lane * 32 + ((1u ^ swz_w) * 16)) = u1;
   __syncwarp();
 #pragma unroll
-  for (int i = 0; i < U; ++i) {
-    const uint32_t r = i * RPI + lane / U, u = lane % U;
-    const uint32_t swz_r = U == 4 ? ((r >> 1) & 3u) : ((r >> 2) & 1u);
-    uint4 v = *reinterpret_cast<const uint4*>(patch + r * (U * 16) + ((u ^ swz_r) * 16));
+  for (int i = 0; i < 2; ++i) {
+    const uint32_t r = i * 16 + (lane >> 1), u = lane & 1u;
+    const uint32_t swz_r = (r >> 2) & 1u;
+    const uint4 v = *reinterpret_cast<const uint4*>(patch + r * 32 + ((u ^ swz_r) * 16));
     if (r < rows_valid && u < units_valid)
       *reinterpret_cast<uint4*>(gbase + size_t(r) * row_stride_bytes + u * 16) = v;
   }
@@ -264,7 +262,8 @@ gemm_tc5_kernel(const __grid_constant__ GemmParams p) {
   } else {
     // ------------------------------ epilogue ------------------------------------
     const uint32_t quad = warp & 3u;                  // TMEM lane quadrant this warp may read
-    uint8_t* patch = smem_gen + C::STAGES * C::STAGE_BYTES + 256 + quad * 2048;
+    const uint32_t ew = uint32_t(warp) - 2u, half = ew >> 2;   // two warps per quadrant split the columns
+    uint8_t* patch = smem_gen + C::STAGES * C::STAGE_BYTES + 256 + ew * 1024;
     uint32_t it = 0;
     bool ok = true;
     for (uint32_t tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x, ++it) {
@@ -297,13 +296,13 @@ gemm_tc5_kernel(const __grid_constant__ GemmParams p) {
             for (int h = 0; h < 2; ++h) {
               float g = __bfloat162float(__float2bfloat16_rn(__uint_as_float(r[4 * i + 2 * h]) * scale));
               float u = __bfloat162float(__float2bfloat16_rn(__uint_as_float(r[4 * i + 2 * h + 1]) * scale));
-              v[h] = __fdiv_rn(g, 1.0f + expf(-g)) * u;
+              v[h] = __fdividef(g, 1.0f + __expf(-g)) * u;   // fast exp/divide: a bf16 result hides their last bits
             }
             w[i] = pack_bf16x2(v[0], v[1]);
           }
-          uint4 units[2] = {make_uint4(w[0], w[1], w[2], w[3]), make_uint4(w[4], w[5], w[6], w[7])};
           uint8_t* g = static_cast<uint8_t*>(p.out) + (size_t(row0) * p.ldo + col0 / 2) * 2;
-          stage_and_store<2>(patch, lane, units, g, size_t(p.ldo) * 2, rows_valid, min(2u, (p.n - col0) / 16));
+          stage_and_store(patch, lane, make_uint4(w[0], w[1], w[2], w[3]), make_uint4(w[4], w[5], w[6], w[7]), g,
+                          size_t(p.ldo) * 2, rows_valid, min(2u, (p.n - col0) / 16));
         } else if (p.out_dtype == MB_DT_BF16) {
           uint4 units[4];
 #pragma unroll
@@ -314,7 +313,9 @@ gemm_tc5_kernel(const __grid_constant__ GemmParams p) {
             units[g].w = pack_bf16x2(__uint_as_float(r[8 * g + 6]) * scale, __uint_as_float(r[8 * g + 7]) * scale);
           }
           uint8_t* g = static_cast<uint8_t*>(p.out) + (size_t(row0) * p.ldo + col0) * 2;
-          stage_and_store<4>(patch, lane, units, g, size_t(p.ldo) * 2, rows_valid, min(4u, (p.n - col0) / 8));
+          const uint32_t uv = (p.n - col0) / 8;
+          stage_and_store(patch, lane, units[0], units[1], g, size_t(p.ldo) * 2, rows_valid, min(2u, uv));
+          if (uv > 2) stage_and_store(patch, lane, units[2], units[3], g + 32, size_t(p.ldo) * 2, rows_valid, min(2u, uv - 2));
         } else {
           // f32: 32 columns = 128 bytes per row, in two passes of 16 columns through the patch
 #pragma unroll
@@ -330,34 +331,41 @@ gemm_tc5_kernel(const __grid_constant__ GemmParams p) {
             const uint32_t c0 = col0 + 16 * hh;
             if (c0 < p.n) {
               uint8_t* g = static_cast<uint8_t*>(p.out) + (size_t(row0) * p.ldo + c0) * 4;
-              stage_and_store<4>(patch, lane, units, g, size_t(p.ldo) * 4, rows_valid, min(4u, (p.n - c0) / 4));
+              const uint32_t uv = (p.n - c0) / 4;
+              stage_and_store(patch, lane, units[0], units[1], g, size_t(p.ldo) * 4, rows_valid, min(2u, uv));
+              if (uv > 2) stage_and_store(patch, lane, units[2], units[3], g + 32, size_t(p.ldo) * 4, rows_valid, min(2u, uv - 2));
             }
           }
         }
       };
-      int first = 0;
       if (C::OVERLAP) {
-        // The 64 columns shared with the other accumulator come out first, both chunks
-        // before any store work, so that the next tile's MMAs are released at once.
-        const int ca = buf == 0 ? CHUNKS - 2 : 0;
-        uint32_t ra[32], rb[32];
+        // The 64 columns shared with the other accumulator come out first (one chunk per
+        // warp of the quadrant), before any store work, so that the next tile's MMAs are
+        // released at once; the other six chunks follow, three per warp.
+        const int ca = (buf == 0 ? CHUNKS - 2 : 0) + int(half);
+        const int rest0 = (buf == 0 ? 0 : 2) + 3 * int(half);
+        uint32_t ra[32];
         tmem_ld_x32(t_acc + ca * 32, ra);
-        tmem_ld_x32(t_acc + (ca + 1) * 32, rb);
         tmem_ld_wait();
         fence_before_sync();
         mbar_arrive(ovl_free_bar);
         process(ca, ra);
-        process(ca + 1, rb);
-        first = 2;
-      }
 #pragma unroll 1
-      for (int ci = first; ci < CHUNKS; ++ci) {
-        int c = ci;
-        if (C::OVERLAP && buf == 0) c = ci - 2;
-        uint32_t r[32];
-        tmem_ld_x32(t_acc + c * 32, r);
-        tmem_ld_wait();
-        process(c, r);
+        for (int ci = 0; ci < 3; ++ci) {
+          uint32_t r[32];
+          tmem_ld_x32(t_acc + (rest0 + ci) * 32, r);
+          tmem_ld_wait();
+          process(rest0 + ci, r);
+        }
+      } else {
+#pragma unroll 1
+        for (int ci = 0; ci < CHUNKS / 2; ++ci) {
+          const int c = int(half) * (CHUNKS / 2) + ci;
+          uint32_t r[32];
+          tmem_ld_x32(t_acc + c * 32, r);
+          tmem_ld_wait();
+          process(c, r);
+        }
       }
       fence_before_sync();
       mbar_arrive(acc_empty_bar(buf));

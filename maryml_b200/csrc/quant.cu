@@ -53,8 +53,25 @@ __device__ __forceinline__ void quant_block_scaled(const float* v, float s2, uin
   float d = __fmul_rn(mb_e4m3_to_f32(sbyte), s2);
   float q[16];
   if (d > 0.0f) {
+    // x / d, correctly rounded. Fast form: with r = RN(1/d) and q0 = RN(x r), the residual
+    // x - q0 d is exact in one fma and RN(q0 + residual r) is the correctly rounded quotient
+    // (Markstein), as long as d's significand is not all ones, nothing leaves the normal
+    // range and the block holds no infinity; otherwise the divide instruction itself.
+    const uint32_t db = __float_as_uint(d);
+    const bool fast = (db & 0x7FFFFFu) != 0x7FFFFFu && d >= 5.4210108624275222e-20f && d <= 1.8446744073709552e19f &&
+                      bamax <= 3.4028234663852886e38f;
+    if (fast) {
+      const float r = __frcp_rn(d);
 #pragma unroll
-    for (int i = 0; i < 16; ++i) q[i] = __fdiv_rn(v[i], d);
+      for (int i = 0; i < 16; ++i) {
+        const float q0 = __fmul_rn(v[i], r);
+        const float rem = __fmaf_rn(-q0, d, v[i]);
+        q[i] = __fmaf_rn(rem, r, q0);
+      }
+    } else {
+#pragma unroll
+      for (int i = 0; i < 16; ++i) q[i] = __fdiv_rn(v[i], d);
+    }
     codes.x = mb_cvt_e2m1x8(q);
     codes.y = mb_cvt_e2m1x8(q + 8);
   } else {
