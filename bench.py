@@ -17,6 +17,15 @@ restatement of the reference's CPU lane timed on a bounded sample.
 
 With N > 1 (torchrun) every rank runs an independent replica of the step: the GEMM
 sweep does not shard (no collective on this path), so scaling is weak.
+
+Other rows of the hot path have their own workloads (same JSON contract, their own metric):
+
+    --workload moe           config 2: 4096 tokens, hidden 2048, 128 experts, top-8 (tokens/s)
+    --workload attn_decode   config 3: batch 32 x 1 query over 32768 keys (GB/s of K/V read)
+    --workload attn_prefill  config 3: batch 4 x 8192 causal (TFLOP/s)
+    --workload tp_decode     config 4: decoder layer, batch 64 over a 4096-token cache (tokens/s),
+    --workload tp_prefill    config 4: decoder layer, 8192-token prefill (tokens/s); both shard over
+                             --gpus N ranks (strong scaling, two NCCL all-reduces per layer)
 """
 import argparse
 import json
@@ -66,7 +75,7 @@ class ClockSampler:
     def start(self):
         try:
             self.proc = subprocess.Popen(
-                ["nvidia-smi", f"--id={self.gpu}", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "100"],
+                ["nvidia-smi", f"--id={self.gpu}", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "50"],
                 stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             threading.Thread(target=self._pump, daemon=True).start()
         except Exception:
@@ -286,7 +295,7 @@ def run_ours(args, rank, world, local_rank):
     d2h = sum(M * q.n() * 2 for q in weights)
 
     if rank == 0:
-        cpu = cpu_lane(32, repeats=1)
+        cpu = cpu_lane(256, repeats=1)
         cpu_tflops = cpu["flops"] / cpu["seconds"][0] / 1e12
         value = world * step_flops() * args.steps / (ms * 1e-3) / 1e12
         line = {
@@ -313,20 +322,219 @@ def run_ours(args, rank, world, local_rank):
         dist.destroy_process_group()
 
 
+# --------------------------------------------------------------------------------------
+# Other workloads of the hot path
+# --------------------------------------------------------------------------------------
+def _time_steps(step, steps, warmup, stream, barrier, sampler):
+    import torch
+    for _ in range(max(warmup, 3)):
+        step()
+    barrier()
+    if sampler:
+        sampler.start()
+    t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t0.record(stream)
+    for _ in range(steps):
+        step()
+    t1.record(stream)
+    barrier()
+    clocks = sampler.stop() if sampler else None
+    return t0.elapsed_time(t1), clocks
+
+
+def run_other(args, rank, world, local_rank):
+    import math
+    import torch
+    import torch.distributed as dist
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    from maryml_b200 import nvfp4 as mb, moe, attention as att, layer, _lib
+    ctx = _lib.context(local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    stream = torch.cuda.current_stream()
+    g = torch.Generator(device=dev)
+    g.manual_seed(99)
+    peaks = measured_peaks()
+    sampler = ClockSampler(local_rank) if rank == 0 else None
+    wl = args.workload
+    extra = {}
+    if wl == "moe":
+        T, h, inter, E, K = 4096, 2048, 768, 128, 8
+        x = torch.randn(T, h, device=dev, generator=g).to(torch.bfloat16)
+        gate = (torch.randn(E, h, device=dev, generator=g) * 0.02).to(torch.bfloat16)
+        b13 = moe.ExpertBank.quantize((torch.randn(E, 2 * inter, h, device=dev, generator=g) * 0.02).to(torch.bfloat16))
+        b2 = moe.ExpertBank.quantize((torch.randn(E, h, inter, device=dev, generator=g) * 0.02).to(torch.bfloat16))
+        step = lambda: moe.moe_layer(x, gate, K, b13, b2)
+        units, metric, unit = T, "moe_layer_tokens_per_s", "tokens/s"
+        flop = T * K * 2 * (h * 2 * inter + inter * h) + 2 * T * h * E
+        byts = (E * (2 * inter * h + h * inter)) * 0.5625 + T * h * 2 + T * h * 4 + E * h * 2
+        h2d, d2h = T * h * 2, T * h * 4
+        hx = x.cpu().pin_memory()
+        hy = torch.empty(T, h, dtype=torch.float32).pin_memory()
+        dx = torch.empty_like(x)
+
+        def e2e():
+            dx.copy_(hx, non_blocking=True)
+            out, _ = moe.moe_layer(dx, gate, K, b13, b2)
+            hy.copy_(out, non_blocking=True)
+        roof = lambda ms: {"bound": "hbm", "kernel": "whole layer (9 launches)", "achieved": byts / (ms * 1e-3) / 1e9,
+                           "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": byts / (ms * 1e-3) / 1e9 / peaks["hbm_gbs"],
+                           "peak_source": peaks["source"], "traffic": None, "flop_per_step": flop,
+                           "note": "min bytes = expert planes + x + out; the layer is weight-streaming bound at 4096 tokens"}
+        cfg = {"workload": "moe_layer_T4096_h2048_E128_top8_inter768", "lane": "bf16 intermediates, fused SwiGLU"}
+        launches = 14
+    elif wl in ("attn_decode", "attn_prefill"):
+        H, KVH, D = 32, 8, 128
+        if wl == "attn_decode":
+            B, nq, L = 32, 1, 32768
+        else:
+            B, nq, L = 4, 8192, 8192
+        if args.batch:
+            B = args.batch
+        q = torch.randn(B, nq, H, D, device=dev, generator=g).to(torch.bfloat16)
+        k = torch.randn(B, L, KVH, D, device=dev, generator=g).to(torch.bfloat16)
+        v = torch.randn(B, L, KVH, D, device=dev, generator=g).to(torch.bfloat16)
+        ws = torch.empty(max(int(_lib.lib.mb_attention_workspace(B, nq, L, H, KVH, D)), 16), dtype=torch.uint8, device=dev)
+        step = lambda: att.flash_attention(q, k, v, q0=L - nq, workspace=ws)
+        hq = q.cpu().pin_memory()
+        ho = torch.empty_like(hq).pin_memory()
+        dq = torch.empty_like(q)
+
+        def e2e():
+            dq.copy_(hq, non_blocking=True)
+            ho.copy_(att.flash_attention(dq, k, v, q0=L - nq, workspace=ws), non_blocking=True)
+        h2d = d2h = q.numel() * 2
+        if wl == "attn_decode":
+            byts = 2 * B * L * KVH * D * 2
+            units, metric, unit = byts / 1e9, "decode_attention_kv_gbytes_per_s", "GB/s"
+            roof = lambda ms: {"bound": "hbm", "kernel": "attn_decode_kernel", "achieved": byts / (ms * 1e-3) / 1e9,
+                               "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                               "frac": byts / (ms * 1e-3) / 1e9 / peaks["hbm_gbs"], "peak_source": peaks["source"],
+                               "frac_of_nominal_8tbs": byts / (ms * 1e-3) / 1e9 / 8000.0, "traffic": None}
+            launches = 2
+        else:
+            flop = 4.0 * B * H * nq * L * D / 2
+            units, metric, unit = flop / 1e12, "prefill_attention_tflops", "TFLOP/s"
+            roof = lambda ms: {"bound": "tensor", "kernel": "attn_prefill_kernel (mma.sync)", "achieved": flop / (ms * 1e-3) / 1e12,
+                               "peak": peaks["bf16"], "unit": "TFLOP/s", "frac": flop / (ms * 1e-3) / 1e12 / peaks["bf16"],
+                               "peak_source": peaks["source"], "traffic": None}
+            launches = 1
+        cfg = {"workload": f"{wl}_B{B}_nq{nq}_keys{L}_heads32_kv8_d128", "rope": "pre-applied (inputs drawn N(0,1))"}
+    else:
+        cfgL = layer.LayerConfig()
+        decode = wl == "tp_decode"
+        batch, t, past = (64, 1, 4096) if decode else (1, 8192, 0)
+        tp = layer.Tp(rank, world)
+
+        def exchange(raw):
+            obj = [raw]
+            dist.broadcast_object_list(obj, src=0)
+            return obj[0]
+        group = layer.Group(tp, local_rank, exchange) if world > 1 else None
+        D = cfgL.head_dim
+        shapes = {"q": (cfgL.heads * D, cfgL.hidden), "k": (cfgL.kv_heads * D, cfgL.hidden),
+                  "v": (cfgL.kv_heads * D, cfgL.hidden), "o": (cfgL.hidden, cfgL.heads * D),
+                  "gate": (cfgL.inter, cfgL.hidden), "up": (cfgL.inter, cfgL.hidden), "down": (cfgL.hidden, cfgL.inter)}
+        gw = torch.Generator(device=dev)
+        gw.manual_seed(7)          # the same stored tensors on every rank, cut after quantisation
+        full = {}
+        for name, (n, kk) in shapes.items():
+            qz = mb.Nvfp4.quantize((torch.randn(n, kk, device=dev, generator=gw) * 0.02).to(torch.bfloat16))
+            full[name] = (qz.codes, qz.scales, qz.scale2)
+        gain = torch.ones(cfgL.hidden, dtype=torch.bfloat16, device=dev)
+        L_ = layer.DecoderLayer(cfgL, full, gain, gain, tp=tp, group=group, device=dev)
+        del full
+        cap = past + t
+        x = torch.randn(batch * t, cfgL.hidden, device=dev, generator=gw).to(torch.bfloat16)
+        kc = torch.randn(batch, cap, L_.local_kv_heads, D, device=dev, generator=g).to(torch.bfloat16)
+        vc = torch.randn(batch, cap, L_.local_kv_heads, D, device=dev, generator=g).to(torch.bfloat16)
+        step = lambda: L_.forward(x, batch, past, kc, vc)
+        hx = x.cpu().pin_memory()
+        hy = torch.empty_like(hx).pin_memory()
+        dx = torch.empty_like(x)
+
+        def e2e():
+            dx.copy_(hx, non_blocking=True)
+            hy.copy_(L_.forward(dx, batch, past, kc, vc), non_blocking=True)
+        h2d = d2h = x.numel() * 2
+        units, metric, unit = batch * t, f"tp_layer_{'decode' if decode else 'prefill'}_tokens_per_s", "tokens/s"
+        params = sum(n * kk for (n, kk) in shapes.values())
+        if decode:
+            byts = (params * 0.5625 + 2 * batch * cap * cfgL.kv_heads * D * 2) / world
+            roof = lambda ms: {"bound": "hbm", "kernel": "whole layer per rank", "achieved": byts / (ms * 1e-3) / 1e9,
+                               "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": byts / (ms * 1e-3) / 1e9 / peaks["hbm_gbs"],
+                               "peak_source": peaks["source"], "traffic": None,
+                               "note": "weights + KV per rank; 2 all-reduces of [64,4096] f32 are latency terms"}
+        else:
+            flop = (2.0 * t * params + 4.0 * cfgL.heads * t * t * D / 2) / world
+            roof = lambda ms: {"bound": "tensor", "kernel": "whole layer per rank", "achieved": flop / (ms * 1e-3) / 1e12,
+                               "peak": 4 * peaks["bf16"], "unit": "TFLOP/s", "frac": flop / (ms * 1e-3) / 1e12 / (4 * peaks["bf16"]),
+                               "peak_source": "4 x " + peaks["source"] + " bf16 burst", "traffic": None,
+                               "note": "projections at the FP4 rate dominate; attention runs at the bf16 rate"}
+        cfg = {"workload": f"{wl}_hidden4096_heads32_kv8_ffn14336_batch{batch}_t{t}_past{past}", "parallelism": f"tp{world}"}
+        launches = 30
+
+    ms, clocks = _time_steps(step, args.steps, args.warmup, stream, barrier, sampler)
+    e2e()
+    barrier()
+    n_e2e = max(2, min(args.steps, 5))
+    s0, s1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    s0.record(stream)
+    for _ in range(n_e2e):
+        e2e()
+    s1.record(stream)
+    barrier()
+    e2e_ms = s0.elapsed_time(s1)
+    if world > 1:
+        tms = torch.tensor([ms, e2e_ms], device=dev)
+        dist.all_reduce(tms, op=dist.ReduceOp.MAX)
+        ms, e2e_ms = float(tms[0].item()), float(tms[1].item())
+    rc, flags = ctx.check_flags(None)
+    if rc != 0:
+        raise SystemExit(f"bench.py: device status words set: {flags}")
+    tp_like = wl.startswith("tp_")
+    mult = 1 if tp_like else world          # the TP layer is one job over all ranks; the others are replicas
+    if rank == 0:
+        per_step = ms / args.steps
+        line = {"metric": metric, "value": mult * units / (per_step * 1e-3), "unit": unit, "n_gpus": world,
+                "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": per_step, "higher_is_better": True,
+                "scaling": "strong" if tp_like else "weak", "vs_baseline": None, "dtype": "nvfp4/bf16, f32 accumulate",
+                "data": "synthetic", "config": cfg, "clocks": clocks,
+                "e2e": {"value": mult * units / (e2e_ms / n_e2e * 1e-3), "unit": unit, "h2d_bytes_per_step": h2d,
+                        "d2h_bytes_per_step": d2h},
+                "gpu_launches": launches * args.steps, "roofline": roof(per_step),
+                "cpu_baseline": None}
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
 def main():
     ap = argparse.ArgumentParser()
+    ap.add_argument("--workload", default="gemm",
+                    choices=["gemm", "moe", "attn_decode", "attn_prefill", "tp_decode", "tp_prefill"])
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--steps", type=int, default=1000)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--batch", type=int, default=0, help="override the batch of the attention workloads (profiling)")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     if args.impl == "reference":
         run_reference(args, rank, world)
-    else:
+    elif args.workload == "gemm":
         run_ours(args, rank, world, local_rank)
+    else:
+        run_other(args, rank, world, local_rank)
 
 
 if __name__ == "__main__":
