@@ -309,7 +309,7 @@ def run_ours(args, rank, world, local_rank):
             "e2e": {"value": world * step_flops() * e2e_steps / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s",
                     "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
             "gpu_launches": launches_per_step * args.steps,
-            "roofline": {"bound": "tensor", "kernel": "gemm_tc5_kernel<NVF4,256>", "achieved": achieved,
+            "roofline": {"bound": "tensor", "kernel": "gemm_tc5_pair_kernel (cta_group::2, 256x256 tiles)", "achieved": achieved,
                          "peak": fp4_peak, "unit": "TFLOP/s", "frac": achieved / fp4_peak,
                          "peak_source": f"4 x {peaks['source']} bf16 burst ({peaks['bf16']} TFLOP/s): no FP4 figure "
                                         f"in MEASURED_PEAKS.json",
@@ -481,6 +481,22 @@ def run_other(args, rank, world, local_rank):
         cfg = {"workload": f"{wl}_hidden4096_heads32_kv8_ffn14336_batch{batch}_t{t}_past{past}", "parallelism": f"tp{world}"}
         launches = 30
 
+    if args.graph:
+        # Serving mode: the step is captured once into a CUDA graph (kernels, memsets and the NCCL
+        # all-reduces alike) and replayed, which takes the host's ~30 launches per layer off the clock.
+        side = torch.cuda.Stream()
+        side.wait_stream(stream)
+        with torch.cuda.stream(side):
+            for _ in range(3):
+                step()
+        stream.wait_stream(side)
+        barrier()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            step()
+        captured = step
+        step = graph.replay
+        cfg["launch"] = "cuda graph replay"
     ms, clocks = _time_steps(step, args.steps, args.warmup, stream, barrier, sampler)
     e2e()
     barrier()
@@ -524,6 +540,7 @@ def main():
     ap.add_argument("--steps", type=int, default=1000)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--graph", action="store_true", help="capture the step into a CUDA graph and time replays")
     ap.add_argument("--batch", type=int, default=0, help="override the batch of the attention workloads (profiling)")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))

@@ -100,6 +100,63 @@ __device__ __forceinline__ void stage_and_store(uint8_t* patch, uint32_t lane, c
   __syncwarp();
 }
 
+// One 32-column chunk of one warp's 32 accumulator rows: scale, convert, transpose, store.
+__device__ __forceinline__ void epilogue_chunk(const GemmParams& p, const uint32_t* r, uint32_t col0, uint32_t row0,
+                                               uint32_t rows_valid, float scale, uint8_t* patch, uint32_t lane) {
+      if (col0 >= p.n) return;       // warp-uniform
+      if (p.epilogue == MB_EPI_SWIGLU_INTERLEAVED) {
+        // (gate, up) pairs -> bf16(silu(bf16 gate) * bf16 up); 16 outputs = 2 units per row.
+        uint32_t w[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          float v[2];
+#pragma unroll
+          for (int h = 0; h < 2; ++h) {
+            float g = __bfloat162float(__float2bfloat16_rn(__uint_as_float(r[4 * i + 2 * h]) * scale));
+            float u = __bfloat162float(__float2bfloat16_rn(__uint_as_float(r[4 * i + 2 * h + 1]) * scale));
+            v[h] = __fdividef(g, 1.0f + __expf(-g)) * u;   // fast exp/divide: a bf16 result hides their last bits
+          }
+          w[i] = pack_bf16x2(v[0], v[1]);
+        }
+        uint8_t* g = static_cast<uint8_t*>(p.out) + (size_t(row0) * p.ldo + col0 / 2) * 2;
+        stage_and_store(patch, lane, make_uint4(w[0], w[1], w[2], w[3]), make_uint4(w[4], w[5], w[6], w[7]), g,
+                        size_t(p.ldo) * 2, rows_valid, min(2u, (p.n - col0) / 16));
+      } else if (p.out_dtype == MB_DT_BF16) {
+        uint4 units[4];
+#pragma unroll
+        for (int g = 0; g < 4; ++g) {
+          units[g].x = pack_bf16x2(__uint_as_float(r[8 * g + 0]) * scale, __uint_as_float(r[8 * g + 1]) * scale);
+          units[g].y = pack_bf16x2(__uint_as_float(r[8 * g + 2]) * scale, __uint_as_float(r[8 * g + 3]) * scale);
+          units[g].z = pack_bf16x2(__uint_as_float(r[8 * g + 4]) * scale, __uint_as_float(r[8 * g + 5]) * scale);
+          units[g].w = pack_bf16x2(__uint_as_float(r[8 * g + 6]) * scale, __uint_as_float(r[8 * g + 7]) * scale);
+        }
+        uint8_t* g = static_cast<uint8_t*>(p.out) + (size_t(row0) * p.ldo + col0) * 2;
+        const uint32_t uv = (p.n - col0) / 8;
+        stage_and_store(patch, lane, units[0], units[1], g, size_t(p.ldo) * 2, rows_valid, min(2u, uv));
+        if (uv > 2) stage_and_store(patch, lane, units[2], units[3], g + 32, size_t(p.ldo) * 2, rows_valid, min(2u, uv - 2));
+      } else {
+        // f32: 32 columns = 128 bytes per row, in two passes of 16 columns through the patch
+#pragma unroll
+        for (int hh = 0; hh < 2; ++hh) {
+          uint4 units[4];
+#pragma unroll
+          for (int g = 0; g < 4; ++g) {
+            units[g].x = __float_as_uint(__uint_as_float(r[16 * hh + 4 * g + 0]) * scale);
+            units[g].y = __float_as_uint(__uint_as_float(r[16 * hh + 4 * g + 1]) * scale);
+            units[g].z = __float_as_uint(__uint_as_float(r[16 * hh + 4 * g + 2]) * scale);
+            units[g].w = __float_as_uint(__uint_as_float(r[16 * hh + 4 * g + 3]) * scale);
+          }
+          const uint32_t c0 = col0 + 16 * hh;
+          if (c0 < p.n) {
+            uint8_t* g = static_cast<uint8_t*>(p.out) + (size_t(row0) * p.ldo + c0) * 4;
+            const uint32_t uv = (p.n - c0) / 4;
+            stage_and_store(patch, lane, units[0], units[1], g, size_t(p.ldo) * 4, rows_valid, min(2u, uv));
+            if (uv > 2) stage_and_store(patch, lane, units[2], units[3], g + 32, size_t(p.ldo) * 4, rows_valid, min(2u, uv - 2));
+          }
+        }
+      }
+}
+
 template <int KIND, int BN>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_tc5_kernel(const __grid_constant__ GemmParams p) {
@@ -284,59 +341,7 @@ gemm_tc5_kernel(const __grid_constant__ GemmParams p) {
       const uint32_t t_acc = tmem_base + ((quad * 32u) << 16) + (buf ? C::ACC1 : C::ACC0);
       constexpr int CHUNKS = BN / 32;
       auto process = [&](int c, const uint32_t* r) {
-        const uint32_t col0 = nt * BN + c * 32;
-        if (col0 >= p.n) return;       // warp-uniform
-        if (p.epilogue == MB_EPI_SWIGLU_INTERLEAVED) {
-          // (gate, up) pairs -> bf16(silu(bf16 gate) * bf16 up); 16 outputs = 2 units per row.
-          uint32_t w[8];
-#pragma unroll
-          for (int i = 0; i < 8; ++i) {
-            float v[2];
-#pragma unroll
-            for (int h = 0; h < 2; ++h) {
-              float g = __bfloat162float(__float2bfloat16_rn(__uint_as_float(r[4 * i + 2 * h]) * scale));
-              float u = __bfloat162float(__float2bfloat16_rn(__uint_as_float(r[4 * i + 2 * h + 1]) * scale));
-              v[h] = __fdividef(g, 1.0f + __expf(-g)) * u;   // fast exp/divide: a bf16 result hides their last bits
-            }
-            w[i] = pack_bf16x2(v[0], v[1]);
-          }
-          uint8_t* g = static_cast<uint8_t*>(p.out) + (size_t(row0) * p.ldo + col0 / 2) * 2;
-          stage_and_store(patch, lane, make_uint4(w[0], w[1], w[2], w[3]), make_uint4(w[4], w[5], w[6], w[7]), g,
-                          size_t(p.ldo) * 2, rows_valid, min(2u, (p.n - col0) / 16));
-        } else if (p.out_dtype == MB_DT_BF16) {
-          uint4 units[4];
-#pragma unroll
-          for (int g = 0; g < 4; ++g) {
-            units[g].x = pack_bf16x2(__uint_as_float(r[8 * g + 0]) * scale, __uint_as_float(r[8 * g + 1]) * scale);
-            units[g].y = pack_bf16x2(__uint_as_float(r[8 * g + 2]) * scale, __uint_as_float(r[8 * g + 3]) * scale);
-            units[g].z = pack_bf16x2(__uint_as_float(r[8 * g + 4]) * scale, __uint_as_float(r[8 * g + 5]) * scale);
-            units[g].w = pack_bf16x2(__uint_as_float(r[8 * g + 6]) * scale, __uint_as_float(r[8 * g + 7]) * scale);
-          }
-          uint8_t* g = static_cast<uint8_t*>(p.out) + (size_t(row0) * p.ldo + col0) * 2;
-          const uint32_t uv = (p.n - col0) / 8;
-          stage_and_store(patch, lane, units[0], units[1], g, size_t(p.ldo) * 2, rows_valid, min(2u, uv));
-          if (uv > 2) stage_and_store(patch, lane, units[2], units[3], g + 32, size_t(p.ldo) * 2, rows_valid, min(2u, uv - 2));
-        } else {
-          // f32: 32 columns = 128 bytes per row, in two passes of 16 columns through the patch
-#pragma unroll
-          for (int hh = 0; hh < 2; ++hh) {
-            uint4 units[4];
-#pragma unroll
-            for (int g = 0; g < 4; ++g) {
-              units[g].x = __float_as_uint(__uint_as_float(r[16 * hh + 4 * g + 0]) * scale);
-              units[g].y = __float_as_uint(__uint_as_float(r[16 * hh + 4 * g + 1]) * scale);
-              units[g].z = __float_as_uint(__uint_as_float(r[16 * hh + 4 * g + 2]) * scale);
-              units[g].w = __float_as_uint(__uint_as_float(r[16 * hh + 4 * g + 3]) * scale);
-            }
-            const uint32_t c0 = col0 + 16 * hh;
-            if (c0 < p.n) {
-              uint8_t* g = static_cast<uint8_t*>(p.out) + (size_t(row0) * p.ldo + c0) * 4;
-              const uint32_t uv = (p.n - c0) / 4;
-              stage_and_store(patch, lane, units[0], units[1], g, size_t(p.ldo) * 4, rows_valid, min(2u, uv));
-              if (uv > 2) stage_and_store(patch, lane, units[2], units[3], g + 32, size_t(p.ldo) * 4, rows_valid, min(2u, uv - 2));
-            }
-          }
-        }
+        epilogue_chunk(p, r, nt * BN + c * 32, row0, rows_valid, scale, patch, lane);
       };
       if (C::OVERLAP) {
         // The 64 columns shared with the other accumulator come out first (one chunk per
@@ -378,6 +383,207 @@ gemm_tc5_kernel(const __grid_constant__ GemmParams p) {
   if (warp == 1) {
     fence_after_sync();
     tmem_dealloc(tmem_base, C::TMEM_COLS);
+  }
+}
+
+
+// ---------------------------------------------------------------------------------
+// CTA-pair variant (cta_group::2): one 256 x 256 output tile per pair of CTAs.
+//
+// Each CTA of the pair loads its own 128 rows of A, its own half (128 rows) of the B
+// tile, its own A scales and the B scales of all 256 columns; the leader CTA issues
+// one 256 x 256 x 64 MMA per K block for both tensor cores, so that per SM only
+// 128 + 128 operand rows cross L2 -> shared memory per K step instead of 128 + 256.
+// No load is multicast: every CTA fetches what lands in its own shared memory; only
+// the completion counts (leader's barrier) and tcgen05.commit cross the pair.
+// ---------------------------------------------------------------------------------
+struct Cfg2 {
+  static constexpr int BN = 256;
+  static constexpr int A_BYTES = 128 * 128;
+  static constexpr int B_BYTES = 128 * 128;          // this CTA's half of the B tile
+  static constexpr int SFA_BYTES = 2048;
+  static constexpr int SFB_BYTES = 4096;             // scales of all 256 columns
+  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES + SFA_BYTES + SFB_BYTES;   // 38 KB
+  static constexpr int STAGES = 5;
+  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + 256 + 8 * 1024;
+  static constexpr int ACC0 = 0, ACC1 = 192, SFA_COL = 448, SFB_COL = 464, TMEM_COLS = 512;
+};
+
+struct Gemm2Params {
+  GemmParams g;
+  CUtensorMap tmap_sfa;   // tiled scale planes as [atoms, 128 x int32], box 4 atoms
+  CUtensorMap tmap_sfb;
+  uint32_t m_pairs;
+};
+
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREADS, 1)
+gemm_tc5_pair_kernel(const __grid_constant__ Gemm2Params pp) {
+  using C = Cfg2;
+  const GemmParams& p = pp.g;
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
+  const uint32_t bar_base = smem_base + C::STAGES * C::STAGE_BYTES;
+  auto full_bar = [&](int s) { return bar_base + 8u * s; };
+  auto empty_bar = [&](int s) { return bar_base + 8u * (C::STAGES + s); };
+  auto acc_full_bar = [&](int b) { return bar_base + 8u * (2 * C::STAGES + b); };
+  const uint32_t ovl_free_bar = bar_base + 8u * (2 * C::STAGES + 2);
+  const uint32_t drain_bar = bar_base + 8u * (2 * C::STAGES + 3);
+  uint32_t* tmem_ptr_smem = reinterpret_cast<uint32_t*>(smem_gen + C::STAGES * C::STAGE_BYTES + 8 * (2 * C::STAGES + 4));
+  volatile int* abort_smem = reinterpret_cast<volatile int*>(tmem_ptr_smem + 1);
+
+  const int warp = __shfl_sync(0xFFFFFFFFu, int(threadIdx.x >> 5), 0);
+  const uint32_t lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();
+  const bool leader = rank == 0;
+  int* tflag = p.flags ? p.flags + MB_FLAG_WAIT_TIMEOUT : nullptr;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < C::STAGES; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
+    for (int b = 0; b < 2; ++b) mbar_init(acc_full_bar(b), 1);
+    mbar_init(ovl_free_bar, 16);       // one arrival per epilogue warp of both CTAs
+    mbar_init(drain_bar, 1);
+    *abort_smem = 0;
+    fence_barrier_init();
+    tma_prefetch_desc(&p.tmap_a);
+    tma_prefetch_desc(&p.tmap_b);
+    tma_prefetch_desc(&pp.tmap_sfa);
+    tma_prefetch_desc(&pp.tmap_sfb);
+  }
+  if (warp == 1) {
+    tmem_alloc_pair(smem_u32(tmem_ptr_smem), C::TMEM_COLS);
+    tmem_relinquish_pair();
+  }
+  fence_before_sync();
+  __syncthreads();
+  cluster_sync_all();                  // the peer's barriers exist before anything is signalled on them
+  fence_after_sync();
+  const uint32_t tmem_base = *tmem_ptr_smem;
+
+  const uint32_t total_tiles = pp.m_pairs * p.n_tiles;
+  const uint32_t pair = blockIdx.x >> 1, n_pairs = gridDim.x >> 1;
+
+  if (warp == 0) {
+    // ------------------------------ producer (both CTAs) --------------------------
+    int stage = 0;
+    uint32_t phase = 0;
+    bool ok = true;
+    for (uint32_t tile = pair; ok && tile < total_tiles; tile += n_pairs) {
+      const uint32_t mp = tile % pp.m_pairs, nt = tile / pp.m_pairs;
+      const uint32_t mt = mp * 2 + rank;                         // this CTA's 128-row tile of A
+      for (uint32_t ks = 0; ks < p.k_steps; ++ks) {
+        if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_smem, tflag, 21)) { ok = false; break; }
+        const uint32_t sa = smem_base + stage * C::STAGE_BYTES;
+        const uint32_t sb = sa + C::A_BYTES;
+        const uint32_t ssfa = sb + C::B_BYTES;
+        const uint32_t ssfb = ssfa + C::SFA_BYTES;
+        if (elect_one()) {
+          // all bytes of both CTAs are counted on the leader's barrier
+          const uint32_t fb = map_to_cta(full_bar(stage), 0);
+          if (leader) mbar_arrive_expect_tx(full_bar(stage), 2 * C::STAGE_BYTES);
+          tma_load_2d_pair(sa, &p.tmap_a, int(ks * 128), int(mt * 128), fb);
+          tma_load_2d_pair(sb, &p.tmap_b, int(ks * 128), int(nt * C::BN + rank * 128), fb);
+          tma_load_2d_pair(ssfa, &pp.tmap_sfa, 0, int(mt * p.sf_kchunks + ks * 4u), fb);
+          tma_load_2d_pair(ssfb, &pp.tmap_sfb, 0, int((nt * 2) * p.sf_kchunks + ks * 4u), fb);
+          tma_load_2d_pair(ssfb + 2048, &pp.tmap_sfb, 0, int((nt * 2 + 1) * p.sf_kchunks + ks * 4u), fb);
+        }
+        __syncwarp();
+        if (++stage == C::STAGES) { stage = 0; phase ^= 1u; }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------ MMA issuer (leader CTA only) ------------------
+    if (leader) {
+      int stage = 0;
+      uint32_t phase = 0;
+      const uint32_t idesc = idesc_nvf4(C::BN, 256);
+      uint32_t it = 0;
+      bool ok = true;
+      for (uint32_t tile = pair; ok && tile < total_tiles; tile += n_pairs, ++it) {
+        const uint32_t buf = it & 1u;
+        if (it > 0 && !mbar_wait_cluster(ovl_free_bar, (it - 1u) & 1u, abort_smem, tflag, 22)) { ok = false; break; }
+        fence_after_sync();
+        const uint32_t d_tmem = tmem_base + (buf ? C::ACC1 : C::ACC0);
+        for (uint32_t ks = 0; ks < p.k_steps; ++ks) {
+          if (!mbar_wait_cluster(full_bar(stage), phase, abort_smem, tflag, 23)) { ok = false; break; }
+          fence_after_sync();
+          const uint32_t sa = smem_base + stage * C::STAGE_BYTES;
+          const uint32_t sb = sa + C::A_BYTES;
+          const uint32_t ssfa = sb + C::B_BYTES;
+          const uint32_t ssfb = ssfa + C::SFA_BYTES;
+          if (elect_one()) {
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              utccp_32x128b_warpx4_pair(tmem_base + C::SFA_COL + 4 * j, make_sf_desc(ssfa + 512 * j));
+              utccp_32x128b_warpx4_pair(tmem_base + C::SFB_COL + j * 8, make_sf_desc(ssfb + 512 * j));
+              utccp_32x128b_warpx4_pair(tmem_base + C::SFB_COL + j * 8 + 4, make_sf_desc(ssfb + 2048 + 512 * j));
+            }
+            const uint64_t adesc = make_kmajor_sw128_desc(sa);
+            const uint64_t bdesc = make_kmajor_sw128_desc(sb);
+#pragma unroll
+            for (int j = 0; j < 4; ++j)
+              mma_nvf4_pair(d_tmem, adesc + 2 * j, bdesc + 2 * j, idesc, tmem_base + C::SFA_COL + 4 * j,
+                            tmem_base + C::SFB_COL + j * 8, (ks | uint32_t(j)) != 0u);
+            umma_commit_pair(empty_bar(stage), 3);                 // frees the stage in both CTAs
+            if (ks + 1 == p.k_steps) umma_commit_pair(acc_full_bar(buf), 3);
+          }
+          __syncwarp();
+          if (++stage == C::STAGES) { stage = 0; phase ^= 1u; }
+        }
+      }
+      if (!ok) {
+        if (elect_one()) umma_commit(drain_bar);
+        __syncwarp();
+        long long t0 = clock64();
+        while (!mbar_try_wait(drain_bar, 0u) && clock64() - t0 < WAIT_LIMIT_CYCLES) {}
+      }
+    }
+  } else {
+    // ------------------------------ epilogue (both CTAs) --------------------------
+    const uint32_t quad = warp & 3u;
+    const uint32_t ew = uint32_t(warp) - 2u, half = ew >> 2;
+    uint8_t* patch = smem_gen + C::STAGES * C::STAGE_BYTES + 256 + ew * 1024;
+    const uint32_t ovl_remote = map_to_cta(ovl_free_bar, 0);
+    uint32_t it = 0;
+    bool ok = true;
+    for (uint32_t tile = pair; ok && tile < total_tiles; tile += n_pairs, ++it) {
+      const uint32_t mp = tile % pp.m_pairs, nt = tile / pp.m_pairs;
+      const uint32_t buf = it & 1u;
+      const uint32_t row0 = (mp * 2 + rank) * 128 + quad * 32u;
+      const uint32_t row = row0 + lane;
+      const uint32_t rows_valid = row0 < p.m ? min(32u, p.m - row0) : 0u;
+      float scale = p.alpha;
+      if (p.rowscale && row < p.m) scale = p.rowscale[row] * p.alpha;
+      if (!mbar_wait_cluster(acc_full_bar(buf), (it >> 1) & 1u, abort_smem, tflag, 24)) { ok = false; break; }
+      fence_after_sync();
+      const uint32_t t_acc = tmem_base + ((quad * 32u) << 16) + (buf ? C::ACC1 : C::ACC0);
+      constexpr int CHUNKS = C::BN / 32;
+      const int ca = (buf == 0 ? CHUNKS - 2 : 0) + int(half);
+      const int rest0 = (buf == 0 ? 0 : 2) + 3 * int(half);
+      uint32_t ra[32];
+      tmem_ld_x32(t_acc + ca * 32, ra);
+      tmem_ld_wait();
+      fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_cluster(ovl_remote);              // this warp has read its shared columns
+      epilogue_chunk(p, ra, nt * C::BN + ca * 32, row0, rows_valid, scale, patch, lane);
+#pragma unroll 1
+      for (int ci = 0; ci < 3; ++ci) {
+        uint32_t r[32];
+        tmem_ld_x32(t_acc + (rest0 + ci) * 32, r);
+        tmem_ld_wait();
+        epilogue_chunk(p, r, nt * C::BN + (rest0 + ci) * 32, row0, rows_valid, scale, patch, lane);
+      }
+    }
+  }
+
+  // ------------------------------ teardown ----------------------------------------
+  fence_before_sync();
+  __syncthreads();
+  cluster_sync_all();                  // neither CTA leaves while the peer may still touch it
+  if (warp == 1) {
+    fence_after_sync();
+    tmem_dealloc_pair(tmem_base, C::TMEM_COLS);
   }
 }
 
@@ -435,6 +641,50 @@ int launch(mb_ctx* ctx, cudaStream_t stream, const GemmParams& p, uint32_t max_t
   return MB_OK;
 }
 
+
+// A tiled scale plane seen as [atoms, 512 bytes]: 128 int32 per atom, box of 4 atoms (one K step).
+int make_sf_tmap(mb_ctx* ctx, CUtensorMap* tm, const void* base, uint64_t atoms) {
+  EncodeTiledFn enc;
+  int rc = get_encoder(ctx, &enc);
+  if (rc) return rc;
+  cuuint64_t dims[2] = {128, atoms};
+  cuuint64_t strides[1] = {512};
+  cuuint32_t box[2] = {128, 4};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = enc(tm, CU_TENSOR_MAP_DATA_TYPE_INT32, 2, const_cast<void*>(base), dims, strides, box, estr,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return mb_fail(ctx, MB_ERR_CUDA, "cuTensorMapEncodeTiled (scales) failed with %d", int(r));
+  return MB_OK;
+}
+
+// Launch of the CTA-pair kernel: as many clusters as the device can hold at once, persistent.
+int launch_pair(mb_ctx* ctx, cudaStream_t stream, Gemm2Params& pp) {
+  static int clusters[16] = {};
+  const int d = ctx->device & 15;
+  if (!clusters[d]) {
+    MB_CUDA_OK(ctx, cudaFuncSetAttribute(gemm_tc5_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg2::SMEM_BYTES));
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(unsigned(ctx->sm_count) & ~1u);
+    cfg.blockDim = dim3(NUM_THREADS);
+    cfg.dynamicSmemBytes = Cfg2::SMEM_BYTES;
+    cudaLaunchAttribute attr;
+    attr.id = cudaLaunchAttributeClusterDimension;
+    attr.val.clusterDim.x = 2; attr.val.clusterDim.y = 1; attr.val.clusterDim.z = 1;
+    cfg.attrs = &attr;
+    cfg.numAttrs = 1;
+    int n = 0;
+    MB_CUDA_OK(ctx, cudaOccupancyMaxActiveClusters(&n, gemm_tc5_pair_kernel, &cfg));
+    if (n < 1) return mb_fail(ctx, MB_ERR_CUDA, "no CTA pair of the GEMM kernel fits on this device");
+    clusters[d] = n;
+  }
+  const uint32_t tiles = pp.m_pairs * pp.g.n_tiles;
+  const unsigned grid = 2u * std::min<uint32_t>(tiles, uint32_t(clusters[d]));
+  gemm_tc5_pair_kernel<<<grid, NUM_THREADS, Cfg2::SMEM_BYTES, stream>>>(pp);
+  MB_LAUNCH_OK(ctx);
+  return MB_OK;
+}
+
 int gemm_w4a4_common(mb_ctx* ctx, cudaStream_t stream, const uint8_t* a_codes, const uint8_t* a_sf,
                      const uint8_t* b_codes, const uint8_t* b_sf, const float* rowscale, float alpha,
                      const float* alpha_vec, const int32_t* tile_expert, const int32_t* n_tiles_dev, size_t m,
@@ -470,6 +720,22 @@ int gemm_w4a4_common(mb_ctx* ctx, cudaStream_t stream, const uint8_t* a_codes, c
   p.ldo = uint32_t(epilogue == MB_EPI_SWIGLU_INTERLEAVED ? n / 2 : n);
   p.out_dtype = out_dtype; p.epilogue = epilogue;
   uint32_t tiles = p.m_tiles * p.n_tiles;
+  // Dense products with at least one full pair of row tiles go to the CTA-pair kernel
+  // (MB_GEMM_CTA_GROUP=1 in the environment keeps the single-CTA kernel, for comparison runs).
+  static const bool single_only = [] { const char* e = getenv("MB_GEMM_CTA_GROUP"); return e && e[0] == '1'; }();
+  if (wide && !tile_expert && m > 128 && !single_only) {
+    Gemm2Params pp;
+    memset(&pp, 0, sizeof pp);
+    pp.g = p;
+    rc = make_tmap(ctx, &pp.g.tmap_b, b_codes, false, n, k / 2, 128);   // each CTA loads half of the B tile
+    if (rc) return rc;
+    rc = make_sf_tmap(ctx, &pp.tmap_sfa, a_sf, uint64_t(p.m_tiles) * p.sf_kchunks);
+    if (rc) return rc;
+    rc = make_sf_tmap(ctx, &pp.tmap_sfb, b_sf, uint64_t((n + 127) / 128) * p.sf_kchunks);
+    if (rc) return rc;
+    pp.m_pairs = (p.m_tiles + 1) / 2;
+    return launch_pair(ctx, stream, pp);
+  }
   return wide ? launch<KIND_NVF4, 256>(ctx, stream, p, tiles) : launch<KIND_NVF4, 128>(ctx, stream, p, tiles);
 }
 
