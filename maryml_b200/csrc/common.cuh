@@ -131,10 +131,19 @@ __device__ __forceinline__ uint32_t mb_cvt_e2m1x2(float lo, float hi) {
   return uint32_t(r) & 0xFFu;
 }
 
-// Eight f32 -> one u32 of eight codes, element i at bits 4*i.
+// Eight f32 -> one u32 of eight codes, element i at bits 4*i: four e2m1x2 converts
+// packed by one byte-vector move.
 __device__ __forceinline__ uint32_t mb_cvt_e2m1x8(const float* v) {
-  return mb_cvt_e2m1x2(v[0], v[1]) | (mb_cvt_e2m1x2(v[2], v[3]) << 8) | (mb_cvt_e2m1x2(v[4], v[5]) << 16) |
-         (mb_cvt_e2m1x2(v[6], v[7]) << 24);
+  uint32_t r;
+  asm("{\n\t.reg .b8 b0, b1, b2, b3;\n\t"
+      "cvt.rn.satfinite.e2m1x2.f32 b0, %2, %1;\n\t"
+      "cvt.rn.satfinite.e2m1x2.f32 b1, %4, %3;\n\t"
+      "cvt.rn.satfinite.e2m1x2.f32 b2, %6, %5;\n\t"
+      "cvt.rn.satfinite.e2m1x2.f32 b3, %8, %7;\n\t"
+      "mov.b32 %0, {b0, b1, b2, b3};\n\t}"
+      : "=r"(r)
+      : "f"(v[0]), "f"(v[1]), "f"(v[2]), "f"(v[3]), "f"(v[4]), "f"(v[5]), "f"(v[6]), "f"(v[7]));
+  return r;
 }
 
 // Byte offset of scale (row, kb) [kb = index of the 16-element block along K] in

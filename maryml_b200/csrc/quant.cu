@@ -48,7 +48,8 @@ __device__ __forceinline__ float amax16(const float* v) {
 // and the mary::nn activation recipe.
 __device__ __forceinline__ void quant_block_scaled(const float* v, float s2, uint32_t& sbyte, uint2& codes) {
   float bamax = amax16(v);
-  float t = __fdiv_rn(__fdiv_rn(bamax, 6.0f), s2);
+  float t = __fdiv_rn(bamax, 6.0f);
+  if (s2 != 1.0f) t = __fdiv_rn(t, s2);            // x / 1 is x: the unit global costs no divide
   sbyte = mb_e4m3_from_f32(fminf(t, 448.0f));
   float d = __fmul_rn(mb_e4m3_to_f32(sbyte), s2);
   float q[16];
@@ -100,11 +101,21 @@ __global__ void __launch_bounds__(QUANT_THREADS)
 quantize_kernel(const T* __restrict__ x, size_t rows, size_t k, int recipe, float input_scale,
                 const float* __restrict__ rowscale, const int32_t* __restrict__ gather, uint2* __restrict__ codes,
                 uint8_t* __restrict__ scales, int tiled, size_t kchunks, int vec_ok) {
-  size_t row_blocks = k / 16;
-  size_t blocks = rows * row_blocks;
-  size_t blk = size_t(blockIdx.x) * QUANT_THREADS + threadIdx.x;
-  bool live = blk < blocks;
-  size_t row = live ? blk / row_blocks : 0, kb = live ? blk % row_blocks : 0;
+  // 32-bit block index (the launcher checks the extent); a power-of-two row splits by shift.
+  const uint32_t row_blocks = uint32_t(k / 16);
+  const uint32_t blocks = uint32_t(rows) * row_blocks;
+  const uint32_t blk = blockIdx.x * QUANT_THREADS + threadIdx.x;
+  const bool live = blk < blocks;
+  uint32_t row = 0, kb = 0;
+  if (live) {
+    if ((row_blocks & (row_blocks - 1)) == 0) {
+      row = blk >> (31 - __clz(row_blocks));
+      kb = blk & (row_blocks - 1);
+    } else {
+      row = blk / row_blocks;
+      kb = blk - row * row_blocks;
+    }
+  }
   uint32_t sbyte = 0;
   uint2 c = make_uint2(0u, 0u);
   if (live) {
@@ -114,7 +125,7 @@ quantize_kernel(const T* __restrict__ x, size_t rows, size_t k, int recipe, floa
 #pragma unroll
       for (int i = 0; i < 16; ++i) v[i] = 0.0f;
     } else {
-      const T* p = x + size_t(src) * k + kb * 16;
+      const T* p = x + size_t(src) * k + size_t(kb) * 16;
       if (vec_ok) load16(p, v); else load16_scalar(p, v);
     }
     if (recipe == MB_QUANT_RECIP) {
@@ -238,7 +249,7 @@ MB_API int mb_nvfp4_quantize_act(mb_ctx* ctx, mb_stream stream_, const void* x, 
   MB_REQUIRE(ctx, x_dtype == MB_DT_BF16 || x_dtype == MB_DT_F32, "quantize_act: activations are bf16 or f32");
   MB_REQUIRE(ctx, recipe >= MB_QUANT_SCALED && recipe <= MB_QUANT_ROWS, "quantize_act: unknown recipe %d", recipe);
   MB_REQUIRE(ctx, sf_layout == MB_SF_ROWMAJOR || sf_layout == MB_SF_TILED, "quantize_act: unknown scale layout");
-  MB_REQUIRE(ctx, rows * k <= 0xFFFFFFFFull * 16, "quantize_act: extent overflow");
+  MB_REQUIRE(ctx, rows * (k / 16) <= 0xFFFFFF00ull, "quantize_act: exceeds u32 block indexing");
   MB_REQUIRE(ctx, mb_aligned(codes, 8) && mb_aligned(scales, 4), "quantize_act: outputs need 8/4-byte alignment");
   size_t esz = x_dtype == MB_DT_BF16 ? 2 : 4;
   MB_REQUIRE(ctx, mb_aligned(x, esz == 2 ? 4 : 4), "quantize_act: activation needs 4-byte alignment");
