@@ -422,7 +422,7 @@ def run_other(args, rank, world, local_rank):
         else:
             flop = 4.0 * B * H * nq * L * D / 2
             units, metric, unit = flop / 1e12, "prefill_attention_tflops", "TFLOP/s"
-            roof = lambda ms: {"bound": "tensor", "kernel": "attn_prefill_kernel (mma.sync)", "achieved": flop / (ms * 1e-3) / 1e12,
+            roof = lambda ms: {"bound": "tensor", "kernel": "attn_prefill_tc5_kernel (tcgen05, TMEM-resident O)", "achieved": flop / (ms * 1e-3) / 1e12,
                                "peak": peaks["bf16"], "unit": "TFLOP/s", "frac": flop / (ms * 1e-3) / 1e12 / peaks["bf16"],
                                "peak_source": peaks["source"], "traffic": None}
             launches = 1

@@ -11,14 +11,16 @@
 //    16 keys of each 64-key tile; partial (o, m, l) of the warps and of the key
 //    splits are merged at the end (flash-decoding). HBM-bound: algorithmic bytes =
 //    2 * keys * kv_heads * D * 2 per sequence.
-//  * prefill: one CTA per (128-query tile, head, sequence), eight compute warps of 16
-//    query rows each, online softmax, causal tiles beyond the diagonal skipped.
-//    Tensor-bound: 4 * nq * keys * D flop per head (half of it under the causal mask).
+//  * prefill runs on tcgen05 (attention_tc5.cu). The warp-level prefill kernel below
+//    (one CTA per 128-query tile, eight compute warps of 16 rows) is kept as the
+//    comparison arm, selected with MB_ATTN_PREFILL=legacy in the environment.
 //
-// The S = QK^T and O += PV products use warp-level mma.sync m16n8k16 (bf16, f32
-// accumulate). Every mbarrier wait is bounded.
+// Decode (and the comparison prefill) use warp-level mma.sync m16n8k16 (bf16, f32
+// accumulate): with 4 valid rows per 16-row tile the product is HBM-bound, not
+// tensor-bound. Every mbarrier wait is bounded.
 #include "common.cuh"
 #include "tc5.cuh"
+#include "attention.cuh"
 
 namespace {
 
@@ -28,27 +30,6 @@ constexpr int D = 128;            // head dim
 constexpr int BC = 64;            // keys per tile
 constexpr int TILE_HALF_BYTES = BC * 128;       // one 64-dim half of a K or V tile
 constexpr int KV_STAGE_BYTES = 4 * TILE_HALF_BYTES;   // K lo, K hi, V lo, V hi = 32 KB
-
-struct AttnParams {
-  CUtensorMap tmap_q;   // [batch, nq, heads, D], box 64 x 1 x 128 x 1 (prefill only)
-  CUtensorMap tmap_k;   // [batch, keys, kv_heads, D], box 64 x 1 x 64 x 1
-  CUtensorMap tmap_v;
-  const __nv_bfloat16* q;
-  __nv_bfloat16* out;
-  float* part;          // decode partials [batch, kv_heads, splits, 16 rows, D + 2]
-  int* flags;
-  uint32_t batch, nq, keys, heads, kv_heads, q0, splits, keys_per_split;
-  float scale_log2;     // scale * log2(e)
-  int causal;
-};
-
-__device__ __forceinline__ void tma_load_4d(uint32_t dst, const void* tmap, int c0, int c1, int c2, int c3,
-                                            uint32_t bar) {
-  asm volatile(
-      "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4, %5}], [%6];"
-      ::"r"(dst), "l"(tmap), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(bar)
-      : "memory");
-}
 
 __device__ __forceinline__ void ldsm_x4(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
   asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
@@ -563,6 +544,11 @@ MB_API int mb_attention(mb_ctx* ctx, mb_stream stream_, const void* q, const voi
       attn_combine_kernel<<<unsigned(batch * nq * heads), 128, 0, stream>>>(p.part, p.out, p.nq, p.heads, p.kv_heads, splits);
       MB_LAUNCH_OK(ctx);
     }
+  } else if (!mb_attention_prefill_legacy()) {
+    rc = make_tmap_4d(ctx, &p.tmap_q, q, batch, nq, heads, 128);
+    if (rc) return rc;
+    p.splits = 1;
+    return mb_attention_prefill_tc5(ctx, stream, p);
   } else {
     rc = make_tmap_4d(ctx, &p.tmap_q, q, batch, nq, heads, BR);
     if (rc) return rc;

@@ -1,0 +1,35 @@
+// Parameters shared by the attention kernels (decode, mma.sync prefill, tcgen05 prefill).
+#pragma once
+
+#include "common.cuh"
+#include "tc5.cuh"
+
+struct AttnParams {
+  CUtensorMap tmap_q;   // [batch, nq, heads, D], box 64 x 1 x 128 x 1 (prefill only)
+  CUtensorMap tmap_k;   // [batch, keys, kv_heads, D], box 64 x 1 x 64 x 1
+  CUtensorMap tmap_v;
+  const __nv_bfloat16* q;
+  __nv_bfloat16* out;
+  float* part;          // decode partials [batch, kv_heads, splits, 16 rows, D + 2]
+  int* flags;
+  uint32_t batch, nq, keys, heads, kv_heads, q0, splits, keys_per_split;
+  float scale_log2;     // scale * log2(e)
+  int causal;
+};
+
+__device__ __forceinline__ void tma_load_4d(uint32_t dst, const void* tmap, int c0, int c1, int c2, int c3,
+                                            uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4, %5}], [%6];"
+      ::"r"(dst), "l"(tmap), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(bar)
+      : "memory");
+}
+
+
+// tcgen05 prefill (attention_tc5.cu). MB_ATTN_PREFILL=legacy in the environment keeps the
+// mma.sync kernel, for comparison runs.
+int mb_attention_prefill_tc5(mb_ctx* ctx, cudaStream_t stream, const AttnParams& p);
+inline bool mb_attention_prefill_legacy() {
+  static const bool legacy = [] { const char* e = getenv("MB_ATTN_PREFILL"); return e && e[0] == 'l'; }();
+  return legacy;
+}

@@ -1,0 +1,353 @@
+// Causal GQA prefill attention on the sm_100a tensor cores (tcgen05 + TMEM), head_dim 128.
+//
+// One CTA owns 256 query rows of one head as two 128-row tiles. Per 64-key tile:
+//
+//   S_t  = Q_t K^T      tcgen05.mma kind::f16, 128 x 64 x 128, accumulator in TMEM
+//   P_t  = 2^(S_t*c - m) one softmax thread per query row reads its row of S_t from
+//                        TMEM (no cross-thread reduction), writes bf16 P_t to shared
+//                        memory in the K-major 128B-swizzled layout the MMA reads
+//   O_t += P_t V         tcgen05.mma, 128 x 128 x 64, V read MN-major straight from the
+//                        TMA tile; O_t stays in TMEM over the whole key loop
+//
+// The running maximum a row subtracts is allowed to lag the true one by up to 2^8: O_t in
+// TMEM is rescaled (tcgen05.ld, multiply, tcgen05.st) only when a tile raises a row's maximum
+// by more than that, which after the first tiles is rare; the final O_t / l is exact either way.
+//
+// Warp roles: 0 = TMA producer (Q once, K/V ring), 1 = MMA issuer, 2-5 and 6-9 = the two
+// softmax groups (one per query tile) that alternate on the tensor core: while one group
+// exponentiates, the other group's products run. TMEM: S0, S1 (64 columns each), PV0, PV1
+// (128 each). Algorithmic work: 4 * nq * keys * 128 flop per head, half under the mask.
+// Every mbarrier wait is bounded.
+#include "attention.cuh"
+
+namespace {
+
+using namespace tc5;
+
+constexpr int D = 128;
+constexpr int BC = 64;                         // keys per tile
+constexpr int QT = 128;                        // query rows per tile (two tiles per CTA)
+constexpr int HALF = BC * 128;                 // one 64-dim half of a K or V tile: 8 KB
+constexpr int KV_STAGE = 4 * HALF;             // K lo, K hi, V lo, V hi: 32 KB
+constexpr int STAGES = 3;
+constexpr int Q_BYTES = 2 * QT * D * 2;        // 64 KB: [tile][half][128 rows][64 dims]
+constexpr int P_BYTES = QT * BC * 2;           // 16 KB per query tile
+constexpr int SMEM = STAGES * KV_STAGE + Q_BYTES + 4 * P_BYTES + 1024 + 256;   // P double-buffered per query tile
+constexpr int THREADS = 320;
+constexpr int S_COL0 = 0, S_COL1 = 64, PV_COL0 = 128, PV_COL1 = 256, TMEM_COLS = 512;
+
+// bf16 A and B, f32 accumulate, M = 128; B either K-major (0) or MN-major (1).
+__host__ __device__ constexpr uint32_t idesc(uint32_t n, uint32_t b_mn_major) {
+  return (1u << 4) | (1u << 7) | (1u << 10) | (b_mn_major << 16) | ((n >> 3) << 17) | ((128u >> 4) << 24);
+}
+// V tile [64 keys][128 dims] as two 64-dim halves of 128-byte rows: MN-major operand with
+// 8 KB between the 64-element MN blocks (leading offset) and 1 KB between 8-key groups.
+__device__ __forceinline__ uint64_t make_v_desc(uint32_t saddr) {
+  return make_smem_desc(saddr, HALF, 1024, LAYOUT_SWIZZLE_128B);
+}
+
+__device__ __forceinline__ float ex2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+__device__ __forceinline__ uint32_t pack2(float lo, float hi) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+
+__global__ void __launch_bounds__(THREADS, 1)
+attn_prefill_tc5_kernel(const __grid_constant__ AttnParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* gen = smem_raw + (base - smem_u32(smem_raw));
+  const uint32_t q_smem = base + STAGES * KV_STAGE;
+  const uint32_t p_smem = q_smem + Q_BYTES;
+  const uint32_t bar_base = p_smem + 4 * P_BYTES;
+  // barriers: kv_full[3], kv_empty[3], q_full, s_full[2], s_free[2], p_full[2], pv_done[2], (2 spare), drain
+  auto kv_full = [&](int s) { return bar_base + 8u * s; };
+  auto kv_empty = [&](int s) { return bar_base + 8u * (STAGES + s); };
+  const uint32_t q_full = bar_base + 8u * (2 * STAGES);
+  auto s_full = [&](int t) { return bar_base + 8u * (2 * STAGES + 1 + t); };
+  auto s_free = [&](int t) { return bar_base + 8u * (2 * STAGES + 3 + t); };
+  auto p_full = [&](int t) { return bar_base + 8u * (2 * STAGES + 5 + t); };
+  auto pv_done = [&](int t) { return bar_base + 8u * (2 * STAGES + 7 + t); };
+  const uint32_t drain_bar = bar_base + 8u * (2 * STAGES + 11);
+  uint32_t* tmem_ptr_smem = reinterpret_cast<uint32_t*>(gen + (bar_base - base) + 8 * (2 * STAGES + 12));
+  volatile int* abort_smem = reinterpret_cast<volatile int*>(tmem_ptr_smem + 1);
+  int* tflag = p.flags ? p.flags + MB_FLAG_WAIT_TIMEOUT : nullptr;
+
+  const int warp = __shfl_sync(0xFFFFFFFFu, int(threadIdx.x >> 5), 0);
+  const uint32_t lane = threadIdx.x & 31;
+  // heavy (late) query blocks first
+  const uint32_t qb = gridDim.x - 1 - blockIdx.x, h = blockIdx.y, b = blockIdx.z;
+  const uint32_t kvh = h / (p.heads / p.kv_heads);
+  const uint32_t q_row0 = qb * 2 * QT;
+  const uint32_t q_rows = min(uint32_t(2 * QT), p.nq - q_row0);
+  const uint32_t last_q = p.q0 + q_row0 + q_rows - 1;
+  const uint32_t k_end = p.causal ? min(p.keys, last_q + 1) : p.keys;
+  const uint32_t n_tiles = (k_end + BC - 1) / BC;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) { mbar_init(kv_full(s), 1); mbar_init(kv_empty(s), 1); }
+    mbar_init(q_full, 1);
+    for (int t = 0; t < 2; ++t) {
+      mbar_init(s_full(t), 1);
+      mbar_init(s_free(t), 128);
+      mbar_init(p_full(t), 128);
+      mbar_init(pv_done(t), 1);
+    }
+    mbar_init(drain_bar, 1);
+    *abort_smem = 0;
+    fence_barrier_init();
+    tma_prefetch_desc(&p.tmap_q);
+    tma_prefetch_desc(&p.tmap_k);
+    tma_prefetch_desc(&p.tmap_v);
+  }
+  if (warp == 1) {
+    tmem_alloc(smem_u32(tmem_ptr_smem), TMEM_COLS);
+    tmem_relinquish();
+  }
+  fence_before_sync();
+  __syncthreads();
+  fence_after_sync();
+  const uint32_t tmem_base = *tmem_ptr_smem;
+
+  if (warp == 0) {
+    // ------------------------------ producer ------------------------------------
+    if (elect_one()) {
+      mbar_arrive_expect_tx(q_full, Q_BYTES);
+#pragma unroll
+      for (int t = 0; t < 2; ++t)
+#pragma unroll
+        for (int hf = 0; hf < 2; ++hf)
+          tma_load_4d(q_smem + (t * 2 + hf) * (QT * 128), &p.tmap_q, hf * 64, int(h), int(q_row0 + t * QT), int(b), q_full);
+    }
+    __syncwarp();
+    int stage = 0;
+    uint32_t phase = 0;
+    for (uint32_t j = 0; j < n_tiles; ++j) {
+      if (!mbar_wait(kv_empty(stage), phase ^ 1u, abort_smem, tflag, 31)) break;
+      if (elect_one()) {
+        const uint32_t s0 = base + stage * KV_STAGE;
+        const int key0 = int(j * BC);
+        mbar_arrive_expect_tx(kv_full(stage), KV_STAGE);
+        tma_load_4d(s0, &p.tmap_k, 0, int(kvh), key0, int(b), kv_full(stage));
+        tma_load_4d(s0 + HALF, &p.tmap_k, 64, int(kvh), key0, int(b), kv_full(stage));
+        tma_load_4d(s0 + 2 * HALF, &p.tmap_v, 0, int(kvh), key0, int(b), kv_full(stage));
+        tma_load_4d(s0 + 3 * HALF, &p.tmap_v, 64, int(kvh), key0, int(b), kv_full(stage));
+      }
+      __syncwarp();
+      if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+    }
+  } else if (warp == 1) {
+    // ------------------------------ MMA issuer ----------------------------------
+    // Order per key tile j: S(0, j), S(1, j), PV(0, j-1), PV(1, j-1): a group's next scores are
+    // computed while it exponentiates tile j-1, and its PV product runs while it works on tile j.
+    bool ok = mbar_wait(q_full, 0u, abort_smem, tflag, 32);
+    const uint32_t id_s = idesc(BC, 0), id_pv = idesc(D, 1);
+    int stage = 0;                 // stage of key tile j (for S); PV(j-1) uses the previous stage
+    uint32_t phase = 0;
+    int pstage = 0;
+    for (uint32_t j = 0; ok && j <= n_tiles; ++j) {
+      if (j < n_tiles) {
+        if (!mbar_wait(kv_full(stage), phase, abort_smem, tflag, 33)) { ok = false; break; }
+      }
+      // scores of tile j first (they only need the group to have READ the previous scores),
+      // then the PV products of tile j-1 (they need the group's finished P)
+      for (int t = 0; t < 2 && ok; ++t) {
+        if (j < n_tiles) {
+          // S(t, j): previous S_t read by its softmax group
+          if (!mbar_wait(s_free(t), (j & 1u) ^ 1u, abort_smem, tflag, 36)) { ok = false; break; }
+          fence_after_sync();
+          if (elect_one()) {
+            const uint32_t k0 = base + stage * KV_STAGE;
+#pragma unroll
+            for (int hf = 0; hf < 2; ++hf) {
+              const uint64_t adesc = make_kmajor_sw128_desc(q_smem + (t * 2 + hf) * (QT * 128));
+              const uint64_t bdesc = make_kmajor_sw128_desc(k0 + hf * HALF);
+#pragma unroll
+              for (int kk = 0; kk < 4; ++kk)
+                mma_f16(tmem_base + (t ? S_COL1 : S_COL0), adesc + 2 * kk, bdesc + 2 * kk, id_s, (hf | kk) != 0);
+            }
+            umma_commit(s_full(t));
+          }
+          __syncwarp();
+        }
+      }
+      for (int t = 0; t < 2 && ok; ++t) {
+        if (j > 0) {
+          // O_t += P_t(j-1) V(j-1): the group has written P_t (and rescaled O_t if it had to)
+          const uint32_t u = j - 1;
+          if (!mbar_wait(p_full(t), u & 1u, abort_smem, tflag, 34)) { ok = false; break; }
+          fence_after_sync();
+          if (elect_one()) {
+            const uint32_t v0 = base + pstage * KV_STAGE + 2 * HALF;
+            const uint64_t adesc = make_kmajor_sw128_desc(p_smem + (t * 2 + (u & 1u)) * P_BYTES);
+            const uint64_t bdesc = make_v_desc(v0);
+#pragma unroll
+            for (int kk = 0; kk < BC / 16; ++kk)            // 16 keys per instruction: 32 B of P, 16 rows of V
+              mma_f16(tmem_base + (t ? PV_COL1 : PV_COL0), adesc + 2 * kk, bdesc + 128 * kk, id_pv, (u | uint32_t(kk)) != 0u);
+            umma_commit(pv_done(t));
+            if (t == 1) umma_commit(kv_empty(pstage));      // both tiles are done with this K/V stage
+          }
+          __syncwarp();
+        }
+      }
+      if (j > 0) { if (++pstage == STAGES) pstage = 0; }
+      if (j < n_tiles) { if (++stage == STAGES) { stage = 0; phase ^= 1u; } }
+    }
+    if (!ok) {
+      if (elect_one()) umma_commit(drain_bar);
+      __syncwarp();
+      long long t0 = clock64();
+      while (!mbar_try_wait(drain_bar, 0u) && clock64() - t0 < WAIT_LIMIT_CYCLES) {}
+    }
+  } else {
+    // ------------------------------ softmax groups -------------------------------
+    const int t = (warp - 2) >> 2;                        // query tile of this group
+    const uint32_t quad = warp & 3u;                      // TMEM lane quadrant of this warp
+    const uint32_t r = quad * 32u + lane;                 // row within the tile
+    const uint32_t row = q_row0 + t * QT + r;             // row within the sequence's queries
+    const int qpos = int(p.q0 + row);
+    const uint32_t lane_addr = (quad * 32u) << 16;
+    const uint32_t t_s = tmem_base + lane_addr + (t ? S_COL1 : S_COL0);
+    const uint32_t t_pv = tmem_base + lane_addr + (t ? PV_COL1 : PV_COL0);
+    uint8_t* p_rows = gen + (p_smem - base) + t * 2 * P_BYTES + r * 128;
+    float m = -INFINITY, l = 0.0f;       // m: the maximum this row currently subtracts (may lag, see header)
+    bool ok = true;
+    for (uint32_t j = 0; ok && j < n_tiles; ++j) {
+      const int kabs = int(j * BC);
+      int vis = int(p.keys) - kabs;
+      if (p.causal) vis = min(vis, qpos + 1 - kabs);
+      bool pv_waited = j == 0;           // whether PV(j-1) is known to be complete
+      const bool full_tile = __all_sync(0xFFFFFFFFu, vis >= BC);   // no mask work away from the diagonal
+      if (!mbar_wait(s_full(t), j & 1u, abort_smem, tflag, 37)) { ok = false; break; }
+      fence_after_sync();
+      // pass 1: the row maximum of this tile
+      float mx = -INFINITY;
+      uint32_t s[32];
+#pragma unroll
+      for (int c = 0; c < 2; ++c) {
+        tmem_ld_x32(t_s + c * 32, s);
+        tmem_ld_wait();
+        if (full_tile) {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(s[i]));
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i)
+            if (c * 32 + i < vis) mx = fmaxf(mx, __uint_as_float(s[i]));
+        }
+      }
+      const float mt = mx * p.scale_log2;
+      if (j == 0) {
+        m = mt;
+      } else if (__any_sync(0xFFFFFFFFu, mt > m + 8.0f)) {
+        // some row of this warp outgrew its maximum: bring O_t (and l) of the whole warp to the new maxima
+        if (!mbar_wait(pv_done(t), (j - 1u) & 1u, abort_smem, tflag, 38)) { ok = false; break; }
+        pv_waited = true;
+        fence_after_sync();
+        const float m_new = fmaxf(m, mt);
+        const float f = (m == -INFINITY || m_new == -INFINITY) ? 0.0f : ex2(m - m_new);
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          uint32_t v[32];
+          tmem_ld_x32(t_pv + c * 32, v);
+          tmem_ld_wait();
+#pragma unroll
+          for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) * f);
+          tmem_st_x32(t_pv + c * 32, v);
+        }
+        tmem_st_wait();
+        l *= f;
+        m = m_new;
+      }
+      // pass 2: probabilities, row sum, bf16 P into the swizzled shared tile
+      uint8_t* p_row = p_rows + (j & 1u) * P_BYTES;
+      float sum = 0.0f;
+#pragma unroll
+      for (int c = 0; c < 2; ++c) {
+        tmem_ld_x32(t_s + c * 32, s);
+        tmem_ld_wait();
+        if (c == 1) {
+          fence_before_sync();
+          mbar_arrive(s_free(t));                          // S_t may be overwritten by the next scores
+        }
+        uint32_t w[16];
+        const float neg_m = m == -INFINITY ? -INFINITY : -m;      // a row with nothing visible so far gives p = 0
+        if (full_tile) {
+#pragma unroll
+          for (int i = 0; i < 16; ++i) {
+            const float p0 = ex2(fmaf(__uint_as_float(s[2 * i]), p.scale_log2, neg_m));
+            const float p1 = ex2(fmaf(__uint_as_float(s[2 * i + 1]), p.scale_log2, neg_m));
+            sum += p0 + p1;
+            w[i] = pack2(p0, p1);
+          }
+        } else {
+#pragma unroll
+          for (int i = 0; i < 16; ++i) {
+            float p0 = 0.0f, p1 = 0.0f;
+            if (c * 32 + 2 * i < vis) p0 = ex2(fmaf(__uint_as_float(s[2 * i]), p.scale_log2, neg_m));
+            if (c * 32 + 2 * i + 1 < vis) p1 = ex2(fmaf(__uint_as_float(s[2 * i + 1]), p.scale_log2, neg_m));
+            sum += p0 + p1;
+            w[i] = pack2(p0, p1);
+          }
+        }
+#pragma unroll
+        for (int ch = 0; ch < 4; ++ch) {
+          const uint32_t chunk = uint32_t(c * 4 + ch);
+          *reinterpret_cast<uint4*>(p_row + ((chunk ^ (r & 7u)) << 4)) =
+              make_uint4(w[4 * ch], w[4 * ch + 1], w[4 * ch + 2], w[4 * ch + 3]);
+        }
+      }
+      l += sum;
+      fence_proxy_async();                                 // generic-proxy writes of P before the MMA reads them
+      fence_before_sync();                                 // and any O_t rescale before the next PV product
+      mbar_arrive(p_full(t));
+      // PV(j-1) must be complete before the next tile reuses its P buffer (never a stall in
+      // practice: it was issued a whole softmax pass ago), and the wait keeps the phase in step
+      if (!pv_waited && !mbar_wait(pv_done(t), (j - 1u) & 1u, abort_smem, tflag, 39)) { ok = false; break; }
+    }
+    if (ok && n_tiles > 0) ok = mbar_wait(pv_done(t), (n_tiles - 1u) & 1u, abort_smem, tflag, 40);
+    fence_after_sync();
+    const float inv = l > 0.0f ? 1.0f / l : 0.0f;
+    __nv_bfloat16* dst_row = p.out + ((size_t(b) * p.nq + row) * p.heads + h) * D;
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+      uint32_t v[32];
+      tmem_ld_x32(t_pv + c * 32, v);
+      tmem_ld_wait();
+      if (ok && row < p.nq) {
+        uint4* dst = reinterpret_cast<uint4*>(dst_row + c * 32);
+#pragma unroll
+        for (int g = 0; g < 4; ++g)
+          dst[g] = make_uint4(pack2(__uint_as_float(v[8 * g]) * inv, __uint_as_float(v[8 * g + 1]) * inv),
+                              pack2(__uint_as_float(v[8 * g + 2]) * inv, __uint_as_float(v[8 * g + 3]) * inv),
+                              pack2(__uint_as_float(v[8 * g + 4]) * inv, __uint_as_float(v[8 * g + 5]) * inv),
+                              pack2(__uint_as_float(v[8 * g + 6]) * inv, __uint_as_float(v[8 * g + 7]) * inv));
+      }
+    }
+  }
+
+  fence_before_sync();
+  __syncthreads();
+  if (warp == 1) {
+    fence_after_sync();
+    tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
+}  // namespace
+
+int mb_attention_prefill_tc5(mb_ctx* ctx, cudaStream_t stream, const AttnParams& p) {
+  static bool attr_set[16] = {};
+  if (!attr_set[ctx->device & 15]) {
+    MB_CUDA_OK(ctx, cudaFuncSetAttribute(attn_prefill_tc5_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM));
+    attr_set[ctx->device & 15] = true;
+  }
+  dim3 grid(unsigned((p.nq + 2 * QT - 1) / (2 * QT)), p.heads, p.batch);
+  attn_prefill_tc5_kernel<<<grid, THREADS, SMEM, stream>>>(p);
+  MB_LAUNCH_OK(ctx);
+  return MB_OK;
+}
