@@ -211,12 +211,18 @@ gemm_tc5_kernel(const __grid_constant__ GemmParams p) {
     uint32_t armed = 0;   // bit s: stage s armed at least once; parity of its last arming in armed_par
     uint32_t armed_par = 0;
     bool ok = true;
+    // Grouped products: the expert of a tile comes from device memory; it is fetched one tile
+    // ahead so that its latency never sits between two tiles' loads.
+    int e_next = 0;
+    if (p.tile_expert && blockIdx.x < total_tiles) e_next = p.tile_expert[blockIdx.x % m_tiles];
     for (uint32_t tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
       const uint32_t mt = tile % m_tiles, nt = tile / m_tiles;
       uint32_t brow = nt * BN;
       const uint8_t* sfb = p.sfb;
       if (p.tile_expert) {
-        int e = p.tile_expert[mt];
+        int e = e_next;
+        const uint32_t nxt = tile + gridDim.x;
+        if (nxt < total_tiles) e_next = p.tile_expert[nxt % m_tiles];
         if (e < 0) e = 0;
         brow += uint32_t(e) * p.b_rows_per_expert;
         sfb += uint64_t(e) * p.sfb_expert_stride;

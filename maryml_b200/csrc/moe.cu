@@ -96,6 +96,19 @@ router_softmax_topk_kernel(const float* __restrict__ logits, uint32_t tokens, ui
 // ---------------------------------------------------------------------------------
 constexpr int PLAN_PAD = 128;   // rows per GEMM tile: each expert's rows are padded to this
 
+// One pass that puts every plan buffer in its empty state: no token on any row (-1), zero
+// weights, no expert on any tile (-1), no row for any pick (-1), zero counts.
+__global__ void __launch_bounds__(256)
+plan_init_kernel(int32_t* __restrict__ row_tok, float* __restrict__ row_wgt, uint32_t m_cap,
+                 int32_t* __restrict__ tile_expert, uint32_t tiles, int32_t* __restrict__ tok_rows, uint32_t picks,
+                 int32_t* __restrict__ counts, uint32_t n_experts) {
+  const uint32_t stride = gridDim.x * 256;
+  for (uint32_t i = blockIdx.x * 256 + threadIdx.x; i < m_cap; i += stride) { row_tok[i] = -1; row_wgt[i] = 0.0f; }
+  for (uint32_t i = blockIdx.x * 256 + threadIdx.x; i < picks; i += stride) tok_rows[i] = -1;
+  for (uint32_t i = blockIdx.x * 256 + threadIdx.x; i < tiles; i += stride) tile_expert[i] = -1;
+  for (uint32_t i = blockIdx.x * 256 + threadIdx.x; i < n_experts; i += stride) counts[i] = 0;
+}
+
 // counts[e] = picks of expert e; checks range and per-token duplicates.
 __global__ void __launch_bounds__(256)
 plan_count_kernel(const int32_t* __restrict__ idx, uint32_t tokens, uint32_t k, uint32_t n_experts,
@@ -286,11 +299,10 @@ MB_API int mb_moe_plan(mb_ctx* ctx, mb_stream stream_, const int32_t* idx, const
   MB_REQUIRE(ctx, tokens * k < (1ull << 31), "moe_plan: exceeds i32 indexing");
   size_t m_cap = mb_moe_plan_rows(tokens, k, n_experts);
   int32_t* counts = static_cast<int32_t*>(workspace);
-  MB_CUDA_OK(ctx, cudaMemsetAsync(counts, 0, n_experts * 4, stream));
-  MB_CUDA_OK(ctx, cudaMemsetAsync(row_tok, 0xFF, m_cap * 4, stream));   // -1: pad rows carry no token
-  MB_CUDA_OK(ctx, cudaMemsetAsync(row_wgt, 0, m_cap * 4, stream));
-  MB_CUDA_OK(ctx, cudaMemsetAsync(tile_expert, 0xFF, (m_cap / PLAN_PAD) * 4, stream));
-  MB_CUDA_OK(ctx, cudaMemsetAsync(tok_rows, 0xFF, tokens * k * 4, stream));
+  plan_init_kernel<<<unsigned(std::min<size_t>((m_cap + 255) / 256, 592)), 256, 0, stream>>>(
+      row_tok, row_wgt, uint32_t(m_cap), tile_expert, uint32_t(m_cap / PLAN_PAD), tok_rows, uint32_t(tokens * k),
+      counts, uint32_t(n_experts));
+  MB_LAUNCH_OK(ctx);
   int* flag = ctx->flags_dev + MB_FLAG_PLAN_FAULT;
   plan_count_kernel<<<unsigned((tokens + 255) / 256), 256, 0, stream>>>(idx, uint32_t(tokens), uint32_t(k),
                                                                          uint32_t(n_experts), counts, flag);
