@@ -449,7 +449,14 @@ def run_other(args, rank, world, local_rank):
             qz = mb.Nvfp4.quantize((torch.randn(n, kk, device=dev, generator=gw) * 0.02).to(torch.bfloat16))
             full[name] = (qz.codes, qz.scales, qz.scale2)
         gain = torch.ones(cfgL.hidden, dtype=torch.bfloat16, device=dev)
-        L_ = layer.DecoderLayer(cfgL, full, gain, gain, tp=tp, group=group, device=dev)
+        fx = None
+        if args.fused and world > 1:
+            def exchange_all(raw):
+                got = [None] * world
+                dist.all_gather_object(got, raw)
+                return got
+            fx = layer.FusedExchange(tp, local_rank, batch * t, cfgL.hidden, exchange_all)
+        L_ = layer.DecoderLayer(cfgL, full, gain, gain, tp=tp, group=group, device=dev, fused=fx)
         del full
         cap = past + t
         x = torch.randn(batch * t, cfgL.hidden, device=dev, generator=gw).to(torch.bfloat16)
@@ -478,7 +485,9 @@ def run_other(args, rank, world, local_rank):
                                "peak": 4 * peaks["bf16"], "unit": "TFLOP/s", "frac": flop / (ms * 1e-3) / 1e12 / (4 * peaks["bf16"]),
                                "peak_source": "4 x " + peaks["source"] + " bf16 burst", "traffic": None,
                                "note": "projections at the FP4 rate dominate; attention runs at the bf16 rate"}
-        cfg = {"workload": f"{wl}_hidden4096_heads32_kv8_ffn14336_batch{batch}_t{t}_past{past}", "parallelism": f"tp{world}"}
+        cfg = {"workload": f"{wl}_hidden4096_heads32_kv8_ffn14336_batch{batch}_t{t}_past{past}", "parallelism": f"tp{world}",
+               "reduce": "fused: GEMM epilogue scatters to peers, one reduce+residual+gather kernel" if fx else
+                         ("nccl all-reduce f32 + add" if world > 1 else "none (world 1)")}
         launches = 30
 
     if args.graph:
@@ -540,6 +549,8 @@ def main():
     ap.add_argument("--steps", type=int, default=1000)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--fused", action="store_true",
+                    help="tp workloads: reduce over peer memory from the GEMM epilogue instead of NCCL")
     ap.add_argument("--graph", action="store_true", help="capture the step into a CUDA graph and time replays")
     ap.add_argument("--batch", type=int, default=0, help="override the batch of the attention workloads (profiling)")
     args = ap.parse_args()

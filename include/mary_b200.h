@@ -234,6 +234,27 @@ int mb_tp_warm(mb_ctx* ctx, mb_stream stream);
 int mb_tp_all_reduce(mb_ctx* ctx, mb_stream stream, void* buf, size_t count, int dtype);
 int mb_tp_close(mb_ctx* ctx);
 
+/* Fused row-parallel path over peer memory: tp_reduce (src/models/inkling/tpcomm.rs:1453-1467)
+ * + the residual add that follows it (src/models/inkling/session.rs:2713-2717, 2793, 2843-2846,
+ * 2930), as one exchange that overlaps the GEMM. Each rank creates exchange memory for activations
+ * up to [t_max, n] (mb_tp_symm_create returns a 64-byte CUDA IPC handle), the handles of all ranks
+ * travel over the host link in rank order, and mb_tp_symm_attach maps them. Per reduction, with a
+ * step counter that grows by one each time (from 1): mb_nvfp4_gemm_w4a4_scatter is
+ * mb_nvfp4_gemm_w4a4 whose epilogue pushes each f32 partial tile into the rank owning those
+ * columns (reduce-scatter by peer stores); mb_tp_reduce_residual then sums this rank's columns
+ * in rank order, forms bf16(resid + bf16(sum)), stores it into every rank's output (all-gather by
+ * peer stores) and returns the device address of the local [t, n] bf16 result, valid until the
+ * step after next. Waits on peers are bounded (status word on timeout). world <= 8. */
+size_t mb_tp_symm_bytes(size_t t_max, size_t n);
+int mb_tp_symm_create(mb_ctx* ctx, size_t t_max, size_t n, uint8_t handle_out[64]);
+int mb_tp_symm_attach(mb_ctx* ctx, const uint8_t* handles_world_x64, int rank, int world);
+int mb_nvfp4_gemm_w4a4_scatter(mb_ctx* ctx, mb_stream stream, const uint8_t* a_codes, const uint8_t* a_sf_tiled,
+                               const uint8_t* b_codes, const uint8_t* b_sf_tiled, float alpha, size_t m, size_t n,
+                               size_t k, int step);
+int mb_tp_reduce_residual(mb_ctx* ctx, mb_stream stream, const void* resid_bf16, size_t t, size_t n, int step,
+                          void** out_dev);
+int mb_tp_symm_destroy(mb_ctx* ctx);
+
 #ifdef __cplusplus
 }
 #endif

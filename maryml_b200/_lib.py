@@ -59,6 +59,12 @@ SIGNATURES = {
     "mb_tp_warm": (_i, [_vp, _vp]),
     "mb_tp_all_reduce": (_i, [_vp, _vp, _vp, _sz, _i]),
     "mb_tp_close": (_i, [_vp]),
+    "mb_tp_symm_bytes": (_sz, [_sz, _sz]),
+    "mb_tp_symm_create": (_i, [_vp, _sz, _sz, C.POINTER(C.c_uint8)]),
+    "mb_tp_symm_attach": (_i, [_vp, C.POINTER(C.c_uint8), _i, _i]),
+    "mb_nvfp4_gemm_w4a4_scatter": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _f, _sz, _sz, _sz, _i]),
+    "mb_tp_reduce_residual": (_i, [_vp, _vp, _vp, _sz, _sz, _i, C.POINTER(_vp)]),
+    "mb_tp_symm_destroy": (_i, [_vp]),
 }
 
 for _name, (_res, _args) in SIGNATURES.items():

@@ -37,7 +37,25 @@ struct mb_ctx {
   void* nccl_lib = nullptr;
   void* nccl_comm = nullptr;
   int tp_rank = 0, tp_world = 1;
+  // Peer-mapped exchange memory of the fused row-parallel path (tp.cu).
+  struct mb_symm* symm = nullptr;
 };
+
+// Exchange memory of one rank, mapped into every rank of the group (CUDA IPC). Layout:
+//   flags   2 x 64 ints    [0..63]: "my GEMM of step s has landed", [64..127]: "my slice of step s has landed"
+//   recv    2 x world x t_max x (n / world) f32   partial tiles pushed here by every rank's GEMM epilogue
+//   out     2 x t_max x n bf16                     reduced + residual-added activations, gathered from all ranks
+struct mb_symm {
+  void* local = nullptr;            // this rank's allocation
+  void* peer[8] = {};               // every rank's allocation as seen from here (peer[rank] == local)
+  void** peer_dev = nullptr;        // the same table in device memory
+  size_t t_max = 0, n = 0, bytes = 0;
+  int world = 1, rank = 0;
+  int* done_counter = nullptr;      // device counter of the reduce kernel's finished CTAs
+};
+__host__ __device__ inline size_t mb_symm_flags_bytes() { return 2 * 64 * sizeof(int); }
+__host__ __device__ inline size_t mb_symm_recv_bytes(size_t t_max, size_t n) { return 2 * t_max * n * sizeof(float); }
+__host__ __device__ inline size_t mb_symm_out_bytes(size_t t_max, size_t n) { return 2 * t_max * n * 2; }
 
 inline int mb_fail(mb_ctx* ctx, int code, const char* fmt, ...) {
   char buf[512];

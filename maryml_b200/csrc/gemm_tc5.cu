@@ -46,7 +46,13 @@ struct GemmParams {
   uint32_t ldo;               // output row stride in elements
   int out_dtype;
   int epilogue;
+  // MB_EPI_SCATTER: f32 partial tiles go straight into the owning rank's exchange memory.
+  float* scatter_base[8];     // recv area (this step's half) of every rank, peer-mapped
+  uint32_t scatter_world, scatter_rank, scatter_nw;   // nw = n / world columns per owner
+  uint32_t scatter_tmax;      // rows of one source slot
 };
+
+constexpr int MB_EPI_SCATTER = 2;   // internal: used by mb_nvfp4_gemm_w4a4_scatter only
 
 template <int KIND, int BN>
 struct Cfg {
@@ -104,6 +110,28 @@ __device__ __forceinline__ void stage_and_store(uint8_t* patch, uint32_t lane, c
 __device__ __forceinline__ void epilogue_chunk(const GemmParams& p, const uint32_t* r, uint32_t col0, uint32_t row0,
                                                uint32_t rows_valid, float scale, uint8_t* patch, uint32_t lane) {
       if (col0 >= p.n) return;       // warp-uniform
+      if (p.epilogue == MB_EPI_SCATTER) {
+        // Reduce-scatter by peer stores: the 32 columns belong to one owner rank; this rank's
+        // f32 partial lands in slot [rank] of the owner's receive area while the next tile's
+        // MMAs run. Two passes of 16 columns through the patch, as for any f32 output.
+        const uint32_t owner = col0 / p.scatter_nw, c_in = col0 - owner * p.scatter_nw;
+        float* dst = p.scatter_base[owner] + (size_t(p.scatter_rank) * p.scatter_tmax + row0) * p.scatter_nw + c_in;
+#pragma unroll
+        for (int hh = 0; hh < 2; ++hh) {
+          uint4 units[4];
+#pragma unroll
+          for (int g = 0; g < 4; ++g) {
+            units[g].x = __float_as_uint(__uint_as_float(r[16 * hh + 4 * g + 0]) * scale);
+            units[g].y = __float_as_uint(__uint_as_float(r[16 * hh + 4 * g + 1]) * scale);
+            units[g].z = __float_as_uint(__uint_as_float(r[16 * hh + 4 * g + 2]) * scale);
+            units[g].w = __float_as_uint(__uint_as_float(r[16 * hh + 4 * g + 3]) * scale);
+          }
+          uint8_t* g8 = reinterpret_cast<uint8_t*>(dst + 16 * hh);
+          stage_and_store(patch, lane, units[0], units[1], g8, size_t(p.scatter_nw) * 4, rows_valid, 2u);
+          stage_and_store(patch, lane, units[2], units[3], g8 + 32, size_t(p.scatter_nw) * 4, rows_valid, 2u);
+        }
+        return;
+      }
       if (p.epilogue == MB_EPI_SWIGLU_INTERLEAVED) {
         // (gate, up) pairs -> bf16(silu(bf16 gate) * bf16 up); 16 outputs = 2 units per row.
         uint32_t w[8];
@@ -694,7 +722,8 @@ int launch_pair(mb_ctx* ctx, cudaStream_t stream, Gemm2Params& pp) {
 int gemm_w4a4_common(mb_ctx* ctx, cudaStream_t stream, const uint8_t* a_codes, const uint8_t* a_sf,
                      const uint8_t* b_codes, const uint8_t* b_sf, const float* rowscale, float alpha,
                      const float* alpha_vec, const int32_t* tile_expert, const int32_t* n_tiles_dev, size_t m,
-                     size_t experts, size_t n, size_t k, void* out, int out_dtype, int epilogue) {
+                     size_t experts, size_t n, size_t k, void* out, int out_dtype, int epilogue,
+                     const mb_symm* symm = nullptr, int step = 0) {
   MB_REQUIRE(ctx, ctx && a_codes && a_sf && b_codes && b_sf && out, "gemm_w4a4: null argument");
   MB_REQUIRE(ctx, m > 0 && n > 0 && k > 0, "gemm_w4a4: empty extent");
   MB_REQUIRE(ctx, k % 64 == 0, "W4A4 needs k a multiple of 64, got %zu", k);
@@ -702,7 +731,8 @@ int gemm_w4a4_common(mb_ctx* ctx, cudaStream_t stream, const uint8_t* a_codes, c
   MB_REQUIRE(ctx, m * k <= 0xFFFFFFFFull && n * k <= 0xFFFFFFFFull && experts * n < (1ull << 31),
              "gemm_w4a4: exceeds u32 indexing");
   MB_REQUIRE(ctx, out_dtype == MB_DT_BF16 || out_dtype == MB_DT_F32, "gemm_w4a4: output is bf16 or f32");
-  MB_REQUIRE(ctx, epilogue == MB_EPI_PLAIN || (epilogue == MB_EPI_SWIGLU_INTERLEAVED && out_dtype == MB_DT_BF16),
+  MB_REQUIRE(ctx, epilogue == MB_EPI_PLAIN || epilogue == MB_EPI_SCATTER ||
+                      (epilogue == MB_EPI_SWIGLU_INTERLEAVED && out_dtype == MB_DT_BF16),
              "gemm_w4a4: the SwiGLU epilogue writes bf16");
   MB_REQUIRE(ctx, mb_aligned(a_codes, 16) && mb_aligned(b_codes, 16) && mb_aligned(a_sf, 16) && mb_aligned(b_sf, 16) &&
                       mb_aligned(out, 16),
@@ -725,6 +755,14 @@ int gemm_w4a4_common(mb_ctx* ctx, cudaStream_t stream, const uint8_t* a_codes, c
   p.sfb_expert_stride = mb_sf_plane_bytes(n, k);
   p.ldo = uint32_t(epilogue == MB_EPI_SWIGLU_INTERLEAVED ? n / 2 : n);
   p.out_dtype = out_dtype; p.epilogue = epilogue;
+  if (epilogue == MB_EPI_SCATTER) {
+    p.scatter_world = uint32_t(symm->world); p.scatter_rank = uint32_t(symm->rank);
+    p.scatter_nw = uint32_t(n / symm->world); p.scatter_tmax = uint32_t(symm->t_max);
+    const size_t half = symm->t_max * symm->n;     // floats in one step's half of a receive area
+    for (int r = 0; r < symm->world; ++r)
+      p.scatter_base[r] = reinterpret_cast<float*>(static_cast<uint8_t*>(symm->peer[r]) + mb_symm_flags_bytes()) +
+                          size_t(step & 1) * half;
+  }
   uint32_t tiles = p.m_tiles * p.n_tiles;
   // Dense products with at least one full pair of row tiles go to the CTA-pair kernel
   // (MB_GEMM_CTA_GROUP=1 in the environment keeps the single-CTA kernel, for comparison runs).
@@ -754,6 +792,19 @@ MB_API int mb_nvfp4_gemm_w4a4(mb_ctx* ctx, mb_stream stream, const uint8_t* a_co
              "W4A4 calibrated globals/product must be finite positive");
   return gemm_w4a4_common(ctx, static_cast<cudaStream_t>(stream), a_codes, a_sf_tiled, b_codes, b_sf_tiled, rowscale,
                           alpha, nullptr, nullptr, nullptr, m, 1, n, k, out, out_dtype, epilogue);
+}
+
+MB_API int mb_nvfp4_gemm_w4a4_scatter(mb_ctx* ctx, mb_stream stream, const uint8_t* a_codes,
+                                      const uint8_t* a_sf_tiled, const uint8_t* b_codes, const uint8_t* b_sf_tiled,
+                                      float alpha, size_t m, size_t n, size_t k, int step) {
+  MB_REQUIRE(ctx, ctx && ctx->symm, "gemm_w4a4_scatter: no exchange memory attached (mb_tp_symm_attach)");
+  const mb_symm* sy = ctx->symm;
+  MB_REQUIRE(ctx, n == sy->n && m <= sy->t_max, "gemm_w4a4_scatter: [%zu, %zu] does not fit the exchange memory [%zu, %zu]",
+             m, n, sy->t_max, sy->n);
+  MB_REQUIRE(ctx, (n / sy->world) % 32 == 0 && n % sy->world == 0, "gemm_w4a4_scatter: n / world must be a multiple of 32");
+  MB_REQUIRE(ctx, alpha == alpha && alpha > 0.0f && alpha <= 3.4e38f, "W4A4 calibrated globals/product must be finite positive");
+  return gemm_w4a4_common(ctx, static_cast<cudaStream_t>(stream), a_codes, a_sf_tiled, b_codes, b_sf_tiled, nullptr,
+                          alpha, nullptr, nullptr, nullptr, m, 1, n, k, sy->local, MB_DT_F32, MB_EPI_SCATTER, sy, step);
 }
 
 MB_API int mb_nvfp4_gemm_w4a4_grouped(mb_ctx* ctx, mb_stream stream, const uint8_t* a_codes,

@@ -6,6 +6,8 @@
 
 #include <dlfcn.h>
 
+#include <algorithm>
+
 namespace {
 
 typedef struct { char internal[128]; } NcclUniqueId;
@@ -118,5 +120,197 @@ MB_API int mb_tp_close(mb_ctx* ctx) {
   }
   ctx->tp_rank = 0;
   ctx->tp_world = 1;
+  return MB_OK;
+}
+
+// ---------------------------------------------------------------------------------
+// Fused row-parallel path over peer memory.
+//
+// The row-parallel GEMM (o, down) pushes its f32 partial tiles from its epilogue straight
+// into the owning rank's receive area (reduce-scatter by peer stores, overlapped with the
+// MMAs of the next tile: mb_nvfp4_gemm_w4a4_scatter). The kernel below then, on every rank:
+//   A  tells every peer "my partials of step s have landed" and waits for theirs,
+//   B  sums its column slice over the source slots in rank order (deterministic), rounds
+//      to bf16, adds the residual, and stores the result into EVERY rank's output buffer
+//      (all-gather by peer stores),
+//   C  tells every peer "my slice of step s has landed" once all its CTAs are done,
+//   D  waits for every peer's slice before it ends, so that the next kernel on the stream
+//      may read the whole output.
+// Plain peer loads/stores only (no multicast). Every wait is bounded; a wait that runs out
+// raises the context's timeout word and the kernel ends. The grid never exceeds the SM
+// count, so CTAs waiting in A or D cannot keep the others from running.
+// ---------------------------------------------------------------------------------
+namespace {
+
+constexpr long long SYMM_WAIT_CYCLES = 2000000000LL;
+
+struct ReduceParams {
+  void* const* peer;          // device table of every rank's exchange memory
+  const __nv_bfloat16* resid; // [t, n] replicated residual stream
+  int* done_counter;
+  int* flag_timeout;
+  uint32_t t, n, nw, t_max, world, rank;
+  int step;
+};
+
+__device__ __forceinline__ int* symm_flags(void* base) { return static_cast<int*>(base); }
+
+__device__ bool wait_flags(volatile int* flags, uint32_t world, int step, int* flag_timeout, int code) {
+  long long t0 = clock64();
+  for (uint32_t r = 0; r < world; ++r) {
+    while (flags[r] < step) {
+      if (clock64() - t0 > SYMM_WAIT_CYCLES) {
+        if (flag_timeout) atomicCAS(flag_timeout, 0, code);
+        return false;
+      }
+    }
+  }
+  return true;
+}
+
+__global__ void __launch_bounds__(256)
+tp_reduce_gather_kernel(const ReduceParams p) {
+  __shared__ int s_ok;
+  void* const local = p.peer[p.rank];
+  // ---- A: my partials have landed everywhere (the GEMM kernel before this one is complete)
+  if (blockIdx.x == 0 && threadIdx.x < p.world) {
+    __threadfence_system();
+    volatile int* f = symm_flags(p.peer[threadIdx.x]);
+    f[p.rank] = p.step;
+  }
+  if (threadIdx.x == 0) s_ok = wait_flags(symm_flags(local), p.world, p.step, p.flag_timeout, 51) ? 1 : 0;
+  __syncthreads();
+  if (!s_ok) return;
+  __threadfence_system();
+  // ---- B: reduce my slice, add the residual, store it into every rank's output
+  const size_t half_recv = size_t(p.t_max) * p.n;                    // floats per step parity
+  const float* recv = reinterpret_cast<const float*>(static_cast<uint8_t*>(local) + mb_symm_flags_bytes()) +
+                      size_t(p.step & 1) * half_recv;
+  const size_t out_off = mb_symm_flags_bytes() + mb_symm_recv_bytes(p.t_max, p.n) +
+                         size_t(p.step & 1) * size_t(p.t_max) * p.n * 2;
+  const uint32_t groups_per_row = p.nw / 8;
+  const size_t total = size_t(p.t) * groups_per_row;
+  for (size_t g = size_t(blockIdx.x) * 256 + threadIdx.x; g < total; g += size_t(gridDim.x) * 256) {
+    const uint32_t row = uint32_t(g / groups_per_row), c = uint32_t(g % groups_per_row) * 8;
+    float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    for (uint32_t r = 0; r < p.world; ++r) {
+      const float4* src = reinterpret_cast<const float4*>(recv + (size_t(r) * p.t_max + row) * p.nw + c);
+      const float4 a = src[0], b = src[1];
+      acc[0] += a.x; acc[1] += a.y; acc[2] += a.z; acc[3] += a.w;
+      acc[4] += b.x; acc[5] += b.y; acc[6] += b.z; acc[7] += b.w;
+    }
+    const uint32_t col = p.rank * p.nw + c;
+    const uint4 rv = *reinterpret_cast<const uint4*>(p.resid + size_t(row) * p.n + col);
+    const uint32_t rw[4] = {rv.x, rv.y, rv.z, rv.w};
+    uint32_t ow[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      // out = bf16(resid + bf16(sum)): the rounding points of add(x, linear(..))
+      const float s0 = __bfloat162float(__float2bfloat16_rn(acc[2 * i]));
+      const float s1 = __bfloat162float(__float2bfloat16_rn(acc[2 * i + 1]));
+      __nv_bfloat162 o = __floats2bfloat162_rn(__uint_as_float(rw[i] << 16) + s0,
+                                               __uint_as_float(rw[i] & 0xFFFF0000u) + s1);
+      ow[i] = *reinterpret_cast<uint32_t*>(&o);
+    }
+    const uint4 ov = make_uint4(ow[0], ow[1], ow[2], ow[3]);
+    for (uint32_t r = 0; r < p.world; ++r) {
+      __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(static_cast<uint8_t*>(p.peer[r]) + out_off);
+      *reinterpret_cast<uint4*>(dst + size_t(row) * p.n + col) = ov;
+    }
+  }
+  // ---- C: the last CTA of this rank tells every peer that the slice has landed
+  __threadfence_system();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const int done = atomicAdd(p.done_counter, 1);
+    if (done == int(gridDim.x) - 1) {
+      *p.done_counter = 0;
+      __threadfence_system();
+      for (uint32_t r = 0; r < p.world; ++r) {
+        volatile int* f = symm_flags(p.peer[r]) + 64;
+        f[p.rank] = p.step;
+      }
+    }
+    // ---- D: every rank's slice is in my output before this kernel ends
+    wait_flags(symm_flags(local) + 64, p.world, p.step, p.flag_timeout, 52);
+    __threadfence_system();
+  }
+}
+
+}  // namespace
+
+MB_API size_t mb_tp_symm_bytes(size_t t_max, size_t n) {
+  return mb_symm_flags_bytes() + mb_symm_recv_bytes(t_max, n) + mb_symm_out_bytes(t_max, n);
+}
+
+MB_API int mb_tp_symm_create(mb_ctx* ctx, size_t t_max, size_t n, uint8_t handle_out[64]) {
+  MB_REQUIRE(ctx, ctx && handle_out && t_max > 0 && n > 0 && n % 8 == 0, "tp_symm_create: bad arguments");
+  MB_REQUIRE(ctx, ctx->symm == nullptr, "tp_symm_create: this context already holds exchange memory");
+  static_assert(sizeof(cudaIpcMemHandle_t) == 64, "IPC handle size");
+  MB_CUDA_OK(ctx, cudaSetDevice(ctx->device));
+  mb_symm* sy = new mb_symm();
+  sy->t_max = t_max; sy->n = n; sy->bytes = mb_tp_symm_bytes(t_max, n);
+  MB_CUDA_OK(ctx, cudaMalloc(&sy->local, sy->bytes));
+  MB_CUDA_OK(ctx, cudaMemset(sy->local, 0, sy->bytes));
+  MB_CUDA_OK(ctx, cudaMalloc(&sy->peer_dev, 8 * sizeof(void*)));
+  MB_CUDA_OK(ctx, cudaMalloc(&sy->done_counter, sizeof(int)));
+  MB_CUDA_OK(ctx, cudaMemset(sy->done_counter, 0, sizeof(int)));
+  cudaIpcMemHandle_t h;
+  MB_CUDA_OK(ctx, cudaIpcGetMemHandle(&h, sy->local));
+  memcpy(handle_out, &h, 64);
+  ctx->symm = sy;
+  return MB_OK;
+}
+
+MB_API int mb_tp_symm_attach(mb_ctx* ctx, const uint8_t* handles, int rank, int world) {
+  MB_REQUIRE(ctx, ctx && ctx->symm && handles, "tp_symm_attach: create the exchange memory first");
+  MB_REQUIRE(ctx, world >= 1 && world <= 8 && rank >= 0 && rank < world, "tp_symm_attach: rank %d of %d", rank, world);
+  mb_symm* sy = ctx->symm;
+  MB_REQUIRE(ctx, sy->n % size_t(world) == 0 && (sy->n / world) % 32 == 0, "tp_symm_attach: n / world must be a multiple of 32");
+  MB_CUDA_OK(ctx, cudaSetDevice(ctx->device));
+  sy->world = world; sy->rank = rank;
+  for (int r = 0; r < world; ++r) {
+    if (r == rank) { sy->peer[r] = sy->local; continue; }
+    cudaIpcMemHandle_t h;
+    memcpy(&h, handles + 64 * r, 64);
+    MB_CUDA_OK(ctx, cudaIpcOpenMemHandle(&sy->peer[r], h, cudaIpcMemLazyEnablePeerAccess));
+  }
+  MB_CUDA_OK(ctx, cudaMemcpy(sy->peer_dev, sy->peer, 8 * sizeof(void*), cudaMemcpyHostToDevice));
+  return MB_OK;
+}
+
+MB_API int mb_tp_reduce_residual(mb_ctx* ctx, mb_stream stream_, const void* resid_bf16, size_t t, size_t n, int step,
+                                 void** out_dev) {
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  MB_REQUIRE(ctx, ctx && ctx->symm && resid_bf16 && out_dev, "tp_reduce_residual: null argument");
+  mb_symm* sy = ctx->symm;
+  MB_REQUIRE(ctx, n == sy->n && t > 0 && t <= sy->t_max, "tp_reduce_residual: [%zu, %zu] does not fit the exchange memory", t, n);
+  MB_REQUIRE(ctx, step > 0, "tp_reduce_residual: steps count from 1");
+  MB_REQUIRE(ctx, mb_aligned(resid_bf16, 16), "tp_reduce_residual: 16-byte alignment");
+  ReduceParams p;
+  p.peer = sy->peer_dev; p.resid = static_cast<const __nv_bfloat16*>(resid_bf16); p.done_counter = sy->done_counter;
+  p.flag_timeout = ctx->flags_dev + MB_FLAG_WAIT_TIMEOUT;
+  p.t = uint32_t(t); p.n = uint32_t(n); p.nw = uint32_t(n / sy->world); p.t_max = uint32_t(sy->t_max);
+  p.world = uint32_t(sy->world); p.rank = uint32_t(sy->rank); p.step = step;
+  const size_t total = t * (p.nw / 8);
+  unsigned grid = unsigned(std::min<size_t>((total + 255) / 256, size_t(ctx->sm_count)));
+  tp_reduce_gather_kernel<<<grid, 256, 0, stream>>>(p);
+  MB_LAUNCH_OK(ctx);
+  *out_dev = static_cast<uint8_t*>(sy->local) + mb_symm_flags_bytes() + mb_symm_recv_bytes(sy->t_max, sy->n) +
+             size_t(step & 1) * sy->t_max * sy->n * 2;
+  return MB_OK;
+}
+
+MB_API int mb_tp_symm_destroy(mb_ctx* ctx) {
+  if (!ctx || !ctx->symm) return MB_OK;
+  mb_symm* sy = ctx->symm;
+  cudaDeviceSynchronize();
+  for (int r = 0; r < sy->world; ++r)
+    if (r != sy->rank && sy->peer[r]) cudaIpcCloseMemHandle(sy->peer[r]);
+  cudaFree(sy->local);
+  cudaFree(sy->peer_dev);
+  cudaFree(sy->done_counter);
+  delete sy;
+  ctx->symm = nullptr;
   return MB_OK;
 }

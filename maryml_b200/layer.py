@@ -149,6 +149,43 @@ class Group:
         lib.mb_tp_close(self.ctx.handle)
 
 
+class FusedExchange:
+    """Peer-mapped exchange memory of the fused row-parallel path (see mb_tp_symm_* in the header):
+    the GEMM epilogue scatters f32 partial tiles into the owning ranks, one kernel reduces, adds the
+    residual and gathers. `exchange_all` all-gathers one bytes object per rank, in rank order."""
+
+    def __init__(self, tp, device, t_max, n, exchange_all):
+        self.tp, self.ctx, self.t_max, self.n, self.step = tp, context(device), t_max, n, 0
+        h = (C.c_uint8 * 64)()
+        self.ctx.check(lib.mb_tp_symm_create(self.ctx.handle, t_max, n, h))
+        handles = b"".join(exchange_all(bytes(h)))
+        buf = (C.c_uint8 * (64 * tp.world)).from_buffer_copy(handles)
+        self.ctx.check(lib.mb_tp_symm_attach(self.ctx.handle, buf, tp.rank, tp.world))
+
+    def gemm_reduce_residual(self, a_codes, a_sf, w, resid, t):
+        """bf16(resid + bf16(sum over ranks of a . w^T * scale2)) as a [t, n] bf16 tensor living in the
+        exchange memory (valid until the step after next)."""
+        self.step += 1
+        self.ctx.check(lib.mb_nvfp4_gemm_w4a4_scatter(self.ctx.handle, _stream(), _p(a_codes), _p(a_sf), _p(w.codes),
+                                                      _p(w.sf_tiled()), w.scale2, t, w.n(), w.k(), self.step))
+        out = C.c_void_p()
+        self.ctx.check(lib.mb_tp_reduce_residual(self.ctx.handle, _stream(), _p(resid), t, self.n, self.step,
+                                                 C.byref(out)))
+        return _wrap_bf16(out.value, t, self.n, resid.device)
+
+    def close(self):
+        lib.mb_tp_symm_destroy(self.ctx.handle)
+
+
+class _DevBuf:
+    def __init__(self, ptr, shape):
+        self.__cuda_array_interface__ = {"shape": shape, "typestr": "<i2", "data": (ptr, False), "version": 3}
+
+
+def _wrap_bf16(ptr, rows, cols, device):
+    return torch.as_tensor(_DevBuf(ptr, (rows, cols)), device=device).view(torch.bfloat16)
+
+
 # ---- the layer -----------------------------------------------------------------------
 class LayerConfig:
     def __init__(self, hidden=4096, heads=32, kv_heads=8, head_dim=128, inter=14336, eps=1e-6, theta=1e6):
@@ -163,8 +200,8 @@ class DecoderLayer:
     (codes [n, k/2], scales [n, k/16], scale2) quantised BEFORE the cut, so every rank
     holds bytes of the same stored tensor (the reference cuts stored planes)."""
 
-    def __init__(self, cfg, full, input_gain, post_gain, tp=None, group=None, device=None):
-        self.cfg, self.tp, self.group = cfg, tp or Tp(), group
+    def __init__(self, cfg, full, input_gain, post_gain, tp=None, group=None, device=None, fused=None):
+        self.cfg, self.tp, self.group, self.fused = cfg, tp or Tp(), group, fused
         dev = device if device is not None else torch.device("cuda", torch.cuda.current_device())
         D = cfg.head_dim
         qh, kvh = self.tp.q_heads(cfg.heads), self.tp.kv_heads(cfg.kv_heads)
@@ -199,11 +236,17 @@ class DecoderLayer:
         codes, sf, _ = nv.quantize_act(x, _lib.QUANT_SCALED, 1.0, tiled=True)
         return nv.gemm_w4a4(codes, sf, w.codes, w.sf_tiled(), w.scale2, t, w.n(), w.k(), out_dtype=out_dtype)
 
-    def _reduced(self, x, w):
+    def _reduced_residual(self, resid, x, w):
+        """bf16(resid + bf16(all-reduced x . w^T)): NCCL all-reduce of the f32 partial then the add,
+        or the fused peer-memory exchange when one is attached."""
+        t = x.shape[0]
+        if self.fused is not None:
+            codes, sf, _ = nv.quantize_act(x, _lib.QUANT_SCALED, 1.0, tiled=True)
+            return self.fused.gemm_reduce_residual(codes, sf, w, resid, t)
         partial = self._linear(x, w, out_dtype=torch.float32)
         if self.group is not None and self.tp.is_split():
             self.group.all_reduce_f32(partial)
-        return partial
+        return add_f32(resid, partial)
 
     def forward(self, x, batch, past, k_cache, v_cache):
         """x [batch * t, hidden] bf16 (t new tokens per sequence, sequence-major). Caches
@@ -230,8 +273,8 @@ class DecoderLayer:
                             if keys != k_cache.shape[1] else k_cache,
                             v_cache[:, :keys].contiguous() if keys != v_cache.shape[1] else v_cache,
                             q0=past, scale=1.0 / math.sqrt(D), causal=True)
-        residual = add_f32(x, self._reduced(a.view(batch * t, self.local_heads * D), self.wo))
+        residual = self._reduced_residual(x, a.view(batch * t, self.local_heads * D), self.wo)
         n = rmsnorm(residual, self.post_gain, cfg.eps)
         gate = self._linear(n, self.wgate)
         up = self._linear(n, self.wup)
-        return add_f32(residual, self._reduced(swiglu(gate, up), self.wdown))
+        return self._reduced_residual(residual, swiglu(gate, up), self.wdown)

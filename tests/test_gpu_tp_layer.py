@@ -39,7 +39,7 @@ def _inputs(orc, cfg, batch, t, cap):
     return x, kc, vc
 
 
-def _worker(rank, world, port, out_path):
+def _worker(rank, world, port, out_path, fused=False):
     os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
     sys.path.insert(0, os.path.dirname(HERE))
     sys.path.insert(0, HERE)
@@ -57,22 +57,41 @@ def _worker(rank, world, port, out_path):
     orc, full, g1, g2 = _fixture(cfg)
     tp = layer.Tp(rank, world)
     group = layer.Group(tp, rank, exchange)
-    L = layer.DecoderLayer(cfg, full, g1, g2, tp=tp, group=group, device=torch.device("cuda", rank))
+    fx = None
+    if fused:
+        def exchange_all(raw):
+            store.set(f"ipc{rank}", raw)
+            return [store.get(f"ipc{r}") for r in range(world)]
+        fx = layer.FusedExchange(tp, rank, 64, cfg.hidden, exchange_all)
+    L = layer.DecoderLayer(cfg, full, g1, g2, tp=tp, group=group, device=torch.device("cuda", rank), fused=fx)
     batch, t, past = 3, 1, 21
     x, kc, vc = _inputs(orc, cfg, batch, t, past + t)
     kv = tp.kv_heads(cfg.kv_heads)
-    y = L.forward(x.cuda(), batch, past, kc[:, :, kv.start:kv.stop].contiguous().cuda(),
-                  vc[:, :, kv.start:kv.stop].contiguous().cuda())
+    kd, vd = kc[:, :, kv.start:kv.stop].contiguous().cuda(), vc[:, :, kv.start:kv.stop].contiguous().cuda()
+    y = L.forward(x.cuda(), batch, past, kd, vd)
+    if fused:
+        # a second and third step through the same exchange memory (both step parities, reused slots)
+        for _ in range(2):
+            y2 = L.forward(x.cuda(), batch, past, kd, vd)
+        torch.cuda.synchronize()
+        assert torch.equal(y2, y)
+        from maryml_b200 import _lib
+        rc, flags = _lib.context(rank).check_flags(None)
+        assert rc == 0, flags
+    y = y.clone()
     torch.cuda.synchronize()
     if rank == 0:
         np.save(out_path, y.float().cpu().numpy())
     store.set(f"done{rank}", b"1")
     for r in range(world):
         store.get(f"done{r}")
+    if fx is not None:
+        fx.close()
     group.close()
 
 
-def test_two_gpu_layer_matches_one_gpu(tmp_path):
+@pytest.mark.parametrize("fused", [False, True])
+def test_two_gpu_layer_matches_one_gpu(tmp_path, fused):
     if not torch.cuda.is_available() or torch.cuda.device_count() < 2:
         pytest.skip("needs two CUDA devices")
     import socket
@@ -82,7 +101,7 @@ def test_two_gpu_layer_matches_one_gpu(tmp_path):
     port = s.getsockname()[1]
     s.close()
     out = str(tmp_path / "tp2.npy")
-    mp.spawn(_worker, args=(2, port, out), nprocs=2, join=True)
+    mp.spawn(_worker, args=(2, port, out, fused), nprocs=2, join=True)
     from maryml_b200 import layer
     cfg = layer.LayerConfig(hidden=512, heads=4, kv_heads=2, head_dim=128, inter=1024)
     orc, full, g1, g2 = _fixture(cfg)
