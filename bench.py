@@ -455,7 +455,9 @@ def run_other(args, rank, world, local_rank):
                 got = [None] * world
                 dist.all_gather_object(got, raw)
                 return got
-            fx = layer.FusedExchange(tp, local_rank, batch * t, cfgL.hidden, exchange_all)
+            # peer stores of 32-byte segments suit decode-sized messages; an 8192-token prompt's 134 MB
+            # partial moves faster through NCCL's bulk all-reduce, so the exchange is sized for <= 1024 rows
+            fx = layer.FusedExchange(tp, local_rank, min(batch * t, 1024), cfgL.hidden, exchange_all)
         L_ = layer.DecoderLayer(cfgL, full, gain, gain, tp=tp, group=group, device=dev, fused=fx)
         del full
         cap = past + t
@@ -486,7 +488,7 @@ def run_other(args, rank, world, local_rank):
                                "peak_source": "4 x " + peaks["source"] + " bf16 burst", "traffic": None,
                                "note": "projections at the FP4 rate dominate; attention runs at the bf16 rate"}
         cfg = {"workload": f"{wl}_hidden4096_heads32_kv8_ffn14336_batch{batch}_t{t}_past{past}", "parallelism": f"tp{world}",
-               "reduce": "fused: GEMM epilogue scatters to peers, one reduce+residual+gather kernel" if fx else
+               "reduce": "fused: GEMM epilogue scatters to peers, one reduce+residual+gather kernel" if (fx and batch * t <= 1024) else
                          ("nccl all-reduce f32 + add" if world > 1 else "none (world 1)")}
         launches = 30
 

@@ -240,7 +240,7 @@ class DecoderLayer:
         """bf16(resid + bf16(all-reduced x . w^T)): NCCL all-reduce of the f32 partial then the add,
         or the fused peer-memory exchange when one is attached."""
         t = x.shape[0]
-        if self.fused is not None:
+        if self.fused is not None and t <= self.fused.t_max:      # decode-sized messages; long prompts go through NCCL
             codes, sf, _ = nv.quantize_act(x, _lib.QUANT_SCALED, 1.0, tiled=True)
             return self.fused.gemm_reduce_residual(codes, sf, w, resid, t)
         partial = self._linear(x, w, out_dtype=torch.float32)
