@@ -230,11 +230,22 @@ class DecoderLayer:
         for w in (self.wq, self.wk, self.wv, self.wo, self.wgate, self.wup, self.wdown):
             w.sf_tiled()
 
-    def _linear(self, x, w, out_dtype=torch.bfloat16):
-        """W4A4 projection (activation quantised per 16 with unit global, src/nn/nvfp4_gemm.rs:644-694)."""
-        t = x.shape[0]
+    @staticmethod
+    def _quantize(x):
+        """The W4A4 lane's activation planes (per-16 scales, unit global; src/nn/nvfp4_gemm.rs:644-669).
+        Projections that share an input share these planes: the bytes are the same as if each
+        projection had quantised the input itself."""
         codes, sf, _ = nv.quantize_act(x, _lib.QUANT_SCALED, 1.0, tiled=True)
+        return codes, sf, x.shape[0]
+
+    @staticmethod
+    def _project(xq, w, out_dtype=torch.bfloat16):
+        codes, sf, t = xq
         return nv.gemm_w4a4(codes, sf, w.codes, w.sf_tiled(), w.scale2, t, w.n(), w.k(), out_dtype=out_dtype)
+
+    def _linear(self, x, w, out_dtype=torch.bfloat16):
+        """W4A4 projection (src/nn/nvfp4_gemm.rs:644-694)."""
+        return self._project(self._quantize(x), w, out_dtype)
 
     def _reduced_residual(self, resid, x, w):
         """bf16(resid + bf16(all-reduced x . w^T)): NCCL all-reduce of the f32 partial then the add,
@@ -254,10 +265,10 @@ class DecoderLayer:
         cfg = self.cfg
         D = cfg.head_dim
         t = x.shape[0] // batch
-        n = rmsnorm(x, self.input_gain, cfg.eps)
-        q = self._linear(n, self.wq)
-        k = self._linear(n, self.wk)
-        v = self._linear(n, self.wv)
+        nq_ = self._quantize(rmsnorm(x, self.input_gain, cfg.eps))
+        q = self._project(nq_, self.wq)
+        k = self._project(nq_, self.wk)
+        v = self._project(nq_, self.wv)
         # rope positions restart for every sequence: one call per sequence when t > 1, one call when t == 1
         if t == 1:
             q = rope(q, 1, batch * self.local_heads, D, past, self.inv_freq)
@@ -274,7 +285,7 @@ class DecoderLayer:
                             v_cache[:, :keys].contiguous() if keys != v_cache.shape[1] else v_cache,
                             q0=past, scale=1.0 / math.sqrt(D), causal=True)
         residual = self._reduced_residual(x, a.view(batch * t, self.local_heads * D), self.wo)
-        n = rmsnorm(residual, self.post_gain, cfg.eps)
-        gate = self._linear(n, self.wgate)
-        up = self._linear(n, self.wup)
+        nq_ = self._quantize(rmsnorm(residual, self.post_gain, cfg.eps))
+        gate = self._project(nq_, self.wgate)
+        up = self._project(nq_, self.wup)
         return self._reduced_residual(residual, swiglu(gate, up), self.wdown)
