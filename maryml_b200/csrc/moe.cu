@@ -151,43 +151,46 @@ plan_scan_kernel(const int32_t* __restrict__ counts, uint32_t n_experts, int32_t
   }
 }
 
-// One block per expert walks the tokens in order; a token that picked the expert
-// takes the next stacked row. Deterministic: expert-ascending, token-ascending.
+// One block per expert. Thread i owns a contiguous run of tokens, counts the run's hits,
+// a block-wide exclusive scan turns the counts into row offsets, and the thread then writes
+// its hits in token order. Deterministic: expert-ascending, token-ascending.
 __global__ void __launch_bounds__(256)
 plan_place_kernel(const int32_t* __restrict__ idx, const float* __restrict__ weight, uint32_t tokens, uint32_t k,
                   const int32_t* __restrict__ expert_row0, int32_t* __restrict__ row_tok,
                   float* __restrict__ row_wgt, int32_t* __restrict__ tok_rows) {
   const int32_t e = blockIdx.x;
   const uint32_t lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const uint32_t per = (tokens + 255) / 256;
+  const uint32_t t_begin = min(tokens, threadIdx.x * per), t_end = min(tokens, t_begin + per);
   __shared__ int32_t s_warp[8];
-  __shared__ int32_t s_base;
-  if (threadIdx.x == 0) s_base = expert_row0[e];
+  int32_t mine = 0;
+  for (uint32_t t = t_begin; t < t_end; ++t) {
+    const int32_t* p = idx + size_t(t) * k;
+    for (uint32_t j = 0; j < k; ++j) mine += p[j] == e;
+  }
+  // exclusive scan of `mine` over the block
+  int32_t incl = mine;
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    int32_t v = __shfl_up_sync(0xFFFFFFFFu, incl, o);
+    if (lane >= uint32_t(o)) incl += v;
+  }
+  if (lane == 31) s_warp[warp] = incl;
   __syncthreads();
-  for (uint32_t t0 = 0; t0 < tokens; t0 += 256) {
-    uint32_t t = t0 + threadIdx.x;
-    int hit = -1;
-    if (t < tokens) {
-      const int32_t* p = idx + size_t(t) * k;
-      for (uint32_t j = 0; j < k; ++j)
-        if (p[j] == e) { hit = int(j); break; }
+  int32_t before = 0;
+  for (uint32_t w = 0; w < warp; ++w) before += s_warp[w];
+  int32_t row = expert_row0[e] + before + incl - mine;
+  for (uint32_t t = t_begin; t < t_end && mine > 0; ++t) {
+    const int32_t* p = idx + size_t(t) * k;
+    for (uint32_t j = 0; j < k; ++j) {
+      if (p[j] == e) {
+        row_tok[row] = int32_t(t);
+        row_wgt[row] = weight[size_t(t) * k + j];
+        tok_rows[size_t(t) * k + j] = row;
+        ++row;
+        break;
+      }
     }
-    uint32_t ballot = __ballot_sync(0xFFFFFFFFu, hit >= 0);
-    if (lane == 0) s_warp[warp] = __popc(ballot);
-    __syncthreads();
-    int32_t before = 0, total = 0;
-    for (int w = 0; w < 8; ++w) {
-      if (w < int(warp)) before += s_warp[w];
-      total += s_warp[w];
-    }
-    if (hit >= 0) {
-      int32_t row = s_base + before + __popc(ballot & ((1u << lane) - 1u));
-      row_tok[row] = int32_t(t);
-      row_wgt[row] = weight[size_t(t) * k + hit];
-      tok_rows[size_t(t) * k + hit] = row;
-    }
-    __syncthreads();
-    if (threadIdx.x == 0) s_base += total;
-    __syncthreads();
   }
 }
 
