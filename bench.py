@@ -386,12 +386,13 @@ def run_other(args, rank, world, local_rank):
             dx.copy_(hx, non_blocking=True)
             out, _ = moe.moe_layer(dx, gate, K, b13, b2)
             hy.copy_(out, non_blocking=True)
-        roof = lambda ms: {"bound": "hbm", "kernel": "whole layer (9 launches)", "achieved": byts / (ms * 1e-3) / 1e9,
+        roof = lambda ms: {"bound": "hbm", "kernel": "whole layer", "achieved": byts / (ms * 1e-3) / 1e9,
                            "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": byts / (ms * 1e-3) / 1e9 / peaks["hbm_gbs"],
                            "peak_source": peaks["source"], "traffic": None, "flop_per_step": flop,
                            "note": "min bytes = expert planes + x + out; the layer is weight-streaming bound at 4096 tokens"}
-        cfg = {"workload": "moe_layer_T4096_h2048_E128_top8_inter768", "lane": "bf16 intermediates, fused SwiGLU"}
-        launches = 14
+        cfg = {"workload": "moe_layer_T4096_h2048_E128_top8_inter768",
+               "lane": "SwiGLU and the second projection's quantizer fused into the first grouped product"}
+        launches = 13
     elif wl in ("attn_decode", "attn_prefill"):
         H, KVH, D = 32, 8, 128
         if wl == "attn_decode":
@@ -492,7 +493,20 @@ def run_other(args, rank, world, local_rank):
         cfg = {"workload": f"{wl}_hidden4096_heads32_kv8_ffn14336_batch{batch}_t{t}_past{past}", "parallelism": f"tp{world}",
                "reduce": "fused: GEMM epilogue scatters to peers, one reduce+residual+gather kernel" if (fx and batch * t <= 1024) else
                          ("nccl all-reduce f32 + add" if world > 1 else "none (world 1)")}
-        launches = 30
+        # kernels of ours per step: norm+quantize, q|k|v product, rotation+append, attention, quantize, o product,
+        # add+norm+quantize, gate/up+SwiGLU+quantize product, down product, add = 10; the decode kernel adds its
+        # combine pass; a product with <= 128 rows and few tiles adds a split-K sum; the fused exchange swaps
+        # (sum, add) for its reduce+residual kernel and runs the second norm+quantize on its own
+        rows = batch * t
+        from maryml_b200 import _lib as _l
+        splitk = lambda n, k: 1 if _l.lib.mb_nvfp4_gemm_splitk_workspace(rows, n, k) else 0
+        hd = cfgL.hidden
+        n_qkv = (L_.local_heads + 2 * L_.local_kv_heads) * D
+        launches = 10 + (1 if decode else 0) + splitk(n_qkv, hd)
+        if fx and rows <= 1024:
+            launches += 1
+        else:
+            launches += splitk(hd, L_.local_heads * D) + splitk(hd, L_.local_inter)
 
     if args.graph:
         # Serving mode: the step is captured once into a CUDA graph (kernels, memsets and the NCCL

@@ -63,9 +63,18 @@ enum {
 /* GEMM epilogues. */
 enum {
   MB_EPI_PLAIN = 0,            /* out = acc * alpha [* rowscale[m]] */
-  MB_EPI_SWIGLU_INTERLEAVED = 1 /* columns (2i, 2i+1) = (gate, up), each rounded to bf16, then
+  MB_EPI_SWIGLU_INTERLEAVED = 1,/* columns (2i, 2i+1) = (gate, up), each rounded to bf16, then
                                   out[m, i] = bf16(silu(gate) * up); out has N/2 columns.
                                   src/models/inkling/fp4gemm.rs:472-507 fused into the GEMM. */
+  MB_EPI_SWIGLU_ROUNDED = 3,    /* the same with silu(gate) itself rounded to bf16 before the product and
+                                  exact exp/divide: the rounding points of the dense layer's swiglu on
+                                  bf16 gate and up tensors (mb_swiglu), so the fusion changes no bit. */
+  /* flags for the two SwiGLU epilogues: the bf16 result is not stored but quantized where it is
+   * produced (32 accumulator columns = 16 results = one NVFP4 block): `out` receives the code
+   * plane [m, n/4 bytes] and `out_sf` the tiled scale plane of an [m, n/2] tensor, the bytes
+   * mb_nvfp4_quantize_act would have written for the stored bf16 result. */
+  MB_EPI_QUANT_RECIP = 0x100,   /* recipe MB_QUANT_RECIP */
+  MB_EPI_QUANT_SCALED = 0x200   /* recipe MB_QUANT_SCALED with input_scale 1 */
 };
 
 /* ---- context ---------------------------------------------------------------- */
@@ -132,6 +141,18 @@ int mb_nvfp4_gemm_w4a4(mb_ctx* ctx, mb_stream stream, const uint8_t* a_codes, co
                        const uint8_t* b_codes, const uint8_t* b_sf_tiled, const float* rowscale, float alpha,
                        size_t m, size_t n, size_t k, void* out, int out_dtype, int epilogue);
 
+/* The same product for decode-sized activations (m <= 128), where a [m, n] output has too few
+ * tiles to keep 148 SMs streaming weights (the reference's own answer at this size is its
+ * one-plane-per-tile grid, src/nn/nvfp4_gemm.rs:200-291): K is cut into slices that land in f32
+ * planes of `workspace` and are summed in slice order (deterministic) with the epilogue scale.
+ * mb_nvfp4_gemm_splitk_workspace returns the bytes to provide, 0 when the shape is not split;
+ * with a null or short workspace the call is mb_nvfp4_gemm_w4a4. */
+size_t mb_nvfp4_gemm_splitk_workspace(size_t m, size_t n, size_t k);
+int mb_nvfp4_gemm_w4a4_splitk(mb_ctx* ctx, mb_stream stream, const uint8_t* a_codes, const uint8_t* a_sf_tiled,
+                              const uint8_t* b_codes, const uint8_t* b_sf_tiled, const float* rowscale, float alpha,
+                              size_t m, size_t n, size_t k, void* out, int out_dtype, void* workspace,
+                              size_t workspace_bytes);
+
 /* fp4_linear_grouped(_bf16)_launch (src/models/inkling/moegroup.rs:430-751): the
  * stacked rows of all active experts against an expert bank. a: [m_cap, k] planes
  * (each expert's rows padded to 128). bank: [experts, n, k] planes with tiled scales
@@ -140,7 +161,20 @@ int mb_nvfp4_gemm_w4a4(mb_ctx* ctx, mb_stream stream, const uint8_t* a_codes, co
 int mb_nvfp4_gemm_w4a4_grouped(mb_ctx* ctx, mb_stream stream, const uint8_t* a_codes, const uint8_t* a_sf_tiled,
                                const uint8_t* bank_codes, const uint8_t* bank_sf_tiled, const float* alpha,
                                const int32_t* tile_expert, const int32_t* n_tiles_dev, size_t m_cap,
-                               size_t experts, size_t n, size_t k, void* out, int out_dtype, int epilogue);
+                               size_t experts, size_t n, size_t k, void* out, int out_dtype, int epilogue,
+                               void* out_sf);
+
+/* Several projections of one input stacked along n (q|k|v, or gate and up interleaved row by
+ * row), each stored tensor keeping its own global scale: colscale[n] holds the scale2 of the
+ * tensor a column belongs to, out[m, c] = acc * colscale[c], rounded once, which is what the
+ * separate products give (src/nn/nvfp4_gemm.rs:644-694 called once per projection). The
+ * activation planes carry a unit global. epilogue: any MB_EPI_* word; out_sf as for the flags
+ * above, else null. workspace: optional split-K planes as for mb_nvfp4_gemm_w4a4_splitk (plain
+ * epilogue only). n % 32 == 0. */
+int mb_nvfp4_gemm_w4a4_stacked(mb_ctx* ctx, mb_stream stream, const uint8_t* a_codes, const uint8_t* a_sf_tiled,
+                               const uint8_t* b_codes, const uint8_t* b_sf_tiled, const float* colscale, size_t m,
+                               size_t n, size_t k, void* out, int out_dtype, int epilogue, void* out_sf,
+                               void* workspace, size_t workspace_bytes);
 
 /* bf16_linear_launch (src/models/inkling/bf16gemm.rs:64-152): [m, k] x [n, k]^T,
  * bf16 operands, f32 accumulation (tcgen05 kind::f16), out = acc * alpha as bf16 or
@@ -221,6 +255,26 @@ int mb_add_f32(mb_ctx* ctx, mb_stream stream, const void* a_bf16, const float* b
 /* rope_kernel (src/models/breeze/cuda_ops.rs:286-320): x [tokens, heads, d], in place allowed. */
 int mb_rope(mb_ctx* ctx, mb_stream stream, const void* x_bf16, size_t tokens, size_t heads, size_t d,
             size_t past, const float* inv_freq, void* out_bf16);
+
+/* The same glue with fewer passes over the activations; every value is computed by the
+ * arithmetic, in the order, of the separate entry points above, so the bytes are the same.
+ *
+ * mb_residual_norm_quantize: [r = bf16(resid + bf16(partial)), stored to resid_out, when a
+ * partial f32 sum is given, else r = resid;] y = rmsnorm(r, gain) as mb_rmsnorm; y goes out as
+ * W4A4 activation planes (codes [rows, width/2], tiled scale plane) as mb_nvfp4_quantize_act
+ * with MB_QUANT_SCALED and input_scale 1 writes them. width % 64 == 0, width <= 8192.
+ * The chain add_bf16 -> RmsNorm::forward -> quantize of src/nn/nvfp4_gemm.rs:644-669. */
+int mb_residual_norm_quantize(mb_ctx* ctx, mb_stream stream, const void* resid, const float* partial, const void* gain,
+                              size_t rows, size_t width, float eps, void* resid_out, uint8_t* codes,
+                              uint8_t* sf_tiled);
+
+/* mb_rope_append: qkv is a stacked projection [batch * t, (hq + 2 hkv) * d] bf16 (sequence
+ * major, t new tokens per sequence at positions past .. past + t). q heads are rotated into
+ * q_out [batch * t, hq * d]; k heads are rotated and v heads copied into the caches
+ * [batch, capacity, hkv, d] at [past, past + t). Per element it is mb_rope. d % 16 == 0. */
+int mb_rope_append(mb_ctx* ctx, mb_stream stream, const void* qkv, size_t batch, size_t t, size_t hq, size_t hkv,
+                   size_t d, size_t past, const float* inv_freq, void* q_out, void* k_cache, void* v_cache,
+                   size_t capacity);
 
 /* ---- tensor parallel ---------------------------------------------------------------- */
 /* Tp::shard (src/models/inkling/tp.rs:540-555). Host arithmetic only. */

@@ -20,7 +20,8 @@ OK, ERR_INVALID, ERR_CUDA, ERR_NONFINITE, ERR_DEVICE_FLAG, ERR_UNAVAILABLE = 0, 
 DT_BF16, DT_F32 = 0, 1
 SF_ROWMAJOR, SF_TILED = 0, 1
 QUANT_SCALED, QUANT_RECIP, QUANT_ROWS = 0, 1, 2
-EPI_PLAIN, EPI_SWIGLU_INTERLEAVED = 0, 1
+EPI_PLAIN, EPI_SWIGLU_INTERLEAVED, EPI_SWIGLU_ROUNDED = 0, 1, 3
+EPI_QUANT_RECIP, EPI_QUANT_SCALED = 0x100, 0x200
 
 _vp, _sz, _f, _i = C.c_void_p, C.c_size_t, C.c_float, C.c_int
 
@@ -38,7 +39,11 @@ SIGNATURES = {
     "mb_nvfp4_untile_scales": (_i, [_vp, _vp, _vp, _sz, _sz, _vp]),
     "mb_nvfp4_gemv_w4a16": (_i, [_vp, _vp, _vp, _sz, _vp, _vp, _f, _sz, _sz, _vp, _i]),
     "mb_nvfp4_gemm_w4a4": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _f, _sz, _sz, _sz, _vp, _i, _i]),
-    "mb_nvfp4_gemm_w4a4_grouped": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _sz, _sz, _sz, _sz, _vp, _i, _i]),
+    "mb_nvfp4_gemm_splitk_workspace": (_sz, [_sz, _sz, _sz]),
+    "mb_nvfp4_gemm_w4a4_splitk": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _f, _sz, _sz, _sz, _vp, _i, _vp, _sz]),
+    "mb_nvfp4_gemm_w4a4_grouped": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _sz, _sz, _sz, _sz, _vp, _i, _i,
+                                        _vp]),
+    "mb_nvfp4_gemm_w4a4_stacked": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _sz, _sz, _sz, _vp, _i, _i, _vp, _vp, _sz]),
     "mb_bf16_gemm": (_i, [_vp, _vp, _vp, _vp, _f, _sz, _sz, _sz, _vp, _i]),
     "mb_router_topk_softmax": (_i, [_vp, _vp, _vp, _sz, _sz, _sz, _i, _f, _vp, _vp]),
     "mb_moe_plan_rows": (_sz, [_sz, _sz, _sz]),
@@ -53,6 +58,8 @@ SIGNATURES = {
     "mb_add_f32": (_i, [_vp, _vp, _vp, _vp, _sz, _vp]),
     "mb_swiglu": (_i, [_vp, _vp, _vp, _vp, _sz, _vp]),
     "mb_rope": (_i, [_vp, _vp, _vp, _sz, _sz, _sz, _sz, _vp, _vp]),
+    "mb_residual_norm_quantize": (_i, [_vp, _vp, _vp, _vp, _vp, _sz, _sz, _f, _vp, _vp, _vp]),
+    "mb_rope_append": (_i, [_vp, _vp, _vp, _sz, _sz, _sz, _sz, _sz, _sz, _vp, _vp, _vp, _vp, _sz]),
     "mb_tp_shard": (_i, [_sz, _sz, _sz, C.POINTER(_sz), C.POINTER(_sz)]),
     "mb_tp_unique_id": (_i, [_vp, C.POINTER(C.c_uint8)]),
     "mb_tp_form": (_i, [_vp, C.POINTER(C.c_uint8), _i, _i]),

@@ -7,8 +7,8 @@
 //   warp 1   MMA issuer: tcgen05.mma (kind::mxf4nvf4 block-scaled, or kind::f16)
 //            with the accumulator in tensor memory; scale atoms are copied
 //            shared -> TMEM by tcgen05.cp right before the MMAs that read them.
-//   warps 2-9 epilogue: tcgen05.ld the finished accumulator, scale, convert, store;
-//            two warps per TMEM lane quadrant, each taking half of the columns.
+//   warps 2-17 epilogue: tcgen05.ld the finished accumulator, scale, convert, store;
+//            four warps per TMEM lane quadrant, each taking a quarter of the columns.
 //
 // Two accumulators alternate so that the epilogue of tile i overlaps the MMAs of
 // tile i+1. TMEM has 512 columns; the NVFP4 kernel also keeps scale factors there,
@@ -18,6 +18,7 @@
 // NVFP4 algorithmic work per tile: 2*128*BN*K flop; bytes from L2: (128+BN)*K*(1/2+1/16).
 // Every mbarrier wait is bounded (tc5::mbar_wait).
 #include "common.cuh"
+#include "quant_block.cuh"
 #include "tc5.cuh"
 
 namespace {
@@ -50,9 +51,19 @@ struct GemmParams {
   float* scatter_base[8];     // recv area (this step's half) of every rank, peer-mapped
   uint32_t scatter_world, scatter_rank, scatter_nw;   // nw = n / world columns per owner
   uint32_t scatter_tmax;      // rows of one source slot
+  // split-K (few output tiles, long K): tile index carries a K slice; partial sums go to a workspace
+  uint32_t splits, ks_per_split;
+  // stacked projections / fused output quantization
+  const float* colscale;      // [n] per-column factor or null
+  uint8_t* out_sf;            // tiled scale plane of the quantized output
+  uint32_t out_sf_kchunks;
+  int silu_rounded;           // SwiGLU epilogue: round silu(gate) to bf16 before the product
+  int quant;                  // SwiGLU epilogue: 0 bf16 out, 1 NVFP4 (reciprocal recipe), 2 NVFP4 (divide recipe, unit global)
 };
 
 constexpr int MB_EPI_SCATTER = 2;   // internal: used by mb_nvfp4_gemm_w4a4_scatter only
+
+constexpr int EPI_WARPS_ = 16;      // four epilogue warps per TMEM lane quadrant
 
 template <int KIND, int BN>
 struct Cfg {
@@ -63,7 +74,7 @@ struct Cfg {
   static constexpr int SFB_BYTES = KIND == KIND_NVF4 ? (BN / 128) * 2048 : 0;
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES + SFA_BYTES + SFB_BYTES;
   static constexpr int STAGES = (KIND == KIND_NVF4) ? (BN == 256 ? 4 : 6) : (BN == 256 ? 4 : 6);
-  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*alignment*/ + 256 /*barriers*/ + 8 * 1024 /*store patches*/;
+  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*alignment*/ + 256 /*barriers*/ + EPI_WARPS_ * 512 /*store patches*/;
   // TMEM columns
   static constexpr bool OVERLAP = (KIND == KIND_NVF4 && BN == 256);
   static constexpr int ACC0 = 0;
@@ -75,8 +86,25 @@ struct Cfg {
   static_assert(KIND == KIND_NVF4 || 2 * BN <= 512, "TMEM budget");
 };
 
-constexpr int NUM_THREADS = 320;   // producer warp, MMA warp, eight epilogue warps (two per TMEM lane quadrant)
-constexpr int EPI_THREADS = 256;
+// Development aid, compiled in only with -DMB_GEMM_PROFILE: cycles each role of the single-CTA kernel spends
+// waiting, per CTA. Slots: 0 producer on a free stage, 1 MMA on a free accumulator, 2 MMA on loaded operands,
+// 3 first epilogue warp on a finished accumulator, 4 that warp's work, 5 whole kernel, 6 tiles.
+#ifdef MB_GEMM_PROFILE
+__device__ unsigned long long g_gemm_prof[160 * 8];
+__device__ int g_gemm_dbg;
+#define PROF_T0() const long long prof_t0_ = clock64()
+#define PROF_ADD(slot) do { if ((threadIdx.x & 31) == 0) atomicAdd(&g_gemm_prof[blockIdx.x * 8 + (slot)], (unsigned long long)(clock64() - prof_t0_)); } while (0)
+#else
+#define PROF_T0() do {} while (0)
+#define PROF_ADD(slot) do {} while (0)
+#endif
+
+// Producer warp, MMA warp, sixteen epilogue warps. The epilogue is a chain of dependent conversions,
+// special-function ops and shared-memory round trips; four warps per scheduler hide those latencies where two
+// left the issue slots three quarters empty (measured: the epilogue, not the tensor pipe, bounded short-K tiles).
+constexpr int EPI_WARPS = EPI_WARPS_;
+constexpr int NUM_THREADS = 64 + 32 * EPI_WARPS;
+constexpr int EPI_THREADS = 32 * EPI_WARPS;
 
 __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
   __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
@@ -84,32 +112,61 @@ __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
 }
 
 
-// Warp-level transpose through a 1 KB shared-memory patch so that global stores are
-// coalesced: on entry lane l holds two 16-byte units of ITS row (32 rows x 32 bytes);
-// on exit each store instruction writes 16 rows x 32 contiguous bytes (whole sectors).
-// The XOR on the unit index keeps the 128-bit shared stores and loads conflict free.
+// Warp-level transpose through a 512-byte shared-memory patch so that global stores are
+// coalesced: on entry lane l holds two 16-byte units of ITS row (32 rows x 32 bytes); each
+// half of the warp in turn parks its 16 rows in the patch and the whole warp stores them,
+// one instruction writing 16 rows x 32 contiguous bytes (whole sectors). The XOR on the unit
+// index keeps the 128-bit shared stores and loads conflict free.
 __device__ __forceinline__ void stage_and_store(uint8_t* patch, uint32_t lane, const uint4& u0, const uint4& u1,
                                                 uint8_t* gbase, size_t row_stride_bytes, uint32_t rows_valid,
                                                 uint32_t units_valid) {
-  const uint32_t swz_w = (lane >> 2) & 1u;
-  *reinterpret_cast<uint4*>(patch + lane * 32 + ((0u ^ swz_w) * 16)) = u0;
-  *reinterpret_cast<uint4*>(patch + lane * 32 + ((1u ^ swz_w) * 16)) = u1;
-  __syncwarp();
+#ifdef MB_GEMM_PROFILE
+  const int dbg = g_gemm_dbg;
+  if (dbg & 2) { if ((u0.x ^ u1.y) == 0x12345678u && rows_valid == 77u) *reinterpret_cast<uint4*>(gbase) = u0; return; }
+#endif
+  const uint32_t lr = lane & 15u;
+  const uint32_t swz_w = (lr >> 2) & 1u;
+  const uint32_t rr = lane >> 1, u = lane & 1u;          // the row (of 16) and unit this lane stores
+  const uint32_t swz_r = (rr >> 2) & 1u;
 #pragma unroll
   for (int i = 0; i < 2; ++i) {
-    const uint32_t r = i * 16 + (lane >> 1), u = lane & 1u;
-    const uint32_t swz_r = (r >> 2) & 1u;
-    const uint4 v = *reinterpret_cast<const uint4*>(patch + r * 32 + ((u ^ swz_r) * 16));
+    if ((lane >> 4) == uint32_t(i)) {
+      *reinterpret_cast<uint4*>(patch + lr * 32 + ((0u ^ swz_w) * 16)) = u0;
+      *reinterpret_cast<uint4*>(patch + lr * 32 + ((1u ^ swz_w) * 16)) = u1;
+    }
+    __syncwarp();
+    const uint4 v = *reinterpret_cast<const uint4*>(patch + rr * 32 + ((u ^ swz_r) * 16));
+    const uint32_t r = i * 16 + rr;
+#ifdef MB_GEMM_PROFILE
+    if (dbg & 1) { if (v.x == 0x12345678u && rows_valid == 77u) *reinterpret_cast<uint4*>(gbase) = v; __syncwarp(); continue; }
+#endif
     if (r < rows_valid && u < units_valid)
       *reinterpret_cast<uint4*>(gbase + size_t(r) * row_stride_bytes + u * 16) = v;
+    __syncwarp();
   }
-  __syncwarp();
 }
 
 // One 32-column chunk of one warp's 32 accumulator rows: scale, convert, transpose, store.
 __device__ __forceinline__ void epilogue_chunk(const GemmParams& p, const uint32_t* r, uint32_t col0, uint32_t row0,
                                                uint32_t rows_valid, float scale, uint8_t* patch, uint32_t lane) {
       if (col0 >= p.n) return;       // warp-uniform
+      // acc * alpha [* rowscale], and for stacked projections * the column's own global scale
+      // (the entry point keeps alpha at 1 there, so the product is rounded once)
+      float v[32];
+      if (p.colscale) {
+        const float4* cs = reinterpret_cast<const float4*>(p.colscale + col0);
+#pragma unroll
+        for (int g = 0; g < 8; ++g) {
+          const float4 c = __ldg(cs + g);
+          v[4 * g + 0] = __uint_as_float(r[4 * g + 0]) * scale * c.x;
+          v[4 * g + 1] = __uint_as_float(r[4 * g + 1]) * scale * c.y;
+          v[4 * g + 2] = __uint_as_float(r[4 * g + 2]) * scale * c.z;
+          v[4 * g + 3] = __uint_as_float(r[4 * g + 3]) * scale * c.w;
+        }
+      } else {
+#pragma unroll
+        for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]) * scale;
+      }
       if (p.epilogue == MB_EPI_SCATTER) {
         // Reduce-scatter by peer stores: the 32 columns belong to one owner rank; this rank's
         // f32 partial lands in slot [rank] of the owner's receive area while the next tile's
@@ -121,10 +178,10 @@ __device__ __forceinline__ void epilogue_chunk(const GemmParams& p, const uint32
           uint4 units[4];
 #pragma unroll
           for (int g = 0; g < 4; ++g) {
-            units[g].x = __float_as_uint(__uint_as_float(r[16 * hh + 4 * g + 0]) * scale);
-            units[g].y = __float_as_uint(__uint_as_float(r[16 * hh + 4 * g + 1]) * scale);
-            units[g].z = __float_as_uint(__uint_as_float(r[16 * hh + 4 * g + 2]) * scale);
-            units[g].w = __float_as_uint(__uint_as_float(r[16 * hh + 4 * g + 3]) * scale);
+            units[g].x = __float_as_uint(v[16 * hh + 4 * g + 0]);
+            units[g].y = __float_as_uint(v[16 * hh + 4 * g + 1]);
+            units[g].z = __float_as_uint(v[16 * hh + 4 * g + 2]);
+            units[g].w = __float_as_uint(v[16 * hh + 4 * g + 3]);
           }
           uint8_t* g8 = reinterpret_cast<uint8_t*>(dst + 16 * hh);
           stage_and_store(patch, lane, units[0], units[1], g8, size_t(p.scatter_nw) * 4, rows_valid, 2u);
@@ -133,19 +190,45 @@ __device__ __forceinline__ void epilogue_chunk(const GemmParams& p, const uint32
         return;
       }
       if (p.epilogue == MB_EPI_SWIGLU_INTERLEAVED) {
-        // (gate, up) pairs -> bf16(silu(bf16 gate) * bf16 up); 16 outputs = 2 units per row.
+        // (gate, up) pairs -> bf16(silu(bf16 gate) * bf16 up); 16 outputs per row = one NVFP4 block.
+        float o[16];
+#pragma unroll
+        for (int i = 0; i < 16; i += 2) {
+          // packed conversions (one instruction per pair) instead of scalar ones, which share the
+          // special-function unit with the exponential and the reciprocal
+          const uint32_t gu0 = pack_bf16x2(v[2 * i], v[2 * i + 1]), gu1 = pack_bf16x2(v[2 * i + 2], v[2 * i + 3]);
+          const float g0 = __uint_as_float(gu0 << 16), u0 = __uint_as_float(gu0 & 0xFFFF0000u);
+          const float g1 = __uint_as_float(gu1 << 16), u1 = __uint_as_float(gu1 & 0xFFFF0000u);
+          float t0, t1;
+          if (p.silu_rounded) {   // the dense layer's order: silu rounded to bf16, then the product
+            const uint32_t s01 = pack_bf16x2(__fdiv_rn(g0, 1.0f + expf(-g0)), __fdiv_rn(g1, 1.0f + expf(-g1)));
+            t0 = __uint_as_float(s01 << 16) * u0;
+            t1 = __uint_as_float(s01 & 0xFFFF0000u) * u1;
+          } else {                // fast exp/divide: a bf16 result hides their last bits
+            t0 = __fdividef(g0, 1.0f + __expf(-g0)) * u0;
+            t1 = __fdividef(g1, 1.0f + __expf(-g1)) * u1;
+          }
+          const uint32_t o01 = pack_bf16x2(t0, t1);
+          o[i] = __uint_as_float(o01 << 16);
+          o[i + 1] = __uint_as_float(o01 & 0xFFFF0000u);
+        }
+        if (p.quant) {
+          // The block goes out as NVFP4 for the next projection: 8 bytes of codes and one byte of
+          // the tiled scale plane per row, the bytes the stand-alone quantizer would write.
+          uint32_t sbyte;
+          uint2 codes;
+          if (p.quant == 1) quant_block_recip(o, sbyte, codes);
+          else quant_block_scaled(o, 1.0f, sbyte, codes);
+          if (lane < rows_valid) {
+            const uint32_t row = row0 + lane, kb = col0 >> 5;
+            *reinterpret_cast<uint2*>(static_cast<uint8_t*>(p.out) + size_t(row) * (p.n >> 2) + size_t(kb) * 8) = codes;
+            p.out_sf[mb_sf_offset(row, kb, p.out_sf_kchunks)] = uint8_t(sbyte);
+          }
+          return;
+        }
         uint32_t w[8];
 #pragma unroll
-        for (int i = 0; i < 8; ++i) {
-          float v[2];
-#pragma unroll
-          for (int h = 0; h < 2; ++h) {
-            float g = __bfloat162float(__float2bfloat16_rn(__uint_as_float(r[4 * i + 2 * h]) * scale));
-            float u = __bfloat162float(__float2bfloat16_rn(__uint_as_float(r[4 * i + 2 * h + 1]) * scale));
-            v[h] = __fdividef(g, 1.0f + __expf(-g)) * u;   // fast exp/divide: a bf16 result hides their last bits
-          }
-          w[i] = pack_bf16x2(v[0], v[1]);
-        }
+        for (int i = 0; i < 8; ++i) w[i] = pack_bf16x2(o[2 * i], o[2 * i + 1]);
         uint8_t* g = static_cast<uint8_t*>(p.out) + (size_t(row0) * p.ldo + col0 / 2) * 2;
         stage_and_store(patch, lane, make_uint4(w[0], w[1], w[2], w[3]), make_uint4(w[4], w[5], w[6], w[7]), g,
                         size_t(p.ldo) * 2, rows_valid, min(2u, (p.n - col0) / 16));
@@ -153,10 +236,10 @@ __device__ __forceinline__ void epilogue_chunk(const GemmParams& p, const uint32
         uint4 units[4];
 #pragma unroll
         for (int g = 0; g < 4; ++g) {
-          units[g].x = pack_bf16x2(__uint_as_float(r[8 * g + 0]) * scale, __uint_as_float(r[8 * g + 1]) * scale);
-          units[g].y = pack_bf16x2(__uint_as_float(r[8 * g + 2]) * scale, __uint_as_float(r[8 * g + 3]) * scale);
-          units[g].z = pack_bf16x2(__uint_as_float(r[8 * g + 4]) * scale, __uint_as_float(r[8 * g + 5]) * scale);
-          units[g].w = pack_bf16x2(__uint_as_float(r[8 * g + 6]) * scale, __uint_as_float(r[8 * g + 7]) * scale);
+          units[g].x = pack_bf16x2(v[8 * g + 0], v[8 * g + 1]);
+          units[g].y = pack_bf16x2(v[8 * g + 2], v[8 * g + 3]);
+          units[g].z = pack_bf16x2(v[8 * g + 4], v[8 * g + 5]);
+          units[g].w = pack_bf16x2(v[8 * g + 6], v[8 * g + 7]);
         }
         uint8_t* g = static_cast<uint8_t*>(p.out) + (size_t(row0) * p.ldo + col0) * 2;
         const uint32_t uv = (p.n - col0) / 8;
@@ -169,10 +252,10 @@ __device__ __forceinline__ void epilogue_chunk(const GemmParams& p, const uint32
           uint4 units[4];
 #pragma unroll
           for (int g = 0; g < 4; ++g) {
-            units[g].x = __float_as_uint(__uint_as_float(r[16 * hh + 4 * g + 0]) * scale);
-            units[g].y = __float_as_uint(__uint_as_float(r[16 * hh + 4 * g + 1]) * scale);
-            units[g].z = __float_as_uint(__uint_as_float(r[16 * hh + 4 * g + 2]) * scale);
-            units[g].w = __float_as_uint(__uint_as_float(r[16 * hh + 4 * g + 3]) * scale);
+            units[g].x = __float_as_uint(v[16 * hh + 4 * g + 0]);
+            units[g].y = __float_as_uint(v[16 * hh + 4 * g + 1]);
+            units[g].z = __float_as_uint(v[16 * hh + 4 * g + 2]);
+            units[g].w = __float_as_uint(v[16 * hh + 4 * g + 3]);
           }
           const uint32_t c0 = col0 + 16 * hh;
           if (c0 < p.n) {
@@ -206,6 +289,9 @@ gemm_tc5_kernel(const __grid_constant__ GemmParams p) {
   const int warp = __shfl_sync(0xFFFFFFFFu, int(threadIdx.x >> 5), 0);   // warp-uniform by construction
   const int lane = threadIdx.x & 31;
   int* tflag = p.flags ? p.flags + MB_FLAG_WAIT_TIMEOUT : nullptr;
+#ifdef MB_GEMM_PROFILE
+  const long long prof_k0 = clock64();
+#endif
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < C::STAGES; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
@@ -227,7 +313,7 @@ gemm_tc5_kernel(const __grid_constant__ GemmParams p) {
   const uint32_t tmem_base = *tmem_ptr_smem;
 
   const uint32_t m_tiles = p.n_mtiles_dev ? uint32_t(*p.n_mtiles_dev) : p.m_tiles;
-  const uint32_t total_tiles = m_tiles * p.n_tiles;
+  const uint32_t total_tiles = m_tiles * p.n_tiles * p.splits;
 
   // The two issuing roles run with all 32 lanes converged; every asynchronous
   // instruction (TMA, tcgen05.cp/mma/commit) sits under elect_one() so that the
@@ -244,7 +330,9 @@ gemm_tc5_kernel(const __grid_constant__ GemmParams p) {
     int e_next = 0;
     if (p.tile_expert && blockIdx.x < total_tiles) e_next = p.tile_expert[blockIdx.x % m_tiles];
     for (uint32_t tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
-      const uint32_t mt = tile % m_tiles, nt = tile / m_tiles;
+      const uint32_t sp = tile % p.splits, rest = tile / p.splits;
+      const uint32_t mt = rest % m_tiles, nt = rest / m_tiles;
+      const uint32_t ks0 = sp * p.ks_per_split, ks1 = min(p.k_steps, ks0 + p.ks_per_split);
       uint32_t brow = nt * BN;
       const uint8_t* sfb = p.sfb;
       if (p.tile_expert) {
@@ -255,8 +343,10 @@ gemm_tc5_kernel(const __grid_constant__ GemmParams p) {
         brow += uint32_t(e) * p.b_rows_per_expert;
         sfb += uint64_t(e) * p.sfb_expert_stride;
       }
-      for (uint32_t ks = 0; ks < p.k_steps; ++ks) {
+      for (uint32_t ks = ks0; ks < ks1; ++ks) {
+        { PROF_T0();
         if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_smem, tflag, 1)) { ok = false; break; }
+        PROF_ADD(0); }
         const uint32_t sa = smem_base + stage * C::STAGE_BYTES;
         const uint32_t sb = sa + C::A_BYTES;
         armed |= 1u << stage;
@@ -300,14 +390,22 @@ gemm_tc5_kernel(const __grid_constant__ GemmParams p) {
       const uint32_t buf = it & 1u;
       if (C::OVERLAP) {
         // The previous tile's epilogue has drained the 64 shared columns.
+        PROF_T0();
         if (it > 0 && !mbar_wait(ovl_free_bar, (it - 1u) & 1u, abort_smem, tflag, 2)) { ok = false; break; }
+        PROF_ADD(1);
       } else {
+        PROF_T0();
         if (!mbar_wait(acc_empty_bar(buf), ((it >> 1) & 1u) ^ 1u, abort_smem, tflag, 2)) { ok = false; break; }
+        PROF_ADD(1);
       }
       fence_after_sync();
       const uint32_t d_tmem = tmem_base + (buf ? C::ACC1 : C::ACC0);
-      for (uint32_t ks = 0; ks < p.k_steps; ++ks) {
+      const uint32_t sp = tile % p.splits;
+      const uint32_t ks0 = sp * p.ks_per_split, ks1 = min(p.k_steps, ks0 + p.ks_per_split);
+      for (uint32_t ks = ks0; ks < ks1; ++ks) {
+        { PROF_T0();
         if (!mbar_wait(full_bar(stage), phase, abort_smem, tflag, 3)) { ok = false; break; }
+        PROF_ADD(2); }
         fence_after_sync();
         const uint32_t sa = smem_base + stage * C::STAGE_BYTES;
         const uint32_t sb = sa + C::A_BYTES;
@@ -328,7 +426,7 @@ gemm_tc5_kernel(const __grid_constant__ GemmParams p) {
           const uint64_t bdesc = make_kmajor_sw128_desc(sb);
 #pragma unroll
           for (int j = 0; j < 4; ++j) {
-            const uint32_t acc = (ks | uint32_t(j)) != 0u;
+            const uint32_t acc = ((ks - ks0) | uint32_t(j)) != 0u;
             // 32 bytes of K per instruction: the descriptor start address advances by 2 (16-byte units).
             if (KIND == KIND_NVF4)
               mma_nvf4(d_tmem, adesc + 2 * j, bdesc + 2 * j, idesc, tmem_base + C::SFA_COL + 4 * j,
@@ -337,7 +435,7 @@ gemm_tc5_kernel(const __grid_constant__ GemmParams p) {
               mma_f16(d_tmem, adesc + 2 * j, bdesc + 2 * j, idesc, acc);
           }
           umma_commit(empty_bar(stage));   // the stage is free once these MMAs have read it
-          if (ks + 1 == p.k_steps) umma_commit(acc_full_bar(buf));
+          if (ks + 1 == ks1) umma_commit(acc_full_bar(buf));
         }
         __syncwarp();
         if (++stage == C::STAGES) { stage = 0; phase ^= 1u; }
@@ -353,12 +451,13 @@ gemm_tc5_kernel(const __grid_constant__ GemmParams p) {
   } else {
     // ------------------------------ epilogue ------------------------------------
     const uint32_t quad = warp & 3u;                  // TMEM lane quadrant this warp may read
-    const uint32_t ew = uint32_t(warp) - 2u, half = ew >> 2;   // two warps per quadrant split the columns
-    uint8_t* patch = smem_gen + C::STAGES * C::STAGE_BYTES + 256 + ew * 1024;
+    const uint32_t ew = uint32_t(warp) - 2u, part = ew >> 2;   // four warps per quadrant split the columns
+    uint8_t* patch = smem_gen + C::STAGES * C::STAGE_BYTES + 256 + ew * 512;
     uint32_t it = 0;
     bool ok = true;
     for (uint32_t tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x, ++it) {
-      const uint32_t mt = tile % m_tiles, nt = tile / m_tiles;
+      const uint32_t sp = tile % p.splits, rest = tile / p.splits;
+      const uint32_t mt = rest % m_tiles, nt = rest / m_tiles;
       const uint32_t buf = it & 1u;
       float alpha = p.alpha;
       if (p.tile_expert) {
@@ -370,36 +469,46 @@ gemm_tc5_kernel(const __grid_constant__ GemmParams p) {
       const uint32_t rows_valid = row0 < p.m ? min(32u, p.m - row0) : 0u;
       float scale = alpha;
       if (p.rowscale && row < p.m) scale = p.rowscale[row] * alpha;
+#ifdef MB_GEMM_PROFILE
+      const long long prof_e0 = clock64();
+#endif
       if (!mbar_wait(acc_full_bar(buf), (it >> 1) & 1u, abort_smem, tflag, 4)) { ok = false; break; }
+#ifdef MB_GEMM_PROFILE
+      const long long prof_e1 = clock64();
+#endif
       fence_after_sync();
       const uint32_t t_acc = tmem_base + ((quad * 32u) << 16) + (buf ? C::ACC1 : C::ACC0);
       constexpr int CHUNKS = BN / 32;
+      // split-K: slice sp of the K sum lands in plane sp of the f32 workspace (p.out, p.m rows per plane)
+      const uint32_t row0_store = row0 + sp * p.m;
       auto process = [&](int c, const uint32_t* r) {
-        epilogue_chunk(p, r, nt * BN + c * 32, row0, rows_valid, scale, patch, lane);
+        epilogue_chunk(p, r, nt * BN + c * 32, row0_store, rows_valid, scale, patch, lane);
       };
+      constexpr int PER = CHUNKS / (EPI_WARPS / 4);     // chunks per warp: 2 (BN 256) or 1 (BN 128)
       if (C::OVERLAP) {
-        // The 64 columns shared with the other accumulator come out first (one chunk per
-        // warp of the quadrant), before any store work, so that the next tile's MMAs are
-        // released at once; the other six chunks follow, three per warp.
-        const int ca = (buf == 0 ? CHUNKS - 2 : 0) + int(half);
-        const int rest0 = (buf == 0 ? 0 : 2) + 3 * int(half);
+        // The 64 columns shared with the other accumulator come out first (one chunk each for the
+        // first two warps of the quadrant), before any store work, so that the next tile's MMAs are
+        // released at once; the other six chunks follow: one more for those two warps, two each
+        // for the other two.
+        const int shared0 = buf == 0 ? CHUNKS - 2 : 0, rest0 = buf == 0 ? 0 : 2;
+        const int c0 = part < 2 ? shared0 + int(part) : rest0 + 2 * int(part) - 2;
+        const int c1 = part < 2 ? rest0 + int(part) : rest0 + 2 * int(part) - 1;
         uint32_t ra[32];
-        tmem_ld_x32(t_acc + ca * 32, ra);
+        { PROF_T0();
+        tmem_ld_x32(t_acc + c0 * 32, ra);
         tmem_ld_wait();
+        if (warp == 2) PROF_ADD(7); }
         fence_before_sync();
         mbar_arrive(ovl_free_bar);
-        process(ca, ra);
-#pragma unroll 1
-        for (int ci = 0; ci < 3; ++ci) {
-          uint32_t r[32];
-          tmem_ld_x32(t_acc + (rest0 + ci) * 32, r);
-          tmem_ld_wait();
-          process(rest0 + ci, r);
-        }
+        process(c0, ra);
+        uint32_t r[32];
+        tmem_ld_x32(t_acc + c1 * 32, r);
+        tmem_ld_wait();
+        process(c1, r);
       } else {
 #pragma unroll 1
-        for (int ci = 0; ci < CHUNKS / 2; ++ci) {
-          const int c = int(half) * (CHUNKS / 2) + ci;
+        for (int ci = 0; ci < PER; ++ci) {
+          const int c = int(part) * PER + ci;
           uint32_t r[32];
           tmem_ld_x32(t_acc + c * 32, r);
           tmem_ld_wait();
@@ -408,6 +517,13 @@ gemm_tc5_kernel(const __grid_constant__ GemmParams p) {
       }
       fence_before_sync();
       mbar_arrive(acc_empty_bar(buf));
+#ifdef MB_GEMM_PROFILE
+      if (warp == 2 && lane == 0) {
+        atomicAdd(&g_gemm_prof[blockIdx.x * 8 + 3], (unsigned long long)(prof_e1 - prof_e0));
+        atomicAdd(&g_gemm_prof[blockIdx.x * 8 + 4], (unsigned long long)(clock64() - prof_e1));
+        atomicAdd(&g_gemm_prof[blockIdx.x * 8 + 6], 1ull);
+      }
+#endif
     }
   }
 
@@ -418,6 +534,9 @@ gemm_tc5_kernel(const __grid_constant__ GemmParams p) {
     fence_after_sync();
     tmem_dealloc(tmem_base, C::TMEM_COLS);
   }
+#ifdef MB_GEMM_PROFILE
+  if (threadIdx.x == 0) atomicAdd(&g_gemm_prof[blockIdx.x * 8 + 5], (unsigned long long)(clock64() - prof_k0));
+#endif
 }
 
 
@@ -439,7 +558,7 @@ struct Cfg2 {
   static constexpr int SFB_BYTES = 4096;             // scales of all 256 columns
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES + SFA_BYTES + SFB_BYTES;   // 38 KB
   static constexpr int STAGES = 5;
-  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + 256 + 8 * 1024;
+  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + 256 + EPI_WARPS_ * 512;
   static constexpr int ACC0 = 0, ACC1 = 192, SFA_COL = 448, SFB_COL = 464, TMEM_COLS = 512;
 };
 
@@ -475,7 +594,7 @@ gemm_tc5_pair_kernel(const __grid_constant__ Gemm2Params pp) {
   if (threadIdx.x == 0) {
     for (int s = 0; s < C::STAGES; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
     for (int b = 0; b < 2; ++b) mbar_init(acc_full_bar(b), 1);
-    mbar_init(ovl_free_bar, 16);       // one arrival per epilogue warp of both CTAs
+    mbar_init(ovl_free_bar, 2 * EPI_WARPS);       // one arrival per epilogue warp of both CTAs
     mbar_init(drain_bar, 1);
     *abort_smem = 0;
     fence_barrier_init();
@@ -575,8 +694,8 @@ gemm_tc5_pair_kernel(const __grid_constant__ Gemm2Params pp) {
   } else {
     // ------------------------------ epilogue (both CTAs) --------------------------
     const uint32_t quad = warp & 3u;
-    const uint32_t ew = uint32_t(warp) - 2u, half = ew >> 2;
-    uint8_t* patch = smem_gen + C::STAGES * C::STAGE_BYTES + 256 + ew * 1024;
+    const uint32_t ew = uint32_t(warp) - 2u, part = ew >> 2;
+    uint8_t* patch = smem_gen + C::STAGES * C::STAGE_BYTES + 256 + ew * 512;
     const uint32_t ovl_remote = map_to_cta(ovl_free_bar, 0);
     uint32_t it = 0;
     bool ok = true;
@@ -592,22 +711,20 @@ gemm_tc5_pair_kernel(const __grid_constant__ Gemm2Params pp) {
       fence_after_sync();
       const uint32_t t_acc = tmem_base + ((quad * 32u) << 16) + (buf ? C::ACC1 : C::ACC0);
       constexpr int CHUNKS = C::BN / 32;
-      const int ca = (buf == 0 ? CHUNKS - 2 : 0) + int(half);
-      const int rest0 = (buf == 0 ? 0 : 2) + 3 * int(half);
+      const int shared0 = buf == 0 ? CHUNKS - 2 : 0, rest0 = buf == 0 ? 0 : 2;
+      const int c0 = part < 2 ? shared0 + int(part) : rest0 + 2 * int(part) - 2;
+      const int c1 = part < 2 ? rest0 + int(part) : rest0 + 2 * int(part) - 1;
       uint32_t ra[32];
-      tmem_ld_x32(t_acc + ca * 32, ra);
+      tmem_ld_x32(t_acc + c0 * 32, ra);
       tmem_ld_wait();
       fence_before_sync();
       __syncwarp();
-      if (lane == 0) mbar_arrive_cluster(ovl_remote);              // this warp has read its shared columns
-      epilogue_chunk(p, ra, nt * C::BN + ca * 32, row0, rows_valid, scale, patch, lane);
-#pragma unroll 1
-      for (int ci = 0; ci < 3; ++ci) {
-        uint32_t r[32];
-        tmem_ld_x32(t_acc + (rest0 + ci) * 32, r);
-        tmem_ld_wait();
-        epilogue_chunk(p, r, nt * C::BN + (rest0 + ci) * 32, row0, rows_valid, scale, patch, lane);
-      }
+      if (lane == 0) mbar_arrive_cluster(ovl_remote);              // this warp is past the shared columns
+      epilogue_chunk(p, ra, nt * C::BN + c0 * 32, row0, rows_valid, scale, patch, lane);
+      uint32_t r[32];
+      tmem_ld_x32(t_acc + c1 * 32, r);
+      tmem_ld_wait();
+      epilogue_chunk(p, r, nt * C::BN + c1 * 32, row0, rows_valid, scale, patch, lane);
     }
   }
 
@@ -619,6 +736,46 @@ gemm_tc5_pair_kernel(const __grid_constant__ Gemm2Params pp) {
     fence_after_sync();
     tmem_dealloc_pair(tmem_base, C::TMEM_COLS);
   }
+}
+
+// Sum of the split-K planes in plane order, times the epilogue scale, one cast.
+template <typename O>
+__global__ void __launch_bounds__(256)
+splitk_reduce_kernel(const float4* __restrict__ partial, uint32_t splits, size_t plane4, uint32_t n4,
+                     const float* __restrict__ rowscale, const float4* __restrict__ colscale, float alpha,
+                     O* __restrict__ out) {
+  size_t i = size_t(blockIdx.x) * 256 + threadIdx.x;
+  if (i >= plane4) return;
+  float4 acc = partial[i];
+  for (uint32_t s = 1; s < splits; ++s) {
+    const float4 v = partial[size_t(s) * plane4 + i];
+    acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+  }
+  const float scale = rowscale ? rowscale[i / n4] * alpha : alpha;
+  float4 c = make_float4(1.0f, 1.0f, 1.0f, 1.0f);
+  if (colscale) c = __ldg(colscale + i % n4);
+  const float4 r = colscale ? make_float4(acc.x * scale * c.x, acc.y * scale * c.y, acc.z * scale * c.z, acc.w * scale * c.w)
+                            : make_float4(acc.x * scale, acc.y * scale, acc.z * scale, acc.w * scale);
+  if (sizeof(O) == 4) {
+    reinterpret_cast<float4*>(out)[i] = r;
+  } else {
+    reinterpret_cast<uint2*>(out)[i] = make_uint2(pack_bf16x2(r.x, r.y), pack_bf16x2(r.z, r.w));
+  }
+}
+
+// How many K slices a product with few output tiles is cut into (1 = no split).
+uint32_t splitk_factor(int sm_count, size_t m, size_t n, size_t k) {
+  if (m > 128 || n % 4 != 0) return 1;
+  const uint32_t bn = n % 256 == 0 ? 256 : 128;
+  const uint32_t tiles = uint32_t((n + bn - 1) / bn);
+  const uint32_t k_steps = uint32_t((k + 255) / 256);
+  if (tiles * 2 > uint32_t(sm_count) || k_steps < 4) return 1;
+  uint32_t want = uint32_t(sm_count) / tiles;             // one wave: tiles x slices <= SMs
+  want = std::min<uint32_t>(want, k_steps);
+  want = std::min<uint32_t>(want, 32);
+  if (want < 2) return 1;
+  const uint32_t per = (k_steps + want - 1) / want;
+  return (k_steps + per - 1) / per;
 }
 
 // ---------------------------------------------------------------------------------
@@ -719,11 +876,39 @@ int launch_pair(mb_ctx* ctx, cudaStream_t stream, Gemm2Params& pp) {
   return MB_OK;
 }
 
+// What the plain product does not need: the fused exchange, the split-K workspace, per-column
+// scales of stacked projections, the quantized output of a SwiGLU epilogue.
+struct GemmExtra {
+  const mb_symm* symm = nullptr;
+  int step = 0;
+  void* workspace = nullptr;
+  size_t workspace_bytes = 0;
+  const float* colscale = nullptr;
+  void* out_sf = nullptr;
+};
+
 int gemm_w4a4_common(mb_ctx* ctx, cudaStream_t stream, const uint8_t* a_codes, const uint8_t* a_sf,
                      const uint8_t* b_codes, const uint8_t* b_sf, const float* rowscale, float alpha,
                      const float* alpha_vec, const int32_t* tile_expert, const int32_t* n_tiles_dev, size_t m,
-                     size_t experts, size_t n, size_t k, void* out, int out_dtype, int epilogue,
-                     const mb_symm* symm = nullptr, int step = 0) {
+                     size_t experts, size_t n, size_t k, void* out, int out_dtype, int epilogue_word,
+                     const GemmExtra& ex = GemmExtra()) {
+  const mb_symm* symm = ex.symm;
+  const int step = ex.step;
+  void* workspace = ex.workspace;
+  const size_t workspace_bytes = ex.workspace_bytes;
+  // epilogue word: kind in the low byte, output quantization in the flag bits
+  const int kind = epilogue_word & 0xFF;
+  const int quant = (epilogue_word & MB_EPI_QUANT_RECIP) ? 1 : (epilogue_word & MB_EPI_QUANT_SCALED) ? 2 : 0;
+  const bool swiglu = kind == MB_EPI_SWIGLU_INTERLEAVED || kind == MB_EPI_SWIGLU_ROUNDED;
+  const int epilogue = swiglu ? MB_EPI_SWIGLU_INTERLEAVED : kind;
+  MB_REQUIRE(ctx, (epilogue_word & ~(0xFF | MB_EPI_QUANT_RECIP | MB_EPI_QUANT_SCALED)) == 0 &&
+                      (epilogue_word & (MB_EPI_QUANT_RECIP | MB_EPI_QUANT_SCALED)) !=
+                          (MB_EPI_QUANT_RECIP | MB_EPI_QUANT_SCALED),
+             "gemm_w4a4: unknown epilogue word 0x%x", epilogue_word);
+  MB_REQUIRE(ctx, !quant || (swiglu && ex.out_sf && n % 32 == 0 && mb_aligned(ex.out_sf, 16)),
+             "gemm_w4a4: a quantized output needs a SwiGLU epilogue, n a multiple of 32 and a scale plane");
+  MB_REQUIRE(ctx, !ex.colscale || (n % 32 == 0 && mb_aligned(ex.colscale, 16)),
+             "gemm_w4a4: column scales need n a multiple of 32 and 16-byte alignment");
   MB_REQUIRE(ctx, ctx && a_codes && a_sf && b_codes && b_sf && out, "gemm_w4a4: null argument");
   MB_REQUIRE(ctx, m > 0 && n > 0 && k > 0, "gemm_w4a4: empty extent");
   MB_REQUIRE(ctx, k % 64 == 0, "W4A4 needs k a multiple of 64, got %zu", k);
@@ -733,7 +918,7 @@ int gemm_w4a4_common(mb_ctx* ctx, cudaStream_t stream, const uint8_t* a_codes, c
   MB_REQUIRE(ctx, out_dtype == MB_DT_BF16 || out_dtype == MB_DT_F32, "gemm_w4a4: output is bf16 or f32");
   MB_REQUIRE(ctx, epilogue == MB_EPI_PLAIN || epilogue == MB_EPI_SCATTER ||
                       (epilogue == MB_EPI_SWIGLU_INTERLEAVED && out_dtype == MB_DT_BF16),
-             "gemm_w4a4: the SwiGLU epilogue writes bf16");
+             "gemm_w4a4: the SwiGLU epilogue writes bf16 (or NVFP4 planes)");
   MB_REQUIRE(ctx, mb_aligned(a_codes, 16) && mb_aligned(b_codes, 16) && mb_aligned(a_sf, 16) && mb_aligned(b_sf, 16) &&
                       mb_aligned(out, 16),
              "gemm_w4a4: operands and output need 16-byte alignment");
@@ -755,6 +940,11 @@ int gemm_w4a4_common(mb_ctx* ctx, cudaStream_t stream, const uint8_t* a_codes, c
   p.sfb_expert_stride = mb_sf_plane_bytes(n, k);
   p.ldo = uint32_t(epilogue == MB_EPI_SWIGLU_INTERLEAVED ? n / 2 : n);
   p.out_dtype = out_dtype; p.epilogue = epilogue;
+  p.colscale = ex.colscale; p.silu_rounded = kind == MB_EPI_SWIGLU_ROUNDED; p.quant = quant;
+  p.out_sf = static_cast<uint8_t*>(ex.out_sf); p.out_sf_kchunks = uint32_t(mb_sf_kchunks(n / 2));
+  // Scale bytes of the K padding (up to the next 256 values) are read by the product that consumes the
+  // plane and must decode to a finite value; the epilogue writes live blocks only.
+  if (quant && (n / 2) % 256 != 0) MB_CUDA_OK(ctx, cudaMemsetAsync(ex.out_sf, 0, mb_sf_plane_bytes(m, n / 2), stream));
   if (epilogue == MB_EPI_SCATTER) {
     p.scatter_world = uint32_t(symm->world); p.scatter_rank = uint32_t(symm->rank);
     p.scatter_nw = uint32_t(n / symm->world); p.scatter_tmax = uint32_t(symm->t_max);
@@ -762,6 +952,35 @@ int gemm_w4a4_common(mb_ctx* ctx, cudaStream_t stream, const uint8_t* a_codes, c
     for (int r = 0; r < symm->world; ++r)
       p.scatter_base[r] = reinterpret_cast<float*>(static_cast<uint8_t*>(symm->peer[r]) + mb_symm_flags_bytes()) +
                           size_t(step & 1) * half;
+  }
+  p.splits = 1; p.ks_per_split = p.k_steps;
+  if (workspace && epilogue == MB_EPI_PLAIN && !tile_expert) {
+    const uint32_t sk = splitk_factor(ctx->sm_count, m, n, k);
+    if (sk > 1 && workspace_bytes >= size_t(sk) * m * n * sizeof(float)) {
+      // K slices into f32 planes of the workspace, then one ordered sum with the epilogue scale
+      p.ks_per_split = (p.k_steps + sk - 1) / sk;
+      p.splits = (p.k_steps + p.ks_per_split - 1) / p.ks_per_split;
+      GemmParams ps = p;
+      ps.out = workspace; ps.out_dtype = MB_DT_F32; ps.ldo = uint32_t(n); ps.alpha = 1.0f; ps.rowscale = nullptr;
+      ps.colscale = nullptr;
+      rc = wide ? launch<KIND_NVF4, 256>(ctx, stream, ps, ps.m_tiles * ps.n_tiles * ps.splits)
+                : launch<KIND_NVF4, 128>(ctx, stream, ps, ps.m_tiles * ps.n_tiles * ps.splits);
+      if (rc) return rc;
+      const size_t plane4 = m * n / 4;
+      const unsigned grid = unsigned((plane4 + 255) / 256);
+      if (out_dtype == MB_DT_F32)
+        splitk_reduce_kernel<float><<<grid, 256, 0, stream>>>(static_cast<const float4*>(workspace), p.splits, plane4,
+                                                              uint32_t(n / 4), rowscale,
+                                                              reinterpret_cast<const float4*>(ex.colscale), alpha,
+                                                              static_cast<float*>(out));
+      else
+        splitk_reduce_kernel<__nv_bfloat16><<<grid, 256, 0, stream>>>(static_cast<const float4*>(workspace), p.splits,
+                                                                      plane4, uint32_t(n / 4), rowscale,
+                                                                      reinterpret_cast<const float4*>(ex.colscale), alpha,
+                                                                      static_cast<__nv_bfloat16*>(out));
+      MB_LAUNCH_OK(ctx);
+      return MB_OK;
+    }
   }
   uint32_t tiles = p.m_tiles * p.n_tiles;
   // Dense products with at least one full pair of row tiles go to the CTA-pair kernel
@@ -785,6 +1004,15 @@ int gemm_w4a4_common(mb_ctx* ctx, cudaStream_t stream, const uint8_t* a_codes, c
 
 }  // namespace
 
+#ifdef MB_GEMM_PROFILE
+MB_API int mb_debug_gemm_dbg(int v) { cudaMemcpyToSymbol(g_gemm_dbg, &v, sizeof v); return 0; }
+MB_API int mb_debug_gemm_profile(unsigned long long* host_out, int reset) {
+  if (host_out) cudaMemcpyFromSymbol(host_out, g_gemm_prof, sizeof g_gemm_prof);
+  if (reset) { static unsigned long long z[160 * 8]; cudaMemcpyToSymbol(g_gemm_prof, z, sizeof z); }
+  return 0;
+}
+#endif
+
 MB_API int mb_nvfp4_gemm_w4a4(mb_ctx* ctx, mb_stream stream, const uint8_t* a_codes, const uint8_t* a_sf_tiled,
                               const uint8_t* b_codes, const uint8_t* b_sf_tiled, const float* rowscale, float alpha,
                               size_t m, size_t n, size_t k, void* out, int out_dtype, int epilogue) {
@@ -792,6 +1020,36 @@ MB_API int mb_nvfp4_gemm_w4a4(mb_ctx* ctx, mb_stream stream, const uint8_t* a_co
              "W4A4 calibrated globals/product must be finite positive");
   return gemm_w4a4_common(ctx, static_cast<cudaStream_t>(stream), a_codes, a_sf_tiled, b_codes, b_sf_tiled, rowscale,
                           alpha, nullptr, nullptr, nullptr, m, 1, n, k, out, out_dtype, epilogue);
+}
+
+MB_API size_t mb_nvfp4_gemm_splitk_workspace(size_t m, size_t n, size_t k) {
+  const uint32_t sk = splitk_factor(148, m, n, k);
+  return sk > 1 ? size_t(sk) * m * n * sizeof(float) : 0;
+}
+
+MB_API int mb_nvfp4_gemm_w4a4_splitk(mb_ctx* ctx, mb_stream stream, const uint8_t* a_codes, const uint8_t* a_sf_tiled,
+                                     const uint8_t* b_codes, const uint8_t* b_sf_tiled, const float* rowscale,
+                                     float alpha, size_t m, size_t n, size_t k, void* out, int out_dtype,
+                                     void* workspace, size_t workspace_bytes) {
+  MB_REQUIRE(ctx, alpha == alpha && alpha > 0.0f && alpha <= 3.4e38f,
+             "W4A4 calibrated globals/product must be finite positive");
+  MB_REQUIRE(ctx, workspace == nullptr || mb_aligned(workspace, 16), "gemm_w4a4_splitk: workspace needs 16-byte alignment");
+  GemmExtra ex;
+  ex.workspace = workspace; ex.workspace_bytes = workspace_bytes;
+  return gemm_w4a4_common(ctx, static_cast<cudaStream_t>(stream), a_codes, a_sf_tiled, b_codes, b_sf_tiled, rowscale,
+                          alpha, nullptr, nullptr, nullptr, m, 1, n, k, out, out_dtype, MB_EPI_PLAIN, ex);
+}
+
+MB_API int mb_nvfp4_gemm_w4a4_stacked(mb_ctx* ctx, mb_stream stream, const uint8_t* a_codes, const uint8_t* a_sf_tiled,
+                                      const uint8_t* b_codes, const uint8_t* b_sf_tiled, const float* colscale,
+                                      size_t m, size_t n, size_t k, void* out, int out_dtype, int epilogue, void* out_sf,
+                                      void* workspace, size_t workspace_bytes) {
+  MB_REQUIRE(ctx, colscale != nullptr, "gemm_w4a4_stacked: the column scales carry the weights' globals");
+  MB_REQUIRE(ctx, workspace == nullptr || mb_aligned(workspace, 16), "gemm_w4a4_stacked: workspace needs 16-byte alignment");
+  GemmExtra ex;
+  ex.colscale = colscale; ex.out_sf = out_sf; ex.workspace = workspace; ex.workspace_bytes = workspace_bytes;
+  return gemm_w4a4_common(ctx, static_cast<cudaStream_t>(stream), a_codes, a_sf_tiled, b_codes, b_sf_tiled, nullptr,
+                          1.0f, nullptr, nullptr, nullptr, m, 1, n, k, out, out_dtype, epilogue, ex);
 }
 
 MB_API int mb_nvfp4_gemm_w4a4_scatter(mb_ctx* ctx, mb_stream stream, const uint8_t* a_codes,
@@ -803,19 +1061,23 @@ MB_API int mb_nvfp4_gemm_w4a4_scatter(mb_ctx* ctx, mb_stream stream, const uint8
              m, n, sy->t_max, sy->n);
   MB_REQUIRE(ctx, (n / sy->world) % 32 == 0 && n % sy->world == 0, "gemm_w4a4_scatter: n / world must be a multiple of 32");
   MB_REQUIRE(ctx, alpha == alpha && alpha > 0.0f && alpha <= 3.4e38f, "W4A4 calibrated globals/product must be finite positive");
+  GemmExtra ex;
+  ex.symm = sy; ex.step = step;
   return gemm_w4a4_common(ctx, static_cast<cudaStream_t>(stream), a_codes, a_sf_tiled, b_codes, b_sf_tiled, nullptr,
-                          alpha, nullptr, nullptr, nullptr, m, 1, n, k, sy->local, MB_DT_F32, MB_EPI_SCATTER, sy, step);
+                          alpha, nullptr, nullptr, nullptr, m, 1, n, k, sy->local, MB_DT_F32, MB_EPI_SCATTER, ex);
 }
 
 MB_API int mb_nvfp4_gemm_w4a4_grouped(mb_ctx* ctx, mb_stream stream, const uint8_t* a_codes,
                                       const uint8_t* a_sf_tiled, const uint8_t* bank_codes,
                                       const uint8_t* bank_sf_tiled, const float* alpha, const int32_t* tile_expert,
                                       const int32_t* n_tiles_dev, size_t m_cap, size_t experts, size_t n, size_t k,
-                                      void* out, int out_dtype, int epilogue) {
+                                      void* out, int out_dtype, int epilogue, void* out_sf) {
   MB_REQUIRE(ctx, alpha && tile_expert && n_tiles_dev && experts > 0, "grouped gemm: null argument");
+  GemmExtra ex;
+  ex.out_sf = out_sf;
   return gemm_w4a4_common(ctx, static_cast<cudaStream_t>(stream), a_codes, a_sf_tiled, bank_codes, bank_sf_tiled,
                           nullptr, 1.0f, alpha, tile_expert, n_tiles_dev, m_cap, experts, n, k, out, out_dtype,
-                          epilogue);
+                          epilogue, ex);
 }
 
 MB_API int mb_bf16_gemm(mb_ctx* ctx, mb_stream stream_, const void* a, const void* b, float alpha, size_t m, size_t n,
@@ -838,6 +1100,7 @@ MB_API int mb_bf16_gemm(mb_ctx* ctx, mb_stream stream_, const void* a, const voi
   p.m_tiles = uint32_t((m + 127) / 128);
   p.n_tiles = uint32_t((n + (wide ? 255 : 127)) / (wide ? 256 : 128));
   p.ldo = uint32_t(n); p.out_dtype = out_dtype; p.epilogue = MB_EPI_PLAIN;
+  p.splits = 1; p.ks_per_split = p.k_steps;
   uint32_t tiles = p.m_tiles * p.n_tiles;
   return wide ? launch<KIND_BF16, 256>(ctx, stream, p, tiles) : launch<KIND_BF16, 128>(ctx, stream, p, tiles);
 }

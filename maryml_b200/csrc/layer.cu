@@ -2,6 +2,7 @@
 // add, SwiGLU, RoPE. HBM-bound elementwise kernels with 128-bit accesses; the norm
 // keeps a row in registers between the sum-of-squares pass and the scaling pass.
 #include "common.cuh"
+#include "quant_block.cuh"
 
 namespace {
 
@@ -114,6 +115,127 @@ rope_kernel(const __nv_bfloat16* __restrict__ x, __nv_bfloat16* __restrict__ out
   out[row * d + half + f] = __float2bfloat16_rn(bf16r(high * c) + bf16r(low * s));
 }
 
+// Residual add, RMSNorm and the W4A4 activation quantizer in one pass over a row:
+//   r = bf16(resid + bf16(partial))          (only with a partial; r is stored)
+//   y = bf16(bf16(r * inv) * gain)           (the rmsnorm kernel's arithmetic and summation order)
+//   codes, scale bytes = divide recipe with a unit global on y.
+// Same chunk-to-thread assignment as rmsnorm_kernel, so the bytes equal those of the three
+// separate kernels. A 16-value block is two neighbouring threads; four blocks (eight lanes)
+// merge their scale bytes into one store of the tiled plane. width % 64 == 0.
+template <int VEC>
+__global__ void __launch_bounds__(256)
+residual_norm_quantize_kernel(const uint4* __restrict__ resid, const float4* __restrict__ partial,
+                              const uint4* __restrict__ gain, uint4* __restrict__ resid_out, uint32_t* __restrict__ codes,
+                              uint8_t* __restrict__ scales, uint32_t width, float eps, uint32_t kchunks) {
+  const uint32_t row = blockIdx.x, chunks = width / 8;
+  const uint4* xr = resid + size_t(row) * chunks;
+  float v[VEC][8];
+  float sum = 0.0f;
+#pragma unroll
+  for (int i = 0; i < VEC; ++i) {
+    const uint32_t c = threadIdx.x + i * 256;
+    if (c < chunks) {
+      unpack8(__ldg(xr + c), v[i]);
+      if (partial) {
+        const float4* pr = partial + (size_t(row) * chunks + c) * 2;
+        const float4 p0 = __ldg(pr), p1 = __ldg(pr + 1);
+        const float y[8] = {p0.x, p0.y, p0.z, p0.w, p1.x, p1.y, p1.z, p1.w};
+#pragma unroll
+        for (int j = 0; j < 8; ++j) v[i][j] = bf16r(v[i][j] + bf16r(y[j]));
+        resid_out[size_t(row) * chunks + c] = pack8(v[i]);
+      }
+#pragma unroll
+      for (int j = 0; j < 8; ++j) sum += v[i][j] * v[i][j];
+    }
+  }
+  __shared__ float red[8];
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xFFFFFFFFu, sum, o);
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = sum;
+  __syncthreads();
+  float total = 0.0f;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) total += red[i];
+  const float inv = 1.0f / sqrtf(total / float(width) + eps);
+#pragma unroll
+  for (int i = 0; i < VEC; ++i) {
+    const uint32_t c = threadIdx.x + i * 256;
+    const bool live = c < chunks;          // uniform over each aligned group of eight lanes
+    float o[8];
+    float amax = 0.0f;
+    if (live) {
+      float g[8];
+      unpack8(__ldg(gain + c), g);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        o[j] = bf16r(bf16r(v[i][j] * inv) * g[j]);
+        amax = fmaxf(amax, fabsf(o[j]));
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) o[j] = 0.0f;
+    }
+    const float bamax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, 1));
+    uint32_t sbyte;
+    const float d = quant_divisor_scaled(bamax, 1.0f, sbyte);
+    const uint32_t mine = quant_codes8_div(o, d, bamax);
+    // scale bytes of the four blocks of this group of eight lanes -> lane 0 of the group
+    uint32_t w = sbyte;
+    w |= __shfl_down_sync(0xFFFFFFFFu, sbyte, 2) << 8;
+    w |= __shfl_down_sync(0xFFFFFFFFu, sbyte, 4) << 16;
+    w |= __shfl_down_sync(0xFFFFFFFFu, sbyte, 6) << 24;
+    if (live) {
+      codes[size_t(row) * chunks + c] = mine;
+      if ((threadIdx.x & 7) == 0)
+        *reinterpret_cast<uint32_t*>(scales + mb_sf_offset(row, c >> 1, kchunks)) = w;
+    }
+  }
+}
+
+// Rotation of the q and k heads of a stacked [tokens, (hq + 2 hkv) d] projection and the
+// cache append in one pass: q goes out contiguous, rotated k and plain v land in the caches
+// [batch, capacity, hkv, d] at position past + i of their sequence. The per-element
+// arithmetic is rope_kernel's. One thread per eight (f, f + d/2) pairs.
+__global__ void __launch_bounds__(256)
+rope_append_kernel(const uint4* __restrict__ qkv, uint4* __restrict__ q_out, uint4* __restrict__ k_cache,
+                   uint4* __restrict__ v_cache, uint32_t batch, uint32_t t, uint32_t hq, uint32_t hkv, uint32_t d,
+                   uint32_t past, uint32_t capacity, const float* __restrict__ inv_freq) {
+  const uint32_t groups = d / 16;                      // eight-pair groups per head
+  const uint32_t heads = hq + 2 * hkv;
+  const size_t total = size_t(batch) * t * heads * groups;
+  const size_t idx = size_t(blockIdx.x) * 256 + threadIdx.x;
+  if (idx >= total) return;
+  const uint32_t g = uint32_t(idx % groups);
+  const uint32_t head = uint32_t((idx / groups) % heads);
+  const size_t tok = idx / (size_t(groups) * heads);   // b * t + i
+  const uint32_t i = uint32_t(tok % t), b = uint32_t(tok / t);
+  const uint32_t d8 = d / 8, half8 = d8 / 2;
+  const uint4* src = qkv + (tok * heads + head) * d8;
+  const uint4 lo_q = __ldg(src + g), hi_q = __ldg(src + half8 + g);
+  uint4* dst;
+  if (head < hq) dst = q_out + (tok * hq + head) * d8;
+  else if (head < hq + hkv) dst = k_cache + ((size_t(b) * capacity + past + i) * hkv + (head - hq)) * d8;
+  else dst = v_cache + ((size_t(b) * capacity + past + i) * hkv + (head - hq - hkv)) * d8;
+  if (head >= hq + hkv) {
+    dst[g] = lo_q;
+    dst[half8 + g] = hi_q;
+    return;
+  }
+  float low[8], high[8], ol[8], oh[8];
+  unpack8(lo_q, low);
+  unpack8(hi_q, high);
+  const float position = float(past + i);
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    const float angle = position * inv_freq[g * 8 + j];
+    const float c = bf16r(cosf(angle)), s = bf16r(sinf(angle));
+    ol[j] = bf16r(low[j] * c) - bf16r(high[j] * s);
+    oh[j] = bf16r(high[j] * c) + bf16r(low[j] * s);
+  }
+  dst[g] = pack8(ol);
+  dst[half8 + g] = pack8(oh);
+}
+
 }  // namespace
 
 MB_API int mb_rmsnorm(mb_ctx* ctx, mb_stream stream_, const void* x, const void* gain, size_t rows, size_t width,
@@ -179,6 +301,57 @@ MB_API int mb_rope(mb_ctx* ctx, mb_stream stream_, const void* x, size_t tokens,
   rope_kernel<<<unsigned((total + 255) / 256), 256, 0, stream>>>(static_cast<const __nv_bfloat16*>(x),
                                                                  static_cast<__nv_bfloat16*>(out), rows,
                                                                  uint32_t(heads), uint32_t(d), uint32_t(past), inv_freq);
+  MB_LAUNCH_OK(ctx);
+  return MB_OK;
+}
+
+MB_API int mb_residual_norm_quantize(mb_ctx* ctx, mb_stream stream_, const void* resid, const float* partial,
+                                     const void* gain, size_t rows, size_t width, float eps, void* resid_out,
+                                     uint8_t* codes, uint8_t* sf_tiled) {
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  MB_REQUIRE(ctx, ctx && resid && gain && codes && sf_tiled, "residual_norm_quantize: null argument");
+  MB_REQUIRE(ctx, !partial || resid_out, "residual_norm_quantize: a partial sum needs somewhere to put the new residual");
+  MB_REQUIRE(ctx, rows > 0 && width > 0 && width % 64 == 0 && width <= 256 * 8 * 4,
+             "residual_norm_quantize: width must be a multiple of 64 up to 8192, got %zu", width);
+  MB_REQUIRE(ctx, mb_aligned(resid, 16) && mb_aligned(gain, 16) && mb_aligned(partial, 16) && mb_aligned(resid_out, 16) &&
+                      mb_aligned(codes, 4) && mb_aligned(sf_tiled, 4),
+             "residual_norm_quantize: alignment");
+  const uint4* xv = static_cast<const uint4*>(resid);
+  const float4* pv = reinterpret_cast<const float4*>(partial);
+  const uint4* gv = static_cast<const uint4*>(gain);
+  uint4* rv = static_cast<uint4*>(resid_out);
+  uint32_t* cv = reinterpret_cast<uint32_t*>(codes);
+  const uint32_t kc = uint32_t(mb_sf_kchunks(width));
+  const unsigned grid = unsigned(rows);
+  // scale bytes of the K padding must decode to a finite value for the product that reads the plane
+  if (width % 256 != 0) MB_CUDA_OK(ctx, cudaMemsetAsync(sf_tiled, 0, mb_sf_plane_bytes(rows, width), stream));
+  if (width <= 2048)
+    residual_norm_quantize_kernel<1><<<grid, 256, 0, stream>>>(xv, pv, gv, rv, cv, sf_tiled, uint32_t(width), eps, kc);
+  else if (width <= 4096)
+    residual_norm_quantize_kernel<2><<<grid, 256, 0, stream>>>(xv, pv, gv, rv, cv, sf_tiled, uint32_t(width), eps, kc);
+  else
+    residual_norm_quantize_kernel<4><<<grid, 256, 0, stream>>>(xv, pv, gv, rv, cv, sf_tiled, uint32_t(width), eps, kc);
+  MB_LAUNCH_OK(ctx);
+  return MB_OK;
+}
+
+MB_API int mb_rope_append(mb_ctx* ctx, mb_stream stream_, const void* qkv, size_t batch, size_t t, size_t hq,
+                          size_t hkv, size_t d, size_t past, const float* inv_freq, void* q_out, void* k_cache,
+                          void* v_cache, size_t capacity) {
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  MB_REQUIRE(ctx, ctx && qkv && inv_freq && q_out && k_cache && v_cache, "rope_append: null argument");
+  MB_REQUIRE(ctx, batch > 0 && t > 0 && hq > 0 && hkv > 0 && d > 0 && d % 16 == 0, "rope_append: d must be a multiple of 16");
+  MB_REQUIRE(ctx, past + t <= capacity, "rope_append: positions [%zu, %zu) exceed the cache capacity %zu", past, past + t,
+             capacity);
+  MB_REQUIRE(ctx, mb_aligned(qkv, 16) && mb_aligned(q_out, 16) && mb_aligned(k_cache, 16) && mb_aligned(v_cache, 16),
+             "rope_append: 16-byte alignment");
+  const size_t total = batch * t * (hq + 2 * hkv) * (d / 16);
+  MB_REQUIRE(ctx, total < (1ull << 40) && batch * capacity < (1ull << 32) && past + t < (1ull << 31),
+             "rope_append: extent too large");
+  rope_append_kernel<<<unsigned((total + 255) / 256), 256, 0, stream>>>(
+      static_cast<const uint4*>(qkv), static_cast<uint4*>(q_out), static_cast<uint4*>(k_cache),
+      static_cast<uint4*>(v_cache), uint32_t(batch), uint32_t(t), uint32_t(hq), uint32_t(hkv), uint32_t(d), uint32_t(past),
+      uint32_t(capacity), inv_freq);
   MB_LAUNCH_OK(ctx);
   return MB_OK;
 }

@@ -200,8 +200,8 @@ class DecoderLayer:
     (codes [n, k/2], scales [n, k/16], scale2) quantised BEFORE the cut, so every rank
     holds bytes of the same stored tensor (the reference cuts stored planes)."""
 
-    def __init__(self, cfg, full, input_gain, post_gain, tp=None, group=None, device=None, fused=None):
-        self.cfg, self.tp, self.group, self.fused = cfg, tp or Tp(), group, fused
+    def __init__(self, cfg, full, input_gain, post_gain, tp=None, group=None, device=None, fused=None, fuse=True):
+        self.cfg, self.tp, self.group, self.fused, self.fuse = cfg, tp or Tp(), group, fused, fuse
         dev = device if device is not None else torch.device("cuda", torch.cuda.current_device())
         D = cfg.head_dim
         qh, kvh = self.tp.q_heads(cfg.heads), self.tp.kv_heads(cfg.kv_heads)
@@ -227,8 +227,17 @@ class DecoderLayer:
         self.wdown = row_parallel("down", inter)
         self.input_gain, self.post_gain = input_gain.to(dev), post_gain.to(dev)
         self.inv_freq = torch.from_numpy(inv_freq(D, cfg.theta)).to(dev)
-        for w in (self.wq, self.wk, self.wv, self.wo, self.wgate, self.wup, self.wdown):
+        for w in (self.wo, self.wdown):
             w.sf_tiled()
+        if fuse:
+            # Projections of one input run as one product: q|k|v stacked, gate and up interleaved
+            # row by row for the SwiGLU epilogue. The separate planes are not kept.
+            self.wqkv = nv.Stacked([self.wq, self.wk, self.wv])
+            self.wgu = nv.Stacked([self.wgate, self.wup], interleave=True)
+            self.wq = self.wk = self.wv = self.wgate = self.wup = None
+        else:
+            for w in (self.wq, self.wk, self.wv, self.wgate, self.wup):
+                w.sf_tiled()
 
     @staticmethod
     def _quantize(x):
@@ -259,9 +268,66 @@ class DecoderLayer:
             self.group.all_reduce_f32(partial)
         return add_f32(resid, partial)
 
+    def _norm_quantize(self, resid, partial, gain):
+        """(new residual, activation planes of rmsnorm(new residual)) in one pass; the new residual
+        is resid itself without a partial sum."""
+        rows, width = resid.shape
+        dev = resid.device
+        codes = torch.empty((rows, width // 2), dtype=torch.uint8, device=dev)
+        sf = torch.empty(nv.sf_bytes(rows, width), dtype=torch.uint8, device=dev)
+        out = torch.empty_like(resid) if partial is not None else resid
+        ctx = context(dev.index)
+        ctx.check(lib.mb_residual_norm_quantize(ctx.handle, _stream(), _p(resid), _p(partial), _p(gain), rows, width,
+                                                float(self.cfg.eps), _p(out) if partial is not None else None,
+                                                _p(codes), _p(sf)))
+        return out, (codes, sf, rows)
+
+    def _partial(self, x, w):
+        """This rank's f32 share of a row-parallel projection, all-reduced when the layer is split."""
+        partial = self._linear(x, w, out_dtype=torch.float32)
+        if self.group is not None and self.tp.is_split():
+            self.group.all_reduce_f32(partial)
+        return partial
+
+    def _forward_fused(self, x, batch, past, k_cache, v_cache):
+        """The same layer in fewer passes: norm + quantize in one kernel, q|k|v as one product,
+        rotation + cache append in one kernel, gate/up + SwiGLU + quantize in one product, the
+        residual add folded into the next norm. Every value is computed by the arithmetic of the
+        separate kernels."""
+        cfg = self.cfg
+        D = cfg.head_dim
+        t = x.shape[0] // batch
+        dev = x.device
+        ctx = context(dev.index)
+        _, xq = self._norm_quantize(x, None, self.input_gain)
+        qkv = nv.gemm_w4a4_stacked(xq[0], xq[1], self.wqkv, xq[2])
+        q = torch.empty((batch, t, self.local_heads, D), dtype=torch.bfloat16, device=dev)
+        assert k_cache.is_contiguous() and v_cache.is_contiguous()
+        ctx.check(lib.mb_rope_append(ctx.handle, _stream(), _p(qkv), batch, t, self.local_heads, self.local_kv_heads, D,
+                                     past, _p(self.inv_freq), _p(q), _p(k_cache), _p(v_cache), k_cache.shape[1]))
+        keys = past + t
+        a = flash_attention(q, k_cache[:, :keys].contiguous() if keys != k_cache.shape[1] else k_cache,
+                            v_cache[:, :keys].contiguous() if keys != v_cache.shape[1] else v_cache,
+                            q0=past, scale=1.0 / math.sqrt(D), causal=True).view(batch * t, self.local_heads * D)
+        if self.fused is not None and batch * t <= self.fused.t_max:
+            residual = self._reduced_residual(x, a, self.wo)
+            _, nq_ = self._norm_quantize(residual, None, self.post_gain)
+        else:
+            residual, nq_ = self._norm_quantize(x, self._partial(a, self.wo), self.post_gain)
+        act = nv.gemm_w4a4_stacked(nq_[0], nq_[1], self.wgu, nq_[2],
+                                   epilogue=_lib.EPI_SWIGLU_ROUNDED | _lib.EPI_QUANT_SCALED)
+        if self.fused is not None and batch * t <= self.fused.t_max:
+            return self.fused.gemm_reduce_residual(act[0], act[1], self.wdown, residual, batch * t)
+        partial = self._project((act[0], act[1], batch * t), self.wdown, out_dtype=torch.float32)
+        if self.group is not None and self.tp.is_split():
+            self.group.all_reduce_f32(partial)
+        return add_f32(residual, partial)
+
     def forward(self, x, batch, past, k_cache, v_cache):
         """x [batch * t, hidden] bf16 (t new tokens per sequence, sequence-major). Caches
         [batch, capacity, local_kv_heads, D]; the new keys/values land at [past, past + t)."""
+        if self.fuse:
+            return self._forward_fused(x, batch, past, k_cache, v_cache)
         cfg = self.cfg
         D = cfg.head_dim
         t = x.shape[0] // batch

@@ -96,24 +96,37 @@ class ExpertBank:
 
 
 def grouped_gemm(a_codes, a_sf, bank, plan, out_dtype=torch.bfloat16, epilogue=_lib.EPI_PLAIN):
-    """fp4_linear_grouped(_bf16)_launch (src/models/inkling/moegroup.rs:612-751)."""
+    """fp4_linear_grouped(_bf16)_launch (src/models/inkling/moegroup.rs:612-751). With an
+    EPI_QUANT_* flag on a SwiGLU epilogue the result comes back as (codes, tiled scale plane)."""
     ctx = context(a_codes.device.index)
-    cols = bank.n // 2 if epilogue == _lib.EPI_SWIGLU_INTERLEAVED else bank.n
-    out = torch.empty((plan.m_cap, cols), dtype=out_dtype, device=a_codes.device)
+    dev = a_codes.device
+    swiglu = (epilogue & 0xFF) in (_lib.EPI_SWIGLU_INTERLEAVED, _lib.EPI_SWIGLU_ROUNDED)
+    quant = epilogue & (_lib.EPI_QUANT_RECIP | _lib.EPI_QUANT_SCALED)
+    out_sf = None
+    if quant:
+        out = torch.empty((plan.m_cap, bank.n // 4), dtype=torch.uint8, device=dev)
+        out_sf = torch.empty(nv.sf_bytes(plan.m_cap, bank.n // 2), dtype=torch.uint8, device=dev)
+    else:
+        out = torch.empty((plan.m_cap, bank.n // 2 if swiglu else bank.n), dtype=out_dtype, device=dev)
     ctx.check(lib.mb_nvfp4_gemm_w4a4_grouped(ctx.handle, _stream(), _p(a_codes), _p(a_sf), _p(bank.codes),
                                              _p(bank.sf_tiled), _p(bank.scale2), _p(plan.tile_expert),
                                              _p(plan.n_tiles), plan.m_cap, bank.experts, bank.n, bank.k, _p(out),
-                                             _lib.DT_BF16 if out_dtype == torch.bfloat16 else _lib.DT_F32, epilogue))
-    return out
+                                             _lib.DT_BF16 if out.dtype != torch.float32 else _lib.DT_F32, epilogue,
+                                             _p(out_sf)))
+    return (out, out_sf) if quant else out
 
 
-def moe_experts(x, idx, weight, w13, w2, fuse_swiglu=True):
+def moe_experts(x, idx, weight, w13, w2, fuse_swiglu=True, fuse_quant=True):
     """grouped_experts_core on the narrow (bf16) lane. x [tokens, h] bf16; w13 bank
     [E, 2*inter, h] with interleaved gate/up rows; w2 bank [E, h, inter]. Returns [tokens, h] f32."""
     tokens, h = x.shape
     inter = w2.k
     plan = RowPlan(idx, weight, w13.experts)
     a_codes, a_sf, _ = nv.quantize_act(x, _lib.QUANT_RECIP, tiled=True, gather=plan.row_tok)
+    if fuse_swiglu and fuse_quant:
+        # SwiGLU and the second projection's activation quantizer both in the first product's epilogue
+        c2, sf2 = grouped_gemm(a_codes, a_sf, w13, plan, epilogue=_lib.EPI_SWIGLU_INTERLEAVED | _lib.EPI_QUANT_RECIP)
+        return scatter_weighted(grouped_gemm(c2, sf2, w2, plan), plan, h), plan
     if fuse_swiglu:
         act = grouped_gemm(a_codes, a_sf, w13, plan, epilogue=_lib.EPI_SWIGLU_INTERLEAVED)
     else:

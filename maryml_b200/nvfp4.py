@@ -92,16 +92,87 @@ def untile_scales(scales_tiled, rows, k):
     return out
 
 
+_SPLITK_WS = {}
+
+
+def _splitk_workspace(device, nbytes):
+    """One reusable split-K workspace per device (grown on demand, never shrunk)."""
+    ws = _SPLITK_WS.get(device)
+    if ws is None or ws.numel() < nbytes:
+        ws = torch.empty(nbytes, dtype=torch.uint8, device=device)
+        _SPLITK_WS[device] = ws
+    return ws
+
+
 def gemm_w4a4(a_codes, a_sf, b_codes, b_sf, alpha, m, n, k, rowscale=None, out_dtype=torch.bfloat16,
               epilogue=_lib.EPI_PLAIN, out=None):
     ctx = context(a_codes.device.index)
     cols = n // 2 if epilogue == _lib.EPI_SWIGLU_INTERLEAVED else n
     if out is None:
         out = torch.empty((m, cols), dtype=out_dtype, device=a_codes.device)
+    if epilogue == _lib.EPI_PLAIN and m <= 128:
+        need = int(lib.mb_nvfp4_gemm_splitk_workspace(m, n, k))
+        if need:
+            ws = _splitk_workspace(a_codes.device, need)
+            ctx.check(lib.mb_nvfp4_gemm_w4a4_splitk(ctx.handle, _stream(), _p(a_codes), _p(a_sf), _p(b_codes), _p(b_sf),
+                                                    _p(rowscale), float(alpha), m, n, k, _p(out),
+                                                    _lib.DT_BF16 if out.dtype == torch.bfloat16 else _lib.DT_F32,
+                                                    _p(ws), need))
+            return out
     ctx.check(lib.mb_nvfp4_gemm_w4a4(ctx.handle, _stream(), _p(a_codes), _p(a_sf), _p(b_codes), _p(b_sf), _p(rowscale),
                                      float(alpha), m, n, k, _p(out),
                                      _lib.DT_BF16 if out.dtype == torch.bfloat16 else _lib.DT_F32, epilogue))
     return out
+
+
+class Stacked:
+    """Several stored NVFP4 tensors with the same k laid one after another along n, so that
+    projections of one input run as one product; every tensor keeps its own global scale in
+    `colscale` (one f32 per output column). `interleave` lays two tensors row by row (gate,
+    up, gate, up ...), the order the SwiGLU epilogues read."""
+
+    def __init__(self, parts, interleave=False):
+        k = parts[0].k()
+        assert all(w.k() == k for w in parts)
+        dev = parts[0].codes.device
+        if interleave:
+            assert len(parts) == 2 and parts[0].n() == parts[1].n()
+            n = parts[0].n()
+            self.codes = torch.stack([parts[0].codes.view(n, k // 2), parts[1].codes.view(n, k // 2)], 1) \
+                .reshape(2 * n, k // 2).contiguous()
+            scales = torch.stack([parts[0].scales.view(n, k // GROUP), parts[1].scales.view(n, k // GROUP)], 1) \
+                .reshape(2 * n, k // GROUP).contiguous()
+            self.colscale = torch.tensor([parts[0].scale2, parts[1].scale2], dtype=torch.float32, device=dev).repeat(n)
+        else:
+            self.codes = torch.cat([w.codes.view(w.n(), k // 2) for w in parts]).contiguous()
+            scales = torch.cat([w.scales.view(w.n(), k // GROUP) for w in parts]).contiguous()
+            self.colscale = torch.cat([torch.full((w.n(),), w.scale2, dtype=torch.float32, device=dev) for w in parts])
+        self.n, self.k = self.codes.shape[0], k
+        self.sf_tiled = tile_scales(scales, self.n, k)
+
+
+def gemm_w4a4_stacked(a_codes, a_sf, w, m, out_dtype=torch.bfloat16, epilogue=_lib.EPI_PLAIN):
+    """One product against a `Stacked` weight. Plain epilogue: [m, n] in out_dtype. SwiGLU
+    epilogues: [m, n/2] bf16, or with an EPI_QUANT_* flag the (codes, tiled scale plane) of it."""
+    ctx = context(a_codes.device.index)
+    dev = a_codes.device
+    swiglu = (epilogue & 0xFF) in (_lib.EPI_SWIGLU_INTERLEAVED, _lib.EPI_SWIGLU_ROUNDED)
+    quant = epilogue & (_lib.EPI_QUANT_RECIP | _lib.EPI_QUANT_SCALED)
+    ws, need, out_sf = None, 0, None
+    if quant:
+        out = torch.empty((m, w.n // 4), dtype=torch.uint8, device=dev)
+        out_sf = torch.empty(sf_bytes(m, w.n // 2), dtype=torch.uint8, device=dev)
+        dt = _lib.DT_BF16
+    else:
+        out = torch.empty((m, w.n // 2 if swiglu else w.n), dtype=torch.bfloat16 if swiglu else out_dtype, device=dev)
+        dt = _lib.DT_BF16 if out.dtype == torch.bfloat16 else _lib.DT_F32
+        if not swiglu and m <= 128:
+            need = int(lib.mb_nvfp4_gemm_splitk_workspace(m, w.n, w.k))
+            ws = _splitk_workspace(dev, need) if need else None
+    ctx.check(lib.mb_nvfp4_gemm_w4a4_stacked(ctx.handle, _stream(), _p(a_codes), _p(a_sf), _p(w.codes), _p(w.sf_tiled),
+                                             _p(w.colscale), m, w.n, w.k, _p(out), dt, epilogue, _p(out_sf), _p(ws),
+                                             need))
+    return (out, out_sf) if quant else out
 
 
 def bf16_gemm(a, b, out_dtype=torch.float32, out=None, alpha=1.0):

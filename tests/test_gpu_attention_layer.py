@@ -216,3 +216,113 @@ def test_decoder_layer_against_oracle(mods, orc, batch, t, past):
     rms = np.sqrt(np.mean(want.astype(np.float64) ** 2))
     err = np.abs(got - want)
     assert cos >= 0.9999 and err.max() <= 5e-2 * rms and err.mean() <= 1e-2 * rms, (err.max() / rms, err.mean() / rms, cos)
+
+
+# --------------------------------------------------------------------------- fused glue
+@pytest.mark.parametrize("rows,width,with_partial", [(1, 64, False), (37, 4096, True), (64, 4096, False),
+                                                     (5, 8192, True), (9, 1984, True)])
+def test_residual_norm_quantize_equals_the_three_kernels(mods, orc, rows, width, with_partial):
+    """One pass (add + norm + W4A4 quantizer) writes the bytes of mb_add_f32 -> mb_rmsnorm ->
+    mb_nvfp4_quantize_act, and those are pinned to the oracle's quantizer above."""
+    _, layer = mods
+    from maryml_b200 import nvfp4 as nv, _lib
+    x = dev_bf16(f32_to_bf16_bits(orc.normal_f32(1, rows * width, 1.0))).view(rows, width)
+    gain = dev_bf16(f32_to_bf16_bits(1.0 + orc.normal_f32(2, width, 0.1)))
+    partial = torch.from_numpy(orc.normal_f32(3, rows * width, 0.5).reshape(rows, width)).cuda() if with_partial else None
+    r_ref = layer.add_f32(x, partial) if with_partial else x
+    y_ref = layer.rmsnorm(r_ref, gain, 1e-6)
+    c_ref, sf_ref, _ = nv.quantize_act(y_ref, _lib.QUANT_SCALED, 1.0, tiled=True)
+    L = layer.DecoderLayer.__new__(layer.DecoderLayer)
+    L.cfg = layer.LayerConfig(hidden=width, eps=1e-6)
+    r, (codes, sf, n) = L._norm_quantize(x, partial, gain)
+    assert n == rows
+    assert torch.equal(r.view(torch.int16), r_ref.view(torch.int16))
+    assert torch.equal(codes, c_ref)
+    assert torch.equal(nv.untile_scales(sf, rows, width), nv.untile_scales(sf_ref, rows, width))
+    # and against the oracle's norm + quantizer on the same bytes
+    y_or = orc.rmsnorm_breeze(host_bits(r_ref).ravel(), host_bits(gain).ravel(), rows, width, 1e-6)
+    c_or, s_or = orc.quantize_act_scaled(bf16_bits_to_f32(y_or), rows, width, 1.0)
+    match = (codes.cpu().numpy().ravel() == c_or.ravel()).mean()
+    assert match >= 0.999, match       # the f32 sum of squares is ordered differently on the two sides
+
+
+@pytest.mark.parametrize("batch,t,hq,hkv,past,cap", [(3, 1, 4, 2, 21, 22), (2, 40, 4, 1, 0, 64), (1, 5, 8, 8, 7, 12)])
+def test_rope_append_equals_rope_and_copy(mods, orc, batch, t, hq, hkv, past, cap):
+    _, layer = mods
+    from maryml_b200 import _lib
+    D = 128
+    width = (hq + 2 * hkv) * D
+    qkv = dev_bf16(f32_to_bf16_bits(orc.normal_f32(4, batch * t * width, 1.0))).view(batch * t, width)
+    inv = torch.from_numpy(layer.inv_freq(D, 1e6)).cuda()
+    kc = dev_bf16(f32_to_bf16_bits(orc.normal_f32(5, batch * cap * hkv * D, 1.0))).view(batch, cap, hkv, D).clone()
+    vc = kc.clone() + 1
+    kc2, vc2 = kc.clone(), vc.clone()
+    # separate kernels: one rope call per sequence, then the cache writes
+    q_sep = qkv[:, :hq * D].contiguous().view(batch, t * hq * D)
+    k_sep = qkv[:, hq * D:(hq + hkv) * D].contiguous().view(batch, t * hkv * D)
+    v_sep = qkv[:, (hq + hkv) * D:].contiguous().view(batch, t, hkv, D)
+    q_ref = torch.stack([layer.rope(q_sep[b], t, hq, D, past, inv) for b in range(batch)]).view(batch, t, hq, D)
+    k_ref = torch.stack([layer.rope(k_sep[b], t, hkv, D, past, inv) for b in range(batch)]).view(batch, t, hkv, D)
+    kc[:, past:past + t].copy_(k_ref)
+    vc[:, past:past + t].copy_(v_sep)
+    q = torch.empty((batch, t, hq, D), dtype=torch.bfloat16, device="cuda")
+    ctx = _lib.context(0)
+    ctx.check(_lib.lib.mb_rope_append(ctx.handle, None, qkv.data_ptr(), batch, t, hq, hkv, D, past, inv.data_ptr(),
+                                      q.data_ptr(), kc2.data_ptr(), vc2.data_ptr(), cap))
+    assert torch.equal(q.view(torch.int16), q_ref.view(torch.int16))
+    assert torch.equal(kc2.view(torch.int16), kc.view(torch.int16))
+    assert torch.equal(vc2.view(torch.int16), vc.view(torch.int16))
+    with pytest.raises(_lib.MaryError):
+        ctx.check(_lib.lib.mb_rope_append(ctx.handle, None, qkv.data_ptr(), batch, t, hq, hkv, D, cap, inv.data_ptr(),
+                                          q.data_ptr(), kc2.data_ptr(), vc2.data_ptr(), cap))
+
+
+@pytest.mark.parametrize("m", [1, 64, 300])
+def test_stacked_products_equal_the_separate_ones(mods, orc, m):
+    """q|k|v as one product and gate/up + SwiGLU + quantizer as one product against the separate
+    projections, the stand-alone SwiGLU and the stand-alone quantizer: the same bytes."""
+    _, layer = mods
+    from maryml_b200 import nvfp4 as nv, _lib
+    k, nq, nkv, inter = 512, 512, 256, 768
+    ws = [nv.Nvfp4.quantize(dev_bf16(f32_to_bf16_bits(orc.normal_f32(10 + i, n * k, 0.02 * (i + 1)))).view(n, k))
+          for i, n in enumerate((nq, nkv, nkv, inter, inter))]
+    x = dev_bf16(f32_to_bf16_bits(orc.normal_f32(3, m * k, 1.0))).view(m, k)
+    codes, sf, _ = nv.quantize_act(x, _lib.QUANT_SCALED, 1.0, tiled=True)
+    sep = [nv.gemm_w4a4(codes, sf, w.codes, w.sf_tiled(), w.scale2, m, w.n(), k) for w in ws]
+    qkv = nv.gemm_w4a4_stacked(codes, sf, nv.Stacked(ws[:3]), m)
+    assert torch.equal(qkv.view(torch.int16), torch.cat(sep[:3], 1).view(torch.int16))
+    qkv32 = nv.gemm_w4a4_stacked(codes, sf, nv.Stacked(ws[:3]), m, out_dtype=torch.float32)
+    assert torch.equal(qkv32.to(torch.bfloat16).view(torch.int16), qkv.view(torch.int16))
+    gu = nv.Stacked(ws[3:], interleave=True)
+    act_ref = layer.swiglu(sep[3], sep[4])
+    act = nv.gemm_w4a4_stacked(codes, sf, gu, m, epilogue=_lib.EPI_SWIGLU_ROUNDED)
+    assert torch.equal(act.view(torch.int16), act_ref.view(torch.int16))
+    c_ref, sf_ref, _ = nv.quantize_act(act_ref, _lib.QUANT_SCALED, 1.0, tiled=True)
+    c, s = nv.gemm_w4a4_stacked(codes, sf, gu, m, epilogue=_lib.EPI_SWIGLU_ROUNDED | _lib.EPI_QUANT_SCALED)
+    assert torch.equal(c, c_ref)
+    assert torch.equal(nv.untile_scales(s, m, inter), nv.untile_scales(sf_ref, m, inter))
+    c_ref, sf_ref, _ = nv.quantize_act(act_ref, _lib.QUANT_RECIP, tiled=True)
+    c, s = nv.gemm_w4a4_stacked(codes, sf, gu, m, epilogue=_lib.EPI_SWIGLU_ROUNDED | _lib.EPI_QUANT_RECIP)
+    assert torch.equal(c, c_ref)
+    assert torch.equal(nv.untile_scales(s, m, inter), nv.untile_scales(sf_ref, m, inter))
+    ctx = _lib.context(0)
+    with pytest.raises(_lib.MaryError):      # a quantized output without a SwiGLU epilogue is refused
+        nv.gemm_w4a4_stacked(codes, sf, gu, m, epilogue=_lib.EPI_PLAIN | _lib.EPI_QUANT_RECIP)
+
+
+@pytest.mark.parametrize("batch,t,past", [(1, 40, 0), (3, 1, 21), (2, 150, 10)])
+def test_fused_layer_equals_the_kernel_by_kernel_layer(mods, orc, batch, t, past):
+    _, layer = mods
+    cfg = layer.LayerConfig(hidden=512, heads=4, kv_heads=2, head_dim=128, inter=1024)
+    full, g1, g2 = _layer_fixture(orc, layer, cfg)
+    cap = past + t
+    x = dev_bf16(f32_to_bf16_bits(orc.normal_f32(7, batch * t * cfg.hidden, 1.0))).view(batch * t, cfg.hidden)
+    kc = dev_bf16(f32_to_bf16_bits(orc.normal_f32(8, batch * cap * cfg.kv_heads * 128, 1.0))).view(batch, cap, cfg.kv_heads, 128)
+    vc = dev_bf16(f32_to_bf16_bits(orc.normal_f32(9, batch * cap * cfg.kv_heads * 128, 1.0))).view(batch, cap, cfg.kv_heads, 128)
+    outs = []
+    for fuse in (False, True):
+        L = layer.DecoderLayer(cfg, full, dev_bf16(g1), dev_bf16(g2), fuse=fuse)
+        kd, vd = kc.clone(), vc.clone()
+        outs.append((L.forward(x, batch, past, kd, vd), kd, vd))
+    for a, b in zip(outs[0], outs[1]):
+        assert torch.equal(a.view(torch.int16), b.view(torch.int16))

@@ -136,6 +136,11 @@ def test_moe_experts_against_oracle(moe, orc, tokens, h, inter, n_experts, k):
     assert cos >= 0.9999 and rel <= 5e-2, (rel, cos)
     rel2, cos2 = rel_check(out_unfused.cpu().numpy(), got)
     assert cos2 >= 0.99999, (rel2, cos2)
+    # the second projection's quantizer inside the first product's epilogue: the same bytes as
+    # storing the bf16 activations and quantizing them in a pass of their own
+    out_stored, _ = moe.moe_experts(x, torch.from_numpy(idx).cuda(), torch.from_numpy(wgt).cuda(), b13, b2,
+                                    fuse_quant=False)
+    assert torch.equal(out_stored, out)
 
 
 def test_moe_layer_config2_shapes_smoke(moe, orc):

@@ -230,6 +230,44 @@ def test_gemm_w4a4_exact_on_power_of_two_scales(mb, orc, m, n, k):
     assert np.array_equal(got, ref), f"max abs err {np.abs(got - ref).max()}"
 
 
+@pytest.mark.parametrize("m,n,k", [(16, 4096, 4096), (64, 512, 7168), (100, 1280, 2048), (1, 256, 2816),
+                                   (128, 384, 2816)])
+def test_gemm_w4a4_split_k_exact_and_ordered(mb, orc, m, n, k):
+    """Decode-sized products are cut along K into f32 planes and summed in slice order. With
+    power-of-two scales every partial sum is exact, so the split result equals the oracle to the
+    bit (f32 output) and the unsplit entry point to the bit (bf16 output with a row scale)."""
+    from maryml_b200 import _lib
+    need = int(_lib.lib.mb_nvfp4_gemm_splitk_workspace(m, n, k))
+    assert need > 0 and need % (m * n * 4) == 0
+    rng = np.random.default_rng(m * 7 + n * 3 + k)
+    a_codes, a_scales = _pow2_planes(orc, rng, m, k)
+    b_codes, b_scales = _pow2_planes(orc, rng, n, k)
+    ref = orc.linear_w4a4(a_codes, a_scales, b_codes, b_scales, 1.0, m, n, k)
+    ac = torch.from_numpy(a_codes).cuda()
+    bc = torch.from_numpy(b_codes).cuda()
+    asf = mb.tile_scales(torch.from_numpy(a_scales).cuda(), m, k)
+    bsf = mb.tile_scales(torch.from_numpy(b_scales).cuda(), n, k)
+    got = mb.gemm_w4a4(ac, asf, bc, bsf, 1.0, m, n, k, out_dtype=torch.float32).cpu().numpy()
+    assert np.array_equal(got, ref), f"max abs err {np.abs(got - ref).max()}"
+    # bf16 + row scale, twice (the workspace is reused), against the single-pass kernel
+    rowscale = torch.from_numpy(rng.choice(np.array([0.5, 1.0, 2.0], np.float32), size=m)).cuda()
+    ctx = _lib.context(0)
+    plain = torch.empty((m, n), dtype=torch.bfloat16, device="cuda")
+    ctx.check(_lib.lib.mb_nvfp4_gemm_w4a4(ctx.handle, None, ac.data_ptr(), asf.data_ptr(), bc.data_ptr(), bsf.data_ptr(),
+                                          rowscale.data_ptr(), 0.25, m, n, k, plain.data_ptr(), _lib.DT_BF16,
+                                          _lib.EPI_PLAIN))
+    for _ in range(2):
+        split = mb.gemm_w4a4(ac, asf, bc, bsf, 0.25, m, n, k, rowscale=rowscale)
+        assert torch.equal(split.view(torch.int16), plain.view(torch.int16))
+    # a short workspace falls back to the single pass instead of overrunning it
+    short = torch.empty(16, dtype=torch.uint8, device="cuda")
+    out = torch.empty((m, n), dtype=torch.bfloat16, device="cuda")
+    ctx.check(_lib.lib.mb_nvfp4_gemm_w4a4_splitk(ctx.handle, None, ac.data_ptr(), asf.data_ptr(), bc.data_ptr(),
+                                                 bsf.data_ptr(), rowscale.data_ptr(), 0.25, m, n, k, out.data_ptr(),
+                                                 _lib.DT_BF16, short.data_ptr(), 16))
+    assert torch.equal(out.view(torch.int16), plain.view(torch.int16))
+
+
 @pytest.mark.parametrize("m,n,k", [(16, 4096, 4096), (128, 256, 4096), (1000, 1280, 2048)])
 def test_project_w4a4_against_same_operand_f64(mb, orc, m, n, k):
     wbits = f32_to_bf16_bits(orc.normal_f32(2, n * k, 0.02))
