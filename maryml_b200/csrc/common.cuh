@@ -139,6 +139,54 @@ __device__ __forceinline__ uint32_t mb_e4m3_from_f32(float v) {
   return byte > 0x7E ? 0x7E : byte;
 }
 
+// The same two conversions by the hardware converters (one instruction each way instead of a
+// dozen): cvt.rn.satfinite.e4m3x2.f32 rounds to nearest even and saturates at 448; the decode
+// goes through f16, which holds every E4M3 value exactly. Callers clamp to [0, 448] first, so
+// the NaN and negative cases of the arithmetic form above never reach them.
+__device__ __forceinline__ uint32_t mb_e4m3_encode(float v) {
+  uint16_t r;
+  asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(r) : "f"(0.0f), "f"(v));
+  return uint32_t(r) & 0xFFu;
+}
+__device__ __forceinline__ float mb_e4m3_decode(uint32_t b) {
+  uint32_t h2;
+  asm("cvt.rn.f16x2.e4m3x2 %0, %1;" : "=r"(h2) : "h"(uint16_t(b)));
+  float f;
+  asm("{ .reg .b16 lo, hi; mov.b32 {lo, hi}, %1; cvt.f32.f16 %0, lo; }" : "=f"(f) : "r"(h2));
+  return f;
+}
+
+// RN(a / 6) without the divide subroutine: q = RN(a c), c = RN(1/6); the residual a - 6 q is
+// exact in one fma and RN(q + residual c) is the correctly rounded quotient (Markstein; 6's
+// significand is not all ones). Tiny, infinite and NaN operands take the divide itself.
+__device__ __forceinline__ float mb_div6(float a) {
+  const float c = 0.16666667163372040f;   // 0x3E2AAAAB
+  if (a >= 1.0e-30f && a <= 3.0e38f) {
+    const float q = __fmul_rn(a, c);
+    return __fmaf_rn(__fmaf_rn(-q, 6.0f, a), c, q);
+  }
+  return __fdiv_rn(a, 6.0f);
+}
+
+// n / d and n % d for a divisor fixed at launch (Granlund-Montgomery, exact for every 32-bit n).
+struct mb_fastdiv {
+  uint32_t d, mul, sh1, sh2;
+};
+inline mb_fastdiv mb_fastdiv_make(uint32_t d) {
+  mb_fastdiv f;
+  f.d = d;
+  uint32_t l = 0;
+  while ((1ull << l) < d) ++l;
+  f.mul = uint32_t(((1ull << 32) * ((1ull << l) - d)) / d + 1);
+  f.sh1 = l < 1 ? l : 1;
+  f.sh2 = l - f.sh1;
+  return f;
+}
+__device__ __forceinline__ uint32_t mb_fastdiv_q(uint32_t n, const mb_fastdiv& f) {
+  const uint32_t t = __umulhi(f.mul, n);
+  return (t + ((n - t) >> f.sh1)) >> f.sh2;
+}
+
 // Two f32 -> one byte of E2M1 codes, `lo` in the LOW nibble: the hardware
 // cvt.rn.satfinite.e2m1x2.f32 (ties to the even code, saturating at 6, sign kept
 // on a zero result). PTX puts its first source operand in the HIGH nibble.

@@ -1,8 +1,8 @@
 // NVFP4 quantizers, dequantizer and scale-plane re-layout.
 //
-// All of these are HBM-bound byte kernels: one thread owns one 16-element block
-// (32 B of bf16 or 64 B of f32 in, 8 B of codes + 1 scale byte out), loads are
-// 128-bit, four neighbouring lanes merge their scale bytes into one 32-bit store.
+// All of these are HBM-bound byte kernels: one thread owns one or two 16-element blocks
+// (32 B of bf16 or 64 B of f32 in, 8 B of codes + 1 scale byte out per block), loads are
+// 128-bit, neighbouring lanes merge their scale bytes into one 32-bit store.
 // Algorithmic traffic per element: 2 (bf16) or 4 (f32) bytes read + 0.5625 written.
 #include "common.cuh"
 #include "quant_block.cuh"
@@ -36,60 +36,138 @@ __device__ __forceinline__ void load16_scalar(const T* p, float* v) {
   for (int i = 0; i < 16; ++i) v[i] = float(p[i]);
 }
 
-template <typename T>
+// One thread per 16-value block. The kernel is bound by instruction issue, not by memory,
+// unless the per-block instruction count stays near a hundred: the recipe is a template
+// parameter, the block index splits into (row, k-block) by a multiply-high, the scale byte
+// goes through the hardware E4M3 converters, amax / 6 is a three-instruction exact quotient.
+template <typename T, int RECIPE>
 __global__ void __launch_bounds__(QUANT_THREADS)
-quantize_kernel(const T* __restrict__ x, size_t rows, size_t k, int recipe, float input_scale,
+quantize_kernel(const T* __restrict__ x, uint32_t blocks, uint32_t k, mb_fastdiv rb, float input_scale,
                 const float* __restrict__ rowscale, const int32_t* __restrict__ gather, uint2* __restrict__ codes,
-                uint8_t* __restrict__ scales, int tiled, size_t kchunks, int vec_ok) {
-  // 32-bit block index (the launcher checks the extent); a power-of-two row splits by shift.
-  const uint32_t row_blocks = uint32_t(k / 16);
-  const uint32_t blocks = uint32_t(rows) * row_blocks;
+                uint8_t* __restrict__ scales, int tiled, uint32_t kchunks, int vec_ok) {
   const uint32_t blk = blockIdx.x * QUANT_THREADS + threadIdx.x;
   const bool live = blk < blocks;
-  uint32_t row = 0, kb = 0;
-  if (live) {
-    if ((row_blocks & (row_blocks - 1)) == 0) {
-      row = blk >> (31 - __clz(row_blocks));
-      kb = blk & (row_blocks - 1);
-    } else {
-      row = blk / row_blocks;
-      kb = blk - row * row_blocks;
-    }
-  }
+  const uint32_t row = mb_fastdiv_q(live ? blk : 0u, rb);
+  const uint32_t kb = (live ? blk : 0u) - row * rb.d;
   uint32_t sbyte = 0;
-  uint2 c = make_uint2(0u, 0u);
   if (live) {
     float v[16];
-    long long src = gather ? (long long)gather[row] : (long long)row;
+    const int32_t src = gather ? gather[row] : int32_t(row);
     if (src < 0) {
 #pragma unroll
       for (int i = 0; i < 16; ++i) v[i] = 0.0f;
     } else {
-      const T* p = x + size_t(src) * k + size_t(kb) * 16;
+      const T* p = x + size_t(uint32_t(src)) * k + kb * 16u;
       if (vec_ok) load16(p, v); else load16_scalar(p, v);
     }
-    if (recipe == MB_QUANT_RECIP) {
+    uint2 c;
+    if (RECIPE == MB_QUANT_RECIP) {
       quant_block_recip(v, sbyte, c);
     } else {
-      float s2 = recipe == MB_QUANT_ROWS ? rowscale[row] : input_scale;
+      const float s2 = RECIPE == MB_QUANT_ROWS ? rowscale[row] : input_scale;
       quant_block_scaled(v, s2, sbyte, c);
     }
     codes[blk] = c;
   }
   // Four neighbouring lanes (same row, kb%4 = 0..3) merge their scale bytes.
-  if ((row_blocks & 3) == 0) {
+  if ((rb.d & 3u) == 0) {
     uint32_t w = sbyte;
     w |= __shfl_down_sync(0xFFFFFFFFu, sbyte, 1) << 8;
     w |= __shfl_down_sync(0xFFFFFFFFu, sbyte, 2) << 16;
     w |= __shfl_down_sync(0xFFFFFFFFu, sbyte, 3) << 24;
     if (live && (threadIdx.x & 3) == 0) {
-      size_t off = tiled ? mb_sf_offset(row, kb, kchunks) : blk;
+      const size_t off = tiled ? mb_sf_offset(row, kb, kchunks) : blk;
       *reinterpret_cast<uint32_t*>(scales + off) = w;
     }
   } else if (live) {
-    size_t off = tiled ? mb_sf_offset(row, kb, kchunks) : blk;
+    const size_t off = tiled ? mb_sf_offset(row, kb, kchunks) : blk;
     scales[off] = uint8_t(sbyte);
   }
+}
+
+// The same with two neighbouring blocks of a row per thread (k a multiple of 32): the index
+// arithmetic, the parameter loads and the control flow are paid once per 32 values, the codes
+// leave as one 128-bit store and two lanes fill a 32-bit word of scale bytes.
+template <typename T, int RECIPE>
+__global__ void __launch_bounds__(QUANT_THREADS)
+quantize2_kernel(const T* __restrict__ x, uint32_t pairs, uint32_t k, mb_fastdiv rbp, float input_scale,
+                 const float* __restrict__ rowscale, const int32_t* __restrict__ gather, uint4* __restrict__ codes,
+                 uint8_t* __restrict__ scales, int tiled, uint32_t kchunks, int vec_ok) {
+  const uint32_t pr = blockIdx.x * QUANT_THREADS + threadIdx.x;
+  const bool live = pr < pairs;
+  const uint32_t row = mb_fastdiv_q(live ? pr : 0u, rbp);
+  const uint32_t kb = ((live ? pr : 0u) - row * rbp.d) * 2u;
+  uint32_t s0 = 0, s1 = 0;
+  if (live) {
+    float v[32];
+    const int32_t src = gather ? gather[row] : int32_t(row);
+    if (src < 0) {
+#pragma unroll
+      for (int i = 0; i < 32; ++i) v[i] = 0.0f;
+    } else {
+      const T* p = x + size_t(uint32_t(src)) * k + kb * 16u;
+      if (vec_ok) { load16(p, v); load16(p + 16, v + 16); }
+      else { load16_scalar(p, v); load16_scalar(p + 16, v + 16); }
+    }
+    uint2 c0, c1;
+    if (RECIPE == MB_QUANT_RECIP) {
+      quant_block_recip(v, s0, c0);
+      quant_block_recip(v + 16, s1, c1);
+    } else {
+      const float s2 = RECIPE == MB_QUANT_ROWS ? rowscale[row] : input_scale;
+      quant_block_scaled(v, s2, s0, c0);
+      quant_block_scaled(v + 16, s2, s1, c1);
+    }
+    codes[pr] = make_uint4(c0.x, c0.y, c1.x, c1.y);
+  }
+  const uint32_t w2 = s0 | (s1 << 8);
+  if ((rbp.d & 1u) == 0) {
+    // k-blocks per row a multiple of four: lanes (2j, 2j+1) hold kb % 4 = 0 and 2 of one word
+    const uint32_t w = w2 | (__shfl_down_sync(0xFFFFFFFFu, w2, 1) << 16);
+    if (live && (threadIdx.x & 1) == 0) {
+      const size_t off = tiled ? mb_sf_offset(row, kb, kchunks) : size_t(pr) * 2;
+      *reinterpret_cast<uint32_t*>(scales + off) = w;
+    }
+  } else if (live) {
+    const size_t off = tiled ? mb_sf_offset(row, kb, kchunks) : size_t(pr) * 2;
+    *reinterpret_cast<uint16_t*>(scales + off) = uint16_t(w2);
+  }
+}
+
+template <typename T>
+static void launch_quantize(cudaStream_t stream, int recipe, const T* x, size_t rows, size_t k, float input_scale,
+                            const float* rowscale, const int32_t* gather, uint8_t* codes, uint8_t* scales, int tiled,
+                            int vec_ok) {
+  const uint32_t kc = uint32_t(mb_sf_kchunks(k));
+  if (k % 32 == 0 && mb_aligned(codes, 16)) {
+    const uint32_t pairs = uint32_t(rows * (k / 32));
+    const unsigned grid2 = (pairs + QUANT_THREADS - 1) / QUANT_THREADS;
+    const mb_fastdiv rbp = mb_fastdiv_make(uint32_t(k / 32));
+    uint4* c4 = reinterpret_cast<uint4*>(codes);
+    if (recipe == MB_QUANT_RECIP)
+      quantize2_kernel<T, MB_QUANT_RECIP><<<grid2, QUANT_THREADS, 0, stream>>>(x, pairs, uint32_t(k), rbp, input_scale,
+                                                                               rowscale, gather, c4, scales, tiled, kc, vec_ok);
+    else if (recipe == MB_QUANT_ROWS)
+      quantize2_kernel<T, MB_QUANT_ROWS><<<grid2, QUANT_THREADS, 0, stream>>>(x, pairs, uint32_t(k), rbp, input_scale,
+                                                                              rowscale, gather, c4, scales, tiled, kc, vec_ok);
+    else
+      quantize2_kernel<T, MB_QUANT_SCALED><<<grid2, QUANT_THREADS, 0, stream>>>(x, pairs, uint32_t(k), rbp, input_scale,
+                                                                                rowscale, gather, c4, scales, tiled, kc, vec_ok);
+    return;
+  }
+  const uint32_t blocks = uint32_t(rows * (k / 16));
+  const unsigned grid = (blocks + QUANT_THREADS - 1) / QUANT_THREADS;
+  const mb_fastdiv rb = mb_fastdiv_make(uint32_t(k / 16));
+  uint2* c = reinterpret_cast<uint2*>(codes);
+  if (recipe == MB_QUANT_RECIP)
+    quantize_kernel<T, MB_QUANT_RECIP><<<grid, QUANT_THREADS, 0, stream>>>(x, blocks, uint32_t(k), rb, input_scale,
+                                                                           rowscale, gather, c, scales, tiled, kc, vec_ok);
+  else if (recipe == MB_QUANT_ROWS)
+    quantize_kernel<T, MB_QUANT_ROWS><<<grid, QUANT_THREADS, 0, stream>>>(x, blocks, uint32_t(k), rb, input_scale,
+                                                                          rowscale, gather, c, scales, tiled, kc, vec_ok);
+  else
+    quantize_kernel<T, MB_QUANT_SCALED><<<grid, QUANT_THREADS, 0, stream>>>(x, blocks, uint32_t(k), rb, input_scale,
+                                                                            rowscale, gather, c, scales, tiled, kc, vec_ok);
 }
 
 // amax over a tensor with a separate NaN/Inf witness: max drops a NaN operand,
@@ -118,16 +196,24 @@ amax_kernel(const __nv_bfloat16* __restrict__ w, size_t len, uint32_t* __restric
 // rowscale[r] = amax(|x[r,:]|)/2688, 1.0 for an all-zero row, NaN for a NaN row.
 template <typename T>
 __global__ void __launch_bounds__(256)
-row_scale_kernel(const T* __restrict__ x, size_t k, const int32_t* __restrict__ gather, float* __restrict__ rowscale) {
+row_scale_kernel(const T* __restrict__ x, size_t k, const int32_t* __restrict__ gather, float* __restrict__ rowscale,
+                 int vec_ok) {
   size_t r = blockIdx.x;
   long long src = gather ? (long long)gather[r] : (long long)r;
   float m = 0.0f;
   uint32_t nan = 0;
   if (src >= 0) {
-    for (size_t j = threadIdx.x; j < k; j += blockDim.x) {
-      float v = fabsf(float(x[size_t(src) * k + j]));
-      if (v != v) nan = 1;
-      m = fmaxf(m, v);
+    // sixteen values (two 128-bit loads) per thread and step; k is a multiple of 16
+    for (size_t j = size_t(threadIdx.x) * 16; j < k; j += size_t(blockDim.x) * 16) {
+      float v[16];
+      const T* p = x + size_t(src) * k + j;
+      if (vec_ok) load16(p, v); else load16_scalar(p, v);
+#pragma unroll
+      for (int i = 0; i < 16; ++i) {
+        const float a = fabsf(v[i]);
+        if (a != a) nan = 1;
+        m = fmaxf(m, a);
+      }
     }
   }
   __shared__ float sm[8];
@@ -198,31 +284,26 @@ MB_API int mb_nvfp4_quantize_act(mb_ctx* ctx, mb_stream stream_, const void* x, 
   if (recipe == MB_QUANT_ROWS) MB_REQUIRE(ctx, rowscale != nullptr, "quantize_act: the rows recipe writes rowscale");
   if (gather) MB_REQUIRE(ctx, src_rows > 0, "quantize_act: gather needs the source row count");
   int vec_ok = mb_aligned(x, 16) && (k * esz) % 16 == 0;
-  size_t kchunks = mb_sf_kchunks(k);
-  if (sf_layout == MB_SF_TILED) {
-    // Pad rows and pad K-chunks of the tiled plane must not hold stale NaN patterns
-    // next to live rows of the same 128-row atom only cosmetically: those rows are
-    // never stored. They are zeroed so that the plane is deterministic.
+  if (sf_layout == MB_SF_TILED && (rows % 128 != 0 || k % 256 != 0)) {
+    // Scale bytes of the K padding are read by the product that consumes the plane and must decode
+    // to a finite value; the bytes of pad rows only make the plane deterministic (their outputs
+    // are never stored). A plane without padding is written whole by the kernel.
     MB_CUDA_OK(ctx, cudaMemsetAsync(scales, 0, mb_sf_plane_bytes(rows, k), stream));
   }
   if (recipe == MB_QUANT_ROWS) {
     if (x_dtype == MB_DT_BF16)
-      row_scale_kernel<<<unsigned(rows), 256, 0, stream>>>(static_cast<const __nv_bfloat16*>(x), k, gather, rowscale);
+      row_scale_kernel<<<unsigned(rows), 256, 0, stream>>>(static_cast<const __nv_bfloat16*>(x), k, gather, rowscale,
+                                                           vec_ok);
     else
-      row_scale_kernel<<<unsigned(rows), 256, 0, stream>>>(static_cast<const float*>(x), k, gather, rowscale);
+      row_scale_kernel<<<unsigned(rows), 256, 0, stream>>>(static_cast<const float*>(x), k, gather, rowscale, vec_ok);
     MB_LAUNCH_OK(ctx);
   }
-  size_t blocks = rows * (k / 16);
-  unsigned grid = unsigned((blocks + QUANT_THREADS - 1) / QUANT_THREADS);
   if (x_dtype == MB_DT_BF16)
-    quantize_kernel<<<grid, QUANT_THREADS, 0, stream>>>(static_cast<const __nv_bfloat16*>(x), rows, k, recipe,
-                                                        input_scale, rowscale, gather,
-                                                        reinterpret_cast<uint2*>(codes), scales,
-                                                        sf_layout == MB_SF_TILED, kchunks, vec_ok);
+    launch_quantize(stream, recipe, static_cast<const __nv_bfloat16*>(x), rows, k, input_scale, rowscale, gather, codes,
+                    scales, sf_layout == MB_SF_TILED, vec_ok);
   else
-    quantize_kernel<<<grid, QUANT_THREADS, 0, stream>>>(static_cast<const float*>(x), rows, k, recipe, input_scale,
-                                                        rowscale, gather, reinterpret_cast<uint2*>(codes), scales,
-                                                        sf_layout == MB_SF_TILED, kchunks, vec_ok);
+    launch_quantize(stream, recipe, static_cast<const float*>(x), rows, k, input_scale, rowscale, gather, codes, scales,
+                    sf_layout == MB_SF_TILED, vec_ok);
   MB_LAUNCH_OK(ctx);
   return MB_OK;
 }
