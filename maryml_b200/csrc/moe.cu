@@ -96,51 +96,69 @@ router_softmax_topk_kernel(const float* __restrict__ logits, uint32_t tokens, ui
 // ---------------------------------------------------------------------------------
 constexpr int PLAN_PAD = 128;   // rows per GEMM tile: each expert's rows are padded to this
 
-// One pass that puts every plan buffer in its empty state: no token on any row (-1), zero
-// weights, no expert on any tile (-1), no row for any pick (-1), zero counts.
-__global__ void __launch_bounds__(256)
-plan_init_kernel(int32_t* __restrict__ row_tok, float* __restrict__ row_wgt, uint32_t m_cap,
-                 int32_t* __restrict__ tile_expert, uint32_t tiles, int32_t* __restrict__ tok_rows, uint32_t picks,
-                 int32_t* __restrict__ counts, uint32_t n_experts) {
-  const uint32_t stride = gridDim.x * 256;
-  for (uint32_t i = blockIdx.x * 256 + threadIdx.x; i < m_cap; i += stride) { row_tok[i] = -1; row_wgt[i] = 0.0f; }
-  for (uint32_t i = blockIdx.x * 256 + threadIdx.x; i < picks; i += stride) tok_rows[i] = -1;
-  for (uint32_t i = blockIdx.x * 256 + threadIdx.x; i < tiles; i += stride) tile_expert[i] = -1;
-  for (uint32_t i = blockIdx.x * 256 + threadIdx.x; i < n_experts; i += stride) counts[i] = 0;
+constexpr int PLAN_CHUNK = 256;   // tokens per block of the count and place passes
+
+// A pick (t, j) takes a row unless its expert is out of range or repeats an earlier pick of the token.
+__device__ __forceinline__ bool plan_pick_ok(const int32_t* p, uint32_t j, uint32_t n_experts) {
+  const int32_t e = p[j];
+  bool ok = e >= 0 && uint32_t(e) < n_experts;
+  for (uint32_t i = 0; ok && i < j; ++i) ok = p[i] != e;
+  return ok;
 }
 
-// counts[e] = picks of expert e; checks range and per-token duplicates.
-__global__ void __launch_bounds__(256)
+// Pass 1, one block per 256 tokens: picks per expert within the chunk (a shared-memory
+// histogram; the sums do not depend on the order of the adds) -> chunk_counts[chunk][expert].
+// The same launch puts the row arrays in their empty state (-1, weight 0).
+__global__ void __launch_bounds__(PLAN_CHUNK)
 plan_count_kernel(const int32_t* __restrict__ idx, uint32_t tokens, uint32_t k, uint32_t n_experts,
-                  int32_t* __restrict__ counts, int* __restrict__ flag) {
-  uint32_t t = blockIdx.x * 256 + threadIdx.x;
-  if (t >= tokens) return;
-  const int32_t* p = idx + size_t(t) * k;
-  for (uint32_t j = 0; j < k; ++j) {
-    int32_t e = p[j];
-    bool ok = e >= 0 && uint32_t(e) < n_experts;
-    for (uint32_t i = 0; ok && i < j; ++i) ok = p[i] != e;
-    if (!ok) { atomicCAS(flag, 0, int(t) + 1); continue; }
-    atomicAdd(counts + e, 1);
+                  int32_t* __restrict__ chunk_counts, int32_t* __restrict__ row_tok, float* __restrict__ row_wgt,
+                  uint32_t m_cap, int* __restrict__ flag) {
+  extern __shared__ int32_t s_hist[];
+  for (uint32_t e = threadIdx.x; e < n_experts; e += PLAN_CHUNK) s_hist[e] = 0;
+  for (uint32_t i = blockIdx.x * PLAN_CHUNK + threadIdx.x; i < m_cap; i += gridDim.x * PLAN_CHUNK) {
+    row_tok[i] = -1;
+    row_wgt[i] = 0.0f;
   }
+  __syncthreads();
+  const uint32_t t = blockIdx.x * PLAN_CHUNK + threadIdx.x;
+  if (t < tokens) {
+    const int32_t* p = idx + size_t(t) * k;
+    for (uint32_t j = 0; j < k; ++j) {
+      if (plan_pick_ok(p, j, n_experts)) atomicAdd(&s_hist[p[j]], 1);
+      else atomicCAS(flag, 0, int(t) + 1);
+    }
+  }
+  __syncthreads();
+  for (uint32_t e = threadIdx.x; e < n_experts; e += PLAN_CHUNK)
+    chunk_counts[size_t(blockIdx.x) * n_experts + e] = s_hist[e];
 }
 
-// One block: exclusive scan of the padded counts -> first stacked row of each
-// expert, the expert of each 128-row tile, the number of tiles in use.
+// Pass 2, one block, thread e = expert e: the chunk counts become exclusive prefixes over
+// the chunks (rows of expert e that earlier chunks take); the totals, padded to 128, give the
+// first stacked row of each expert, the expert of each tile and the number of tiles in use.
 __global__ void __launch_bounds__(1024)
-plan_scan_kernel(const int32_t* __restrict__ counts, uint32_t n_experts, int32_t* __restrict__ expert_rows,
-                 int32_t* __restrict__ expert_row0, int32_t* __restrict__ tile_expert, uint32_t tile_cap,
-                 int32_t* __restrict__ n_tiles) {
+plan_scan_kernel(int32_t* __restrict__ chunk_counts, uint32_t chunks, uint32_t n_experts,
+                 int32_t* __restrict__ expert_rows, int32_t* __restrict__ expert_row0,
+                 int32_t* __restrict__ tile_expert, uint32_t tile_cap, int32_t* __restrict__ n_tiles) {
   __shared__ int32_t s_pad[1024];
   __shared__ int32_t s_off[1024];
-  uint32_t e = threadIdx.x;
-  int32_t c = e < n_experts ? counts[e] : 0;
+  __shared__ int32_t s_total;
+  const uint32_t e = threadIdx.x;
+  int32_t c = 0;
+  if (e < n_experts) {
+    for (uint32_t ch = 0; ch < chunks; ++ch) {
+      const int32_t here = chunk_counts[size_t(ch) * n_experts + e];
+      chunk_counts[size_t(ch) * n_experts + e] = c;
+      c += here;
+    }
+  }
   s_pad[e] = (c + PLAN_PAD - 1) / PLAN_PAD;   // tiles of this expert
   __syncthreads();
   if (e == 0) {
     int32_t run = 0;
     for (uint32_t i = 0; i < n_experts; ++i) { s_off[i] = run; run += s_pad[i]; }
     *n_tiles = run;
+    s_total = run;
   }
   __syncthreads();
   if (e < n_experts) {
@@ -149,63 +167,52 @@ plan_scan_kernel(const int32_t* __restrict__ counts, uint32_t n_experts, int32_t
     for (int32_t i = 0; i < s_pad[e]; ++i)
       if (uint32_t(s_off[e] + i) < tile_cap) tile_expert[s_off[e] + i] = int32_t(e);
   }
+  for (uint32_t i = uint32_t(s_total) + e; i < tile_cap; i += 1024) tile_expert[i] = -1;
 }
 
-// One block per expert. Thread i owns a contiguous run of tokens, counts the run's hits,
-// a block-wide exclusive scan turns the counts into row offsets, and the thread then writes
-// its hits in token order. Deterministic: expert-ascending, token-ascending.
-__global__ void __launch_bounds__(256)
+// Pass 3, one block per 256 tokens, thread = token. A bit mask per expert records which
+// tokens of the chunk picked it; a pick's row is the expert's first row + the rows earlier
+// chunks take + the number of earlier tokens of this chunk in the mask. Deterministic:
+// expert-ascending, token-ascending. The token's k rows are then sorted and stored.
+__global__ void __launch_bounds__(PLAN_CHUNK)
 plan_place_kernel(const int32_t* __restrict__ idx, const float* __restrict__ weight, uint32_t tokens, uint32_t k,
-                  const int32_t* __restrict__ expert_row0, int32_t* __restrict__ row_tok,
-                  float* __restrict__ row_wgt, int32_t* __restrict__ tok_rows) {
-  const int32_t e = blockIdx.x;
-  const uint32_t lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const uint32_t per = (tokens + 255) / 256;
-  const uint32_t t_begin = min(tokens, threadIdx.x * per), t_end = min(tokens, t_begin + per);
-  __shared__ int32_t s_warp[8];
-  int32_t mine = 0;
-  for (uint32_t t = t_begin; t < t_end; ++t) {
-    const int32_t* p = idx + size_t(t) * k;
-    for (uint32_t j = 0; j < k; ++j) mine += p[j] == e;
-  }
-  // exclusive scan of `mine` over the block
-  int32_t incl = mine;
-#pragma unroll
-  for (int o = 1; o < 32; o <<= 1) {
-    int32_t v = __shfl_up_sync(0xFFFFFFFFu, incl, o);
-    if (lane >= uint32_t(o)) incl += v;
-  }
-  if (lane == 31) s_warp[warp] = incl;
+                  uint32_t n_experts, const int32_t* __restrict__ chunk_base, const int32_t* __restrict__ expert_row0,
+                  int32_t* __restrict__ row_tok, float* __restrict__ row_wgt, int32_t* __restrict__ tok_rows) {
+  extern __shared__ uint32_t s_mask[];   // [n_experts][8]
+  for (uint32_t i = threadIdx.x; i < n_experts * 8; i += PLAN_CHUNK) s_mask[i] = 0u;
   __syncthreads();
-  int32_t before = 0;
-  for (uint32_t w = 0; w < warp; ++w) before += s_warp[w];
-  int32_t row = expert_row0[e] + before + incl - mine;
-  for (uint32_t t = t_begin; t < t_end && mine > 0; ++t) {
-    const int32_t* p = idx + size_t(t) * k;
+  const uint32_t t = blockIdx.x * PLAN_CHUNK + threadIdx.x;
+  const uint32_t word = threadIdx.x >> 5, bit = threadIdx.x & 31;
+  const int32_t* p = idx + size_t(t) * k;
+  uint32_t ok_bits = 0;
+  if (t < tokens) {
     for (uint32_t j = 0; j < k; ++j) {
-      if (p[j] == e) {
-        row_tok[row] = int32_t(t);
-        row_wgt[row] = weight[size_t(t) * k + j];
-        tok_rows[size_t(t) * k + j] = row;
-        ++row;
-        break;
+      if (plan_pick_ok(p, j, n_experts)) {
+        ok_bits |= 1u << j;
+        atomicOr(&s_mask[uint32_t(p[j]) * 8 + word], 1u << bit);
       }
     }
   }
-}
-
-// Each token's k rows, ascending (the order its experts were stacked in).
-__global__ void __launch_bounds__(256)
-plan_sort_kernel(int32_t* __restrict__ tok_rows, uint32_t tokens, uint32_t k) {
-  uint32_t t = blockIdx.x * 256 + threadIdx.x;
+  __syncthreads();
   if (t >= tokens) return;
-  int32_t* p = tok_rows + size_t(t) * k;
-  for (uint32_t i = 1; i < k; ++i) {
-    int32_t v = p[i];
-    int j = int(i) - 1;
-    while (j >= 0 && p[j] > v) { p[j + 1] = p[j]; --j; }
-    p[j + 1] = v;
+  int32_t rows[32];
+  for (uint32_t j = 0; j < k; ++j) {
+    int32_t row = -1;
+    if (ok_bits >> j & 1u) {
+      const uint32_t e = uint32_t(p[j]);
+      const uint32_t* m = s_mask + e * 8;
+      int32_t rank = __popc(m[word] & ((1u << bit) - 1u));
+      for (uint32_t w = 0; w < word; ++w) rank += __popc(m[w]);
+      row = expert_row0[e] + chunk_base[size_t(blockIdx.x) * n_experts + e] + rank;
+      row_tok[row] = int32_t(t);
+      row_wgt[row] = weight[size_t(t) * k + j];
+    }
+    // insertion into the ascending list (a pick without a row, -1, sorts first)
+    int i = int(j) - 1;
+    while (i >= 0 && rows[i] > row) { rows[i + 1] = rows[i]; --i; }
+    rows[i + 1] = row;
   }
+  for (uint32_t j = 0; j < k; ++j) tok_rows[size_t(t) * k + j] = rows[j];
 }
 
 // out[t, c..c+7] = sum_j fma(y[row_j, c..c+7], wgt[row_j], acc), rows ascending.
@@ -284,8 +291,8 @@ MB_API size_t mb_moe_plan_rows(size_t tokens, size_t k, size_t n_experts) {
 }
 
 MB_API size_t mb_moe_plan_workspace(size_t tokens, size_t k, size_t n_experts) {
-  (void)tokens; (void)k;
-  return n_experts * sizeof(int32_t);
+  (void)k;
+  return ((tokens + PLAN_CHUNK - 1) / PLAN_CHUNK) * n_experts * sizeof(int32_t);   // picks per (chunk of 256 tokens, expert)
 }
 
 MB_API int mb_moe_plan(mb_ctx* ctx, mb_stream stream_, const int32_t* idx, const float* weight, size_t tokens,
@@ -301,22 +308,18 @@ MB_API int mb_moe_plan(mb_ctx* ctx, mb_stream stream_, const int32_t* idx, const
   MB_REQUIRE(ctx, workspace_bytes >= mb_moe_plan_workspace(tokens, k, n_experts), "moe_plan: workspace too small");
   MB_REQUIRE(ctx, tokens * k < (1ull << 31), "moe_plan: exceeds i32 indexing");
   size_t m_cap = mb_moe_plan_rows(tokens, k, n_experts);
-  int32_t* counts = static_cast<int32_t*>(workspace);
-  plan_init_kernel<<<unsigned(std::min<size_t>((m_cap + 255) / 256, 592)), 256, 0, stream>>>(
-      row_tok, row_wgt, uint32_t(m_cap), tile_expert, uint32_t(m_cap / PLAN_PAD), tok_rows, uint32_t(tokens * k),
-      counts, uint32_t(n_experts));
-  MB_LAUNCH_OK(ctx);
+  int32_t* chunk_counts = static_cast<int32_t*>(workspace);
+  const unsigned chunks = unsigned((tokens + PLAN_CHUNK - 1) / PLAN_CHUNK);
   int* flag = ctx->flags_dev + MB_FLAG_PLAN_FAULT;
-  plan_count_kernel<<<unsigned((tokens + 255) / 256), 256, 0, stream>>>(idx, uint32_t(tokens), uint32_t(k),
-                                                                         uint32_t(n_experts), counts, flag);
+  plan_count_kernel<<<chunks, PLAN_CHUNK, n_experts * sizeof(int32_t), stream>>>(
+      idx, uint32_t(tokens), uint32_t(k), uint32_t(n_experts), chunk_counts, row_tok, row_wgt, uint32_t(m_cap), flag);
   MB_LAUNCH_OK(ctx);
-  plan_scan_kernel<<<1, 1024, 0, stream>>>(counts, uint32_t(n_experts), expert_rows, expert_row0, tile_expert,
-                                           uint32_t(m_cap / PLAN_PAD), n_tiles);
+  plan_scan_kernel<<<1, 1024, 0, stream>>>(chunk_counts, chunks, uint32_t(n_experts), expert_rows, expert_row0,
+                                           tile_expert, uint32_t(m_cap / PLAN_PAD), n_tiles);
   MB_LAUNCH_OK(ctx);
-  plan_place_kernel<<<unsigned(n_experts), 256, 0, stream>>>(idx, weight, uint32_t(tokens), uint32_t(k), expert_row0,
-                                                             row_tok, row_wgt, tok_rows);
-  MB_LAUNCH_OK(ctx);
-  plan_sort_kernel<<<unsigned((tokens + 255) / 256), 256, 0, stream>>>(tok_rows, uint32_t(tokens), uint32_t(k));
+  plan_place_kernel<<<chunks, PLAN_CHUNK, n_experts * 32, stream>>>(idx, weight, uint32_t(tokens), uint32_t(k),
+                                                                    uint32_t(n_experts), chunk_counts, expert_row0,
+                                                                    row_tok, row_wgt, tok_rows);
   MB_LAUNCH_OK(ctx);
   return MB_OK;
 }

@@ -99,26 +99,26 @@ quantize2_kernel(const T* __restrict__ x, uint32_t pairs, uint32_t k, mb_fastdiv
   const uint32_t kb = ((live ? pr : 0u) - row * rbp.d) * 2u;
   uint32_t s0 = 0, s1 = 0;
   if (live) {
-    float v[32];
     const int32_t src = gather ? gather[row] : int32_t(row);
     if (src < 0) {
-#pragma unroll
-      for (int i = 0; i < 32; ++i) v[i] = 0.0f;
+      // a pad row of a gathered plan: zero codes and zero scales, which is what zeros quantize to
+      codes[pr] = make_uint4(0u, 0u, 0u, 0u);
     } else {
+      float v[32];
       const T* p = x + size_t(uint32_t(src)) * k + kb * 16u;
       if (vec_ok) { load16(p, v); load16(p + 16, v + 16); }
       else { load16_scalar(p, v); load16_scalar(p + 16, v + 16); }
+      uint2 c0, c1;
+      if (RECIPE == MB_QUANT_RECIP) {
+        quant_block_recip(v, s0, c0);
+        quant_block_recip(v + 16, s1, c1);
+      } else {
+        const float s2 = RECIPE == MB_QUANT_ROWS ? rowscale[row] : input_scale;
+        quant_block_scaled(v, s2, s0, c0);
+        quant_block_scaled(v + 16, s2, s1, c1);
+      }
+      codes[pr] = make_uint4(c0.x, c0.y, c1.x, c1.y);
     }
-    uint2 c0, c1;
-    if (RECIPE == MB_QUANT_RECIP) {
-      quant_block_recip(v, s0, c0);
-      quant_block_recip(v + 16, s1, c1);
-    } else {
-      const float s2 = RECIPE == MB_QUANT_ROWS ? rowscale[row] : input_scale;
-      quant_block_scaled(v, s2, s0, c0);
-      quant_block_scaled(v + 16, s2, s1, c1);
-    }
-    codes[pr] = make_uint4(c0.x, c0.y, c1.x, c1.y);
   }
   const uint32_t w2 = s0 | (s1 << 8);
   if ((rbp.d & 1u) == 0) {
