@@ -188,6 +188,7 @@ attn_decode_kernel(const __grid_constant__ AttnParams p) {
     tma_prefetch_desc(&p.tmap_k);
     tma_prefetch_desc(&p.tmap_v);
   }
+  mb_grid_dependency_sync();      // shared-memory set-up above; Q, K and V are read from here on
   // Q rows r = qi * group + hg, zero beyond `rows`; 16 chunks of 16 bytes per row.
   for (uint32_t i = threadIdx.x; i < 16 * 16; i += DEC_THREADS) {
     const uint32_t r = i >> 4, c = i & 15;
@@ -309,6 +310,7 @@ attn_decode_kernel(const __grid_constant__ AttnParams p) {
 __global__ void __launch_bounds__(128)
 attn_combine_kernel(const float* __restrict__ part, __nv_bfloat16* __restrict__ out, uint32_t nq, uint32_t heads,
                     uint32_t kv_heads, uint32_t splits) {
+  mb_grid_dependency_sync();
   const uint32_t h = blockIdx.x % heads, qi = (blockIdx.x / heads) % nq, b = blockIdx.x / (heads * nq);
   const uint32_t group = heads / kv_heads, kvh = h / group, r = qi * group + h % group, d = threadIdx.x;
   const float* src = part + ((size_t(b) * kv_heads + kvh) * splits * 16 + r) * (D + 2);
@@ -538,10 +540,11 @@ MB_API int mb_attention(mb_ctx* ctx, mb_stream stream_, const void* q, const voi
       attr_dec[ctx->device & 15] = true;
     }
     dim3 grid(splits, unsigned(kv_heads), unsigned(batch));
-    attn_decode_kernel<<<grid, DEC_THREADS, DEC_SMEM, stream>>>(p);
+    MB_CUDA_OK(ctx, mb_launch_pdl(attn_decode_kernel, grid, dim3(DEC_THREADS), DEC_SMEM, stream, p));
     MB_LAUNCH_OK(ctx);
     if (splits > 1) {
-      attn_combine_kernel<<<unsigned(batch * nq * heads), 128, 0, stream>>>(p.part, p.out, p.nq, p.heads, p.kv_heads, splits);
+      MB_CUDA_OK(ctx, mb_launch_pdl(attn_combine_kernel, dim3(unsigned(batch * nq * heads)), dim3(128), 0, stream, p.part, p.out,
+                                    p.nq, p.heads, p.kv_heads, splits));
       MB_LAUNCH_OK(ctx);
     }
   } else if (!mb_attention_prefill_legacy()) {
@@ -632,10 +635,11 @@ MB_API int mb_attention_decode_static(mb_ctx* ctx, mb_stream stream_, const void
     attr_set[current] = true;
   }
   dim3 grid(splits, unsigned(kv_heads), unsigned(batch));
-  attn_decode_kernel<<<grid, DEC_THREADS, DEC_SMEM, stream>>>(p);
+  MB_CUDA_OK(ctx, mb_launch_pdl(attn_decode_kernel, grid, dim3(DEC_THREADS), DEC_SMEM, stream, p));
   MB_LAUNCH_OK(ctx);
   if (splits > 1) {
-    attn_combine_kernel<<<unsigned(batch * nq * heads), 128, 0, stream>>>(p.part, p.out, p.nq, p.heads, p.kv_heads, splits);
+    MB_CUDA_OK(ctx, mb_launch_pdl(attn_combine_kernel, dim3(unsigned(batch * nq * heads)), dim3(128), 0, stream, p.part, p.out,
+                                    p.nq, p.heads, p.kv_heads, splits));
     MB_LAUNCH_OK(ctx);
   }
   return MB_OK;

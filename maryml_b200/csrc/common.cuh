@@ -9,6 +9,7 @@
 #include <cstdarg>
 #include <cstdint>
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <mutex>
 #include <string>
@@ -91,6 +92,35 @@ inline bool mb_aligned(const void* p, size_t a) { return (reinterpret_cast<uintp
 // Device helpers
 // ---------------------------------------------------------------------------
 #if defined(__CUDACC__)
+
+// Programmatic dependent launch. A kernel launched through mb_launch_pdl may be set up on the
+// SMs (block scheduling, parameter and barrier set-up, TMEM allocation) while the kernel before
+// it in the stream is still draining; it calls mb_grid_dependency_sync() before its first access
+// to global memory, which waits until that kernel has completed and its writes are visible. The
+// same call lets the NEXT kernel start its own set-up. Between short kernels of a decode step
+// this hides most of the launch gap. MB_PDL=0 in the environment launches everything serialized.
+__device__ __forceinline__ void mb_grid_dependency_sync() {
+  asm volatile("griddepcontrol.launch_dependents;\n\tgriddepcontrol.wait;" ::: "memory");
+}
+inline bool mb_pdl_enabled() {
+  static const bool on = [] { const char* e = getenv("MB_PDL"); return !(e && e[0] == '0'); }();
+  return on;
+}
+template <typename... KArgs, typename... Args>
+inline cudaError_t mb_launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                                 Args&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = mb_pdl_enabled() ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
 
 __device__ __forceinline__ float mb_bf16_to_f32(__nv_bfloat16 v) { return __bfloat162float(v); }
 

@@ -311,6 +311,8 @@ gemm_tc5_kernel(const __grid_constant__ GemmParams p) {
   __syncthreads();
   fence_after_sync();
   const uint32_t tmem_base = *tmem_ptr_smem;
+  // everything above touched only this CTA's own shared and tensor memory; global memory from here on
+  mb_grid_dependency_sync();
 
   const uint32_t m_tiles = p.n_mtiles_dev ? uint32_t(*p.n_mtiles_dev) : p.m_tiles;
   const uint32_t total_tiles = m_tiles * p.n_tiles * p.splits;
@@ -744,6 +746,7 @@ __global__ void __launch_bounds__(256)
 splitk_reduce_kernel(const float4* __restrict__ partial, uint32_t splits, size_t plane4, uint32_t n4,
                      const float* __restrict__ rowscale, const float4* __restrict__ colscale, float alpha,
                      O* __restrict__ out) {
+  mb_grid_dependency_sync();
   size_t i = size_t(blockIdx.x) * 256 + threadIdx.x;
   if (i >= plane4) return;
   float4 acc = partial[i];
@@ -827,7 +830,7 @@ int launch(mb_ctx* ctx, cudaStream_t stream, const GemmParams& p, uint32_t max_t
   }
   unsigned grid = std::min<uint32_t>(max_tiles, uint32_t(ctx->sm_count));
   if (grid == 0) return MB_OK;
-  kern<<<grid, NUM_THREADS, C::SMEM_BYTES, stream>>>(p);
+  MB_CUDA_OK(ctx, mb_launch_pdl(kern, dim3(grid), dim3(NUM_THREADS), C::SMEM_BYTES, stream, p));
   MB_LAUNCH_OK(ctx);
   return MB_OK;
 }
@@ -969,15 +972,14 @@ int gemm_w4a4_common(mb_ctx* ctx, cudaStream_t stream, const uint8_t* a_codes, c
       const size_t plane4 = m * n / 4;
       const unsigned grid = unsigned((plane4 + 255) / 256);
       if (out_dtype == MB_DT_F32)
-        splitk_reduce_kernel<float><<<grid, 256, 0, stream>>>(static_cast<const float4*>(workspace), p.splits, plane4,
-                                                              uint32_t(n / 4), rowscale,
-                                                              reinterpret_cast<const float4*>(ex.colscale), alpha,
-                                                              static_cast<float*>(out));
+        MB_CUDA_OK(ctx, mb_launch_pdl(splitk_reduce_kernel<float>, dim3(grid), dim3(256), 0, stream,
+                                      static_cast<const float4*>(workspace), p.splits, plane4, uint32_t(n / 4), rowscale,
+                                      reinterpret_cast<const float4*>(ex.colscale), alpha, static_cast<float*>(out)));
       else
-        splitk_reduce_kernel<__nv_bfloat16><<<grid, 256, 0, stream>>>(static_cast<const float4*>(workspace), p.splits,
-                                                                      plane4, uint32_t(n / 4), rowscale,
-                                                                      reinterpret_cast<const float4*>(ex.colscale), alpha,
-                                                                      static_cast<__nv_bfloat16*>(out));
+        MB_CUDA_OK(ctx, mb_launch_pdl(splitk_reduce_kernel<__nv_bfloat16>, dim3(grid), dim3(256), 0, stream,
+                                      static_cast<const float4*>(workspace), p.splits, plane4, uint32_t(n / 4), rowscale,
+                                      reinterpret_cast<const float4*>(ex.colscale), alpha,
+                                      static_cast<__nv_bfloat16*>(out)));
       MB_LAUNCH_OK(ctx);
       return MB_OK;
     }

@@ -53,7 +53,11 @@ gemv_w4a16_kernel(const uint4* __restrict__ x, const uint4* __restrict__ codes, 
   for (uint32_t c = lane; c < chunks; c += 32) {
     const uint4 words = __ldg(crow + c);
     const uint32_t s01 = __ldg(srow + c);
-    const float s0 = mb_e4m3_to_f32(s01 & 0xFFu), s1 = mb_e4m3_to_f32(s01 >> 8);
+    // both scale bytes through one e4m3x2 -> f16x2 convert (f16 holds every E4M3 value exactly)
+    uint32_t sh2;
+    asm("cvt.rn.f16x2.e4m3x2 %0, %1;" : "=r"(sh2) : "h"(uint16_t(s01)));
+    const float2 s01f = __half22float2(*reinterpret_cast<__half2*>(&sh2));
+    const float s0 = s01f.x, s1 = s01f.y;
 #pragma unroll
     for (int r = 0; r < ROWS; ++r) {
       const uint4* xr = x + (size_t(r) * k + size_t(c) * 32) / 8;

@@ -86,6 +86,7 @@ element_kernel(const uint4* __restrict__ a, const uint4* __restrict__ b, uint4* 
 // out = bf16(a + bf16(b)) with b an f32 partial sum.
 __global__ void __launch_bounds__(256)
 add_f32_kernel(const uint4* __restrict__ a, const float4* __restrict__ b, uint4* __restrict__ out, size_t n8) {
+  mb_grid_dependency_sync();
   size_t i = size_t(blockIdx.x) * 256 + threadIdx.x;
   if (i >= n8) return;
   float x[8], o[8];
@@ -127,6 +128,7 @@ __global__ void __launch_bounds__(256)
 residual_norm_quantize_kernel(const uint4* __restrict__ resid, const float4* __restrict__ partial,
                               const uint4* __restrict__ gain, uint4* __restrict__ resid_out, uint32_t* __restrict__ codes,
                               uint8_t* __restrict__ scales, uint32_t width, float eps, uint32_t kchunks) {
+  mb_grid_dependency_sync();
   const uint32_t row = blockIdx.x, chunks = width / 8;
   const uint4* xr = resid + size_t(row) * chunks;
   float v[VEC][8];
@@ -200,6 +202,7 @@ __global__ void __launch_bounds__(256)
 rope_append_kernel(const uint4* __restrict__ qkv, uint4* __restrict__ q_out, uint4* __restrict__ k_cache,
                    uint4* __restrict__ v_cache, uint32_t batch, uint32_t t, uint32_t hq, uint32_t hkv, uint32_t d,
                    uint32_t past, uint32_t capacity, const float* __restrict__ inv_freq) {
+  mb_grid_dependency_sync();
   const uint32_t groups = d / 16;                      // eight-pair groups per head
   const uint32_t heads = hq + 2 * hkv;
   const size_t total = size_t(batch) * t * heads * groups;
@@ -281,9 +284,9 @@ MB_API int mb_add_f32(mb_ctx* ctx, mb_stream stream_, const void* a, const float
   MB_REQUIRE(ctx, n > 0 && n % 8 == 0, "add_f32: the element count must be a positive multiple of 8");
   MB_REQUIRE(ctx, mb_aligned(a, 16) && mb_aligned(b, 16) && mb_aligned(out, 16), "add_f32: 16-byte alignment");
   size_t n8 = n / 8;
-  add_f32_kernel<<<unsigned((n8 + 255) / 256), 256, 0, stream>>>(static_cast<const uint4*>(a),
-                                                                  reinterpret_cast<const float4*>(b),
-                                                                  static_cast<uint4*>(out), n8);
+  MB_CUDA_OK(ctx, mb_launch_pdl(add_f32_kernel, dim3(unsigned((n8 + 255) / 256)), dim3(256), 0, stream,
+                                static_cast<const uint4*>(a), reinterpret_cast<const float4*>(b),
+                                static_cast<uint4*>(out), n8));
   MB_LAUNCH_OK(ctx);
   return MB_OK;
 }
@@ -325,12 +328,9 @@ MB_API int mb_residual_norm_quantize(mb_ctx* ctx, mb_stream stream_, const void*
   const unsigned grid = unsigned(rows);
   // scale bytes of the K padding must decode to a finite value for the product that reads the plane
   if (width % 256 != 0) MB_CUDA_OK(ctx, cudaMemsetAsync(sf_tiled, 0, mb_sf_plane_bytes(rows, width), stream));
-  if (width <= 2048)
-    residual_norm_quantize_kernel<1><<<grid, 256, 0, stream>>>(xv, pv, gv, rv, cv, sf_tiled, uint32_t(width), eps, kc);
-  else if (width <= 4096)
-    residual_norm_quantize_kernel<2><<<grid, 256, 0, stream>>>(xv, pv, gv, rv, cv, sf_tiled, uint32_t(width), eps, kc);
-  else
-    residual_norm_quantize_kernel<4><<<grid, 256, 0, stream>>>(xv, pv, gv, rv, cv, sf_tiled, uint32_t(width), eps, kc);
+  auto kern = width <= 2048 ? residual_norm_quantize_kernel<1>
+              : width <= 4096 ? residual_norm_quantize_kernel<2> : residual_norm_quantize_kernel<4>;
+  MB_CUDA_OK(ctx, mb_launch_pdl(kern, dim3(grid), dim3(256), 0, stream, xv, pv, gv, rv, cv, sf_tiled, uint32_t(width), eps, kc));
   MB_LAUNCH_OK(ctx);
   return MB_OK;
 }
@@ -348,10 +348,10 @@ MB_API int mb_rope_append(mb_ctx* ctx, mb_stream stream_, const void* qkv, size_
   const size_t total = batch * t * (hq + 2 * hkv) * (d / 16);
   MB_REQUIRE(ctx, total < (1ull << 40) && batch * capacity < (1ull << 32) && past + t < (1ull << 31),
              "rope_append: extent too large");
-  rope_append_kernel<<<unsigned((total + 255) / 256), 256, 0, stream>>>(
-      static_cast<const uint4*>(qkv), static_cast<uint4*>(q_out), static_cast<uint4*>(k_cache),
-      static_cast<uint4*>(v_cache), uint32_t(batch), uint32_t(t), uint32_t(hq), uint32_t(hkv), uint32_t(d), uint32_t(past),
-      uint32_t(capacity), inv_freq);
+  MB_CUDA_OK(ctx, mb_launch_pdl(rope_append_kernel, dim3(unsigned((total + 255) / 256)), dim3(256), 0, stream,
+                                static_cast<const uint4*>(qkv), static_cast<uint4*>(q_out), static_cast<uint4*>(k_cache),
+                                static_cast<uint4*>(v_cache), uint32_t(batch), uint32_t(t), uint32_t(hq), uint32_t(hkv),
+                                uint32_t(d), uint32_t(past), uint32_t(capacity), inv_freq));
   MB_LAUNCH_OK(ctx);
   return MB_OK;
 }

@@ -93,6 +93,7 @@ __global__ void __launch_bounds__(QUANT_THREADS)
 quantize2_kernel(const T* __restrict__ x, uint32_t pairs, uint32_t k, mb_fastdiv rbp, float input_scale,
                  const float* __restrict__ rowscale, const int32_t* __restrict__ gather, uint4* __restrict__ codes,
                  uint8_t* __restrict__ scales, int tiled, uint32_t kchunks, int vec_ok) {
+  mb_grid_dependency_sync();
   const uint32_t pr = blockIdx.x * QUANT_THREADS + threadIdx.x;
   const bool live = pr < pairs;
   const uint32_t row = mb_fastdiv_q(live ? pr : 0u, rbp);
@@ -145,14 +146,14 @@ static void launch_quantize(cudaStream_t stream, int recipe, const T* x, size_t 
     const mb_fastdiv rbp = mb_fastdiv_make(uint32_t(k / 32));
     uint4* c4 = reinterpret_cast<uint4*>(codes);
     if (recipe == MB_QUANT_RECIP)
-      quantize2_kernel<T, MB_QUANT_RECIP><<<grid2, QUANT_THREADS, 0, stream>>>(x, pairs, uint32_t(k), rbp, input_scale,
-                                                                               rowscale, gather, c4, scales, tiled, kc, vec_ok);
+      mb_launch_pdl(quantize2_kernel<T, MB_QUANT_RECIP>, dim3(grid2), dim3(QUANT_THREADS), 0, stream, x, pairs, uint32_t(k), rbp,
+                    input_scale, rowscale, gather, c4, scales, tiled, kc, vec_ok);
     else if (recipe == MB_QUANT_ROWS)
-      quantize2_kernel<T, MB_QUANT_ROWS><<<grid2, QUANT_THREADS, 0, stream>>>(x, pairs, uint32_t(k), rbp, input_scale,
-                                                                              rowscale, gather, c4, scales, tiled, kc, vec_ok);
+      mb_launch_pdl(quantize2_kernel<T, MB_QUANT_ROWS>, dim3(grid2), dim3(QUANT_THREADS), 0, stream, x, pairs, uint32_t(k), rbp,
+                    input_scale, rowscale, gather, c4, scales, tiled, kc, vec_ok);
     else
-      quantize2_kernel<T, MB_QUANT_SCALED><<<grid2, QUANT_THREADS, 0, stream>>>(x, pairs, uint32_t(k), rbp, input_scale,
-                                                                                rowscale, gather, c4, scales, tiled, kc, vec_ok);
+      mb_launch_pdl(quantize2_kernel<T, MB_QUANT_SCALED>, dim3(grid2), dim3(QUANT_THREADS), 0, stream, x, pairs, uint32_t(k), rbp,
+                    input_scale, rowscale, gather, c4, scales, tiled, kc, vec_ok);
     return;
   }
   const uint32_t blocks = uint32_t(rows * (k / 16));
