@@ -267,23 +267,55 @@ def run_ours(args, rank, world, local_rank):
     for k in acts:
         h_x[k].copy_(acts[k])
     h_y = [torch.empty(M, q.n(), dtype=torch.bfloat16).pin_memory() for q in weights]
-    d_x = {k: torch.empty_like(acts[k]) for k in acts}
+    # Three streams, as a serving host would run it: activations of the next projection travel up while
+    # the current one computes and the previous result travels down (PCIe is full duplex). Device input
+    # buffers are double-buffered per projection; every copy and every projection of every step is inside
+    # the timed region, and the region ends only when the last result has landed in host memory.
+    n_proj = len(weights)
+    d_x2 = [[torch.empty(M, q.k(), dtype=torch.bfloat16, device=dev) for q in weights] for _ in range(2)]
+    s_in, s_cmp, s_out = torch.cuda.Stream(), torch.cuda.Stream(), torch.cuda.Stream()
+    ev_in = [[torch.cuda.Event() for _ in range(n_proj)] for _ in range(2)]
+    ev_cmp = [[torch.cuda.Event() for _ in range(n_proj)] for _ in range(2)]
+    ev_out = [torch.cuda.Event() for _ in range(n_proj)]
+    e2e_count = [0]
 
     def e2e_step():
-        for q, out, hy in zip(weights, outs, h_y):
-            k = q.k()
-            d_x[k].copy_(h_x[k], non_blocking=True)
-            y = q.project(d_x[k], mb.PromptLane.W4A4)
-            hy.copy_(y.view(M, q.n()), non_blocking=True)
+        slot = e2e_count[0] & 1
+        first = e2e_count[0] < 2
+        e2e_count[0] += 1
+        for i, (q, hy) in enumerate(zip(weights, h_y)):
+            with torch.cuda.stream(s_in):
+                if not first:
+                    s_in.wait_event(ev_cmp[slot][i])          # the projection that last read this buffer is done
+                d_x2[slot][i].copy_(h_x[q.k()], non_blocking=True)
+                ev_in[slot][i].record(s_in)
+            with torch.cuda.stream(s_cmp):
+                s_cmp.wait_event(ev_in[slot][i])
+                y = q.project(d_x2[slot][i], mb.PromptLane.W4A4)
+                ev_cmp[slot][i].record(s_cmp)
+            with torch.cuda.stream(s_out):
+                s_out.wait_event(ev_cmp[slot][i])
+                hy.copy_(y.view(M, q.n()), non_blocking=True)
+                y.record_stream(s_out)
+                ev_out[i].record(s_out)
 
-    e2e_steps = max(2, min(args.steps, 5))
+    def e2e_join():
+        for st in (s_in, s_cmp, s_out):
+            stream.wait_stream(st)
+
+    e2e_steps = max(4, min(args.steps, 8))
     e2e_step()
+    e2e_step()
+    e2e_join()
     barrier()
     s0 = torch.cuda.Event(enable_timing=True)
     s1 = torch.cuda.Event(enable_timing=True)
     s0.record(stream)
+    for st in (s_in, s_cmp, s_out):
+        st.wait_stream(stream)
     for _ in range(e2e_steps):
         e2e_step()
+    e2e_join()
     s1.record(stream)
     barrier()
     e2e_ms = s0.elapsed_time(s1)

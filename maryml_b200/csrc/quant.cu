@@ -10,6 +10,9 @@
 namespace {
 
 constexpr int QUANT_THREADS = 256;
+#ifndef QUANT_MIN_BLOCKS
+#define QUANT_MIN_BLOCKS 5   // blocks per SM the two-block kernel is compiled for (register cap 48)
+#endif
 
 __device__ __forceinline__ void load16(const __nv_bfloat16* p, float* v) {
   const uint4* q = reinterpret_cast<const uint4*>(p);
@@ -89,7 +92,7 @@ quantize_kernel(const T* __restrict__ x, uint32_t blocks, uint32_t k, mb_fastdiv
 // arithmetic, the parameter loads and the control flow are paid once per 32 values, the codes
 // leave as one 128-bit store and two lanes fill a 32-bit word of scale bytes.
 template <typename T, int RECIPE>
-__global__ void __launch_bounds__(QUANT_THREADS)
+__global__ void __launch_bounds__(QUANT_THREADS, QUANT_MIN_BLOCKS)
 quantize2_kernel(const T* __restrict__ x, uint32_t pairs, uint32_t k, mb_fastdiv rbp, float input_scale,
                  const float* __restrict__ rowscale, const int32_t* __restrict__ gather, uint4* __restrict__ codes,
                  uint8_t* __restrict__ scales, int tiled, uint32_t kchunks, int vec_ok) {

@@ -51,6 +51,22 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
       : "memory");
   return ok != 0;
 }
+// The same with a suspend-time hint (nanoseconds): the thread may sleep in hardware until the phase
+// completes or the hint runs out, instead of coming back to poll. The retry loops use it so that
+// warps that wait most of the time (the epilogue of a long-K tile) do not burn issue slots and
+// power that the tensor pipe needs under the board's power cap.
+constexpr uint32_t WAIT_HINT_NS = 20000;
+__device__ __forceinline__ bool mbar_try_wait_hint(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity), "r"(WAIT_HINT_NS)
+      : "memory");
+  return ok != 0;
+}
 
 // Cycle budget of one wait (about a second at B200 clocks). A wait that runs out
 // sets the CTA's abort word and the context's timeout flag and returns false;
@@ -62,7 +78,7 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
   if (mbar_try_wait(bar, parity)) return true;
   long long t0 = clock64();
   for (;;) {
-    if (mbar_try_wait(bar, parity)) return true;
+    if (mbar_try_wait_hint(bar, parity)) return true;
     if (*abort_smem) return false;
     if (clock64() - t0 > WAIT_LIMIT_CYCLES) {
       *abort_smem = 1;
@@ -199,12 +215,23 @@ __device__ __forceinline__ bool mbar_try_wait_cluster(uint32_t bar, uint32_t par
       : "memory");
   return ok != 0;
 }
+__device__ __forceinline__ bool mbar_try_wait_cluster_hint(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2, %3;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity), "r"(WAIT_HINT_NS)
+      : "memory");
+  return ok != 0;
+}
 __device__ __forceinline__ bool mbar_wait_cluster(uint32_t bar, uint32_t parity, volatile int* abort_smem,
                                                   int* flag_gmem, int code) {
   if (mbar_try_wait_cluster(bar, parity)) return true;
   long long t0 = clock64();
   for (;;) {
-    if (mbar_try_wait_cluster(bar, parity)) return true;
+    if (mbar_try_wait_cluster_hint(bar, parity)) return true;
     if (*abort_smem) return false;
     if (clock64() - t0 > WAIT_LIMIT_CYCLES) {
       *abort_smem = 1;
