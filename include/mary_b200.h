@@ -82,6 +82,12 @@ enum {
  * (src/models/inkling/rawcuda.rs:31-80). One per device and host thread. */
 int mb_ctx_create(int device, mb_ctx** out);
 void mb_ctx_destroy(mb_ctx* ctx);
+/* The persistent GEMM kernels launch one CTA (or CTA pair) per SM and walk their tiles in a fixed
+ * round-robin; a collective that runs beside them on another stream (the all-reduce of the previous
+ * chunk of a prompt, src/models/inkling/tpcomm.rs:1453-1467) holds some SMs for its whole duration and
+ * would stall the CTAs that were to run there. `sms` > 0 makes those kernels use at most that many SMs,
+ * 0 restores all of them. No counterpart in the reference, whose GEMMs are not persistent. */
+int mb_ctx_set_sm_limit(mb_ctx* ctx, int sms);
 const char* mb_last_error(mb_ctx* ctx);
 const char* mb_version(void);
 /* Reads and clears the device status words (bounded-wait timeouts, non-finite

@@ -28,6 +28,7 @@ _vp, _sz, _f, _i = C.c_void_p, C.c_size_t, C.c_float, C.c_int
 SIGNATURES = {
     "mb_ctx_create": (_i, [_i, C.POINTER(_vp)]),
     "mb_ctx_destroy": (None, [_vp]),
+    "mb_ctx_set_sm_limit": (_i, [_vp, _i]),
     "mb_last_error": (C.c_char_p, [_vp]),
     "mb_version": (C.c_char_p, []),
     "mb_check_flags": (_i, [_vp, _vp, C.POINTER(C.c_int32)]),

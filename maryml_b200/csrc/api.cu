@@ -33,6 +33,13 @@ MB_API void mb_ctx_destroy(mb_ctx* ctx) {
   delete ctx;
 }
 
+MB_API int mb_ctx_set_sm_limit(mb_ctx* ctx, int sms) {
+  MB_REQUIRE(ctx, ctx != nullptr, "set_sm_limit: null context");
+  MB_REQUIRE(ctx, sms >= 0 && sms <= ctx->sm_count, "set_sm_limit: 0 (all) .. %d SMs, got %d", ctx->sm_count, sms);
+  ctx->sm_limit = sms;
+  return MB_OK;
+}
+
 MB_API const char* mb_last_error(mb_ctx* ctx) {
   if (!ctx) return "no context";
   std::lock_guard<std::mutex> g(ctx->mu);

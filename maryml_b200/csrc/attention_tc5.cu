@@ -127,7 +127,10 @@ attn_prefill_tc5_kernel(const __grid_constant__ AttnParams p) {
     int stage = 0;
     uint32_t phase = 0;
     for (uint32_t j = 0; j < n_tiles; ++j) {
-      if (!mbar_wait(kv_empty(stage), phase ^ 1u, abort_smem, tflag, 31)) break;
+      if (!mbar_wait(kv_empty(stage), phase ^ 1u, abort_smem, tflag, 31)) {
+        if (tflag && lane == 0) atomicCAS(tflag + 7, 0, int(j | n_tiles << 10 | (p.q0 >> 6) << 20));
+        break;
+      }
       if (elect_one()) {
         const uint32_t s0 = base + stage * KV_STAGE;
         const int key0 = int(j * BC);
@@ -149,8 +152,11 @@ attn_prefill_tc5_kernel(const __grid_constant__ AttnParams p) {
     int stage = 0;                 // stage of key tile j (for S); PV(j-1) uses the previous stage
     uint32_t phase = 0;
     int pstage = 0;
+    uint32_t mma_where = 0, mma_j = 0;     // the wait the issuer was in, for the status block of a run-out wait
     for (uint32_t j = 0; ok && j <= n_tiles; ++j) {
+      mma_j = j;
       if (j < n_tiles) {
+        mma_where = 33;
         if (!mbar_wait(kv_full(stage), phase, abort_smem, tflag, 33)) { ok = false; break; }
       }
       // scores of tile j first (they only need the group to have READ the previous scores),
@@ -158,6 +164,7 @@ attn_prefill_tc5_kernel(const __grid_constant__ AttnParams p) {
       for (int t = 0; t < 2 && ok; ++t) {
         if (j < n_tiles) {
           // S(t, j): previous S_t read by its softmax group
+          mma_where = 36 + 64 * t;
           if (!mbar_wait(s_free(t), (j & 1u) ^ 1u, abort_smem, tflag, 36)) { ok = false; break; }
           fence_after_sync();
           if (elect_one()) {
@@ -179,6 +186,7 @@ attn_prefill_tc5_kernel(const __grid_constant__ AttnParams p) {
         if (j > 0) {
           // O_t += P_t(j-1) V(j-1): the group has written P_t (and rescaled O_t if it had to)
           const uint32_t u = j - 1;
+          mma_where = 34 + 64 * t;
           if (!mbar_wait(p_full(t), u & 1u, abort_smem, tflag, 34)) { ok = false; break; }
           fence_after_sync();
           if (elect_one()) {
@@ -198,6 +206,7 @@ attn_prefill_tc5_kernel(const __grid_constant__ AttnParams p) {
       if (j < n_tiles) { if (++stage == STAGES) { stage = 0; phase ^= 1u; } }
     }
     if (!ok) {
+      if (tflag && lane == 0) atomicCAS(tflag + 5, 0, int(1u << 30 | mma_where << 20 | mma_j));
       if (elect_one()) umma_commit(drain_bar);
       __syncwarp();
       long long t0 = clock64();
@@ -216,12 +225,15 @@ attn_prefill_tc5_kernel(const __grid_constant__ AttnParams p) {
     uint8_t* p_rows = gen + (p_smem - base) + t * 2 * P_BYTES + r * 128;
     float m = -INFINITY, l = 0.0f;       // m: the maximum this row currently subtracts (may lag, see header)
     bool ok = true;
+    uint32_t sm_where = 0, sm_j = 0;
     for (uint32_t j = 0; ok && j < n_tiles; ++j) {
+      sm_j = j;
       const int kabs = int(j * BC);
       int vis = int(p.keys) - kabs;
       if (p.causal) vis = min(vis, qpos + 1 - kabs);
       bool pv_waited = j == 0;           // whether PV(j-1) is known to be complete
       const bool full_tile = __all_sync(0xFFFFFFFFu, vis >= BC);   // no mask work away from the diagonal
+      sm_where = 37;
       if (!mbar_wait(s_full(t), j & 1u, abort_smem, tflag, 37)) { ok = false; break; }
       fence_after_sync();
       // pass 1: the row maximum of this tile
@@ -245,6 +257,7 @@ attn_prefill_tc5_kernel(const __grid_constant__ AttnParams p) {
         m = mt;
       } else if (__any_sync(0xFFFFFFFFu, mt > m + 8.0f)) {
         // some row of this warp outgrew its maximum: bring O_t (and l) of the whole warp to the new maxima
+        sm_where = 38;
         if (!mbar_wait(pv_done(t), (j - 1u) & 1u, abort_smem, tflag, 38)) { ok = false; break; }
         pv_waited = true;
         fence_after_sync();
@@ -302,13 +315,19 @@ attn_prefill_tc5_kernel(const __grid_constant__ AttnParams p) {
         }
       }
       l += sum;
+      // PV(j-1) must be complete before P(j) is published (never a stall in practice: it was issued a
+      // whole softmax pass ago). The order matters: a parity wait tells apart only two neighbouring
+      // phases, so this group may not complete phase j of p_full before the issuer has consumed phase
+      // j-1 (it has, once PV(j-1) is committed), nor may the issuer commit PV(j) before this group has
+      // consumed pv_done of j-1. With the arrive first, an issuer held up between its two query tiles
+      // (waiting for the other group's S buffer) found p_full two phases ahead and waited for ever.
+      sm_where = 39;
+      if (!pv_waited && !mbar_wait(pv_done(t), (j - 1u) & 1u, abort_smem, tflag, 39)) { ok = false; break; }
       fence_proxy_async();                                 // generic-proxy writes of P before the MMA reads them
       fence_before_sync();                                 // and any O_t rescale before the next PV product
       mbar_arrive(p_full(t));
-      // PV(j-1) must be complete before the next tile reuses its P buffer (never a stall in
-      // practice: it was issued a whole softmax pass ago), and the wait keeps the phase in step
-      if (!pv_waited && !mbar_wait(pv_done(t), (j - 1u) & 1u, abort_smem, tflag, 39)) { ok = false; break; }
     }
+    if (!ok && tflag && r == 0 && t == 0) atomicCAS(tflag + 6, 0, int(1u << 30 | sm_where << 20 | sm_j));
     if (ok && n_tiles > 0) ok = mbar_wait(pv_done(t), (n_tiles - 1u) & 1u, abort_smem, tflag, 40);
     fence_after_sync();
     const float inv = l > 0.0f ? 1.0f / l : 0.0f;

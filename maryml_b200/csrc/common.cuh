@@ -29,6 +29,7 @@ enum : int {
 struct mb_ctx {
   int device = 0;
   int sm_count = 148;
+  int sm_limit = 0;                  // persistent kernels use at most this many SMs (0 = all): room for a collective
   int* flags_dev = nullptr;          // MB_FLAG_COUNT ints
   std::string last_error;
   std::mutex mu;

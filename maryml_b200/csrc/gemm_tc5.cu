@@ -828,7 +828,8 @@ int launch(mb_ctx* ctx, cudaStream_t stream, const GemmParams& p, uint32_t max_t
     MB_CUDA_OK(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES));
     attr_set[ctx->device & 15] = true;
   }
-  unsigned grid = std::min<uint32_t>(max_tiles, uint32_t(ctx->sm_count));
+  const int sms = ctx->sm_limit > 0 ? std::min(ctx->sm_limit, ctx->sm_count) : ctx->sm_count;
+  unsigned grid = std::min<uint32_t>(max_tiles, uint32_t(sms));
   if (grid == 0) return MB_OK;
   MB_CUDA_OK(ctx, mb_launch_pdl(kern, dim3(grid), dim3(NUM_THREADS), C::SMEM_BYTES, stream, p));
   MB_LAUNCH_OK(ctx);
@@ -873,7 +874,9 @@ int launch_pair(mb_ctx* ctx, cudaStream_t stream, Gemm2Params& pp) {
     clusters[d] = n;
   }
   const uint32_t tiles = pp.m_pairs * pp.g.n_tiles;
-  const unsigned grid = 2u * std::min<uint32_t>(tiles, uint32_t(clusters[d]));
+  uint32_t pairs = uint32_t(clusters[d]);
+  if (ctx->sm_limit > 0) pairs = std::min<uint32_t>(pairs, std::max(1, ctx->sm_limit / 2));
+  const unsigned grid = 2u * std::min<uint32_t>(tiles, pairs);
   gemm_tc5_pair_kernel<<<grid, NUM_THREADS, Cfg2::SMEM_BYTES, stream>>>(pp);
   MB_LAUNCH_OK(ctx);
   return MB_OK;

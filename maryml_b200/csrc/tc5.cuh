@@ -77,12 +77,21 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
                                           int code) {
   if (mbar_try_wait(bar, parity)) return true;
   long long t0 = clock64();
+  unsigned long long g0;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(g0));
   for (;;) {
     if (mbar_try_wait_hint(bar, parity)) return true;
     if (*abort_smem) return false;
     if (clock64() - t0 > WAIT_LIMIT_CYCLES) {
       *abort_smem = 1;
-      if (flag_gmem) atomicCAS(flag_gmem, 0, code);
+      if (flag_gmem && atomicCAS(flag_gmem, 0, code) == 0) {
+        // the first wait of the context to run out also leaves where and how long: words 3 and 4 of the
+        // status block = wall time waited in microseconds, block index (x | y << 12 | z << 24)
+        unsigned long long g1;
+        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(g1));
+        flag_gmem[3] = int((g1 - g0) / 1000ull);
+        flag_gmem[4] = int(blockIdx.x | (blockIdx.y << 12) | (blockIdx.z << 24));
+      }
       return false;
     }
   }

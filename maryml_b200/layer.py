@@ -9,6 +9,7 @@ one SUM all-reduce of the f32 partial after o and after down, before the residua
 """
 import ctypes as C
 import math
+import os
 
 import numpy as np
 import torch
@@ -38,9 +39,10 @@ def add(a, b):
     return out
 
 
-def add_f32(a, b_f32):
+def add_f32(a, b_f32, out=None):
     ctx = context(a.device.index)
-    out = torch.empty_like(a)
+    if out is None:
+        out = torch.empty_like(a)
     ctx.check(lib.mb_add_f32(ctx.handle, _stream(), _p(a), _p(b_f32), a.numel(), _p(out)))
     return out
 
@@ -289,11 +291,11 @@ class DecoderLayer:
             self.group.all_reduce_f32(partial)
         return partial
 
-    def _forward_fused(self, x, batch, past, k_cache, v_cache):
+    def _forward_fused(self, x, batch, past, k_cache, v_cache, out=None, after_rope=None, before_rope=None):
         """The same layer in fewer passes: norm + quantize in one kernel, q|k|v as one product,
         rotation + cache append in one kernel, gate/up + SwiGLU + quantize in one product, the
         residual add folded into the next norm. Every value is computed by the arithmetic of the
-        separate kernels."""
+        separate kernels. `before_rope` / `after_rope` are hooks of the chunked prompt path."""
         cfg = self.cfg
         D = cfg.head_dim
         t = x.shape[0] // batch
@@ -303,8 +305,12 @@ class DecoderLayer:
         qkv = nv.gemm_w4a4_stacked(xq[0], xq[1], self.wqkv, xq[2])
         q = torch.empty((batch, t, self.local_heads, D), dtype=torch.bfloat16, device=dev)
         assert k_cache.is_contiguous() and v_cache.is_contiguous()
+        if before_rope is not None:
+            before_rope()
         ctx.check(lib.mb_rope_append(ctx.handle, _stream(), _p(qkv), batch, t, self.local_heads, self.local_kv_heads, D,
                                      past, _p(self.inv_freq), _p(q), _p(k_cache), _p(v_cache), k_cache.shape[1]))
+        if after_rope is not None:
+            after_rope()
         keys = past + t
         a = flash_attention(q, k_cache[:, :keys].contiguous() if keys != k_cache.shape[1] else k_cache,
                             v_cache[:, :keys].contiguous() if keys != v_cache.shape[1] else v_cache,
@@ -317,16 +323,66 @@ class DecoderLayer:
         act = nv.gemm_w4a4_stacked(nq_[0], nq_[1], self.wgu, nq_[2],
                                    epilogue=_lib.EPI_SWIGLU_ROUNDED | _lib.EPI_QUANT_SCALED)
         if self.fused is not None and batch * t <= self.fused.t_max:
-            return self.fused.gemm_reduce_residual(act[0], act[1], self.wdown, residual, batch * t)
+            y = self.fused.gemm_reduce_residual(act[0], act[1], self.wdown, residual, batch * t)
+            if out is not None:
+                out.copy_(y)
+                return out
+            return y
         partial = self._project((act[0], act[1], batch * t), self.wdown, out_dtype=torch.float32)
         if self.group is not None and self.tp.is_split():
             self.group.all_reduce_f32(partial)
-        return add_f32(residual, partial)
+        return add_f32(residual, partial, out=out)
+
+    # rows per chunk of the pipelined prompt path, and the SMs left to the all-reduce that runs beside the products
+    PROMPT_CHUNK = 2048
+    COLLECTIVE_SMS = 20
+
+    def forward_chunked(self, x, past, k_cache, v_cache, chunk=None):
+        """One long prompt (batch 1) as a pipeline of token chunks on two streams: while chunk c's f32
+        all-reduce crosses NVLink, chunk c + 1 runs its products and attention. Causal attention
+        only needs the keys of earlier chunks, which their rope + append passes wrote (ordered by
+        events). Per query row the arithmetic is that of the unchunked layer."""
+        chunk = chunk or self.PROMPT_CHUNK
+        rows = x.shape[0]
+        assert rows % chunk == 0 and chunk % 256 == 0, "chunks are whole 256-row attention tiles"
+        n = rows // chunk
+        main = torch.cuda.current_stream()
+        if getattr(self, "_side", None) is None:
+            self._side = [torch.cuda.Stream(device=x.device), torch.cuda.Stream(device=x.device)]
+        out = torch.empty_like(x)
+        ev_rope = [torch.cuda.Event() for _ in range(n)]
+        ctx = context(x.device.index)
+        split = self.group is not None and self.tp.is_split()
+        if split:
+            sms = torch.cuda.get_device_properties(x.device).multi_processor_count
+            ctx.check(lib.mb_ctx_set_sm_limit(ctx.handle, sms - self.COLLECTIVE_SMS))
+        try:
+            for st in self._side:
+                st.wait_stream(main)
+            for c in range(n):
+                st = self._side[c & 1]
+                with torch.cuda.stream(st):
+                    before = (lambda c=c, st=st: st.wait_event(ev_rope[c - 1])) if c > 0 else None
+                    after = lambda c=c, st=st: ev_rope[c].record(st)
+                    self._forward_fused(x[c * chunk:(c + 1) * chunk], 1, past + c * chunk, k_cache, v_cache,
+                                        out=out[c * chunk:(c + 1) * chunk], after_rope=after, before_rope=before)
+            for st in self._side:
+                main.wait_stream(st)
+        finally:
+            if split:
+                ctx.check(lib.mb_ctx_set_sm_limit(ctx.handle, 0))
+        return out
 
     def forward(self, x, batch, past, k_cache, v_cache):
         """x [batch * t, hidden] bf16 (t new tokens per sequence, sequence-major). Caches
         [batch, capacity, local_kv_heads, D]; the new keys/values land at [past, past + t)."""
         if self.fuse:
+            # the pipelined prompt path is opt-in (MB_TP_PROMPT_CHUNK=rows): at two GPUs the all-reduce is too
+            # short to pay for the extra launches (1.58 vs 1.50 ms on the 8192-token prompt)
+            chunk = int(os.environ.get("MB_TP_PROMPT_CHUNK", 0))
+            if (batch == 1 and chunk > 0 and x.shape[0] >= 2 * chunk and x.shape[0] % chunk == 0
+                    and self.group is not None and self.tp.is_split()):
+                return self.forward_chunked(x, past, k_cache, v_cache, chunk)
             return self._forward_fused(x, batch, past, k_cache, v_cache)
         cfg = self.cfg
         D = cfg.head_dim

@@ -80,6 +80,20 @@ def _worker(rank, world, port, out_path, fused=False):
         assert rc == 0, flags
     y = y.clone()
     torch.cuda.synchronize()
+    if not fused:
+        # a prompt as a pipeline of chunks on two streams (all-reduces of the same communicator issued
+        # from both) against one pass over the whole prompt, on every rank
+        pt, ppast = 512, 0
+        px, pk, pv = _inputs(orc, cfg, 1, pt, ppast + pt)
+        pk, pv = pk[:, :, kv.start:kv.stop].contiguous().cuda(), pv[:, :, kv.start:kv.stop].contiguous().cuda()
+        pk2, pv2 = pk.clone(), pv.clone()
+        whole = L._forward_fused(px.cuda(), 1, ppast, pk, pv)
+        parts = L.forward_chunked(px.cuda(), ppast, pk2, pv2, chunk=256)
+        torch.cuda.synchronize()
+        a, b = whole.float(), parts.float()
+        rms = a.pow(2).mean().sqrt()
+        assert (a - b).abs().max() <= 2e-2 * rms, float((a - b).abs().max() / rms)
+        assert torch.equal(pk.view(torch.int16), pk2.view(torch.int16))
     if rank == 0:
         np.save(out_path, y.float().cpu().numpy())
     store.set(f"done{rank}", b"1")
