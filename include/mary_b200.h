@@ -188,6 +188,12 @@ int mb_nvfp4_gemm_w4a4_stacked(mb_ctx* ctx, mb_stream stream, const uint8_t* a_c
  * (the W4A16 lane, src/nn/nvfp4_gemm.rs:93-197: scale2 applied once to the accumulator). */
 int mb_bf16_gemm(mb_ctx* ctx, mb_stream stream, const void* a_bf16, const void* b_bf16, float alpha, size_t m,
                  size_t n, size_t k, void* out, int out_dtype);
+/* The same product when the output has few tiles and K is long (the router projection
+ * src/models/k3/router.rs:300-340 `Router::logits`: [tokens, hidden] x [experts, hidden]^T): K slices into f32 planes of
+ * `workspace`, summed in slice order. mb_bf16_gemm_splitk_workspace gives the bytes, 0 = not split. */
+size_t mb_bf16_gemm_splitk_workspace(size_t m, size_t n, size_t k);
+int mb_bf16_gemm_splitk(mb_ctx* ctx, mb_stream stream, const void* a_bf16, const void* b_bf16, float alpha, size_t m,
+                        size_t n, size_t k, void* out, int out_dtype, void* workspace, size_t workspace_bytes);
 
 /* ---- MoE routing and permutation -------------------------------------------------- */
 /* Router::scores/select/combine_weights/normalize, softmax branch

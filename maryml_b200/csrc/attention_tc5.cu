@@ -4,10 +4,16 @@
 //
 //   S_t  = Q_t K^T      tcgen05.mma kind::f16, 128 x 64 x 128, accumulator in TMEM
 //   P_t  = 2^(S_t*c - m) one softmax thread per query row reads its row of S_t from
-//                        TMEM (no cross-thread reduction), writes bf16 P_t to shared
-//                        memory in the K-major 128B-swizzled layout the MMA reads
-//   O_t += P_t V         tcgen05.mma, 128 x 128 x 64, V read MN-major straight from the
-//                        TMA tile; O_t stays in TMEM over the whole key loop
+//                        TMEM (no cross-thread reduction) and writes bf16 P_t back over
+//                        the first 32 columns of the same score buffer (tcgen05.st)
+//   O_t += P_t V         tcgen05.mma with the A operand in TMEM, 128 x 128 x 64, V read
+//                        MN-major straight from the TMA tile; O_t stays in TMEM over the
+//                        whole key loop
+//
+// Keeping P in tensor memory matters because the kernel is bound by shared-memory bandwidth:
+// per 64-key tile pair the score products read 96 KB (Q is re-read for every 64 keys), a P
+// tile in shared memory cost 32 KB to write and 32 KB to read back, V is 32 KB and the TMA
+// fill 32 KB, against 128 B/clk. Without the P round trip the five K/V stages also fit.
 //
 // The running maximum a row subtracts is allowed to lag the true one by up to 2^8: O_t in
 // TMEM is rescaled (tcgen05.ld, multiply, tcgen05.st) only when a tile raises a row's maximum
@@ -15,8 +21,8 @@
 //
 // Warp roles: 0 = TMA producer (Q once, K/V ring), 1 = MMA issuer, 2-5 and 6-9 = the two
 // softmax groups (one per query tile) that alternate on the tensor core: while one group
-// exponentiates, the other group's products run. TMEM: S0, S1 (64 columns each), PV0, PV1
-// (128 each). Algorithmic work: 4 * nq * keys * 128 flop per head, half under the mask.
+// exponentiates, the other group's products run. TMEM: two score buffers of 64 columns per
+// query tile (tile j + 1's scores land while tile j's buffer still holds P), PV0, PV1 (128 each). Algorithmic work: 4 * nq * keys * 128 flop per head, half under the mask.
 // Every mbarrier wait is bounded.
 #include "attention.cuh"
 
@@ -29,12 +35,25 @@ constexpr int BC = 64;                         // keys per tile
 constexpr int QT = 128;                        // query rows per tile (two tiles per CTA)
 constexpr int HALF = BC * 128;                 // one 64-dim half of a K or V tile: 8 KB
 constexpr int KV_STAGE = 4 * HALF;             // K lo, K hi, V lo, V hi: 32 KB
-constexpr int STAGES = 3;
+constexpr int STAGES = 5;
 constexpr int Q_BYTES = 2 * QT * D * 2;        // 64 KB: [tile][half][128 rows][64 dims]
-constexpr int P_BYTES = QT * BC * 2;           // 16 KB per query tile
-constexpr int SMEM = STAGES * KV_STAGE + Q_BYTES + 4 * P_BYTES + 1024 + 256;   // P double-buffered per query tile
+constexpr int SMEM = STAGES * KV_STAGE + Q_BYTES + 1024 + 256;
 constexpr int THREADS = 320;
-constexpr int S_COL0 = 0, S_COL1 = 64, PV_COL0 = 128, PV_COL1 = 256, TMEM_COLS = 512;
+constexpr int S_COL0 = 0, S_COL1 = 128, S_BUF = 64, PV_COL0 = 256, PV_COL1 = 384, TMEM_COLS = 512;
+
+// Development aid (-DMB_ATTN_PROFILE): cycles per phase, summed over CTAs. Slots: 0 issuer waits K/V, 1 issuer waits
+// P of tile 0, 2 issuer waits P of tile 1, 3 whole kernel, 4 key tiles; first warp of softmax group 0: 5 waits scores,
+// 6 score load + maximum, 8 exponentials, 9 P store, 10 waits PV, 11 rescales taken.
+#ifdef MB_ATTN_PROFILE
+__device__ unsigned long long g_attn_prof[16];
+#define APROF_T0() long long aprof_t0_ = clock64()
+#define APROF_LAP(slot) do { const long long n_ = clock64(); if ((threadIdx.x & 31) == 0) atomicAdd(&g_attn_prof[slot], (unsigned long long)(n_ - aprof_t0_)); aprof_t0_ = n_; } while (0)
+#define APROF_COUNT(slot) do { if ((threadIdx.x & 31) == 0) atomicAdd(&g_attn_prof[slot], 1ull); } while (0)
+#else
+#define APROF_T0() do {} while (0)
+#define APROF_LAP(slot) do {} while (0)
+#define APROF_COUNT(slot) do {} while (0)
+#endif
 
 // bf16 A and B, f32 accumulate, M = 128; B either K-major (0) or MN-major (1).
 __host__ __device__ constexpr uint32_t idesc(uint32_t n, uint32_t b_mn_major) {
@@ -58,22 +77,23 @@ __device__ __forceinline__ uint32_t pack2(float lo, float hi) {
 
 __global__ void __launch_bounds__(THREADS, 1)
 attn_prefill_tc5_kernel(const __grid_constant__ AttnParams p) {
+#ifdef MB_ATTN_PROFILE
+  const long long aprof_k0 = clock64();
+#endif
   extern __shared__ uint8_t smem_raw[];
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* gen = smem_raw + (base - smem_u32(smem_raw));
   const uint32_t q_smem = base + STAGES * KV_STAGE;
-  const uint32_t p_smem = q_smem + Q_BYTES;
-  const uint32_t bar_base = p_smem + 4 * P_BYTES;
-  // barriers: kv_full[3], kv_empty[3], q_full, s_full[2], s_free[2], p_full[2], pv_done[2], (2 spare), drain
+  const uint32_t bar_base = q_smem + Q_BYTES;
+  // barriers: kv_full[STAGES], kv_empty[STAGES], q_full, s_full[tile][buffer], p_full[2], pv_done[2], drain
   auto kv_full = [&](int s) { return bar_base + 8u * s; };
   auto kv_empty = [&](int s) { return bar_base + 8u * (STAGES + s); };
   const uint32_t q_full = bar_base + 8u * (2 * STAGES);
-  auto s_full = [&](int t) { return bar_base + 8u * (2 * STAGES + 1 + t); };
-  auto s_free = [&](int t) { return bar_base + 8u * (2 * STAGES + 3 + t); };
+  auto s_full = [&](int t, uint32_t bf) { return bar_base + 8u * (2 * STAGES + 1 + 2 * t + bf); };
   auto p_full = [&](int t) { return bar_base + 8u * (2 * STAGES + 5 + t); };
   auto pv_done = [&](int t) { return bar_base + 8u * (2 * STAGES + 7 + t); };
-  const uint32_t drain_bar = bar_base + 8u * (2 * STAGES + 11);
-  uint32_t* tmem_ptr_smem = reinterpret_cast<uint32_t*>(gen + (bar_base - base) + 8 * (2 * STAGES + 12));
+  const uint32_t drain_bar = bar_base + 8u * (2 * STAGES + 9);
+  uint32_t* tmem_ptr_smem = reinterpret_cast<uint32_t*>(gen + (bar_base - base) + 8 * (2 * STAGES + 10));
   volatile int* abort_smem = reinterpret_cast<volatile int*>(tmem_ptr_smem + 1);
   int* tflag = p.flags ? p.flags + MB_FLAG_WAIT_TIMEOUT : nullptr;
 
@@ -92,8 +112,8 @@ attn_prefill_tc5_kernel(const __grid_constant__ AttnParams p) {
     for (int s = 0; s < STAGES; ++s) { mbar_init(kv_full(s), 1); mbar_init(kv_empty(s), 1); }
     mbar_init(q_full, 1);
     for (int t = 0; t < 2; ++t) {
-      mbar_init(s_full(t), 1);
-      mbar_init(s_free(t), 128);
+      mbar_init(s_full(t, 0), 1);
+      mbar_init(s_full(t, 1), 1);
       mbar_init(p_full(t), 128);
       mbar_init(pv_done(t), 1);
     }
@@ -157,15 +177,18 @@ attn_prefill_tc5_kernel(const __grid_constant__ AttnParams p) {
       mma_j = j;
       if (j < n_tiles) {
         mma_where = 33;
+        APROF_T0();
         if (!mbar_wait(kv_full(stage), phase, abort_smem, tflag, 33)) { ok = false; break; }
+        APROF_LAP(0);
+        APROF_COUNT(4);
       }
       // scores of tile j first (they only need the group to have READ the previous scores),
       // then the PV products of tile j-1 (they need the group's finished P)
       for (int t = 0; t < 2 && ok; ++t) {
         if (j < n_tiles) {
-          // S(t, j): previous S_t read by its softmax group
-          mma_where = 36 + 64 * t;
-          if (!mbar_wait(s_free(t), (j & 1u) ^ 1u, abort_smem, tflag, 36)) { ok = false; break; }
+          // S(t, j) goes to score buffer j & 1. That buffer last held P(t, j-2), which PV(t, j-2) read; that
+          // product was issued before this one and the tensor core runs its instructions in issue order.
+          const uint32_t bf = j & 1u;
           fence_after_sync();
           if (elect_one()) {
             const uint32_t k0 = base + stage * KV_STAGE;
@@ -175,9 +198,9 @@ attn_prefill_tc5_kernel(const __grid_constant__ AttnParams p) {
               const uint64_t bdesc = make_kmajor_sw128_desc(k0 + hf * HALF);
 #pragma unroll
               for (int kk = 0; kk < 4; ++kk)
-                mma_f16(tmem_base + (t ? S_COL1 : S_COL0), adesc + 2 * kk, bdesc + 2 * kk, id_s, (hf | kk) != 0);
+                mma_f16(tmem_base + (t ? S_COL1 : S_COL0) + bf * S_BUF, adesc + 2 * kk, bdesc + 2 * kk, id_s, (hf | kk) != 0);
             }
-            umma_commit(s_full(t));
+            umma_commit(s_full(t, bf));
           }
           __syncwarp();
         }
@@ -187,15 +210,17 @@ attn_prefill_tc5_kernel(const __grid_constant__ AttnParams p) {
           // O_t += P_t(j-1) V(j-1): the group has written P_t (and rescaled O_t if it had to)
           const uint32_t u = j - 1;
           mma_where = 34 + 64 * t;
+          APROF_T0();
           if (!mbar_wait(p_full(t), u & 1u, abort_smem, tflag, 34)) { ok = false; break; }
+          APROF_LAP(1 + t);
           fence_after_sync();
           if (elect_one()) {
             const uint32_t v0 = base + pstage * KV_STAGE + 2 * HALF;
-            const uint64_t adesc = make_kmajor_sw128_desc(p_smem + (t * 2 + (u & 1u)) * P_BYTES);
+            const uint32_t a_tmem = tmem_base + (t ? S_COL1 : S_COL0) + (u & 1u) * S_BUF;   // P_t(u): 32 columns of bf16 pairs
             const uint64_t bdesc = make_v_desc(v0);
 #pragma unroll
-            for (int kk = 0; kk < BC / 16; ++kk)            // 16 keys per instruction: 32 B of P, 16 rows of V
-              mma_f16(tmem_base + (t ? PV_COL1 : PV_COL0), adesc + 2 * kk, bdesc + 128 * kk, id_pv, (u | uint32_t(kk)) != 0u);
+            for (int kk = 0; kk < BC / 16; ++kk)            // 16 keys per instruction: 8 columns of P, 16 rows of V
+              mma_f16_ts(tmem_base + (t ? PV_COL1 : PV_COL0), a_tmem + 8 * kk, bdesc + 128 * kk, id_pv, (u | uint32_t(kk)) != 0u);
             umma_commit(pv_done(t));
             if (t == 1) umma_commit(kv_empty(pstage));      // both tiles are done with this K/V stage
           }
@@ -220,9 +245,8 @@ attn_prefill_tc5_kernel(const __grid_constant__ AttnParams p) {
     const uint32_t row = q_row0 + t * QT + r;             // row within the sequence's queries
     const int qpos = int(p.q0 + row);
     const uint32_t lane_addr = (quad * 32u) << 16;
-    const uint32_t t_s = tmem_base + lane_addr + (t ? S_COL1 : S_COL0);
+    const uint32_t t_s0 = tmem_base + lane_addr + (t ? S_COL1 : S_COL0);
     const uint32_t t_pv = tmem_base + lane_addr + (t ? PV_COL1 : PV_COL0);
-    uint8_t* p_rows = gen + (p_smem - base) + t * 2 * P_BYTES + r * 128;
     float m = -INFINITY, l = 0.0f;       // m: the maximum this row currently subtracts (may lag, see header)
     bool ok = true;
     uint32_t sm_where = 0, sm_j = 0;
@@ -233,29 +257,40 @@ attn_prefill_tc5_kernel(const __grid_constant__ AttnParams p) {
       if (p.causal) vis = min(vis, qpos + 1 - kabs);
       bool pv_waited = j == 0;           // whether PV(j-1) is known to be complete
       const bool full_tile = __all_sync(0xFFFFFFFFu, vis >= BC);   // no mask work away from the diagonal
+      const uint32_t t_s = t_s0 + (j & 1u) * S_BUF;
       sm_where = 37;
-      if (!mbar_wait(s_full(t), j & 1u, abort_smem, tflag, 37)) { ok = false; break; }
+#ifdef MB_ATTN_PROFILE
+      long long aprof_t0_ = clock64();
+      const bool aprof_on = warp == 2;
+#define SPROF(slot) do { if (aprof_on) APROF_LAP(slot); } while (0)
+#else
+#define SPROF(slot) do {} while (0)
+#endif
+      if (!mbar_wait(s_full(t, j & 1u), (j >> 1) & 1u, abort_smem, tflag, 37)) { ok = false; break; }
+      SPROF(5);
       fence_after_sync();
-      // pass 1: the row maximum of this tile
+      // the row's 64 scores, read once
+      uint32_t s[64];
+      tmem_ld_x32(t_s, s);
+      tmem_ld_x32(t_s + 32, s + 32);
+      tmem_ld_wait();
       float mx = -INFINITY;
-      uint32_t s[32];
+      if (full_tile) {
 #pragma unroll
-      for (int c = 0; c < 2; ++c) {
-        tmem_ld_x32(t_s + c * 32, s);
-        tmem_ld_wait();
-        if (full_tile) {
+        for (int i = 0; i < 64; ++i) mx = fmaxf(mx, __uint_as_float(s[i]));
+      } else {
 #pragma unroll
-          for (int i = 0; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(s[i]));
-        } else {
-#pragma unroll
-          for (int i = 0; i < 32; ++i)
-            if (c * 32 + i < vis) mx = fmaxf(mx, __uint_as_float(s[i]));
-        }
+        for (int i = 0; i < 64; ++i)
+          if (i < vis) mx = fmaxf(mx, __uint_as_float(s[i]));
       }
       const float mt = mx * p.scale_log2;
+      SPROF(6);
       if (j == 0) {
         m = mt;
       } else if (__any_sync(0xFFFFFFFFu, mt > m + 8.0f)) {
+#ifdef MB_ATTN_PROFILE
+        if (aprof_on) APROF_COUNT(11);
+#endif
         // some row of this warp outgrew its maximum: bring O_t (and l) of the whole warp to the new maxima
         sm_where = 38;
         if (!mbar_wait(pv_done(t), (j - 1u) & 1u, abort_smem, tflag, 38)) { ok = false; break; }
@@ -263,7 +298,7 @@ attn_prefill_tc5_kernel(const __grid_constant__ AttnParams p) {
         fence_after_sync();
         const float m_new = fmaxf(m, mt);
         const float f = (m == -INFINITY || m_new == -INFINITY) ? 0.0f : ex2(m - m_new);
-#pragma unroll
+#pragma unroll 1
         for (int c = 0; c < 4; ++c) {
           uint32_t v[32];
           tmem_ld_x32(t_pv + c * 32, v);
@@ -276,55 +311,43 @@ attn_prefill_tc5_kernel(const __grid_constant__ AttnParams p) {
         l *= f;
         m = m_new;
       }
-      // pass 2: probabilities, row sum, bf16 P into the swizzled shared tile
-      uint8_t* p_row = p_rows + (j & 1u) * P_BYTES;
+      // probabilities, row sum, bf16 P (two keys per 32-bit column) over the first half of the score buffer
       float sum = 0.0f;
+      uint32_t w[32];
+      const float neg_m = m == -INFINITY ? -INFINITY : -m;      // a row with nothing visible so far gives p = 0
+      if (full_tile) {
 #pragma unroll
-      for (int c = 0; c < 2; ++c) {
-        tmem_ld_x32(t_s + c * 32, s);
-        tmem_ld_wait();
-        if (c == 1) {
-          fence_before_sync();
-          mbar_arrive(s_free(t));                          // S_t may be overwritten by the next scores
+        for (int i = 0; i < 32; ++i) {
+          const float p0 = ex2(fmaf(__uint_as_float(s[2 * i]), p.scale_log2, neg_m));
+          const float p1 = ex2(fmaf(__uint_as_float(s[2 * i + 1]), p.scale_log2, neg_m));
+          sum += p0 + p1;
+          w[i] = pack2(p0, p1);
         }
-        uint32_t w[16];
-        const float neg_m = m == -INFINITY ? -INFINITY : -m;      // a row with nothing visible so far gives p = 0
-        if (full_tile) {
+      } else {
 #pragma unroll
-          for (int i = 0; i < 16; ++i) {
-            const float p0 = ex2(fmaf(__uint_as_float(s[2 * i]), p.scale_log2, neg_m));
-            const float p1 = ex2(fmaf(__uint_as_float(s[2 * i + 1]), p.scale_log2, neg_m));
-            sum += p0 + p1;
-            w[i] = pack2(p0, p1);
-          }
-        } else {
-#pragma unroll
-          for (int i = 0; i < 16; ++i) {
-            float p0 = 0.0f, p1 = 0.0f;
-            if (c * 32 + 2 * i < vis) p0 = ex2(fmaf(__uint_as_float(s[2 * i]), p.scale_log2, neg_m));
-            if (c * 32 + 2 * i + 1 < vis) p1 = ex2(fmaf(__uint_as_float(s[2 * i + 1]), p.scale_log2, neg_m));
-            sum += p0 + p1;
-            w[i] = pack2(p0, p1);
-          }
-        }
-#pragma unroll
-        for (int ch = 0; ch < 4; ++ch) {
-          const uint32_t chunk = uint32_t(c * 4 + ch);
-          *reinterpret_cast<uint4*>(p_row + ((chunk ^ (r & 7u)) << 4)) =
-              make_uint4(w[4 * ch], w[4 * ch + 1], w[4 * ch + 2], w[4 * ch + 3]);
+        for (int i = 0; i < 32; ++i) {
+          float p0 = 0.0f, p1 = 0.0f;
+          if (2 * i < vis) p0 = ex2(fmaf(__uint_as_float(s[2 * i]), p.scale_log2, neg_m));
+          if (2 * i + 1 < vis) p1 = ex2(fmaf(__uint_as_float(s[2 * i + 1]), p.scale_log2, neg_m));
+          sum += p0 + p1;
+          w[i] = pack2(p0, p1);
         }
       }
+      SPROF(8);
+      tmem_st_x32(t_s, w);
+      tmem_st_wait();
+      SPROF(9);
       l += sum;
       // PV(j-1) must be complete before P(j) is published (never a stall in practice: it was issued a
       // whole softmax pass ago). The order matters: a parity wait tells apart only two neighbouring
       // phases, so this group may not complete phase j of p_full before the issuer has consumed phase
       // j-1 (it has, once PV(j-1) is committed), nor may the issuer commit PV(j) before this group has
       // consumed pv_done of j-1. With the arrive first, an issuer held up between its two query tiles
-      // (waiting for the other group's S buffer) found p_full two phases ahead and waited for ever.
+      // found p_full two phases ahead and waited for ever.
       sm_where = 39;
       if (!pv_waited && !mbar_wait(pv_done(t), (j - 1u) & 1u, abort_smem, tflag, 39)) { ok = false; break; }
-      fence_proxy_async();                                 // generic-proxy writes of P before the MMA reads them
-      fence_before_sync();                                 // and any O_t rescale before the next PV product
+      SPROF(10);
+      fence_before_sync();                                 // P in tensor memory, and any O_t rescale, before the PV product
       mbar_arrive(p_full(t));
     }
     if (!ok && tflag && r == 0 && t == 0) atomicCAS(tflag + 6, 0, int(1u << 30 | sm_where << 20 | sm_j));
@@ -355,9 +378,20 @@ attn_prefill_tc5_kernel(const __grid_constant__ AttnParams p) {
     fence_after_sync();
     tmem_dealloc(tmem_base, TMEM_COLS);
   }
+#ifdef MB_ATTN_PROFILE
+  if (threadIdx.x == 0) atomicAdd(&g_attn_prof[3], (unsigned long long)(clock64() - aprof_k0));
+#endif
 }
 
 }  // namespace
+
+#ifdef MB_ATTN_PROFILE
+MB_API int mb_debug_attn_profile(unsigned long long* host_out, int reset) {
+  if (host_out) cudaMemcpyFromSymbol(host_out, g_attn_prof, sizeof g_attn_prof);
+  if (reset) { static unsigned long long z[16]; cudaMemcpyToSymbol(g_attn_prof, z, sizeof z); }
+  return 0;
+}
+#endif
 
 int mb_attention_prefill_tc5(mb_ctx* ctx, cudaStream_t stream, const AttnParams& p) {
   static bool attr_set[16] = {};

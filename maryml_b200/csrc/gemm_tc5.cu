@@ -1085,14 +1085,26 @@ MB_API int mb_nvfp4_gemm_w4a4_grouped(mb_ctx* ctx, mb_stream stream, const uint8
                           epilogue, ex);
 }
 
-MB_API int mb_bf16_gemm(mb_ctx* ctx, mb_stream stream_, const void* a, const void* b, float alpha, size_t m, size_t n,
-                        size_t k, void* out, int out_dtype) {
-  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+// K slices of a bf16 product with few output tiles (the MoE router projection: 32 tiles of a [4096, 128] output).
+static uint32_t bf16_splitk_factor(int sm_count, size_t m, size_t n, size_t k) {
+  const uint32_t bn = n % 256 == 0 ? 256 : 128;
+  const uint32_t tiles = uint32_t((m + 127) / 128) * uint32_t((n + bn - 1) / bn);
+  const uint32_t k_steps = uint32_t((k + 63) / 64);
+  if (tiles * 2 > uint32_t(sm_count) || k_steps < 8 || n % 4 != 0) return 1;
+  uint32_t want = std::min<uint32_t>(uint32_t(sm_count) / tiles, k_steps / 4);   // at least four K steps per slice
+  if (want < 2) return 1;
+  const uint32_t per = (k_steps + want - 1) / want;
+  return (k_steps + per - 1) / per;
+}
+
+static int bf16_gemm_common(mb_ctx* ctx, cudaStream_t stream, const void* a, const void* b, float alpha, size_t m,
+                            size_t n, size_t k, void* out, int out_dtype, void* workspace, size_t workspace_bytes) {
   MB_REQUIRE(ctx, ctx && a && b && out, "bf16_gemm: null argument");
   MB_REQUIRE(ctx, m > 0 && n > 0 && k > 0 && k % 8 == 0 && n % 8 == 0, "bf16_gemm: k and n must be positive multiples of 8");
   MB_REQUIRE(ctx, m * k <= 0xFFFFFFFFull && n * k <= 0xFFFFFFFFull, "bf16_gemm: exceeds u32 indexing");
   MB_REQUIRE(ctx, out_dtype == MB_DT_BF16 || out_dtype == MB_DT_F32, "bf16_gemm: output is bf16 or f32");
-  MB_REQUIRE(ctx, mb_aligned(a, 16) && mb_aligned(b, 16) && mb_aligned(out, 16), "bf16_gemm: 16-byte alignment");
+  MB_REQUIRE(ctx, mb_aligned(a, 16) && mb_aligned(b, 16) && mb_aligned(out, 16) && mb_aligned(workspace, 16),
+             "bf16_gemm: 16-byte alignment");
   GemmParams p;
   memset(&p, 0, sizeof p);
   const bool wide = (n % 256 == 0);
@@ -1107,5 +1119,44 @@ MB_API int mb_bf16_gemm(mb_ctx* ctx, mb_stream stream_, const void* a, const voi
   p.ldo = uint32_t(n); p.out_dtype = out_dtype; p.epilogue = MB_EPI_PLAIN;
   p.splits = 1; p.ks_per_split = p.k_steps;
   uint32_t tiles = p.m_tiles * p.n_tiles;
+  const uint32_t sk = workspace ? bf16_splitk_factor(ctx->sm_count, m, n, k) : 1;
+  if (sk > 1 && workspace_bytes >= size_t(sk) * m * n * sizeof(float)) {
+    // K slices into f32 planes, then one ordered sum with alpha (deterministic)
+    p.ks_per_split = (p.k_steps + sk - 1) / sk;
+    p.splits = (p.k_steps + p.ks_per_split - 1) / p.ks_per_split;
+    p.out = workspace; p.out_dtype = MB_DT_F32; p.alpha = 1.0f;
+    tiles *= p.splits;
+    rc = wide ? launch<KIND_BF16, 256>(ctx, stream, p, tiles) : launch<KIND_BF16, 128>(ctx, stream, p, tiles);
+    if (rc) return rc;
+    const size_t plane4 = m * n / 4;
+    const unsigned grid = unsigned((plane4 + 255) / 256);
+    if (out_dtype == MB_DT_F32)
+      MB_CUDA_OK(ctx, mb_launch_pdl(splitk_reduce_kernel<float>, dim3(grid), dim3(256), 0, stream,
+                                    static_cast<const float4*>(workspace), p.splits, plane4, uint32_t(n / 4),
+                                    static_cast<const float*>(nullptr), static_cast<const float4*>(nullptr), alpha,
+                                    static_cast<float*>(out)));
+    else
+      MB_CUDA_OK(ctx, mb_launch_pdl(splitk_reduce_kernel<__nv_bfloat16>, dim3(grid), dim3(256), 0, stream,
+                                    static_cast<const float4*>(workspace), p.splits, plane4, uint32_t(n / 4),
+                                    static_cast<const float*>(nullptr), static_cast<const float4*>(nullptr), alpha,
+                                    static_cast<__nv_bfloat16*>(out)));
+    return MB_OK;
+  }
   return wide ? launch<KIND_BF16, 256>(ctx, stream, p, tiles) : launch<KIND_BF16, 128>(ctx, stream, p, tiles);
+}
+
+MB_API int mb_bf16_gemm(mb_ctx* ctx, mb_stream stream, const void* a, const void* b, float alpha, size_t m, size_t n,
+                        size_t k, void* out, int out_dtype) {
+  return bf16_gemm_common(ctx, static_cast<cudaStream_t>(stream), a, b, alpha, m, n, k, out, out_dtype, nullptr, 0);
+}
+
+MB_API size_t mb_bf16_gemm_splitk_workspace(size_t m, size_t n, size_t k) {
+  const uint32_t sk = bf16_splitk_factor(148, m, n, k);
+  return sk > 1 ? size_t(sk) * m * n * sizeof(float) : 0;
+}
+
+MB_API int mb_bf16_gemm_splitk(mb_ctx* ctx, mb_stream stream, const void* a, const void* b, float alpha, size_t m,
+                               size_t n, size_t k, void* out, int out_dtype, void* workspace, size_t workspace_bytes) {
+  return bf16_gemm_common(ctx, static_cast<cudaStream_t>(stream), a, b, alpha, m, n, k, out, out_dtype, workspace,
+                          workspace_bytes);
 }

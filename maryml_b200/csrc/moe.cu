@@ -137,8 +137,8 @@ plan_count_kernel(const int32_t* __restrict__ idx, uint32_t tokens, uint32_t k, 
 // the chunks (rows of expert e that earlier chunks take); the totals, padded to 128, give the
 // first stacked row of each expert, the expert of each tile and the number of tiles in use.
 __global__ void __launch_bounds__(1024)
-plan_scan_kernel(int32_t* __restrict__ chunk_counts, uint32_t chunks, uint32_t n_experts,
-                 int32_t* __restrict__ expert_rows, int32_t* __restrict__ expert_row0,
+plan_scan_kernel(const int32_t* __restrict__ chunk_counts, int32_t* __restrict__ chunk_base, uint32_t chunks,
+                 uint32_t n_experts, int32_t* __restrict__ expert_rows, int32_t* __restrict__ expert_row0,
                  int32_t* __restrict__ tile_expert, uint32_t tile_cap, int32_t* __restrict__ n_tiles) {
   __shared__ int32_t s_pad[1024];
   __shared__ int32_t s_off[1024];
@@ -146,10 +146,16 @@ plan_scan_kernel(int32_t* __restrict__ chunk_counts, uint32_t chunks, uint32_t n
   const uint32_t e = threadIdx.x;
   int32_t c = 0;
   if (e < n_experts) {
-    for (uint32_t ch = 0; ch < chunks; ++ch) {
-      const int32_t here = chunk_counts[size_t(ch) * n_experts + e];
-      chunk_counts[size_t(ch) * n_experts + e] = c;
-      c += here;
+    // counts and prefixes live in separate arrays so that the loads of a batch are independent
+    for (uint32_t ch0 = 0; ch0 < chunks; ch0 += 8) {
+      int32_t here[8];
+#pragma unroll
+      for (uint32_t i = 0; i < 8; ++i) here[i] = ch0 + i < chunks ? __ldg(chunk_counts + size_t(ch0 + i) * n_experts + e) : 0;
+#pragma unroll
+      for (uint32_t i = 0; i < 8; ++i) {
+        if (ch0 + i < chunks) chunk_base[size_t(ch0 + i) * n_experts + e] = c;
+        c += here[i];
+      }
     }
   }
   s_pad[e] = (c + PLAN_PAD - 1) / PLAN_PAD;   // tiles of this expert
@@ -292,7 +298,8 @@ MB_API size_t mb_moe_plan_rows(size_t tokens, size_t k, size_t n_experts) {
 
 MB_API size_t mb_moe_plan_workspace(size_t tokens, size_t k, size_t n_experts) {
   (void)k;
-  return ((tokens + PLAN_CHUNK - 1) / PLAN_CHUNK) * n_experts * sizeof(int32_t);   // picks per (chunk of 256 tokens, expert)
+  // picks per (chunk of 256 tokens, expert) and their exclusive prefixes over the chunks
+  return 2 * ((tokens + PLAN_CHUNK - 1) / PLAN_CHUNK) * n_experts * sizeof(int32_t);
 }
 
 MB_API int mb_moe_plan(mb_ctx* ctx, mb_stream stream_, const int32_t* idx, const float* weight, size_t tokens,
@@ -314,11 +321,12 @@ MB_API int mb_moe_plan(mb_ctx* ctx, mb_stream stream_, const int32_t* idx, const
   plan_count_kernel<<<chunks, PLAN_CHUNK, n_experts * sizeof(int32_t), stream>>>(
       idx, uint32_t(tokens), uint32_t(k), uint32_t(n_experts), chunk_counts, row_tok, row_wgt, uint32_t(m_cap), flag);
   MB_LAUNCH_OK(ctx);
-  plan_scan_kernel<<<1, 1024, 0, stream>>>(chunk_counts, chunks, uint32_t(n_experts), expert_rows, expert_row0,
-                                           tile_expert, uint32_t(m_cap / PLAN_PAD), n_tiles);
+  int32_t* chunk_base = chunk_counts + size_t(chunks) * n_experts;
+  plan_scan_kernel<<<1, 1024, 0, stream>>>(chunk_counts, chunk_base, chunks, uint32_t(n_experts), expert_rows,
+                                           expert_row0, tile_expert, uint32_t(m_cap / PLAN_PAD), n_tiles);
   MB_LAUNCH_OK(ctx);
   plan_place_kernel<<<chunks, PLAN_CHUNK, n_experts * 32, stream>>>(idx, weight, uint32_t(tokens), uint32_t(k),
-                                                                    uint32_t(n_experts), chunk_counts, expert_row0,
+                                                                    uint32_t(n_experts), chunk_base, expert_row0,
                                                                     row_tok, row_wgt, tok_rows);
   MB_LAUNCH_OK(ctx);
   return MB_OK;

@@ -183,8 +183,14 @@ def bf16_gemm(a, b, out_dtype=torch.float32, out=None, alpha=1.0):
     n = b.shape[0]
     if out is None:
         out = torch.empty((m, n), dtype=out_dtype, device=a.device)
-    ctx.check(lib.mb_bf16_gemm(ctx.handle, _stream(), _p(a), _p(b), float(alpha), m, n, k, _p(out),
-                               _lib.DT_BF16 if out.dtype == torch.bfloat16 else _lib.DT_F32))
+    dt = _lib.DT_BF16 if out.dtype == torch.bfloat16 else _lib.DT_F32
+    need = int(lib.mb_bf16_gemm_splitk_workspace(m, n, k))
+    if need:        # few output tiles, long K (the router projection): K slices, summed in order
+        ws = _splitk_workspace(a.device, need)
+        ctx.check(lib.mb_bf16_gemm_splitk(ctx.handle, _stream(), _p(a), _p(b), float(alpha), m, n, k, _p(out), dt,
+                                          _p(ws), need))
+        return out
+    ctx.check(lib.mb_bf16_gemm(ctx.handle, _stream(), _p(a), _p(b), float(alpha), m, n, k, _p(out), dt))
     return out
 
 

@@ -339,8 +339,9 @@ def test_w4a4_rows_nan_row_poisons_only_itself(mb, orc):
     assert torch.equal(dirty[0, keep].view(torch.int16), clean[0, keep].view(torch.int16))
 
 
-@pytest.mark.parametrize("m,n,k", [(128, 128, 64), (200, 264, 1032), (512, 1024, 2048)])
+@pytest.mark.parametrize("m,n,k", [(128, 128, 64), (200, 264, 1032), (512, 1024, 2048), (512, 128, 2048), (100, 128, 1096)])
 def test_bf16_gemm_against_f64(mb, orc, m, n, k):
+    """The last two shapes have few output tiles and a long K: they run as K slices (split-K)."""
     abits = f32_to_bf16_bits(orc.normal_f32(31, m * k, 1.0))
     bbits = f32_to_bf16_bits(orc.normal_f32(32, n * k, 0.02))
     ref = orc.linear_bf16(abits, bbits, m, n, k)
