@@ -1,28 +1,33 @@
 // Causal GQA prefill attention on the sm_100a tensor cores (tcgen05 + TMEM), head_dim 128.
 //
-// One CTA owns 256 query rows of one head as two 128-row tiles. Per 64-key tile:
+// One CTA owns 256 query rows of one head as two 128-row tiles. Per 128-key tile:
 //
-//   S_t  = Q_t K^T      tcgen05.mma kind::f16, 128 x 64 x 128, accumulator in TMEM
+//   S_t  = Q_t K^T      tcgen05.mma kind::f16, 128 x 128 x 128, accumulator in TMEM
 //   P_t  = 2^(S_t*c - m) one softmax thread per query row reads its row of S_t from
 //                        TMEM (no cross-thread reduction) and writes bf16 P_t back over
-//                        the first 32 columns of the same score buffer (tcgen05.st)
-//   O_t += P_t V         tcgen05.mma with the A operand in TMEM, 128 x 128 x 64, V read
+//                        the first 64 columns of the same score buffer (tcgen05.st)
+//   O_t += P_t V         tcgen05.mma with the A operand in TMEM, 128 x 128 x 128, V read
 //                        MN-major straight from the TMA tile; O_t stays in TMEM over the
 //                        whole key loop
 //
-// Keeping P in tensor memory matters because the kernel is bound by shared-memory bandwidth:
-// per 64-key tile pair the score products read 96 KB (Q is re-read for every 64 keys), a P
-// tile in shared memory cost 32 KB to write and 32 KB to read back, V is 32 KB and the TMA
-// fill 32 KB, against 128 B/clk. Without the P round trip the five K/V stages also fit.
+// Why these shapes. Per-phase cycle counters of the 64-key version showed the MMA warp busy
+// issuing 1.7 k of the 2.1 k cycles a tile took: a 128 x 64 score instruction occupies the tensor
+// pipe as long as a 128 x 128 one, so the score products ran at half rate; 128-key tiles make
+// every instruction 128 x 128. P lives in tensor memory because shared-memory bandwidth is
+// the next limit (a P tile in shared memory is written once and read once per tile, on top of
+// the Q re-read of every score product, the V read and the TMA fill).
+//
+// TMEM: S0, S1 (128 columns each), PV0, PV1 (128 each) = 512. One score buffer per query tile:
+// the issuer sends PV(t, j) and then S(t, j + 1) as soon as group t publishes P(t, j), and the
+// tensor core works for the other group while group t exponentiates (the two groups alternate).
 //
 // The running maximum a row subtracts is allowed to lag the true one by up to 2^8: O_t in
 // TMEM is rescaled (tcgen05.ld, multiply, tcgen05.st) only when a tile raises a row's maximum
 // by more than that, which after the first tiles is rare; the final O_t / l is exact either way.
 //
-// Warp roles: 0 = TMA producer (Q once, K/V ring), 1 = MMA issuer, 2-5 and 6-9 = the two
-// softmax groups (one per query tile) that alternate on the tensor core: while one group
-// exponentiates, the other group's products run. TMEM: two score buffers of 64 columns per
-// query tile (tile j + 1's scores land while tile j's buffer still holds P), PV0, PV1 (128 each). Algorithmic work: 4 * nq * keys * 128 flop per head, half under the mask.
+// Warp roles: 0 = TMA producer (Q once, a ring of three K tiles and a ring of two V tiles),
+// 1 = MMA issuer, 2-5 and 6-9 = the two softmax groups (one per query tile).
+// Algorithmic work: 4 * nq * keys * 128 flop per head, half under the mask.
 // Every mbarrier wait is bounded.
 #include "attention.cuh"
 
@@ -31,15 +36,16 @@ namespace {
 using namespace tc5;
 
 constexpr int D = 128;
-constexpr int BC = 64;                         // keys per tile
+constexpr int BC = 128;                        // keys per tile
+constexpr int BOX = 64;                        // key rows of one TMA box (the tensor maps are shared with the decode kernel)
 constexpr int QT = 128;                        // query rows per tile (two tiles per CTA)
-constexpr int HALF = BC * 128;                 // one 64-dim half of a K or V tile: 8 KB
-constexpr int KV_STAGE = 4 * HALF;             // K lo, K hi, V lo, V hi: 32 KB
-constexpr int STAGES = 5;
+constexpr int HALF = BC * 128;                 // one 64-dim half of a K or V tile: 16 KB
+constexpr int TILE = 2 * HALF;                 // a K tile or a V tile: 32 KB
+constexpr int KSTAGES = 3, VSTAGES = 2;
 constexpr int Q_BYTES = 2 * QT * D * 2;        // 64 KB: [tile][half][128 rows][64 dims]
-constexpr int SMEM = STAGES * KV_STAGE + Q_BYTES + 1024 + 256;
+constexpr int SMEM = (KSTAGES + VSTAGES) * TILE + Q_BYTES + 1024 + 256;
 constexpr int THREADS = 320;
-constexpr int S_COL0 = 0, S_COL1 = 128, S_BUF = 64, PV_COL0 = 256, PV_COL1 = 384, TMEM_COLS = 512;
+constexpr int S_COL0 = 0, S_COL1 = 128, PV_COL0 = 256, PV_COL1 = 384, TMEM_COLS = 512;
 
 // Development aid (-DMB_ATTN_PROFILE): cycles per phase, summed over CTAs. Slots: 0 issuer waits K/V, 1 issuer waits
 // P of tile 0, 2 issuer waits P of tile 1, 3 whole kernel, 4 key tiles; first warp of softmax group 0: 5 waits scores,
@@ -66,9 +72,33 @@ __device__ __forceinline__ uint64_t make_v_desc(uint32_t saddr) {
 }
 
 __device__ __forceinline__ float ex2(float x) {
+#ifdef MB_ATTN_NOEXP   // timing experiment only: what the kernel costs without the special-function unit (wrong results)
+  return x * 0.001f + 0.01f;
+#else
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
+#endif
+}
+// Two-lane f32 arithmetic of sm_100 (each lane an IEEE round-to-nearest op): half the issue slots of the scalar forms.
+typedef unsigned long long f32x2;
+__device__ __forceinline__ f32x2 f2_pack(float a, float b) {
+  f32x2 r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(a), "f"(b));
+  return r;
+}
+__device__ __forceinline__ void f2_unpack(f32x2 v, float& a, float& b) {
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(a), "=f"(b) : "l"(v));
+}
+__device__ __forceinline__ f32x2 f2_fma(f32x2 a, f32x2 b, f32x2 c) {
+  f32x2 r;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c));
+  return r;
+}
+__device__ __forceinline__ f32x2 f2_add(f32x2 a, f32x2 b) {
+  f32x2 r;
+  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+  return r;
 }
 __device__ __forceinline__ uint32_t pack2(float lo, float hi) {
   __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
@@ -83,17 +113,21 @@ attn_prefill_tc5_kernel(const __grid_constant__ AttnParams p) {
   extern __shared__ uint8_t smem_raw[];
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* gen = smem_raw + (base - smem_u32(smem_raw));
-  const uint32_t q_smem = base + STAGES * KV_STAGE;
+  const uint32_t k_smem = base, v_smem = base + KSTAGES * TILE;
+  const uint32_t q_smem = v_smem + VSTAGES * TILE;
   const uint32_t bar_base = q_smem + Q_BYTES;
-  // barriers: kv_full[STAGES], kv_empty[STAGES], q_full, s_full[tile][buffer], p_full[2], pv_done[2], drain
-  auto kv_full = [&](int s) { return bar_base + 8u * s; };
-  auto kv_empty = [&](int s) { return bar_base + 8u * (STAGES + s); };
-  const uint32_t q_full = bar_base + 8u * (2 * STAGES);
-  auto s_full = [&](int t, uint32_t bf) { return bar_base + 8u * (2 * STAGES + 1 + 2 * t + bf); };
-  auto p_full = [&](int t) { return bar_base + 8u * (2 * STAGES + 5 + t); };
-  auto pv_done = [&](int t) { return bar_base + 8u * (2 * STAGES + 7 + t); };
-  const uint32_t drain_bar = bar_base + 8u * (2 * STAGES + 9);
-  uint32_t* tmem_ptr_smem = reinterpret_cast<uint32_t*>(gen + (bar_base - base) + 8 * (2 * STAGES + 10));
+  // barriers: k_full[3], k_empty[3], v_full[2], v_empty[2], q_full, s_full[2], p_full[2], pv_done[2], drain
+  auto k_full = [&](int s) { return bar_base + 8u * s; };
+  auto k_empty = [&](int s) { return bar_base + 8u * (KSTAGES + s); };
+  auto v_full = [&](int s) { return bar_base + 8u * (2 * KSTAGES + s); };
+  auto v_empty = [&](int s) { return bar_base + 8u * (2 * KSTAGES + VSTAGES + s); };
+  constexpr int NB = 2 * KSTAGES + 2 * VSTAGES;
+  const uint32_t q_full = bar_base + 8u * NB;
+  auto s_full = [&](int t) { return bar_base + 8u * (NB + 1 + t); };
+  auto p_full = [&](int t) { return bar_base + 8u * (NB + 3 + t); };
+  auto pv_done = [&](int t) { return bar_base + 8u * (NB + 5 + t); };
+  const uint32_t drain_bar = bar_base + 8u * (NB + 7);
+  uint32_t* tmem_ptr_smem = reinterpret_cast<uint32_t*>(gen + (bar_base - base) + 8 * (NB + 8));
   volatile int* abort_smem = reinterpret_cast<volatile int*>(tmem_ptr_smem + 1);
   int* tflag = p.flags ? p.flags + MB_FLAG_WAIT_TIMEOUT : nullptr;
 
@@ -109,11 +143,11 @@ attn_prefill_tc5_kernel(const __grid_constant__ AttnParams p) {
   const uint32_t n_tiles = (k_end + BC - 1) / BC;
 
   if (threadIdx.x == 0) {
-    for (int s = 0; s < STAGES; ++s) { mbar_init(kv_full(s), 1); mbar_init(kv_empty(s), 1); }
+    for (int s = 0; s < KSTAGES; ++s) { mbar_init(k_full(s), 1); mbar_init(k_empty(s), 1); }
+    for (int s = 0; s < VSTAGES; ++s) { mbar_init(v_full(s), 1); mbar_init(v_empty(s), 1); }
     mbar_init(q_full, 1);
     for (int t = 0; t < 2; ++t) {
-      mbar_init(s_full(t, 0), 1);
-      mbar_init(s_full(t, 1), 1);
+      mbar_init(s_full(t), 1);
       mbar_init(p_full(t), 128);
       mbar_init(pv_done(t), 1);
     }
@@ -144,91 +178,106 @@ attn_prefill_tc5_kernel(const __grid_constant__ AttnParams p) {
           tma_load_4d(q_smem + (t * 2 + hf) * (QT * 128), &p.tmap_q, hf * 64, int(h), int(q_row0 + t * QT), int(b), q_full);
     }
     __syncwarp();
-    int stage = 0;
-    uint32_t phase = 0;
-    for (uint32_t j = 0; j < n_tiles; ++j) {
-      if (!mbar_wait(kv_empty(stage), phase ^ 1u, abort_smem, tflag, 31)) {
-        if (tflag && lane == 0) atomicCAS(tflag + 7, 0, int(j | n_tiles << 10 | (p.q0 >> 6) << 20));
-        break;
-      }
+    // A tile of 128 keys is four boxes: [64-dim half][64-key box]; K(0), then V(j) and K(j + 1) alternate.
+    auto load_tile = [&](const CUtensorMap* tm, uint32_t dst, uint32_t j, uint32_t bar) {
       if (elect_one()) {
-        const uint32_t s0 = base + stage * KV_STAGE;
-        const int key0 = int(j * BC);
-        mbar_arrive_expect_tx(kv_full(stage), KV_STAGE);
-        tma_load_4d(s0, &p.tmap_k, 0, int(kvh), key0, int(b), kv_full(stage));
-        tma_load_4d(s0 + HALF, &p.tmap_k, 64, int(kvh), key0, int(b), kv_full(stage));
-        tma_load_4d(s0 + 2 * HALF, &p.tmap_v, 0, int(kvh), key0, int(b), kv_full(stage));
-        tma_load_4d(s0 + 3 * HALF, &p.tmap_v, 64, int(kvh), key0, int(b), kv_full(stage));
+        mbar_arrive_expect_tx(bar, TILE);
+#pragma unroll
+        for (int hf = 0; hf < 2; ++hf)
+#pragma unroll
+          for (int bx = 0; bx < 2; ++bx)
+            tma_load_4d(dst + hf * HALF + bx * (BOX * 128), tm, hf * 64, int(kvh), int(j * BC + bx * BOX), int(b), bar);
       }
       __syncwarp();
-      if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+    };
+    bool ok = true;
+    for (uint32_t i = 0; ok && i <= n_tiles; ++i) {
+      if (i < n_tiles) {                                   // K(i)
+        const int st = int(i % KSTAGES);
+        if (!mbar_wait(k_empty(st), ((i / KSTAGES) & 1u) ^ 1u, abort_smem, tflag, 31)) {
+          if (tflag && lane == 0) atomicCAS(tflag + 7, 0, int(i | n_tiles << 10 | (p.q0 >> 6) << 20));
+          ok = false;
+          break;
+        }
+        load_tile(&p.tmap_k, k_smem + st * TILE, i, k_full(st));
+      }
+      if (i > 0) {                                         // V(i - 1)
+        const uint32_t j = i - 1;
+        const int st = int(j % VSTAGES);
+        if (!mbar_wait(v_empty(st), ((j / VSTAGES) & 1u) ^ 1u, abort_smem, tflag, 30)) { ok = false; break; }
+        load_tile(&p.tmap_v, v_smem + st * TILE, j, v_full(st));
+      }
     }
   } else if (warp == 1) {
     // ------------------------------ MMA issuer ----------------------------------
-    // Order per key tile j: S(0, j), S(1, j), PV(0, j-1), PV(1, j-1): a group's next scores are
-    // computed while it exponentiates tile j-1, and its PV product runs while it works on tile j.
+    // S(0, 0), S(1, 0); then per key tile and query tile: wait for P(t, j), issue O_t += P V(j) and at once
+    // S(t, j + 1) into the same score buffer (the tensor core runs its instructions in issue order, so the
+    // scores overwrite P only after the PV product has read it).
     bool ok = mbar_wait(q_full, 0u, abort_smem, tflag, 32);
     const uint32_t id_s = idesc(BC, 0), id_pv = idesc(D, 1);
-    int stage = 0;                 // stage of key tile j (for S); PV(j-1) uses the previous stage
-    uint32_t phase = 0;
-    int pstage = 0;
     uint32_t mma_where = 0, mma_j = 0;     // the wait the issuer was in, for the status block of a run-out wait
-    for (uint32_t j = 0; ok && j <= n_tiles; ++j) {
+    auto issue_s = [&](int t, uint32_t j) {                // K(j) is resident
+      if (elect_one()) {
+        const uint32_t k0 = k_smem + (j % KSTAGES) * TILE;
+#pragma unroll
+        for (int hf = 0; hf < 2; ++hf) {
+          const uint64_t adesc = make_kmajor_sw128_desc(q_smem + (t * 2 + hf) * (QT * 128));
+          const uint64_t bdesc = make_kmajor_sw128_desc(k0 + hf * HALF);
+#pragma unroll
+          for (int kk = 0; kk < 4; ++kk)
+            mma_f16(tmem_base + (t ? S_COL1 : S_COL0), adesc + 2 * kk, bdesc + 2 * kk, id_s, (hf | kk) != 0);
+        }
+        umma_commit(s_full(t));
+        if (t == 1) umma_commit(k_empty(int(j % KSTAGES)));   // both query tiles have their scores of K(j)
+      }
+      __syncwarp();
+    };
+    if (ok) {
+      mma_where = 33;
+      APROF_T0();
+      ok = mbar_wait(k_full(0), 0u, abort_smem, tflag, 33);
+      APROF_LAP(0);
+      if (ok) {
+        fence_after_sync();
+        issue_s(0, 0);
+        issue_s(1, 0);
+      }
+    }
+    for (uint32_t j = 0; ok && j < n_tiles; ++j) {
       mma_j = j;
-      if (j < n_tiles) {
-        mma_where = 33;
+      APROF_COUNT(4);
+      const int vst = int(j % VSTAGES);
+      for (int t = 0; t < 2 && ok; ++t) {
+        mma_where = 34 + 64 * t;
         APROF_T0();
-        if (!mbar_wait(kv_full(stage), phase, abort_smem, tflag, 33)) { ok = false; break; }
-        APROF_LAP(0);
-        APROF_COUNT(4);
-      }
-      // scores of tile j first (they only need the group to have READ the previous scores),
-      // then the PV products of tile j-1 (they need the group's finished P)
-      for (int t = 0; t < 2 && ok; ++t) {
-        if (j < n_tiles) {
-          // S(t, j) goes to score buffer j & 1. That buffer last held P(t, j-2), which PV(t, j-2) read; that
-          // product was issued before this one and the tensor core runs its instructions in issue order.
-          const uint32_t bf = j & 1u;
-          fence_after_sync();
-          if (elect_one()) {
-            const uint32_t k0 = base + stage * KV_STAGE;
+        if (!mbar_wait(p_full(t), j & 1u, abort_smem, tflag, 34)) { ok = false; break; }
+        APROF_LAP(1 + t);
+        if (t == 0) {
+          mma_where = 35;
+          if (!mbar_wait(v_full(vst), (j / VSTAGES) & 1u, abort_smem, tflag, 35)) { ok = false; break; }
+          APROF_LAP(0);
+        }
+        fence_after_sync();
+        if (elect_one()) {
+          const uint32_t a_tmem = tmem_base + (t ? S_COL1 : S_COL0);      // P_t(j): 64 columns of bf16 pairs
+          const uint64_t bdesc = make_v_desc(v_smem + vst * TILE);
 #pragma unroll
-            for (int hf = 0; hf < 2; ++hf) {
-              const uint64_t adesc = make_kmajor_sw128_desc(q_smem + (t * 2 + hf) * (QT * 128));
-              const uint64_t bdesc = make_kmajor_sw128_desc(k0 + hf * HALF);
-#pragma unroll
-              for (int kk = 0; kk < 4; ++kk)
-                mma_f16(tmem_base + (t ? S_COL1 : S_COL0) + bf * S_BUF, adesc + 2 * kk, bdesc + 2 * kk, id_s, (hf | kk) != 0);
-            }
-            umma_commit(s_full(t, bf));
+          for (int kk = 0; kk < BC / 16; ++kk)            // 16 keys per instruction: 8 columns of P, 16 rows of V
+            mma_f16_ts(tmem_base + (t ? PV_COL1 : PV_COL0), a_tmem + 8 * kk, bdesc + 128 * kk, id_pv, (j | uint32_t(kk)) != 0u);
+          umma_commit(pv_done(t));
+          if (t == 1) umma_commit(v_empty(vst));          // both query tiles are done with V(j)
+        }
+        __syncwarp();
+        if (j + 1 < n_tiles) {
+          if (t == 0) {
+            mma_where = 33;
+            if (!mbar_wait(k_full(int((j + 1) % KSTAGES)), ((j + 1) / KSTAGES) & 1u, abort_smem, tflag, 33)) { ok = false; break; }
+            APROF_LAP(0);
+            fence_after_sync();
           }
-          __syncwarp();
+          issue_s(t, j + 1);
         }
       }
-      for (int t = 0; t < 2 && ok; ++t) {
-        if (j > 0) {
-          // O_t += P_t(j-1) V(j-1): the group has written P_t (and rescaled O_t if it had to)
-          const uint32_t u = j - 1;
-          mma_where = 34 + 64 * t;
-          APROF_T0();
-          if (!mbar_wait(p_full(t), u & 1u, abort_smem, tflag, 34)) { ok = false; break; }
-          APROF_LAP(1 + t);
-          fence_after_sync();
-          if (elect_one()) {
-            const uint32_t v0 = base + pstage * KV_STAGE + 2 * HALF;
-            const uint32_t a_tmem = tmem_base + (t ? S_COL1 : S_COL0) + (u & 1u) * S_BUF;   // P_t(u): 32 columns of bf16 pairs
-            const uint64_t bdesc = make_v_desc(v0);
-#pragma unroll
-            for (int kk = 0; kk < BC / 16; ++kk)            // 16 keys per instruction: 8 columns of P, 16 rows of V
-              mma_f16_ts(tmem_base + (t ? PV_COL1 : PV_COL0), a_tmem + 8 * kk, bdesc + 128 * kk, id_pv, (u | uint32_t(kk)) != 0u);
-            umma_commit(pv_done(t));
-            if (t == 1) umma_commit(kv_empty(pstage));      // both tiles are done with this K/V stage
-          }
-          __syncwarp();
-        }
-      }
-      if (j > 0) { if (++pstage == STAGES) pstage = 0; }
-      if (j < n_tiles) { if (++stage == STAGES) { stage = 0; phase ^= 1u; } }
     }
     if (!ok) {
       if (tflag && lane == 0) atomicCAS(tflag + 5, 0, int(1u << 30 | mma_where << 20 | mma_j));
@@ -245,7 +294,7 @@ attn_prefill_tc5_kernel(const __grid_constant__ AttnParams p) {
     const uint32_t row = q_row0 + t * QT + r;             // row within the sequence's queries
     const int qpos = int(p.q0 + row);
     const uint32_t lane_addr = (quad * 32u) << 16;
-    const uint32_t t_s0 = tmem_base + lane_addr + (t ? S_COL1 : S_COL0);
+    const uint32_t t_s = tmem_base + lane_addr + (t ? S_COL1 : S_COL0);
     const uint32_t t_pv = tmem_base + lane_addr + (t ? PV_COL1 : PV_COL0);
     float m = -INFINITY, l = 0.0f;       // m: the maximum this row currently subtracts (may lag, see header)
     bool ok = true;
@@ -257,7 +306,6 @@ attn_prefill_tc5_kernel(const __grid_constant__ AttnParams p) {
       if (p.causal) vis = min(vis, qpos + 1 - kabs);
       bool pv_waited = j == 0;           // whether PV(j-1) is known to be complete
       const bool full_tile = __all_sync(0xFFFFFFFFu, vis >= BC);   // no mask work away from the diagonal
-      const uint32_t t_s = t_s0 + (j & 1u) * S_BUF;
       sm_where = 37;
 #ifdef MB_ATTN_PROFILE
       long long aprof_t0_ = clock64();
@@ -266,75 +314,112 @@ attn_prefill_tc5_kernel(const __grid_constant__ AttnParams p) {
 #else
 #define SPROF(slot) do {} while (0)
 #endif
-      if (!mbar_wait(s_full(t, j & 1u), (j >> 1) & 1u, abort_smem, tflag, 37)) { ok = false; break; }
+      if (!mbar_wait(s_full(t), j & 1u, abort_smem, tflag, 37)) { ok = false; break; }
       SPROF(5);
       fence_after_sync();
-      // the row's 64 scores, read once
-      uint32_t s[64];
-      tmem_ld_x32(t_s, s);
-      tmem_ld_x32(t_s + 32, s + 32);
-      tmem_ld_wait();
-      float mx = -INFINITY;
-      if (full_tile) {
+      // One pass in the common case: the probabilities are taken against the maximum the row already
+      // subtracts (it may lag the true one by 2^8, see the header) while the tile's own maximum is
+      // collected on the side; P stays in registers until the maximum is known to be within reach.
+      // Only the first tile, and a tile that outgrows the lag, read the scores a second time.
+      uint32_t w[64];
+      float sum = 0.0f, mx = -INFINITY;
+      auto probabilities = [&](bool with_max) {
+        const float neg_m = m == -INFINITY ? -INFINITY : -m;      // a row with nothing visible so far gives p = 0
+        const f32x2 c2 = f2_pack(p.scale_log2, p.scale_log2), nm2 = f2_pack(neg_m, neg_m);
+        f32x2 acc0 = f2_pack(0.0f, 0.0f), acc1 = acc0;           // two running pairs of partial row sums
+        // 32 scores at a time; the load of the next 32 is in flight while these are exponentiated
+        auto quarter = [&](const uint32_t* s, int q) {
+          if (full_tile) {
 #pragma unroll
-        for (int i = 0; i < 64; ++i) mx = fmaxf(mx, __uint_as_float(s[i]));
-      } else {
+            for (int i = 0; i < 16; ++i) {
+              const float s0 = __uint_as_float(s[2 * i]), s1 = __uint_as_float(s[2 * i + 1]);
+              if (with_max) mx = fmaxf(mx, fmaxf(s0, s1));
+              float x0, x1;
+              f2_unpack(f2_fma(f2_pack(s0, s1), c2, nm2), x0, x1);
+              const float p0 = ex2(x0), p1 = ex2(x1);
+              if (i & 1) acc1 = f2_add(acc1, f2_pack(p0, p1)); else acc0 = f2_add(acc0, f2_pack(p0, p1));
+              w[q * 16 + i] = pack2(p0, p1);
+            }
+          } else {
 #pragma unroll
-        for (int i = 0; i < 64; ++i)
-          if (i < vis) mx = fmaxf(mx, __uint_as_float(s[i]));
-      }
-      const float mt = mx * p.scale_log2;
-      SPROF(6);
+            for (int i = 0; i < 16; ++i) {
+              const float s0 = __uint_as_float(s[2 * i]), s1 = __uint_as_float(s[2 * i + 1]);
+              const bool v0 = q * 32 + 2 * i < vis, v1 = q * 32 + 2 * i + 1 < vis;
+              if (with_max) mx = fmaxf(mx, fmaxf(v0 ? s0 : -INFINITY, v1 ? s1 : -INFINITY));
+              const float p0 = v0 ? ex2(fmaf(s0, p.scale_log2, neg_m)) : 0.0f;
+              const float p1 = v1 ? ex2(fmaf(s1, p.scale_log2, neg_m)) : 0.0f;
+              acc0 = f2_add(acc0, f2_pack(p0, p1));
+              w[q * 16 + i] = pack2(p0, p1);
+            }
+          }
+        };
+        uint32_t sa[32], sb[32];
+        tmem_ld_x32(t_s, sa);
+        tmem_ld_wait();
+        tmem_ld_x32(t_s + 32, sb);
+        quarter(sa, 0);
+        tmem_ld_wait();
+        tmem_ld_x32(t_s + 64, sa);
+        quarter(sb, 1);
+        tmem_ld_wait();
+        tmem_ld_x32(t_s + 96, sb);
+        quarter(sa, 2);
+        tmem_ld_wait();
+        quarter(sb, 3);
+        float a0, a1, b0, b1;
+        f2_unpack(acc0, a0, a1);
+        f2_unpack(acc1, b0, b1);
+        sum = (a0 + a1) + (b0 + b1);
+      };
       if (j == 0) {
-        m = mt;
-      } else if (__any_sync(0xFFFFFFFFu, mt > m + 8.0f)) {
-#ifdef MB_ATTN_PROFILE
-        if (aprof_on) APROF_COUNT(11);
-#endif
-        // some row of this warp outgrew its maximum: bring O_t (and l) of the whole warp to the new maxima
-        sm_where = 38;
-        if (!mbar_wait(pv_done(t), (j - 1u) & 1u, abort_smem, tflag, 38)) { ok = false; break; }
-        pv_waited = true;
-        fence_after_sync();
-        const float m_new = fmaxf(m, mt);
-        const float f = (m == -INFINITY || m_new == -INFINITY) ? 0.0f : ex2(m - m_new);
+        // first tile: the maximum first (64 scores at a time), then the probabilities
 #pragma unroll 1
-        for (int c = 0; c < 4; ++c) {
-          uint32_t v[32];
-          tmem_ld_x32(t_pv + c * 32, v);
+        for (int hf = 0; hf < 2; ++hf) {
+          uint32_t s[64];
+          tmem_ld_x32(t_s + hf * 64, s);
+          tmem_ld_x32(t_s + hf * 64 + 32, s + 32);
           tmem_ld_wait();
 #pragma unroll
-          for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) * f);
-          tmem_st_x32(t_pv + c * 32, v);
+          for (int i = 0; i < 64; ++i)
+            if (full_tile || hf * 64 + i < vis) mx = fmaxf(mx, __uint_as_float(s[i]));
         }
-        tmem_st_wait();
-        l *= f;
-        m = m_new;
-      }
-      // probabilities, row sum, bf16 P (two keys per 32-bit column) over the first half of the score buffer
-      float sum = 0.0f;
-      uint32_t w[32];
-      const float neg_m = m == -INFINITY ? -INFINITY : -m;      // a row with nothing visible so far gives p = 0
-      if (full_tile) {
-#pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          const float p0 = ex2(fmaf(__uint_as_float(s[2 * i]), p.scale_log2, neg_m));
-          const float p1 = ex2(fmaf(__uint_as_float(s[2 * i + 1]), p.scale_log2, neg_m));
-          sum += p0 + p1;
-          w[i] = pack2(p0, p1);
-        }
+        m = mx * p.scale_log2;
+        SPROF(6);
+        probabilities(false);
       } else {
+        probabilities(true);
+        const float mt = mx * p.scale_log2;
+        if (__any_sync(0xFFFFFFFFu, mt > m + 8.0f)) {
+#ifdef MB_ATTN_PROFILE
+          if (aprof_on) APROF_COUNT(11);
+#endif
+          // some row of this warp outgrew its maximum: bring O_t (and l) of the whole warp to the new maxima
+          // and take the probabilities again (the scores are still in place: P has not been stored yet)
+          sm_where = 38;
+          if (!mbar_wait(pv_done(t), (j - 1u) & 1u, abort_smem, tflag, 38)) { ok = false; break; }
+          pv_waited = true;
+          fence_after_sync();
+          const float m_new = fmaxf(m, mt);
+          const float f = (m == -INFINITY || m_new == -INFINITY) ? 0.0f : ex2(m - m_new);
+#pragma unroll 1
+          for (int c = 0; c < 4; ++c) {
+            uint32_t v[32];
+            tmem_ld_x32(t_pv + c * 32, v);
+            tmem_ld_wait();
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          float p0 = 0.0f, p1 = 0.0f;
-          if (2 * i < vis) p0 = ex2(fmaf(__uint_as_float(s[2 * i]), p.scale_log2, neg_m));
-          if (2 * i + 1 < vis) p1 = ex2(fmaf(__uint_as_float(s[2 * i + 1]), p.scale_log2, neg_m));
-          sum += p0 + p1;
-          w[i] = pack2(p0, p1);
+            for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) * f);
+            tmem_st_x32(t_pv + c * 32, v);
+          }
+          tmem_st_wait();
+          l *= f;
+          m = m_new;
+          probabilities(false);
         }
       }
-      SPROF(8);
+      // bf16 P (two keys per 32-bit column) over the first 64 columns of the score buffer
       tmem_st_x32(t_s, w);
+      tmem_st_x32(t_s + 32, w + 32);
+      SPROF(8);
       tmem_st_wait();
       SPROF(9);
       l += sum;
