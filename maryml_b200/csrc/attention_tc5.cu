@@ -25,8 +25,11 @@
 // TMEM is rescaled (tcgen05.ld, multiply, tcgen05.st) only when a tile raises a row's maximum
 // by more than that, which after the first tiles is rare; the final O_t / l is exact either way.
 //
-// Warp roles: 0 = TMA producer (Q once, a ring of three K tiles and a ring of two V tiles),
-// 1 = MMA issuer, 2-5 and 6-9 = the two softmax groups (one per query tile).
+// Warp roles: 0 = TMA producer (Q once, a ring of two K tiles and a ring of two V tiles),
+// 1 = MMA issuer, 2-9 and 10-17 = the two softmax groups (one per query tile). A row of 128 scores is shared by
+// two threads (warps w and w + 4 of a group take columns 0-63 and 64-127 of the same TMEM lanes): the chain
+// load -> exponentials -> store of one thread per row was the longest link of the pipeline, and two warps
+// per scheduler and group hide each other's latencies. The pair swaps its maxima through shared memory.
 // Algorithmic work: 4 * nq * keys * 128 flop per head, half under the mask.
 // Every mbarrier wait is bounded.
 #include "attention.cuh"
@@ -41,10 +44,11 @@ constexpr int BOX = 64;                        // key rows of one TMA box (the t
 constexpr int QT = 128;                        // query rows per tile (two tiles per CTA)
 constexpr int HALF = BC * 128;                 // one 64-dim half of a K or V tile: 16 KB
 constexpr int TILE = 2 * HALF;                 // a K tile or a V tile: 32 KB
-constexpr int KSTAGES = 3, VSTAGES = 2;
+constexpr int KSTAGES = 2, VSTAGES = 2;
 constexpr int Q_BYTES = 2 * QT * D * 2;        // 64 KB: [tile][half][128 rows][64 dims]
-constexpr int SMEM = (KSTAGES + VSTAGES) * TILE + Q_BYTES + 1024 + 256;
-constexpr int THREADS = 320;
+constexpr int XCHG_BYTES = 2 * 2 * 2 * 128 * 4; // row maxima (later row sums) the two threads of a row swap: [phase parity][tile][part][row]
+constexpr int SMEM = (KSTAGES + VSTAGES) * TILE + Q_BYTES + XCHG_BYTES + 1024 + 256;
+constexpr int THREADS = 576;                   // producer, issuer, two softmax groups of eight warps
 constexpr int S_COL0 = 0, S_COL1 = 128, PV_COL0 = 256, PV_COL1 = 384, TMEM_COLS = 512;
 
 // Development aid (-DMB_ATTN_PROFILE): cycles per phase, summed over CTAs. Slots: 0 issuer waits K/V, 1 issuer waits
@@ -115,8 +119,9 @@ attn_prefill_tc5_kernel(const __grid_constant__ AttnParams p) {
   uint8_t* gen = smem_raw + (base - smem_u32(smem_raw));
   const uint32_t k_smem = base, v_smem = base + KSTAGES * TILE;
   const uint32_t q_smem = v_smem + VSTAGES * TILE;
-  const uint32_t bar_base = q_smem + Q_BYTES;
-  // barriers: k_full[3], k_empty[3], v_full[2], v_empty[2], q_full, s_full[2], p_full[2], pv_done[2], drain
+  float* xchg = reinterpret_cast<float*>(gen + (q_smem - base) + Q_BYTES);
+  const uint32_t bar_base = q_smem + Q_BYTES + XCHG_BYTES;
+  // barriers: k_full[2], k_empty[2], v_full[2], v_empty[2], q_full, s_full[2], p_full[2], pv_done[2], drain, pair[2][4]
   auto k_full = [&](int s) { return bar_base + 8u * s; };
   auto k_empty = [&](int s) { return bar_base + 8u * (KSTAGES + s); };
   auto v_full = [&](int s) { return bar_base + 8u * (2 * KSTAGES + s); };
@@ -127,7 +132,8 @@ attn_prefill_tc5_kernel(const __grid_constant__ AttnParams p) {
   auto p_full = [&](int t) { return bar_base + 8u * (NB + 3 + t); };
   auto pv_done = [&](int t) { return bar_base + 8u * (NB + 5 + t); };
   const uint32_t drain_bar = bar_base + 8u * (NB + 7);
-  uint32_t* tmem_ptr_smem = reinterpret_cast<uint32_t*>(gen + (bar_base - base) + 8 * (NB + 8));
+  auto pair_bar = [&](int t, uint32_t quad) { return bar_base + 8u * (NB + 8 + 4 * t + quad); };   // the two warps of a row set
+  uint32_t* tmem_ptr_smem = reinterpret_cast<uint32_t*>(gen + (bar_base - base) + 8 * (NB + 16));
   volatile int* abort_smem = reinterpret_cast<volatile int*>(tmem_ptr_smem + 1);
   int* tflag = p.flags ? p.flags + MB_FLAG_WAIT_TIMEOUT : nullptr;
 
@@ -148,8 +154,9 @@ attn_prefill_tc5_kernel(const __grid_constant__ AttnParams p) {
     mbar_init(q_full, 1);
     for (int t = 0; t < 2; ++t) {
       mbar_init(s_full(t), 1);
-      mbar_init(p_full(t), 128);
+      mbar_init(p_full(t), 256);
       mbar_init(pv_done(t), 1);
+      for (uint32_t q = 0; q < 4; ++q) mbar_init(pair_bar(t, q), 64);
     }
     mbar_init(drain_bar, 1);
     *abort_smem = 0;
@@ -288,24 +295,41 @@ attn_prefill_tc5_kernel(const __grid_constant__ AttnParams p) {
     }
   } else {
     // ------------------------------ softmax groups -------------------------------
-    const int t = (warp - 2) >> 2;                        // query tile of this group
+    const int t = (warp - 2) >> 3;                        // query tile of this group
+    const uint32_t part = uint32_t(warp - 2) >> 2 & 1u;   // which 64 of the row's 128 scores this thread takes
     const uint32_t quad = warp & 3u;                      // TMEM lane quadrant of this warp
     const uint32_t r = quad * 32u + lane;                 // row within the tile
     const uint32_t row = q_row0 + t * QT + r;             // row within the sequence's queries
     const int qpos = int(p.q0 + row);
     const uint32_t lane_addr = (quad * 32u) << 16;
-    const uint32_t t_s = tmem_base + lane_addr + (t ? S_COL1 : S_COL0);
-    const uint32_t t_pv = tmem_base + lane_addr + (t ? PV_COL1 : PV_COL0);
-    float m = -INFINITY, l = 0.0f;       // m: the maximum this row currently subtracts (may lag, see header)
+    const uint32_t t_s = tmem_base + lane_addr + (t ? S_COL1 : S_COL0) + part * 64;     // this thread's scores
+    const uint32_t t_p = tmem_base + lane_addr + (t ? S_COL1 : S_COL0) + part * 32;     // and where its P goes
+    const uint32_t t_pv = tmem_base + lane_addr + (t ? PV_COL1 : PV_COL0) + part * 64;  // its half of the output columns
+    float* x_mine = xchg + (t * 2 + part) * 128 + r;
+    const float* x_other = xchg + (t * 2 + (part ^ 1u)) * 128 + r;
+    float m = -INFINITY, l = 0.0f;       // m: the maximum this row currently subtracts (may lag, see header); l: this thread's part of the row sum
+    uint32_t xph = 0;                    // phase of the pair barrier
     bool ok = true;
     uint32_t sm_where = 0, sm_j = 0;
+    // the pair's hand-shake: both threads of a row have published a value and finished their score loads
+    // (two slots by phase parity: a slot is rewritten only after the partner has arrived for the phase in between,
+    // which it does after reading)
+    auto swap = [&](float mine) -> float {
+      const uint32_t slot = (xph & 1u) * (2 * 2 * 128);
+      x_mine[slot] = mine;
+      mbar_arrive(pair_bar(t, quad));
+      sm_where = 42;
+      if (!mbar_wait(pair_bar(t, quad), xph & 1u, abort_smem, tflag, 42)) { ok = false; return mine; }
+      ++xph;
+      return x_other[slot];
+    };
     for (uint32_t j = 0; ok && j < n_tiles; ++j) {
       sm_j = j;
-      const int kabs = int(j * BC);
+      const int kabs = int(j * BC + part * 64);
       int vis = int(p.keys) - kabs;
       if (p.causal) vis = min(vis, qpos + 1 - kabs);
       bool pv_waited = j == 0;           // whether PV(j-1) is known to be complete
-      const bool full_tile = __all_sync(0xFFFFFFFFu, vis >= BC);   // no mask work away from the diagonal
+      const bool full_tile = __all_sync(0xFFFFFFFFu, vis >= 64);   // no mask work away from the diagonal
       sm_where = 37;
 #ifdef MB_ATTN_PROFILE
       long long aprof_t0_ = clock64();
@@ -319,16 +343,14 @@ attn_prefill_tc5_kernel(const __grid_constant__ AttnParams p) {
       fence_after_sync();
       // One pass in the common case: the probabilities are taken against the maximum the row already
       // subtracts (it may lag the true one by 2^8, see the header) while the tile's own maximum is
-      // collected on the side; P stays in registers until the maximum is known to be within reach.
-      // Only the first tile, and a tile that outgrows the lag, read the scores a second time.
-      uint32_t w[64];
+      // collected on the side; P stays in registers until the pair knows the maximum is within reach.
+      uint32_t w[32];
       float sum = 0.0f, mx = -INFINITY;
       auto probabilities = [&](bool with_max) {
         const float neg_m = m == -INFINITY ? -INFINITY : -m;      // a row with nothing visible so far gives p = 0
         const f32x2 c2 = f2_pack(p.scale_log2, p.scale_log2), nm2 = f2_pack(neg_m, neg_m);
         f32x2 acc0 = f2_pack(0.0f, 0.0f), acc1 = acc0;           // two running pairs of partial row sums
-        // 32 scores at a time; the load of the next 32 is in flight while these are exponentiated
-        auto quarter = [&](const uint32_t* s, int q) {
+        auto half = [&](const uint32_t* s, int q) {
           if (full_tile) {
 #pragma unroll
             for (int i = 0; i < 16; ++i) {
@@ -355,46 +377,48 @@ attn_prefill_tc5_kernel(const __grid_constant__ AttnParams p) {
         };
         uint32_t sa[32], sb[32];
         tmem_ld_x32(t_s, sa);
-        tmem_ld_wait();
         tmem_ld_x32(t_s + 32, sb);
-        quarter(sa, 0);
         tmem_ld_wait();
-        tmem_ld_x32(t_s + 64, sa);
-        quarter(sb, 1);
-        tmem_ld_wait();
-        tmem_ld_x32(t_s + 96, sb);
-        quarter(sa, 2);
-        tmem_ld_wait();
-        quarter(sb, 3);
+        half(sa, 0);
+        half(sb, 1);
         float a0, a1, b0, b1;
         f2_unpack(acc0, a0, a1);
         f2_unpack(acc1, b0, b1);
         sum = (a0 + a1) + (b0 + b1);
       };
       if (j == 0) {
-        // first tile: the maximum first (64 scores at a time), then the probabilities
-#pragma unroll 1
-        for (int hf = 0; hf < 2; ++hf) {
-          uint32_t s[64];
-          tmem_ld_x32(t_s + hf * 64, s);
-          tmem_ld_x32(t_s + hf * 64 + 32, s + 32);
+        // first tile: the row maximum first (this thread's 64 scores, then the partner's), then the probabilities
+        {
+          uint32_t sa[32], sb[32];
+          tmem_ld_x32(t_s, sa);
+          tmem_ld_x32(t_s + 32, sb);
           tmem_ld_wait();
 #pragma unroll
-          for (int i = 0; i < 64; ++i)
-            if (full_tile || hf * 64 + i < vis) mx = fmaxf(mx, __uint_as_float(s[i]));
+          for (int i = 0; i < 32; ++i) {
+            if (full_tile || i < vis) mx = fmaxf(mx, __uint_as_float(sa[i]));
+            if (full_tile || 32 + i < vis) mx = fmaxf(mx, __uint_as_float(sb[i]));
+          }
         }
-        m = mx * p.scale_log2;
+        const float other = swap(mx);
+        if (!ok) break;
+        m = fmaxf(mx, other) * p.scale_log2;
         SPROF(6);
         probabilities(false);
+        // the partner may store its P over columns this thread has just read a second time: one more hand-shake
+        (void)swap(0.0f);
+        if (!ok) break;
       } else {
         probabilities(true);
-        const float mt = mx * p.scale_log2;
+        const float other = swap(mx);         // also: both threads are past their score loads
+        if (!ok) break;
+        const float mt = fmaxf(mx, other) * p.scale_log2;
         if (__any_sync(0xFFFFFFFFu, mt > m + 8.0f)) {
 #ifdef MB_ATTN_PROFILE
           if (aprof_on) APROF_COUNT(11);
 #endif
-          // some row of this warp outgrew its maximum: bring O_t (and l) of the whole warp to the new maxima
-          // and take the probabilities again (the scores are still in place: P has not been stored yet)
+          // some row of this warp pair outgrew its maximum (both warps see the same maxima and decide alike):
+          // bring this thread's half of O_t, and l, to the new maxima and take the probabilities again
+          // (the scores are still in place: no P has been stored yet)
           sm_where = 38;
           if (!mbar_wait(pv_done(t), (j - 1u) & 1u, abort_smem, tflag, 38)) { ok = false; break; }
           pv_waited = true;
@@ -402,7 +426,7 @@ attn_prefill_tc5_kernel(const __grid_constant__ AttnParams p) {
           const float m_new = fmaxf(m, mt);
           const float f = (m == -INFINITY || m_new == -INFINITY) ? 0.0f : ex2(m - m_new);
 #pragma unroll 1
-          for (int c = 0; c < 4; ++c) {
+          for (int c = 0; c < 2; ++c) {
             uint32_t v[32];
             tmem_ld_x32(t_pv + c * 32, v);
             tmem_ld_wait();
@@ -414,11 +438,12 @@ attn_prefill_tc5_kernel(const __grid_constant__ AttnParams p) {
           l *= f;
           m = m_new;
           probabilities(false);
+          (void)swap(0.0f);                   // both threads are past their second read of the scores
+          if (!ok) break;
         }
       }
-      // bf16 P (two keys per 32-bit column) over the first 64 columns of the score buffer
-      tmem_st_x32(t_s, w);
-      tmem_st_x32(t_s + 32, w + 32);
+      // bf16 P (two keys per 32-bit column): this thread's 64 keys take 32 columns of the first half of the score buffer
+      tmem_st_x32(t_p, w);
       SPROF(8);
       tmem_st_wait();
       SPROF(9);
@@ -435,13 +460,16 @@ attn_prefill_tc5_kernel(const __grid_constant__ AttnParams p) {
       fence_before_sync();                                 // P in tensor memory, and any O_t rescale, before the PV product
       mbar_arrive(p_full(t));
     }
-    if (!ok && tflag && r == 0 && t == 0) atomicCAS(tflag + 6, 0, int(1u << 30 | sm_where << 20 | sm_j));
+    if (!ok && tflag && r == 0 && t == 0 && part == 0) atomicCAS(tflag + 6, 0, int(1u << 30 | sm_where << 20 | sm_j));
     if (ok && n_tiles > 0) ok = mbar_wait(pv_done(t), (n_tiles - 1u) & 1u, abort_smem, tflag, 40);
     fence_after_sync();
-    const float inv = l > 0.0f ? 1.0f / l : 0.0f;
-    __nv_bfloat16* dst_row = p.out + ((size_t(b) * p.nq + row) * p.heads + h) * D;
+    // the row sum is the pair's
+    float l_row = l;
+    if (ok) l_row += swap(l);
+    const float inv = l_row > 0.0f ? 1.0f / l_row : 0.0f;
+    __nv_bfloat16* dst_row = p.out + ((size_t(b) * p.nq + row) * p.heads + h) * D + part * 64;
 #pragma unroll
-    for (int c = 0; c < 4; ++c) {
+    for (int c = 0; c < 2; ++c) {
       uint32_t v[32];
       tmem_ld_x32(t_pv + c * 32, v);
       tmem_ld_wait();
