@@ -132,7 +132,9 @@ int mb_nvfp4_untile_scales(mb_ctx* ctx, mb_stream stream, const uint8_t* scales_
 
 /* ---- linears ---------------------------------------------------------------------- */
 /* Nvfp4::gemv (src/nn/nvfp4_gemv.rs:202-250, 529-578): [rows<=8, k] x [n, k]^T,
- * W4A16, one warp per output row, f32 carry, x scale2 once, one cast.
+ * W4A16: every product x * (w * block scale) is exact in f32 (the decoded, scaled weight has at most
+ * 7 significant bits), sums carried in f32, x scale2 once, one cast. One to eight rows cost the same
+ * (the rows are the N side of a warp-level tensor-core product over 16 weight rows).
  * x 16-byte aligned, k % 32 == 0. */
 int mb_nvfp4_gemv_w4a16(mb_ctx* ctx, mb_stream stream, const void* x_bf16, size_t rows, const uint8_t* codes,
                         const uint8_t* scales_rowmajor, float scale2, size_t n, size_t k, void* out,

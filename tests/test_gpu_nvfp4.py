@@ -174,9 +174,10 @@ def test_scale_tiling_is_a_bijection(mb, orc):
 
 
 # --------------------------------------------------------------------------- GEMV
+@pytest.mark.parametrize("n,k", [(512, 4096), (200, 96), (33, 4128)])
 @pytest.mark.parametrize("rows", [1, 3, 8])
-def test_gemv_w4a16_against_f64(mb, orc, rows):
-    n, k = 512, 4096
+def test_gemv_w4a16_against_f64(mb, orc, rows, n, k):
+    """(200, 96) and (33, 4128): output rows that do not fill a 16-row block, K that does not fill a 128-value slice."""
     wbits = f32_to_bf16_bits(orc.normal_f32(0x0F16CAFE, n * k, 0.02))
     xbits = f32_to_bf16_bits(orc.normal_f32(21 + rows, rows * k, 1.0))
     q = mb.Nvfp4.quantize(dev_bf16(wbits).view(n, k))
