@@ -53,6 +53,9 @@ struct GemmParams {
   uint32_t scatter_tmax;      // rows of one source slot
   // split-K (few output tiles, long K): tile index carries a K slice; partial sums go to a workspace
   uint32_t splits, ks_per_split;
+  // tile order: 0 = row tiles fastest (dense), 1 = column tiles fastest (grouped: the CTAs that run together share a
+  // row tile of activations and the column tiles of one expert, so both operands come from DRAM once)
+  uint32_t n_fastest;
   // stacked projections / fused output quantization
   const float* colscale;      // [n] per-column factor or null
   uint8_t* out_sf;            // tiled scale plane of the quantized output
@@ -330,17 +333,19 @@ gemm_tc5_kernel(const __grid_constant__ GemmParams p) {
     // Grouped products: the expert of a tile comes from device memory; it is fetched one tile
     // ahead so that its latency never sits between two tiles' loads.
     int e_next = 0;
-    if (p.tile_expert && blockIdx.x < total_tiles) e_next = p.tile_expert[blockIdx.x % m_tiles];
+    auto row_tile = [&](uint32_t tl) { return p.n_fastest ? tl / p.n_tiles : tl % m_tiles; };   // splits is 1 when grouped
+    if (p.tile_expert && blockIdx.x < total_tiles) e_next = p.tile_expert[row_tile(blockIdx.x)];
     for (uint32_t tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
       const uint32_t sp = tile % p.splits, rest = tile / p.splits;
-      const uint32_t mt = rest % m_tiles, nt = rest / m_tiles;
+      const uint32_t mt = p.n_fastest ? rest / p.n_tiles : rest % m_tiles;
+      const uint32_t nt = p.n_fastest ? rest % p.n_tiles : rest / m_tiles;
       const uint32_t ks0 = sp * p.ks_per_split, ks1 = min(p.k_steps, ks0 + p.ks_per_split);
       uint32_t brow = nt * BN;
       const uint8_t* sfb = p.sfb;
       if (p.tile_expert) {
         int e = e_next;
         const uint32_t nxt = tile + gridDim.x;
-        if (nxt < total_tiles) e_next = p.tile_expert[nxt % m_tiles];
+        if (nxt < total_tiles) e_next = p.tile_expert[row_tile(nxt)];
         if (e < 0) e = 0;
         brow += uint32_t(e) * p.b_rows_per_expert;
         sfb += uint64_t(e) * p.sfb_expert_stride;
@@ -459,7 +464,8 @@ gemm_tc5_kernel(const __grid_constant__ GemmParams p) {
     bool ok = true;
     for (uint32_t tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x, ++it) {
       const uint32_t sp = tile % p.splits, rest = tile / p.splits;
-      const uint32_t mt = rest % m_tiles, nt = rest / m_tiles;
+      const uint32_t mt = p.n_fastest ? rest / p.n_tiles : rest % m_tiles;
+      const uint32_t nt = p.n_fastest ? rest % p.n_tiles : rest / m_tiles;
       const uint32_t buf = it & 1u;
       float alpha = p.alpha;
       if (p.tile_expert) {
@@ -960,6 +966,7 @@ int gemm_w4a4_common(mb_ctx* ctx, cudaStream_t stream, const uint8_t* a_codes, c
                           size_t(step & 1) * half;
   }
   p.splits = 1; p.ks_per_split = p.k_steps;
+  p.n_fastest = tile_expert ? 1u : 0u;
   if (workspace && epilogue == MB_EPI_PLAIN && !tile_expert) {
     const uint32_t sk = splitk_factor(ctx->sm_count, m, n, k);
     if (sk > 1 && workspace_bytes >= size_t(sk) * m * n * sizeof(float)) {
