@@ -108,7 +108,7 @@ def test_upload_round_trip_and_refusals(mb, orc):
 
 
 @pytest.mark.parametrize("dtype", ["bf16", "f32"])
-@pytest.mark.parametrize("rows,k", [(1, 64), (37, 256), (130, 2048)])
+@pytest.mark.parametrize("rows,k", [(1, 64), (37, 256), (130, 2048), (5, 48), (7, 96), (300, 14336)])
 def test_activation_quantizers_bit_exact(mb, orc, dtype, rows, k):
     from maryml_b200 import _lib
     x32 = orc.normal_f32(100 + rows, rows * k, 1.0)
