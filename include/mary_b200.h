@@ -238,6 +238,13 @@ size_t mb_attention_workspace(size_t batch, size_t nq, size_t keys, size_t heads
 int mb_attention(mb_ctx* ctx, mb_stream stream, const void* q, const void* k, const void* v, size_t batch,
                  size_t nq, size_t keys, size_t heads, size_t kv_heads, size_t d, size_t q0, float scale,
                  int causal, void* out, void* workspace, size_t workspace_bytes);
+/* The same with a sliding window (banded_attention_kernel src/models/inkling/banded.rs:109-245 and the window
+ * term of flash.rs:751-785): the query at position q sees the keys in (q - window, q]. Causal by definition;
+ * keys >= q0 + nq. Key tiles wholly below the window are neither loaded nor multiplied; the decode splits
+ * share only the window's keys. Workspace as for mb_attention (its size is an upper bound here). */
+int mb_attention_window(mb_ctx* ctx, mb_stream stream, const void* q, const void* k, const void* v, size_t batch,
+                        size_t nq, size_t keys, size_t heads, size_t kv_heads, size_t d, size_t q0, float scale,
+                        size_t window, void* out, void* workspace, size_t workspace_bytes);
 
 /* Decode attention without any allocation; it has no counterpart in the reference.
  * For hosts that gave all device memory to their own arena at start-up and may not

@@ -55,6 +55,7 @@ SIGNATURES = {
     "mb_moe_scatter_weighted": (_i, [_vp, _vp, _vp, _i, _vp, _vp, _sz, _sz, _sz, _vp]),
     "mb_attention_workspace": (_sz, [_sz, _sz, _sz, _sz, _sz, _sz]),
     "mb_attention": (_i, [_vp, _vp, _vp, _vp, _vp, _sz, _sz, _sz, _sz, _sz, _sz, _sz, _f, _i, _vp, _vp, _sz]),
+    "mb_attention_window": (_i, [_vp, _vp, _vp, _vp, _vp, _sz, _sz, _sz, _sz, _sz, _sz, _sz, _f, _sz, _vp, _vp, _sz]),
     "mb_attention_decode_static": (_i, [_vp, _vp, _vp, _vp, _vp, _sz, _sz, _sz, _sz, _sz, _sz, _sz, _f, _i, _vp]),
     "mb_rmsnorm": (_i, [_vp, _vp, _vp, _vp, _sz, _sz, _f, _vp]),
     "mb_add": (_i, [_vp, _vp, _vp, _vp, _sz, _vp]),

@@ -14,9 +14,10 @@ from ._lib import lib, context
 from .nvfp4 import _p, _stream
 
 
-def flash_attention(q, k, v, q0=0, scale=None, causal=True, workspace=None):
+def flash_attention(q, k, v, q0=0, scale=None, causal=True, workspace=None, window=0):
     """q [batch, nq, heads, D], k/v [batch, keys, kv_heads, D] bf16 -> out like q.
-    Query i sits at absolute position q0 + i, key j at j."""
+    Query i sits at absolute position q0 + i, key j at j. window > 0: the query at position p sees the keys
+    in (p - window, p] only (sliding-window attention; causal)."""
     assert q.dtype == k.dtype == v.dtype == torch.bfloat16
     assert q.is_contiguous() and k.is_contiguous() and v.is_contiguous()
     batch, nq, heads, d = q.shape
@@ -28,6 +29,11 @@ def flash_attention(q, k, v, q0=0, scale=None, causal=True, workspace=None):
     need = int(lib.mb_attention_workspace(batch, nq, keys, heads, kv_heads, d))
     if need and (workspace is None or workspace.numel() < need):
         workspace = torch.empty(need, dtype=torch.uint8, device=q.device)
+    if window:
+        assert causal, "a sliding window is a causal window"
+        ctx.check(lib.mb_attention_window(ctx.handle, _stream(), _p(q), _p(k), _p(v), batch, nq, keys, heads, kv_heads, d,
+                                          q0, float(scale), int(window), _p(out), _p(workspace) if need else None, need))
+        return out
     ctx.check(lib.mb_attention(ctx.handle, _stream(), _p(q), _p(k), _p(v), batch, nq, keys, heads, kv_heads, d, q0,
                                float(scale), int(causal), _p(out), _p(workspace) if need else None, need))
     return out

@@ -104,7 +104,7 @@ __device__ __forceinline__ void pv_tile(float (*o)[4], const float (*pfrag)[4], 
 // Rows g (regs 0, 1) and g + 8 (regs 2, 3); mask_lo/hi = number of visible keys from `kbase` for those rows.
 template <int NT>
 __device__ __forceinline__ void softmax_step(float (*s)[4], float (*o)[4], float* m, float* l, float scale_log2,
-                                             int vis_lo, int vis_hi, uint32_t lane) {
+                                             int vis_lo, int vis_hi, uint32_t lane, int first_lo = 0, int first_hi = 0) {
   const int t2 = (lane & 3) * 2;
   float mx[2] = {-INFINITY, -INFINITY};
 #pragma unroll
@@ -112,8 +112,8 @@ __device__ __forceinline__ void softmax_step(float (*s)[4], float (*o)[4], float
 #pragma unroll
     for (int e = 0; e < 4; ++e) {
       const int key = j * 8 + t2 + (e & 1);
-      const int vis = e < 2 ? vis_lo : vis_hi;
-      s[j][e] = key < vis ? s[j][e] * scale_log2 : -INFINITY;
+      const int vis = e < 2 ? vis_lo : vis_hi, first = e < 2 ? first_lo : first_hi;   // first: keys below the window
+      s[j][e] = (key < vis && key >= first) ? s[j][e] * scale_log2 : -INFINITY;
       mx[e >> 1] = fmaxf(mx[e >> 1], s[j][e]);
     }
   }
@@ -177,7 +177,7 @@ attn_decode_kernel(const __grid_constant__ AttnParams p) {
   const uint32_t rows = p.nq * group;                      // <= 16
   // keys this query block can see at all, and this CTA's slice of them
   const uint32_t visible = p.causal ? min(p.keys, p.q0 + p.nq) : p.keys;
-  const uint32_t k_begin = split * p.keys_per_split;
+  const uint32_t k_begin = p.k_lo + split * p.keys_per_split;
   const uint32_t k_end = min(visible, k_begin + p.keys_per_split);
   const uint32_t n_tiles = k_end > k_begin ? (k_end - k_begin + BC - 1) / BC : 0;
 
@@ -249,7 +249,12 @@ attn_decode_kernel(const __grid_constant__ AttnParams p) {
         vis_lo = min(vis_lo, int(qpos_lo) + 1 - kabs);
         vis_hi = min(vis_hi, int(qpos_hi) + 1 - kabs);
       }
-      softmax_step<2>(s, o, m, l, p.scale_log2, vis_lo, vis_hi, lane);
+      int first_lo = 0, first_hi = 0;
+      if (p.window) {
+        first_lo = int(qpos_lo) + 1 - int(p.window) - kabs;
+        first_hi = int(qpos_hi) + 1 - int(p.window) - kabs;
+      }
+      softmax_step<2>(s, o, m, l, p.scale_log2, vis_lo, vis_hi, lane, first_lo, first_hi);
       pv_tile<1>(o, s, s0 + 2 * TILE_HALF_BYTES, key0, lane);
       __syncwarp();
       if (lane == 0) mbar_arrive(empty_bar(stage));
@@ -498,10 +503,13 @@ MB_API size_t mb_attention_workspace(size_t batch, size_t nq, size_t keys, size_
   return batch * kv_heads * size_t(decode_splits(batch, kv_heads, keys)) * 16 * (D + 2) * sizeof(float);
 }
 
-MB_API int mb_attention(mb_ctx* ctx, mb_stream stream_, const void* q, const void* k, const void* v, size_t batch,
-                        size_t nq, size_t keys, size_t heads, size_t kv_heads, size_t d, size_t q0, float scale,
-                        int causal, void* out, void* workspace, size_t workspace_bytes) {
+static int attention_common(mb_ctx* ctx, mb_stream stream_, const void* q, const void* k, const void* v, size_t batch,
+                            size_t nq, size_t keys, size_t heads, size_t kv_heads, size_t d, size_t q0, float scale,
+                            int causal, size_t window, void* out, void* workspace, size_t workspace_bytes) {
   cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  MB_REQUIRE(ctx, window == 0 || causal, "attention: a sliding window is a causal window");
+  MB_REQUIRE(ctx, window < (1ull << 31), "attention: bad window");
+  MB_REQUIRE(ctx, window == 0 || keys >= q0 + nq, "attention: with a window every query needs its own key in the cache");
   MB_REQUIRE(ctx, ctx && q && k && v && out, "attention: null argument");
   MB_REQUIRE(ctx, d == D, "attention: head_dim must be 128, got %zu", d);
   MB_REQUIRE(ctx, batch > 0 && nq > 0 && keys > 0 && heads > 0 && kv_heads > 0 && heads % kv_heads == 0,
@@ -523,17 +531,21 @@ MB_API int mb_attention(mb_ctx* ctx, mb_stream stream_, const void* q, const voi
   p.batch = uint32_t(batch); p.nq = uint32_t(nq); p.keys = uint32_t(keys); p.heads = uint32_t(heads);
   p.kv_heads = uint32_t(kv_heads); p.q0 = uint32_t(q0); p.causal = causal;
   p.scale_log2 = scale * 1.4426950408889634f;
+  p.window = uint32_t(window);
+  // the first key the call's first query can see, on a tile boundary
+  p.k_lo = (window && q0 + 1 > window) ? uint32_t((q0 + 1 - window) / BC * BC) : 0u;
   const size_t group = heads / kv_heads;
   static bool attr_dec[16] = {}, attr_pre[16] = {};
   if (nq * group <= 16) {
-    uint32_t splits = decode_splits(batch, kv_heads, keys);
+    const size_t span = keys > p.k_lo ? keys - p.k_lo : 1;   // keys the splits share (the window's, when there is one)
+    uint32_t splits = decode_splits(batch, kv_heads, span);
     size_t need = batch * kv_heads * splits * 16 * (D + 2) * sizeof(float);
     if (splits > 1) {
       MB_REQUIRE(ctx, workspace && workspace_bytes >= need, "attention: decode needs %zu workspace bytes", need);
       MB_REQUIRE(ctx, mb_aligned(workspace, 16), "attention: workspace needs 16-byte alignment");
     }
     p.splits = splits;
-    p.keys_per_split = uint32_t(((keys + splits - 1) / splits + BC - 1) / BC * BC);
+    p.keys_per_split = uint32_t(((span + splits - 1) / splits + BC - 1) / BC * BC);
     p.part = static_cast<float*>(workspace);
     if (!attr_dec[ctx->device & 15]) {
       MB_CUDA_OK(ctx, cudaFuncSetAttribute(attn_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, DEC_SMEM));
@@ -553,6 +565,7 @@ MB_API int mb_attention(mb_ctx* ctx, mb_stream stream_, const void* q, const voi
     p.splits = 1;
     return mb_attention_prefill_tc5(ctx, stream, p);
   } else {
+    MB_REQUIRE(ctx, window == 0, "attention: the comparison (mma.sync) prefill kernel has no sliding window");
     rc = make_tmap_4d(ctx, &p.tmap_q, q, batch, nq, heads, BR);
     if (rc) return rc;
     p.splits = 1;
@@ -565,6 +578,20 @@ MB_API int mb_attention(mb_ctx* ctx, mb_stream stream_, const void* q, const voi
     MB_LAUNCH_OK(ctx);
   }
   return MB_OK;
+}
+
+MB_API int mb_attention(mb_ctx* ctx, mb_stream stream, const void* q, const void* k, const void* v, size_t batch,
+                        size_t nq, size_t keys, size_t heads, size_t kv_heads, size_t d, size_t q0, float scale,
+                        int causal, void* out, void* workspace, size_t workspace_bytes) {
+  return attention_common(ctx, stream, q, k, v, batch, nq, keys, heads, kv_heads, d, q0, scale, causal, 0, out, workspace,
+                          workspace_bytes);
+}
+
+MB_API int mb_attention_window(mb_ctx* ctx, mb_stream stream, const void* q, const void* k, const void* v, size_t batch,
+                               size_t nq, size_t keys, size_t heads, size_t kv_heads, size_t d, size_t q0, float scale,
+                               size_t window, void* out, void* workspace, size_t workspace_bytes) {
+  return attention_common(ctx, stream, q, k, v, batch, nq, keys, heads, kv_heads, d, q0, scale, 1, window, out, workspace,
+                          workspace_bytes);
 }
 
 // ---------------------------------------------------------------------------------

@@ -15,6 +15,9 @@ struct AttnParams {
   uint32_t batch, nq, keys, heads, kv_heads, q0, splits, keys_per_split;
   float scale_log2;     // scale * log2(e)
   int causal;
+  // sliding window (0 = none): query at position q sees keys in (q - window, q]; k_lo = first key any query of
+  // the call can see, rounded down to a tile (the decode splits start there)
+  uint32_t window, k_lo;
 };
 
 __device__ __forceinline__ void tma_load_4d(uint32_t dst, const void* tmap, int c0, int c1, int c2, int c3,

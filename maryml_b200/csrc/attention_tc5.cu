@@ -146,7 +146,10 @@ attn_prefill_tc5_kernel(const __grid_constant__ AttnParams p) {
   const uint32_t q_rows = min(uint32_t(2 * QT), p.nq - q_row0);
   const uint32_t last_q = p.q0 + q_row0 + q_rows - 1;
   const uint32_t k_end = p.causal ? min(p.keys, last_q + 1) : p.keys;
-  const uint32_t n_tiles = (k_end + BC - 1) / BC;
+  // with a sliding window the block's first query row bounds the keys from below: whole tiles under it are skipped
+  const uint32_t first_q = p.q0 + q_row0;
+  const uint32_t j_start = (p.window && first_q + 1 > p.window) ? (first_q + 1 - p.window) / BC : 0u;
+  const uint32_t n_tiles = (k_end + BC - 1) / BC - j_start;   // >= 1: the window holds at least the row's own key
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < KSTAGES; ++s) { mbar_init(k_full(s), 1); mbar_init(k_empty(s), 1); }
@@ -193,7 +196,7 @@ attn_prefill_tc5_kernel(const __grid_constant__ AttnParams p) {
         for (int hf = 0; hf < 2; ++hf)
 #pragma unroll
           for (int bx = 0; bx < 2; ++bx)
-            tma_load_4d(dst + hf * HALF + bx * (BOX * 128), tm, hf * 64, int(kvh), int(j * BC + bx * BOX), int(b), bar);
+            tma_load_4d(dst + hf * HALF + bx * (BOX * 128), tm, hf * 64, int(kvh), int((j + j_start) * BC + bx * BOX), int(b), bar);
       }
       __syncwarp();
     };
@@ -325,11 +328,12 @@ attn_prefill_tc5_kernel(const __grid_constant__ AttnParams p) {
     };
     for (uint32_t j = 0; ok && j < n_tiles; ++j) {
       sm_j = j;
-      const int kabs = int(j * BC + part * 64);
+      const int kabs = int((j + j_start) * BC + part * 64);
       int vis = int(p.keys) - kabs;
       if (p.causal) vis = min(vis, qpos + 1 - kabs);
+      const int first = p.window ? qpos + 1 - int(p.window) - kabs : 0;   // keys [first, vis) of this thread's 64 are visible
       bool pv_waited = j == 0;           // whether PV(j-1) is known to be complete
-      const bool full_tile = __all_sync(0xFFFFFFFFu, vis >= 64);   // no mask work away from the diagonal
+      const bool full_tile = __all_sync(0xFFFFFFFFu, vis >= 64 && first <= 0);   // no mask work away from the band's edges
       sm_where = 37;
 #ifdef MB_ATTN_PROFILE
       long long aprof_t0_ = clock64();
@@ -366,7 +370,8 @@ attn_prefill_tc5_kernel(const __grid_constant__ AttnParams p) {
 #pragma unroll
             for (int i = 0; i < 16; ++i) {
               const float s0 = __uint_as_float(s[2 * i]), s1 = __uint_as_float(s[2 * i + 1]);
-              const bool v0 = q * 32 + 2 * i < vis, v1 = q * 32 + 2 * i + 1 < vis;
+              const int i0 = q * 32 + 2 * i, i1 = i0 + 1;
+              const bool v0 = i0 < vis && i0 >= first, v1 = i1 < vis && i1 >= first;
               if (with_max) mx = fmaxf(mx, fmaxf(v0 ? s0 : -INFINITY, v1 ? s1 : -INFINITY));
               const float p0 = v0 ? ex2(fmaf(s0, p.scale_log2, neg_m)) : 0.0f;
               const float p1 = v1 ? ex2(fmaf(s1, p.scale_log2, neg_m)) : 0.0f;
@@ -395,8 +400,8 @@ attn_prefill_tc5_kernel(const __grid_constant__ AttnParams p) {
           tmem_ld_wait();
 #pragma unroll
           for (int i = 0; i < 32; ++i) {
-            if (full_tile || i < vis) mx = fmaxf(mx, __uint_as_float(sa[i]));
-            if (full_tile || 32 + i < vis) mx = fmaxf(mx, __uint_as_float(sb[i]));
+            if (full_tile || (i < vis && i >= first)) mx = fmaxf(mx, __uint_as_float(sa[i]));
+            if (full_tile || (32 + i < vis && 32 + i >= first)) mx = fmaxf(mx, __uint_as_float(sb[i]));
           }
         }
         const float other = swap(mx);

@@ -27,16 +27,16 @@ def _qkv(orc, seed, batch, nq, keys, heads, kvh, D=128):
     return q, k, v
 
 
-def _check(att, orc, q, k, v, batch, nq, keys, heads, kvh, q0, causal=True, D=128):
+def _check(att, orc, q, k, v, batch, nq, keys, heads, kvh, q0, causal=True, D=128, window=0):
     qd = dev_bf16(q).view(batch, nq, heads, D)
     kd = dev_bf16(k).view(batch, keys, kvh, D)
     vd = dev_bf16(v).view(batch, keys, kvh, D)
-    out = att.flash_attention(qd, kd, vd, q0=q0, causal=causal)
+    out = att.flash_attention(qd, kd, vd, q0=q0, causal=causal, window=window)
     got = bf16_bits_to_f32(host_bits(out)).reshape(batch, nq, heads * D)
     scale = 1.0 / math.sqrt(D)
     for b in range(batch):
         ref = orc.attention(bf16_bits_to_f32(q[b]), bf16_bits_to_f32(k[b]), bf16_bits_to_f32(v[b]), heads, kvh, D,
-                            q0 if causal else keys + nq, scale)
+                            q0 if causal else keys + nq, scale, window=window)
         # bf16 probabilities and a bf16 output: 2^-8 relative on values of O(1/sqrt(visible keys))
         err = np.abs(got[b] - ref).max()
         assert err <= 2e-2 * max(np.abs(ref).max(), 1e-3), (b, err, np.abs(ref).max())
@@ -55,6 +55,21 @@ def test_decode_attention(mods, orc, batch, nq, keys, heads, kvh, q0):
     att, _ = mods
     q, k, v = _qkv(orc, 11 * keys + nq, batch, nq, keys, heads, kvh)
     _check(att, orc, q, k, v, batch, nq, keys, heads, kvh, q0)
+
+
+@pytest.mark.parametrize("batch,nq,keys,heads,kvh,q0,window", [
+    (2, 1, 5000, 8, 2, 4999, 1024),     # decode: the splits share only the window's keys
+    (1, 1, 300, 4, 1, 299, 64),
+    (2, 2, 700, 8, 2, 650, 100),        # two queries, keys beyond them in the cache
+    (1, 600, 600, 4, 1, 0, 200),        # prompt: the band skips whole key tiles below it
+    (2, 300, 1000, 8, 2, 700, 129),     # prompt after a prefix, window edge inside a tile
+    (1, 257, 257, 4, 4, 0, 1),          # a window of one key: every query sees itself only
+])
+def test_sliding_window_attention(mods, orc, batch, nq, keys, heads, kvh, q0, window):
+    """mb_attention_window against the CPU rule (query p sees keys in (p - window, p])."""
+    att, _ = mods
+    q, k, v = _qkv(orc, 13 * keys + nq + window, batch, nq, keys, heads, kvh)
+    _check(att, orc, q, k, v, batch, nq, keys, heads, kvh, q0, window=window)
 
 
 @pytest.mark.parametrize("batch,nq,heads,kvh", [(1, 128, 4, 1), (2, 200, 8, 2), (1, 515, 4, 4)])
