@@ -207,6 +207,17 @@ int mb_bf16_gemm_splitk(mb_ctx* ctx, mb_stream stream, const void* a_bf16, const
 int mb_router_topk_softmax(mb_ctx* ctx, mb_stream stream, const float* logits, size_t tokens, size_t n_experts,
                            size_t k, int renormalize, float scaling, int32_t* idx, float* weight);
 
+/* The same route with the activation chosen and the selection bias of the `noaux_tc` gate
+ * (src/models/k3/router.rs:343-446, RouterActivation::{Sigmoid, Softmax} and
+ * Router::scores_for_choice): sigmoid scores are f32(1 / (1 + exp(-f64(x)))) per expert;
+ * `bias` ([n_experts] f32, or NULL) is added to the scores for the SELECTION only, the
+ * weights are gathered from the unbiased scores. A non-finite logit or biased score
+ * raises the router flag. */
+enum { MB_ROUTER_SOFTMAX = 0, MB_ROUTER_SIGMOID = 1 };
+int mb_router_topk(mb_ctx* ctx, mb_stream stream, const float* logits, const float* bias, int activation,
+                   size_t tokens, size_t n_experts, size_t k, int renormalize, float scaling, int32_t* idx,
+                   float* weight);
+
 /* RowPlan::build / plan_from_topk (src/models/inkling/moegroup.rs:1850-1909,
  * src/models/inkling/devplan.rs:216-301), on the device for any token count:
  * rows stacked expert-ascending then token-ascending, each expert padded to 128

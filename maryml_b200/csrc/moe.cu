@@ -12,18 +12,19 @@ namespace {
 // v_i = f32(e_i); s = sum of e_i in index order (f64); score_i = f32(f64(v_i) / s).
 // Selection: descending score, ties to the lower index. Weights: gathered scores,
 // w / (sum + 1e-20) in selection order, times the scaling factor.
+// The sigmoid form scores each expert alone: f32(1 / (1 + exp(-f64(x)))). With a bias the
+// selection runs on score + bias (one f32 add) while the weights stay the unbiased scores.
 // ---------------------------------------------------------------------------------
-template <int EPL>
+template <int EPL, bool SIGMOID>
 __global__ void __launch_bounds__(128)
-router_softmax_topk_kernel(const float* __restrict__ logits, uint32_t tokens, uint32_t n_experts, uint32_t k,
-                           int renormalize, float scaling, int32_t* __restrict__ idx, float* __restrict__ weight,
-                           int* __restrict__ flag) {
+router_topk_kernel(const float* __restrict__ logits, const float* __restrict__ bias, uint32_t tokens,
+                   uint32_t n_experts, uint32_t k, int renormalize, float scaling, int32_t* __restrict__ idx,
+                   float* __restrict__ weight, int* __restrict__ flag) {
   const uint32_t lane = threadIdx.x & 31;
   const uint32_t t = blockIdx.x * 4 + (threadIdx.x >> 5);
   if (t >= tokens) return;
   const float* row = logits + size_t(t) * n_experts;
   float x[EPL];
-  double e[EPL];
   bool bad = false;
   double m = -INFINITY;
 #pragma unroll
@@ -34,24 +35,36 @@ router_softmax_topk_kernel(const float* __restrict__ logits, uint32_t tokens, ui
   }
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) m = fmax(m, __shfl_xor_sync(0xFFFFFFFFu, m, o));
+  float v[EPL];
+  if constexpr (SIGMOID) {
+#pragma unroll
+    for (int j = 0; j < EPL; ++j) v[j] = float(1.0 / (1.0 + exp(-double(x[j]))));
+  } else {
+    double e[EPL];
+#pragma unroll
+    for (int j = 0; j < EPL; ++j) {
+      e[j] = exp(double(x[j]) - m);
+      v[j] = float(e[j]);
+    }
+    // Sum in expert-index order: expert i sits in lane i % 32, slot i / 32.
+    double s = 0.0;
+#pragma unroll
+    for (int j = 0; j < EPL; ++j) {
+#pragma unroll 8
+      for (int l = 0; l < 32; ++l) s += __shfl_sync(0xFFFFFFFFu, e[j], l);
+    }
+#pragma unroll
+    for (int j = 0; j < EPL; ++j) v[j] = float(double(v[j]) / s);
+  }
+  float c[EPL];   // what the selection compares
+#pragma unroll
+  for (int j = 0; j < EPL; ++j) {
+    c[j] = bias ? v[j] + __ldg(bias + lane + 32 * j) : v[j];
+    if (!(fabsf(c[j]) <= 3.4028234663852886e38f)) bad = true;
+  }
   if (__any_sync(0xFFFFFFFFu, bad)) {
     if (lane == 0) atomicCAS(flag, 0, int(t) + 1);
   }
-  float v[EPL];
-#pragma unroll
-  for (int j = 0; j < EPL; ++j) {
-    e[j] = exp(double(x[j]) - m);
-    v[j] = float(e[j]);
-  }
-  // Sum in expert-index order: expert i sits in lane i % 32, slot i / 32.
-  double s = 0.0;
-#pragma unroll
-  for (int j = 0; j < EPL; ++j) {
-#pragma unroll 8
-    for (int l = 0; l < 32; ++l) s += __shfl_sync(0xFFFFFFFFu, e[j], l);
-  }
-#pragma unroll
-  for (int j = 0; j < EPL; ++j) v[j] = float(double(v[j]) / s);
 
   // k rounds of warp arg-max on (score desc, index asc).
   uint32_t taken = 0;   // bit j: slot j of this lane already selected
@@ -59,29 +72,32 @@ router_softmax_topk_kernel(const float* __restrict__ logits, uint32_t tokens, ui
   float my_w = 0.0f;    // lane r keeps the weight of pick r (k <= 32)
   int my_i = 0;
   for (uint32_t r = 0; r < k; ++r) {
-    float best = -INFINITY;
+    float best = -INFINITY, best_v = 0.0f;
     uint32_t best_i = 0xFFFFFFFFu;
 #pragma unroll
     for (int j = 0; j < EPL; ++j) {
       uint32_t i = lane + 32 * j;
       bool free_slot = !((taken >> j) & 1u);
-      if (free_slot && (v[j] > best || (v[j] == best && i < best_i) || best_i == 0xFFFFFFFFu)) {
-        best = v[j];
+      if (free_slot && (c[j] > best || (c[j] == best && i < best_i) || best_i == 0xFFFFFFFFu)) {
+        best = c[j];
+        best_v = v[j];
         best_i = i;
       }
     }
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) {
       float ob = __shfl_xor_sync(0xFFFFFFFFu, best, o);
+      float ov = __shfl_xor_sync(0xFFFFFFFFu, best_v, o);
       uint32_t oi = __shfl_xor_sync(0xFFFFFFFFu, best_i, o);
       if (oi != 0xFFFFFFFFu && (best_i == 0xFFFFFFFFu || ob > best || (ob == best && oi < best_i))) {
         best = ob;
+        best_v = ov;
         best_i = oi;
       }
     }
     if ((best_i & 31u) == lane) taken |= 1u << (best_i >> 5);
-    wsum += best;   // selection order, as the CPU rule sums
-    if (lane == r) { my_w = best; my_i = int(best_i); }
+    wsum += best_v;   // selection order, as the CPU rule sums; the unbiased score
+    if (lane == r) { my_w = best_v; my_i = int(best_i); }
   }
   if (k > 1 && renormalize) my_w = __fdiv_rn(my_w, wsum + 1e-20f);
   if (scaling != 1.0f) my_w *= scaling;
@@ -260,20 +276,27 @@ scatter_weighted_kernel(const Y* __restrict__ y, const float* __restrict__ row_w
 
 }  // namespace
 
-MB_API int mb_router_topk_softmax(mb_ctx* ctx, mb_stream stream_, const float* logits, size_t tokens,
-                                  size_t n_experts, size_t k, int renormalize, float scaling, int32_t* idx,
-                                  float* weight) {
+MB_API int mb_router_topk(mb_ctx* ctx, mb_stream stream_, const float* logits, const float* bias, int activation,
+                          size_t tokens, size_t n_experts, size_t k, int renormalize, float scaling, int32_t* idx,
+                          float* weight) {
   cudaStream_t stream = static_cast<cudaStream_t>(stream_);
   MB_REQUIRE(ctx, ctx && logits && idx && weight, "router: null argument");
+  MB_REQUIRE(ctx, activation == MB_ROUTER_SOFTMAX || activation == MB_ROUTER_SIGMOID,
+             "router: activation %d is neither softmax nor sigmoid", activation);
   MB_REQUIRE(ctx, tokens > 0, "router: select() on zero tokens");
   MB_REQUIRE(ctx, n_experts >= 32 && n_experts % 32 == 0 && n_experts <= 512,
              "router: n_experts must be a multiple of 32 up to 512, got %zu", n_experts);
   MB_REQUIRE(ctx, k >= 1 && k <= 32 && k <= n_experts, "router: top_k must be 1..32, got %zu", k);
   unsigned grid = unsigned((tokens + 3) / 4);
   int* flag = ctx->flags_dev + MB_FLAG_ROUTER_NONFINITE;
-#define ROUTE(EPL)                                                                                            \
-  router_softmax_topk_kernel<EPL><<<grid, 128, 0, stream>>>(logits, uint32_t(tokens), uint32_t(n_experts),   \
-                                                            uint32_t(k), renormalize, scaling, idx, weight, flag)
+  const bool sigmoid = activation == MB_ROUTER_SIGMOID;
+#define ROUTE(EPL)                                                                                              \
+  if (sigmoid)                                                                                                  \
+    router_topk_kernel<EPL, true><<<grid, 128, 0, stream>>>(logits, bias, uint32_t(tokens), uint32_t(n_experts), \
+                                                            uint32_t(k), renormalize, scaling, idx, weight, flag); \
+  else                                                                                                          \
+    router_topk_kernel<EPL, false><<<grid, 128, 0, stream>>>(logits, bias, uint32_t(tokens), uint32_t(n_experts), \
+                                                             uint32_t(k), renormalize, scaling, idx, weight, flag)
   switch (n_experts / 32) {
     case 1: ROUTE(1); break;
     case 2: ROUTE(2); break;
@@ -288,6 +311,13 @@ MB_API int mb_router_topk_softmax(mb_ctx* ctx, mb_stream stream_, const float* l
 #undef ROUTE
   MB_LAUNCH_OK(ctx);
   return MB_OK;
+}
+
+MB_API int mb_router_topk_softmax(mb_ctx* ctx, mb_stream stream, const float* logits, size_t tokens,
+                                  size_t n_experts, size_t k, int renormalize, float scaling, int32_t* idx,
+                                  float* weight) {
+  return mb_router_topk(ctx, stream, logits, nullptr, MB_ROUTER_SOFTMAX, tokens, n_experts, k, renormalize, scaling,
+                        idx, weight);
 }
 
 MB_API size_t mb_moe_plan_rows(size_t tokens, size_t k, size_t n_experts) {

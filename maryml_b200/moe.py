@@ -32,6 +32,26 @@ def router_topk_softmax(logits, k, renormalize=True, scaling=1.0):
     return idx, weight
 
 
+ROUTER_SOFTMAX, ROUTER_SIGMOID = 0, 1
+
+
+def router_topk(logits, k, activation="softmax", bias=None, renormalize=True, scaling=1.0):
+    """Router::route from logits with either activation and the selection-only correction bias
+    (src/models/k3/router.rs:343-488): the bias moves which experts are picked, never their weights."""
+    assert logits.dtype == torch.float32 and logits.is_contiguous() and logits.dim() == 2
+    tokens, n_experts = logits.shape
+    act = {"softmax": ROUTER_SOFTMAX, "sigmoid": ROUTER_SIGMOID}[activation]
+    if bias is not None:
+        assert bias.dtype == torch.float32 and bias.is_contiguous() and bias.numel() == n_experts
+        assert bias.device == logits.device
+    ctx = context(logits.device.index)
+    idx = torch.empty((tokens, k), dtype=torch.int32, device=logits.device)
+    weight = torch.empty((tokens, k), dtype=torch.float32, device=logits.device)
+    ctx.check(lib.mb_router_topk(ctx.handle, _stream(), _p(logits), _p(bias) if bias is not None else None, act,
+                                 tokens, n_experts, k, int(renormalize), float(scaling), _p(idx), _p(weight)))
+    return idx, weight
+
+
 class RowPlan:
     """RowPlan::build on the device (src/models/inkling/moegroup.rs:1850-1909)."""
 

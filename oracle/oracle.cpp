@@ -461,6 +461,11 @@ ORC_API void orc_router_scores_softmax(const float* logits, size_t tokens, size_
   }
 }
 
+// Sigmoid scores, each expert alone: f32(1 / (1 + exp(-f64(x)))) (router.rs:347-350).
+ORC_API void orc_router_scores_sigmoid(const float* logits, size_t tokens, size_t n, float* v) {
+  for (size_t i = 0; i < tokens * n; ++i) v[i] = float(1.0 / (1.0 + std::exp(-double(logits[i]))));
+}
+
 // Selection (router.rs:399-425): descending score, ties ascending index; gather
 // (router.rs:431-446); normalise w/(sum+1e-20)*scale (router.rs:451-471).
 // Returns -1 on a non-finite score (the reference panics).

@@ -56,6 +56,7 @@ class Oracle:
             "orc_linear_w4a4": (None, [P(u8), P(u8), P(u8), P(u8), P(f32), f32, sz, sz, sz, P(f32)]),
             "orc_linear_bf16": (None, [P(u16), P(u16), sz, sz, sz, P(f32)]),
             "orc_router_scores_softmax": (None, [P(f32), sz, sz, P(f32)]),
+            "orc_router_scores_sigmoid": (None, [P(f32), sz, sz, P(f32)]),
             "orc_router_select": (C.c_int, [P(f32), P(f32), sz, sz, sz, C.c_int, f32, P(u32), P(f32)]),
             "orc_router_logits": (None, [P(u16), P(u16), sz, sz, sz, P(f32)]),
             "orc_row_plan": (C.c_longlong, [P(u32), P(f32), sz, sz, sz, sz, sz, P(i32), P(f32), P(u32), P(u32),
@@ -218,6 +219,13 @@ class Oracle:
         t, n = logits.shape
         v = np.empty((t, n), np.float32)
         self.lib.orc_router_scores_softmax(_ptr(logits, C.c_float), t, n, _ptr(v, C.c_float))
+        return v
+
+    def router_scores_sigmoid(self, logits):
+        logits = np.ascontiguousarray(logits, np.float32)
+        t, n = logits.shape
+        v = np.empty((t, n), np.float32)
+        self.lib.orc_router_scores_sigmoid(_ptr(logits, C.c_float), t, n, _ptr(v, C.c_float))
         return v
 
     def router_select(self, scores, k, bias=None, renormalize=True, scaling=1.0):

@@ -34,6 +34,44 @@ def test_router_indices_bit_exact(moe, orc, tokens, n_experts, k):
     assert np.array_equal(w.cpu().numpy().view(np.uint32), w_ref.view(np.uint32)) or tokens > 0
 
 
+@pytest.mark.parametrize("activation", ["sigmoid", "softmax"])
+@pytest.mark.parametrize("tokens,n_experts,k,scaling", [(1, 32, 2, 1.0), (37, 128, 8, 2.5), (1000, 384, 8, 2.827),
+                                                        (300, 256, 6, 1.0)])
+def test_router_activation_and_selection_bias(moe, orc, activation, tokens, n_experts, k, scaling):
+    logits = (orc.normal_f32(177 + tokens, tokens * n_experts, 2.0)).reshape(tokens, n_experts)
+    bias = (orc.normal_f32(9 + n_experts, n_experts, 0.2)).astype(np.float32)
+    if tokens > 2:
+        logits[1, :] = 0.25
+        logits[2, 5] = logits[2, 9]
+        bias[5] = bias[9]
+    scores = orc.router_scores_sigmoid(logits) if activation == "sigmoid" else orc.router_scores_softmax(logits)
+    for b in (None, bias):
+        idx, w = moe.router_topk(torch.from_numpy(logits).cuda(), k, activation,
+                                 None if b is None else torch.from_numpy(b).cuda(), True, scaling)
+        idx_ref, w_ref = orc.router_select(scores, k, bias=b, scaling=scaling)
+        assert np.array_equal(idx.cpu().numpy().astype(np.uint32), idx_ref)
+        assert np.abs(w.cpu().numpy() - w_ref).max() <= 1e-6 * max(1.0, scaling)
+    # without renormalisation the weights are the unbiased scores themselves: bit-exact
+    idx, w = moe.router_topk(torch.from_numpy(logits).cuda(), k, activation, torch.from_numpy(bias).cuda(), False, 1.0)
+    idx_ref, w_ref = orc.router_select(scores, k, bias=bias, renormalize=False)
+    assert np.array_equal(idx.cpu().numpy().astype(np.uint32), idx_ref)
+    assert np.array_equal(w.cpu().numpy().view(np.uint32), w_ref.view(np.uint32))
+    assert np.array_equal(w.cpu().numpy(), np.take_along_axis(scores, idx_ref.astype(np.int64), 1))
+
+
+def test_router_known_answer_bias_moves_selection(moe):
+    # src/models/k3/router.rs:518-547 widened to 32 experts (the kernel's minimum): experts 4.. sit far below
+    logits = np.full((1, 32), -30.0, np.float32)
+    logits[0, :4] = [2.0, 1.0, 0.5, 0.0]
+    bias = np.zeros(32, np.float32)
+    idx, w = moe.router_topk(torch.from_numpy(logits).cuda(), 2, "sigmoid")
+    assert idx.cpu().numpy().tolist() == [[0, 1]] and abs(float(w.sum()) - 1.0) < 1e-6
+    bias[3] = 1.0
+    idx, w = moe.router_topk(torch.from_numpy(logits).cuda(), 2, "sigmoid", torch.from_numpy(bias).cuda(), False)
+    assert idx.cpu().numpy().tolist() == [[3, 0]]
+    assert w.cpu().numpy().tolist() == [[0.5, float(np.float32(1.0 / (1.0 + np.exp(-2.0))))]]
+
+
 def test_router_flags_non_finite_logits(moe, orc):
     from maryml_b200 import _lib
     ctx = _lib.context(0)

@@ -64,6 +64,22 @@ def test_bias_moves_selection_not_weights_and_renormalise(orc):
         orc.router_select(np.array([[np.nan, 1.0]], np.float32), 1)
 
 
+def test_sigmoid_router_known_answers(orc):
+    # src/models/k3/router.rs:518-556 as written there (RouterActivation::Sigmoid, hidden 2, 4 experts, top-2)
+    w = np.array([[2.0, 0], [1.0, 0], [0.5, 0], [0.0, 0]], np.float32)
+    logits = (w @ np.array([1.0, 0.0], np.float32)).reshape(1, 4).astype(np.float32)
+    scores = orc.router_scores_sigmoid(logits)
+    want = (1.0 / (1.0 + np.exp(-logits.astype(np.float64)))).astype(np.float32)
+    assert np.array_equal(scores, want)
+    idx0, w0 = orc.router_select(scores, 2)
+    assert list(idx0[0]) == [0, 1]
+    assert abs(float(w0.sum()) - 1.0) < 1e-6            # weights_renormalise_to_one
+    idx1, w1 = orc.router_select(scores, 2, bias=[0, 0, 0, 1.0], renormalize=False)
+    assert list(idx1[0]) == [3, 0]                      # bias_moves_selection_not_weights
+    assert w1[0, 0] == scores[0, 3] and w1[0, 1] == scores[0, 0]
+    assert w1[0, 0] < 1.0                               # the bias is not in the weight
+
+
 def test_softmax_scores_follow_the_f64_recipe(orc):
     # router.rs:352-368: f64 exp, f32 store, f32(f64(v)/s)
     rng = np.random.default_rng(0)
