@@ -424,7 +424,7 @@ def run_other(args, rank, world, local_rank):
                            "note": "min bytes = expert planes + x + out; the layer is weight-streaming bound at 4096 tokens"}
         cfg = {"workload": "moe_layer_T4096_h2048_E128_top8_inter768",
                "lane": "SwiGLU and the second projection's quantizer fused into the first grouped product"}
-        launches = 13
+        launches = 14
     elif wl in ("attn_decode", "attn_prefill"):
         H, KVH, D = 32, 8, 128
         if wl == "attn_decode":

@@ -116,6 +116,16 @@ int mb_nvfp4_quantize_act(mb_ctx* ctx, mb_stream stream, const void* x, int x_dt
                           int recipe, float input_scale, const int32_t* gather, size_t src_rows,
                           uint8_t* codes, uint8_t* scales, int sf_layout, float* rowscale);
 
+/* gather_rows(_bf16) followed by the activation quantizer (src/models/inkling/moegroup.rs:313-331,
+ * :3429-3470) with the two steps exchanged: a row's NVFP4 bytes do not depend on where the row
+ * lands, so the tokens are quantized once ([src_rows, k], tiled scales) and their planes are
+ * copied into plan order: out row r = source row gather[r]; a negative entry is a zero row
+ * (zero codes, zero scales); an entry >= src_rows raises the plan flag and is written as zeros.
+ * Both scale planes are tiled; the output planes hold `rows` rows. k % 64 == 0. */
+int mb_nvfp4_gather_rows(mb_ctx* ctx, mb_stream stream, const uint8_t* codes, const uint8_t* sf_tiled,
+                         size_t src_rows, size_t k, const int32_t* gather, size_t rows, uint8_t* out_codes,
+                         uint8_t* out_sf_tiled);
+
 /* dequantize_nvfp4(_bf16) (src/models/inkling/fp4quant.rs:437-459) and
  * nvfp4::decode_payload (src/nvfp4.rs:170-182): out = E2M1[code]*(e4m3(scale)*scale2). */
 int mb_nvfp4_dequantize(mb_ctx* ctx, mb_stream stream, const uint8_t* codes, const uint8_t* scales_rowmajor,

@@ -142,7 +142,12 @@ def moe_experts(x, idx, weight, w13, w2, fuse_swiglu=True, fuse_quant=True):
     tokens, h = x.shape
     inter = w2.k
     plan = RowPlan(idx, weight, w13.experts)
-    a_codes, a_sf, _ = nv.quantize_act(x, _lib.QUANT_RECIP, tiled=True, gather=plan.row_tok)
+    if h % 64 == 0:
+        # a row's bytes do not depend on its place in the plan: quantize each token once, copy planes
+        t_codes, t_sf, _ = nv.quantize_act(x, _lib.QUANT_RECIP, tiled=True)
+        a_codes, a_sf = nv.gather_rows(t_codes, t_sf, tokens, h, plan.row_tok)
+    else:
+        a_codes, a_sf, _ = nv.quantize_act(x, _lib.QUANT_RECIP, tiled=True, gather=plan.row_tok)
     if fuse_swiglu and fuse_quant:
         # SwiGLU and the second projection's activation quantizer both in the first product's epilogue
         c2, sf2 = grouped_gemm(a_codes, a_sf, w13, plan, epilogue=_lib.EPI_SWIGLU_INTERLEAVED | _lib.EPI_QUANT_RECIP)

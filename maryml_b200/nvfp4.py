@@ -70,6 +70,17 @@ def quantize_act(x, recipe=_lib.QUANT_SCALED, input_scale=1.0, tiled=True, gathe
     return codes, scales, rowscale
 
 
+def gather_rows(codes, sf_tiled, src_rows, k, gather):
+    """Quantized activation planes copied into the row order of `gather` (negative = zero row)."""
+    ctx = context(codes.device.index)
+    rows = gather.numel()
+    out = torch.empty((rows, k // 2), dtype=torch.uint8, device=codes.device)
+    out_sf = torch.empty(sf_bytes(rows, k), dtype=torch.uint8, device=codes.device)
+    ctx.check(lib.mb_nvfp4_gather_rows(ctx.handle, _stream(), _p(codes), _p(sf_tiled), src_rows, k, _p(gather), rows,
+                                       _p(out), _p(out_sf)))
+    return out, out_sf
+
+
 def dequantize(codes, scales_rowmajor, scale2, rows, k, dtype=torch.float32):
     ctx = context(codes.device.index)
     out = torch.empty((rows, k), dtype=dtype, device=codes.device)

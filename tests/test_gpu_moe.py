@@ -72,6 +72,30 @@ def test_router_known_answer_bias_moves_selection(moe):
     assert w.cpu().numpy().tolist() == [[0.5, float(np.float32(1.0 / (1.0 + np.exp(-2.0))))]]
 
 
+@pytest.mark.parametrize("tokens,k,rows", [(300, 2048, 1000), (64, 192, 128), (5, 64, 37)])
+def test_gather_of_quantized_planes_equals_quantizer_with_gather(moe, tokens, k, rows):
+    from maryml_b200 import _lib, nvfp4 as nv
+    g = torch.Generator(device="cuda").manual_seed(tokens + k)
+    x = (torch.randn(tokens, k, device="cuda", generator=g) * 3).to(torch.bfloat16)
+    rng = np.random.default_rng(rows)
+    gather = rng.integers(-1, tokens, rows).astype(np.int32)
+    gather[0] = -1
+    gd = torch.from_numpy(gather).cuda()
+    want_c, want_s, _ = nv.quantize_act(x, _lib.QUANT_RECIP, tiled=True, gather=gd)
+    t_c, t_s, _ = nv.quantize_act(x, _lib.QUANT_RECIP, tiled=True)
+    got_c, got_s = nv.gather_rows(t_c, t_s, tokens, k, gd)
+    assert torch.equal(got_c, want_c)
+    # pad rows of the last 128-row tile are unspecified in neither plane: both are zero-filled first
+    assert torch.equal(nv.untile_scales(got_s, rows, k), nv.untile_scales(want_s, rows, k))
+    ctx = _lib.context(0)
+    assert ctx.check_flags(None)[0] == 0
+    gd[1] = tokens                                   # a source row that does not exist
+    c2, _ = nv.gather_rows(t_c, t_s, tokens, k, gd)
+    rc, flags = ctx.check_flags(None)
+    assert rc == _lib.ERR_DEVICE_FLAG and flags[2] == 2 and not c2[1].any()
+    assert ctx.check_flags(None)[0] == 0
+
+
 def test_router_flags_non_finite_logits(moe, orc):
     from maryml_b200 import _lib
     ctx = _lib.context(0)
