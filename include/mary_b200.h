@@ -175,12 +175,16 @@ int mb_nvfp4_gemm_w4a4_splitk(mb_ctx* ctx, mb_stream stream, const uint8_t* a_co
  * stacked rows of all active experts against an expert bank. a: [m_cap, k] planes
  * (each expert's rows padded to 128). bank: [experts, n, k] planes with tiled scales
  * per expert. tile_expert: [m_cap/128] int32, the expert of each 128-row tile or -1;
- * n_tiles_dev: device int32, tiles in use. alpha: [experts] f32 (the expert's scale2). */
+ * n_tiles_dev: device int32, tiles in use. alpha: [experts] f32 (the expert's scale2).
+ * row_tok: optional [m_cap] int32, the plan's token of each stacked row; rows with a negative
+ * entry are the padding that closes an expert's last tile, and with row_tok given a bf16 or f32
+ * output keeps its old bytes there instead of receiving the products of zero rows (a third of
+ * the rows at 4096 tokens x top-8 over 128 experts). Quantized output is always written whole. */
 int mb_nvfp4_gemm_w4a4_grouped(mb_ctx* ctx, mb_stream stream, const uint8_t* a_codes, const uint8_t* a_sf_tiled,
                                const uint8_t* bank_codes, const uint8_t* bank_sf_tiled, const float* alpha,
                                const int32_t* tile_expert, const int32_t* n_tiles_dev, size_t m_cap,
                                size_t experts, size_t n, size_t k, void* out, int out_dtype, int epilogue,
-                               void* out_sf);
+                               void* out_sf, const int32_t* row_tok);
 
 /* Several projections of one input stacked along n (q|k|v, or gate and up interleaved row by
  * row), each stored tensor keeping its own global scale: colscale[n] holds the scale2 of the

@@ -44,7 +44,7 @@ SIGNATURES = {
     "mb_nvfp4_gemm_splitk_workspace": (_sz, [_sz, _sz, _sz]),
     "mb_nvfp4_gemm_w4a4_splitk": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _f, _sz, _sz, _sz, _vp, _i, _vp, _sz]),
     "mb_nvfp4_gemm_w4a4_grouped": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _sz, _sz, _sz, _sz, _vp, _i, _i,
-                                        _vp]),
+                                        _vp, _vp]),
     "mb_nvfp4_gemm_w4a4_stacked": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _sz, _sz, _sz, _vp, _i, _i, _vp, _vp, _sz]),
     "mb_bf16_gemm": (_i, [_vp, _vp, _vp, _vp, _f, _sz, _sz, _sz, _vp, _i]),
     "mb_bf16_gemm_splitk_workspace": (_sz, [_sz, _sz, _sz]),

@@ -37,6 +37,7 @@ struct GemmParams {
   const float* alpha_vec;     // [experts] or null
   const int32_t* tile_expert; // grouped: expert of each 128-row tile
   const int32_t* n_mtiles_dev;// grouped: tiles in use (device word)
+  const int32_t* row_tok;     // grouped, optional: token of each stacked row, negative = pad row (not stored)
   int* flags;
   float alpha;
   uint32_t m, n, k_steps;     // k_steps: 128-byte K steps
@@ -474,7 +475,9 @@ gemm_tc5_kernel(const __grid_constant__ GemmParams p) {
       }
       const uint32_t row0 = mt * C::BM + quad * 32u;       // first row of this warp's 32
       const uint32_t row = row0 + lane;
-      const uint32_t rows_valid = row0 < p.m ? min(32u, p.m - row0) : 0u;
+      uint32_t rows_valid = row0 < p.m ? min(32u, p.m - row0) : 0u;
+      // pad rows close an expert's last tile, so the live rows of a warp are a prefix
+      if (p.row_tok) rows_valid = __popc(__ballot_sync(0xFFFFFFFFu, row < p.m && __ldg(p.row_tok + row) >= 0));
       float scale = alpha;
       if (p.rowscale && row < p.m) scale = p.rowscale[row] * alpha;
 #ifdef MB_GEMM_PROFILE
@@ -897,6 +900,7 @@ struct GemmExtra {
   size_t workspace_bytes = 0;
   const float* colscale = nullptr;
   void* out_sf = nullptr;
+  const int32_t* row_tok = nullptr;
 };
 
 int gemm_w4a4_common(mb_ctx* ctx, cudaStream_t stream, const uint8_t* a_codes, const uint8_t* a_sf,
@@ -943,7 +947,7 @@ int gemm_w4a4_common(mb_ctx* ctx, cudaStream_t stream, const uint8_t* a_codes, c
   rc = make_tmap(ctx, &p.tmap_b, b_codes, false, experts * n, k / 2, wide ? 256 : 128);
   if (rc) return rc;
   p.sfa = a_sf; p.sfb = b_sf; p.out = out; p.rowscale = rowscale; p.alpha_vec = alpha_vec;
-  p.tile_expert = tile_expert; p.n_mtiles_dev = n_tiles_dev; p.flags = ctx->flags_dev; p.alpha = alpha;
+  p.tile_expert = tile_expert; p.n_mtiles_dev = n_tiles_dev; p.row_tok = quant ? nullptr : ex.row_tok; p.flags = ctx->flags_dev; p.alpha = alpha;
   p.m = uint32_t(m); p.n = uint32_t(n); p.k_steps = uint32_t((k + 255) / 256);
   p.m_tiles = uint32_t((m + 127) / 128);
   p.n_tiles = uint32_t((n + (wide ? 255 : 127)) / (wide ? 256 : 128));
@@ -1083,10 +1087,12 @@ MB_API int mb_nvfp4_gemm_w4a4_grouped(mb_ctx* ctx, mb_stream stream, const uint8
                                       const uint8_t* a_sf_tiled, const uint8_t* bank_codes,
                                       const uint8_t* bank_sf_tiled, const float* alpha, const int32_t* tile_expert,
                                       const int32_t* n_tiles_dev, size_t m_cap, size_t experts, size_t n, size_t k,
-                                      void* out, int out_dtype, int epilogue, void* out_sf) {
+                                      void* out, int out_dtype, int epilogue, void* out_sf,
+                                      const int32_t* row_tok) {
   MB_REQUIRE(ctx, alpha && tile_expert && n_tiles_dev && experts > 0, "grouped gemm: null argument");
   GemmExtra ex;
   ex.out_sf = out_sf;
+  ex.row_tok = row_tok;
   return gemm_w4a4_common(ctx, static_cast<cudaStream_t>(stream), a_codes, a_sf_tiled, bank_codes, bank_sf_tiled,
                           nullptr, 1.0f, alpha, tile_expert, n_tiles_dev, m_cap, experts, n, k, out, out_dtype,
                           epilogue, ex);

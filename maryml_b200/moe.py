@@ -115,9 +115,10 @@ class ExpertBank:
         return ExpertBank(codes, scales, s2.to(w.device), experts, n, k)
 
 
-def grouped_gemm(a_codes, a_sf, bank, plan, out_dtype=torch.bfloat16, epilogue=_lib.EPI_PLAIN):
+def grouped_gemm(a_codes, a_sf, bank, plan, out_dtype=torch.bfloat16, epilogue=_lib.EPI_PLAIN, skip_pad_rows=False):
     """fp4_linear_grouped(_bf16)_launch (src/models/inkling/moegroup.rs:612-751). With an
-    EPI_QUANT_* flag on a SwiGLU epilogue the result comes back as (codes, tiled scale plane)."""
+    EPI_QUANT_* flag on a SwiGLU epilogue the result comes back as (codes, tiled scale plane).
+    skip_pad_rows leaves the plan's padding rows of a bf16/f32 result unwritten (nothing reads them)."""
     ctx = context(a_codes.device.index)
     dev = a_codes.device
     swiglu = (epilogue & 0xFF) in (_lib.EPI_SWIGLU_INTERLEAVED, _lib.EPI_SWIGLU_ROUNDED)
@@ -132,7 +133,7 @@ def grouped_gemm(a_codes, a_sf, bank, plan, out_dtype=torch.bfloat16, epilogue=_
                                              _p(bank.sf_tiled), _p(bank.scale2), _p(plan.tile_expert),
                                              _p(plan.n_tiles), plan.m_cap, bank.experts, bank.n, bank.k, _p(out),
                                              _lib.DT_BF16 if out.dtype != torch.float32 else _lib.DT_F32, epilogue,
-                                             _p(out_sf)))
+                                             _p(out_sf), _p(plan.row_tok) if skip_pad_rows else None))
     return (out, out_sf) if quant else out
 
 
@@ -151,7 +152,7 @@ def moe_experts(x, idx, weight, w13, w2, fuse_swiglu=True, fuse_quant=True):
     if fuse_swiglu and fuse_quant:
         # SwiGLU and the second projection's activation quantizer both in the first product's epilogue
         c2, sf2 = grouped_gemm(a_codes, a_sf, w13, plan, epilogue=_lib.EPI_SWIGLU_INTERLEAVED | _lib.EPI_QUANT_RECIP)
-        return scatter_weighted(grouped_gemm(c2, sf2, w2, plan), plan, h), plan
+        return scatter_weighted(grouped_gemm(c2, sf2, w2, plan, skip_pad_rows=True), plan, h), plan
     if fuse_swiglu:
         act = grouped_gemm(a_codes, a_sf, w13, plan, epilogue=_lib.EPI_SWIGLU_INTERLEAVED)
     else:
@@ -159,7 +160,7 @@ def moe_experts(x, idx, weight, w13, w2, fuse_swiglu=True, fuse_quant=True):
         g, u = both[:, 0::2].float(), both[:, 1::2].float()
         act = ((g / (1.0 + torch.exp(-g))) * u).to(torch.bfloat16)
     c2, sf2, _ = nv.quantize_act(act, _lib.QUANT_RECIP, tiled=True)
-    y = grouped_gemm(c2, sf2, w2, plan)
+    y = grouped_gemm(c2, sf2, w2, plan, skip_pad_rows=True)
     return scatter_weighted(y, plan, h), plan
 
 

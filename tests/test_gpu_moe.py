@@ -205,6 +205,34 @@ def test_moe_experts_against_oracle(moe, orc, tokens, h, inter, n_experts, k):
     assert torch.equal(out_stored, out)
 
 
+def test_grouped_product_leaves_pad_rows_unwritten(moe, orc):
+    from maryml_b200 import _lib, nvfp4 as nv
+    tokens, h, n, n_experts, k = 150, 256, 384, 8, 2
+    rng = np.random.default_rng(11)
+    idx = np.stack([rng.permutation(n_experts)[:k] for _ in range(tokens)]).astype(np.int32)
+    wgt = rng.random((tokens, k), dtype=np.float32)
+    plan = moe.RowPlan(torch.from_numpy(idx).cuda(), torch.from_numpy(wgt).cuda(), n_experts)
+    bank = moe.ExpertBank.quantize(dev_bf16(_bank(orc, 8, n_experts, n, h)).view(n_experts, n, h))
+    x = dev_bf16(f32_to_bf16_bits(orc.normal_f32(6, tokens * h, 1.0))).view(tokens, h)
+    t_c, t_s, _ = nv.quantize_act(x, _lib.QUANT_RECIP, tiled=True)
+    a_c, a_s = nv.gather_rows(t_c, t_s, tokens, h, plan.row_tok)
+    live = plan.row_tok >= 0
+    assert int(live.sum()) == tokens * k and not bool(live.all())
+    for dt in (torch.bfloat16, torch.float32):
+        whole = moe.grouped_gemm(a_c, a_s, bank, plan, out_dtype=dt)
+        ctx = _lib.context(0)
+        out = torch.full((plan.m_cap, n), 7.0, dtype=dt, device="cuda")
+        ctx.check(_lib.lib.mb_nvfp4_gemm_w4a4_grouped(
+            ctx.handle, nv._stream(), nv._p(a_c), nv._p(a_s), nv._p(bank.codes), nv._p(bank.sf_tiled),
+            nv._p(bank.scale2), nv._p(plan.tile_expert), nv._p(plan.n_tiles), plan.m_cap, n_experts, n, h, nv._p(out),
+            _lib.DT_BF16 if dt == torch.bfloat16 else _lib.DT_F32, _lib.EPI_PLAIN, None, nv._p(plan.row_tok)))
+        assert torch.equal(out[live], whole[live])
+        assert bool((out[~live] == 7.0).all())
+        # the rows of an expert are contiguous from its first row: products of zero rows are zero
+        used = int(plan.n_tiles.item()) * 128
+        assert bool((whole[:used][~live[:used]] == 0).all())
+
+
 def test_moe_layer_config2_shapes_smoke(moe, orc):
     """Config 2 at reduced token count: 128 experts, top-8, hidden 2048, intermediate 768."""
     tokens, h, inter, n_experts, k = 256, 2048, 768, 128, 8
