@@ -7,103 +7,134 @@
 namespace {
 
 // ---------------------------------------------------------------------------------
-// Router. One warp per token, expert e lives in lane e % 32, slot e / 32.
+// Router. A block routes 32 tokens, one per warp (four per warp beyond 128 experts, where the
+// registers of a 1024-thread block run short); expert e of a token lives in lane e % 32,
+// slot e / 32 of the token's warp.
 // Scores follow the CPU rule exactly: m = max logit; e_i = exp(f64(x_i) - m);
 // v_i = f32(e_i); s = sum of e_i in index order (f64); score_i = f32(f64(v_i) / s).
-// Selection: descending score, ties to the lower index. Weights: gathered scores,
-// w / (sum + 1e-20) in selection order, times the scaling factor.
+// The index-order sum is a chain of dependent f64 adds: the block parks its e_i in shared
+// memory and one warp walks the 32 chains side by side, lane t summing token t.
 // The sigmoid form scores each expert alone: f32(1 / (1 + exp(-f64(x)))). With a bias the
 // selection runs on score + bias (one f32 add) while the weights stay the unbiased scores.
+// Selection: descending score, ties to the lower index: per round every lane offers its best
+// free slot as an order-preserving integer key; a warp max on the keys and a warp min on the
+// indices that hold it find the pick (two redux instructions), one shuffle fetches its score.
+// Weights: gathered scores, w / (sum + 1e-20) in selection order, times the scaling factor.
 // ---------------------------------------------------------------------------------
-template <int EPL, bool SIGMOID>
-__global__ void __launch_bounds__(128)
+constexpr int ROUTER_TOKENS = 32;    // tokens per block
+
+// f32 -> u32 whose unsigned order is the float order (-0 was folded into +0 by the caller).
+__device__ __forceinline__ uint32_t router_key(float c) {
+  const uint32_t u = __float_as_uint(c);
+  return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
+}
+
+template <int EPL, bool SIGMOID, int ROUTER_WARPS>
+__global__ void __launch_bounds__(32 * ROUTER_WARPS)
 router_topk_kernel(const float* __restrict__ logits, const float* __restrict__ bias, uint32_t tokens,
                    uint32_t n_experts, uint32_t k, int renormalize, float scaling, int32_t* __restrict__ idx,
                    float* __restrict__ weight, int* __restrict__ flag) {
-  const uint32_t lane = threadIdx.x & 31;
-  const uint32_t t = blockIdx.x * 4 + (threadIdx.x >> 5);
-  if (t >= tokens) return;
-  const float* row = logits + size_t(t) * n_experts;
-  float x[EPL];
-  bool bad = false;
-  double m = -INFINITY;
+  extern __shared__ double s_router[];
+  constexpr uint32_t ROW = 32 * EPL + 1;             // odd stride in doubles: the column walk below meets no bank twice
+  double* s_e = s_router;                            // [ROUTER_TOKENS][ROW]
+  double* s_sum = s_router + ROUTER_TOKENS * ROW;    // [ROUTER_TOKENS]
+  const uint32_t lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  constexpr uint32_t PER = ROUTER_TOKENS / ROUTER_WARPS;
+  const uint32_t t0 = blockIdx.x * ROUTER_TOKENS;
+  float bs[EPL];
 #pragma unroll
-  for (int j = 0; j < EPL; ++j) {
-    x[j] = row[lane + 32 * j];
-    if (!(fabsf(x[j]) <= 3.4028234663852886e38f)) bad = true;
-    m = fmax(m, double(x[j]));
-  }
-#pragma unroll
-  for (int o = 16; o > 0; o >>= 1) m = fmax(m, __shfl_xor_sync(0xFFFFFFFFu, m, o));
-  float v[EPL];
-  if constexpr (SIGMOID) {
-#pragma unroll
-    for (int j = 0; j < EPL; ++j) v[j] = float(1.0 / (1.0 + exp(-double(x[j]))));
-  } else {
-    double e[EPL];
+  for (int j = 0; j < EPL; ++j) bs[j] = bias ? __ldg(bias + lane + 32 * j) : 0.0f;
+
+  // phase 1: logits -> e_i (softmax) or the finished score (sigmoid), parked in shared memory
+#pragma unroll 1
+  for (uint32_t q = 0; q < PER; ++q) {
+    const uint32_t tl = warp * PER + q, t = t0 + tl;
+    if (t >= tokens) break;                          // warp-uniform
+    const float* row = logits + size_t(t) * n_experts;
+    float x[EPL];
+    bool bad = false;
+    double m = -INFINITY;
 #pragma unroll
     for (int j = 0; j < EPL; ++j) {
-      e[j] = exp(double(x[j]) - m);
-      v[j] = float(e[j]);
+      x[j] = __ldg(row + lane + 32 * j);
+      if (!(fabsf(x[j]) <= 3.4028234663852886e38f)) bad = true;
+      m = fmax(m, double(x[j]));
     }
-    // Sum in expert-index order: expert i sits in lane i % 32, slot i / 32.
-    double s = 0.0;
+    if (!SIGMOID) {
 #pragma unroll
-    for (int j = 0; j < EPL; ++j) {
+      for (int o = 16; o > 0; o >>= 1) m = fmax(m, __shfl_xor_sync(0xFFFFFFFFu, m, o));
+    }
+    if (__any_sync(0xFFFFFFFFu, bad)) {
+      if (lane == 0) atomicCAS(flag, 0, int(t) + 1);
+    }
+#pragma unroll
+    for (int j = 0; j < EPL; ++j)
+      s_e[tl * ROW + lane + 32 * j] = SIGMOID ? 1.0 / (1.0 + exp(-double(x[j]))) : exp(double(x[j]) - m);
+  }
+  if (!SIGMOID) {
+    __syncthreads();
+    // phase 2: lane t of warp 0 sums token t's e_i in expert order
+    if (warp == 0) {
+      const double* col = s_e + lane * ROW;
+      double s = 0.0;
 #pragma unroll 8
-      for (int l = 0; l < 32; ++l) s += __shfl_sync(0xFFFFFFFFu, e[j], l);
+      for (uint32_t i = 0; i < 32 * EPL; ++i) s += col[i];
+      s_sum[lane] = s;
     }
-#pragma unroll
-    for (int j = 0; j < EPL; ++j) v[j] = float(double(v[j]) / s);
-  }
-  float c[EPL];   // what the selection compares
-#pragma unroll
-  for (int j = 0; j < EPL; ++j) {
-    c[j] = bias ? v[j] + __ldg(bias + lane + 32 * j) : v[j];
-    if (!(fabsf(c[j]) <= 3.4028234663852886e38f)) bad = true;
-  }
-  if (__any_sync(0xFFFFFFFFu, bad)) {
-    if (lane == 0) atomicCAS(flag, 0, int(t) + 1);
+    __syncthreads();
+  } else {
+    __syncwarp();
   }
 
-  // k rounds of warp arg-max on (score desc, index asc).
-  uint32_t taken = 0;   // bit j: slot j of this lane already selected
-  float wsum = 0.0f;
-  float my_w = 0.0f;    // lane r keeps the weight of pick r (k <= 32)
-  int my_i = 0;
-  for (uint32_t r = 0; r < k; ++r) {
-    float best = -INFINITY, best_v = 0.0f;
-    uint32_t best_i = 0xFFFFFFFFu;
+  // phase 3: scores, k rounds of arg-max on (score desc, index asc), weights
+#pragma unroll 1
+  for (uint32_t q = 0; q < PER; ++q) {
+    const uint32_t tl = warp * PER + q, t = t0 + tl;
+    if (t >= tokens) break;
+    float v[EPL];
+    uint32_t key[EPL];
+    bool bad = false;
+    const double s = SIGMOID ? 1.0 : s_sum[tl];
 #pragma unroll
     for (int j = 0; j < EPL; ++j) {
-      uint32_t i = lane + 32 * j;
-      bool free_slot = !((taken >> j) & 1u);
-      if (free_slot && (c[j] > best || (c[j] == best && i < best_i) || best_i == 0xFFFFFFFFu)) {
-        best = c[j];
-        best_v = v[j];
-        best_i = i;
-      }
+      const float e32 = float(s_e[tl * ROW + lane + 32 * j]);
+      v[j] = SIGMOID ? e32 : float(double(e32) / s);
+      const float c = (bias ? v[j] + bs[j] : v[j]) + 0.0f;       // what the selection compares; -0 -> +0
+      if (!(fabsf(c) <= 3.4028234663852886e38f)) bad = true;
+      key[j] = router_key(c);
     }
+    if (__any_sync(0xFFFFFFFFu, bad)) {
+      if (lane == 0) atomicCAS(flag, 0, int(t) + 1);
+    }
+    uint32_t taken = 0;   // bit j: slot j of this lane already selected
+    float wsum = 0.0f;
+    float my_w = 0.0f;    // lane r keeps the weight of pick r (k <= 32)
+    int my_i = 0;
+    for (uint32_t r = 0; r < k; ++r) {
+      uint32_t bk = 0, bi = 0xFFFFFFFFu;
+      float bv = 0.0f;
 #pragma unroll
-    for (int o = 16; o > 0; o >>= 1) {
-      float ob = __shfl_xor_sync(0xFFFFFFFFu, best, o);
-      float ov = __shfl_xor_sync(0xFFFFFFFFu, best_v, o);
-      uint32_t oi = __shfl_xor_sync(0xFFFFFFFFu, best_i, o);
-      if (oi != 0xFFFFFFFFu && (best_i == 0xFFFFFFFFu || ob > best || (ob == best && oi < best_i))) {
-        best = ob;
-        best_v = ov;
-        best_i = oi;
+      for (int j = 0; j < EPL; ++j) {
+        const bool free_slot = !((taken >> j) & 1u);
+        if (free_slot && (bi == 0xFFFFFFFFu || key[j] > bk)) {   // ascending j: a tie keeps the lower index
+          bk = key[j];
+          bi = lane + 32 * j;
+          bv = v[j];
+        }
       }
+      const uint32_t mk = __reduce_max_sync(0xFFFFFFFFu, bk);
+      const uint32_t best_i = __reduce_min_sync(0xFFFFFFFFu, bk == mk ? bi : 0xFFFFFFFFu);
+      const float best_v = __shfl_sync(0xFFFFFFFFu, bv, best_i & 31u);
+      if ((best_i & 31u) == lane) taken |= 1u << (best_i >> 5);
+      wsum += best_v;   // selection order, as the CPU rule sums; the unbiased score
+      if (lane == r) { my_w = best_v; my_i = int(best_i); }
     }
-    if ((best_i & 31u) == lane) taken |= 1u << (best_i >> 5);
-    wsum += best_v;   // selection order, as the CPU rule sums; the unbiased score
-    if (lane == r) { my_w = best_v; my_i = int(best_i); }
-  }
-  if (k > 1 && renormalize) my_w = __fdiv_rn(my_w, wsum + 1e-20f);
-  if (scaling != 1.0f) my_w *= scaling;
-  if (lane < k) {
-    idx[size_t(t) * k + lane] = my_i;
-    weight[size_t(t) * k + lane] = my_w;
+    if (k > 1 && renormalize) my_w = __fdiv_rn(my_w, wsum + 1e-20f);
+    if (scaling != 1.0f) my_w *= scaling;
+    if (lane < k) {
+      idx[size_t(t) * k + lane] = my_i;
+      weight[size_t(t) * k + lane] = my_w;
+    }
   }
 }
 
@@ -274,6 +305,74 @@ scatter_weighted_kernel(const Y* __restrict__ y, const float* __restrict__ row_w
   o[1] = make_float4(acc[4], acc[5], acc[6], acc[7]);
 }
 
+// The same pass for k <= 8 with a token's picks in registers: its picks and weights, then the two
+// bases of every pick, are loaded together instead of as one dependent pair of loads per pick,
+// and the rows are sorted by a fixed exchange network.
+__global__ void __launch_bounds__(PLAN_CHUNK)
+plan_place8_kernel(const int32_t* __restrict__ idx, const float* __restrict__ weight, uint32_t tokens, uint32_t k,
+                   uint32_t n_experts, const int32_t* __restrict__ chunk_base, const int32_t* __restrict__ expert_row0,
+                   int32_t* __restrict__ row_tok, float* __restrict__ row_wgt, int32_t* __restrict__ tok_rows) {
+  extern __shared__ uint32_t s_mask[];   // [n_experts][8]
+  for (uint32_t i = threadIdx.x; i < n_experts * 8; i += PLAN_CHUNK) s_mask[i] = 0u;
+  const uint32_t t = blockIdx.x * PLAN_CHUNK + threadIdx.x;
+  const uint32_t word = threadIdx.x >> 5, bit = threadIdx.x & 31;
+  const bool live = t < tokens;
+  int32_t e[8];
+  float w[8];
+#pragma unroll
+  for (uint32_t j = 0; j < 8; ++j) {
+    const bool have = live && j < k;
+    e[j] = have ? __ldg(idx + size_t(t) * k + j) : -1;
+    w[j] = have ? __ldg(weight + size_t(t) * k + j) : 0.0f;
+  }
+  __syncthreads();
+  uint32_t ok_bits = 0;
+#pragma unroll
+  for (uint32_t j = 0; j < 8; ++j) {
+    bool ok = live && j < k && e[j] >= 0 && uint32_t(e[j]) < n_experts;
+#pragma unroll
+    for (uint32_t i = 0; i < j; ++i) ok = ok && e[i] != e[j];
+    if (ok) {
+      ok_bits |= 1u << j;
+      atomicOr(&s_mask[uint32_t(e[j]) * 8 + word], 1u << bit);
+    }
+  }
+  __syncthreads();
+  if (!live) return;
+  int32_t base[8];
+#pragma unroll
+  for (uint32_t j = 0; j < 8; ++j)
+    base[j] = (ok_bits >> j & 1u)
+                  ? __ldg(expert_row0 + e[j]) + __ldg(chunk_base + size_t(blockIdx.x) * n_experts + uint32_t(e[j]))
+                  : 0;
+  int32_t rows[8];
+#pragma unroll
+  for (uint32_t j = 0; j < 8; ++j) {
+    int32_t row = j < k ? -1 : 0x7FFFFFFF;          // a pick without a row sorts first, an absent pick last
+    if (ok_bits >> j & 1u) {
+      const uint32_t* m = s_mask + uint32_t(e[j]) * 8;
+      int32_t rank = __popc(m[word] & ((1u << bit) - 1u));
+      for (uint32_t ww = 0; ww < word; ++ww) rank += __popc(m[ww]);
+      row = base[j] + rank;
+      row_tok[row] = int32_t(t);
+      row_wgt[row] = w[j];
+    }
+    rows[j] = row;
+  }
+#pragma unroll
+  for (int pass = 0; pass < 8; ++pass) {
+#pragma unroll
+    for (int i = pass & 1; i + 1 < 8; i += 2) {
+      const int32_t lo = min(rows[i], rows[i + 1]), hi = max(rows[i], rows[i + 1]);
+      rows[i] = lo;
+      rows[i + 1] = hi;
+    }
+  }
+#pragma unroll
+  for (uint32_t j = 0; j < 8; ++j)
+    if (j < k) tok_rows[size_t(t) * k + j] = rows[j];
+}
+
 }  // namespace
 
 MB_API int mb_router_topk(mb_ctx* ctx, mb_stream stream_, const float* logits, const float* bias, int activation,
@@ -287,16 +386,20 @@ MB_API int mb_router_topk(mb_ctx* ctx, mb_stream stream_, const float* logits, c
   MB_REQUIRE(ctx, n_experts >= 32 && n_experts % 32 == 0 && n_experts <= 512,
              "router: n_experts must be a multiple of 32 up to 512, got %zu", n_experts);
   MB_REQUIRE(ctx, k >= 1 && k <= 32 && k <= n_experts, "router: top_k must be 1..32, got %zu", k);
-  unsigned grid = unsigned((tokens + 3) / 4);
+  const unsigned grid = unsigned((tokens + ROUTER_TOKENS - 1) / ROUTER_TOKENS);
   int* flag = ctx->flags_dev + MB_FLAG_ROUTER_NONFINITE;
   const bool sigmoid = activation == MB_ROUTER_SIGMOID;
-#define ROUTE(EPL)                                                                                              \
-  if (sigmoid)                                                                                                  \
-    router_topk_kernel<EPL, true><<<grid, 128, 0, stream>>>(logits, bias, uint32_t(tokens), uint32_t(n_experts), \
-                                                            uint32_t(k), renormalize, scaling, idx, weight, flag); \
-  else                                                                                                          \
-    router_topk_kernel<EPL, false><<<grid, 128, 0, stream>>>(logits, bias, uint32_t(tokens), uint32_t(n_experts), \
-                                                             uint32_t(k), renormalize, scaling, idx, weight, flag)
+  const size_t smem = (size_t(ROUTER_TOKENS) * (n_experts + 1) + ROUTER_TOKENS) * sizeof(double);
+#define ROUTE1(EPL, SIG)                                                                                        \
+  do {                                                                                                          \
+    constexpr int WARPS = EPL <= 4 ? 32 : 8;                                                                    \
+    auto kern = router_topk_kernel<EPL, SIG, WARPS>;                                                            \
+    if (smem > 48 * 1024)                                                                                       \
+      MB_CUDA_OK(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)));      \
+    kern<<<grid, 32 * WARPS, smem, stream>>>(logits, bias, uint32_t(tokens), uint32_t(n_experts), uint32_t(k),  \
+                                             renormalize, scaling, idx, weight, flag);                          \
+  } while (0)
+#define ROUTE(EPL) do { if (sigmoid) ROUTE1(EPL, true); else ROUTE1(EPL, false); } while (0)
   switch (n_experts / 32) {
     case 1: ROUTE(1); break;
     case 2: ROUTE(2); break;
@@ -308,6 +411,7 @@ MB_API int mb_router_topk(mb_ctx* ctx, mb_stream stream_, const float* logits, c
     case 16: ROUTE(16); break;
     default: return mb_fail(ctx, MB_ERR_INVALID, "router: unsupported expert count %zu", n_experts);
   }
+#undef ROUTE1
 #undef ROUTE
   MB_LAUNCH_OK(ctx);
   return MB_OK;
@@ -355,9 +459,14 @@ MB_API int mb_moe_plan(mb_ctx* ctx, mb_stream stream_, const int32_t* idx, const
   plan_scan_kernel<<<1, 1024, 0, stream>>>(chunk_counts, chunk_base, chunks, uint32_t(n_experts), expert_rows,
                                            expert_row0, tile_expert, uint32_t(m_cap / PLAN_PAD), n_tiles);
   MB_LAUNCH_OK(ctx);
-  plan_place_kernel<<<chunks, PLAN_CHUNK, n_experts * 32, stream>>>(idx, weight, uint32_t(tokens), uint32_t(k),
-                                                                    uint32_t(n_experts), chunk_base, expert_row0,
-                                                                    row_tok, row_wgt, tok_rows);
+  if (k <= 8)
+    plan_place8_kernel<<<chunks, PLAN_CHUNK, n_experts * 32, stream>>>(idx, weight, uint32_t(tokens), uint32_t(k),
+                                                                       uint32_t(n_experts), chunk_base, expert_row0,
+                                                                       row_tok, row_wgt, tok_rows);
+  else
+    plan_place_kernel<<<chunks, PLAN_CHUNK, n_experts * 32, stream>>>(idx, weight, uint32_t(tokens), uint32_t(k),
+                                                                      uint32_t(n_experts), chunk_base, expert_row0,
+                                                                      row_tok, row_wgt, tok_rows);
   MB_LAUNCH_OK(ctx);
   return MB_OK;
 }

@@ -18,7 +18,8 @@ def moe():
     return m
 
 
-@pytest.mark.parametrize("tokens,n_experts,k", [(1, 32, 1), (37, 128, 8), (4096, 128, 8), (300, 256, 6)])
+@pytest.mark.parametrize("tokens,n_experts,k", [(1, 32, 1), (37, 128, 8), (4096, 128, 8), (300, 256, 6), (70, 512, 8),
+                                               (33, 96, 32)])
 def test_router_indices_bit_exact(moe, orc, tokens, n_experts, k):
     logits = (orc.normal_f32(77 + tokens, tokens * n_experts, 2.0)).reshape(tokens, n_experts)
     if tokens > 2:
@@ -109,7 +110,8 @@ def test_router_flags_non_finite_logits(moe, orc):
     assert rc == 0
 
 
-@pytest.mark.parametrize("tokens,n_experts,k", [(2, 3, 2), (130, 4, 3), (4096, 128, 8), (5, 128, 8)])
+@pytest.mark.parametrize("tokens,n_experts,k", [(2, 3, 2), (130, 4, 3), (4096, 128, 8), (5, 128, 8), (300, 64, 12),
+                                               (1000, 32, 1)])
 def test_row_plan_bit_exact(moe, orc, tokens, n_experts, k):
     rng = np.random.default_rng(tokens * 7 + k)
     idx = np.stack([rng.permutation(n_experts)[:k] for _ in range(tokens)]).astype(np.int32)
