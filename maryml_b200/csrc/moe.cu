@@ -205,14 +205,32 @@ plan_scan_kernel(const int32_t* __restrict__ chunk_counts, int32_t* __restrict__
       }
     }
   }
-  s_pad[e] = (c + PLAN_PAD - 1) / PLAN_PAD;   // tiles of this expert
-  __syncthreads();
-  if (e == 0) {
-    int32_t run = 0;
-    for (uint32_t i = 0; i < n_experts; ++i) { s_off[i] = run; run += s_pad[i]; }
-    *n_tiles = run;
-    s_total = run;
+  const int32_t pad = (c + PLAN_PAD - 1) / PLAN_PAD;   // tiles of this expert (0 beyond n_experts)
+  s_pad[e] = pad;
+  // exclusive prefix of the tile counts over the experts: warp scans, then a scan of the 32 warp totals
+  __shared__ int32_t s_warp[32];
+  const uint32_t lane = e & 31, wp = e >> 5;
+  int32_t inc = pad;
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    const int32_t up = __shfl_up_sync(0xFFFFFFFFu, inc, o);
+    if (lane >= uint32_t(o)) inc += up;
   }
+  if (lane == 31) s_warp[wp] = inc;
+  __syncthreads();
+  if (wp == 0) {
+    const int32_t tot = s_warp[lane];
+    int32_t winc = tot;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const int32_t up = __shfl_up_sync(0xFFFFFFFFu, winc, o);
+      if (lane >= uint32_t(o)) winc += up;
+    }
+    s_warp[lane] = winc - tot;
+    if (lane == 31) { *n_tiles = winc; s_total = winc; }
+  }
+  __syncthreads();
+  s_off[e] = s_warp[wp] + inc - pad;
   __syncthreads();
   if (e < n_experts) {
     expert_rows[e] = c;
