@@ -21,7 +21,8 @@ sweep does not shard (no collective on this path), so scaling is weak.
 Other rows of the hot path have their own workloads (same JSON contract, their own metric):
 
     --workload moe           config 2: 4096 tokens, hidden 2048, 128 experts, top-8 (tokens/s)
-    --workload attn_decode   config 3: batch 32 x 1 query over 32768 keys (GB/s of K/V read)
+    --workload attn_decode   config 3: batch 32 x 1 query over 32768 keys (GB/s of K/V read;
+                             --kv nvfp4 reads the same keys as NVFP4 cache rows)
     --workload attn_prefill  config 3: batch 4 x 8192 causal (TFLOP/s)
     --workload tp_decode     config 4: decoder layer, batch 64 over a 4096-token cache (tokens/s),
     --workload tp_prefill    config 4: decoder layer, 8192-token prefill (tokens/s); both shard over
@@ -437,19 +438,29 @@ def run_other(args, rank, world, local_rank):
         k = torch.randn(B, L, KVH, D, device=dev, generator=g).to(torch.bfloat16)
         v = torch.randn(B, L, KVH, D, device=dev, generator=g).to(torch.bfloat16)
         ws = torch.empty(max(int(_lib.lib.mb_attention_workspace(B, nq, L, H, KVH, D)), 16), dtype=torch.uint8, device=dev)
-        step = lambda: att.flash_attention(q, k, v, q0=L - nq, workspace=ws)
+        packed = wl == "attn_decode" and args.kv == "nvfp4"
+        if packed:
+            # NVFP4 cache rows (blocks of 16 along the features of a row, no global scale)
+            kc, ks = att.quantize_kv_rows(k)
+            vc, vs = att.quantize_kv_rows(v)
+            del k, v
+            attend = lambda qq: att.flash_attention_fp4kv(qq, kc, ks, vc, vs, KVH, q0=L - nq, workspace=ws)
+        else:
+            attend = lambda qq: att.flash_attention(qq, k, v, q0=L - nq, workspace=ws)
+        step = lambda: attend(q)
         hq = q.cpu().pin_memory()
         ho = torch.empty_like(hq).pin_memory()
         dq = torch.empty_like(q)
 
         def e2e():
             dq.copy_(hq, non_blocking=True)
-            ho.copy_(att.flash_attention(dq, k, v, q0=L - nq, workspace=ws), non_blocking=True)
+            ho.copy_(attend(dq), non_blocking=True)
         h2d = d2h = q.numel() * 2
         if wl == "attn_decode":
-            byts = 2 * B * L * KVH * D * 2
+            byts = 2 * B * L * KVH * D * (0.5625 if packed else 2)
             units, metric, unit = byts / 1e9, "decode_attention_kv_gbytes_per_s", "GB/s"
-            roof = lambda ms: {"bound": "hbm", "kernel": "attn_decode_kernel", "achieved": byts / (ms * 1e-3) / 1e9,
+            roof = lambda ms: {"bound": "hbm", "kernel": "attn_decode_kernel<nvfp4 rows>" if packed else "attn_decode_kernel",
+                               "achieved": byts / (ms * 1e-3) / 1e9,
                                "peak": peaks["hbm_gbs"], "unit": "GB/s",
                                "frac": byts / (ms * 1e-3) / 1e9 / peaks["hbm_gbs"], "peak_source": peaks["source"],
                                "frac_of_nominal_8tbs": byts / (ms * 1e-3) / 1e9 / 8000.0, "traffic": None}
@@ -462,6 +473,9 @@ def run_other(args, rank, world, local_rank):
                                "peak_source": peaks["source"], "traffic": None}
             launches = 1
         cfg = {"workload": f"{wl}_B{B}_nq{nq}_keys{L}_heads32_kv8_d128", "rope": "pre-applied (inputs drawn N(0,1))"}
+        if packed:
+            cfg["workload"] += "_nvfp4rows"
+            cfg["kv"] = "NVFP4 cache rows: 0.5625 B per value counted; the bf16 cache of the same keys is 3.56x the bytes"
     else:
         cfgL = layer.LayerConfig()
         decode = wl == "tp_decode"
@@ -595,6 +609,8 @@ def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--workload", default="gemm",
                     choices=["gemm", "moe", "attn_decode", "attn_prefill", "tp_decode", "tp_prefill"])
+    ap.add_argument("--kv", default="bf16", choices=["bf16", "nvfp4"],
+                    help="attn_decode: read the cache as bf16 rows (the BASELINE config) or as NVFP4 rows")
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=1000)
     ap.add_argument("--warmup", type=int, default=3)

@@ -271,6 +271,23 @@ int mb_attention_window(mb_ctx* ctx, mb_stream stream, const void* q, const void
                         size_t nq, size_t keys, size_t heads, size_t kv_heads, size_t d, size_t q0, float scale,
                         size_t window, void* out, void* workspace, size_t workspace_bytes);
 
+/* Decode attention over an NVFP4 key/value cache: the packed reader of flash_attention_kernel
+ * (`nvfp4_at`, src/models/inkling/flash.rs:520-540, 827-859) over the Fp4Rows page layout
+ * (src/models/inkling/kvpages.rs:1378-1404): a cache row of kv_heads * D features is quantized
+ * row-major in blocks of 16 along the features with no global scale, i.e. the bytes
+ * mb_nvfp4_quantize_act(MB_QUANT_RECIP, row-major scales) writes for the [keys, kv_heads * D]
+ * rows. codes [batch, keys, kv_heads * D / 2], scales [batch, keys, kv_heads * D / 16].
+ * A value is E2M1[code] * e4m3(scale), exact in f16: the kernel expands rows to f16 and runs
+ * both products as f16 x f16 with f32 accumulation (Q converted to f16, probabilities kept
+ * to 11 bits), reading 0.5625 bytes per cached value instead of 2. The result agrees with
+ * mb_attention (mb_attention_window when window > 0) over the dequantized rows to a bf16 step
+ * of the output. Decode shapes only
+ * (nq * heads / kv_heads <= 16); workspace as for mb_attention. Codes 16-byte, scales 8-byte aligned. */
+int mb_attention_fp4kv(mb_ctx* ctx, mb_stream stream, const void* q, const uint8_t* k_codes, const uint8_t* k_scales,
+                       const uint8_t* v_codes, const uint8_t* v_scales, size_t batch, size_t nq, size_t keys,
+                       size_t heads, size_t kv_heads, size_t d, size_t q0, float scale, int causal, size_t window,
+                       void* out, void* workspace, size_t workspace_bytes);
+
 /* Decode attention without any allocation; it has no counterpart in the reference.
  * For hosts that gave all device memory to their own arena at start-up and may not
  * call the driver's allocator afterwards (an allocation there stalls the token step

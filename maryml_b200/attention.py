@@ -39,6 +39,37 @@ def flash_attention(q, k, v, q0=0, scale=None, causal=True, workspace=None, wind
     return out
 
 
+def quantize_kv_rows(x):
+    """[batch, keys, kv_heads, D] bf16 cache rows -> (codes [batch, keys, kv_heads*D/2], scales
+    [batch, keys, kv_heads*D/16]) in the Fp4Rows layout (src/models/inkling/kvpages.rs:1378-1404):
+    every row quantized on its own, blocks of 16 along the features, no global scale."""
+    from . import nvfp4 as nv
+    batch, keys, kv_heads, d = x.shape
+    codes, scales, _ = nv.quantize_act(x.reshape(batch * keys, kv_heads * d), _lib.QUANT_RECIP, tiled=False)
+    return codes.view(batch, keys, kv_heads * d // 2), scales.view(batch, keys, kv_heads * d // 16)
+
+
+def flash_attention_fp4kv(q, k_codes, k_scales, v_codes, v_scales, kv_heads, q0=0, scale=None, causal=True,
+                          workspace=None, window=0):
+    """Decode attention reading NVFP4 cache rows (the packed reader of src/models/inkling/flash.rs:520-540)."""
+    assert q.dtype == torch.bfloat16 and q.is_contiguous()
+    for t in (k_codes, k_scales, v_codes, v_scales):
+        assert t.dtype == torch.uint8 and t.is_contiguous()
+    batch, nq, heads, d = q.shape
+    keys = k_codes.shape[1]
+    ctx = context(q.device.index)
+    if scale is None:
+        scale = 1.0 / math.sqrt(d)
+    out = torch.empty_like(q)
+    need = int(lib.mb_attention_workspace(batch, nq, keys, heads, kv_heads, d))
+    if need and (workspace is None or workspace.numel() < need):
+        workspace = torch.empty(need, dtype=torch.uint8, device=q.device)
+    ctx.check(lib.mb_attention_fp4kv(ctx.handle, _stream(), _p(q), _p(k_codes), _p(k_scales), _p(v_codes), _p(v_scales),
+                                     batch, nq, keys, heads, kv_heads, d, q0, float(scale), int(causal), int(window),
+                                     _p(out), _p(workspace) if need else None, need))
+    return out
+
+
 def attention_prefill(q, k, v, scale=None):
     """Causal self-attention over a fresh sequence (q0 = 0)."""
     return flash_attention(q, k, v, 0, scale, True)

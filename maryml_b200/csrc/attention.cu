@@ -22,6 +22,8 @@
 #include "tc5.cuh"
 #include "attention.cuh"
 
+#include <cuda_fp16.h>
+
 namespace {
 
 using namespace tc5;
@@ -46,6 +48,16 @@ __device__ __forceinline__ void mma_bf16(float* c, const uint32_t* a, uint32_t b
       : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
       : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
+__device__ __forceinline__ void mma_f16(float* c, const uint32_t* a, uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, "
+               "{%0, %1, %2, %3};"
+               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+               : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t pack2h(float lo, float hi) {
+  __half2 v = __floats2half2_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
 __device__ __forceinline__ uint32_t pack2(float lo, float hi) {
   __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
   return *reinterpret_cast<uint32_t*>(&v);
@@ -57,8 +69,85 @@ __device__ __forceinline__ uint32_t tile_off(uint32_t row, uint32_t c, uint32_t 
   return (c >> 3) * half_bytes + row * 128u + (((c & 7u) ^ (row & 7u)) << 4);
 }
 
+// Four E2M1 codes (two bytes, low nibble first) times their block scale -> two f16x2 registers.
+// code x scale has at most 7 significant bits and lies in [2^-10, 2688]: exact in f16.
+__device__ __forceinline__ void fp4_decode4(uint32_t two_bytes, __half2 s, uint32_t& lo, uint32_t& hi) {
+  uint32_t h0, h1;
+  asm("{ .reg .b8 b0, b1, b2, b3; mov.b32 {b0, b1, b2, b3}, %2;\n\t"
+      "cvt.rn.f16x2.e2m1x2 %0, b0;\n\tcvt.rn.f16x2.e2m1x2 %1, b1; }"
+      : "=r"(h0), "=r"(h1) : "r"(two_bytes));
+  const __half2 p0 = __hmul2(*reinterpret_cast<__half2*>(&h0), s), p1 = __hmul2(*reinterpret_cast<__half2*>(&h1), s);
+  lo = *reinterpret_cast<const uint32_t*>(&p0);
+  hi = *reinterpret_cast<const uint32_t*>(&p1);
+}
+
+// A warp's slot of packed bytes: 16 key rows of K codes [16][64], V codes [16][64] at +1024,
+// K scales [16][8] at +2048, V scales [16][8] at +2176.
+//
+// S[16 x 16] = Q K^T straight from the codes. Lane (g, t4) takes keys g and g + 8 and the 32
+// values d = 32 t4 .. 32 t4 + 31 of each (one 16-byte load, two scale bytes); step ks multiplies
+// d = 32 t4 + 4 ks + 0..3, the same permutation of d the Q fragments were loaded in.
+__device__ __forceinline__ void fp4_qk(float (*s)[4], const uint32_t (*qf)[4], const uint8_t* raw, uint32_t lane) {
+  const uint32_t g = lane >> 2, t4 = lane & 3u;
+#pragma unroll
+  for (int jn = 0; jn < 2; ++jn) {
+    s[jn][0] = s[jn][1] = s[jn][2] = s[jn][3] = 0.0f;
+    const uint32_t key = 8u * jn + g;
+    const uint4 w = *reinterpret_cast<const uint4*>(raw + (key * 4u + t4) * 16u);
+    uint32_t sh;
+    asm("cvt.rn.f16x2.e4m3x2 %0, %1;" : "=r"(sh) : "h"(*reinterpret_cast<const uint16_t*>(raw + 2048u + key * 8u + t4 * 2u)));
+    const __half2 s2 = *reinterpret_cast<__half2*>(&sh);
+    const __half2 s_lo = __low2half2(s2), s_hi = __high2half2(s2);
+    const uint32_t ww[4] = {w.x, w.y, w.z, w.w};
+#pragma unroll
+    for (int ks = 0; ks < 8; ++ks) {
+      uint32_t b0, b1;
+      fp4_decode4((ww[ks >> 1] >> (16 * (ks & 1))) & 0xFFFFu, ks < 4 ? s_lo : s_hi, b0, b1);
+      mma_f16(s[jn], qf[ks], b0, b1);
+    }
+  }
+}
+
+// O[16 x 128] += P[16 x 16] V straight from the codes. Lane (g, t4) takes the 16-value block
+// d = 16 g .. 16 g + 15 (eight code bytes, one scale byte) of keys 2 t4, 2 t4 + 1, 2 t4 + 8 and
+// 2 t4 + 9; output tile n, column g is d = 16 g + n (the caller stores the columns accordingly).
+__device__ __forceinline__ void fp4_pv(float (*o)[4], const float (*pfrag)[4], const uint8_t* raw, uint32_t lane) {
+  const uint32_t g = lane >> 2, t4 = lane & 3u;
+  uint32_t a[4];
+  a[0] = pack2h(pfrag[0][0], pfrag[0][1]);
+  a[1] = pack2h(pfrag[0][2], pfrag[0][3]);
+  a[2] = pack2h(pfrag[1][0], pfrag[1][1]);
+  a[3] = pack2h(pfrag[1][2], pfrag[1][3]);
+  uint2 c[4];
+  __half2 sc[4];
+#pragma unroll
+  for (int q = 0; q < 4; ++q) {
+    const uint32_t key = 2u * t4 + (q & 1u) + 8u * (q >> 1);
+    c[q] = *reinterpret_cast<const uint2*>(raw + 1024u + key * 64u + g * 8u);
+    uint32_t sh;
+    asm("cvt.rn.f16x2.e4m3x2 %0, %1;" : "=r"(sh) : "h"(uint16_t(raw[2176u + key * 8u + g])));
+    sc[q] = __low2half2(*reinterpret_cast<__half2*>(&sh));
+  }
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {                      // code bytes 2 j, 2 j + 1 of each key: values 4 j .. 4 j + 3
+    uint32_t h[4][2];
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      const uint32_t word = (j < 2) ? c[q].x : c[q].y;
+      fp4_decode4((word >> (16 * (j & 1))) & 0xFFFFu, sc[q], h[q][0], h[q][1]);
+    }
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {                    // output tile n = 4 j + e: value e of the four
+      const uint32_t sel = (e & 1) ? 0x7632u : 0x5410u;
+      const uint32_t b0 = __byte_perm(h[0][e >> 1], h[1][e >> 1], sel);
+      const uint32_t b1 = __byte_perm(h[2][e >> 1], h[3][e >> 1], sel);
+      mma_f16(o[4 * j + e], a, b0, b1);
+    }
+  }
+}
+
 // S[16 x 8*NT] = Q[16 x 128] K^T for keys key0.. of a tile; Q fragments come from qf (8 k-steps x 4 regs).
-template <int NT>
+template <int NT, bool F16 = false>
 __device__ __forceinline__ void qk_tile(float (*s)[4], const uint32_t (*qf)[4], uint32_t k_base, uint32_t key0,
                                         uint32_t lane) {
 #pragma unroll
@@ -71,31 +160,38 @@ __device__ __forceinline__ void qk_tile(float (*s)[4], const uint32_t (*qf)[4], 
       uint32_t b0, b1, b2, b3;
       const uint32_t row = key0 + jp * 16 + (mi >> 1) * 8 + l8;
       ldsm_x4(k_base + tile_off(row, ks * 2 + (mi & 1), TILE_HALF_BYTES), b0, b1, b2, b3);
-      mma_bf16(s[2 * jp], qf[ks], b0, b1);
-      mma_bf16(s[2 * jp + 1], qf[ks], b2, b3);
+      if (F16) { mma_f16(s[2 * jp], qf[ks], b0, b1); mma_f16(s[2 * jp + 1], qf[ks], b2, b3); }
+      else { mma_bf16(s[2 * jp], qf[ks], b0, b1); mma_bf16(s[2 * jp + 1], qf[ks], b2, b3); }
     }
   }
 }
 
 // O[16 x 128] += P[16 x 16*KT] V for keys key0.. of a tile; P in C-fragment layout (bf16-rounded here).
-template <int KT>
+template <int KT, bool F16 = false>
 __device__ __forceinline__ void pv_tile(float (*o)[4], const float (*pfrag)[4], uint32_t v_base, uint32_t key0,
                                         uint32_t lane) {
   const uint32_t mi = lane >> 3, l8 = lane & 7;
 #pragma unroll
   for (int kt = 0; kt < KT; ++kt) {
     uint32_t a[4];
-    a[0] = pack2(pfrag[2 * kt][0], pfrag[2 * kt][1]);
-    a[1] = pack2(pfrag[2 * kt][2], pfrag[2 * kt][3]);
-    a[2] = pack2(pfrag[2 * kt + 1][0], pfrag[2 * kt + 1][1]);
-    a[3] = pack2(pfrag[2 * kt + 1][2], pfrag[2 * kt + 1][3]);
+    if (F16) {
+      a[0] = pack2h(pfrag[2 * kt][0], pfrag[2 * kt][1]);
+      a[1] = pack2h(pfrag[2 * kt][2], pfrag[2 * kt][3]);
+      a[2] = pack2h(pfrag[2 * kt + 1][0], pfrag[2 * kt + 1][1]);
+      a[3] = pack2h(pfrag[2 * kt + 1][2], pfrag[2 * kt + 1][3]);
+    } else {
+      a[0] = pack2(pfrag[2 * kt][0], pfrag[2 * kt][1]);
+      a[1] = pack2(pfrag[2 * kt][2], pfrag[2 * kt][3]);
+      a[2] = pack2(pfrag[2 * kt + 1][0], pfrag[2 * kt + 1][1]);
+      a[3] = pack2(pfrag[2 * kt + 1][2], pfrag[2 * kt + 1][3]);
+    }
     const uint32_t row = key0 + kt * 16 + (mi & 1) * 8 + l8;
 #pragma unroll
     for (int np = 0; np < 8; ++np) {
       uint32_t b0, b1, b2, b3;
       ldsm_x4_trans(v_base + tile_off(row, np * 2 + (mi >> 1), TILE_HALF_BYTES), b0, b1, b2, b3);
-      mma_bf16(o[2 * np], a, b0, b1);
-      mma_bf16(o[2 * np + 1], a, b2, b3);
+      if (F16) { mma_f16(o[2 * np], a, b0, b1); mma_f16(o[2 * np + 1], a, b2, b3); }
+      else { mma_bf16(o[2 * np], a, b0, b1); mma_bf16(o[2 * np + 1], a, b2, b3); }
     }
   }
 }
@@ -154,17 +250,28 @@ __device__ __forceinline__ void softmax_step(float (*s)[4], float (*o)[4], float
 // ---------------------------------------------------------------------------------
 constexpr int DEC_STAGES = 3;
 constexpr int DEC_THREADS = 160;
+// NVFP4 rows: no producer warp and no ring. Each compute warp expands the 16 key rows it
+// multiplies (K and V) from codes and scales into its rows of one bf16 tile, with the bytes of the
+// next tile already on their way in registers.
+constexpr int DEC_THREADS_FP4 = 128;
+constexpr int FP4_STAGES = 3;                     // tiles of packed bytes in flight per warp (cp.async groups)
+constexpr int FP4_RAW_WARP = 2 * 16 * (D / 2) + 2 * 16 * (D / 16);   // 16 key rows: K, V codes + K, V scales = 2304 B
+constexpr int DEC_TILE_FP4 = 36 * 1024;           // one bf16 K/V tile (32 KB); the merge patch (33.3 KB) reuses it
+constexpr int DEC_RING_FP4 = DEC_TILE_FP4 + 4 * FP4_STAGES * FP4_RAW_WARP;
+constexpr int DEC_SMEM_FP4 = DEC_RING_FP4 + 16 * D * 2 + 1024 + 128;
 constexpr int DEC_SMEM = DEC_STAGES * KV_STAGE_BYTES + 16 * D * 2 /*Q*/ + 1024 + 128;
 static_assert(4 * 16 * (D + 2) * 4 <= DEC_STAGES * KV_STAGE_BYTES, "the merge patch reuses the tile ring");
 
-__global__ void __launch_bounds__(DEC_THREADS, 2)
+template <bool FP4>
+__global__ void __launch_bounds__(FP4 ? DEC_THREADS_FP4 : DEC_THREADS, FP4 ? 3 : 2)
 attn_decode_kernel(const __grid_constant__ AttnParams p) {
   extern __shared__ uint8_t smem_raw[];
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* gen = smem_raw + (base - smem_u32(smem_raw));
-  const uint32_t q_smem = base + DEC_STAGES * KV_STAGE_BYTES;            // [16][128] bf16, swizzled halves of 16 rows
+  constexpr uint32_t RING = FP4 ? DEC_RING_FP4 : DEC_STAGES * KV_STAGE_BYTES;
+  const uint32_t q_smem = base + RING;            // [16][128] bf16, swizzled halves of 16 rows
   float* merge = reinterpret_cast<float*>(gen);   // reuses the tile ring once every compute warp is done with it
-  const uint32_t bar_base = base + DEC_STAGES * KV_STAGE_BYTES + 16 * D * 2;
+  const uint32_t bar_base = base + RING + 16 * D * 2;
   auto full_bar = [&](int s) { return bar_base + 8u * s; };
   auto empty_bar = [&](int s) { return bar_base + 8u * (DEC_STAGES + s); };
   volatile int* abort_smem = reinterpret_cast<volatile int*>(gen + (bar_base - base) + 8 * 2 * DEC_STAGES);
@@ -185,24 +292,37 @@ attn_decode_kernel(const __grid_constant__ AttnParams p) {
     for (int s = 0; s < DEC_STAGES; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 4); }
     *abort_smem = 0;
     fence_barrier_init();
-    tma_prefetch_desc(&p.tmap_k);
-    tma_prefetch_desc(&p.tmap_v);
+    if (!FP4) {
+      tma_prefetch_desc(&p.tmap_k);
+      tma_prefetch_desc(&p.tmap_v);
+    }
   }
   mb_grid_dependency_sync();      // shared-memory set-up above; Q, K and V are read from here on
   // Q rows r = qi * group + hg, zero beyond `rows`; 16 chunks of 16 bytes per row.
-  for (uint32_t i = threadIdx.x; i < 16 * 16; i += DEC_THREADS) {
+  for (uint32_t i = threadIdx.x; i < 16 * 16; i += blockDim.x) {
     const uint32_t r = i >> 4, c = i & 15;
     uint4 v = make_uint4(0, 0, 0, 0);
     if (r < rows) {
       const uint32_t qi = r / group, hg = r % group;
       const __nv_bfloat16* src = p.q + ((size_t(b) * p.nq + qi) * p.heads + kvh * group + hg) * D + c * 8;
       v = *reinterpret_cast<const uint4*>(src);
+      if (FP4) {
+        // the packed rows expand to f16, so the products run as f16 x f16: Q goes to f16 (exact for
+        // magnitudes in [2^-14, 65504], which bf16's 8 significant bits fit; larger ones saturate)
+        uint32_t* w = reinterpret_cast<uint32_t*>(&v);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const float lo = fminf(fmaxf(__uint_as_float(w[i] << 16), -65504.0f), 65504.0f);
+          const float hi = fminf(fmaxf(__uint_as_float(w[i] & 0xFFFF0000u), -65504.0f), 65504.0f);
+          w[i] = pack2h(lo, hi);
+        }
+      }
     }
     *reinterpret_cast<uint4*>(gen + (q_smem - base) + tile_off(r, c, 16 * 128)) = v;
   }
   __syncthreads();
 
-  if (warp == 4) {
+  if (!FP4 && warp == 4) {
     // producer
     int stage = 0;
     uint32_t phase = 0;
@@ -223,9 +343,22 @@ attn_decode_kernel(const __grid_constant__ AttnParams p) {
   } else {
     // compute warp w takes keys [16 w, 16 w + 16) of every tile
     uint32_t qf[8][4];
+    if (FP4) {
+      // the packed products sum over d in a permuted order: lane (g, t4) holds d = 32 t4 + 4 ks + 0..3 in
+      // step ks, the 32 consecutive values one 16-byte load of codes gives it for a key
+      const uint8_t* qs = gen + (q_smem - base);
 #pragma unroll
-    for (int ks = 0; ks < 8; ++ks)
-      ldsm_x4(q_smem + tile_off(lane & 15, ks * 2 + (lane >> 4), 16 * 128), qf[ks][0], qf[ks][1], qf[ks][2], qf[ks][3]);
+      for (int ks = 0; ks < 8; ++ks) {
+        const uint32_t d0 = 32u * (lane & 3u) + 4u * ks;
+        const uint2 lo = *reinterpret_cast<const uint2*>(qs + tile_off(lane >> 2, d0 >> 3, 16 * 128) + (d0 & 7u) * 2u);
+        const uint2 hi = *reinterpret_cast<const uint2*>(qs + tile_off((lane >> 2) + 8u, d0 >> 3, 16 * 128) + (d0 & 7u) * 2u);
+        qf[ks][0] = lo.x; qf[ks][1] = hi.x; qf[ks][2] = lo.y; qf[ks][3] = hi.y;
+      }
+    } else {
+#pragma unroll
+      for (int ks = 0; ks < 8; ++ks)
+        ldsm_x4(q_smem + tile_off(lane & 15, ks * 2 + (lane >> 4), 16 * 128), qf[ks][0], qf[ks][1], qf[ks][2], qf[ks][3]);
+    }
     float o[16][4];
 #pragma unroll
     for (int n = 0; n < 16; ++n) o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.0f;
@@ -237,13 +370,54 @@ attn_decode_kernel(const __grid_constant__ AttnParams p) {
     int stage = 0;
     uint32_t phase = 0;
     bool ok = true;
+    // NVFP4 rows. The warp keeps FP4_STAGES tiles of its 16 key rows' packed bytes in flight as
+    // cp.async groups into a ring of its own (nobody else reads it, so a __syncwarp is all the
+    // hand-over needs); both products take their fragments straight from those bytes.
+    uint8_t* raw_ring = gen + DEC_TILE_FP4 + uint32_t(warp) * FP4_STAGES * FP4_RAW_WARP;
+    const size_t stride_c = size_t(p.kv_heads) * (D / 2), stride_s = size_t(p.kv_heads) * (D / 16);
+    const uint8_t* kc0 = p.k_codes + (size_t(b) * p.keys * p.kv_heads + kvh) * (D / 2);
+    const uint8_t* vc0 = p.v_codes + (size_t(b) * p.keys * p.kv_heads + kvh) * (D / 2);
+    const uint8_t* ks0 = p.k_scales + (size_t(b) * p.keys * p.kv_heads + kvh) * (D / 16);
+    const uint8_t* vs0 = p.v_scales + (size_t(b) * p.keys * p.kv_heads + kvh) * (D / 16);
+    auto issue = [&](uint32_t t) {
+      if (t < n_tiles) {
+        const uint32_t dst = smem_u32(raw_ring + (t % FP4_STAGES) * FP4_RAW_WARP);
+        const uint32_t kfirst = k_begin + t * BC + uint32_t(warp) * 16u;
+#pragma unroll
+        for (int u = 0; u < 2; ++u) {            // chunk i = lane + 32 u of 64: key row i >> 2, 16-byte part i & 3
+          const uint32_t i = lane + 32u * u, key = kfirst + (i >> 2);
+          const bool live = key < k_end;         // rows past the slice are masked: zeros keep P V finite
+          const size_t off = size_t(live ? key : k_begin) * stride_c + (i & 3u) * 16u;
+          const uint32_t n = live ? 16u : 0u;
+          asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst + i * 16u), "l"(kc0 + off), "r"(n) : "memory");
+          asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst + 1024u + i * 16u), "l"(vc0 + off), "r"(n) : "memory");
+        }
+        {
+          const uint32_t r = lane & 15u, key = kfirst + r;
+          const bool live = key < k_end;
+          const uint8_t* src = (lane < 16 ? ks0 : vs0) + size_t(live ? key : k_begin) * stride_s;
+          const uint32_t n = live ? 8u : 0u;
+          asm volatile("cp.async.ca.shared.global [%0], [%1], 8, %2;" ::"r"(dst + 2048u + lane * 8u), "l"(src), "r"(n) : "memory");
+        }
+      }
+      asm volatile("cp.async.commit_group;" ::: "memory");   // an empty group keeps the count uniform
+    };
+    if (FP4) {
+#pragma unroll
+      for (int s2 = 0; s2 < FP4_STAGES; ++s2) issue(uint32_t(s2));
+    }
     for (uint32_t t = 0; t < n_tiles; ++t) {
-      if (!mbar_wait(full_bar(stage), phase, abort_smem, tflag, 12)) { ok = false; break; }
+      const uint8_t* raw = raw_ring + (t % FP4_STAGES) * FP4_RAW_WARP;
+      if (FP4) {
+        asm volatile("cp.async.wait_group %0;" ::"n"(FP4_STAGES - 1) : "memory");
+        __syncwarp();                              // every lane's copies of tile t have landed
+      } else if (!mbar_wait(full_bar(stage), phase, abort_smem, tflag, 12)) { ok = false; break; }
       const uint32_t s0 = base + stage * KV_STAGE_BYTES;
       const uint32_t key0 = warp * 16;
       const int kabs = int(k_begin + t * BC + key0);       // absolute index of this warp's first key
       float s[2][4];
-      qk_tile<2>(s, qf, s0, key0, lane);
+      if (FP4) fp4_qk(s, qf, raw, lane);
+      else qk_tile<2>(s, qf, s0, key0, lane);
       int vis_lo = int(k_end) - kabs, vis_hi = vis_lo;
       if (p.causal) {
         vis_lo = min(vis_lo, int(qpos_lo) + 1 - kabs);
@@ -255,10 +429,16 @@ attn_decode_kernel(const __grid_constant__ AttnParams p) {
         first_hi = int(qpos_hi) + 1 - int(p.window) - kabs;
       }
       softmax_step<2>(s, o, m, l, p.scale_log2, vis_lo, vis_hi, lane, first_lo, first_hi);
-      pv_tile<1>(o, s, s0 + 2 * TILE_HALF_BYTES, key0, lane);
-      __syncwarp();
-      if (lane == 0) mbar_arrive(empty_bar(stage));
-      if (++stage == DEC_STAGES) { stage = 0; phase ^= 1u; }
+      if (FP4) {
+        fp4_pv(o, s, raw, lane);
+        __syncwarp();                              // the warp is done with the ring slot
+        issue(t + FP4_STAGES);
+      } else {
+        pv_tile<1>(o, s, s0 + 2 * TILE_HALF_BYTES, key0, lane);
+        __syncwarp();
+        if (lane == 0) mbar_arrive(empty_bar(stage));
+        if (++stage == DEC_STAGES) { stage = 0; phase ^= 1u; }
+      }
     }
     (void)ok;
     // quad-reduce l, then publish this warp's partial (o, m, l) for rows g and g + 8
@@ -272,10 +452,12 @@ attn_decode_kernel(const __grid_constant__ AttnParams p) {
     const uint32_t t2 = (lane & 3) * 2;
 #pragma unroll
     for (int n = 0; n < 16; ++n) {
-      mine[g * (D + 2) + n * 8 + t2] = o[n][0];
-      mine[g * (D + 2) + n * 8 + t2 + 1] = o[n][1];
-      mine[(g + 8) * (D + 2) + n * 8 + t2] = o[n][2];
-      mine[(g + 8) * (D + 2) + n * 8 + t2 + 1] = o[n][3];
+      // column c of output tile n is d = 8 n + c, or d = 16 c + n where the packed product permuted them
+      const uint32_t d0 = FP4 ? 16u * t2 + n : n * 8 + t2, d1 = FP4 ? 16u * (t2 + 1) + n : n * 8 + t2 + 1;
+      mine[g * (D + 2) + d0] = o[n][0];
+      mine[g * (D + 2) + d1] = o[n][1];
+      mine[(g + 8) * (D + 2) + d0] = o[n][2];
+      mine[(g + 8) * (D + 2) + d1] = o[n][3];
     }
     if ((lane & 3) == 0) {
       mine[g * (D + 2) + D] = m[0];
@@ -505,26 +687,38 @@ MB_API size_t mb_attention_workspace(size_t batch, size_t nq, size_t keys, size_
 
 static int attention_common(mb_ctx* ctx, mb_stream stream_, const void* q, const void* k, const void* v, size_t batch,
                             size_t nq, size_t keys, size_t heads, size_t kv_heads, size_t d, size_t q0, float scale,
-                            int causal, size_t window, void* out, void* workspace, size_t workspace_bytes) {
+                            int causal, size_t window, void* out, void* workspace, size_t workspace_bytes,
+                            const uint8_t* const* fp4 = nullptr) {
   cudaStream_t stream = static_cast<cudaStream_t>(stream_);
   MB_REQUIRE(ctx, window == 0 || causal, "attention: a sliding window is a causal window");
   MB_REQUIRE(ctx, window < (1ull << 31), "attention: bad window");
   MB_REQUIRE(ctx, window == 0 || keys >= q0 + nq, "attention: with a window every query needs its own key in the cache");
-  MB_REQUIRE(ctx, ctx && q && k && v && out, "attention: null argument");
+  MB_REQUIRE(ctx, ctx && q && out && (fp4 ? fp4[0] && fp4[1] && fp4[2] && fp4[3] : k && v), "attention: null argument");
   MB_REQUIRE(ctx, d == D, "attention: head_dim must be 128, got %zu", d);
   MB_REQUIRE(ctx, batch > 0 && nq > 0 && keys > 0 && heads > 0 && kv_heads > 0 && heads % kv_heads == 0,
              "attention: bad extents (batch %zu, nq %zu, keys %zu, heads %zu, kv_heads %zu)", batch, nq, keys, heads, kv_heads);
   MB_REQUIRE(ctx, scale == scale && scale > 0.0f, "attention: scale must be positive");
-  MB_REQUIRE(ctx, mb_aligned(q, 16) && mb_aligned(k, 16) && mb_aligned(v, 16) && mb_aligned(out, 16),
+  MB_REQUIRE(ctx, mb_aligned(q, 16) && mb_aligned(out, 16) && (fp4 || (mb_aligned(k, 16) && mb_aligned(v, 16))),
              "attention: 16-byte alignment");
+  if (fp4) {
+    MB_REQUIRE(ctx, mb_aligned(fp4[0], 16) && mb_aligned(fp4[2], 16) && mb_aligned(fp4[1], 8) && mb_aligned(fp4[3], 8),
+               "attention: NVFP4 rows need 16-byte aligned codes and 8-byte aligned scales");
+    MB_REQUIRE(ctx, nq * (heads / kv_heads) <= 16,
+               "attention: NVFP4 rows are read by the decode kernel only (nq * heads / kv_heads <= 16)");
+  }
   MB_REQUIRE(ctx, batch <= 65535 && heads <= 65535 && keys < (1ull << 31) && nq < (1ull << 31), "attention: extent overflow");
   MB_REQUIRE(ctx, q0 < (1ull << 31), "attention: bad query offset");
   AttnParams p;
   memset(&p, 0, sizeof p);
-  int rc = make_tmap_4d(ctx, &p.tmap_k, k, batch, keys, kv_heads, BC);
-  if (rc) return rc;
-  rc = make_tmap_4d(ctx, &p.tmap_v, v, batch, keys, kv_heads, BC);
-  if (rc) return rc;
+  int rc = 0;
+  if (fp4) {
+    p.k_codes = fp4[0]; p.k_scales = fp4[1]; p.v_codes = fp4[2]; p.v_scales = fp4[3];
+  } else {
+    rc = make_tmap_4d(ctx, &p.tmap_k, k, batch, keys, kv_heads, BC);
+    if (rc) return rc;
+    rc = make_tmap_4d(ctx, &p.tmap_v, v, batch, keys, kv_heads, BC);
+    if (rc) return rc;
+  }
   p.q = static_cast<const __nv_bfloat16*>(q);
   p.out = static_cast<__nv_bfloat16*>(out);
   p.flags = ctx->flags_dev;
@@ -548,11 +742,15 @@ static int attention_common(mb_ctx* ctx, mb_stream stream_, const void* q, const
     p.keys_per_split = uint32_t(((span + splits - 1) / splits + BC - 1) / BC * BC);
     p.part = static_cast<float*>(workspace);
     if (!attr_dec[ctx->device & 15]) {
-      MB_CUDA_OK(ctx, cudaFuncSetAttribute(attn_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, DEC_SMEM));
+      MB_CUDA_OK(ctx, cudaFuncSetAttribute(attn_decode_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, DEC_SMEM));
+      MB_CUDA_OK(ctx, cudaFuncSetAttribute(attn_decode_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, DEC_SMEM_FP4));
       attr_dec[ctx->device & 15] = true;
     }
     dim3 grid(splits, unsigned(kv_heads), unsigned(batch));
-    MB_CUDA_OK(ctx, mb_launch_pdl(attn_decode_kernel, grid, dim3(DEC_THREADS), DEC_SMEM, stream, p));
+    if (fp4)
+      MB_CUDA_OK(ctx, mb_launch_pdl(attn_decode_kernel<true>, grid, dim3(DEC_THREADS_FP4), DEC_SMEM_FP4, stream, p));
+    else
+      MB_CUDA_OK(ctx, mb_launch_pdl(attn_decode_kernel<false>, grid, dim3(DEC_THREADS), DEC_SMEM, stream, p));
     MB_LAUNCH_OK(ctx);
     if (splits > 1) {
       MB_CUDA_OK(ctx, mb_launch_pdl(attn_combine_kernel, dim3(unsigned(batch * nq * heads)), dim3(128), 0, stream, p.part, p.out,
@@ -592,6 +790,15 @@ MB_API int mb_attention_window(mb_ctx* ctx, mb_stream stream, const void* q, con
                                size_t window, void* out, void* workspace, size_t workspace_bytes) {
   return attention_common(ctx, stream, q, k, v, batch, nq, keys, heads, kv_heads, d, q0, scale, 1, window, out, workspace,
                           workspace_bytes);
+}
+
+MB_API int mb_attention_fp4kv(mb_ctx* ctx, mb_stream stream, const void* q, const uint8_t* k_codes,
+                              const uint8_t* k_scales, const uint8_t* v_codes, const uint8_t* v_scales, size_t batch,
+                              size_t nq, size_t keys, size_t heads, size_t kv_heads, size_t d, size_t q0, float scale,
+                              int causal, size_t window, void* out, void* workspace, size_t workspace_bytes) {
+  const uint8_t* planes[4] = {k_codes, k_scales, v_codes, v_scales};
+  return attention_common(ctx, stream, q, nullptr, nullptr, batch, nq, keys, heads, kv_heads, d, q0, scale, causal,
+                          window, out, workspace, workspace_bytes, planes);
 }
 
 // ---------------------------------------------------------------------------------
@@ -658,11 +865,11 @@ MB_API int mb_attention_decode_static(mb_ctx* ctx, mb_stream stream_, const void
   p.part = g_decode_scratch_ptr[current];
   static bool attr_set[64] = {};
   if (!attr_set[current]) {
-    MB_CUDA_OK(ctx, cudaFuncSetAttribute(attn_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, DEC_SMEM));
+    MB_CUDA_OK(ctx, cudaFuncSetAttribute(attn_decode_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, DEC_SMEM));
     attr_set[current] = true;
   }
   dim3 grid(splits, unsigned(kv_heads), unsigned(batch));
-  MB_CUDA_OK(ctx, mb_launch_pdl(attn_decode_kernel, grid, dim3(DEC_THREADS), DEC_SMEM, stream, p));
+  MB_CUDA_OK(ctx, mb_launch_pdl(attn_decode_kernel<false>, grid, dim3(DEC_THREADS), DEC_SMEM, stream, p));
   MB_LAUNCH_OK(ctx);
   if (splits > 1) {
     MB_CUDA_OK(ctx, mb_launch_pdl(attn_combine_kernel, dim3(unsigned(batch * nq * heads)), dim3(128), 0, stream, p.part, p.out,

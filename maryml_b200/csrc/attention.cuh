@@ -18,6 +18,12 @@ struct AttnParams {
   // sliding window (0 = none): query at position q sees keys in (q - window, q]; k_lo = first key any query of
   // the call can see, rounded down to a tile (the decode splits start there)
   uint32_t window, k_lo;
+  // NVFP4 key/value rows (decode only): codes [batch, keys, kv_heads * D / 2] bytes, E4M3 scales
+  // [batch, keys, kv_heads * D / 16] bytes, blocks of 16 along the features of a row
+  const uint8_t* k_codes;
+  const uint8_t* k_scales;
+  const uint8_t* v_codes;
+  const uint8_t* v_scales;
 };
 
 __device__ __forceinline__ void tma_load_4d(uint32_t dst, const void* tmap, int c0, int c1, int c2, int c3,

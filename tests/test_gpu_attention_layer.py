@@ -72,6 +72,63 @@ def test_sliding_window_attention(mods, orc, batch, nq, keys, heads, kvh, q0, wi
     _check(att, orc, q, k, v, batch, nq, keys, heads, kvh, q0, window=window)
 
 
+@pytest.mark.parametrize("batch,nq,keys,heads,kvh,q0,window", [
+    (1, 1, 64, 4, 1, 63, 0),
+    (2, 1, 1000, 32, 8, 999, 0),        # ragged key count, several splits
+    (3, 1, 4097, 8, 2, 4096, 0),
+    (2, 4, 515, 4, 1, 100, 0),          # queries in the middle of the cache
+    (2, 1, 5000, 8, 2, 4999, 1024),     # sliding window over the packed rows
+])
+def test_decode_attention_over_nvfp4_rows(mods, orc, batch, nq, keys, heads, kvh, q0, window):
+    """The packed reader against the dense reader over the dequantized rows and against the CPU rule
+    (src/models/inkling/flash.rs:520-540: same index arithmetic, values E2M1[code] * e4m3(scale)).
+    The packed reader multiplies in f16 (the expanded rows are exact there, probabilities keep 11
+    bits), the dense one in bf16, so the two agree to a bf16 step of the output, not to the bit."""
+    from maryml_b200 import nvfp4 as nv
+    att, _ = mods
+    D = 128
+    q, k, v = _qkv(orc, 17 * keys + nq, batch, nq, keys, heads, kvh)
+    qd = dev_bf16(q).view(batch, nq, heads, D)
+    kd = dev_bf16(k).view(batch, keys, kvh, D)
+    vd = dev_bf16(v).view(batch, keys, kvh, D)
+    kc, ks = att.quantize_kv_rows(kd)
+    vc, vs = att.quantize_kv_rows(vd)
+    # the cache bytes are the CPU quantizer's bytes for the same rows
+    codes_ref, scales_ref = orc.quantize_act_recip(bf16_bits_to_f32(k[0]), keys, kvh * D)
+    assert np.array_equal(kc[0].cpu().numpy().ravel(), codes_ref)
+    assert np.array_equal(ks[0].cpu().numpy().ravel(), scales_ref)
+    k_deq = nv.dequantize(kc.view(batch * keys, -1), ks.view(batch * keys, -1), 1.0, batch * keys, kvh * D,
+                          torch.bfloat16).view(batch, keys, kvh, D)
+    v_deq = nv.dequantize(vc.view(batch * keys, -1), vs.view(batch * keys, -1), 1.0, batch * keys, kvh * D,
+                          torch.bfloat16).view(batch, keys, kvh, D)
+    assert torch.equal(k_deq.float(), nv.dequantize(kc.view(batch * keys, -1), ks.view(batch * keys, -1), 1.0,
+                                                    batch * keys, kvh * D, torch.float32).view(batch, keys, kvh, D))
+    want = att.flash_attention(qd, k_deq, v_deq, q0=q0, window=window)
+    got = att.flash_attention_fp4kv(qd, kc, ks, vc, vs, kvh, q0=q0, window=window)
+    gw, gg = want.float(), got.float()
+    assert float((gg - gw).abs().max()) <= 1e-2 * float(gw.abs().max())
+    # both readers follow the CPU rule on the dequantized rows
+    kb = host_bits(k_deq).reshape(batch, keys, kvh * D)
+    vb = host_bits(v_deq).reshape(batch, keys, kvh * D)
+    _check(att, orc, q, kb, vb, batch, nq, keys, heads, kvh, q0, window=window)
+    gotf = bf16_bits_to_f32(host_bits(got)).reshape(batch, nq, heads * D)
+    for b in range(batch):
+        ref = orc.attention(bf16_bits_to_f32(q[b]), bf16_bits_to_f32(kb[b]), bf16_bits_to_f32(vb[b]), heads, kvh, D,
+                            q0, 1.0 / math.sqrt(D), window=window)
+        assert np.abs(gotf[b] - ref).max() <= 2e-2 * max(np.abs(ref).max(), 1e-3)
+        assert rel_check(gotf[b], ref)[1] >= 0.9999
+
+
+def test_prompt_shapes_refuse_nvfp4_rows(mods):
+    from maryml_b200 import _lib
+    att, _ = mods
+    q = torch.zeros(1, 64, 4, 128, dtype=torch.bfloat16, device="cuda")
+    z = torch.zeros(1, 64, 64, dtype=torch.uint8, device="cuda")
+    zs = torch.zeros(1, 64, 8, dtype=torch.uint8, device="cuda")
+    with pytest.raises(_lib.MaryError):
+        att.flash_attention_fp4kv(q, z, zs, z, zs, 1)
+
+
 @pytest.mark.parametrize("batch,nq,heads,kvh", [(1, 128, 4, 1), (2, 200, 8, 2), (1, 515, 4, 4)])
 def test_prefill_attention_causal(mods, orc, batch, nq, heads, kvh):
     att, _ = mods
