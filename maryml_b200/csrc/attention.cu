@@ -198,15 +198,18 @@ __device__ __forceinline__ void pv_tile(float (*o)[4], const float (*pfrag)[4], 
 
 // One online-softmax step over NT key tiles of 8: masks, updates (m, l), rescales o, leaves p in s.
 // Rows g (regs 0, 1) and g + 8 (regs 2, 3); mask_lo/hi = number of visible keys from `kbase` for those rows.
-template <int NT>
+// HI = false when rows 8..15 of the tile are all padding (at most eight query rows): their half of the
+// work is left out and their probabilities are zero.
+template <int NT, bool HI = true>
 __device__ __forceinline__ void softmax_step(float (*s)[4], float (*o)[4], float* m, float* l, float scale_log2,
                                              int vis_lo, int vis_hi, uint32_t lane, int first_lo = 0, int first_hi = 0) {
   const int t2 = (lane & 3) * 2;
+  constexpr int E = HI ? 4 : 2, H = HI ? 2 : 1;
   float mx[2] = {-INFINITY, -INFINITY};
 #pragma unroll
   for (int j = 0; j < NT; ++j) {
 #pragma unroll
-    for (int e = 0; e < 4; ++e) {
+    for (int e = 0; e < E; ++e) {
       const int key = j * 8 + t2 + (e & 1);
       const int vis = e < 2 ? vis_lo : vis_hi, first = e < 2 ? first_lo : first_hi;   // first: keys below the window
       s[j][e] = (key < vis && key >= first) ? s[j][e] * scale_log2 : -INFINITY;
@@ -214,13 +217,13 @@ __device__ __forceinline__ void softmax_step(float (*s)[4], float (*o)[4], float
     }
   }
 #pragma unroll
-  for (int h = 0; h < 2; ++h) {
+  for (int h = 0; h < H; ++h) {
     mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xFFFFFFFFu, mx[h], 1));
     mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xFFFFFFFFu, mx[h], 2));
   }
-  float corr[2], sum[2] = {0.0f, 0.0f}, mnew[2];
+  float corr[2] = {1.0f, 1.0f}, sum[2] = {0.0f, 0.0f}, mnew[2] = {-INFINITY, -INFINITY};
 #pragma unroll
-  for (int h = 0; h < 2; ++h) {
+  for (int h = 0; h < H; ++h) {
     mnew[h] = fmaxf(m[h], mx[h]);
     // a fully masked row keeps m = -inf; exp2(-inf - (-inf)) is avoided by the guard
     corr[h] = mnew[h] == -INFINITY ? 1.0f : exp2f(m[h] - mnew[h]);
@@ -230,6 +233,7 @@ __device__ __forceinline__ void softmax_step(float (*s)[4], float (*o)[4], float
   for (int j = 0; j < NT; ++j) {
 #pragma unroll
     for (int e = 0; e < 4; ++e) {
+      if (e >= E) { s[j][e] = 0.0f; continue; }
       const float mm = mnew[e >> 1];
       const float pv = mm == -INFINITY ? 0.0f : exp2f(s[j][e] - mm);
       s[j][e] = pv;
@@ -237,11 +241,11 @@ __device__ __forceinline__ void softmax_step(float (*s)[4], float (*o)[4], float
     }
   }
 #pragma unroll
-  for (int h = 0; h < 2; ++h) l[h] = l[h] * corr[h] + sum[h];   // per-thread partial; quad-reduced at the end
+  for (int h = 0; h < H; ++h) l[h] = l[h] * corr[h] + sum[h];   // per-thread partial; quad-reduced at the end
 #pragma unroll
   for (int n = 0; n < 16; ++n) {
     o[n][0] *= corr[0]; o[n][1] *= corr[0];
-    o[n][2] *= corr[1]; o[n][3] *= corr[1];
+    if (HI) { o[n][2] *= corr[1]; o[n][3] *= corr[1]; }
   }
 }
 
@@ -250,13 +254,12 @@ __device__ __forceinline__ void softmax_step(float (*s)[4], float (*o)[4], float
 // ---------------------------------------------------------------------------------
 constexpr int DEC_STAGES = 3;
 constexpr int DEC_THREADS = 160;
-// NVFP4 rows: no producer warp and no ring. Each compute warp expands the 16 key rows it
-// multiplies (K and V) from codes and scales into its rows of one bf16 tile, with the bytes of the
-// next tile already on their way in registers.
+// NVFP4 rows: no producer warp and no shared ring. Each compute warp brings in the packed bytes of
+// the 16 key rows it multiplies (K and V) through a cp.async ring of its own.
 constexpr int DEC_THREADS_FP4 = 128;
 constexpr int FP4_STAGES = 3;                     // tiles of packed bytes in flight per warp (cp.async groups)
 constexpr int FP4_RAW_WARP = 2 * 16 * (D / 2) + 2 * 16 * (D / 16);   // 16 key rows: K, V codes + K, V scales = 2304 B
-constexpr int DEC_TILE_FP4 = 36 * 1024;           // one bf16 K/V tile (32 KB); the merge patch (33.3 KB) reuses it
+constexpr int DEC_TILE_FP4 = 36 * 1024;           // room for the merge patch (33.3 KB) at the end of the kernel
 constexpr int DEC_RING_FP4 = DEC_TILE_FP4 + 4 * FP4_STAGES * FP4_RAW_WARP;
 constexpr int DEC_SMEM_FP4 = DEC_RING_FP4 + 16 * D * 2 + 1024 + 128;
 constexpr int DEC_SMEM = DEC_STAGES * KV_STAGE_BYTES + 16 * D * 2 /*Q*/ + 1024 + 128;
@@ -428,7 +431,8 @@ attn_decode_kernel(const __grid_constant__ AttnParams p) {
         first_lo = int(qpos_lo) + 1 - int(p.window) - kabs;
         first_hi = int(qpos_hi) + 1 - int(p.window) - kabs;
       }
-      softmax_step<2>(s, o, m, l, p.scale_log2, vis_lo, vis_hi, lane, first_lo, first_hi);
+      if (rows <= 8) softmax_step<2, false>(s, o, m, l, p.scale_log2, vis_lo, vis_hi, lane, first_lo, first_hi);
+      else softmax_step<2, true>(s, o, m, l, p.scale_log2, vis_lo, vis_hi, lane, first_lo, first_hi);
       if (FP4) {
         fp4_pv(o, s, raw, lane);
         __syncwarp();                              // the warp is done with the ring slot
