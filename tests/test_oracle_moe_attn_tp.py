@@ -3,6 +3,8 @@ in-source known-answer tests (cited by file:line, paths relative to the referenc
 import numpy as np
 import pytest
 
+from oracle_lib import bf16_bits_to_f32, f32_to_bf16_bits  # noqa: E402
+
 MTILE = 16  # the reference's m16 MMA tile (src/models/inkling/moegroup.rs)
 
 
@@ -109,6 +111,30 @@ def test_cpu_attention_uses_absolute_positions_and_window_edges(orc):
         out = orc.attention(np.zeros(3), np.zeros(4), np.array([1.0, 10.0, 100.0, 1000.0]), heads=1, kv_heads=1, D=1,
                             q0=3, scale=1.0, key_pos=[0, 2, 5, 9], window=window)
         assert np.allclose(out.ravel(), expected, atol=1e-12)
+
+
+def test_packed_kv_reader_index_rule(orc):
+    # src/models/inkling/flash.rs:520-540 `nvfp4_at`: element idx of a [rows, kv_heads * head_dim] page lives in
+    # word idx / 8 at nibble idx % 8, its scale is E4M3 byte idx / 16, value = E2M1[code] * scale (no global scale);
+    # src/models/inkling/kvpages.rs:1378-1404: the page is the row-major quantization of those rows.
+    rows, kvh, D = 5, 2, 128
+    width = kvh * D
+    x = orc.normal_f32(31, rows * width, 2.0)
+    codes, scales = orc.quantize_act_recip(x, rows, width)
+    words = codes.view(np.uint32)
+    e2m1 = np.array([0, .5, 1, 1.5, 2, 3, 4, 6, -0.0, -.5, -1, -1.5, -2, -3, -4, -6], np.float32)
+    idx = np.arange(rows * width)
+    code = (words[idx // 8] >> ((idx % 8) * 4).astype(np.uint32)) & 15
+    sc = np.array([orc.e4m3_to_f32(int(b)) for b in scales], np.float32)[idx // 16]
+    want = e2m1[code] * sc
+    got = orc.dequantize(codes, scales, 1.0)
+    assert np.array_equal(got.reshape(-1), want)
+    # a row's bytes are its own: appending rows changes no earlier byte (kvpages.rs: "paged-safe")
+    c2, s2 = orc.quantize_act_recip(x[: 3 * width], 3, width)
+    assert np.array_equal(c2, codes[: 3 * width // 2]) and np.array_equal(s2, scales[: 3 * width // 16])
+    # every value is exact in f16 and in bf16 (at most 7 significant bits, magnitude within [2^-10, 2688])
+    assert np.array_equal(want.astype(np.float16).astype(np.float32), want)
+    assert np.array_equal(bf16_bits_to_f32(f32_to_bf16_bits(want)), want)
 
 
 def test_attention_gqa_and_causality(orc):
