@@ -670,14 +670,25 @@ int make_tmap_4d(mb_ctx* ctx, CUtensorMap* tm, const void* basep, uint64_t batch
 }
 
 uint32_t decode_splits(size_t batch, size_t kv_heads, size_t keys) {
-  // Fill a 148-SM part about eight CTAs deep; never split below 256 keys.
+  // Fill a 148-SM part about eight CTAs deep; never split below 256 keys. The CTAs of a launch all
+  // take about the same time, so among a few more splits than that the count whose last wave of
+  // 148 x 2 resident CTAs is fullest wins (5 splits of 256 (sequence, head) pairs leave the fifth wave
+  // a third full, 8 fill seven waves).
   size_t base = batch * kv_heads;
   size_t want = (size_t(148) * 8 + base - 1) / base;
   size_t max_splits = (keys + 255) / 256;
-  size_t s = want < 1 ? 1 : want;
-  if (s > max_splits) s = max_splits;
-  if (s > 64) s = 64;
-  return uint32_t(s ? s : 1);
+  if (max_splits > 64) max_splits = 64;
+  if (want < 1) want = 1;
+  if (want >= max_splits) return uint32_t(max_splits ? max_splits : 1);
+  const size_t slots = size_t(148) * 2;
+  size_t best = want;
+  double best_eff = 0.0;
+  for (size_t s = want; s <= want + 6 && s <= max_splits; ++s) {
+    const size_t total = base * s, waves = (total + slots - 1) / slots;
+    const double eff = double(total) / double(waves * slots);
+    if (eff > best_eff + 0.02) { best_eff = eff; best = s; }
+  }
+  return uint32_t(best);
 }
 
 }  // namespace
