@@ -382,26 +382,36 @@ attn_decode_kernel(const __grid_constant__ AttnParams p) {
     const uint8_t* vc0 = p.v_codes + (size_t(b) * p.keys * p.kv_heads + kvh) * (D / 2);
     const uint8_t* ks0 = p.k_scales + (size_t(b) * p.keys * p.kv_heads + kvh) * (D / 16);
     const uint8_t* vs0 = p.v_scales + (size_t(b) * p.keys * p.kv_heads + kvh) * (D / 16);
+    // lane's sources for tile 0, advanced by 64 rows per tile: two 16-byte chunks of K and of V codes
+    // (chunk i = lane + 32 u of 64: key row i >> 2, part i & 3) and one row's eight scale bytes
+    // (lanes 0-15 K, 16-31 V). Rows past the slice are masked: zero fill keeps P V finite, and their
+    // (unread) source is the slice's first row.
+    const uint32_t key_c = k_begin + uint32_t(warp) * 16u + (lane >> 2), key_s = k_begin + uint32_t(warp) * 16u + (lane & 15u);
+    const uint8_t* kc_first = kc0 + size_t(k_begin) * stride_c;
+    const uint8_t* sc_first = (lane < 16 ? ks0 : vs0) + size_t(k_begin) * stride_s;
+    const ptrdiff_t v_minus_k = vc0 - kc0;
+    const uint8_t* kc_p = kc0 + size_t(key_c) * stride_c + (lane & 3u) * 16u;
+    const uint8_t* sc_p = (lane < 16 ? ks0 : vs0) + size_t(key_s) * stride_s;
+    uint32_t issued = 0;                                 // tiles issued so far: issue() is called for t = 0, 1, 2, ...
     auto issue = [&](uint32_t t) {
       if (t < n_tiles) {
         const uint32_t dst = smem_u32(raw_ring + (t % FP4_STAGES) * FP4_RAW_WARP);
-        const uint32_t kfirst = k_begin + t * BC + uint32_t(warp) * 16u;
 #pragma unroll
-        for (int u = 0; u < 2; ++u) {            // chunk i = lane + 32 u of 64: key row i >> 2, 16-byte part i & 3
-          const uint32_t i = lane + 32u * u, key = kfirst + (i >> 2);
-          const bool live = key < k_end;         // rows past the slice are masked: zeros keep P V finite
-          const size_t off = size_t(live ? key : k_begin) * stride_c + (i & 3u) * 16u;
-          const uint32_t n = live ? 16u : 0u;
-          asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst + i * 16u), "l"(kc0 + off), "r"(n) : "memory");
-          asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst + 1024u + i * 16u), "l"(vc0 + off), "r"(n) : "memory");
+        for (int u = 0; u < 2; ++u) {
+          const bool live = key_c + issued * BC + 8u * u < k_end;
+          const uint8_t* src = live ? kc_p + size_t(8u * u) * stride_c : kc_first;
+          const uint32_t n = live ? 16u : 0u, i = lane + 32u * u;
+          asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst + i * 16u), "l"(src), "r"(n) : "memory");
+          asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst + 1024u + i * 16u), "l"(src + v_minus_k), "r"(n) : "memory");
         }
         {
-          const uint32_t r = lane & 15u, key = kfirst + r;
-          const bool live = key < k_end;
-          const uint8_t* src = (lane < 16 ? ks0 : vs0) + size_t(live ? key : k_begin) * stride_s;
-          const uint32_t n = live ? 8u : 0u;
-          asm volatile("cp.async.ca.shared.global [%0], [%1], 8, %2;" ::"r"(dst + 2048u + lane * 8u), "l"(src), "r"(n) : "memory");
+          const bool live = key_s + issued * BC < k_end;
+          asm volatile("cp.async.ca.shared.global [%0], [%1], 8, %2;" ::"r"(dst + 2048u + lane * 8u),
+                       "l"(live ? sc_p : sc_first), "r"(live ? 8u : 0u) : "memory");
         }
+        kc_p += size_t(BC) * stride_c;
+        sc_p += size_t(BC) * stride_s;
+        ++issued;
       }
       asm volatile("cp.async.commit_group;" ::: "memory");   // an empty group keeps the count uniform
     };
