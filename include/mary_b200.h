@@ -232,6 +232,21 @@ int mb_router_topk(mb_ctx* ctx, mb_stream stream, const float* logits, const flo
                    size_t tokens, size_t n_experts, size_t k, int renormalize, float scaling, int32_t* idx,
                    float* weight);
 
+/* The Inkling router decision with shared-expert sinks: router_topk_launch
+ * (src/models/inkling/routetopk.rs:112-266) and its host twin route_from_logits
+ * (src/models/inkling/block.rs:176-258). logits [tokens, n_routed + n_shared] f32. The k experts
+ * are picked among the n_routed by sigmoid(logit) + bias[e] (f32; descending, ties to the lower
+ * index); the bias takes no part in the weights. The k chosen logits followed by the n_shared sink
+ * logits share one softmax over log_sigmoid (summed in that order):
+ * weight = exp(lp - lse) * route_scale * global_scale -> weight [tokens, k] for the chosen experts,
+ * shared_gammas [tokens, n_shared] for the sinks (NULL when n_shared == 0). The reference packs ids,
+ * weights and a flag column into one f32 buffer for a single readback; here they are separate arrays
+ * and a non-finite logit raises the router flag of the context (token + 1). n_routed % 32 == 0,
+ * n_routed <= 512, n_shared <= 32, k <= 32. */
+int mb_router_topk_sinks(mb_ctx* ctx, mb_stream stream, const float* logits, const float* bias, float global_scale,
+                         float route_scale, size_t tokens, size_t n_routed, size_t n_shared, size_t k, int32_t* idx,
+                         float* weight, float* shared_gammas);
+
 /* RowPlan::build / plan_from_topk (src/models/inkling/moegroup.rs:1850-1909,
  * src/models/inkling/devplan.rs:216-301), on the device for any token count:
  * rows stacked expert-ascending then token-ascending, each expert padded to 128

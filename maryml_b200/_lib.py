@@ -50,6 +50,7 @@ SIGNATURES = {
     "mb_bf16_gemm_splitk_workspace": (_sz, [_sz, _sz, _sz]),
     "mb_bf16_gemm_splitk": (_i, [_vp, _vp, _vp, _vp, _f, _sz, _sz, _sz, _vp, _i, _vp, _sz]),
     "mb_router_topk_softmax": (_i, [_vp, _vp, _vp, _sz, _sz, _sz, _i, _f, _vp, _vp]),
+    "mb_router_topk_sinks": (_i, [_vp, _vp, _vp, _vp, _f, _f, _sz, _sz, _sz, _sz, _vp, _vp, _vp]),
     "mb_router_topk": (_i, [_vp, _vp, _vp, _vp, _i, _sz, _sz, _sz, _i, _f, _vp, _vp]),
     "mb_moe_plan_rows": (_sz, [_sz, _sz, _sz]),
     "mb_moe_plan_workspace": (_sz, [_sz, _sz, _sz]),

@@ -139,6 +139,93 @@ router_topk_kernel(const float* __restrict__ logits, const float* __restrict__ b
 }
 
 // ---------------------------------------------------------------------------------
+// Router with shared-expert sinks. One warp per token; logits [tokens, n_routed + n_shared].
+// Selection among the routed experts by sigmoid(x) + bias in f32 (descending, ties to the lower
+// index), as the rounds above. The k chosen logits (lane r keeps pick r) and the n_shared sink
+// logits (lane r keeps sink r) then share one softmax over log_sigmoid, summed in index order,
+// chosen first; weights are exp(lp - lse) * route_scale * global_scale. Every f32 exp / log of the
+// CPU rule is taken here as the f64 function rounded to f32: the correctly rounded value, which is
+// what a good libm returns in all but a vanishing share of arguments.
+// ---------------------------------------------------------------------------------
+__device__ __forceinline__ float exp32(float x) { return float(exp(double(x))); }
+__device__ __forceinline__ float log32(float x) { return float(log(double(x))); }
+__device__ __forceinline__ float sigmoid32(float x) {
+  if (x >= 0.0f) return __fdiv_rn(1.0f, __fadd_rn(1.0f, exp32(-x)));
+  const float e = exp32(x);
+  return __fdiv_rn(e, __fadd_rn(1.0f, e));
+}
+__device__ __forceinline__ float log_sigmoid32(float x) {
+  if (x >= 0.0f) return -log32(__fadd_rn(1.0f, exp32(-x)));
+  return __fsub_rn(x, log32(__fadd_rn(1.0f, exp32(x))));
+}
+
+template <int EPL>
+__global__ void __launch_bounds__(128)
+router_sinks_kernel(const float* __restrict__ logits, const float* __restrict__ bias, float global_scale,
+                    float route_scale, uint32_t tokens, uint32_t n_routed, uint32_t n_shared, uint32_t k,
+                    int32_t* __restrict__ idx, float* __restrict__ weight, float* __restrict__ gammas,
+                    int* __restrict__ flag) {
+  const uint32_t lane = threadIdx.x & 31;
+  const uint32_t t = blockIdx.x * 4 + (threadIdx.x >> 5);
+  if (t >= tokens) return;
+  const float* row = logits + size_t(t) * (n_routed + n_shared);
+  float x[EPL];
+  uint32_t key[EPL];
+  bool bad = false;
+#pragma unroll
+  for (int j = 0; j < EPL; ++j) {
+    x[j] = __ldg(row + lane + 32 * j);
+    if (!(fabsf(x[j]) <= 3.4028234663852886e38f)) bad = true;
+    const float c = __fadd_rn(sigmoid32(x[j]), __ldg(bias + lane + 32 * j)) + 0.0f;   // -0 -> +0
+    if (!(fabsf(c) <= 3.4028234663852886e38f)) bad = true;
+    key[j] = router_key(c);
+  }
+  const float xs = lane < n_shared ? __ldg(row + n_routed + lane) : 0.0f;
+  if (!(fabsf(xs) <= 3.4028234663852886e38f)) bad = true;
+  if (__any_sync(0xFFFFFFFFu, bad)) {
+    if (lane == 0) atomicCAS(flag, 0, int(t) + 1);
+  }
+  uint32_t taken = 0;
+  float my_x = 0.0f;    // lane r keeps the logit of pick r
+  int my_i = 0;
+  for (uint32_t r = 0; r < k; ++r) {
+    uint32_t bk = 0, bi = 0xFFFFFFFFu;
+    float bx = 0.0f;
+#pragma unroll
+    for (int j = 0; j < EPL; ++j) {
+      const bool free_slot = !((taken >> j) & 1u);
+      if (free_slot && (bi == 0xFFFFFFFFu || key[j] > bk)) {
+        bk = key[j];
+        bi = lane + 32 * j;
+        bx = x[j];
+      }
+    }
+    const uint32_t mk = __reduce_max_sync(0xFFFFFFFFu, bk);
+    const uint32_t best_i = __reduce_min_sync(0xFFFFFFFFu, bk == mk ? bi : 0xFFFFFFFFu);
+    const float best_x = __shfl_sync(0xFFFFFFFFu, bx, best_i & 31u);
+    if ((best_i & 31u) == lane) taken |= 1u << (best_i >> 5);
+    if (lane == r) { my_x = best_x; my_i = int(best_i); }
+  }
+  const float lp_sel = lane < k ? log_sigmoid32(my_x) : -INFINITY;
+  const float lp_sh = lane < n_shared ? log_sigmoid32(xs) : -INFINITY;
+  float m = fmaxf(lp_sel, lp_sh);
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xFFFFFFFFu, m, o));
+  const float e_sel = lane < k ? exp32(__fsub_rn(lp_sel, m)) : 0.0f;
+  const float e_sh = lane < n_shared ? exp32(__fsub_rn(lp_sh, m)) : 0.0f;
+  float sum = 0.0f;     // index order: the chosen experts, then the sinks
+  for (uint32_t r = 0; r < k; ++r) sum = __fadd_rn(sum, __shfl_sync(0xFFFFFFFFu, e_sel, r));
+  for (uint32_t r = 0; r < n_shared; ++r) sum = __fadd_rn(sum, __shfl_sync(0xFFFFFFFFu, e_sh, r));
+  const float lse = __fadd_rn(m, log32(sum));
+  if (lane < k) {
+    idx[size_t(t) * k + lane] = my_i;
+    weight[size_t(t) * k + lane] = __fmul_rn(__fmul_rn(exp32(__fsub_rn(lp_sel, lse)), route_scale), global_scale);
+  }
+  if (lane < n_shared)
+    gammas[size_t(t) * n_shared + lane] = __fmul_rn(__fmul_rn(exp32(__fsub_rn(lp_sh, lse)), route_scale), global_scale);
+}
+
+// ---------------------------------------------------------------------------------
 // Row plan
 // ---------------------------------------------------------------------------------
 constexpr int PLAN_PAD = 128;   // rows per GEMM tile: each expert's rows are padded to this
@@ -440,6 +527,38 @@ MB_API int mb_router_topk_softmax(mb_ctx* ctx, mb_stream stream, const float* lo
                                   float* weight) {
   return mb_router_topk(ctx, stream, logits, nullptr, MB_ROUTER_SOFTMAX, tokens, n_experts, k, renormalize, scaling,
                         idx, weight);
+}
+
+MB_API int mb_router_topk_sinks(mb_ctx* ctx, mb_stream stream_, const float* logits, const float* bias,
+                                float global_scale, float route_scale, size_t tokens, size_t n_routed, size_t n_shared,
+                                size_t k, int32_t* idx, float* weight, float* shared_gammas) {
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  MB_REQUIRE(ctx, ctx && logits && bias && idx && weight && (n_shared == 0 || shared_gammas), "router: null argument");
+  MB_REQUIRE(ctx, tokens > 0, "router: route() on zero tokens");
+  MB_REQUIRE(ctx, n_routed >= 32 && n_routed % 32 == 0 && n_routed <= 512,
+             "router: n_routed must be a multiple of 32 up to 512, got %zu", n_routed);
+  MB_REQUIRE(ctx, n_shared <= 32, "router: at most 32 shared experts, got %zu", n_shared);
+  MB_REQUIRE(ctx, k >= 1 && k <= 32 && k <= n_routed, "router: top_k must be 1..32, got %zu", k);
+  const unsigned grid = unsigned((tokens + 3) / 4);
+  int* flag = ctx->flags_dev + MB_FLAG_ROUTER_NONFINITE;
+#define ROUTE(EPL)                                                                                               \
+  router_sinks_kernel<EPL><<<grid, 128, 0, stream>>>(logits, bias, global_scale, route_scale, uint32_t(tokens),  \
+                                                     uint32_t(n_routed), uint32_t(n_shared), uint32_t(k), idx,   \
+                                                     weight, shared_gammas, flag)
+  switch (n_routed / 32) {
+    case 1: ROUTE(1); break;
+    case 2: ROUTE(2); break;
+    case 3: ROUTE(3); break;
+    case 4: ROUTE(4); break;
+    case 6: ROUTE(6); break;
+    case 8: ROUTE(8); break;
+    case 12: ROUTE(12); break;
+    case 16: ROUTE(16); break;
+    default: return mb_fail(ctx, MB_ERR_INVALID, "router: unsupported expert count %zu", n_routed);
+  }
+#undef ROUTE
+  MB_LAUNCH_OK(ctx);
+  return MB_OK;
 }
 
 MB_API size_t mb_moe_plan_rows(size_t tokens, size_t k, size_t n_experts) {

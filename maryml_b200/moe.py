@@ -52,6 +52,24 @@ def router_topk(logits, k, activation="softmax", bias=None, renormalize=True, sc
     return idx, weight
 
 
+def router_topk_sinks(logits, bias, n_routed, k, global_scale=1.0, route_scale=1.0):
+    """route_from_logits (src/models/inkling/block.rs:176-258; device form routetopk.rs): the k routed experts
+    picked by sigmoid + bias, weighted together with the shared-expert sinks in one softmax over log_sigmoid.
+    Returns (experts [tokens, k] int32, weights [tokens, k], shared_gammas [tokens, n_shared])."""
+    assert logits.dtype == torch.float32 and logits.is_contiguous() and logits.dim() == 2
+    assert bias.dtype == torch.float32 and bias.is_contiguous() and bias.numel() == n_routed
+    tokens, rows = logits.shape
+    n_shared = rows - n_routed
+    ctx = context(logits.device.index)
+    idx = torch.empty((tokens, k), dtype=torch.int32, device=logits.device)
+    weight = torch.empty((tokens, k), dtype=torch.float32, device=logits.device)
+    gammas = torch.empty((tokens, n_shared), dtype=torch.float32, device=logits.device)
+    ctx.check(lib.mb_router_topk_sinks(ctx.handle, _stream(), _p(logits), _p(bias), float(global_scale),
+                                       float(route_scale), tokens, n_routed, n_shared, k, _p(idx), _p(weight),
+                                       _p(gammas) if n_shared else None))
+    return idx, weight, gammas
+
+
 class RowPlan:
     """RowPlan::build on the device (src/models/inkling/moegroup.rs:1850-1909)."""
 

@@ -500,6 +500,50 @@ ORC_API int orc_router_select(const float* scores, const float* bias, size_t tok
   return 0;
 }
 
+// The Inkling router with shared-expert sinks (src/models/inkling/block.rs:176-258, host twin of
+// src/models/inkling/routetopk.rs): selection among the n_routed experts by sigmoid(logit) + bias
+// (f32, descending, ties to the lower index); the weights are a softmax over log_sigmoid of the
+// chosen routed logits followed by the n_shared sink logits, times route_scale, times global_scale.
+// All arithmetic in f32 with the host's expf/logf, sums in index order. logits [tokens, n_routed +
+// n_shared]. Returns 0, or 1 with the first non-finite (token, row) in bad[0..1] (the reference panics).
+static float orc_sigmoid32(float x) {                     // block.rs:260-267
+  if (x >= 0.0f) return 1.0f / (1.0f + std::exp(-x));
+  float e = std::exp(x);
+  return e / (1.0f + e);
+}
+static float orc_log_sigmoid32(float x) {                 // block.rs:20-26
+  if (x >= 0.0f) return -std::log(1.0f + std::exp(-x));
+  return x - std::log(1.0f + std::exp(x));
+}
+ORC_API int orc_router_sinks(const float* logits, const float* bias, float global_scale, float route_scale,
+                             size_t tokens, size_t n_routed, size_t n_shared, size_t k, uint32_t* idx,
+                             float* weight, float* gammas, size_t* bad) {
+  const size_t rows = n_routed + n_shared;
+  std::vector<uint32_t> order(n_routed);
+  std::vector<float> score(n_routed), lp(k + n_shared);
+  for (size_t t = 0; t < tokens; ++t) {
+    const float* row = logits + t * rows;
+    for (size_t r = 0; r < rows; ++r)
+      if (!std::isfinite(row[r])) { bad[0] = t; bad[1] = r; return 1; }
+    for (size_t e = 0; e < n_routed; ++e) score[e] = orc_sigmoid32(row[e]) + bias[e];
+    std::iota(order.begin(), order.end(), 0u);
+    std::sort(order.begin(), order.end(), [&](uint32_t a, uint32_t b) {
+      if (score[a] != score[b]) return score[a] > score[b];
+      return a < b;
+    });
+    for (size_t j = 0; j < k; ++j) { idx[t * k + j] = order[j]; lp[j] = orc_log_sigmoid32(row[order[j]]); }
+    for (size_t j = 0; j < n_shared; ++j) lp[k + j] = orc_log_sigmoid32(row[n_routed + j]);
+    float m = -std::numeric_limits<float>::infinity();
+    for (float v : lp) m = std::max(m, v);
+    float sum = 0.0f;
+    for (float v : lp) sum += std::exp(v - m);
+    const float lse = m + std::log(sum);
+    for (size_t j = 0; j < k; ++j) weight[t * k + j] = std::exp(lp[j] - lse) * route_scale * global_scale;
+    for (size_t j = 0; j < n_shared; ++j) gammas[t * n_shared + j] = std::exp(lp[k + j] - lse) * route_scale * global_scale;
+  }
+  return 0;
+}
+
 // Router logits from bf16 hidden states and a bf16 gate: f32 = sum in f64
 // (router.rs:310-339, Accum::F64) of the widened operands.
 ORC_API void orc_router_logits(const uint16_t* h, const uint16_t* gate, size_t tokens, size_t hid, size_t n,

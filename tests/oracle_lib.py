@@ -58,6 +58,7 @@ class Oracle:
             "orc_router_scores_softmax": (None, [P(f32), sz, sz, P(f32)]),
             "orc_router_scores_sigmoid": (None, [P(f32), sz, sz, P(f32)]),
             "orc_router_select": (C.c_int, [P(f32), P(f32), sz, sz, sz, C.c_int, f32, P(u32), P(f32)]),
+            "orc_router_sinks": (C.c_int, [P(f32), P(f32), f32, f32, sz, sz, sz, sz, P(u32), P(f32), P(f32), P(sz)]),
             "orc_router_logits": (None, [P(u16), P(u16), sz, sz, sz, P(f32)]),
             "orc_row_plan": (C.c_longlong, [P(u32), P(f32), sz, sz, sz, sz, sz, P(i32), P(f32), P(u32), P(u32),
                                             P(u32), P(u32), P(u32), P(u32), P(u32)]),
@@ -242,6 +243,24 @@ class Oracle:
         if rc != 0:
             raise ValueError("router: non-finite score")
         return idx, w
+
+    def router_sinks(self, logits, bias, n_routed, k, global_scale=1.0, route_scale=1.0):
+        """route_from_logits (src/models/inkling/block.rs:176-258) -> (experts, weights, shared_gammas)."""
+        logits = np.ascontiguousarray(logits, np.float32)
+        tokens, rows = logits.shape
+        n_shared = rows - n_routed
+        bias = np.ascontiguousarray(bias, np.float32)
+        assert bias.size == n_routed
+        idx = np.empty((tokens, k), np.uint32)
+        w = np.empty((tokens, k), np.float32)
+        gam = np.empty((tokens, max(n_shared, 1)), np.float32)
+        bad = (C.c_size_t * 2)()
+        rc = self.lib.orc_router_sinks(_ptr(logits, C.c_float), _ptr(bias, C.c_float), float(np.float32(global_scale)),
+                                       float(np.float32(route_scale)), tokens, n_routed, n_shared, k,
+                                       _ptr(idx, C.c_uint32), _ptr(w, C.c_float), _ptr(gam, C.c_float), bad)
+        if rc != 0:
+            raise ValueError(f"router logit is non-finite at token {bad[0]}, row {bad[1]}")
+        return idx, w, gam[:, :n_shared]
 
     def router_logits(self, h_bits, gate_bits, tokens, hid, n):
         h_bits = np.ascontiguousarray(h_bits, np.uint16).reshape(-1)

@@ -97,6 +97,41 @@ def test_gather_of_quantized_planes_equals_quantizer_with_gather(moe, tokens, k,
     assert ctx.check_flags(None)[0] == 0
 
 
+@pytest.mark.parametrize("tokens,n_routed,n_shared,k", [(1, 32, 0, 1), (37, 256, 2, 6), (512, 256, 1, 6), (300, 384, 4, 8),
+                                                         (64, 64, 32, 32)])
+def test_sink_router_against_the_cpu_rule(moe, orc, tokens, n_routed, n_shared, k):
+    rows = n_routed + n_shared
+    logits = (orc.normal_f32(277 + tokens, tokens * rows, 2.0)).reshape(tokens, rows)
+    bias = (orc.normal_f32(5 + n_routed, n_routed, 0.1)).astype(np.float32)
+    if tokens > 2:
+        logits[1, :] = 0.25          # an all-tie row
+        bias[: n_routed // 2] = bias[0]
+        logits[2, 5] = logits[2, 9]
+        bias[9] = bias[5]
+    idx, w, gam = moe.router_topk_sinks(torch.from_numpy(logits).cuda(), torch.from_numpy(bias).cuda(), n_routed, k,
+                                        global_scale=0.75, route_scale=2.5)
+    idx_ref, w_ref, gam_ref = orc.router_sinks(logits, bias, n_routed, k, global_scale=0.75, route_scale=2.5)
+    assert np.array_equal(idx.cpu().numpy().astype(np.uint32), idx_ref)
+    # f32 chains of exp / log: the device takes each as the rounded f64 function, the host its libm
+    assert np.allclose(w.cpu().numpy(), w_ref, rtol=2e-6, atol=1e-9)
+    assert np.allclose(gam.cpu().numpy(), gam_ref, rtol=2e-6, atol=1e-9)
+    total = w.sum(1) + gam.sum(1)
+    assert float((total - 0.75 * 2.5).abs().max()) <= 1e-5
+
+
+def test_sink_router_flags_non_finite_shared_logit(moe):
+    # src/models/inkling/block.rs:273-279: a NaN in a sink column is loud too
+    from maryml_b200 import _lib
+    ctx = _lib.context(0)
+    ctx.check_flags(None)
+    logits = torch.zeros(4, 34, device="cuda")
+    logits[2, 33] = float("nan")
+    moe.router_topk_sinks(logits, torch.zeros(32, device="cuda"), 32, 2)
+    rc, flags = ctx.check_flags(None)
+    assert rc == _lib.ERR_DEVICE_FLAG and flags[1] == 3
+    assert ctx.check_flags(None)[0] == 0
+
+
 def test_router_flags_non_finite_logits(moe, orc):
     from maryml_b200 import _lib
     ctx = _lib.context(0)

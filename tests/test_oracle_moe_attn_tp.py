@@ -82,6 +82,31 @@ def test_sigmoid_router_known_answers(orc):
     assert w1[0, 0] < 1.0                               # the bias is not in the weight
 
 
+def test_sink_router_known_answers(orc):
+    # src/models/inkling/block.rs:273-300 as written there
+    with pytest.raises(ValueError, match="token 0, row 3"):
+        orc.router_sinks(np.array([[0.25, -0.5, 1.0, np.nan]], np.float32), [0.0, 0.0], 2, 1)
+    logits = np.array([[0.25, -0.5, 1.0, -2.0], [0.75, 0.125, -0.25, 0.5]], np.float32)
+    idx, w, gam = orc.router_sinks(logits, [0.0, 0.0], 2, 1)
+    assert w.size + gam.size == 6 and np.isfinite(w).all() and np.isfinite(gam).all()
+    assert idx.tolist() == [[0], [0]]
+    # the chosen routed experts and the sinks share one softmax: the weights sum to route_scale * global_scale
+    idx, w, gam = orc.router_sinks(logits, [0.0, 0.0], 2, 1, global_scale=0.5, route_scale=2.5)
+    assert np.allclose(w.sum(1) + gam.sum(1), 1.25, rtol=1e-6)
+    # restated: weights are softmax(log_sigmoid(logits)) over [chosen, sinks], i.e. sigmoid / sum of sigmoids
+    sg = 1.0 / (1.0 + np.exp(-logits.astype(np.float64)))
+    want = sg[0, [0, 2, 3]] / sg[0, [0, 2, 3]].sum() * 1.25
+    assert np.allclose(np.concatenate([w[0], gam[0]]), want, rtol=1e-5)
+    # the bias moves the selection and takes no part in the weights (block.rs:236-252)
+    idx_b, w_b, gam_b = orc.router_sinks(logits, [0.0, 1.0], 2, 1)
+    assert idx_b.tolist() == [[1], [1]]
+    sg1 = sg[1, [1, 2, 3]] / sg[1, [1, 2, 3]].sum()
+    assert np.allclose(np.concatenate([w_b[1], gam_b[1]]), sg1, rtol=1e-5)
+    # ties go to the lower index
+    idx_t, _, _ = orc.router_sinks(np.zeros((1, 6), np.float32), np.zeros(4, np.float32), 4, 3)
+    assert idx_t.tolist() == [[0, 1, 2]]
+
+
 def test_softmax_scores_follow_the_f64_recipe(orc):
     # router.rs:352-368: f64 exp, f32 store, f32(f64(v)/s)
     rng = np.random.default_rng(0)
