@@ -286,6 +286,19 @@ int mb_attention_window(mb_ctx* ctx, mb_stream stream, const void* q, const void
                         size_t nq, size_t keys, size_t heads, size_t kv_heads, size_t d, size_t q0, float scale,
                         size_t window, void* out, void* workspace, size_t workspace_bytes);
 
+/* Causal decode attention with the remaining terms of flash_attention_kernel
+ * (src/models/inkling/flash.rs:751-785): a relative bias and eviction gaps.
+ * rel (or NULL): [batch, nq, heads, eff] f32; a visible key at distance dist = q_abs - k_abs < eff
+ * gets rel[.., dist] added to its scaled score. gap_rows / gap_cums (ngaps <= 64 device words each,
+ * rows ascending; or NULL, 0): the key in cache row r sits at position r + gap_cums[g] for the last g
+ * with gap_rows[g] <= r, at r when there is none; visibility, the window and the bias distance all
+ * use positions, and q0 is the position of the first query. All sequences of a call share the gap
+ * list. window = 0: none. Decode shapes only (nq * heads / kv_heads <= 16). */
+int mb_attention_decode_ext(mb_ctx* ctx, mb_stream stream, const void* q, const void* k, const void* v, size_t batch,
+                            size_t nq, size_t keys, size_t heads, size_t kv_heads, size_t d, size_t q0, float scale,
+                            size_t window, const float* rel, size_t eff, const uint32_t* gap_rows,
+                            const uint32_t* gap_cums, size_t ngaps, void* out, void* workspace, size_t workspace_bytes);
+
 /* Decode attention over an NVFP4 key/value cache: the packed reader of flash_attention_kernel
  * (`nvfp4_at`, src/models/inkling/flash.rs:520-540, 827-859) over the Fp4Rows page layout
  * (src/models/inkling/kvpages.rs:1378-1404): a cache row of kv_heads * D features is quantized

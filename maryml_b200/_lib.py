@@ -59,6 +59,8 @@ SIGNATURES = {
     "mb_attention_workspace": (_sz, [_sz, _sz, _sz, _sz, _sz, _sz]),
     "mb_attention": (_i, [_vp, _vp, _vp, _vp, _vp, _sz, _sz, _sz, _sz, _sz, _sz, _sz, _f, _i, _vp, _vp, _sz]),
     "mb_attention_window": (_i, [_vp, _vp, _vp, _vp, _vp, _sz, _sz, _sz, _sz, _sz, _sz, _sz, _f, _sz, _vp, _vp, _sz]),
+    "mb_attention_decode_ext": (_i, [_vp, _vp, _vp, _vp, _vp, _sz, _sz, _sz, _sz, _sz, _sz, _sz, _f, _sz, _vp, _sz, _vp, _vp,
+                                     _sz, _vp, _vp, _sz]),
     "mb_attention_fp4kv": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _sz, _sz, _sz, _sz, _sz, _sz, _sz, _f, _i, _sz,
                                 _vp, _vp, _sz]),
     "mb_attention_decode_static": (_i, [_vp, _vp, _vp, _vp, _vp, _sz, _sz, _sz, _sz, _sz, _sz, _sz, _f, _i, _vp]),

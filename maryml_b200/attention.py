@@ -39,6 +39,37 @@ def flash_attention(q, k, v, q0=0, scale=None, causal=True, workspace=None, wind
     return out
 
 
+def decode_attention_ext(q, k, v, q0, scale=None, window=0, rel=None, gaps=None, workspace=None):
+    """Causal decode attention with a relative bias table rel [batch, nq, heads, eff] and eviction gaps
+    (src/models/inkling/flash.rs:751-785). gaps: (gap_rows, gap_cums) int32 CUDA tensors, rows ascending: the key in
+    cache row r sits at position r + gap_cums[g] for the last g with gap_rows[g] <= r. q0 is a position."""
+    assert q.dtype == k.dtype == v.dtype == torch.bfloat16
+    assert q.is_contiguous() and k.is_contiguous() and v.is_contiguous()
+    batch, nq, heads, d = q.shape
+    _, keys, kv_heads, _ = k.shape
+    ctx = context(q.device.index)
+    if scale is None:
+        scale = 1.0 / math.sqrt(d)
+    eff = 0
+    if rel is not None:
+        assert rel.dtype == torch.float32 and rel.is_contiguous() and rel.shape[:3] == (batch, nq, heads)
+        eff = rel.shape[3]
+    rows = cums = None
+    ngaps = 0
+    if gaps is not None:
+        rows, cums = gaps
+        assert rows.dtype == cums.dtype == torch.int32 and rows.numel() == cums.numel()
+        ngaps = rows.numel()
+    out = torch.empty_like(q)
+    need = int(lib.mb_attention_workspace(batch, nq, keys, heads, kv_heads, d))
+    if need and (workspace is None or workspace.numel() < need):
+        workspace = torch.empty(need, dtype=torch.uint8, device=q.device)
+    ctx.check(lib.mb_attention_decode_ext(ctx.handle, _stream(), _p(q), _p(k), _p(v), batch, nq, keys, heads, kv_heads, d,
+                                          q0, float(scale), int(window), _p(rel), eff, _p(rows), _p(cums), ngaps,
+                                          _p(out), _p(workspace) if need else None, need))
+    return out
+
+
 def quantize_kv_rows(x):
     """[batch, keys, kv_heads, D] bf16 cache rows -> (codes [batch, keys, kv_heads*D/2], scales
     [batch, keys, kv_heads*D/16]) in the Fp4Rows layout (src/models/inkling/kvpages.rs:1378-1404):

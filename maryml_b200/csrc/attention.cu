@@ -265,7 +265,8 @@ constexpr int DEC_SMEM_FP4 = DEC_RING_FP4 + 16 * D * 2 + 1024 + 128;
 constexpr int DEC_SMEM = DEC_STAGES * KV_STAGE_BYTES + 16 * D * 2 /*Q*/ + 1024 + 128;
 static_assert(4 * 16 * (D + 2) * 4 <= DEC_STAGES * KV_STAGE_BYTES, "the merge patch reuses the tile ring");
 
-template <bool FP4>
+// EXT: the instantiation with the relative bias and the eviction gaps (positions instead of rows in the masks)
+template <bool FP4, bool EXT = false>
 __global__ void __launch_bounds__(FP4 ? DEC_THREADS_FP4 : DEC_THREADS, FP4 ? 3 : 2)
 attn_decode_kernel(const __grid_constant__ AttnParams p) {
   extern __shared__ uint8_t smem_raw[];
@@ -441,7 +442,30 @@ attn_decode_kernel(const __grid_constant__ AttnParams p) {
         first_lo = int(qpos_lo) + 1 - int(p.window) - kabs;
         first_hi = int(qpos_hi) + 1 - int(p.window) - kabs;
       }
-      if (rows <= 8) softmax_step<2, false>(s, o, m, l, p.scale_log2, vis_lo, vis_hi, lane, first_lo, first_hi);
+      if (EXT) {
+        // positions instead of rows: each score is masked and biased on its own, then the step runs unmasked
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const uint32_t r = g + 8u * (e >> 1);
+            const uint32_t qi = r < rows ? r / group : 0u, hg = r < rows ? r % group : 0u;
+            const uint32_t krow = uint32_t(kabs) + j * 8 + (lane & 3) * 2 + (e & 1);
+            uint32_t pos = krow;
+            for (uint32_t gi = 0; gi < p.ngaps; ++gi)
+              if (__ldg(p.gap_rows + gi) <= krow) pos = krow + __ldg(p.gap_cums + gi);
+            const uint32_t qpos = p.q0 + qi;
+            bool vis = krow < k_end && pos <= qpos;
+            if (vis && p.window && qpos - pos >= p.window) vis = false;
+            float val = s[j][e] * p.scale_log2;
+            if (vis && p.rel && qpos - pos < p.eff)
+              val += __ldg(p.rel + ((size_t(b) * p.nq + qi) * p.heads + kvh * group + hg) * p.eff + (qpos - pos)) *
+                     1.4426950408889634f;
+            s[j][e] = vis ? val : -INFINITY;
+          }
+        }
+        softmax_step<2, true>(s, o, m, l, 1.0f, 16, 16, lane, 0, 0);
+      } else if (rows <= 8) softmax_step<2, false>(s, o, m, l, p.scale_log2, vis_lo, vis_hi, lane, first_lo, first_hi);
       else softmax_step<2, true>(s, o, m, l, p.scale_log2, vis_lo, vis_hi, lane, first_lo, first_hi);
       if (FP4) {
         fp4_pv(o, s, raw, lane);
@@ -710,14 +734,23 @@ MB_API size_t mb_attention_workspace(size_t batch, size_t nq, size_t keys, size_
   return batch * kv_heads * size_t(decode_splits(batch, kv_heads, keys)) * 16 * (D + 2) * sizeof(float);
 }
 
+struct AttnExt {
+  const float* rel = nullptr;
+  size_t eff = 0;
+  const uint32_t* gap_rows = nullptr;
+  const uint32_t* gap_cums = nullptr;
+  size_t ngaps = 0;
+};
+
 static int attention_common(mb_ctx* ctx, mb_stream stream_, const void* q, const void* k, const void* v, size_t batch,
                             size_t nq, size_t keys, size_t heads, size_t kv_heads, size_t d, size_t q0, float scale,
                             int causal, size_t window, void* out, void* workspace, size_t workspace_bytes,
-                            const uint8_t* const* fp4 = nullptr) {
+                            const uint8_t* const* fp4 = nullptr, const AttnExt* ext = nullptr) {
   cudaStream_t stream = static_cast<cudaStream_t>(stream_);
   MB_REQUIRE(ctx, window == 0 || causal, "attention: a sliding window is a causal window");
   MB_REQUIRE(ctx, window < (1ull << 31), "attention: bad window");
-  MB_REQUIRE(ctx, window == 0 || keys >= q0 + nq, "attention: with a window every query needs its own key in the cache");
+  MB_REQUIRE(ctx, window == 0 || (ext && ext->ngaps) || keys >= q0 + nq,
+             "attention: with a window every query needs its own key in the cache");
   MB_REQUIRE(ctx, ctx && q && out && (fp4 ? fp4[0] && fp4[1] && fp4[2] && fp4[3] : k && v), "attention: null argument");
   MB_REQUIRE(ctx, d == D, "attention: head_dim must be 128, got %zu", d);
   MB_REQUIRE(ctx, batch > 0 && nq > 0 && keys > 0 && heads > 0 && kv_heads > 0 && heads % kv_heads == 0,
@@ -753,6 +786,17 @@ static int attention_common(mb_ctx* ctx, mb_stream stream_, const void* q, const
   p.window = uint32_t(window);
   // the first key the call's first query can see, on a tile boundary
   p.k_lo = (window && q0 + 1 > window) ? uint32_t((q0 + 1 - window) / BC * BC) : 0u;
+  if (ext && (ext->rel || ext->ngaps)) {
+    MB_REQUIRE(ctx, causal, "attention: relative bias and eviction gaps belong to causal attention");
+    MB_REQUIRE(ctx, nq * (heads / kv_heads) <= 16,
+               "attention: relative bias and eviction gaps are read by the decode kernel only (nq * heads / kv_heads <= 16)");
+    MB_REQUIRE(ctx, !ext->rel || ext->eff > 0, "attention: a relative bias table needs eff > 0");
+    MB_REQUIRE(ctx, ext->ngaps <= 64 && (ext->ngaps == 0 || (ext->gap_rows && ext->gap_cums)), "attention: bad gap list");
+    MB_REQUIRE(ctx, ext->eff < (1ull << 31), "attention: bad eff");
+    p.rel = ext->rel; p.eff = uint32_t(ext->rel ? ext->eff : 0);
+    p.gap_rows = ext->gap_rows; p.gap_cums = ext->gap_cums; p.ngaps = uint32_t(ext->ngaps);
+    if (p.ngaps) p.k_lo = 0;     // a row's position is at least its index: rows below the window's index can still be inside it
+  }
   const size_t group = heads / kv_heads;
   static bool attr_dec[16] = {}, attr_pre[16] = {};
   if (nq * group <= 16) {
@@ -767,15 +811,22 @@ static int attention_common(mb_ctx* ctx, mb_stream stream_, const void* q, const
     p.keys_per_split = uint32_t(((span + splits - 1) / splits + BC - 1) / BC * BC);
     p.part = static_cast<float*>(workspace);
     if (!attr_dec[ctx->device & 15]) {
-      MB_CUDA_OK(ctx, cudaFuncSetAttribute(attn_decode_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, DEC_SMEM));
-      MB_CUDA_OK(ctx, cudaFuncSetAttribute(attn_decode_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, DEC_SMEM_FP4));
+      MB_CUDA_OK(ctx, cudaFuncSetAttribute(attn_decode_kernel<false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, DEC_SMEM));
+      MB_CUDA_OK(ctx, cudaFuncSetAttribute(attn_decode_kernel<false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, DEC_SMEM));
+      MB_CUDA_OK(ctx, cudaFuncSetAttribute(attn_decode_kernel<true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, DEC_SMEM_FP4));
+      MB_CUDA_OK(ctx, cudaFuncSetAttribute(attn_decode_kernel<true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, DEC_SMEM_FP4));
       attr_dec[ctx->device & 15] = true;
     }
     dim3 grid(splits, unsigned(kv_heads), unsigned(batch));
-    if (fp4)
-      MB_CUDA_OK(ctx, mb_launch_pdl(attn_decode_kernel<true>, grid, dim3(DEC_THREADS_FP4), DEC_SMEM_FP4, stream, p));
+    const bool has_ext = p.rel || p.ngaps;
+    if (fp4 && has_ext)
+      MB_CUDA_OK(ctx, mb_launch_pdl(attn_decode_kernel<true, true>, grid, dim3(DEC_THREADS_FP4), DEC_SMEM_FP4, stream, p));
+    else if (fp4)
+      MB_CUDA_OK(ctx, mb_launch_pdl(attn_decode_kernel<true, false>, grid, dim3(DEC_THREADS_FP4), DEC_SMEM_FP4, stream, p));
+    else if (has_ext)
+      MB_CUDA_OK(ctx, mb_launch_pdl(attn_decode_kernel<false, true>, grid, dim3(DEC_THREADS), DEC_SMEM, stream, p));
     else
-      MB_CUDA_OK(ctx, mb_launch_pdl(attn_decode_kernel<false>, grid, dim3(DEC_THREADS), DEC_SMEM, stream, p));
+      MB_CUDA_OK(ctx, mb_launch_pdl(attn_decode_kernel<false, false>, grid, dim3(DEC_THREADS), DEC_SMEM, stream, p));
     MB_LAUNCH_OK(ctx);
     if (splits > 1) {
       MB_CUDA_OK(ctx, mb_launch_pdl(attn_combine_kernel, dim3(unsigned(batch * nq * heads)), dim3(128), 0, stream, p.part, p.out,
@@ -824,6 +875,17 @@ MB_API int mb_attention_fp4kv(mb_ctx* ctx, mb_stream stream, const void* q, cons
   const uint8_t* planes[4] = {k_codes, k_scales, v_codes, v_scales};
   return attention_common(ctx, stream, q, nullptr, nullptr, batch, nq, keys, heads, kv_heads, d, q0, scale, causal,
                           window, out, workspace, workspace_bytes, planes);
+}
+
+MB_API int mb_attention_decode_ext(mb_ctx* ctx, mb_stream stream, const void* q, const void* k, const void* v,
+                                   size_t batch, size_t nq, size_t keys, size_t heads, size_t kv_heads, size_t d,
+                                   size_t q0, float scale, size_t window, const float* rel, size_t eff,
+                                   const uint32_t* gap_rows, const uint32_t* gap_cums, size_t ngaps, void* out,
+                                   void* workspace, size_t workspace_bytes) {
+  AttnExt ext;
+  ext.rel = rel; ext.eff = eff; ext.gap_rows = gap_rows; ext.gap_cums = gap_cums; ext.ngaps = ngaps;
+  return attention_common(ctx, stream, q, k, v, batch, nq, keys, heads, kv_heads, d, q0, scale, 1, window, out,
+                          workspace, workspace_bytes, nullptr, &ext);
 }
 
 // ---------------------------------------------------------------------------------

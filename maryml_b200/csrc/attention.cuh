@@ -24,6 +24,13 @@ struct AttnParams {
   const uint8_t* k_scales;
   const uint8_t* v_codes;
   const uint8_t* v_scales;
+  // decode only: relative bias rel[batch, nq, heads, eff] added to the scaled score of a visible key at
+  // distance q_abs - k_abs < eff, and eviction gaps: the key in cache row r sits at position
+  // r + gap_cums[g] for the last g with gap_rows[g] <= r (rows ascending; no gap before it: r)
+  const float* rel;
+  const uint32_t* gap_rows;
+  const uint32_t* gap_cums;
+  uint32_t eff, ngaps;
 };
 
 __device__ __forceinline__ void tma_load_4d(uint32_t dst, const void* tmap, int c0, int c1, int c2, int c3,

@@ -697,13 +697,15 @@ ORC_API int orc_moe_experts(const uint16_t* x, size_t tokens, size_t h, size_t i
 
 // ---------------------------------------------------------------------------
 // Attention (src/models/inkling/flash.rs:1937-1987 `cpu_attention`, generalised to
-// a `scale` argument and no relative bias; GQA kv_h = h / groups)
+// a `scale` argument; GQA kv_h = h / groups)
 // ---------------------------------------------------------------------------
 // q [nq, heads*D], k/v [keys, kv_heads*D] token-major f32. Query i sits at
 // absolute position q0+i; key j at key_pos[j] (null -> j). window <= 0: none.
-ORC_API int orc_attention(const float* q, const float* k, const float* v, size_t nq, size_t keys, size_t heads,
-                          size_t kv_heads, size_t D, size_t q0, const int64_t* key_pos, float scale,
-                          long long window, double* out) {
+// rel (null -> none): [nq, heads, eff] f32, added to the scaled score of a visible key at
+// distance dist = q_abs - k_abs < eff (flash.rs:1966-1972).
+ORC_API int orc_attention_rel(const float* q, const float* k, const float* v, size_t nq, size_t keys, size_t heads,
+                              size_t kv_heads, size_t D, size_t q0, const int64_t* key_pos, float scale,
+                              long long window, const float* rel, size_t eff, double* out) {
   size_t q_row = heads * D, kv_row = kv_heads * D;
   int bad = 0;
 #pragma omp parallel for schedule(dynamic, 4)
@@ -720,7 +722,9 @@ ORC_API int orc_attention(const float* q, const float* k, const float* v, size_t
         size_t koff = ki * kv_row + kvh * D;
         double dot = 0.0;
         for (size_t d = 0; d < D; ++d) dot += double(q[qoff + d]) * double(k[koff + d]);
-        scores.push_back({koff, dot * double(scale)});
+        const size_t dist = q_abs - k_abs;
+        const double bias = (rel && dist < eff) ? double(rel[(size_t(qi) * heads + h) * eff + dist]) : 0.0;
+        scores.push_back({koff, dot * double(scale) + bias});
       }
       for (size_t d = 0; d < D; ++d) out[qoff + d] = 0.0;
       if (scores.empty()) { bad = 1; continue; }
@@ -735,6 +739,12 @@ ORC_API int orc_attention(const float* q, const float* k, const float* v, size_t
     }
   }
   return bad ? -1 : 0;
+}
+
+ORC_API int orc_attention(const float* q, const float* k, const float* v, size_t nq, size_t keys, size_t heads,
+                          size_t kv_heads, size_t D, size_t q0, const int64_t* key_pos, float scale,
+                          long long window, double* out) {
+  return orc_attention_rel(q, k, v, nq, keys, heads, kv_heads, D, q0, key_pos, scale, window, nullptr, 0, out);
 }
 
 // ---------------------------------------------------------------------------

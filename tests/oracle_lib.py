@@ -69,6 +69,8 @@ class Oracle:
                                           P(u8), P(f32), C.c_int, P(f32)]),
             "orc_attention": (C.c_int, [P(f32), P(f32), P(f32), sz, sz, sz, sz, sz, sz, P(i64), f32, C.c_longlong,
                                         P(f64)]),
+            "orc_attention_rel": (C.c_int, [P(f32), P(f32), P(f32), sz, sz, sz, sz, sz, sz, P(i64), f32, C.c_longlong,
+                                            P(f32), sz, P(f64)]),
             "orc_rmsnorm_breeze": (None, [P(u16), P(u16), sz, sz, f32, P(u16)]),
             "orc_add_bf16": (None, [P(u16), P(u16), sz, P(u16)]),
             "orc_swiglu_bf16": (None, [P(u16), P(u16), sz, P(u16)]),
@@ -333,7 +335,7 @@ class Oracle:
         return out
 
     # ---- attention / layer glue --------------------------------------------
-    def attention(self, q, k, v, heads, kv_heads, D, q0, scale, key_pos=None, window=0):
+    def attention(self, q, k, v, heads, kv_heads, D, q0, scale, key_pos=None, window=0, rel=None):
         q = np.ascontiguousarray(q, np.float32)
         k = np.ascontiguousarray(k, np.float32)
         v = np.ascontiguousarray(v, np.float32)
@@ -344,8 +346,14 @@ class Oracle:
         if key_pos is not None:
             key_pos = np.ascontiguousarray(key_pos, np.int64)
             kp = _ptr(key_pos, C.c_int64)
-        rc = self.lib.orc_attention(_ptr(q, C.c_float), _ptr(k, C.c_float), _ptr(v, C.c_float), nq, keys, heads,
-                                    kv_heads, D, q0, kp, float(np.float32(scale)), int(window), _ptr(out, C.c_double))
+        rp, eff = None, 0
+        if rel is not None:
+            rel = np.ascontiguousarray(rel, np.float32)
+            eff = rel.size // (nq * heads)
+            rp = _ptr(rel, C.c_float)
+        rc = self.lib.orc_attention_rel(_ptr(q, C.c_float), _ptr(k, C.c_float), _ptr(v, C.c_float), nq, keys, heads,
+                                        kv_heads, D, q0, kp, float(np.float32(scale)), int(window), rp, eff,
+                                        _ptr(out, C.c_double))
         if rc != 0:
             raise ValueError("a query has no visible key")
         return out.reshape(nq, heads * D)

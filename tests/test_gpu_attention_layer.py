@@ -119,6 +119,44 @@ def test_decode_attention_over_nvfp4_rows(mods, orc, batch, nq, keys, heads, kvh
         assert rel_check(gotf[b], ref)[1] >= 0.9999
 
 
+@pytest.mark.parametrize("batch,nq,keys,heads,kvh,window,gaps,eff", [
+    (1, 1, 897, 8, 2, 0, [], 16),                       # the bias alone
+    (1, 1, 897, 8, 2, 19, [], 0),                       # window through the position path is not taken: plain call
+    (1, 1, 897, 8, 2, 0, [(17, 5), (853, 19)], 0),      # gaps alone (the reference's gapped case: flash.rs:2040-2044)
+    (2, 2, 700, 8, 2, 100, [(3, 2), (650, 40)], 33),    # everything, two queries, two sequences
+    (1, 4, 300, 4, 1, 0, [(0, 7)], 300),                # a gap before the first row; bias over every distance
+])
+def test_decode_attention_with_relative_bias_and_gaps(mods, orc, batch, nq, keys, heads, kvh, window, gaps, eff):
+    att, _ = mods
+    D = 128
+    q, k, v = _qkv(orc, 19 * keys + nq + eff, batch, nq, keys, heads, kvh)
+    pos = np.arange(keys, dtype=np.int64)
+    for row, cum in gaps:
+        pos[row:] = np.arange(row, keys) + cum
+    q0 = int(pos[-1]) - (nq - 1)                          # the last query sits on the last key
+    rel = None
+    if eff:
+        rel = (orc.normal_f32(3 + eff, batch * nq * heads * eff, 1.0)).reshape(batch, nq, heads, eff).astype(np.float32)
+    gd = None
+    if gaps:
+        gd = (torch.tensor([g[0] for g in gaps], dtype=torch.int32, device="cuda"),
+              torch.tensor([g[1] for g in gaps], dtype=torch.int32, device="cuda"))
+    qd = dev_bf16(q).view(batch, nq, heads, D)
+    kd = dev_bf16(k).view(batch, keys, kvh, D)
+    vd = dev_bf16(v).view(batch, keys, kvh, D)
+    out = att.decode_attention_ext(qd, kd, vd, q0, window=window, rel=None if rel is None else torch.from_numpy(rel).cuda(),
+                                   gaps=gd)
+    got = bf16_bits_to_f32(host_bits(out)).reshape(batch, nq, heads * D)
+    for b in range(batch):
+        ref = orc.attention(bf16_bits_to_f32(q[b]), bf16_bits_to_f32(k[b]), bf16_bits_to_f32(v[b]), heads, kvh, D, q0,
+                            1.0 / math.sqrt(D), key_pos=pos if gaps else None, window=window,
+                            rel=None if rel is None else rel[b])
+        assert np.abs(got[b] - ref).max() <= 2e-2 * max(np.abs(ref).max(), 1e-3)
+        assert rel_check(got[b], ref)[1] >= 0.9999
+    if not gaps and not eff:
+        assert torch.equal(out, att.flash_attention(qd, kd, vd, q0=q0, window=window))
+
+
 def test_prompt_shapes_refuse_nvfp4_rows(mods):
     from maryml_b200 import _lib
     att, _ = mods

@@ -162,6 +162,21 @@ def test_packed_kv_reader_index_rule(orc):
     assert np.array_equal(bf16_bits_to_f32(f32_to_bf16_bits(want)), want)
 
 
+def test_attention_relative_bias_enters_by_distance(orc):
+    # src/models/inkling/flash.rs:1966-1972: bias rel[(qi * heads + h) * eff + dist] for dist < eff, after the scale
+    q = np.zeros((2, 1)); k = np.zeros((4, 1)); v = np.array([1.0, 10.0, 100.0, 1000.0])
+    rel = np.array([[np.log(3.0), 0.0], [0.0, np.log(2.0)]], np.float32)     # [nq = 2, heads = 1, eff = 2]
+    out = orc.attention(q, k, v, heads=1, kv_heads=1, D=1, q0=2, scale=1.0, rel=rel)
+    # query 0 at position 2 sees keys 0..2: weights 1, 1, 3 (distance 0 carries log 3)
+    assert np.isclose(out[0, 0], (1 + 10 + 3 * 100) / 5, rtol=1e-6)
+    # query 1 at position 3 sees keys 0..3: distance 1 (key 2) carries log 2
+    assert np.isclose(out[1, 0], (1 + 10 + 2 * 100 + 1000) / 5, rtol=1e-6)
+    # with gaps the distance is in absolute positions: key rows 0..3 sit at 0, 1, 5, 6
+    out = orc.attention(q, k, v, heads=1, kv_heads=1, D=1, q0=5, scale=1.0, key_pos=[0, 1, 5, 6], rel=rel)
+    assert np.isclose(out[0, 0], (1 + 10 + 3 * 100) / 5, rtol=1e-6)           # position 5: key row 2 at distance 0
+    assert np.isclose(out[1, 0], (1 + 10 + 2 * 100 + 1000) / 5, rtol=1e-6)    # position 6: key row 2 at distance 1
+
+
 def test_attention_gqa_and_causality(orc):
     rng = np.random.default_rng(1)
     heads, kvh, D, nq, keys = 4, 2, 8, 3, 6
