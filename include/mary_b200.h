@@ -126,6 +126,17 @@ int mb_nvfp4_gather_rows(mb_ctx* ctx, mb_stream stream, const uint8_t* codes, co
                          size_t src_rows, size_t k, const int32_t* gather, size_t rows, uint8_t* out_codes,
                          uint8_t* out_sf_tiled);
 
+/* transcode_to_nvfp4 (src/nn/mxfp4.rs:319-375): the exact relabelling of an MXFP4 tensor (E2M1
+ * codes, one E8M0 scale per 32 values) as NVFP4. The codes are used as they are; this call only
+ * re-expresses the scales: e8m0 [n] device bytes -> block_scales [2 n] E4M3 bytes, row-major (tile
+ * them with mb_nvfp4_tile_scales for the GEMM), and the global scale 2^g with g = e_max - 8, a
+ * power of two, returned on the host. Every decoded weight E2M1[code] * e4m3(scale) * 2^g equals
+ * E2M1[code] * 2^(b - 127) bit for bit. MB_ERR_NONFINITE for a 0xFF scale (the first index is in
+ * the message), MB_ERR_INVALID when the exponents span more than E4M3's 18 octaves or 2^g is not a
+ * normal f32. Synchronises `stream` once. */
+int mb_mxfp4_to_nvfp4_scales(mb_ctx* ctx, mb_stream stream, const uint8_t* e8m0, size_t n, uint8_t* block_scales,
+                             float* global_scale_host_out, int* global_exp_host_out);
+
 /* dequantize_nvfp4(_bf16) (src/models/inkling/fp4quant.rs:437-459) and
  * nvfp4::decode_payload (src/nvfp4.rs:170-182): out = E2M1[code]*(e4m3(scale)*scale2). */
 int mb_nvfp4_dequantize(mb_ctx* ctx, mb_stream stream, const uint8_t* codes, const uint8_t* scales_rowmajor,

@@ -34,6 +34,7 @@ SIGNATURES = {
     "mb_check_flags": (_i, [_vp, _vp, C.POINTER(C.c_int32)]),
     "mb_nvfp4_quantize_weight": (_i, [_vp, _vp, _vp, _sz, _sz, _vp, _vp, C.POINTER(_f)]),
     "mb_nvfp4_quantize_act": (_i, [_vp, _vp, _vp, _i, _sz, _sz, _i, _f, _vp, _sz, _vp, _vp, _i, _vp]),
+    "mb_mxfp4_to_nvfp4_scales": (_i, [_vp, _vp, _vp, _sz, _vp, C.POINTER(C.c_float), C.POINTER(C.c_int)]),
     "mb_nvfp4_gather_rows": (_i, [_vp, _vp, _vp, _vp, _sz, _sz, _vp, _sz, _vp, _vp]),
     "mb_nvfp4_dequantize": (_i, [_vp, _vp, _vp, _vp, _f, _sz, _sz, _vp, _i]),
     "mb_nvfp4_sf_bytes": (_sz, [_sz, _sz]),

@@ -419,6 +419,70 @@ MB_API int mb_nvfp4_quantize_weight(mb_ctx* ctx, mb_stream stream_, const void* 
                                scales, MB_SF_ROWMAJOR, nullptr);
 }
 
+// MXFP4 -> NVFP4 scale relabelling: an E8M0 byte is the power of two 2^(b - 127); E4M3 holds
+// 2^-9 .. 2^8 exactly; with the global exponent g = e_max - 8 each block scale is 2^(e - g),
+// written for both 16-blocks of the 32-block. Pass 1 finds the byte range and the first NaN.
+namespace {
+
+__global__ void __launch_bounds__(256)
+e8m0_range_kernel(const uint8_t* __restrict__ scale, size_t n, uint32_t* __restrict__ out3) {
+  uint32_t hi = 0, lo_inv = 0, nan_inv = 0;
+  const size_t stride = size_t(gridDim.x) * blockDim.x;
+  for (size_t i = size_t(blockIdx.x) * blockDim.x + threadIdx.x; i < n; i += stride) {
+    const uint32_t b = scale[i];
+    if (b == 0xFFu) nan_inv = max(nan_inv, 0xFFFFFFFFu - uint32_t(i));   // the largest of these is the first index
+    else { hi = max(hi, b + 1u); lo_inv = max(lo_inv, 256u - b); }
+  }
+  hi = __reduce_max_sync(0xFFFFFFFFu, hi);
+  lo_inv = __reduce_max_sync(0xFFFFFFFFu, lo_inv);
+  nan_inv = __reduce_max_sync(0xFFFFFFFFu, nan_inv);
+  if ((threadIdx.x & 31) == 0) {
+    atomicMax(out3, hi);
+    atomicMax(out3 + 1, lo_inv);
+    if (nan_inv) atomicMax(out3 + 2, nan_inv);
+  }
+}
+
+__global__ void __launch_bounds__(256)
+e8m0_relabel_kernel(const uint8_t* __restrict__ scale, size_t n, int g, uint16_t* __restrict__ out) {
+  const size_t i = size_t(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  const int e = int(scale[i]) - 127 - g;                        // -9 .. 8 by the range check
+  const uint32_t b = e >= -6 ? uint32_t(e + 7) << 3 : (1u << (e + 9));   // subnormals 2^-9, 2^-8, 2^-7 = mantissa 1, 2, 4
+  out[i] = uint16_t(b | (b << 8));
+}
+
+}  // namespace
+
+MB_API int mb_mxfp4_to_nvfp4_scales(mb_ctx* ctx, mb_stream stream_, const uint8_t* e8m0, size_t n,
+                                    uint8_t* block_scales, float* global_scale_host_out, int* global_exp_host_out) {
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  MB_REQUIRE(ctx, ctx && e8m0 && block_scales && global_scale_host_out, "mxfp4 transcode: null argument");
+  MB_REQUIRE(ctx, n > 0 && n < 0xFFFFFFFFull, "mxfp4 transcode: empty or oversized scale plane");
+  MB_REQUIRE(ctx, mb_aligned(block_scales, 2), "mxfp4 transcode: the NVFP4 scale plane needs 2-byte alignment");
+  uint32_t* scratch = reinterpret_cast<uint32_t*>(ctx->flags_dev + MB_FLAG_COUNT);   // spare words
+  MB_CUDA_OK(ctx, cudaMemsetAsync(scratch, 0, 12, stream));
+  const unsigned grid = unsigned(std::min<size_t>((n + 255) / 256, size_t(ctx->sm_count) * 8));
+  e8m0_range_kernel<<<grid, 256, 0, stream>>>(e8m0, n, scratch);
+  MB_LAUNCH_OK(ctx);
+  uint32_t host[3];
+  MB_CUDA_OK(ctx, cudaMemcpyAsync(host, scratch, 12, cudaMemcpyDeviceToHost, stream));
+  MB_CUDA_OK(ctx, cudaStreamSynchronize(stream));
+  if (host[2]) return mb_fail(ctx, MB_ERR_NONFINITE, "E8M0 scale[%u] is NaN (0xFF)", 0xFFFFFFFFu - host[2]);
+  const int e_max = int(host[0]) - 1 - 127, e_min = 256 - int(host[1]) - 127;
+  const int g = e_max - 8;
+  if (e_min - g < -9)
+    return mb_fail(ctx, MB_ERR_INVALID, "E8M0 exponents span %d octaves (%d..%d); E4M3 holds 18 exactly",
+                   e_max - e_min + 1, e_min, e_max);
+  if (g < -126 || g > 127) return mb_fail(ctx, MB_ERR_INVALID, "global scale 2^%d is not a normal f32", g);
+  e8m0_relabel_kernel<<<unsigned((n + 255) / 256), 256, 0, stream>>>(e8m0, n, g, reinterpret_cast<uint16_t*>(block_scales));
+  MB_LAUNCH_OK(ctx);
+  const uint32_t bits = uint32_t(g + 127) << 23;
+  memcpy(global_scale_host_out, &bits, 4);
+  if (global_exp_host_out) *global_exp_host_out = g;
+  return MB_OK;
+}
+
 MB_API int mb_nvfp4_dequantize(mb_ctx* ctx, mb_stream stream_, const uint8_t* codes, const uint8_t* scales,
                                float scale2, size_t rows, size_t k, void* out, int out_dtype) {
   cudaStream_t stream = static_cast<cudaStream_t>(stream_);

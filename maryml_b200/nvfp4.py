@@ -70,6 +70,20 @@ def quantize_act(x, recipe=_lib.QUANT_SCALED, input_scale=1.0, tiled=True, gathe
     return codes, scales, rowscale
 
 
+def mxfp4_to_nvfp4(packed, e8m0, rows, cols):
+    """transcode_to_nvfp4 (src/nn/mxfp4.rs:319-375): an MXFP4 tensor ([rows, cols/2] code bytes, [rows, cols/32]
+    E8M0 scales) relabelled as NVFP4 without touching the codes. Returns (codes (the same tensor), row-major
+    E4M3 block scales [rows, cols/16], global scale, global exponent)."""
+    assert packed.dtype == torch.uint8 and e8m0.dtype == torch.uint8 and cols % 32 == 0
+    assert packed.numel() == rows * cols // 2 and e8m0.numel() == rows * cols // 32
+    ctx = context(packed.device.index)
+    out = torch.empty((rows, cols // 16), dtype=torch.uint8, device=packed.device)
+    gs, ge = C.c_float(), C.c_int()
+    ctx.check(lib.mb_mxfp4_to_nvfp4_scales(ctx.handle, _stream(), _p(e8m0.contiguous()), e8m0.numel(), _p(out),
+                                           C.byref(gs), C.byref(ge)))
+    return packed, out, float(gs.value), int(ge.value)
+
+
 def gather_rows(codes, sf_tiled, src_rows, k, gather):
     """Quantized activation planes copied into the row order of `gather` (negative = zero row)."""
     ctx = context(codes.device.index)

@@ -441,6 +441,63 @@ ORC_API void orc_linear_bf16(const uint16_t* x, const uint16_t* w, size_t M, siz
 }
 
 // ---------------------------------------------------------------------------
+// MXFP4 -> NVFP4 relabelling (src/nn/mxfp4.rs:141-400). An E8M0 scale byte b is 2^(b - 127)
+// (0xFF = NaN); E4M3 holds the powers of two 2^-9 .. 2^8 exactly. With g = e_max - 8 as the
+// global exponent every block scale becomes 2^(e - g), written twice (one 32-block = two
+// 16-blocks); the codes are not touched.
+// ---------------------------------------------------------------------------
+static int e4m3_from_pow2(int e) {                    // mxfp4.rs:169-177; -1 outside the window
+  if (e == -9) return 0x01;
+  if (e == -8) return 0x02;
+  if (e == -7) return 0x04;
+  if (e >= -6 && e <= 8) return (e + 7) << 3;
+  return -1;
+}
+ORC_API int orc_e4m3_from_pow2(int e) { return e4m3_from_pow2(e); }
+
+// Returns 0; 1 = NaN scale (info[0] = index); 2 = span too wide (info = e_min, e_max, octaves);
+// 3 = global scale 2^g not a normal f32 (info[0] = g). On success info[0] = g, info[1] = 1 when a
+// block scale is an E4M3 subnormal. block_scale: 2 * n bytes.
+ORC_API int orc_mxfp4_transcode(const uint8_t* scale, size_t n, uint8_t* block_scale, long long* info) {
+  int e_min = INT32_MAX, e_max = INT32_MIN;
+  for (size_t i = 0; i < n; ++i) {
+    if (scale[i] == 0xFF) { info[0] = (long long)i; return 1; }
+    int e = int(scale[i]) - 127;
+    e_min = std::min(e_min, e);
+    e_max = std::max(e_max, e);
+  }
+  const int g = e_max - 8;
+  if (e_min - g < -9) { info[0] = e_min; info[1] = e_max; info[2] = e_max - e_min + 1; return 2; }
+  if (g < -126 || g > 127) { info[0] = g; return 3; }
+  bool sub = false;
+  for (size_t i = 0; i < n; ++i) {
+    int e = int(scale[i]) - 127 - g;
+    sub |= e < -6;
+    uint8_t b = uint8_t(e4m3_from_pow2(e));
+    block_scale[2 * i] = b;
+    block_scale[2 * i + 1] = b;
+  }
+  info[0] = g;
+  info[1] = sub ? 1 : 0;
+  return 0;
+}
+
+// decode_mxfp4 (mxfp4.rs:265-300): value = E2M1[code] * 2^(b - 127), low nibble first, blocks of 32 along a row.
+ORC_API void orc_mxfp4_decode(const uint8_t* packed, const uint8_t* scale, size_t rows, size_t cols, float* out) {
+  static const float E2M1[16] = {0.0f, 0.5f, 1.0f, 1.5f, 2.0f, 3.0f, 4.0f, 6.0f,
+                                 -0.0f, -0.5f, -1.0f, -1.5f, -2.0f, -3.0f, -4.0f, -6.0f};
+  for (size_t i = 0; i < rows * cols; ++i) {
+    uint8_t b = scale[i / 32];
+    float s;
+    if (b == 0xFF) s = std::numeric_limits<float>::quiet_NaN();
+    else if (b == 0) { uint32_t bits = 1u << 22; std::memcpy(&s, &bits, 4); }
+    else { uint32_t bits = uint32_t(b) << 23; std::memcpy(&s, &bits, 4); }
+    uint8_t code = (packed[i / 2] >> ((i & 1) * 4)) & 15;
+    out[i] = E2M1[code] * s;
+  }
+}
+
+// ---------------------------------------------------------------------------
 // Router (src/models/k3/router.rs:343-488, softmax branch; equals
 // src/models/gemma/gemma4/layers.rs:288-325 without per_expert_scale)
 // ---------------------------------------------------------------------------

@@ -55,6 +55,9 @@ class Oracle:
             "orc_linear_cpu_lane": (None, [P(u16), P(f32), sz, sz, sz, P(u16)]),
             "orc_linear_w4a4": (None, [P(u8), P(u8), P(u8), P(u8), P(f32), f32, sz, sz, sz, P(f32)]),
             "orc_linear_bf16": (None, [P(u16), P(u16), sz, sz, sz, P(f32)]),
+            "orc_e4m3_from_pow2": (C.c_int, [C.c_int]),
+            "orc_mxfp4_transcode": (C.c_int, [P(u8), sz, P(u8), P(C.c_longlong)]),
+            "orc_mxfp4_decode": (None, [P(u8), P(u8), sz, sz, P(f32)]),
             "orc_router_scores_softmax": (None, [P(f32), sz, sz, P(f32)]),
             "orc_router_scores_sigmoid": (None, [P(f32), sz, sz, P(f32)]),
             "orc_router_select": (C.c_int, [P(f32), P(f32), sz, sz, sz, C.c_int, f32, P(u32), P(f32)]),
@@ -215,6 +218,29 @@ class Oracle:
         out = np.empty(M * N, np.float32)
         self.lib.orc_linear_bf16(_ptr(x_bits, C.c_uint16), _ptr(w_bits, C.c_uint16), M, N, K, _ptr(out, C.c_float))
         return out.reshape(M, N)
+
+    # ---- MXFP4 relabelling ------------------------------------------------
+    def mxfp4_transcode(self, scale):
+        """transcode_to_nvfp4's scale half (src/nn/mxfp4.rs:319-375) -> (block scales [2n], global exponent g,
+        any subnormal block scale); raises ValueError with the reference's error kinds."""
+        scale = np.ascontiguousarray(scale, np.uint8).reshape(-1)
+        out = np.empty(2 * scale.size, np.uint8)
+        info = (C.c_longlong * 3)()
+        rc = self.lib.orc_mxfp4_transcode(_ptr(scale, C.c_uint8), scale.size, _ptr(out, C.c_uint8), info)
+        if rc == 1:
+            raise ValueError(f"ScaleNan index {info[0]}")
+        if rc == 2:
+            raise ValueError(f"ExponentSpan e_min {info[0]} e_max {info[1]} octaves {info[2]}")
+        if rc == 3:
+            raise ValueError(f"GlobalScaleRange g {info[0]}")
+        return out, int(info[0]), bool(info[1])
+
+    def mxfp4_decode(self, packed, scale, rows, cols):
+        packed = np.ascontiguousarray(packed, np.uint8).reshape(-1)
+        scale = np.ascontiguousarray(scale, np.uint8).reshape(-1)
+        out = np.empty(rows * cols, np.float32)
+        self.lib.orc_mxfp4_decode(_ptr(packed, C.c_uint8), _ptr(scale, C.c_uint8), rows, cols, _ptr(out, C.c_float))
+        return out
 
     # ---- router / MoE -----------------------------------------------------
     def router_scores_softmax(self, logits):

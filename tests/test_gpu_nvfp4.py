@@ -387,3 +387,34 @@ def test_full_size_linearity_property(mb, orc):
     y3 = mb.bf16_gemm(xa, wb, out_dtype=torch.float32, alpha=q.scale2)
     err = (y1 - y3).abs().max().item()
     assert err <= 1e-4 * y3.abs().max().item() + 1e-6
+
+
+def test_mxfp4_relabelled_as_nvfp4_decodes_to_the_same_bits(mb, orc):
+    """transcode_to_nvfp4 (src/nn/mxfp4.rs:319-375) on the device: scale bytes equal the CPU relabelling, and the
+    NVFP4 decode of (same codes, new scales, 2^g) equals the MXFP4 decode bit for bit."""
+    nv = mb
+    from maryml_b200 import _lib
+    rows, cols = 96, 256
+    rng = np.random.default_rng(4)
+    packed = rng.integers(0, 256, rows * cols // 2, dtype=np.uint8)
+    exps = rng.integers(-15, -4, rows * cols // 32)              # an 11-octave span like the reference's checkpoint
+    exps[:18] = np.arange(-20, -2)                                # and the full 18-octave window somewhere
+    scale = (exps + 127).astype(np.uint8)
+    pd, sd = torch.from_numpy(packed).cuda(), torch.from_numpy(scale).cuda()
+    codes, bs, gscale, gexp = nv.mxfp4_to_nvfp4(pd, sd, rows, cols)
+    bs_ref, g_ref, _ = orc.mxfp4_transcode(scale)
+    assert codes.data_ptr() == pd.data_ptr()                      # the codes are borrowed, not rebuilt
+    assert gexp == g_ref == int(exps.max()) - 8 and gscale == 2.0 ** g_ref
+    assert np.array_equal(bs.cpu().numpy().ravel(), bs_ref)
+    back = nv.dequantize(codes.view(rows, cols // 2), bs, gscale, rows, cols).cpu().numpy().ravel()
+    want = orc.mxfp4_decode(packed, scale, rows, cols)
+    assert np.array_equal(back.view(np.uint32), want.view(np.uint32))
+    # refusals: a 19-octave span, a NaN scale (the first index is named)
+    wide = scale.copy()
+    wide[5] = np.uint8(127 - 21)                                   # exponents now run -21 .. -3
+    with pytest.raises(_lib.MaryError, match="span 19 octaves"):
+        nv.mxfp4_to_nvfp4(pd, torch.from_numpy(wide).cuda(), rows, cols)
+    bad = scale.copy()
+    bad[[7, 300]] = 0xFF
+    with pytest.raises(_lib.MaryError, match=r"scale\[7\] is NaN"):
+        nv.mxfp4_to_nvfp4(pd, torch.from_numpy(bad).cuda(), rows, cols)
