@@ -24,6 +24,24 @@ def test_library_loads_and_exports_every_declared_symbol():
     assert b"sm_100a" in _lib.lib.mb_version()
 
 
+def test_binding_argument_counts_match_the_header():
+    """A ctypes table that disagrees with a prototype in the number of arguments is a stack of wrong
+    values at run time; the header is the contract, so count its parameters."""
+    from maryml_b200 import _lib
+    text = open(os.path.join(ROOT, "include", "mary_b200.h")).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    protos = dict(re.findall(r"\b(mb_[a-z0-9_]+)\s*\(([^;{]*?)\)\s*;", text, flags=re.S))
+    assert set(protos) == set(_lib.SIGNATURES)
+    wrong = {}
+    for name, params in protos.items():
+        params = " ".join(params.split())
+        n = 0 if params in ("", "void") else params.count(",") + 1
+        have = len(_lib.SIGNATURES[name][1])
+        if n != have:
+            wrong[name] = (n, have)
+    assert not wrong, wrong
+
+
 def test_host_only_entry_points():
     from maryml_b200 import _lib
     lo, hi = ctypes.c_size_t(), ctypes.c_size_t()
