@@ -39,6 +39,32 @@ def test_binding_argument_counts_match_the_header():
         have = len(_lib.SIGNATURES[name][1])
         if n != have:
             wrong[name] = (n, have)
+            continue
+        # and the kind of each: pointer, size_t, int or float
+        for i, (decl, ct) in enumerate(zip(params.split(","), _lib.SIGNATURES[name][1])):
+            decl = decl.strip()
+            if "*" in decl or "[" in decl or decl.startswith("mb_stream"):    # an array parameter is a pointer
+                kind = "p"
+            elif decl.startswith("size_t"):
+                kind = "z"
+            elif decl.startswith("float"):
+                kind = "f"
+            elif decl.startswith("int") or decl.startswith("uint32_t") or decl.startswith("int32_t"):
+                kind = "i"
+            else:
+                kind = "?"
+            if ct is ctypes.c_void_p or ct is ctypes.c_char_p or hasattr(ct, "contents"):
+                got = "p"
+            elif ct is ctypes.c_size_t:
+                got = "z"
+            elif ct is ctypes.c_float:
+                got = "f"
+            elif ct in (ctypes.c_int, ctypes.c_int32, ctypes.c_uint32):
+                got = "i"
+            else:
+                got = "??"
+            if kind != got:
+                wrong[f"{name}[{i}]"] = (decl, str(ct))
     assert not wrong, wrong
 
 
