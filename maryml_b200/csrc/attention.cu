@@ -920,8 +920,11 @@ MB_API int mb_attention_decode_static(mb_ctx* ctx, mb_stream stream_, const void
   MB_REQUIRE(ctx, mb_aligned(q, 16) && mb_aligned(k, 16) && mb_aligned(v, 16) && mb_aligned(out, 16),
              "attention_decode_static: 16-byte alignment");
   MB_REQUIRE(ctx, batch <= 65535 && keys < (1ull << 31) && q0 < (1ull << 31), "attention_decode_static: extent overflow");
-  const uint32_t splits = decode_splits(batch, kv_heads, keys);
-  const size_t need = batch * kv_heads * size_t(splits) * 16 * (D + 2) * sizeof(float);
+  // fewer key splits than the heuristic's when its choice would not fit the built-in array
+  uint32_t splits = decode_splits(batch, kv_heads, keys);
+  const size_t per_split = batch * kv_heads * size_t(16) * (D + 2) * sizeof(float);
+  while (splits > 1 && per_split * splits > STATIC_SCRATCH_BYTES) --splits;
+  const size_t need = per_split * splits;
   MB_REQUIRE(ctx, need <= STATIC_SCRATCH_BYTES,
              "attention_decode_static: this shape needs %zu bytes of split scratch, the built-in array holds %zu; "
              "use mb_attention with a caller workspace",

@@ -41,6 +41,19 @@ def test_static_scratch_decode_matches_workspace_decode_twice():
             # the same kernels on the same inputs: the tolerance the other attention tests use
             assert (out.float() - want.float()).abs().max().item() <= 2e-2 * want.float().abs().max().item()
             assert torch.equal(out, want)
+    # a shape whose preferred split count would not fit the array runs with fewer splits instead of being refused
+    batch, keys, heads, kvh = 32, 4096, 32, 8
+    q = torch.randn(batch, 1, heads, 128, device="cuda", generator=g).to(torch.bfloat16)
+    k = torch.randn(batch, keys, kvh, 128, device="cuda", generator=g).to(torch.bfloat16)
+    v = torch.randn(batch, keys, kvh, 128, device="cuda", generator=g).to(torch.bfloat16)
+    assert lib.mb_attention_workspace(batch, 1, keys, heads, kvh, 128) > (16 << 20)
+    want = flash_attention(q, k, v, q0=keys - 1)
+    out = torch.full_like(q, float("nan"))
+    rc = lib.mb_attention_decode_static(ctx.handle, stream, _p(q), _p(k), _p(v), batch, 1, keys, heads, kvh, 128,
+                                        keys - 1, 1.0 / math.sqrt(128), 1, _p(out))
+    assert rc == 0, lib.mb_last_error(ctx.handle)
+    torch.cuda.synchronize()
+    assert (out.float() - want.float()).abs().max().item() <= 2e-2 * want.float().abs().max().item()
     # a shape beyond the built-in scratch is refused before any launch, with a message
     big = 64
     q = torch.zeros(big, 1, 64, 128, device="cuda", dtype=torch.bfloat16)
