@@ -333,7 +333,8 @@ int mb_attention_fp4kv(mb_ctx* ctx, mb_stream stream, const void* q, const uint8
  * and can fail under a full arena): the key-split scratch lives in a 16 MiB array
  * built into the library, so the caller passes only q, k, v and out. Same arithmetic
  * and argument meaning as mb_attention for decode shapes (nq * heads/kv_heads <= 16);
- * shapes whose split scratch exceeds 16 MiB are refused with MB_ERR_INVALID. The first
+ * it splits the keys less than mb_attention would when that is what fits the array, and
+ * shapes whose scratch exceeds 16 MiB even unsplit are refused with MB_ERR_INVALID. The first
  * call on a device looks up the array's device address (the context's device must be
  * current); make that call before any stream capture begins. All calls share the one
  * array: the partials are fully rewritten by every call, nothing needs clearing, but two
