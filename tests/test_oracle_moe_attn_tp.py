@@ -162,6 +162,30 @@ def test_packed_kv_reader_index_rule(orc):
     assert np.array_equal(bf16_bits_to_f32(f32_to_bf16_bits(want)), want)
 
 
+def test_fp4_cache_rows_geometry_blocks_and_round_trip_bound(orc):
+    # src/models/inkling/kvpages.rs:2996-3010: [rows, width/8] code words, [rows, width/64] scale words, 4.5 bits a value
+    FW = 128
+    x = orc.normal_f32(7, 3 * FW, 1.0)
+    codes, scales = orc.quantize_act_recip(x, 3, FW)
+    assert codes.size == 3 * (FW // 8) * 4 and scales.size == 3 * (FW // 64) * 4
+    assert (FW // 8 + FW // 64) * 4 * 32 == FW * 2 * 9
+    # kvpages.rs:3014-3030: alternating 16-blocks of 0.5 and 200 survive, so the blocks run along the features
+    vals = np.array([0.5 if (j // 16) % 2 == 0 else 200.0 for j in range(FW)], np.float32)
+    c, s = orc.quantize_act_recip(vals, 1, FW)
+    got = orc.dequantize(c, s, 1.0)
+    assert np.all(np.abs(got - vals) <= vals / 16.0)
+    # kvpages.rs:3032-3100: a 1024-wide bf16 row loses less than 1/3 + 1/16 of its block amax
+    KW, n = 1024, 40
+    i = np.arange(n * KW, dtype=np.uint64)
+    t = ((i * np.uint64(2654435761)) % np.uint64(2003)).astype(np.float32) / np.float32(1001.5) - np.float32(1.0)
+    a = bf16_bits_to_f32(f32_to_bf16_bits((t * t * t * np.float32(8.0)).astype(np.float32)))
+    c, s = orc.quantize_act_recip(a, n, KW)
+    b = orc.dequantize(c, s, 1.0)
+    amax = np.maximum(np.abs(a).reshape(-1, 16).max(1), 1e-6)
+    worst = (np.abs(a - b).reshape(-1, 16) / amax[:, None]).max()
+    assert worst < 1.0 / 3.0 + 1.0 / 16.0, worst
+
+
 def test_attention_relative_bias_enters_by_distance(orc):
     # src/models/inkling/flash.rs:1966-1972: bias rel[(qi * heads + h) * eff + dist] for dist < eff, after the scale
     q = np.zeros((2, 1)); k = np.zeros((4, 1)); v = np.array([1.0, 10.0, 100.0, 1000.0])
