@@ -186,6 +186,42 @@ def test_fp4_cache_rows_geometry_blocks_and_round_trip_bound(orc):
     assert worst < 1.0 / 3.0 + 1.0 / 16.0, worst
 
 
+def _band_inputs(tokens, heads, kvh, D, window):
+    fill = lambda n, ph: (np.sin(np.arange(n) * 0.37 + ph) * 0.5).astype(np.float32)
+    eff = min(window, tokens)
+    return (fill(tokens * heads * D, 0.1), fill(tokens * kvh * D, 0.3), fill(tokens * kvh * D, 0.5),
+            fill(tokens * heads * eff, 0.7).reshape(tokens, heads, eff))
+
+
+def test_window_reach_and_group_isolation(orc):
+    # src/models/inkling/banded.rs:412-460: a key `window` back from the last query is outside its window (the
+    # answer does not move at all), the query's own key is inside (it moves)
+    for tokens, heads, kvh, D, window in [(40, 4, 2, 8, 8), (70, 8, 2, 16, 12), (11, 4, 2, 4, 5)]:
+        q, k, v, rel = _band_inputs(tokens, heads, kvh, D, window)
+        band = lambda kk, vv: orc.attention(q, kk, vv, heads, kvh, D, 0, 1.0 / D, window=window, rel=rel)
+        base = band(k, v)
+        last = tokens - 1
+        for j, must_move in [(last - window, False), (last, True)]:
+            kk, vv = k.copy(), v.copy()
+            kk[j * kvh * D:(j + 1) * kvh * D] += 0.75
+            vv[j * kvh * D:(j + 1) * kvh * D] -= 0.75
+            moved = np.abs(band(kk, vv)[last] - base[last]).max()
+            assert (moved > 1e-4) if must_move else (moved == 0.0), (tokens, j, moved)
+    # banded.rs:462-500: a KV head reaches only the query heads of its own group
+    tokens, heads, kvh, D, window = 24, 8, 2, 16, 12
+    q, k, v, rel = _band_inputs(tokens, heads, kvh, D, window)
+    base = orc.attention(q, k, v, heads, kvh, D, 0, 1.0 / D, window=window, rel=rel)
+    at = tokens // 2
+    for c in range(kvh):
+        kk, vv = k.copy(), v.copy()
+        kk[at * kvh * D + c * D: at * kvh * D + (c + 1) * D] += 0.5
+        vv[at * kvh * D + c * D: at * kvh * D + (c + 1) * D] -= 0.5
+        got = orc.attention(q, kk, vv, heads, kvh, D, 0, 1.0 / D, window=window, rel=rel)
+        for h in range(heads):
+            moved = np.abs(got[:, h * D:(h + 1) * D] - base[:, h * D:(h + 1) * D]).max()
+            assert (moved > 1e-4) if h // (heads // kvh) == c else (moved == 0.0), (c, h, moved)
+
+
 def test_attention_relative_bias_enters_by_distance(orc):
     # src/models/inkling/flash.rs:1966-1972: bias rel[(qi * heads + h) * eff + dist] for dist < eff, after the scale
     q = np.zeros((2, 1)); k = np.zeros((4, 1)); v = np.array([1.0, 10.0, 100.0, 1000.0])
