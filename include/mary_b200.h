@@ -88,6 +88,12 @@ void mb_ctx_destroy(mb_ctx* ctx);
  * would stall the CTAs that were to run there. `sms` > 0 makes those kernels use at most that many SMs,
  * 0 restores all of them. No counterpart in the reference, whose GEMMs are not persistent. */
 int mb_ctx_set_sm_limit(mb_ctx* ctx, int sms);
+/* Wall-time budget of one wait on a peer rank inside the fused exchange kernels (mb_tp_reduce_residual):
+ * 100 us .. 60 s, one second by default. A wait that runs out ends the kernel with status word 0 set to
+ * the wait's code (51: a peer's partials, 52: a peer's slice), word 3 the microseconds waited and word 4
+ * the rank waited for; mb_check_flags then returns MB_ERR_DEVICE_FLAG and the context stays usable. The
+ * reference bounds its collectives by a watchdog on the host (src/models/inkling/tpcomm.rs:10-38). */
+int mb_ctx_set_wait_limit_us(mb_ctx* ctx, uint32_t microseconds);
 const char* mb_last_error(mb_ctx* ctx);
 const char* mb_version(void);
 /* Reads and clears the device status words (bounded-wait timeouts, non-finite
@@ -197,6 +203,25 @@ int mb_nvfp4_gemm_w4a4_grouped(mb_ctx* ctx, mb_stream stream, const uint8_t* a_c
                                size_t experts, size_t n, size_t k, void* out, int out_dtype, int epilogue,
                                void* out_sf, const int32_t* row_tok);
 
+/* w4a4_grouped_bf16 (src/nn/nvfp4_gemm.rs:462-523) with its two launches as two entry points: the decode-time
+ * grouped experts, one activation row per group against expert ids[g] of a bank (GroupedBank, :438-451).
+ * mb_nvfp4_quantize_grouped = quantize_grouped_kernel (:293-313): x is one shared bf16 row [k]
+ * (x_per_group = 0) or one row per group [groups, k]; group g is quantized by the divide recipe with the
+ * second-level scale input_scale[ids[g]] into codes [groups, k/2] and ROW-MAJOR scales [groups, k/16].
+ * mb_nvfp4_gemv_w4a4_grouped = w4a4_grouped_kernel (:320-432): out[g, :] = (a[g, :] . bank[ids[g]]^T) *
+ * alpha[ids[g]] with alpha the host's f32 scale2 * input_scale per expert; bank planes [experts, n, k/2] codes
+ * and [experts, n, k/16] ROW-MAJOR scales, streamed once at HBM rate. Per group this is
+ * Nvfp4::project_w4a4_scaled on one row up to the order of the f32 sums. ids: [groups] device int32,
+ * ascending and distinct in the reference's use; an id outside the bank raises the plan flag of the context
+ * (group + 1) and that group's row comes out as zeros. k % 64 == 0, n % 8 == 0, groups <= 65535. */
+int mb_nvfp4_quantize_grouped(mb_ctx* ctx, mb_stream stream, const void* x_bf16, int x_per_group, const int32_t* ids,
+                              size_t groups, const float* input_scale, size_t experts, size_t k, uint8_t* codes,
+                              uint8_t* scales_rowmajor);
+int mb_nvfp4_gemv_w4a4_grouped(mb_ctx* ctx, mb_stream stream, const uint8_t* a_codes, const uint8_t* a_scales_rowmajor,
+                               const uint8_t* bank_codes, const uint8_t* bank_scales_rowmajor, const float* alpha,
+                               const int32_t* ids, size_t groups, size_t experts, size_t n, size_t k, void* out,
+                               int out_dtype);
+
 /* Several projections of one input stacked along n (q|k|v, or gate and up interleaved row by
  * row), each stored tensor keeping its own global scale: colscale[n] holds the scale2 of the
  * tensor a column belongs to, out[m, c] = acc * colscale[c], rounded once, which is what the
@@ -215,6 +240,14 @@ int mb_nvfp4_gemm_w4a4_stacked(mb_ctx* ctx, mb_stream stream, const uint8_t* a_c
  * (the W4A16 lane, src/nn/nvfp4_gemm.rs:93-197: scale2 applied once to the accumulator). */
 int mb_bf16_gemm(mb_ctx* ctx, mb_stream stream, const void* a_bf16, const void* b_bf16, float alpha, size_t m,
                  size_t n, size_t k, void* out, int out_dtype);
+/* Nvfp4::project(W4a16) / w4a16_linear_launch (src/nn/nvfp4_gemm.rs:93-197, src/models/inkling/w4a16gemm.rs):
+ * [m, k] bf16 x [n, k]^T NVFP4 with the weight left four bits in HBM and no 16-bit copy of it anywhere: code
+ * bytes arrive in shared memory by TMA, converter warps expand code x block scale to bf16 (exact) into the
+ * tensor core's operand tile, tcgen05 kind::f16 accumulates in f32, scale2 is applied once to the accumulator,
+ * one cast. codes [n, k/2], scales [n, k/16] ROW-MAJOR (the canonical planes). k % 64 == 0, n % 8 == 0. */
+int mb_nvfp4_gemm_w4a16(mb_ctx* ctx, mb_stream stream, const void* x_bf16, const uint8_t* codes,
+                        const uint8_t* scales_rowmajor, float scale2, size_t m, size_t n, size_t k, void* out,
+                        int out_dtype);
 /* The same product when the output has few tiles and K is long (the router projection
  * src/models/k3/router.rs:300-340 `Router::logits`: [tokens, hidden] x [experts, hidden]^T): K slices into f32 planes of
  * `workspace`, summed in slice order. mb_bf16_gemm_splitk_workspace gives the bytes, 0 = not split. */
@@ -327,18 +360,61 @@ int mb_attention_fp4kv(mb_ctx* ctx, mb_stream stream, const void* q, const uint8
                        size_t heads, size_t kv_heads, size_t d, size_t q0, float scale, int causal, size_t window,
                        void* out, void* workspace, size_t workspace_bytes);
 
+/* flash_attention_launch (src/models/inkling/flash.rs:1140-1316) with its own argument list: one query
+ * block over any number of key runs, one run per page of a paged cache (KeyRun, flash.rs:995-1015).
+ * A run's buffers hold `rows` rows per sequence ([batch, rows, kv_heads * D], token-major; batch = 1 is
+ * the reference's call, more are independent sequences with identical run geometry); `base` is the
+ * absolute position of row 0; rows [lo, hi) are live keys (a page's dropped prefix and its tail padding
+ * are excluded without slicing the buffer); `row0` is the logical row of stored row 0, which the gap
+ * table is indexed by. kv_elem (KvElem, flash.rs:972-981): MB_KV_BF16 rows are read in place by TMA;
+ * MB_KV_NVFP4 runs carry code bytes in k/v ([.., kv_heads * D / 2]) and E4M3 block scales in
+ * k_scales/v_scales ([.., kv_heads * D / 16]) and are read packed; MB_KV_F32 rows are rounded to bf16
+ * into the workspace first (both products multiply bf16). q [batch, nq, heads * D] and out likewise,
+ * each bf16 or f32 (the reference's are f32); query i stands at absolute position q0 + i. Always causal
+ * on positions: a key is visible when key_abs <= q_abs, within `window` when window > 0
+ * (q_abs - key_abs < window), and gets rel[.., dist] added at distance dist < eff (rel [batch, nq, heads,
+ * eff] f32 or NULL). gap_rows/gap_cums (ngaps <= 64 device words each, or NULL, 0): the eviction gaps of
+ * Gaps (flash.rs:1017-1035). Decode shapes (nq * heads / kv_heads <= 16) split every run's visible keys
+ * in proportion to its span (key_run_splits, flash.rs:1318-1327) and merge all partials in one pass;
+ * prompt shapes take a single non-empty bf16 or f32 run without bias or gaps and run on the tcgen05
+ * kernel. At most 64 runs. workspace: mb_attention_runs_workspace bytes, 256-byte aligned. */
+enum { MB_KV_F32 = 0, MB_KV_BF16 = 1, MB_KV_NVFP4 = 2 };
+typedef struct mb_key_run {
+  const void* k;
+  const void* v;
+  const void* k_scales; /* MB_KV_NVFP4 only, else NULL */
+  const void* v_scales;
+  size_t rows;          /* rows per sequence in the buffers */
+  size_t base;          /* absolute sequence position of row 0 */
+  size_t lo;            /* first live row */
+  size_t hi;            /* one past the last live row */
+  size_t row0;          /* logical row of stored row 0 (gap table index) */
+} mb_key_run;
+size_t mb_attention_runs_workspace(const mb_key_run* runs, size_t n_runs, int kv_elem, size_t batch, size_t nq,
+                                   size_t q0, size_t heads, size_t kv_heads, size_t d, size_t window, size_t ngaps,
+                                   int q_dtype, int out_dtype);
+int mb_attention_runs(mb_ctx* ctx, mb_stream stream, const void* q, int q_dtype, const mb_key_run* runs, size_t n_runs,
+                      int kv_elem, const float* rel, size_t eff, const uint32_t* gap_rows, const uint32_t* gap_cums,
+                      size_t ngaps, size_t batch, size_t nq, size_t q0, size_t heads, size_t kv_heads, size_t d,
+                      size_t window, float scale, void* out, int out_dtype, void* workspace, size_t workspace_bytes);
+
 /* Decode attention without any allocation; it has no counterpart in the reference.
  * For hosts that gave all device memory to their own arena at start-up and may not
  * call the driver's allocator afterwards (an allocation there stalls the token step
  * and can fail under a full arena): the key-split scratch lives in a 16 MiB array
  * built into the library, so the caller passes only q, k, v and out. Same arithmetic
  * and argument meaning as mb_attention for decode shapes (nq * heads/kv_heads <= 16);
- * it splits the keys less than mb_attention would when that is what fits the array, and
- * shapes whose scratch exceeds 16 MiB even unsplit are refused with MB_ERR_INVALID. The first
- * call on a device looks up the array's device address (the context's device must be
- * current); make that call before any stream capture begins. All calls share the one
+ * it splits the keys less than mb_attention would when that is what fits the array.
+ * The array is also the entry point's one stated limit: a shape whose partials would not
+ * fit it at a single split (batch * kv_heads > 2016) is refused with MB_ERR_INVALID, by
+ * policy, although an unsplit launch would not use the array.
+ * The array and the two kernels become resident in mb_ctx_create (which runs
+ * mb_attention_decode_static_warm: address look-up, function attributes and one tiny
+ * launch of each kernel inside the array), not at the first call: create the contexts
+ * before the host sizes its arena, and before any stream capture. All calls share the one
  * array: the partials are fully rewritten by every call, nothing needs clearing, but two
  * calls that overlap on the GPU (different streams) race on it. */
+int mb_attention_decode_static_warm(mb_ctx* ctx);
 int mb_attention_decode_static(mb_ctx* ctx, mb_stream stream, const void* q, const void* k, const void* v,
                                size_t batch, size_t nq, size_t keys, size_t heads, size_t kv_heads, size_t d,
                                size_t q0, float scale, int causal, void* out);
@@ -347,6 +423,18 @@ int mb_attention_decode_static(mb_ctx* ctx, mb_stream stream, const void* q, con
 /* norm_kernel (src/models/breeze/cuda_ops.rs:88-117): bf16(bf16(x*inv)*gain). */
 int mb_rmsnorm(mb_ctx* ctx, mb_stream stream, const void* x_bf16, const void* gain_bf16, size_t rows,
                size_t width, float eps, void* out_bf16);
+/* rms_norm_kernel (src/models/inkling/resid.rs:272-322), the Inkling convention: f32 throughout and ONE
+ * rounding, out = O(x / sqrt(mean(x^2) + eps) * gain) with an f32 gain [width]; x and out bf16 or f32.
+ * The sum of squares runs in the reference kernel's order (min(256, next power of two of width) strided
+ * partials, then a halving tree), so the result does not depend on scheduling. width % 8 == 0, <= 8192. */
+int mb_rmsnorm_inkling(mb_ctx* ctx, mb_stream stream, const void* x, int x_dtype, const float* gain_f32, size_t rows,
+                       size_t width, float eps, void* out, int out_dtype);
+/* gate_up_silu(_narrow/_bf16)_launch (src/models/inkling/fp4gemm.rs:472-507, 574-623): the stand-alone pass
+ * over a fused gate/up result both [rows, 2 * inter] (bf16 or f32): act[r, i] = O(silu(g) * u) computed in
+ * f32, (g, u) = columns (2i, 2i + 1) when the rows of w13 interleave, columns (i, inter + i) when
+ * `halved` (all gates, then all ups). inter % 4 == 0. */
+int mb_gate_up_silu(mb_ctx* ctx, mb_stream stream, const void* both, int in_dtype, size_t rows, size_t inter,
+                    int halved, void* act, int out_dtype);
 /* element_kernel mode 0 / mode 2 (src/models/breeze/cuda_ops.rs:230-255). */
 int mb_add(mb_ctx* ctx, mb_stream stream, const void* a_bf16, const void* b_bf16, size_t n, void* out_bf16);
 int mb_swiglu(mb_ctx* ctx, mb_stream stream, const void* gate_bf16, const void* up_bf16, size_t n,
@@ -405,6 +493,12 @@ int mb_tp_close(mb_ctx* ctx);
 size_t mb_tp_symm_bytes(size_t t_max, size_t n);
 int mb_tp_symm_create(mb_ctx* ctx, size_t t_max, size_t n, uint8_t handle_out[64]);
 int mb_tp_symm_attach(mb_ctx* ctx, const uint8_t* handles_world_x64, int rank, int world);
+/* The same for ranks that live in ONE process (the reference's Group is threads of one process,
+ * src/models/inkling/tpcomm.rs:217-310): mb_tp_symm_local gives the device address of this context's
+ * exchange memory, and mb_tp_symm_attach_ptrs takes every rank's address as this process sees it
+ * (peers[rank] is ignored; peer access between the devices is the caller's to enable). */
+int mb_tp_symm_local(mb_ctx* ctx, void** local_out);
+int mb_tp_symm_attach_ptrs(mb_ctx* ctx, void* const* peers, int rank, int world);
 int mb_nvfp4_gemm_w4a4_scatter(mb_ctx* ctx, mb_stream stream, const uint8_t* a_codes, const uint8_t* a_sf_tiled,
                                const uint8_t* b_codes, const uint8_t* b_sf_tiled, float alpha, size_t m, size_t n,
                                size_t k, int step);

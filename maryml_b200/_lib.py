@@ -22,6 +22,14 @@ SF_ROWMAJOR, SF_TILED = 0, 1
 QUANT_SCALED, QUANT_RECIP, QUANT_ROWS = 0, 1, 2
 EPI_PLAIN, EPI_SWIGLU_INTERLEAVED, EPI_SWIGLU_ROUNDED = 0, 1, 3
 EPI_QUANT_RECIP, EPI_QUANT_SCALED = 0x100, 0x200
+KV_F32, KV_BF16, KV_NVFP4 = 0, 1, 2
+
+
+class KeyRun(C.Structure):
+    """mb_key_run: one run of key/value rows (a page of a paged cache)."""
+    _fields_ = [("k", C.c_void_p), ("v", C.c_void_p), ("k_scales", C.c_void_p), ("v_scales", C.c_void_p),
+                ("rows", C.c_size_t), ("base", C.c_size_t), ("lo", C.c_size_t), ("hi", C.c_size_t),
+                ("row0", C.c_size_t)]
 
 _vp, _sz, _f, _i = C.c_void_p, C.c_size_t, C.c_float, C.c_int
 
@@ -29,6 +37,7 @@ SIGNATURES = {
     "mb_ctx_create": (_i, [_i, C.POINTER(_vp)]),
     "mb_ctx_destroy": (None, [_vp]),
     "mb_ctx_set_sm_limit": (_i, [_vp, _i]),
+    "mb_ctx_set_wait_limit_us": (_i, [_vp, C.c_uint32]),
     "mb_last_error": (C.c_char_p, [_vp]),
     "mb_version": (C.c_char_p, []),
     "mb_check_flags": (_i, [_vp, _vp, C.POINTER(C.c_int32)]),
@@ -46,8 +55,11 @@ SIGNATURES = {
     "mb_nvfp4_gemm_w4a4_splitk": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _f, _sz, _sz, _sz, _vp, _i, _vp, _sz]),
     "mb_nvfp4_gemm_w4a4_grouped": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _sz, _sz, _sz, _sz, _vp, _i, _i,
                                         _vp, _vp]),
+    "mb_nvfp4_quantize_grouped": (_i, [_vp, _vp, _vp, _i, _vp, _sz, _vp, _sz, _sz, _vp, _vp]),
+    "mb_nvfp4_gemv_w4a4_grouped": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _sz, _sz, _sz, _sz, _vp, _i]),
     "mb_nvfp4_gemm_w4a4_stacked": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _sz, _sz, _sz, _vp, _i, _i, _vp, _vp, _sz]),
     "mb_bf16_gemm": (_i, [_vp, _vp, _vp, _vp, _f, _sz, _sz, _sz, _vp, _i]),
+    "mb_nvfp4_gemm_w4a16": (_i, [_vp, _vp, _vp, _vp, _vp, _f, _sz, _sz, _sz, _vp, _i]),
     "mb_bf16_gemm_splitk_workspace": (_sz, [_sz, _sz, _sz]),
     "mb_bf16_gemm_splitk": (_i, [_vp, _vp, _vp, _vp, _f, _sz, _sz, _sz, _vp, _i, _vp, _sz]),
     "mb_router_topk_softmax": (_i, [_vp, _vp, _vp, _sz, _sz, _sz, _i, _f, _vp, _vp]),
@@ -64,8 +76,14 @@ SIGNATURES = {
                                      _sz, _vp, _vp, _sz]),
     "mb_attention_fp4kv": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _sz, _sz, _sz, _sz, _sz, _sz, _sz, _f, _i, _sz,
                                 _vp, _vp, _sz]),
+    "mb_attention_runs_workspace": (_sz, [_vp, _sz, _i, _sz, _sz, _sz, _sz, _sz, _sz, _sz, _sz, _i, _i]),
+    "mb_attention_runs": (_i, [_vp, _vp, _vp, _i, _vp, _sz, _i, _vp, _sz, _vp, _vp, _sz, _sz, _sz, _sz, _sz, _sz, _sz,
+                               _sz, _f, _vp, _i, _vp, _sz]),
+    "mb_attention_decode_static_warm": (_i, [_vp]),
     "mb_attention_decode_static": (_i, [_vp, _vp, _vp, _vp, _vp, _sz, _sz, _sz, _sz, _sz, _sz, _sz, _f, _i, _vp]),
     "mb_rmsnorm": (_i, [_vp, _vp, _vp, _vp, _sz, _sz, _f, _vp]),
+    "mb_rmsnorm_inkling": (_i, [_vp, _vp, _vp, _i, _vp, _sz, _sz, _f, _vp, _i]),
+    "mb_gate_up_silu": (_i, [_vp, _vp, _vp, _i, _sz, _sz, _i, _vp, _i]),
     "mb_add": (_i, [_vp, _vp, _vp, _vp, _sz, _vp]),
     "mb_add_f32": (_i, [_vp, _vp, _vp, _vp, _sz, _vp]),
     "mb_swiglu": (_i, [_vp, _vp, _vp, _vp, _sz, _vp]),
@@ -81,6 +99,8 @@ SIGNATURES = {
     "mb_tp_symm_bytes": (_sz, [_sz, _sz]),
     "mb_tp_symm_create": (_i, [_vp, _sz, _sz, C.POINTER(C.c_uint8)]),
     "mb_tp_symm_attach": (_i, [_vp, C.POINTER(C.c_uint8), _i, _i]),
+    "mb_tp_symm_local": (_i, [_vp, C.POINTER(_vp)]),
+    "mb_tp_symm_attach_ptrs": (_i, [_vp, C.POINTER(_vp), _i, _i]),
     "mb_nvfp4_gemm_w4a4_scatter": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _f, _sz, _sz, _sz, _i]),
     "mb_tp_reduce_residual": (_i, [_vp, _vp, _vp, _sz, _sz, _i, C.POINTER(_vp)]),
     "mb_tp_symm_destroy": (_i, [_vp]),

@@ -21,6 +21,13 @@ MB_API int mb_ctx_create(int device, mb_ctx** out) {
     delete ctx;
     return MB_ERR_CUDA;
   }
+  // The allocation-free decode entry point's array and kernels are made resident now, while the host may still
+  // allocate, not at its first call (which may come after the host's arena has taken the device's memory).
+  if (mb_attention_decode_static_warm(ctx) != MB_OK) {
+    cudaFree(ctx->flags_dev);
+    delete ctx;
+    return MB_ERR_CUDA;
+  }
   *out = ctx;
   return MB_OK;
 }
@@ -37,6 +44,13 @@ MB_API int mb_ctx_set_sm_limit(mb_ctx* ctx, int sms) {
   MB_REQUIRE(ctx, ctx != nullptr, "set_sm_limit: null context");
   MB_REQUIRE(ctx, sms >= 0 && sms <= ctx->sm_count, "set_sm_limit: 0 (all) .. %d SMs, got %d", ctx->sm_count, sms);
   ctx->sm_limit = sms;
+  return MB_OK;
+}
+
+MB_API int mb_ctx_set_wait_limit_us(mb_ctx* ctx, uint32_t microseconds) {
+  MB_REQUIRE(ctx, ctx != nullptr, "set_wait_limit_us: null context");
+  MB_REQUIRE(ctx, microseconds >= 100 && microseconds <= 60000000u, "set_wait_limit_us: 100 us .. 60 s, got %u", microseconds);
+  ctx->wait_limit_us = microseconds;
   return MB_OK;
 }
 

@@ -308,8 +308,13 @@ attn_decode_kernel(const __grid_constant__ AttnParams p) {
     uint4 v = make_uint4(0, 0, 0, 0);
     if (r < rows) {
       const uint32_t qi = r / group, hg = r % group;
-      const __nv_bfloat16* src = p.q + ((size_t(b) * p.nq + qi) * p.heads + kvh * group + hg) * D + c * 8;
-      v = *reinterpret_cast<const uint4*>(src);
+      const size_t qoff = ((size_t(b) * p.nq + qi) * p.heads + kvh * group + hg) * D + c * 8;
+      if (p.q_f32) {
+        const float4 f0 = *reinterpret_cast<const float4*>(p.q_f32 + qoff), f1 = *reinterpret_cast<const float4*>(p.q_f32 + qoff + 4);
+        v = make_uint4(pack2(f0.x, f0.y), pack2(f0.z, f0.w), pack2(f1.x, f1.y), pack2(f1.z, f1.w));
+      } else {
+        v = *reinterpret_cast<const uint4*>(p.q + qoff);
+      }
       if (FP4) {
         // the packed rows expand to f16, so the products run as f16 x f16: Q goes to f16 (exact for
         // magnitudes in [2^-14, 65504], which bf16's 8 significant bits fit; larger ones saturate)
@@ -379,10 +384,10 @@ attn_decode_kernel(const __grid_constant__ AttnParams p) {
     // hand-over needs); both products take their fragments straight from those bytes.
     uint8_t* raw_ring = gen + DEC_TILE_FP4 + uint32_t(warp) * FP4_STAGES * FP4_RAW_WARP;
     const size_t stride_c = size_t(p.kv_heads) * (D / 2), stride_s = size_t(p.kv_heads) * (D / 16);
-    const uint8_t* kc0 = p.k_codes + (size_t(b) * p.keys * p.kv_heads + kvh) * (D / 2);
-    const uint8_t* vc0 = p.v_codes + (size_t(b) * p.keys * p.kv_heads + kvh) * (D / 2);
-    const uint8_t* ks0 = p.k_scales + (size_t(b) * p.keys * p.kv_heads + kvh) * (D / 16);
-    const uint8_t* vs0 = p.v_scales + (size_t(b) * p.keys * p.kv_heads + kvh) * (D / 16);
+    const uint8_t* kc0 = p.k_codes + (size_t(b) * p.cap * p.kv_heads + kvh) * (D / 2);
+    const uint8_t* vc0 = p.v_codes + (size_t(b) * p.cap * p.kv_heads + kvh) * (D / 2);
+    const uint8_t* ks0 = p.k_scales + (size_t(b) * p.cap * p.kv_heads + kvh) * (D / 16);
+    const uint8_t* vs0 = p.v_scales + (size_t(b) * p.cap * p.kv_heads + kvh) * (D / 16);
     // lane's sources for tile 0, advanced by 64 rows per tile: two 16-byte chunks of K and of V codes
     // (chunk i = lane + 32 u of 64: key row i >> 2, part i & 3) and one row's eight scale bytes
     // (lanes 0-15 K, 16-31 V). Rows past the slice are masked: zero fill keeps P V finite, and their
@@ -451,10 +456,10 @@ attn_decode_kernel(const __grid_constant__ AttnParams p) {
             const uint32_t r = g + 8u * (e >> 1);
             const uint32_t qi = r < rows ? r / group : 0u, hg = r < rows ? r % group : 0u;
             const uint32_t krow = uint32_t(kabs) + j * 8 + (lane & 3) * 2 + (e & 1);
-            uint32_t pos = krow;
+            uint32_t pos = p.pos0 + krow;
             for (uint32_t gi = 0; gi < p.ngaps; ++gi)
-              if (__ldg(p.gap_rows + gi) <= krow) pos = krow + __ldg(p.gap_cums + gi);
-            const uint32_t qpos = p.q0 + qi;
+              if (__ldg(p.gap_rows + gi) <= p.row0 + krow) pos = p.pos0 + krow + __ldg(p.gap_cums + gi);
+            const uint32_t qpos = p.q0_abs + qi;
             bool vis = krow < k_end && pos <= qpos;
             if (vis && p.window && qpos - pos >= p.window) vis = false;
             float val = s[j][e] * p.scale_log2;
@@ -519,11 +524,12 @@ attn_decode_kernel(const __grid_constant__ AttnParams p) {
         ll += merge[(w * 16 + r) * (D + 2) + D + 1] * f;
       }
       const uint32_t qi = r / group, hg = r % group;
-      if (p.splits == 1) {
+      if (p.slots == 1) {
         const float v = ll > 0.0f ? acc / ll : 0.0f;
-        p.out[((size_t(b) * p.nq + qi) * p.heads + kvh * group + hg) * D + d] = __float2bfloat16_rn(v);
+        const size_t o = ((size_t(b) * p.nq + qi) * p.heads + kvh * group + hg) * D + d;
+        if (p.out_f32) p.out_f32[o] = v; else p.out[o] = __float2bfloat16_rn(v);
       } else {
-        float* dst = p.part + (((size_t(b) * p.kv_heads + kvh) * p.splits + split) * 16 + r) * (D + 2);
+        float* dst = p.part + (((size_t(b) * p.kv_heads + kvh) * p.slots + p.slot0 + split) * 16 + r) * (D + 2);
         dst[d] = acc;
         if (d == 0) { dst[D] = mm; dst[D + 1] = ll; }
       }
@@ -533,8 +539,8 @@ attn_decode_kernel(const __grid_constant__ AttnParams p) {
 
 // Merge the key splits: out = sum_s o_s 2^(m_s - M) / sum_s l_s 2^(m_s - M).
 __global__ void __launch_bounds__(128)
-attn_combine_kernel(const float* __restrict__ part, __nv_bfloat16* __restrict__ out, uint32_t nq, uint32_t heads,
-                    uint32_t kv_heads, uint32_t splits) {
+attn_combine_kernel(const float* __restrict__ part, __nv_bfloat16* __restrict__ out, float* __restrict__ out_f32,
+                    uint32_t nq, uint32_t heads, uint32_t kv_heads, uint32_t splits) {
   mb_grid_dependency_sync();
   const uint32_t h = blockIdx.x % heads, qi = (blockIdx.x / heads) % nq, b = blockIdx.x / (heads * nq);
   const uint32_t group = heads / kv_heads, kvh = h / group, r = qi * group + h % group, d = threadIdx.x;
@@ -549,7 +555,9 @@ attn_combine_kernel(const float* __restrict__ part, __nv_bfloat16* __restrict__ 
     acc += src[s * split_stride + d] * f;
     ll += src[s * split_stride + D + 1] * f;
   }
-  out[((size_t(b) * nq + qi) * heads + h) * D + d] = __float2bfloat16_rn(ll > 0.0f ? acc / ll : 0.0f);
+  const float res = ll > 0.0f ? acc / ll : 0.0f;
+  const size_t o = ((size_t(b) * nq + qi) * heads + h) * D + d;
+  if (out_f32) out_f32[o] = res; else out[o] = __float2bfloat16_rn(res);
 }
 
 // ---------------------------------------------------------------------------------
@@ -681,8 +689,11 @@ typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 
-int make_tmap_4d(mb_ctx* ctx, CUtensorMap* tm, const void* basep, uint64_t batch, uint64_t rows, uint64_t hh,
-                 uint32_t box_rows) {
+// [batch, rows, hh, D] bf16 rows of which `rows` are live per sequence; consecutive sequences are `cap_rows`
+// rows apart (a cache allocated longer than its live keys is read in place: rows past `rows` are out of the
+// map's bounds and arrive as zeros, whatever the memory behind them holds).
+int make_tmap_4d(mb_ctx* ctx, CUtensorMap* tm, const void* basep, uint64_t batch, uint64_t rows, uint64_t cap_rows,
+                 uint64_t hh, uint32_t box_rows) {
   if (!ctx->encode_tiled) {
     void* sym = nullptr;
     cudaDriverEntryPointQueryResult q;
@@ -693,7 +704,7 @@ int make_tmap_4d(mb_ctx* ctx, CUtensorMap* tm, const void* basep, uint64_t batch
   }
   EncodeTiledFn enc = reinterpret_cast<EncodeTiledFn>(ctx->encode_tiled);
   cuuint64_t dims[4] = {uint64_t(D), hh, rows, batch};
-  cuuint64_t strides[3] = {uint64_t(D) * 2, hh * D * 2, rows * hh * D * 2};
+  cuuint64_t strides[3] = {uint64_t(D) * 2, hh * D * 2, cap_rows * hh * D * 2};
   cuuint32_t box[4] = {64, 1, box_rows, 1};
   cuuint32_t estr[4] = {1, 1, 1, 1};
   CUresult r = enc(tm, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(basep), dims, strides, box, estr,
@@ -725,13 +736,23 @@ uint32_t decode_splits(size_t batch, size_t kv_heads, size_t keys) {
   return uint32_t(best);
 }
 
-}  // namespace
-
-MB_API size_t mb_attention_workspace(size_t batch, size_t nq, size_t keys, size_t heads, size_t kv_heads, size_t d) {
-  (void)d;
-  if (kv_heads == 0 || heads % kv_heads != 0) return 0;
-  if (nq * (heads / kv_heads) > 16) return 0;   // prefill needs none
-  return batch * kv_heads * size_t(decode_splits(batch, kv_heads, keys)) * 16 * (D + 2) * sizeof(float);
+// [batch, live rows, elems] out of [batch, cap rows, elems] f32 -> contiguous bf16 (elems a multiple of 4)
+__global__ void __launch_bounds__(256)
+f32_rows_to_bf16_kernel(const float* __restrict__ src, __nv_bfloat16* __restrict__ dst, size_t live_elems,
+                        size_t cap_elems, size_t total4) {
+  const size_t i = size_t(blockIdx.x) * 256 + threadIdx.x;
+  if (i >= total4) return;
+  const size_t e = i * 4, b = e / live_elems, r = e - b * live_elems;
+  const float4 v = *reinterpret_cast<const float4*>(src + b * cap_elems + r);
+  *reinterpret_cast<uint2*>(dst + e) = make_uint2(pack2(v.x, v.y), pack2(v.z, v.w));
+}
+__global__ void __launch_bounds__(256)
+bf16_to_f32_kernel(const __nv_bfloat16* __restrict__ src, float* __restrict__ dst, size_t total4) {
+  const size_t i = size_t(blockIdx.x) * 256 + threadIdx.x;
+  if (i >= total4) return;
+  const uint2 v = *reinterpret_cast<const uint2*>(src + i * 4);
+  *reinterpret_cast<float4*>(dst + i * 4) = make_float4(__uint_as_float(v.x << 16), __uint_as_float(v.x & 0xFFFF0000u),
+                                                        __uint_as_float(v.y << 16), __uint_as_float(v.y & 0xFFFF0000u));
 }
 
 struct AttnExt {
@@ -742,116 +763,254 @@ struct AttnExt {
   size_t ngaps = 0;
 };
 
-static int attention_common(mb_ctx* ctx, mb_stream stream_, const void* q, const void* k, const void* v, size_t batch,
-                            size_t nq, size_t keys, size_t heads, size_t kv_heads, size_t d, size_t q0, float scale,
-                            int causal, size_t window, void* out, void* workspace, size_t workspace_bytes,
-                            const uint8_t* const* fp4 = nullptr, const AttnExt* ext = nullptr) {
-  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+// One run of key/value rows as a launch sees it: its live rows only.
+struct RunView {
+  const void* k = nullptr;          // first live row: bf16 values, or NVFP4 code bytes
+  const void* v = nullptr;
+  const uint8_t* k_scales = nullptr;
+  const uint8_t* v_scales = nullptr;
+  size_t live = 0;                  // live rows
+  size_t cap = 0;                   // rows per sequence of the buffer (the batch stride)
+  size_t pos0 = 0;                  // absolute position of the first live row (gaps aside)
+  size_t row0 = 0;                  // logical row of the first live row (the gap table's index)
+};
+
+// The rows of a run some query of the block can see, [first, end) in live-row numbering, and the split count
+// each run gets: the call's total follows decode_splits over all visible rows, a run takes its share by span
+// (src/models/inkling/flash.rs `key_run_splits`), at least one, never below 256 keys per split.
+struct RunPlan {
+  size_t first = 0, end = 0;
+  uint32_t splits = 0, slot0 = 0;
+};
+
+size_t plan_runs(const RunView* runs, size_t n_runs, size_t batch, size_t kv_heads, size_t nq, size_t q0, int causal,
+                 size_t window, bool gapped, RunPlan* plan) {
+  size_t total = 0;
+  for (size_t i = 0; i < n_runs; ++i) {
+    const RunView& r = runs[i];
+    size_t end = r.live, first = 0;
+    if (causal) {
+      // a key at position pos0 + row (or later, with gaps) is visible to the last query when pos <= q0 + nq - 1
+      end = q0 + nq > r.pos0 ? std::min(r.live, q0 + nq - r.pos0) : 0;
+    }
+    if (window && !gapped && q0 + 1 > window + r.pos0) first = std::min(end, (q0 + 1 - window - r.pos0) / BC * BC);
+    plan[i].first = first;
+    plan[i].end = end;
+    total += end - first;
+  }
+  const size_t want = decode_splits(batch, kv_heads, total ? total : 1);
+  uint32_t slots = 0;
+  for (size_t i = 0; i < n_runs; ++i) {
+    const size_t span = plan[i].end - plan[i].first;
+    uint32_t s = 0;
+    if (span) {
+      const size_t by_span = (want * span + total - 1) / total;
+      const size_t cap = std::min<size_t>((span + 255) / 256, 64);
+      s = uint32_t(std::max<size_t>(1, std::min(by_span, cap)));
+    }
+    plan[i].splits = s;
+    plan[i].slot0 = slots;
+    slots += s;
+  }
+  return slots;
+}
+
+int decode_set_attributes(mb_ctx* ctx) {
+  if (!mb_once(ctx, MB_ONCE_ATTN_DECODE)) {
+    MB_CUDA_OK(ctx, cudaFuncSetAttribute(attn_decode_kernel<false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, DEC_SMEM));
+    MB_CUDA_OK(ctx, cudaFuncSetAttribute(attn_decode_kernel<false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, DEC_SMEM));
+    MB_CUDA_OK(ctx, cudaFuncSetAttribute(attn_decode_kernel<true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, DEC_SMEM_FP4));
+    MB_CUDA_OK(ctx, cudaFuncSetAttribute(attn_decode_kernel<true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, DEC_SMEM_FP4));
+    mb_once_done(ctx, MB_ONCE_ATTN_DECODE);
+  }
+  return MB_OK;
+}
+
+constexpr size_t MAX_RUNS = 64;
+
+// Attention of one query block over key runs. q/out bf16 (q, out) or f32 (q_f32, out_f32).
+int attention_core(mb_ctx* ctx, cudaStream_t stream, const void* q, const float* q_f32, const RunView* runs,
+                   size_t n_runs, bool fp4, size_t batch, size_t nq, size_t heads, size_t kv_heads, size_t d, size_t q0,
+                   float scale, int causal, size_t window, const AttnExt* ext, void* out, float* out_f32,
+                   void* workspace, size_t workspace_bytes) {
+  MB_REQUIRE(ctx, ctx != nullptr, "attention: null context");
   MB_REQUIRE(ctx, window == 0 || causal, "attention: a sliding window is a causal window");
   MB_REQUIRE(ctx, window < (1ull << 31), "attention: bad window");
-  MB_REQUIRE(ctx, window == 0 || (ext && ext->ngaps) || keys >= q0 + nq,
-             "attention: with a window every query needs its own key in the cache");
-  MB_REQUIRE(ctx, ctx && q && out && (fp4 ? fp4[0] && fp4[1] && fp4[2] && fp4[3] : k && v), "attention: null argument");
+  MB_REQUIRE(ctx, (q || q_f32) && (out || out_f32) && runs && n_runs > 0, "attention: null argument");
+  MB_REQUIRE(ctx, n_runs <= MAX_RUNS, "attention: at most %zu key runs per call, got %zu", MAX_RUNS, n_runs);
   MB_REQUIRE(ctx, d == D, "attention: head_dim must be 128, got %zu", d);
-  MB_REQUIRE(ctx, batch > 0 && nq > 0 && keys > 0 && heads > 0 && kv_heads > 0 && heads % kv_heads == 0,
-             "attention: bad extents (batch %zu, nq %zu, keys %zu, heads %zu, kv_heads %zu)", batch, nq, keys, heads, kv_heads);
+  MB_REQUIRE(ctx, batch > 0 && nq > 0 && heads > 0 && kv_heads > 0 && heads % kv_heads == 0,
+             "attention: bad extents (batch %zu, nq %zu, heads %zu, kv_heads %zu)", batch, nq, heads, kv_heads);
   MB_REQUIRE(ctx, scale == scale && scale > 0.0f, "attention: scale must be positive");
-  MB_REQUIRE(ctx, mb_aligned(q, 16) && mb_aligned(out, 16) && (fp4 || (mb_aligned(k, 16) && mb_aligned(v, 16))),
+  MB_REQUIRE(ctx, mb_aligned(q, 16) && mb_aligned(q_f32, 16) && mb_aligned(out, 16) && mb_aligned(out_f32, 16),
              "attention: 16-byte alignment");
-  if (fp4) {
-    MB_REQUIRE(ctx, mb_aligned(fp4[0], 16) && mb_aligned(fp4[2], 16) && mb_aligned(fp4[1], 8) && mb_aligned(fp4[3], 8),
-               "attention: NVFP4 rows need 16-byte aligned codes and 8-byte aligned scales");
-    MB_REQUIRE(ctx, nq * (heads / kv_heads) <= 16,
-               "attention: NVFP4 rows are read by the decode kernel only (nq * heads / kv_heads <= 16)");
+  MB_REQUIRE(ctx, batch <= 65535 && heads <= 65535 && kv_heads <= 65535 && nq < (1ull << 31) && q0 < (1ull << 31),
+             "attention: extent overflow");
+  MB_REQUIRE_DEVICE(ctx, "attention");
+  const bool has_ext = ext && (ext->rel || ext->ngaps);
+  const size_t group = heads / kv_heads;
+  const bool decode = nq * group <= 16;
+  size_t total_live = 0;
+  for (size_t i = 0; i < n_runs; ++i) {
+    const RunView& r = runs[i];
+    MB_REQUIRE(ctx, r.k && r.v && (!fp4 || (r.k_scales && r.v_scales)), "attention: key run %zu has a null plane", i);
+    MB_REQUIRE(ctx, r.live <= r.cap && r.cap < (1ull << 31) && r.pos0 < (1ull << 31) && r.row0 < (1ull << 31),
+               "attention: key run %zu: %zu live rows of %zu, position %zu", i, r.live, r.cap, r.pos0);
+    if (fp4)
+      MB_REQUIRE(ctx, mb_aligned(r.k, 16) && mb_aligned(r.v, 16) && mb_aligned(r.k_scales, 8) && mb_aligned(r.v_scales, 8),
+                 "attention: NVFP4 rows need 16-byte aligned codes and 8-byte aligned scales");
+    else
+      MB_REQUIRE(ctx, mb_aligned(r.k, 16) && mb_aligned(r.v, 16), "attention: 16-byte alignment");
+    total_live += r.live;
   }
-  MB_REQUIRE(ctx, batch <= 65535 && heads <= 65535 && keys < (1ull << 31) && nq < (1ull << 31), "attention: extent overflow");
-  MB_REQUIRE(ctx, q0 < (1ull << 31), "attention: bad query offset");
-  AttnParams p;
-  memset(&p, 0, sizeof p);
-  int rc = 0;
-  if (fp4) {
-    p.k_codes = fp4[0]; p.k_scales = fp4[1]; p.v_codes = fp4[2]; p.v_scales = fp4[3];
-  } else {
-    rc = make_tmap_4d(ctx, &p.tmap_k, k, batch, keys, kv_heads, BC);
-    if (rc) return rc;
-    rc = make_tmap_4d(ctx, &p.tmap_v, v, batch, keys, kv_heads, BC);
-    if (rc) return rc;
-  }
-  p.q = static_cast<const __nv_bfloat16*>(q);
-  p.out = static_cast<__nv_bfloat16*>(out);
-  p.flags = ctx->flags_dev;
-  p.batch = uint32_t(batch); p.nq = uint32_t(nq); p.keys = uint32_t(keys); p.heads = uint32_t(heads);
-  p.kv_heads = uint32_t(kv_heads); p.q0 = uint32_t(q0); p.causal = causal;
-  p.scale_log2 = scale * 1.4426950408889634f;
-  p.window = uint32_t(window);
-  // the first key the call's first query can see, on a tile boundary
-  p.k_lo = (window && q0 + 1 > window) ? uint32_t((q0 + 1 - window) / BC * BC) : 0u;
-  if (ext && (ext->rel || ext->ngaps)) {
+  MB_REQUIRE(ctx, total_live > 0, "attention: no live key in any run");
+  if (fp4)
+    MB_REQUIRE(ctx, decode, "attention: NVFP4 rows are read by the decode kernel only (nq * heads / kv_heads <= 16)");
+  if (has_ext) {
     MB_REQUIRE(ctx, causal, "attention: relative bias and eviction gaps belong to causal attention");
-    MB_REQUIRE(ctx, nq * (heads / kv_heads) <= 16,
+    MB_REQUIRE(ctx, decode,
                "attention: relative bias and eviction gaps are read by the decode kernel only (nq * heads / kv_heads <= 16)");
     MB_REQUIRE(ctx, !ext->rel || ext->eff > 0, "attention: a relative bias table needs eff > 0");
     MB_REQUIRE(ctx, ext->ngaps <= 64 && (ext->ngaps == 0 || (ext->gap_rows && ext->gap_cums)), "attention: bad gap list");
     MB_REQUIRE(ctx, ext->eff < (1ull << 31), "attention: bad eff");
+  }
+  const bool gapped = has_ext && ext->ngaps > 0;
+
+  AttnParams p;
+  memset(&p, 0, sizeof p);
+  p.q = static_cast<const __nv_bfloat16*>(q);
+  p.q_f32 = q_f32;
+  p.out = static_cast<__nv_bfloat16*>(out);
+  p.out_f32 = out_f32;
+  p.flags = ctx->flags_dev;
+  p.batch = uint32_t(batch); p.nq = uint32_t(nq); p.heads = uint32_t(heads);
+  p.kv_heads = uint32_t(kv_heads); p.causal = causal;
+  p.scale_log2 = scale * 1.4426950408889634f;
+  p.window = uint32_t(window);
+  p.q0_abs = uint32_t(q0);
+  if (has_ext) {
     p.rel = ext->rel; p.eff = uint32_t(ext->rel ? ext->eff : 0);
     p.gap_rows = ext->gap_rows; p.gap_cums = ext->gap_cums; p.ngaps = uint32_t(ext->ngaps);
-    if (p.ngaps) p.k_lo = 0;     // a row's position is at least its index: rows below the window's index can still be inside it
   }
-  const size_t group = heads / kv_heads;
-  static bool attr_dec[16] = {}, attr_pre[16] = {};
-  if (nq * group <= 16) {
-    const size_t span = keys > p.k_lo ? keys - p.k_lo : 1;   // keys the splits share (the window's, when there is one)
-    uint32_t splits = decode_splits(batch, kv_heads, span);
-    size_t need = batch * kv_heads * splits * 16 * (D + 2) * sizeof(float);
-    if (splits > 1) {
+
+  if (decode) {
+    RunPlan plan[MAX_RUNS];
+    const size_t slots = plan_runs(runs, n_runs, batch, kv_heads, nq, q0, causal, window, gapped, plan);
+    if (slots == 0) {
+      // no query of the block sees any key: the reference's combine writes zeros there
+      if (out_f32) MB_CUDA_OK(ctx, cudaMemsetAsync(out_f32, 0, batch * nq * heads * D * sizeof(float), stream));
+      else MB_CUDA_OK(ctx, cudaMemsetAsync(out, 0, batch * nq * heads * D * 2, stream));
+      return MB_OK;
+    }
+    const size_t need = batch * kv_heads * slots * 16 * (D + 2) * sizeof(float);
+    if (slots > 1) {
       MB_REQUIRE(ctx, workspace && workspace_bytes >= need, "attention: decode needs %zu workspace bytes", need);
       MB_REQUIRE(ctx, mb_aligned(workspace, 16), "attention: workspace needs 16-byte alignment");
     }
-    p.splits = splits;
-    p.keys_per_split = uint32_t(((span + splits - 1) / splits + BC - 1) / BC * BC);
+    int rc = decode_set_attributes(ctx);
+    if (rc) return rc;
+    p.slots = uint32_t(slots);
     p.part = static_cast<float*>(workspace);
-    if (!attr_dec[ctx->device & 15]) {
-      MB_CUDA_OK(ctx, cudaFuncSetAttribute(attn_decode_kernel<false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, DEC_SMEM));
-      MB_CUDA_OK(ctx, cudaFuncSetAttribute(attn_decode_kernel<false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, DEC_SMEM));
-      MB_CUDA_OK(ctx, cudaFuncSetAttribute(attn_decode_kernel<true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, DEC_SMEM_FP4));
-      MB_CUDA_OK(ctx, cudaFuncSetAttribute(attn_decode_kernel<true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, DEC_SMEM_FP4));
-      attr_dec[ctx->device & 15] = true;
-    }
-    dim3 grid(splits, unsigned(kv_heads), unsigned(batch));
-    const bool has_ext = p.rel || p.ngaps;
-    if (fp4 && has_ext)
-      MB_CUDA_OK(ctx, mb_launch_pdl(attn_decode_kernel<true, true>, grid, dim3(DEC_THREADS_FP4), DEC_SMEM_FP4, stream, p));
-    else if (fp4)
-      MB_CUDA_OK(ctx, mb_launch_pdl(attn_decode_kernel<true, false>, grid, dim3(DEC_THREADS_FP4), DEC_SMEM_FP4, stream, p));
-    else if (has_ext)
-      MB_CUDA_OK(ctx, mb_launch_pdl(attn_decode_kernel<false, true>, grid, dim3(DEC_THREADS), DEC_SMEM, stream, p));
-    else
-      MB_CUDA_OK(ctx, mb_launch_pdl(attn_decode_kernel<false, false>, grid, dim3(DEC_THREADS), DEC_SMEM, stream, p));
-    MB_LAUNCH_OK(ctx);
-    if (splits > 1) {
-      MB_CUDA_OK(ctx, mb_launch_pdl(attn_combine_kernel, dim3(unsigned(batch * nq * heads)), dim3(128), 0, stream, p.part, p.out,
-                                    p.nq, p.heads, p.kv_heads, splits));
+    for (size_t i = 0; i < n_runs; ++i) {
+      if (!plan[i].splits) continue;
+      const RunView& r = runs[i];
+      p.keys = uint32_t(plan[i].end);
+      p.k_lo = uint32_t(plan[i].first);
+      p.q0 = uint32_t(int64_t(q0) - int64_t(r.pos0));       // relative to the run's first live row; may be negative
+      p.pos0 = uint32_t(r.pos0); p.row0 = uint32_t(r.row0);
+      p.cap = uint32_t(r.cap);
+      p.splits = plan[i].splits; p.slot0 = plan[i].slot0;
+      const size_t span = plan[i].end - plan[i].first;
+      p.keys_per_split = uint32_t(((span + p.splits - 1) / p.splits + BC - 1) / BC * BC);
+      if (fp4) {
+        p.k_codes = static_cast<const uint8_t*>(r.k); p.v_codes = static_cast<const uint8_t*>(r.v);
+        p.k_scales = r.k_scales; p.v_scales = r.v_scales;
+      } else {
+        rc = make_tmap_4d(ctx, &p.tmap_k, r.k, batch, plan[i].end, r.cap, kv_heads, BC);
+        if (rc) return rc;
+        rc = make_tmap_4d(ctx, &p.tmap_v, r.v, batch, plan[i].end, r.cap, kv_heads, BC);
+        if (rc) return rc;
+      }
+      dim3 grid(p.splits, unsigned(kv_heads), unsigned(batch));
+      if (fp4 && has_ext)
+        MB_CUDA_OK(ctx, mb_launch_pdl(attn_decode_kernel<true, true>, grid, dim3(DEC_THREADS_FP4), DEC_SMEM_FP4, stream, p));
+      else if (fp4)
+        MB_CUDA_OK(ctx, mb_launch_pdl(attn_decode_kernel<true, false>, grid, dim3(DEC_THREADS_FP4), DEC_SMEM_FP4, stream, p));
+      else if (has_ext)
+        MB_CUDA_OK(ctx, mb_launch_pdl(attn_decode_kernel<false, true>, grid, dim3(DEC_THREADS), DEC_SMEM, stream, p));
+      else
+        MB_CUDA_OK(ctx, mb_launch_pdl(attn_decode_kernel<false, false>, grid, dim3(DEC_THREADS), DEC_SMEM, stream, p));
       MB_LAUNCH_OK(ctx);
     }
-  } else if (!mb_attention_prefill_legacy()) {
-    rc = make_tmap_4d(ctx, &p.tmap_q, q, batch, nq, heads, 128);
-    if (rc) return rc;
-    p.splits = 1;
-    return mb_attention_prefill_tc5(ctx, stream, p);
-  } else {
-    MB_REQUIRE(ctx, window == 0, "attention: the comparison (mma.sync) prefill kernel has no sliding window");
-    rc = make_tmap_4d(ctx, &p.tmap_q, q, batch, nq, heads, BR);
-    if (rc) return rc;
-    p.splits = 1;
-    if (!attr_pre[ctx->device & 15]) {
-      MB_CUDA_OK(ctx, cudaFuncSetAttribute(attn_prefill_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, PRE_SMEM));
-      attr_pre[ctx->device & 15] = true;
+    if (slots > 1) {
+      MB_CUDA_OK(ctx, mb_launch_pdl(attn_combine_kernel, dim3(unsigned(batch * nq * heads)), dim3(128), 0, stream, p.part, p.out,
+                                    p.out_f32, p.nq, p.heads, p.kv_heads, uint32_t(slots)));
+      MB_LAUNCH_OK(ctx);
     }
-    dim3 grid(unsigned((nq + BR - 1) / BR), unsigned(heads), unsigned(batch));
-    attn_prefill_kernel<<<grid, PRE_THREADS, PRE_SMEM, stream>>>(p);
-    MB_LAUNCH_OK(ctx);
+    return MB_OK;
   }
+
+  // prompt shapes: one run (the freshly projected keys and values, or one cache the prompt was appended to)
+  const RunView* one = nullptr;
+  for (size_t i = 0; i < n_runs; ++i) {
+    if (!runs[i].live) continue;
+    MB_REQUIRE(ctx, one == nullptr, "attention: prompt shapes (nq * heads / kv_heads > 16) take one key run, not %zu", n_runs);
+    one = &runs[i];
+  }
+  MB_REQUIRE(ctx, q != nullptr && out != nullptr, "attention: prompt shapes take bf16 queries and write bf16");
+  MB_REQUIRE(ctx, q0 >= one->pos0, "attention: the first query (position %zu) stands before the run's first key (%zu)",
+             q0, one->pos0);
+  MB_REQUIRE(ctx, one->live < (1ull << 31), "attention: extent overflow");
+  MB_REQUIRE(ctx, window == 0 || one->live >= q0 - one->pos0 + nq,
+             "attention: with a window every query needs its own key in the cache");
+  p.keys = uint32_t(one->live);
+  p.q0 = uint32_t(q0 - one->pos0);
+  p.splits = 1; p.slots = 1;
+  int rc = make_tmap_4d(ctx, &p.tmap_k, one->k, batch, one->live, one->cap, kv_heads, BC);
+  if (rc) return rc;
+  rc = make_tmap_4d(ctx, &p.tmap_v, one->v, batch, one->live, one->cap, kv_heads, BC);
+  if (rc) return rc;
+  if (!mb_attention_prefill_legacy()) {
+    rc = make_tmap_4d(ctx, &p.tmap_q, q, batch, nq, nq, heads, 128);
+    if (rc) return rc;
+    return mb_attention_prefill_tc5(ctx, stream, p);
+  }
+  MB_REQUIRE(ctx, window == 0, "attention: the comparison (mma.sync) prefill kernel has no sliding window");
+  rc = make_tmap_4d(ctx, &p.tmap_q, q, batch, nq, nq, heads, BR);
+  if (rc) return rc;
+  if (!mb_once(ctx, MB_ONCE_ATTN_PREFILL_LEGACY)) {
+    MB_CUDA_OK(ctx, cudaFuncSetAttribute(attn_prefill_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, PRE_SMEM));
+    mb_once_done(ctx, MB_ONCE_ATTN_PREFILL_LEGACY);
+  }
+  dim3 grid(unsigned((nq + BR - 1) / BR), unsigned(heads), unsigned(batch));
+  attn_prefill_kernel<<<grid, PRE_THREADS, PRE_SMEM, stream>>>(p);
+  MB_LAUNCH_OK(ctx);
   return MB_OK;
+}
+
+// The single-buffer entry points: one run of `keys` live rows at position 0 in a buffer of `keys` rows.
+int attention_common(mb_ctx* ctx, mb_stream stream_, const void* q, const void* k, const void* v, size_t batch,
+                     size_t nq, size_t keys, size_t heads, size_t kv_heads, size_t d, size_t q0, float scale,
+                     int causal, size_t window, void* out, void* workspace, size_t workspace_bytes,
+                     const uint8_t* const* fp4 = nullptr, const AttnExt* ext = nullptr) {
+  MB_REQUIRE(ctx, keys > 0 && keys < (1ull << 31), "attention: bad key count %zu", keys);
+  MB_REQUIRE(ctx, window == 0 || (ext && ext->ngaps) || keys >= q0 + nq,
+             "attention: with a window every query needs its own key in the cache");
+  RunView r;
+  if (fp4) { r.k = fp4[0]; r.k_scales = fp4[1]; r.v = fp4[2]; r.v_scales = fp4[3]; }
+  else { r.k = k; r.v = v; }
+  r.live = keys; r.cap = keys;
+  return attention_core(ctx, static_cast<cudaStream_t>(stream_), q, nullptr, &r, 1, fp4 != nullptr, batch, nq, heads,
+                        kv_heads, d, q0, scale, causal, window, ext, out, nullptr, workspace, workspace_bytes);
+}
+
+}  // namespace
+
+MB_API size_t mb_attention_workspace(size_t batch, size_t nq, size_t keys, size_t heads, size_t kv_heads, size_t d) {
+  (void)d;
+  if (kv_heads == 0 || heads % kv_heads != 0) return 0;
+  if (nq * (heads / kv_heads) > 16) return 0;   // prefill needs none
+  return batch * kv_heads * size_t(decode_splits(batch, kv_heads, keys)) * 16 * (D + 2) * sizeof(float);
 }
 
 MB_API int mb_attention(mb_ctx* ctx, mb_stream stream, const void* q, const void* k, const void* v, size_t batch,
@@ -873,6 +1032,7 @@ MB_API int mb_attention_fp4kv(mb_ctx* ctx, mb_stream stream, const void* q, cons
                               size_t nq, size_t keys, size_t heads, size_t kv_heads, size_t d, size_t q0, float scale,
                               int causal, size_t window, void* out, void* workspace, size_t workspace_bytes) {
   const uint8_t* planes[4] = {k_codes, k_scales, v_codes, v_scales};
+  MB_REQUIRE(ctx, k_codes && k_scales && v_codes && v_scales, "attention: null argument");
   return attention_common(ctx, stream, q, nullptr, nullptr, batch, nq, keys, heads, kv_heads, d, q0, scale, causal,
                           window, out, workspace, workspace_bytes, planes);
 }
@@ -889,6 +1049,147 @@ MB_API int mb_attention_decode_ext(mb_ctx* ctx, mb_stream stream, const void* q,
 }
 
 // ---------------------------------------------------------------------------------
+// flash_attention_launch over key runs (one run per page of a paged cache).
+// ---------------------------------------------------------------------------------
+namespace {
+
+size_t align256(size_t n) { return (n + 255) / 256 * 256; }
+
+// Live-row views of the caller's runs. For an f32 cache `converted` (when given) is where the bf16 copy of the
+// live rows of K then V of each run goes; the views then point there.
+int view_runs(mb_ctx* ctx, const mb_key_run* runs, size_t n_runs, int kv_elem, size_t batch, size_t kv_heads,
+              uint8_t* converted, RunView* views, size_t* converted_bytes) {
+  const size_t row_bytes = kv_heads * D * (kv_elem == MB_KV_F32 ? 4 : kv_elem == MB_KV_BF16 ? 2 : 0);
+  size_t off = 0;
+  for (size_t i = 0; i < n_runs; ++i) {
+    const mb_key_run& r = runs[i];
+    MB_REQUIRE(ctx, r.lo <= r.hi && r.hi <= r.rows, "attention_runs: run %zu: live range %zu..%zu is not inside its %zu rows",
+               i, r.lo, r.hi, r.rows);
+    MB_REQUIRE(ctx, r.k && r.v, "attention_runs: run %zu has a null plane", i);
+    MB_REQUIRE(ctx, (kv_elem == MB_KV_NVFP4) == (r.k_scales != nullptr && r.v_scales != nullptr),
+               "attention_runs: NVFP4 needs both block-scale planes and no other element type may carry them");
+    RunView& v = views[i];
+    v = RunView();
+    v.live = r.hi - r.lo; v.cap = r.rows; v.pos0 = r.base + r.lo; v.row0 = r.row0 + r.lo;
+    if (kv_elem == MB_KV_NVFP4) {
+      v.k = static_cast<const uint8_t*>(r.k) + r.lo * kv_heads * (D / 2);
+      v.v = static_cast<const uint8_t*>(r.v) + r.lo * kv_heads * (D / 2);
+      v.k_scales = static_cast<const uint8_t*>(r.k_scales) + r.lo * kv_heads * (D / 16);
+      v.v_scales = static_cast<const uint8_t*>(r.v_scales) + r.lo * kv_heads * (D / 16);
+    } else if (kv_elem == MB_KV_BF16) {
+      v.k = static_cast<const uint8_t*>(r.k) + r.lo * row_bytes;
+      v.v = static_cast<const uint8_t*>(r.v) + r.lo * row_bytes;
+    } else {
+      const size_t plane = align256(batch * v.live * kv_heads * D * 2);
+      if (converted) { v.k = converted + off; v.v = converted + off + plane; }
+      else { v.k = r.k; v.v = r.v; }       // sizing pass: any non-null pointer
+      v.cap = v.live;
+      off += 2 * plane;
+    }
+  }
+  *converted_bytes = off;
+  return MB_OK;
+}
+
+}  // namespace
+
+MB_API size_t mb_attention_runs_workspace(const mb_key_run* runs, size_t n_runs, int kv_elem, size_t batch, size_t nq,
+                                          size_t q0, size_t heads, size_t kv_heads, size_t d, size_t window, size_t ngaps,
+                                          int q_dtype, int out_dtype) {
+  (void)d;
+  if (!runs || n_runs == 0 || n_runs > MAX_RUNS || kv_heads == 0 || heads % kv_heads != 0) return 0;
+  RunView views[MAX_RUNS];
+  size_t conv = 0;
+  if (view_runs(nullptr, runs, n_runs, kv_elem, batch, kv_heads, nullptr, views, &conv) != MB_OK) return 0;
+  size_t need = conv;
+  if (nq * (heads / kv_heads) <= 16) {
+    RunPlan plan[MAX_RUNS];
+    const size_t slots = plan_runs(views, n_runs, batch, kv_heads, nq, q0, 1, window, ngaps > 0, plan);
+    if (slots > 1) need += align256(batch * kv_heads * slots * 16 * (D + 2) * sizeof(float));
+  } else {
+    if (q_dtype == MB_DT_F32) need += align256(batch * nq * heads * D * 2);
+    if (out_dtype == MB_DT_F32) need += align256(batch * nq * heads * D * 2);
+  }
+  return need;
+}
+
+MB_API int mb_attention_runs(mb_ctx* ctx, mb_stream stream_, const void* q, int q_dtype, const mb_key_run* runs,
+                             size_t n_runs, int kv_elem, const float* rel, size_t eff, const uint32_t* gap_rows,
+                             const uint32_t* gap_cums, size_t ngaps, size_t batch, size_t nq, size_t q0, size_t heads,
+                             size_t kv_heads, size_t d, size_t window, float scale, void* out, int out_dtype,
+                             void* workspace, size_t workspace_bytes) {
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  MB_REQUIRE(ctx, ctx && q && out && runs, "attention_runs: null argument");
+  MB_REQUIRE(ctx, n_runs > 0 && n_runs <= MAX_RUNS, "attention_runs: 1..%zu key runs, got %zu", MAX_RUNS, n_runs);
+  MB_REQUIRE(ctx, kv_elem == MB_KV_F32 || kv_elem == MB_KV_BF16 || kv_elem == MB_KV_NVFP4, "attention_runs: unknown key/value element type %d", kv_elem);
+  MB_REQUIRE(ctx, (q_dtype == MB_DT_BF16 || q_dtype == MB_DT_F32) && (out_dtype == MB_DT_BF16 || out_dtype == MB_DT_F32),
+             "attention_runs: queries and output are bf16 or f32");
+  MB_REQUIRE(ctx, d == D && kv_heads > 0 && heads > 0 && heads % kv_heads == 0 && batch > 0 && nq > 0,
+             "attention_runs: bad extents (head_dim %zu, heads %zu, kv_heads %zu, batch %zu, nq %zu)", d, heads, kv_heads, batch, nq);
+  MB_REQUIRE(ctx, workspace == nullptr || mb_aligned(workspace, 256), "attention_runs: workspace needs 256-byte alignment");
+  const size_t need = mb_attention_runs_workspace(runs, n_runs, kv_elem, batch, nq, q0, heads, kv_heads, d, window, ngaps,
+                                                  q_dtype, out_dtype);
+  MB_REQUIRE(ctx, need == 0 || (workspace && workspace_bytes >= need), "attention_runs: needs %zu workspace bytes", need);
+  MB_REQUIRE_DEVICE(ctx, "attention_runs");
+  uint8_t* ws = static_cast<uint8_t*>(workspace);
+  RunView views[MAX_RUNS];
+  size_t conv = 0;
+  int rc = view_runs(ctx, runs, n_runs, kv_elem, batch, kv_heads, ws, views, &conv);
+  if (rc) return rc;
+  if (kv_elem == MB_KV_F32) {
+    // f32 rows go through a bf16 copy of the live rows (both products multiply bf16)
+    for (size_t i = 0; i < n_runs; ++i) {
+      const size_t live = views[i].live;
+      if (!live) continue;
+      MB_REQUIRE(ctx, mb_aligned(runs[i].k, 16) && mb_aligned(runs[i].v, 16), "attention_runs: 16-byte alignment");
+      const size_t row = kv_heads * D, total4 = batch * live * row / 4;
+      const float* ksrc = static_cast<const float*>(runs[i].k) + runs[i].lo * row;
+      const float* vsrc = static_cast<const float*>(runs[i].v) + runs[i].lo * row;
+      const unsigned grid = unsigned((total4 + 255) / 256);
+      f32_rows_to_bf16_kernel<<<grid, 256, 0, stream>>>(ksrc, static_cast<__nv_bfloat16*>(const_cast<void*>(views[i].k)),
+                                                        live * row, runs[i].rows * row, total4);
+      f32_rows_to_bf16_kernel<<<grid, 256, 0, stream>>>(vsrc, static_cast<__nv_bfloat16*>(const_cast<void*>(views[i].v)),
+                                                        live * row, runs[i].rows * row, total4);
+      MB_LAUNCH_OK(ctx);
+    }
+  }
+  ws += conv;
+  AttnExt ext;
+  ext.rel = rel; ext.eff = eff; ext.gap_rows = gap_rows; ext.gap_cums = gap_cums; ext.ngaps = ngaps;
+  const bool decode = nq * (heads / kv_heads) <= 16;
+  if (decode) {
+    return attention_core(ctx, stream, q_dtype == MB_DT_BF16 ? q : nullptr,
+                          q_dtype == MB_DT_F32 ? static_cast<const float*>(q) : nullptr, views, n_runs,
+                          kv_elem == MB_KV_NVFP4, batch, nq, heads, kv_heads, d, q0, scale, 1, window, &ext,
+                          out_dtype == MB_DT_BF16 ? out : nullptr, out_dtype == MB_DT_F32 ? static_cast<float*>(out) : nullptr,
+                          ws, workspace_bytes - conv);
+  }
+  // prompt shapes run on the tcgen05 kernel, which reads and writes bf16: f32 queries and output pass through
+  // bf16 staging areas of the workspace
+  const size_t qo4 = batch * nq * heads * D / 4;
+  const void* q16 = q;
+  if (q_dtype == MB_DT_F32) {
+    MB_REQUIRE(ctx, mb_aligned(q, 16), "attention_runs: 16-byte alignment");
+    f32_rows_to_bf16_kernel<<<unsigned((qo4 + 255) / 256), 256, 0, stream>>>(static_cast<const float*>(q),
+                                                                             reinterpret_cast<__nv_bfloat16*>(ws), qo4 * 4, qo4 * 4, qo4);
+    MB_LAUNCH_OK(ctx);
+    q16 = ws;
+    ws += align256(qo4 * 8);
+  }
+  void* out16 = out_dtype == MB_DT_F32 ? static_cast<void*>(ws) : out;
+  rc = attention_core(ctx, stream, q16, nullptr, views, n_runs, false, batch, nq, heads, kv_heads, d, q0, scale, 1, window,
+                      &ext, out16, nullptr, nullptr, 0);
+  if (rc) return rc;
+  if (out_dtype == MB_DT_F32) {
+    MB_REQUIRE(ctx, mb_aligned(out, 16), "attention_runs: 16-byte alignment");
+    bf16_to_f32_kernel<<<unsigned((qo4 + 255) / 256), 256, 0, stream>>>(static_cast<const __nv_bfloat16*>(out16),
+                                                                        static_cast<float*>(out), qo4);
+    MB_LAUNCH_OK(ctx);
+  }
+  return MB_OK;
+}
+
+// ---------------------------------------------------------------------------------
 // Decode attention for hosts that must not allocate.
 //
 // Some hosts of this library hand their whole device-memory budget to an arena of
@@ -898,13 +1199,82 @@ MB_API int mb_attention_decode_ext(mb_ctx* ctx, mb_stream stream, const void* q,
 // nothing. Such a host can pass inputs and outputs it already owns, but it has nowhere
 // to get the scratch the key-split partials need. This entry point keeps that scratch
 // in a fixed array inside the library image instead.
+//
+// The array, like any module-scope device data, comes into being when the driver loads
+// this part of the library, which by default it puts off until first use. So that this
+// does not happen in the middle of serving either, mb_ctx_create runs the set-up below
+// (mb_attention_decode_static_warm): it resolves the array's address, sets the kernels'
+// attributes and launches both kernels once on a tiny problem laid out inside the array
+// itself. A host should create its contexts before it sizes its arena.
 // ---------------------------------------------------------------------------------
 constexpr size_t STATIC_SCRATCH_BYTES = size_t(16) << 20;   // 16 MiB, held by every GPU that loads the library
 static __device__ __align__(256) unsigned char g_decode_scratch[STATIC_SCRATCH_BYTES];
 
 // Device address of the array, resolved once per device. In host code the array's
 // name is only a handle for the runtime; the kernel needs the address looked up here.
-static float* g_decode_scratch_ptr[64] = {};
+constexpr int STATIC_MAX_DEVICES = 64;
+static float* g_decode_scratch_ptr[STATIC_MAX_DEVICES] = {};
+static std::mutex g_decode_scratch_mu;
+
+static int decode_static_launch(mb_ctx* ctx, cudaStream_t stream, const void* q, const void* k, const void* v,
+                                size_t batch, size_t nq, size_t keys, size_t heads, size_t kv_heads, size_t q0,
+                                float scale, int causal, void* out, float* scratch, uint32_t splits) {
+  AttnParams p;
+  memset(&p, 0, sizeof p);
+  int rc = make_tmap_4d(ctx, &p.tmap_k, k, batch, keys, keys, kv_heads, BC);
+  if (rc) return rc;
+  rc = make_tmap_4d(ctx, &p.tmap_v, v, batch, keys, keys, kv_heads, BC);
+  if (rc) return rc;
+  p.q = static_cast<const __nv_bfloat16*>(q);
+  p.out = static_cast<__nv_bfloat16*>(out);
+  p.flags = ctx->flags_dev;
+  p.batch = uint32_t(batch); p.nq = uint32_t(nq); p.keys = uint32_t(keys); p.heads = uint32_t(heads);
+  p.kv_heads = uint32_t(kv_heads); p.q0 = uint32_t(q0); p.q0_abs = uint32_t(q0); p.causal = causal;
+  p.scale_log2 = scale * 1.4426950408889634f;
+  p.splits = splits; p.slots = splits; p.cap = uint32_t(keys);
+  p.keys_per_split = uint32_t(((keys + splits - 1) / splits + BC - 1) / BC * BC);
+  p.part = scratch;
+  dim3 grid(splits, unsigned(kv_heads), unsigned(batch));
+  MB_CUDA_OK(ctx, mb_launch_pdl(attn_decode_kernel<false, false>, grid, dim3(DEC_THREADS), DEC_SMEM, stream, p));
+  MB_LAUNCH_OK(ctx);
+  if (splits > 1) {
+    MB_CUDA_OK(ctx, mb_launch_pdl(attn_combine_kernel, dim3(unsigned(batch * nq * heads)), dim3(128), 0, stream, p.part, p.out,
+                                  static_cast<float*>(nullptr), p.nq, p.heads, p.kv_heads, splits));
+    MB_LAUNCH_OK(ctx);
+  }
+  return MB_OK;
+}
+
+MB_API int mb_attention_decode_static_warm(mb_ctx* ctx) {
+  MB_REQUIRE(ctx, ctx != nullptr, "attention_decode_static_warm: null context");
+  if (mb_once(ctx, MB_ONCE_ATTN_STATIC)) return MB_OK;
+  MB_REQUIRE_DEVICE(ctx, "attention_decode_static_warm");
+  MB_REQUIRE(ctx, ctx->device < STATIC_MAX_DEVICES, "attention_decode_static_warm: device index %d is beyond %d", ctx->device,
+             STATIC_MAX_DEVICES);
+  float* base = nullptr;
+  {
+    std::lock_guard<std::mutex> g(g_decode_scratch_mu);
+    if (!g_decode_scratch_ptr[ctx->device]) {
+      void* ptr = nullptr;
+      MB_CUDA_OK(ctx, cudaGetSymbolAddress(&ptr, g_decode_scratch));
+      g_decode_scratch_ptr[ctx->device] = static_cast<float*>(ptr);
+    }
+    base = g_decode_scratch_ptr[ctx->device];
+  }
+  int rc = decode_set_attributes(ctx);
+  if (rc) return rc;
+  // One launch of the decode kernel and of the combine kernel, so that the driver has their code resident before
+  // the host's first token step: one sequence, one head, 512 zero keys in two splits, every operand carved out of
+  // the array itself (the array starts zeroed; the launch leaves partials and a zero output row in it).
+  uint8_t* a = reinterpret_cast<uint8_t*>(base);
+  const size_t kv_bytes = 512 * D * 2;
+  rc = decode_static_launch(ctx, nullptr, a + (1 << 20), a + (2 << 20), a + (2 << 20) + kv_bytes, 1, 1, 512, 1, 1, 511,
+                            0.088388347648f, 1, a + (1 << 20) + 4096, base, 2);
+  if (rc) return rc;
+  MB_CUDA_OK(ctx, cudaStreamSynchronize(nullptr));
+  mb_once_done(ctx, MB_ONCE_ATTN_STATIC);
+  return MB_OK;
+}
 
 MB_API int mb_attention_decode_static(mb_ctx* ctx, mb_stream stream_, const void* q, const void* k, const void* v,
                                       size_t batch, size_t nq, size_t keys, size_t heads, size_t kv_heads, size_t d,
@@ -919,52 +1289,22 @@ MB_API int mb_attention_decode_static(mb_ctx* ctx, mb_stream stream_, const void
   MB_REQUIRE(ctx, scale == scale && scale > 0.0f, "attention_decode_static: scale must be positive");
   MB_REQUIRE(ctx, mb_aligned(q, 16) && mb_aligned(k, 16) && mb_aligned(v, 16) && mb_aligned(out, 16),
              "attention_decode_static: 16-byte alignment");
-  MB_REQUIRE(ctx, batch <= 65535 && keys < (1ull << 31) && q0 < (1ull << 31), "attention_decode_static: extent overflow");
-  // fewer key splits than the heuristic's when its choice would not fit the built-in array
+  MB_REQUIRE(ctx, batch <= 65535 && heads <= 65535 && kv_heads <= 65535 && keys < (1ull << 31) && q0 < (1ull << 31),
+             "attention_decode_static: extent overflow");
+  // fewer key splits than the heuristic's when its choice would not fit the built-in array. The array's size is
+  // also the entry point's stated limit: a shape whose partials would not fit it at one split is refused, although
+  // an unsplit launch writes the output itself and would not touch the array (one limit, known in advance,
+  // instead of one that depends on the split heuristic).
   uint32_t splits = decode_splits(batch, kv_heads, keys);
   const size_t per_split = batch * kv_heads * size_t(16) * (D + 2) * sizeof(float);
   while (splits > 1 && per_split * splits > STATIC_SCRATCH_BYTES) --splits;
-  const size_t need = per_split * splits;
-  MB_REQUIRE(ctx, need <= STATIC_SCRATCH_BYTES,
-             "attention_decode_static: this shape needs %zu bytes of split scratch, the built-in array holds %zu; "
-             "use mb_attention with a caller workspace",
-             need, STATIC_SCRATCH_BYTES);
-  int current = -1;
-  MB_CUDA_OK(ctx, cudaGetDevice(&current));
-  MB_REQUIRE(ctx, current == ctx->device && current < 64,
-             "attention_decode_static: device %d must be current (it is %d)", ctx->device, current);
-  if (!g_decode_scratch_ptr[current]) {
-    void* ptr = nullptr;
-    MB_CUDA_OK(ctx, cudaGetSymbolAddress(&ptr, g_decode_scratch));
-    g_decode_scratch_ptr[current] = static_cast<float*>(ptr);
-  }
-  AttnParams p;
-  memset(&p, 0, sizeof p);
-  int rc = make_tmap_4d(ctx, &p.tmap_k, k, batch, keys, kv_heads, BC);
+  MB_REQUIRE(ctx, per_split * splits <= STATIC_SCRATCH_BYTES,
+             "attention_decode_static: batch x kv_heads = %zu is beyond the entry point's limit: one split's partials take "
+             "%zu bytes, the built-in array holds %zu; use mb_attention with a caller workspace",
+             batch * kv_heads, per_split, STATIC_SCRATCH_BYTES);
+  MB_REQUIRE_DEVICE(ctx, "attention_decode_static");
+  int rc = mb_attention_decode_static_warm(ctx);      // a no-op after mb_ctx_create
   if (rc) return rc;
-  rc = make_tmap_4d(ctx, &p.tmap_v, v, batch, keys, kv_heads, BC);
-  if (rc) return rc;
-  p.q = static_cast<const __nv_bfloat16*>(q);
-  p.out = static_cast<__nv_bfloat16*>(out);
-  p.flags = ctx->flags_dev;
-  p.batch = uint32_t(batch); p.nq = uint32_t(nq); p.keys = uint32_t(keys); p.heads = uint32_t(heads);
-  p.kv_heads = uint32_t(kv_heads); p.q0 = uint32_t(q0); p.causal = causal;
-  p.scale_log2 = scale * 1.4426950408889634f;
-  p.splits = splits;
-  p.keys_per_split = uint32_t(((keys + splits - 1) / splits + BC - 1) / BC * BC);
-  p.part = g_decode_scratch_ptr[current];
-  static bool attr_set[64] = {};
-  if (!attr_set[current]) {
-    MB_CUDA_OK(ctx, cudaFuncSetAttribute(attn_decode_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, DEC_SMEM));
-    attr_set[current] = true;
-  }
-  dim3 grid(splits, unsigned(kv_heads), unsigned(batch));
-  MB_CUDA_OK(ctx, mb_launch_pdl(attn_decode_kernel<false>, grid, dim3(DEC_THREADS), DEC_SMEM, stream, p));
-  MB_LAUNCH_OK(ctx);
-  if (splits > 1) {
-    MB_CUDA_OK(ctx, mb_launch_pdl(attn_combine_kernel, dim3(unsigned(batch * nq * heads)), dim3(128), 0, stream, p.part, p.out,
-                                    p.nq, p.heads, p.kv_heads, splits));
-    MB_LAUNCH_OK(ctx);
-  }
-  return MB_OK;
+  return decode_static_launch(ctx, stream, q, k, v, batch, nq, keys, heads, kv_heads, q0, scale, causal, out,
+                              g_decode_scratch_ptr[ctx->device], splits);
 }

@@ -10,9 +10,19 @@ struct AttnParams {
   CUtensorMap tmap_v;
   const __nv_bfloat16* q;
   __nv_bfloat16* out;
-  float* part;          // decode partials [batch, kv_heads, splits, 16 rows, D + 2]
+  // decode only: f32 queries / f32 output instead of the bf16 ones when non-null (the reference's
+  // flash_attention_launch takes and returns f32); queries are rounded to bf16 (f16 for NVFP4 rows) on load
+  const float* q_f32;
+  float* out_f32;
+  float* part;          // decode partials [batch, kv_heads, slots, 16 rows, D + 2]
   int* flags;
+  // keys: live rows of the key/value buffer as this launch sees it (row 0 = the first live row);
+  // q0: position of the first query relative to row 0 (two's complement when the queries start before it)
   uint32_t batch, nq, keys, heads, kv_heads, q0, splits, keys_per_split;
+  // a launch may be one of several over the key runs of a paged cache: its splits are slots
+  // [slot0, slot0 + splits) of `slots` partials per (sequence, kv head); slots == 1 writes the output itself
+  uint32_t slots, slot0;
+  uint32_t cap;         // NVFP4 rows: rows per sequence of the buffers (the batch stride); the dense readers' is in the tensor map
   float scale_log2;     // scale * log2(e)
   int causal;
   // sliding window (0 = none): query at position q sees keys in (q - window, q]; k_lo = first key any query of
@@ -31,6 +41,9 @@ struct AttnParams {
   const uint32_t* gap_rows;
   const uint32_t* gap_cums;
   uint32_t eff, ngaps;
+  // the same instantiation works in absolute terms: position of row 0 without gaps, logical row of row 0 (what
+  // the gap table is indexed by), position of the first query
+  uint32_t pos0, row0, q0_abs;
 };
 
 __device__ __forceinline__ void tma_load_4d(uint32_t dst, const void* tmap, int c0, int c1, int c2, int c3,

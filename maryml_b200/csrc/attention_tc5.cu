@@ -512,10 +512,9 @@ MB_API int mb_debug_attn_profile(unsigned long long* host_out, int reset) {
 #endif
 
 int mb_attention_prefill_tc5(mb_ctx* ctx, cudaStream_t stream, const AttnParams& p) {
-  static bool attr_set[16] = {};
-  if (!attr_set[ctx->device & 15]) {
+  if (!mb_once(ctx, MB_ONCE_ATTN_PREFILL_TC5)) {
     MB_CUDA_OK(ctx, cudaFuncSetAttribute(attn_prefill_tc5_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM));
-    attr_set[ctx->device & 15] = true;
+    mb_once_done(ctx, MB_ONCE_ATTN_PREFILL_TC5);
   }
   dim3 grid(unsigned((p.nq + 2 * QT - 1) / (2 * QT)), p.heads, p.batch);
   attn_prefill_tc5_kernel<<<grid, THREADS, SMEM, stream>>>(p);

@@ -10,6 +10,7 @@
 #include <cstdint>
 #include <cstdio>
 #include <cstdlib>
+#include <atomic>
 #include <cstring>
 #include <mutex>
 #include <string>
@@ -26,13 +27,35 @@ enum : int {
   MB_FLAG_COUNT = 8
 };
 
+// One-time per-context set-up steps (function attributes and the like), one bit each.
+enum : uint32_t {
+  MB_ONCE_GEMM_NVF4_256 = 1u << 0,
+  MB_ONCE_GEMM_NVF4_128 = 1u << 1,
+  MB_ONCE_GEMM_BF16_256 = 1u << 2,
+  MB_ONCE_GEMM_BF16_128 = 1u << 3,
+  MB_ONCE_ATTN_DECODE = 1u << 4,
+  MB_ONCE_ATTN_PREFILL_LEGACY = 1u << 5,
+  MB_ONCE_ATTN_PREFILL_TC5 = 1u << 6,
+  MB_ONCE_ATTN_STATIC = 1u << 7,
+  MB_ONCE_GEMM_W4A16_256 = 1u << 8,
+  MB_ONCE_GEMM_W4A16_128 = 1u << 9,
+};
+
 struct mb_ctx {
   int device = 0;
   int sm_count = 148;
   int sm_limit = 0;                  // persistent kernels use at most this many SMs (0 = all): room for a collective
-  int* flags_dev = nullptr;          // MB_FLAG_COUNT ints
+  int* flags_dev = nullptr;          // MB_FLAG_COUNT ints, then 8 spare words (see scratch_mu)
   std::string last_error;
   std::mutex mu;
+  // The spare words behind the status words are scratch of the entry points that read a reduction back
+  // (weight amax, E8M0 range, the warm-up sum): those hold this lock from their memset to their readback.
+  std::mutex scratch_mu;
+  // which one-time set-up steps this context has done (a context belongs to one device)
+  std::atomic<uint32_t> once{0};
+  int pair_clusters = 0;             // CTA pairs of the pair GEMM the device holds at once (0 = not asked yet)
+  // budget of the waits on peers in the fused exchange (tp.cu), microseconds of wall time
+  uint32_t wait_limit_us = 1000000;
   // Lazily resolved driver entry point for tensor-map encoding.
   void* encode_tiled = nullptr;
   // Tensor-parallel state (tp.cu).
@@ -53,7 +76,8 @@ struct mb_symm {
   void** peer_dev = nullptr;        // the same table in device memory
   size_t t_max = 0, n = 0, bytes = 0;
   int world = 1, rank = 0;
-  int* done_counter = nullptr;      // device counter of the reduce kernel's finished CTAs
+  bool ipc = true;                  // peers opened through CUDA IPC (closed at destroy) or handed in as pointers
+  int* done_counter = nullptr;      // two device counters of the reduce kernel's finished CTAs, one per step parity
 };
 __host__ __device__ inline size_t mb_symm_flags_bytes() { return 2 * 64 * sizeof(int); }
 __host__ __device__ inline size_t mb_symm_recv_bytes(size_t t_max, size_t n) { return 2 * t_max * n * sizeof(float); }
@@ -88,6 +112,19 @@ inline int mb_fail(mb_ctx* ctx, int code, const char* fmt, ...) {
 #define MB_LAUNCH_OK(ctx) MB_CUDA_OK(ctx, cudaGetLastError())
 
 inline bool mb_aligned(const void* p, size_t a) { return (reinterpret_cast<uintptr_t>(p) % a) == 0; }
+
+// True when the step was already done for this context; otherwise the caller does it and calls mb_once_done.
+inline bool mb_once(mb_ctx* ctx, uint32_t bit) { return (ctx->once.load(std::memory_order_acquire) & bit) != 0; }
+inline void mb_once_done(mb_ctx* ctx, uint32_t bit) { ctx->once.fetch_or(bit, std::memory_order_release); }
+
+// The context's device must be the calling thread's current device: launches and function attributes go to
+// the current device, tensor maps and pointers belong to the context's.
+#define MB_REQUIRE_DEVICE(ctx, what)                                                                      \
+  do {                                                                                                    \
+    int cur__ = -1;                                                                                       \
+    MB_CUDA_OK(ctx, cudaGetDevice(&cur__));                                                               \
+    MB_REQUIRE(ctx, cur__ == (ctx)->device, "%s: device %d must be current (it is %d)", what, (ctx)->device, cur__); \
+  } while (0)
 
 // ---------------------------------------------------------------------------
 // Device helpers

@@ -578,7 +578,25 @@ struct Gemm2Params {
   CUtensorMap tmap_sfa;   // tiled scale planes as [atoms, 128 x int32], box 4 atoms
   CUtensorMap tmap_sfb;
   uint32_t m_pairs;
+  uint32_t raster_group;  // row pairs per group of the tile order (see pair_tile)
 };
+
+// Tile order of the pair kernel. The pairs that run together take consecutive tile numbers, so the order
+// decides what they share in L2. Row pairs are taken in groups of `group`: inside a group the row pair runs
+// fastest and the column tile slowest, then the next group starts. The concurrent tiles then cover `group`
+// row pairs x (pairs / group) column tiles, a near-square patch whose operands are a few tens of MB, and
+// the A rows of a group stay in L2 while the group walks every column tile: A comes from DRAM once, B once
+// per group at most. With the row pair fastest over ALL rows (group = m_pairs) a K = 14336 activation
+// (66 MB with its scales) was pulled from DRAM again for every wave of column tiles.
+__device__ __forceinline__ void pair_tile(uint32_t tile, uint32_t m_pairs, uint32_t n_tiles, uint32_t group,
+                                          uint32_t& mp, uint32_t& nt) {
+  const uint32_t per_group = group * n_tiles;
+  const uint32_t g = tile / per_group, r = tile - g * per_group;
+  const uint32_t g0 = g * group;
+  const uint32_t gsz = min(group, m_pairs - g0);
+  nt = r / gsz;
+  mp = g0 + (r - nt * gsz);
+}
 
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREADS, 1)
 gemm_tc5_pair_kernel(const __grid_constant__ Gemm2Params pp) {
@@ -633,7 +651,8 @@ gemm_tc5_pair_kernel(const __grid_constant__ Gemm2Params pp) {
     uint32_t phase = 0;
     bool ok = true;
     for (uint32_t tile = pair; ok && tile < total_tiles; tile += n_pairs) {
-      const uint32_t mp = tile % pp.m_pairs, nt = tile / pp.m_pairs;
+      uint32_t mp, nt;
+      pair_tile(tile, pp.m_pairs, p.n_tiles, pp.raster_group, mp, nt);
       const uint32_t mt = mp * 2 + rank;                         // this CTA's 128-row tile of A
       for (uint32_t ks = 0; ks < p.k_steps; ++ks) {
         if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_smem, tflag, 21)) { ok = false; break; }
@@ -711,7 +730,8 @@ gemm_tc5_pair_kernel(const __grid_constant__ Gemm2Params pp) {
     uint32_t it = 0;
     bool ok = true;
     for (uint32_t tile = pair; ok && tile < total_tiles; tile += n_pairs, ++it) {
-      const uint32_t mp = tile % pp.m_pairs, nt = tile / pp.m_pairs;
+      uint32_t mp, nt;
+      pair_tile(tile, pp.m_pairs, p.n_tiles, pp.raster_group, mp, nt);
       const uint32_t buf = it & 1u;
       const uint32_t row0 = (mp * 2 + rank) * 128 + quad * 32u;
       const uint32_t row = row0 + lane;
@@ -831,11 +851,12 @@ int make_tmap(mb_ctx* ctx, CUtensorMap* tm, const void* base, bool bf16, uint64_
 template <int KIND, int BN>
 int launch(mb_ctx* ctx, cudaStream_t stream, const GemmParams& p, uint32_t max_tiles) {
   using C = Cfg<KIND, BN>;
-  static bool attr_set[16] = {};
+  constexpr uint32_t once_bit = KIND == KIND_NVF4 ? (BN == 256 ? MB_ONCE_GEMM_NVF4_256 : MB_ONCE_GEMM_NVF4_128)
+                                                  : (BN == 256 ? MB_ONCE_GEMM_BF16_256 : MB_ONCE_GEMM_BF16_128);
   auto kern = gemm_tc5_kernel<KIND, BN>;
-  if (!attr_set[ctx->device & 15]) {
+  if (!mb_once(ctx, once_bit)) {
     MB_CUDA_OK(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES));
-    attr_set[ctx->device & 15] = true;
+    mb_once_done(ctx, once_bit);
   }
   const int sms = ctx->sm_limit > 0 ? std::min(ctx->sm_limit, ctx->sm_count) : ctx->sm_count;
   unsigned grid = std::min<uint32_t>(max_tiles, uint32_t(sms));
@@ -864,9 +885,7 @@ int make_sf_tmap(mb_ctx* ctx, CUtensorMap* tm, const void* base, uint64_t atoms)
 
 // Launch of the CTA-pair kernel: as many clusters as the device can hold at once, persistent.
 int launch_pair(mb_ctx* ctx, cudaStream_t stream, Gemm2Params& pp) {
-  static int clusters[16] = {};
-  const int d = ctx->device & 15;
-  if (!clusters[d]) {
+  if (!ctx->pair_clusters) {
     MB_CUDA_OK(ctx, cudaFuncSetAttribute(gemm_tc5_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg2::SMEM_BYTES));
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(unsigned(ctx->sm_count) & ~1u);
@@ -880,10 +899,10 @@ int launch_pair(mb_ctx* ctx, cudaStream_t stream, Gemm2Params& pp) {
     int n = 0;
     MB_CUDA_OK(ctx, cudaOccupancyMaxActiveClusters(&n, gemm_tc5_pair_kernel, &cfg));
     if (n < 1) return mb_fail(ctx, MB_ERR_CUDA, "no CTA pair of the GEMM kernel fits on this device");
-    clusters[d] = n;
+    ctx->pair_clusters = n;
   }
   const uint32_t tiles = pp.m_pairs * pp.g.n_tiles;
-  uint32_t pairs = uint32_t(clusters[d]);
+  uint32_t pairs = uint32_t(ctx->pair_clusters);
   if (ctx->sm_limit > 0) pairs = std::min<uint32_t>(pairs, std::max(1, ctx->sm_limit / 2));
   const unsigned grid = 2u * std::min<uint32_t>(tiles, pairs);
   gemm_tc5_pair_kernel<<<grid, NUM_THREADS, Cfg2::SMEM_BYTES, stream>>>(pp);
@@ -923,6 +942,8 @@ int gemm_w4a4_common(mb_ctx* ctx, cudaStream_t stream, const uint8_t* a_codes, c
              "gemm_w4a4: unknown epilogue word 0x%x", epilogue_word);
   MB_REQUIRE(ctx, !quant || (swiglu && ex.out_sf && n % 32 == 0 && mb_aligned(ex.out_sf, 16)),
              "gemm_w4a4: a quantized output needs a SwiGLU epilogue, n a multiple of 32 and a scale plane");
+  MB_REQUIRE(ctx, !swiglu || n % 32 == 0,
+             "gemm_w4a4: a SwiGLU epilogue pairs 32 accumulator columns into 16 results; n must be a multiple of 32, got %zu", n);
   MB_REQUIRE(ctx, !ex.colscale || (n % 32 == 0 && mb_aligned(ex.colscale, 16)),
              "gemm_w4a4: column scales need n a multiple of 32 and 16-byte alignment");
   MB_REQUIRE(ctx, ctx && a_codes && a_sf && b_codes && b_sf && out, "gemm_w4a4: null argument");
@@ -1013,6 +1034,9 @@ int gemm_w4a4_common(mb_ctx* ctx, cudaStream_t stream, const uint8_t* a_codes, c
     rc = make_sf_tmap(ctx, &pp.tmap_sfb, b_sf, uint64_t((n + 127) / 128) * p.sf_kchunks);
     if (rc) return rc;
     pp.m_pairs = (p.m_tiles + 1) / 2;
+    // MB_GEMM_RASTER=<row pairs per group> in the environment overrides the group size (measurement runs)
+    static const uint32_t raster_env = [] { const char* e = getenv("MB_GEMM_RASTER"); return e ? uint32_t(atoi(e)) : 0u; }();
+    pp.raster_group = std::max<uint32_t>(1u, std::min<uint32_t>(pp.m_pairs, raster_env ? raster_env : 8u));
     return launch_pair(ctx, stream, pp);
   }
   return wide ? launch<KIND_NVF4, 256>(ctx, stream, p, tiles) : launch<KIND_NVF4, 128>(ctx, stream, p, tiles);

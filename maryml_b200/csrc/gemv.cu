@@ -15,6 +15,7 @@
 // activations of row g; the instruction's K slots are a permutation of those 128 values that
 // is the same for both operands, which is all the product needs.
 #include "common.cuh"
+#include "quant_block.cuh"
 
 #include <cuda_fp16.h>
 
@@ -117,6 +118,160 @@ gemv_w4a16_kernel(const uint4* __restrict__ x, const uint4* __restrict__ codes, 
   }
 }
 
+// ---------------------------------------------------------------------------------
+// Decode-time grouped experts: one activation row per group against expert ids[g] of a bank.
+//
+// Two launches, as the reference's lane (src/nn/nvfp4_gemm.rs:293-523). The quantizer is the
+// divide recipe with the expert's own second-level scale input_scale[ids[g]]. The product is the
+// GEMV above with both operands four bits: a decoded code times its block scale is exact in f16
+// (at most 7 significant bits, magnitudes in [2^-10, 2688]) for the weights AND for the quantized
+// activation, so the row is expanded to f16 once in shared memory, the weights of sixteen rows per
+// block stream through registers, and the products (exact in f32) are summed by the warp-level
+// tensor cores in f32. Per group that is project_w4a4_scaled on one row up to the order of the
+// f32 sums. HBM-bound: each chosen expert's planes (0.5625 B per weight) are read once.
+// ---------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256)
+quantize_grouped_kernel(const __nv_bfloat16* __restrict__ x, const int32_t* __restrict__ ids,
+                        const float* __restrict__ input_scale, uint32_t group_blocks, uint32_t total_blocks,
+                        uint32_t x_group_blocks, uint32_t experts, uint2* __restrict__ codes,
+                        uint8_t* __restrict__ scales, int* __restrict__ flag) {
+  const uint32_t blk = blockIdx.x * 256 + threadIdx.x;
+  if (blk >= total_blocks) return;
+  const uint32_t g = blk / group_blocks, within = blk - g * group_blocks;
+  int32_t e = __ldg(ids + g);
+  if (e < 0 || uint32_t(e) >= experts) {      // a bad expert id: flagged, quantized with a unit scale
+    atomicCAS(flag, 0, int(g) + 1);
+    e = -1;
+  }
+  const float s2 = e < 0 ? 1.0f : __ldg(input_scale + e);
+  const uint4* p = reinterpret_cast<const uint4*>(x + (size_t(g) * x_group_blocks + within) * 16);
+  const uint4 a = __ldg(p), b = __ldg(p + 1);
+  const uint32_t w[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+  float v[16];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    v[2 * i] = __uint_as_float(w[i] << 16);
+    v[2 * i + 1] = __uint_as_float(w[i] & 0xFFFF0000u);
+  }
+  uint32_t sbyte;
+  uint2 c;
+  quant_block_scaled(v, s2, sbyte, c);
+  codes[blk] = c;
+  scales[blk] = uint8_t(sbyte);
+}
+
+// Four codes (two bytes) times their block scale -> two f16x2 registers (exact).
+__device__ __forceinline__ void decode4h(uint32_t two_bytes, __half2 s, uint32_t& lo, uint32_t& hi) {
+  uint32_t h0, h1;
+  asm("{ .reg .b8 b0, b1, b2, b3; mov.b32 {b0, b1, b2, b3}, %2;\n\t"
+      "cvt.rn.f16x2.e2m1x2 %0, b0;\n\tcvt.rn.f16x2.e2m1x2 %1, b1; }"
+      : "=r"(h0), "=r"(h1) : "r"(two_bytes));
+  const __half2 p0 = __hmul2(*reinterpret_cast<__half2*>(&h0), s), p1 = __hmul2(*reinterpret_cast<__half2*>(&h1), s);
+  lo = *reinterpret_cast<const uint32_t*>(&p0);
+  hi = *reinterpret_cast<const uint32_t*>(&p1);
+}
+__device__ __forceinline__ void mma_f16(float* d, uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
+                                        uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, "
+               "{%0, %1, %2, %3};"
+               : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+               : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+// grid (n / 16, groups); dynamic shared memory: the group's activation row as k f16 values.
+template <typename O>
+__global__ void __launch_bounds__(32 * GEMV_WARPS)
+gemv_w4a4_grouped_kernel(const uint2* __restrict__ a_codes, const uint8_t* __restrict__ a_scales,
+                         const uint4* __restrict__ bank_codes, const uint8_t* __restrict__ bank_scales,
+                         const int32_t* __restrict__ ids, const float* __restrict__ alpha, O* __restrict__ out,
+                         uint32_t n, uint32_t k, uint32_t experts) {
+  extern __shared__ __align__(16) uint8_t xs_raw[];
+  uint4* xs = reinterpret_cast<uint4*>(xs_raw);                 // k / 8 units of eight f16 values
+  __shared__ float part[GEMV_WARPS][16];
+  const uint32_t lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const uint32_t g = lane >> 2, t = lane & 3;
+  const uint32_t grp = blockIdx.y;
+  const int32_t e_raw = __ldg(ids + grp);
+  const bool bad = e_raw < 0 || uint32_t(e_raw) >= experts;     // flagged by the quantizer; the row comes out as zeros
+  const uint32_t e = bad ? 0u : uint32_t(e_raw);
+  // the activation row: one 16-block per thread and step -> sixteen f16 values
+  for (uint32_t kb = threadIdx.x; kb < k / 16; kb += 32 * GEMV_WARPS) {
+    const uint2 c = __ldg(a_codes + size_t(grp) * (k / 16) + kb);
+    uint32_t sh;
+    asm("cvt.rn.f16x2.e4m3x2 %0, %1;" : "=r"(sh) : "h"(uint16_t(__ldg(a_scales + size_t(grp) * (k / 16) + kb))));
+    const __half2 s = __low2half2(*reinterpret_cast<__half2*>(&sh));
+    uint32_t h[8];
+    decode4h(c.x & 0xFFFFu, s, h[0], h[1]);
+    decode4h(c.x >> 16, s, h[2], h[3]);
+    decode4h(c.y & 0xFFFFu, s, h[4], h[5]);
+    decode4h(c.y >> 16, s, h[6], h[7]);
+    xs[kb * 2] = make_uint4(h[0], h[1], h[2], h[3]);
+    xs[kb * 2 + 1] = make_uint4(h[4], h[5], h[6], h[7]);
+  }
+  __syncthreads();
+  const uint32_t row_base = blockIdx.x * 16;
+  const uint32_t r0 = min(row_base + g, n - 1), r1 = min(row_base + g + 8, n - 1);
+  const uint32_t slices = (k + 127) / 128;
+  const uint4* c0 = bank_codes + (size_t(e) * n + r0) * (k / 32);
+  const uint4* c1 = bank_codes + (size_t(e) * n + r1) * (k / 32);
+  const uint16_t* s0p = reinterpret_cast<const uint16_t*>(bank_scales + (size_t(e) * n + r0) * (k / 16));
+  const uint16_t* s1p = reinterpret_cast<const uint16_t*>(bank_scales + (size_t(e) * n + r1) * (k / 16));
+  float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+  constexpr int U = 4;
+  for (uint32_t sl0 = warp; sl0 < slices; sl0 += GEMV_WARPS * U) {
+    uint4 wa[U], wb[U];
+    uint32_t sa[U], sb[U];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const uint32_t k0 = (sl0 + u * GEMV_WARPS) * 128 + t * 32;
+      const bool live = k0 < k;
+      wa[u] = live ? __ldg(c0 + k0 / 32) : make_uint4(0u, 0u, 0u, 0u);
+      wb[u] = live ? __ldg(c1 + k0 / 32) : make_uint4(0u, 0u, 0u, 0u);
+      sa[u] = live ? uint32_t(__ldg(s0p + k0 / 32)) : 0u;
+      sb[u] = live ? uint32_t(__ldg(s1p + k0 / 32)) : 0u;
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const uint32_t k0 = (sl0 + u * GEMV_WARPS) * 128 + t * 32;
+      if (sl0 + u * GEMV_WARPS >= slices) break;           // warp-uniform
+      // the one activation row is column 0 of the instruction's N side: lanes with g == 0 supply it
+      const bool live = g == 0 && k0 < k;
+      uint4 xv[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) xv[i] = live ? xs[k0 / 8 + i] : make_uint4(0u, 0u, 0u, 0u);
+      uint32_t sah, sbh;
+      asm("cvt.rn.f16x2.e4m3x2 %0, %1;" : "=r"(sah) : "h"(uint16_t(sa[u])));
+      asm("cvt.rn.f16x2.e4m3x2 %0, %1;" : "=r"(sbh) : "h"(uint16_t(sb[u])));
+      const __half2 sa2 = *reinterpret_cast<__half2*>(&sah), sb2 = *reinterpret_cast<__half2*>(&sbh);
+      const __half2 sa_lo = __low2half2(sa2), sa_hi = __high2half2(sa2);
+      const __half2 sb_lo = __low2half2(sb2), sb_hi = __high2half2(sb2);
+      const uint32_t wwa[4] = {wa[u].x, wa[u].y, wa[u].z, wa[u].w}, wwb[4] = {wb[u].x, wb[u].y, wb[u].z, wb[u].w};
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const uint32_t ba = (wwa[i >> 1] >> ((i & 1) * 16)) & 0xFFFFu, bb = (wwb[i >> 1] >> ((i & 1) * 16)) & 0xFFFFu;
+        uint32_t a0, a1, a2, a3;
+        decode4h(ba, i < 4 ? sa_lo : sa_hi, a0, a2);
+        decode4h(bb, i < 4 ? sb_lo : sb_hi, a1, a3);
+        const uint4& xq = xv[i >> 1];
+        const uint32_t b0 = (i & 1) ? xq.z : xq.x, b1 = (i & 1) ? xq.w : xq.y;
+        mma_f16(acc, a0, a1, a2, a3, b0, b1);
+      }
+    }
+  }
+  // column 0 of the accumulator tile: lanes with t == 0 hold weight rows g (acc[0]) and g + 8 (acc[2])
+  if (t == 0) {
+    part[warp][g] = acc[0];
+    part[warp][g + 8] = acc[2];
+  }
+  __syncthreads();
+  if (threadIdx.x < 16 && row_base + threadIdx.x < n) {
+    float sum = 0.0f;
+#pragma unroll
+    for (int w = 0; w < GEMV_WARPS; ++w) sum += part[w][threadIdx.x];
+    out[size_t(grp) * n + row_base + threadIdx.x] = O(bad ? 0.0f : sum * __ldg(alpha + e));
+  }
+}
+
 template <typename O>
 int launch_rows(cudaStream_t stream, size_t rows, const void* x, const uint8_t* codes, const uint8_t* scales, O* out,
                 uint32_t n, uint32_t k, float scale2) {
@@ -147,6 +302,50 @@ MB_API int mb_nvfp4_gemv_w4a16(mb_ctx* ctx, mb_stream stream_, const void* x_bf1
   else
     return mb_fail(ctx, MB_ERR_INVALID, "gemv: output is bf16 or f32");
   if (rc) return mb_fail(ctx, MB_ERR_INVALID, "gemv: unsupported row count");
+  MB_LAUNCH_OK(ctx);
+  return MB_OK;
+}
+
+MB_API int mb_nvfp4_quantize_grouped(mb_ctx* ctx, mb_stream stream_, const void* x_bf16, int x_per_group,
+                                     const int32_t* ids, size_t groups, const float* input_scale, size_t experts,
+                                     size_t k, uint8_t* codes, uint8_t* scales_rowmajor) {
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  MB_REQUIRE(ctx, ctx && x_bf16 && ids && input_scale && codes && scales_rowmajor, "quantize_grouped: null argument");
+  MB_REQUIRE(ctx, k > 0 && k % 64 == 0 && groups > 0 && groups <= 65535 && experts > 0,
+             "grouped W4A4 geometry [%zu groups, k %zu]", groups, k);
+  MB_REQUIRE(ctx, groups * (k / 16) <= 0xFFFFFF00ull, "quantize_grouped: exceeds u32 block indexing");
+  MB_REQUIRE(ctx, mb_aligned(x_bf16, 16) && mb_aligned(codes, 8), "quantize_grouped: 16/8-byte alignment");
+  const uint32_t group_blocks = uint32_t(k / 16), total = uint32_t(groups * (k / 16));
+  quantize_grouped_kernel<<<(total + 255) / 256, 256, 0, stream>>>(
+      static_cast<const __nv_bfloat16*>(x_bf16), ids, input_scale, group_blocks, total, x_per_group ? group_blocks : 0u,
+      uint32_t(experts), reinterpret_cast<uint2*>(codes), scales_rowmajor, ctx->flags_dev + MB_FLAG_PLAN_FAULT);
+  MB_LAUNCH_OK(ctx);
+  return MB_OK;
+}
+
+MB_API int mb_nvfp4_gemv_w4a4_grouped(mb_ctx* ctx, mb_stream stream_, const uint8_t* a_codes,
+                                      const uint8_t* a_scales_rowmajor, const uint8_t* bank_codes,
+                                      const uint8_t* bank_scales_rowmajor, const float* alpha, const int32_t* ids,
+                                      size_t groups, size_t experts, size_t n, size_t k, void* out, int out_dtype) {
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  MB_REQUIRE(ctx, ctx && a_codes && a_scales_rowmajor && bank_codes && bank_scales_rowmajor && alpha && ids && out,
+             "gemv_w4a4_grouped: null argument");
+  MB_REQUIRE(ctx, k > 0 && k % 64 == 0 && n > 0 && n % 8 == 0 && groups > 0 && groups <= 65535 && experts > 0,
+             "grouped W4A4 geometry [%zu x %zu, %zu]", groups, n, k);
+  MB_REQUIRE(ctx, n * k <= 0xFFFFFFFFull && k <= 24576, "gemv_w4a4_grouped: [%zu, %zu] exceeds u32 indexing or k > 24576", n, k);
+  MB_REQUIRE(ctx, mb_aligned(a_codes, 8) && mb_aligned(bank_codes, 16) && mb_aligned(bank_scales_rowmajor, 2),
+             "gemv_w4a4_grouped: planes need 8/16/2-byte alignment");
+  MB_REQUIRE(ctx, out_dtype == MB_DT_BF16 || out_dtype == MB_DT_F32, "gemv_w4a4_grouped: output is bf16 or f32");
+  const dim3 grid(unsigned((n + 15) / 16), unsigned(groups)), block(32 * GEMV_WARPS);
+  const size_t smem = k * 2;
+  if (out_dtype == MB_DT_BF16)
+    gemv_w4a4_grouped_kernel<__nv_bfloat16><<<grid, block, smem, stream>>>(
+        reinterpret_cast<const uint2*>(a_codes), a_scales_rowmajor, reinterpret_cast<const uint4*>(bank_codes),
+        bank_scales_rowmajor, ids, alpha, static_cast<__nv_bfloat16*>(out), uint32_t(n), uint32_t(k), uint32_t(experts));
+  else
+    gemv_w4a4_grouped_kernel<float><<<grid, block, smem, stream>>>(
+        reinterpret_cast<const uint2*>(a_codes), a_scales_rowmajor, reinterpret_cast<const uint4*>(bank_codes),
+        bank_scales_rowmajor, ids, alpha, static_cast<float*>(out), uint32_t(n), uint32_t(k), uint32_t(experts));
   MB_LAUNCH_OK(ctx);
   return MB_OK;
 }

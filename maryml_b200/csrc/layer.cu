@@ -239,7 +239,122 @@ rope_append_kernel(const uint4* __restrict__ qkv, uint4* __restrict__ q_out, uin
   dst[half8 + g] = pack8(oh);
 }
 
+
+// The Inkling convention (src/models/inkling/resid.rs:272-322): everything in f32 and ONE rounding at the end,
+// out = O(x / sqrt(mean(x^2) + eps) * gain) with an f32 gain. The sum of squares follows the reference kernel's
+// order exactly: `units` = min(256, next power of two of the width) partial sums, unit u adding elements u,
+// u + units, ... in turn (a * a + acc as one fused multiply-add, which is what the run-time compiler the
+// reference goes through makes of that expression), then a shared-memory tree that halves the partials. The
+// row is staged in shared memory as f32 so that the global loads stay 128-bit while the sums keep that order.
+template <typename I, typename O>
+__global__ void __launch_bounds__(256)
+rmsnorm_inkling_kernel(const I* __restrict__ x, const float* __restrict__ gain, O* __restrict__ out, uint32_t h,
+                       float eps, uint32_t units) {
+  extern __shared__ float srow[];
+  __shared__ float red[256];
+  mb_grid_dependency_sync();
+  const uint32_t u = threadIdx.x;
+  const size_t base = size_t(blockIdx.x) * h;
+  if (sizeof(I) == 2) {
+    const uint4* xr = reinterpret_cast<const uint4*>(x + base);
+    for (uint32_t c = u; c < h / 8; c += 256) unpack8(__ldg(xr + c), srow + c * 8);
+  } else {
+    const float4* xr = reinterpret_cast<const float4*>(x + base);
+    for (uint32_t c = u; c < h / 4; c += 256) *reinterpret_cast<float4*>(srow + c * 4) = __ldg(xr + c);
+  }
+  __syncthreads();
+  float acc = 0.0f;
+  if (u < units)
+    for (uint32_t i = u; i < h; i += units) acc = __fmaf_rn(srow[i], srow[i], acc);
+  red[u] = acc;
+  __syncthreads();
+  for (uint32_t step = units / 2; step > 0; step /= 2) {
+    if (u < step) red[u] = __fadd_rn(red[u], red[u + step]);
+    __syncthreads();
+  }
+  const float denom = __fsqrt_rn(__fadd_rn(__fdiv_rn(red[0], float(h)), eps));
+  for (uint32_t j = u; j < h; j += 256) {
+    const float r = __fmul_rn(__fdiv_rn(srow[j], denom), __ldg(gain + j));
+    if (sizeof(O) == 2) reinterpret_cast<__nv_bfloat16*>(out)[base + j] = __float2bfloat16_rn(r);
+    else reinterpret_cast<float*>(out)[base + j] = r;
+  }
+}
+
+
+// gate_up_silu (src/models/inkling/fp4gemm.rs:472-507) as the stand-alone pass the reference runs after its
+// fused gate/up product: act[r, i] = O(silu(g) * u) in f32, with (g, u) = both[r, 2i], both[r, 2i + 1]
+// (interleaved rows of w13) or both[r, i], both[r, inter + i] (halved). Four outputs per thread.
+template <typename I, typename O>
+__global__ void __launch_bounds__(256)
+gate_up_silu_kernel(const I* __restrict__ both, O* __restrict__ act, size_t total4, uint32_t inter, int halved) {
+  const size_t q = size_t(blockIdx.x) * 256 + threadIdx.x;
+  if (q >= total4) return;
+  const size_t idx = q * 4, r = idx / inter;
+  const uint32_t i = uint32_t(idx - r * inter);
+  const I* row = both + r * 2 * size_t(inter);
+  float g[4], u[4];
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    g[j] = float(halved ? row[i + j] : row[2 * (i + j)]);
+    u[j] = float(halved ? row[inter + i + j] : row[2 * (i + j) + 1]);
+  }
+#pragma unroll
+  for (int j = 0; j < 4; ++j) act[idx + j] = O(__fmul_rn(__fdiv_rn(g[j], __fadd_rn(1.0f, expf(-g[j]))), u[j]));
+}
+
 }  // namespace
+
+MB_API int mb_gate_up_silu(mb_ctx* ctx, mb_stream stream_, const void* both, int in_dtype, size_t rows, size_t inter,
+                           int halved, void* act, int out_dtype) {
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  MB_REQUIRE(ctx, ctx && both && act, "gate_up_silu: null argument");
+  MB_REQUIRE(ctx, rows > 0 && inter > 0 && inter % 4 == 0 && inter < (1ull << 30), "gate_up_silu: inter must be a positive multiple of 4, got %zu", inter);
+  MB_REQUIRE(ctx, (in_dtype == MB_DT_BF16 || in_dtype == MB_DT_F32) && (out_dtype == MB_DT_BF16 || out_dtype == MB_DT_F32),
+             "gate_up_silu: input and output are bf16 or f32");
+  const size_t total4 = rows * inter / 4;
+  const unsigned grid = unsigned((total4 + 255) / 256);
+  const uint32_t it = uint32_t(inter);
+  if (in_dtype == MB_DT_F32 && out_dtype == MB_DT_F32)
+    gate_up_silu_kernel<<<grid, 256, 0, stream>>>(static_cast<const float*>(both), static_cast<float*>(act), total4, it, halved);
+  else if (in_dtype == MB_DT_F32)
+    gate_up_silu_kernel<<<grid, 256, 0, stream>>>(static_cast<const float*>(both), static_cast<__nv_bfloat16*>(act), total4, it, halved);
+  else if (out_dtype == MB_DT_F32)
+    gate_up_silu_kernel<<<grid, 256, 0, stream>>>(static_cast<const __nv_bfloat16*>(both), static_cast<float*>(act), total4, it, halved);
+  else
+    gate_up_silu_kernel<<<grid, 256, 0, stream>>>(static_cast<const __nv_bfloat16*>(both), static_cast<__nv_bfloat16*>(act), total4, it, halved);
+  MB_LAUNCH_OK(ctx);
+  return MB_OK;
+}
+
+MB_API int mb_rmsnorm_inkling(mb_ctx* ctx, mb_stream stream_, const void* x, int x_dtype, const float* gain_f32,
+                              size_t rows, size_t width, float eps, void* out, int out_dtype) {
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  MB_REQUIRE(ctx, ctx && x && gain_f32 && out, "rmsnorm_inkling: null argument");
+  MB_REQUIRE(ctx, rows > 0 && rows < (1ull << 31) && width > 0 && width % 8 == 0 && width <= 8192,
+             "rmsnorm_inkling: width must be a multiple of 8 up to 8192, got %zu", width);
+  MB_REQUIRE(ctx, (x_dtype == MB_DT_BF16 || x_dtype == MB_DT_F32) && (out_dtype == MB_DT_BF16 || out_dtype == MB_DT_F32),
+             "rmsnorm_inkling: input and output are bf16 or f32");
+  MB_REQUIRE(ctx, mb_aligned(x, 16) && mb_aligned(gain_f32, 4) && mb_aligned(out, 4), "rmsnorm_inkling: alignment");
+  uint32_t units = 1;
+  while (units < width && units < 256) units *= 2;     // min(256, next power of two)
+  const size_t smem = width * sizeof(float);
+  const uint32_t h = uint32_t(width);
+  const dim3 grid(static_cast<unsigned>(rows));
+  if (x_dtype == MB_DT_BF16 && out_dtype == MB_DT_BF16)
+    rmsnorm_inkling_kernel<__nv_bfloat16, __nv_bfloat16><<<grid, 256, smem, stream>>>(
+        static_cast<const __nv_bfloat16*>(x), gain_f32, static_cast<__nv_bfloat16*>(out), h, eps, units);
+  else if (x_dtype == MB_DT_BF16)
+    rmsnorm_inkling_kernel<__nv_bfloat16, float><<<grid, 256, smem, stream>>>(
+        static_cast<const __nv_bfloat16*>(x), gain_f32, static_cast<float*>(out), h, eps, units);
+  else if (out_dtype == MB_DT_BF16)
+    rmsnorm_inkling_kernel<float, __nv_bfloat16><<<grid, 256, smem, stream>>>(
+        static_cast<const float*>(x), gain_f32, static_cast<__nv_bfloat16*>(out), h, eps, units);
+  else
+    rmsnorm_inkling_kernel<float, float><<<grid, 256, smem, stream>>>(static_cast<const float*>(x), gain_f32,
+                                                                      static_cast<float*>(out), h, eps, units);
+  MB_LAUNCH_OK(ctx);
+  return MB_OK;
+}
 
 MB_API int mb_rmsnorm(mb_ctx* ctx, mb_stream stream_, const void* x, const void* gain, size_t rows, size_t width,
                       float eps, void* out) {

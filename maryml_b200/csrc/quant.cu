@@ -401,15 +401,18 @@ MB_API int mb_nvfp4_quantize_weight(mb_ctx* ctx, mb_stream stream_, const void* 
   MB_REQUIRE(ctx, ctx && w_bf16 && codes && scales && scale2_host_out, "quantize_weight: null argument");
   MB_REQUIRE(ctx, n > 0 && k > 0 && k % 32 == 0, "NVFP4 needs contiguous [n, k] with k a multiple of 32, got [%zu, %zu]", n, k);
   MB_REQUIRE(ctx, n * k <= 0xFFFFFFFFull, "NVFP4 weight exceeds u32 indexing");
+  uint32_t host[2];
+  {
+  std::lock_guard<std::mutex> scratch_lock(ctx->scratch_mu);   // the spare words are shared by the context's streams
   uint32_t* scratch = reinterpret_cast<uint32_t*>(ctx->flags_dev + MB_FLAG_COUNT);  // two spare words
   MB_CUDA_OK(ctx, cudaMemsetAsync(scratch, 0, 8, stream));
   size_t len = n * k;
   unsigned grid = unsigned(std::min<size_t>((len + 255) / 256, size_t(ctx->sm_count) * 8));
   amax_kernel<<<grid, 256, 0, stream>>>(static_cast<const __nv_bfloat16*>(w_bf16), len, scratch);
   MB_LAUNCH_OK(ctx);
-  uint32_t host[2];
   MB_CUDA_OK(ctx, cudaMemcpyAsync(host, scratch, 8, cudaMemcpyDeviceToHost, stream));
   MB_CUDA_OK(ctx, cudaStreamSynchronize(stream));
+  }
   if (host[1]) return mb_fail(ctx, MB_ERR_NONFINITE, "NVFP4 source has a non-finite weight");
   float amax;
   memcpy(&amax, &host[0], 4);
@@ -460,14 +463,17 @@ MB_API int mb_mxfp4_to_nvfp4_scales(mb_ctx* ctx, mb_stream stream_, const uint8_
   MB_REQUIRE(ctx, ctx && e8m0 && block_scales && global_scale_host_out, "mxfp4 transcode: null argument");
   MB_REQUIRE(ctx, n > 0 && n < 0xFFFFFFFFull, "mxfp4 transcode: empty or oversized scale plane");
   MB_REQUIRE(ctx, mb_aligned(block_scales, 2), "mxfp4 transcode: the NVFP4 scale plane needs 2-byte alignment");
+  uint32_t host[3];
+  {
+  std::lock_guard<std::mutex> scratch_lock(ctx->scratch_mu);   // the spare words are shared by the context's streams
   uint32_t* scratch = reinterpret_cast<uint32_t*>(ctx->flags_dev + MB_FLAG_COUNT);   // spare words
   MB_CUDA_OK(ctx, cudaMemsetAsync(scratch, 0, 12, stream));
   const unsigned grid = unsigned(std::min<size_t>((n + 255) / 256, size_t(ctx->sm_count) * 8));
   e8m0_range_kernel<<<grid, 256, 0, stream>>>(e8m0, n, scratch);
   MB_LAUNCH_OK(ctx);
-  uint32_t host[3];
   MB_CUDA_OK(ctx, cudaMemcpyAsync(host, scratch, 12, cudaMemcpyDeviceToHost, stream));
   MB_CUDA_OK(ctx, cudaStreamSynchronize(stream));
+  }
   if (host[2]) return mb_fail(ctx, MB_ERR_NONFINITE, "E8M0 scale[%u] is NaN (0xFF)", 0xFFFFFFFFu - host[2]);
   const int e_max = int(host[0]) - 1 - 127, e_min = 256 - int(host[1]) - 127;
   const int g = e_max - 8;

@@ -100,6 +100,7 @@ MB_API int mb_tp_all_reduce(mb_ctx* ctx, mb_stream stream, void* buf, size_t cou
 MB_API int mb_tp_warm(mb_ctx* ctx, mb_stream stream_) {
   cudaStream_t stream = static_cast<cudaStream_t>(stream_);
   MB_REQUIRE(ctx, ctx != nullptr, "tp_warm: null context");
+  std::lock_guard<std::mutex> scratch(ctx->scratch_mu);
   float* probe = reinterpret_cast<float*>(ctx->flags_dev + MB_FLAG_COUNT + 4);
   float one = 1.0f, got = 0.0f;
   MB_CUDA_OK(ctx, cudaMemcpyAsync(probe, &one, 4, cudaMemcpyHostToDevice, stream));
@@ -142,25 +143,37 @@ MB_API int mb_tp_close(mb_ctx* ctx) {
 // ---------------------------------------------------------------------------------
 namespace {
 
-constexpr long long SYMM_WAIT_CYCLES = 2000000000LL;
-
 struct ReduceParams {
   void* const* peer;          // device table of every rank's exchange memory
   const __nv_bfloat16* resid; // [t, n] replicated residual stream
-  int* done_counter;
-  int* flag_timeout;
+  int* done_counter;          // two counters, one per step parity
+  int* flags;                 // the context's status words
+  unsigned long long wait_ns; // budget of one wait on the peers
   uint32_t t, n, nw, t_max, world, rank;
   int step;
 };
 
 __device__ __forceinline__ int* symm_flags(void* base) { return static_cast<int*>(base); }
+__device__ __forceinline__ unsigned long long wall_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
 
-__device__ bool wait_flags(volatile int* flags, uint32_t world, int step, int* flag_timeout, int code) {
-  long long t0 = clock64();
+// Waits until every rank's flag has reached `step`, for at most `wait_ns` of wall time. A wait that runs out
+// puts `code` into the context's timeout word; the first one of the context also leaves the time waited
+// (microseconds) in word 3 and the rank it was waiting for in word 4.
+__device__ bool wait_flags(volatile int* flags, uint32_t world, int step, int* status, unsigned long long wait_ns,
+                           int code) {
+  const unsigned long long t0 = wall_ns();
   for (uint32_t r = 0; r < world; ++r) {
     while (flags[r] < step) {
-      if (clock64() - t0 > SYMM_WAIT_CYCLES) {
-        if (flag_timeout) atomicCAS(flag_timeout, 0, code);
+      const unsigned long long waited = wall_ns() - t0;
+      if (waited > wait_ns) {
+        if (status && atomicCAS(status + MB_FLAG_WAIT_TIMEOUT, 0, code) == 0) {
+          status[3] = int(waited / 1000ull);
+          status[4] = int(r);
+        }
         return false;
       }
     }
@@ -178,7 +191,10 @@ tp_reduce_gather_kernel(const ReduceParams p) {
     volatile int* f = symm_flags(p.peer[threadIdx.x]);
     f[p.rank] = p.step;
   }
-  if (threadIdx.x == 0) s_ok = wait_flags(symm_flags(local), p.world, p.step, p.flag_timeout, 51) ? 1 : 0;
+  // The counter of the other step parity is cleared here for the next step: the kernel that used it has ended
+  // (stream order), also when it gave up in a wait and left its count unfinished.
+  if (blockIdx.x == 0 && threadIdx.x == 0) p.done_counter[(p.step + 1) & 1] = 0;
+  if (threadIdx.x == 0) s_ok = wait_flags(symm_flags(local), p.world, p.step, p.flags, p.wait_ns, 51) ? 1 : 0;
   __syncthreads();
   if (!s_ok) return;
   __threadfence_system();
@@ -222,9 +238,8 @@ tp_reduce_gather_kernel(const ReduceParams p) {
   __threadfence_system();
   __syncthreads();
   if (threadIdx.x == 0) {
-    const int done = atomicAdd(p.done_counter, 1);
+    const int done = atomicAdd(p.done_counter + (p.step & 1), 1);
     if (done == int(gridDim.x) - 1) {
-      *p.done_counter = 0;
       __threadfence_system();
       for (uint32_t r = 0; r < p.world; ++r) {
         volatile int* f = symm_flags(p.peer[r]) + 64;
@@ -232,7 +247,7 @@ tp_reduce_gather_kernel(const ReduceParams p) {
       }
     }
     // ---- D: every rank's slice is in my output before this kernel ends
-    wait_flags(symm_flags(local) + 64, p.world, p.step, p.flag_timeout, 52);
+    wait_flags(symm_flags(local) + 64, p.world, p.step, p.flags, p.wait_ns, 52);
     __threadfence_system();
   }
 }
@@ -253,8 +268,8 @@ MB_API int mb_tp_symm_create(mb_ctx* ctx, size_t t_max, size_t n, uint8_t handle
   MB_CUDA_OK(ctx, cudaMalloc(&sy->local, sy->bytes));
   MB_CUDA_OK(ctx, cudaMemset(sy->local, 0, sy->bytes));
   MB_CUDA_OK(ctx, cudaMalloc(&sy->peer_dev, 8 * sizeof(void*)));
-  MB_CUDA_OK(ctx, cudaMalloc(&sy->done_counter, sizeof(int)));
-  MB_CUDA_OK(ctx, cudaMemset(sy->done_counter, 0, sizeof(int)));
+  MB_CUDA_OK(ctx, cudaMalloc(&sy->done_counter, 2 * sizeof(int)));
+  MB_CUDA_OK(ctx, cudaMemset(sy->done_counter, 0, 2 * sizeof(int)));
   cudaIpcMemHandle_t h;
   MB_CUDA_OK(ctx, cudaIpcGetMemHandle(&h, sy->local));
   memcpy(handle_out, &h, 64);
@@ -268,13 +283,33 @@ MB_API int mb_tp_symm_attach(mb_ctx* ctx, const uint8_t* handles, int rank, int 
   mb_symm* sy = ctx->symm;
   MB_REQUIRE(ctx, sy->n % size_t(world) == 0 && (sy->n / world) % 32 == 0, "tp_symm_attach: n / world must be a multiple of 32");
   MB_CUDA_OK(ctx, cudaSetDevice(ctx->device));
-  sy->world = world; sy->rank = rank;
+  sy->world = world; sy->rank = rank; sy->ipc = true;
   for (int r = 0; r < world; ++r) {
     if (r == rank) { sy->peer[r] = sy->local; continue; }
     cudaIpcMemHandle_t h;
     memcpy(&h, handles + 64 * r, 64);
     MB_CUDA_OK(ctx, cudaIpcOpenMemHandle(&sy->peer[r], h, cudaIpcMemLazyEnablePeerAccess));
   }
+  MB_CUDA_OK(ctx, cudaMemcpy(sy->peer_dev, sy->peer, 8 * sizeof(void*), cudaMemcpyHostToDevice));
+  return MB_OK;
+}
+
+MB_API int mb_tp_symm_local(mb_ctx* ctx, void** local_out) {
+  MB_REQUIRE(ctx, ctx && ctx->symm && local_out, "tp_symm_local: create the exchange memory first");
+  *local_out = ctx->symm->local;
+  return MB_OK;
+}
+
+MB_API int mb_tp_symm_attach_ptrs(mb_ctx* ctx, void* const* peers, int rank, int world) {
+  MB_REQUIRE(ctx, ctx && ctx->symm && peers, "tp_symm_attach_ptrs: create the exchange memory first");
+  MB_REQUIRE(ctx, world >= 1 && world <= 8 && rank >= 0 && rank < world, "tp_symm_attach_ptrs: rank %d of %d", rank, world);
+  mb_symm* sy = ctx->symm;
+  MB_REQUIRE(ctx, sy->n % size_t(world) == 0 && (sy->n / world) % 32 == 0, "tp_symm_attach_ptrs: n / world must be a multiple of 32");
+  for (int r = 0; r < world; ++r)
+    MB_REQUIRE(ctx, r == rank || (peers[r] != nullptr && mb_aligned(peers[r], 256)), "tp_symm_attach_ptrs: peer %d is null or unaligned", r);
+  MB_CUDA_OK(ctx, cudaSetDevice(ctx->device));
+  sy->world = world; sy->rank = rank; sy->ipc = false;
+  for (int r = 0; r < world; ++r) sy->peer[r] = r == rank ? sy->local : peers[r];
   MB_CUDA_OK(ctx, cudaMemcpy(sy->peer_dev, sy->peer, 8 * sizeof(void*), cudaMemcpyHostToDevice));
   return MB_OK;
 }
@@ -289,7 +324,8 @@ MB_API int mb_tp_reduce_residual(mb_ctx* ctx, mb_stream stream_, const void* res
   MB_REQUIRE(ctx, mb_aligned(resid_bf16, 16), "tp_reduce_residual: 16-byte alignment");
   ReduceParams p;
   p.peer = sy->peer_dev; p.resid = static_cast<const __nv_bfloat16*>(resid_bf16); p.done_counter = sy->done_counter;
-  p.flag_timeout = ctx->flags_dev + MB_FLAG_WAIT_TIMEOUT;
+  p.flags = ctx->flags_dev;
+  p.wait_ns = uint64_t(ctx->wait_limit_us) * 1000ull;
   p.t = uint32_t(t); p.n = uint32_t(n); p.nw = uint32_t(n / sy->world); p.t_max = uint32_t(sy->t_max);
   p.world = uint32_t(sy->world); p.rank = uint32_t(sy->rank); p.step = step;
   const size_t total = t * (p.nw / 8);
@@ -306,7 +342,7 @@ MB_API int mb_tp_symm_destroy(mb_ctx* ctx) {
   mb_symm* sy = ctx->symm;
   cudaDeviceSynchronize();
   for (int r = 0; r < sy->world; ++r)
-    if (r != sy->rank && sy->peer[r]) cudaIpcCloseMemHandle(sy->peer[r]);
+    if (sy->ipc && r != sy->rank && sy->peer[r]) cudaIpcCloseMemHandle(sy->peer[r]);
   cudaFree(sy->local);
   cudaFree(sy->peer_dev);
   cudaFree(sy->done_counter);

@@ -284,18 +284,9 @@ class DecoderLayer:
                                                 _p(codes), _p(sf)))
         return out, (codes, sf, rows)
 
-    def _partial(self, x, w):
-        """This rank's f32 share of a row-parallel projection, all-reduced when the layer is split."""
-        partial = self._linear(x, w, out_dtype=torch.float32)
-        if self.group is not None and self.tp.is_split():
-            self.group.all_reduce_f32(partial)
-        return partial
-
-    def _forward_fused(self, x, batch, past, k_cache, v_cache, out=None, after_rope=None, before_rope=None):
-        """The same layer in fewer passes: norm + quantize in one kernel, q|k|v as one product,
-        rotation + cache append in one kernel, gate/up + SwiGLU + quantize in one product, the
-        residual add folded into the next norm. Every value is computed by the arithmetic of the
-        separate kernels. `before_rope` / `after_rope` are hooks of the chunked prompt path."""
+    def _attention(self, x, batch, past, k_cache, v_cache, after_rope=None, before_rope=None):
+        """Input norm + quantizer, q|k|v as one product, rotation + cache append, attention of this rank's
+        heads: [batch * t, local_heads * D] bf16."""
         cfg = self.cfg
         D = cfg.head_dim
         t = x.shape[0] // batch
@@ -311,27 +302,57 @@ class DecoderLayer:
                                      past, _p(self.inv_freq), _p(q), _p(k_cache), _p(v_cache), k_cache.shape[1]))
         if after_rope is not None:
             after_rope()
-        keys = past + t
-        a = flash_attention(q, k_cache[:, :keys].contiguous() if keys != k_cache.shape[1] else k_cache,
-                            v_cache[:, :keys].contiguous() if keys != v_cache.shape[1] else v_cache,
-                            q0=past, scale=1.0 / math.sqrt(D), causal=True).view(batch * t, self.local_heads * D)
-        if self.fused is not None and batch * t <= self.fused.t_max:
-            residual = self._reduced_residual(x, a, self.wo)
-            _, nq_ = self._norm_quantize(residual, None, self.post_gain)
-        else:
-            residual, nq_ = self._norm_quantize(x, self._partial(a, self.wo), self.post_gain)
+        # a cache allocated longer than its live keys is read in place (one key run of past + t live rows)
+        return flash_attention(q, k_cache, v_cache, q0=past, scale=1.0 / math.sqrt(D), causal=True,
+                               keys=past + t).view(batch * t, self.local_heads * D)
+
+    def half_attention(self, x, batch, past, k_cache, v_cache, after_rope=None, before_rope=None):
+        """The attention half up to the exchange step: this rank's f32 share of the o projection, [rows, hidden].
+        The shares of all ranks sum to the whole projection (src/models/inkling/session.rs:2713-2717)."""
+        a = self._attention(x, batch, past, k_cache, v_cache, after_rope, before_rope)
+        return self._linear(a, self.wo, out_dtype=torch.float32)
+
+    def half_mlp(self, x, o_sum):
+        """The MLP half between the two exchange steps: given the layer input and the SUMMED o partial, the new
+        residual bf16(x + bf16(o_sum)) and this rank's f32 share of the down projection
+        (src/models/inkling/session.rs:2843-2846)."""
+        residual, nq_ = self._norm_quantize(x, o_sum, self.post_gain)
         act = nv.gemm_w4a4_stacked(nq_[0], nq_[1], self.wgu, nq_[2],
                                    epilogue=_lib.EPI_SWIGLU_ROUNDED | _lib.EPI_QUANT_SCALED)
-        if self.fused is not None and batch * t <= self.fused.t_max:
-            y = self.fused.gemm_reduce_residual(act[0], act[1], self.wdown, residual, batch * t)
+        return residual, self._project((act[0], act[1], x.shape[0]), self.wdown, out_dtype=torch.float32)
+
+    @staticmethod
+    def finish(residual, down_sum, out=None):
+        """bf16(residual + bf16(down_sum)): the layer's output from the SUMMED down partial."""
+        return add_f32(residual, down_sum, out=out)
+
+    def _all_reduce(self, partial):
+        if self.group is not None and self.tp.is_split():
+            self.group.all_reduce_f32(partial)
+        return partial
+
+    def _forward_fused(self, x, batch, past, k_cache, v_cache, out=None, after_rope=None, before_rope=None):
+        """The same layer in fewer passes: norm + quantize in one kernel, q|k|v as one product,
+        rotation + cache append in one kernel, gate/up + SwiGLU + quantize in one product, the
+        residual add folded into the next norm. Every value is computed by the arithmetic of the
+        separate kernels. `before_rope` / `after_rope` are hooks of the chunked prompt path."""
+        rows = x.shape[0]
+        if self.fused is not None and rows <= self.fused.t_max:
+            # peer-memory exchange: the row-parallel products scatter their partial tiles, one kernel per
+            # exchange reduces, adds the residual and gathers
+            a = self._attention(x, batch, past, k_cache, v_cache, after_rope, before_rope)
+            residual = self._reduced_residual(x, a, self.wo)
+            _, nq_ = self._norm_quantize(residual, None, self.post_gain)
+            act = nv.gemm_w4a4_stacked(nq_[0], nq_[1], self.wgu, nq_[2],
+                                       epilogue=_lib.EPI_SWIGLU_ROUNDED | _lib.EPI_QUANT_SCALED)
+            y = self.fused.gemm_reduce_residual(act[0], act[1], self.wdown, residual, rows)
             if out is not None:
                 out.copy_(y)
                 return out
             return y
-        partial = self._project((act[0], act[1], batch * t), self.wdown, out_dtype=torch.float32)
-        if self.group is not None and self.tp.is_split():
-            self.group.all_reduce_f32(partial)
-        return add_f32(residual, partial, out=out)
+        o_sum = self._all_reduce(self.half_attention(x, batch, past, k_cache, v_cache, after_rope, before_rope))
+        residual, down = self.half_mlp(x, o_sum)
+        return self.finish(residual, self._all_reduce(down), out=out)
 
     # rows per chunk of the pipelined prompt path, and the SMs left to the all-reduce that runs beside the products
     PROMPT_CHUNK = 2048
@@ -401,11 +422,8 @@ class DecoderLayer:
             k = torch.stack([rope(ks[b], t, self.local_kv_heads, D, past, self.inv_freq) for b in range(batch)])
         k_cache[:, past:past + t].copy_(k.view(batch, t, self.local_kv_heads, D))
         v_cache[:, past:past + t].copy_(v.view(batch, t, self.local_kv_heads, D))
-        keys = past + t
-        a = flash_attention(q.view(batch, t, self.local_heads, D), k_cache[:, :keys].contiguous()
-                            if keys != k_cache.shape[1] else k_cache,
-                            v_cache[:, :keys].contiguous() if keys != v_cache.shape[1] else v_cache,
-                            q0=past, scale=1.0 / math.sqrt(D), causal=True)
+        a = flash_attention(q.view(batch, t, self.local_heads, D), k_cache, v_cache, q0=past,
+                            scale=1.0 / math.sqrt(D), causal=True, keys=past + t)
         residual = self._reduced_residual(x, a.view(batch * t, self.local_heads * D), self.wo)
         nq_ = self._quantize(rmsnorm(residual, self.post_gain, cfg.eps))
         gate = self._project(nq_, self.wgate)

@@ -174,9 +174,9 @@ def moe_experts(x, idx, weight, w13, w2, fuse_swiglu=True, fuse_quant=True):
     if fuse_swiglu:
         act = grouped_gemm(a_codes, a_sf, w13, plan, epilogue=_lib.EPI_SWIGLU_INTERLEAVED)
     else:
-        both = grouped_gemm(a_codes, a_sf, w13, plan)
-        g, u = both[:, 0::2].float(), both[:, 1::2].float()
-        act = ((g / (1.0 + torch.exp(-g))) * u).to(torch.bfloat16)
+        # the reference's own order: the fused gate/up product stored, then gate_up_silu as a pass of its own
+        from .inkling import gate_up_silu
+        act = gate_up_silu(grouped_gemm(a_codes, a_sf, w13, plan), inter)
     c2, sf2, _ = nv.quantize_act(act, _lib.QUANT_RECIP, tiled=True)
     y = grouped_gemm(c2, sf2, w2, plan, skip_pad_rows=True)
     return scatter_weighted(y, plan, h), plan

@@ -219,6 +219,18 @@ def bf16_gemm(a, b, out_dtype=torch.float32, out=None, alpha=1.0):
     return out
 
 
+def w4a16_gemm(x, codes, scales, scale2, n, k, out_dtype=torch.bfloat16):
+    """The W4A16 prompt product (src/nn/nvfp4_gemm.rs:93-197): x [m, k] bf16 against resident NVFP4 planes
+    (row-major scales); the weight is decoded between shared memory and the tensor core, never into HBM."""
+    assert x.dtype == torch.bfloat16 and x.is_contiguous() and x.dim() == 2 and x.shape[1] == k
+    ctx = context(x.device.index)
+    m = x.shape[0]
+    out = torch.empty((m, n), dtype=out_dtype, device=x.device)
+    ctx.check(lib.mb_nvfp4_gemm_w4a16(ctx.handle, _stream(), _p(x), _p(codes), _p(scales), float(scale2), m, n, k, _p(out),
+                                      _lib.DT_BF16 if out_dtype == torch.bfloat16 else _lib.DT_F32))
+    return out
+
+
 class Nvfp4:
     """A resident NVFP4 weight [n, k]: row-major code and scale planes (the
     canonical payload layout) plus the tiled scale plane the tensor-core GEMM reads."""
@@ -371,10 +383,12 @@ class Nvfp4:
         return out.view(1, t, self._n)
 
     def _w4a16(self, x2, t):
-        # The weight stays four bits at rest; code x block scale is decoded to bf16
-        # (exact: at most six significant bits) into a scratch plane, multiplied by the
-        # bf16 tensor-core GEMM with f32 accumulation, and scale2 is applied once to
-        # the accumulator, as in the reference's W4A16 kernel.
+        # The weight stays four bits in HBM: code x block scale is expanded to bf16 (exact) between shared
+        # memory and the tensor core, f32 accumulation, scale2 applied once to the accumulator, as in the
+        # reference's W4A16 kernel. k % 64 != 0 (the reference's W4A16 takes k % 32) goes through a decoded
+        # scratch plane and the bf16 product instead.
+        if self._k % KTILE4 == 0 and x2.data_ptr() % 16 == 0:
+            return w4a16_gemm(x2, self.codes, self.scales, self.scale2, self._n, self._k, out_dtype=self._dtype)
         w = dequantize(self.codes, self.scales, 1.0, self._n, self._k, dtype=torch.bfloat16)
         return bf16_gemm(x2, w, out_dtype=self._dtype, alpha=self.scale2)
 

@@ -425,6 +425,29 @@ ORC_API void orc_linear_w4a4(const uint8_t* a_codes, const uint8_t* a_scales, co
   }
 }
 
+// Decode-time grouped experts (src/nn/nvfp4_gemm.rs:293-313, 320-432, 462-523): group g's row (the shared row
+// when x_per_group == 0) is quantized with input_scale[ids[g]] as the second-level scale and multiplied with
+// expert ids[g] of the bank, epilogue alpha[ids[g]]: "per group exactly project_w4a4_scaled on one row".
+// x bf16 bits; bank planes [experts, n, k/2], [experts, n, k/16]. out f32 [groups, n] (the caller rounds to bf16);
+// a_codes / a_scales (may be null) receive the activation planes.
+ORC_API void orc_w4a4_grouped(const uint16_t* x, int x_per_group, const uint32_t* ids, size_t groups,
+                              const float* input_scale, const float* alpha, const uint8_t* bank_codes,
+                              const uint8_t* bank_scales, size_t n, size_t k, uint8_t* a_codes, uint8_t* a_scales,
+                              float* out) {
+  std::vector<float> row(k);
+  std::vector<uint8_t> c(k / 2), sc(k / 16);
+  for (size_t g = 0; g < groups; ++g) {
+    const uint16_t* xr = x + (x_per_group ? g * k : 0);
+    for (size_t i = 0; i < k; ++i) row[i] = bf16_to_f32(xr[i]);
+    const size_t e = ids[g];
+    orc_quantize_act_scaled(row.data(), 1, k, input_scale[e], c.data(), sc.data());
+    if (a_codes) std::memcpy(a_codes + g * k / 2, c.data(), k / 2);
+    if (a_scales) std::memcpy(a_scales + g * k / 16, sc.data(), k / 16);
+    orc_linear_w4a4(c.data(), sc.data(), bank_codes + e * n * k / 2, bank_scales + e * n * k / 16, nullptr, alpha[e], 1,
+                    n, k, out + g * n);
+  }
+}
+
 // BF16 x BF16 -> f32 (src/models/inkling/bf16gemm.rs:64-152): f64 accumulation of
 // the identical bf16 operands. Parity unpinned in the reference (no numeric pin).
 ORC_API void orc_linear_bf16(const uint16_t* x, const uint16_t* w, size_t M, size_t N, size_t K, float* out) {
@@ -823,6 +846,34 @@ ORC_API void orc_rmsnorm_breeze(const uint16_t* x, const uint16_t* w, size_t row
       float value = bf16_to_f32(x[r * width + j]) * inv;
       float normalized = round_bf16(value);
       y[r * width + j] = f32_to_bf16(normalized * bf16_to_f32(w[j]));
+    }
+  }
+}
+
+// src/models/inkling/resid.rs:272-322 (`rms_norm_kernel`), the Inkling convention: every element widened to f32,
+// `units` = min(256, next power of two of h) partial sums (unit u adds elements u, u + units, ... in turn), a
+// halving tree over the partials, denom = sqrt(red[0] / h + eps), out = O(v / denom * gain[j]) with an f32 gain:
+// one rounding. The reference's kernel source reaches the GPU through a run-time compiler that contracts
+// `acc += v * v` into a fused multiply-add, stated here explicitly (this file is built with contraction off).
+// x: bf16 bits (x_bf16) or f32 (x_f32), exactly one non-null; out_bf16 or out_f32 likewise.
+ORC_API void orc_rmsnorm_inkling(const uint16_t* x_bf16, const float* x_f32, const float* gain, size_t rows, size_t h,
+                                 float eps, uint16_t* out_bf16, float* out_f32) {
+  size_t units = 1;
+  while (units < h && units < 256) units *= 2;
+  std::vector<float> v(h), red(units);
+  for (size_t r = 0; r < rows; ++r) {
+    for (size_t j = 0; j < h; ++j) v[j] = x_bf16 ? bf16_to_f32(x_bf16[r * h + j]) : x_f32[r * h + j];
+    for (size_t u = 0; u < units; ++u) {
+      float acc = 0.0f;
+      for (size_t i = u; i < h; i += units) acc = std::fmaf(v[i], v[i], acc);
+      red[u] = acc;
+    }
+    for (size_t step = units / 2; step > 0; step /= 2)
+      for (size_t u = 0; u < step; ++u) red[u] += red[u + step];
+    const float denom = std::sqrt(red[0] / float(h) + eps);
+    for (size_t j = 0; j < h; ++j) {
+      const float o = v[j] / denom * gain[j];
+      if (out_bf16) out_bf16[r * h + j] = f32_to_bf16(o); else out_f32[r * h + j] = o;
     }
   }
 }

@@ -15,3 +15,18 @@ def pytest_configure(config):
 def orc():
     from oracle_lib import oracle
     return oracle()
+
+
+@pytest.fixture(scope="session")
+def figures():
+    """record(name, **numbers): appends one JSON line per measured parity figure to the file named by
+    MB_FIGURES_FILE (nothing is written when the variable is unset). The figures quoted in the design notes
+    come from such a file."""
+    import json
+    path = os.environ.get("MB_FIGURES_FILE")
+
+    def record(name, **numbers):
+        if path:
+            with open(path, "a") as f:
+                f.write(json.dumps({"name": name, **{k: float(v) for k, v in numbers.items()}}) + "\n")
+    return record

@@ -54,6 +54,9 @@ class Oracle:
             "orc_linear_w4a16": (None, [P(u16), P(u8), P(u8), f32, sz, sz, sz, P(f64)]),
             "orc_linear_cpu_lane": (None, [P(u16), P(f32), sz, sz, sz, P(u16)]),
             "orc_linear_w4a4": (None, [P(u8), P(u8), P(u8), P(u8), P(f32), f32, sz, sz, sz, P(f32)]),
+            "orc_w4a4_grouped": (None, [P(u16), C.c_int, P(u32), sz, P(f32), P(f32), P(u8), P(u8), sz, sz, P(u8), P(u8),
+                                        P(f32)]),
+            "orc_rmsnorm_inkling": (None, [P(u16), P(f32), P(f32), sz, sz, f32, P(u16), P(f32)]),
             "orc_linear_bf16": (None, [P(u16), P(u16), sz, sz, sz, P(f32)]),
             "orc_e4m3_from_pow2": (C.c_int, [C.c_int]),
             "orc_mxfp4_transcode": (C.c_int, [P(u8), sz, P(u8), P(C.c_longlong)]),
@@ -211,6 +214,37 @@ class Oracle:
                                  _ptr(b_scales, C.c_uint8), rs, float(np.float32(alpha)), M, N, K,
                                  _ptr(out, C.c_float))
         return out.reshape(M, N)
+
+    def w4a4_grouped(self, x_bits, x_per_group, ids, input_scale, alpha, bank_codes, bank_scales, n, k):
+        """w4a4_grouped_bf16 (src/nn/nvfp4_gemm.rs:462-523) -> (out f32 [groups, n], activation codes, scales)."""
+        x_bits = np.ascontiguousarray(x_bits, np.uint16).reshape(-1)
+        ids = np.ascontiguousarray(ids, np.uint32)
+        input_scale = np.ascontiguousarray(input_scale, np.float32)
+        alpha = np.ascontiguousarray(alpha, np.float32)
+        bank_codes = np.ascontiguousarray(bank_codes, np.uint8).reshape(-1)
+        bank_scales = np.ascontiguousarray(bank_scales, np.uint8).reshape(-1)
+        groups = ids.size
+        out = np.empty((groups, n), np.float32)
+        a_codes = np.empty((groups, k // 2), np.uint8)
+        a_scales = np.empty((groups, k // 16), np.uint8)
+        self.lib.orc_w4a4_grouped(_ptr(x_bits, C.c_uint16), int(x_per_group), _ptr(ids, C.c_uint32), groups,
+                                  _ptr(input_scale, C.c_float), _ptr(alpha, C.c_float), _ptr(bank_codes, C.c_uint8),
+                                  _ptr(bank_scales, C.c_uint8), n, k, _ptr(a_codes, C.c_uint8),
+                                  _ptr(a_scales, C.c_uint8), _ptr(out, C.c_float))
+        return out, a_codes, a_scales
+
+    def rmsnorm_inkling(self, x, gain, rows, width, eps, out_bf16=True):
+        """rms_norm_kernel (src/models/inkling/resid.rs:272-322). x: uint16 array = bf16 bits, float32 array = f32."""
+        gain = np.ascontiguousarray(gain, np.float32)
+        x = np.ascontiguousarray(x)
+        xb = _ptr(x, C.c_uint16) if x.dtype == np.uint16 else None
+        xf = _ptr(x, C.c_float) if x.dtype == np.float32 else None
+        assert (xb is None) != (xf is None)
+        out = np.empty(rows * width, np.uint16 if out_bf16 else np.float32)
+        self.lib.orc_rmsnorm_inkling(xb, xf, _ptr(gain, C.c_float), rows, width, float(np.float32(eps)),
+                                     _ptr(out, C.c_uint16) if out_bf16 else None,
+                                     None if out_bf16 else _ptr(out, C.c_float))
+        return out.reshape(rows, width)
 
     def linear_bf16(self, x_bits, w_bits, M, N, K):
         x_bits = np.ascontiguousarray(x_bits, np.uint16).reshape(-1)

@@ -32,7 +32,11 @@ def test_router_indices_bit_exact(moe, orc, tokens, n_experts, k):
     # weights: f32 arithmetic of identical scores; the reference's own stage gate allows 1e-6
     # (src/bin/k3_router_gate.rs:60-95)
     assert np.abs(w.cpu().numpy() - w_ref).max() <= 1e-6
-    assert np.array_equal(w.cpu().numpy().view(np.uint32), w_ref.view(np.uint32)) or tokens > 0
+    # without the renormalising divide the weights are the gathered scores themselves: the oracle's bits
+    idx_u, w_u = moe.router_topk_softmax(torch.from_numpy(logits).cuda(), k, renormalize=False)
+    _, w_u_ref = orc.router_select(scores, k, renormalize=False)
+    assert np.array_equal(idx_u.cpu().numpy().astype(np.uint32), idx_ref)
+    assert np.array_equal(w_u.cpu().numpy().view(np.uint32), w_u_ref.view(np.uint32))
 
 
 @pytest.mark.parametrize("activation", ["sigmoid", "softmax"])
@@ -240,6 +244,124 @@ def test_moe_experts_against_oracle(moe, orc, tokens, h, inter, n_experts, k):
     out_stored, _ = moe.moe_experts(x, torch.from_numpy(idx).cuda(), torch.from_numpy(wgt).cuda(), b13, b2,
                                     fuse_quant=False)
     assert torch.equal(out_stored, out)
+
+
+@pytest.mark.parametrize("tokens,h,inter,n_experts,k", [(300, 512, 256, 16, 4), (256, 2048, 768, 128, 8)])
+def test_moe_experts_stage_by_stage(moe, orc, figures, tokens, h, inter, n_experts, k):
+    """The expert lane checked the way the reference's own gates do it (src/bin/k3_router_gate.rs:60-95 stage by
+    stage, src/bin/fp4quant_gate.rs:12-24 counting near-ties): every stage is fed the GPU's OWN previous output, so
+    identical inputs must give identical bytes where the arithmetic is integer (quantizers, scatter order) and
+    agree within the same-operand gate where it is a sum (products). The end-to-end comparison then COUNTS the
+    rows whose second-stage codes flipped against the all-CPU chain; tokens without a flipped row must meet the
+    1e-2 bound, the others are bounded by what a flipped E2M1 code can move."""
+    from maryml_b200 import _lib, nvfp4 as nv
+    xbits = f32_to_bf16_bits(orc.normal_f32(1, tokens * h, 1.0)).reshape(tokens, h)
+    rng = np.random.default_rng(tokens)
+    idx = np.stack([rng.permutation(n_experts)[:k] for _ in range(tokens)]).astype(np.int32)
+    wgt = rng.random((tokens, k), dtype=np.float32)
+    wgt /= wgt.sum(1, keepdims=True)
+    b13 = moe.ExpertBank.quantize(dev_bf16(_bank(orc, 2, n_experts, 2 * inter, h)).view(n_experts, 2 * inter, h))
+    b2 = moe.ExpertBank.quantize(dev_bf16(_bank(orc, 3, n_experts, h, inter)).view(n_experts, h, inter))
+    c13, s13, g13 = b13.codes.cpu().numpy(), b13.scales.cpu().numpy(), b13.scale2.cpu().numpy()
+    c2w, s2w, g2 = b2.codes.cpu().numpy(), b2.scales.cpu().numpy(), b2.scale2.cpu().numpy()
+    x = dev_bf16(xbits).view(tokens, h)
+    plan = moe.RowPlan(torch.from_numpy(idx).cuda(), torch.from_numpy(wgt).cuda(), n_experts)
+    row_tok = plan.row_tok.cpu().numpy()
+    m_cap = plan.m_cap
+    live = row_tok >= 0
+    e_rows, e_row0 = plan.expert_rows.cpu().numpy(), plan.expert_row0.cpu().numpy()
+
+    # stage 1: token planes, bit-exact; gathered into plan order
+    t_codes, t_sf, _ = nv.quantize_act(x, _lib.QUANT_RECIP, tiled=True)
+    tc_ref, ts_ref = orc.quantize_act_recip(bf16_bits_to_f32(xbits), tokens, h)
+    assert np.array_equal(t_codes.cpu().numpy().ravel(), tc_ref)
+    assert np.array_equal(nv.untile_scales(t_sf, tokens, h).cpu().numpy().ravel(), ts_ref)
+    a_codes, a_sf = nv.gather_rows(t_codes, t_sf, tokens, h, plan.row_tok)
+    a_c = a_codes.cpu().numpy()
+    a_s = nv.untile_scales(a_sf, m_cap, h).cpu().numpy()
+    assert np.array_equal(a_c[live], tc_ref.reshape(tokens, h // 2)[row_tok[live]])
+
+    def per_expert(codes_rows, scales_rows, wc, ws, wg, n, kk):
+        out = np.zeros((m_cap, n), np.float32)
+        for e in range(n_experts):
+            r0, cnt = int(e_row0[e]), int(e_rows[e])
+            if cnt:
+                out[r0:r0 + cnt] = orc.linear_w4a4(codes_rows[r0:r0 + cnt].ravel(), scales_rows[r0:r0 + cnt].ravel(),
+                                                   wc[e].ravel(), ws[e].ravel(), np.float32(wg[e]), cnt, n, kk)
+        return out
+
+    # stage 2: first grouped product, f32 out, against f64 sums of the SAME operands (reference gate: 1e-4)
+    both32 = moe.grouped_gemm(a_codes, a_sf, b13, plan, out_dtype=torch.float32).cpu().numpy()
+    both_ref = per_expert(a_c, a_s, c13, s13, g13, 2 * inter, h)
+    e2 = np.abs(both32[live] - both_ref[live]).max() / np.abs(both_ref[live]).max()
+    assert e2 <= 1e-4, e2
+
+    # stage 3: SwiGLU on the GPU's own product. The fused epilogue rounds gate and up to bf16, then silu * up in
+    # f32 with the fast exponential, then bf16: against the CPU form on the same bf16 gate/up a few results land
+    # on the neighbouring bf16 value; they are counted.
+    act = moe.grouped_gemm(a_codes, a_sf, b13, plan, epilogue=_lib.EPI_SWIGLU_INTERLEAVED)
+    act_bits = host_bits(act).reshape(m_cap, inter)
+    act_ref = f32_to_bf16_bits(orc.gate_up_silu(bf16_bits_to_f32(f32_to_bf16_bits(both32)), m_cap, inter, round_bf16=True))
+    act_ref = act_ref.reshape(m_cap, inter)
+    moved = (act_bits[live] != act_ref[live])
+    step = np.abs(bf16_bits_to_f32(act_bits[live]) - bf16_bits_to_f32(act_ref[live]))
+    assert moved.mean() <= 5e-3 and (step <= 2.0 ** -7 * np.abs(bf16_bits_to_f32(act_ref[live])) + 1e-30).all()
+
+    # stage 3b: the second projection's quantizer on the GPU's own activations: identical input, identical bytes
+    q_c, q_sf, _ = nv.quantize_act(act, _lib.QUANT_RECIP, tiled=True)
+    qc_ref, qs_ref = orc.quantize_act_recip(bf16_bits_to_f32(act_bits), m_cap, inter)
+    q_cn, q_sn = q_c.cpu().numpy(), nv.untile_scales(q_sf, m_cap, inter).cpu().numpy()
+    assert np.array_equal(q_cn[live], qc_ref.reshape(m_cap, -1)[live])
+    assert np.array_equal(q_sn[live], qs_ref.reshape(m_cap, -1)[live])
+    # and the epilogue that quantizes where it produces writes those bytes
+    f_c, f_sf = moe.grouped_gemm(a_codes, a_sf, b13, plan, epilogue=_lib.EPI_SWIGLU_INTERLEAVED | _lib.EPI_QUANT_RECIP)
+    assert np.array_equal(f_c.cpu().numpy()[live], q_cn[live])
+    assert np.array_equal(nv.untile_scales(f_sf, m_cap, inter).cpu().numpy()[live], q_sn[live])
+
+    # stage 4: second grouped product from the GPU's codes
+    y32 = moe.grouped_gemm(q_c, q_sf, b2, plan, out_dtype=torch.float32).cpu().numpy()
+    y_ref = per_expert(q_cn, q_sn, c2w, s2w, g2, h, inter)
+    e4 = np.abs(y32[live] - y_ref[live]).max() / np.abs(y_ref[live]).max()
+    assert e4 <= 1e-4, e4
+
+    # stage 5: ordered weighted sum of the GPU's own bf16 rows: the fma chain in ascending row order, bit for bit
+    y16 = moe.grouped_gemm(q_c, q_sf, b2, plan, skip_pad_rows=True)
+    out = moe.scatter_weighted(y16, plan, h).cpu().numpy()
+    yf = bf16_bits_to_f32(host_bits(y16)).reshape(m_cap, h)
+    yf[~live] = 0.0
+    tok_rows = plan.tok_rows.cpu().numpy().astype(np.uint32)
+    out_ref = orc.scatter_weighted(yf, plan.row_wgt.cpu().numpy(), tok_rows, np.full(tokens, k, np.uint32), h)
+    assert np.array_equal(out.view(np.uint32), out_ref.view(np.uint32))
+
+    # end to end against the all-CPU chain, with the flipped rows counted
+    both_cpu = bf16_bits_to_f32(f32_to_bf16_bits(both_ref))
+    act_cpu = orc.gate_up_silu(both_cpu, m_cap, inter, round_bf16=True)
+    qc_cpu, qs_cpu = orc.quantize_act_recip(act_cpu, m_cap, inter)
+    flipped_rows = live & ((q_cn != qc_cpu.reshape(m_cap, -1)).any(1) | (q_sn != qs_cpu.reshape(m_cap, -1)).any(1))
+    flipped_codes = int((((q_cn ^ qc_cpu.reshape(m_cap, -1)) & 0x0F) != 0)[live].sum() +
+                        (((q_cn ^ qc_cpu.reshape(m_cap, -1)) & 0xF0) != 0)[live].sum())
+    touched = np.zeros(tokens, bool)
+    touched[row_tok[flipped_rows]] = True
+    final, _ = moe.moe_experts(x, torch.from_numpy(idx).cuda(), torch.from_numpy(wgt).cuda(), b13, b2)
+    ref = orc.moe_experts(xbits, idx.astype(np.uint32), wgt, (c13.ravel(), s13.ravel(), g13), (c2w.ravel(), s2w.ravel(), g2),
+                          h, inter, n_experts)
+    got = final.cpu().numpy()
+    # relative to the larger of the element and the output's rms: the second product's rows are stored as bf16, and
+    # where the GPU's and the CPU's f32 sums straddle a bf16 rounding boundary a row value moves by 2^-8 of itself,
+    # an absolute error no element far below the rms can absorb
+    rms = np.sqrt(np.mean(ref.astype(np.float64) ** 2))
+    rel = np.abs(got - ref) / np.maximum(np.abs(ref), rms)
+    clean = rel[~touched].max() if (~touched).any() else 0.0
+    dirty = (np.abs(got - ref)[touched].max() / rms) if touched.any() else 0.0
+    figures("moe_stagewise", tokens=tokens, experts=n_experts, gemm1_rel=e2, gemm2_rel=e4, swiglu_moved=moved.mean(),
+            flipped_codes=flipped_codes, codes=int(live.sum()) * inter, tokens_touched=int(touched.sum()),
+            clean_max_rel=clean, touched_max_over_rms=dirty)
+    print(f"moe stage-wise: {flipped_codes} of {int(live.sum()) * inter} second-stage codes flipped in {int(flipped_rows.sum())} rows "
+          f"({int(touched.sum())} of {tokens} tokens); clean tokens max rel {clean:.2e}, touched tokens max |err|/rms {dirty:.2e}")
+    assert flipped_codes <= 2e-3 * int(live.sum()) * inter
+    assert clean <= 1e-2, clean
+    assert dirty <= 5e-2, dirty
+    assert rel_check(got, ref)[1] >= 0.9999
 
 
 def test_grouped_product_leaves_pad_rows_unwritten(moe, orc):

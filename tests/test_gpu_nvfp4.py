@@ -55,6 +55,19 @@ def rel_check(got, ref, max_rel=1e-2, cos_min=0.9999):
     return float(rel.max()), cos
 
 
+def attn_check(got, ref):
+    """The attention bound: every element within 1e-2 of max(|ref|, rms of the reference), cosine >= 0.9999.
+    The probabilities enter the second product as bf16 (f16 over NVFP4 rows), which puts an absolute error of
+    about 2^-9 of the output's rms on EVERY element, so an element far below the rms cannot meet a bound relative
+    to itself; relative to the larger of itself and the rms the figure is the one north_star states."""
+    got = np.asarray(got, np.float64).ravel()
+    ref = np.asarray(ref, np.float64).ravel()
+    rms = np.sqrt(np.mean(ref ** 2)) + 1e-30
+    rel = np.abs(got - ref) / np.maximum(np.abs(ref), rms)
+    cos = float(np.dot(got, ref) / (np.linalg.norm(got) * np.linalg.norm(ref) + 1e-30))
+    return float(rel.max()), cos
+
+
 # --------------------------------------------------------------------------- codec
 @pytest.mark.parametrize("n,k", [(8, 128), (64, 4096), (33, 96)])
 def test_weight_quantizer_bit_exact(mb, orc, n, k):
@@ -387,6 +400,42 @@ def test_full_size_linearity_property(mb, orc):
     y3 = mb.bf16_gemm(xa, wb, out_dtype=torch.float32, alpha=q.scale2)
     err = (y1 - y3).abs().max().item()
     assert err <= 1e-4 * y3.abs().max().item() + 1e-6
+
+
+@pytest.mark.parametrize("k,n", [(4096, 4096), (4096, 14336), (14336, 4096)])
+def test_config1_full_shapes_against_the_oracle_at_128_rows(mb, orc, figures, k, n):
+    """The three projection shapes of the sweep at their full (K, N), 128 activation rows: quantizer bytes and
+    the three lanes (W4A4, W4A4 per-row scale, W4A16) compared directly with the CPU restatement."""
+    m = 128
+    wb = f32_to_bf16_bits(orc.normal_f32(2, n * k, 0.02))
+    xb = f32_to_bf16_bits(orc.normal_f32(1, m * k, 1.0))
+    q = mb.Nvfp4.quantize(dev_bf16(wb).view(n, k))
+    codes, scales = q.read_planes()
+    c_ref, s_ref, g_ref = orc.quantize_weight_bf16(wb, n, k)
+    assert np.array_equal(codes, c_ref) and np.array_equal(scales, s_ref) and np.float32(q.scale2) == g_ref
+    x = dev_bf16(xb).view(1, m, k)
+    xf = bf16_bits_to_f32(xb)
+    # W4A4, unit input scale: against f64 sums of the SAME quantized operands (reference gate 1e-4 on f32 output)
+    a_c, a_s = orc.quantize_act_scaled(xf, m, k, 1.0)
+    ref = orc.linear_w4a4(a_c, a_s, c_ref, s_ref, g_ref, m, n, k)
+    d_c, d_sf, _ = mb.quantize_act(x.view(m, k), tiled=True)
+    assert np.array_equal(d_c.cpu().numpy().ravel(), a_c)
+    y32 = mb.gemm_w4a4(d_c, d_sf, q.codes, q.sf_tiled(), q.scale2, m, n, k, out_dtype=torch.float32).cpu().numpy()
+    e_w4a4 = np.abs(y32 - ref).max() / np.abs(ref).max()
+    assert e_w4a4 <= 1e-4, e_w4a4
+    y = bf16_bits_to_f32(host_bits(q.project(x, mb.PromptLane.W4A4))).reshape(m, n)
+    rel, cos = rel_check(y, ref)
+    assert rel <= 1e-2 and cos >= 0.9999, (rel, cos)
+    # per-row activation scale
+    r_c, r_s, r_rs = orc.quantize_act_rows(xf, m, k)
+    ref_rows = orc.linear_w4a4(r_c, r_s, c_ref, s_ref, g_ref, m, n, k, rowscale=r_rs)
+    rel_r, cos_r = rel_check(bf16_bits_to_f32(host_bits(q.project_w4a4_rows(x))).reshape(m, n), ref_rows)
+    assert rel_r <= 1e-2 and cos_r >= 0.9999, (rel_r, cos_r)
+    # W4A16: exact weights, bf16 activations
+    ref16 = orc.linear_w4a16(xb, c_ref, s_ref, g_ref, m, n, k)
+    rel_16, cos_16 = rel_check(bf16_bits_to_f32(host_bits(q.project(x, mb.PromptLane.W4A16))).reshape(m, n), ref16)
+    assert rel_16 <= 1e-2 and cos_16 >= 0.9999, (rel_16, cos_16)
+    figures("config1_m128", k=k, n=n, w4a4_f32_rel=e_w4a4, w4a4_bf16_rel=rel, rows_rel=rel_r, w4a16_rel=rel_16)
 
 
 def test_mxfp4_relabelled_as_nvfp4_decodes_to_the_same_bits(mb, orc):
