@@ -592,25 +592,57 @@ def build_tp(env, args, decode, setup=None, fused=None):
 
 
 def tp_parity(env, setup, w):
-    """The sharded layer's output against the unsharded layer on rank 0 (the same stored planes, the same inputs).
-    Returned on rank 0; every rank runs the sharded step."""
-    torch = env.torch
+    """Parity of the sharded layer against the unsharded layer on rank 0 (same stored planes, same inputs), exchange
+    by exchange. The cut changes one thing, the association of the K sums of the two row-parallel products, so each
+    all-reduced partial is compared with the unsharded product of the SAME input bytes: `max_rel` is the larger of
+    the two relative errors (|err| / max|ref|). The layer's output through the production path (fused exchange or
+    row-sharded prompt path) against the unsharded layer end to end is reported beside it: W4A4 re-quantizes bf16
+    intermediates three times per layer, so noise in the last bf16 bit of the attention output (another key-split
+    count is enough) flips E2M1 codes downstream, and two correct evaluations of this layer sit a few percent of
+    the output's rms apart (the CPU oracle included; the design notes carry the numbers). Returned on rank 0."""
+    torch, dist = env.torch, env.dist
+    L = w["layer"]
     batch, t, past, x, kc_full, vc_full = w["parity_inputs"]
-    y = w["layer"].forward(x, batch, past, w["kc"], w["vc"]).float()
+    y_prod = L.forward(x, batch, past, w["kc"], w["vc"]).clone()
+    a = L._attention(x, batch, past, w["kc"], w["vc"])
+    o_sum = L._all_reduce(L._linear(a, L.wo, out_dtype=torch.float32))
+    residual, down = L.half_mlp(x, o_sum)
+    down_sum = L._all_reduce(down)
+    y = L.finish(residual, down_sum)
+    if env.world > 1:
+        parts = [torch.empty_like(a) for _ in range(env.world)]
+        dist.all_gather(parts, a.contiguous())
+        a_full = torch.cat(parts, 1)          # heads in rank order
+    else:
+        a_full = a
     env.barrier()
     if env.rank != 0:
         return None
     L1 = setup.reference_layer()
-    y1 = L1.forward(x, batch, past, kc_full.clone(), vc_full.clone()).float()
+    o1 = L1._linear(a_full, L1.wo, out_dtype=torch.float32)
+    res1, down1 = L1.half_mlp(x, o_sum)
+    y1 = L1.finish(res1, down1)
+    e_o = float((o_sum - o1).abs().max() / o1.abs().max())
+    e_d = float((down_sum - down1).abs().max() / down1.abs().max())
+    same_resid = bool(torch.equal(res1.view(torch.int16), residual.view(torch.int16)))
+    moved = float((y.view(torch.int16) != y1.view(torch.int16)).float().mean())
+    y_ref = L1.forward(x, batch, past, kc_full.clone(), vc_full.clone()).float()
     torch.cuda.synchronize()
-    err = (y - y1).abs()
-    rms = y1.pow(2).mean().sqrt()
-    rel = err / torch.maximum(y1.abs(), rms)
-    cos = torch.nn.functional.cosine_similarity(y.ravel().double(), y1.ravel().double(), dim=0)
+
+    def dist_of(got, ref):
+        err = (got.float() - ref).abs()
+        rms = ref.pow(2).mean().sqrt()
+        cos = torch.nn.functional.cosine_similarity(got.float().ravel().double(), ref.ravel().double(), dim=0)
+        return {"max_err_over_rms": float(err.max() / rms), "mean_err_over_rms": float(err.mean() / rms), "cosine": float(cos)}
+    out = {"max_rel": max(e_o, e_d), "o_sum_rel": e_o, "down_sum_rel": e_d, "residual_bit_equal": same_resid,
+           "output_bf16_moved": moved,
+           "vs": "1-rank layer on rank 0 fed the same bytes at each exchange; rel = max|err| / max|ref| of the all-reduced f32 partial",
+           "end_to_end": dict(dist_of(y_prod, y_ref), path=w["reduce"],
+                              note="every stage on its own previous output: re-quantized bf16 intermediates amplify last-bit "
+                                   "noise of the attention output, see the design notes"),
+           "production_vs_allreduce_bf16_moved": float((y_prod.view(torch.int16) != y.view(torch.int16)).float().mean())}
     del L1
-    return {"max_rel": float(rel.max()), "within_1e-2": float((rel <= 1e-2).double().mean()),
-            "mean_err_over_rms": float(err.mean() / rms), "cosine": float(cos),
-            "vs": "1-rank layer on rank 0, same stored planes and inputs; rel = |err| / max(|ref|, rms)"}
+    return out
 
 
 def measure_extra(env, w, steps, warmup, cpu=True, graph=False):
@@ -976,14 +1008,27 @@ def run_sweep(args, rank, world, local_rank):
                 for mode, pool in (("rotating", qs if rotating else qs[:1]), ("resident", qs[:1])):
                     if mode == "resident" and not rotating:
                         continue
-                    it = [0]
-
-                    def step():
-                        fn(pool[it[0] % len(pool)])
-                        it[0] += 1
-                    steps = max(20, min(args.steps, 200))
-                    t, _ = time_steps(env, step, steps, 3, sample_clocks=False)
-                    res[mode] = t / steps
+                    # One CUDA graph of a pass over the pool (at least eight calls), replayed: the host layer's
+                    # per-call cost (a few tens of microseconds of Python) would otherwise hide every kernel that
+                    # is shorter than that, which is all of them below a thousand rows.
+                    calls = max(8, len(pool))
+                    for q_ in pool:
+                        fn(q_)
+                    torch.cuda.synchronize()
+                    side = torch.cuda.Stream()
+                    side.wait_stream(env.stream)
+                    with torch.cuda.stream(side):
+                        fn(pool[0])
+                    env.stream.wait_stream(side)
+                    torch.cuda.synchronize()
+                    graph = torch.cuda.CUDAGraph()
+                    with torch.cuda.graph(graph):
+                        for c in range(calls):
+                            fn(pool[c % len(pool)])
+                    replays = max(3, min(args.steps, 200) // calls + 1)
+                    t, _ = time_steps(env, graph.replay, replays, 3, sample_clocks=False)
+                    res[mode] = t / (replays * calls)
+                    del graph
                 ms_ = res["rotating"]
                 flop = 2.0 * m * n * k
                 byts = (wbytes if lane != "bf16" else n * k * 2) + 2 * m * k + 2 * m * n

@@ -167,6 +167,18 @@ int mb_nvfp4_gemv_w4a16(mb_ctx* ctx, mb_stream stream, const void* x_bf16, size_
                         const uint8_t* scales_rowmajor, float scale2, size_t n, size_t k, void* out,
                         int out_dtype);
 
+/* The same GEMV with a workspace (mb_nvfp4_gemv_workspace bytes, 256-byte aligned): a pass of one block per row
+ * first makes an f16 copy of the activation rows, which is exact for zero, infinite, NaN and every value in f16's
+ * normal range (bf16 carries 8 significant bits, f16 11), and the product then runs f16 x f16 with the decoded
+ * weights left in f16: five instructions per four weights instead of eleven, the difference between an
+ * instruction-bound kernel and one that streams weights at the HBM rate. A row holding a finite value outside
+ * f16's normal range raises a flag in the workspace and the whole call takes the bf16 form above; either way
+ * every product is exact in f32. A null or short workspace is the call above. */
+size_t mb_nvfp4_gemv_workspace(size_t rows, size_t k);
+int mb_nvfp4_gemv_w4a16_ws(mb_ctx* ctx, mb_stream stream, const void* x_bf16, size_t rows, const uint8_t* codes,
+                           const uint8_t* scales_rowmajor, float scale2, size_t n, size_t k, void* out, int out_dtype,
+                           void* workspace, size_t workspace_bytes);
+
 /* Nvfp4::project(W4a4) / project_w4a4_scaled / project_w4a4_rows and fp4_linear_launch
  * (src/nn/nvfp4_gemm.rs:200-291, 644-694, 814-945; src/models/inkling/fp4gemm.rs:154-245):
  * out[m, n] = (sum_k a[m,k] b[n,k]) * alpha [* rowscale[m]], both operands NVFP4
@@ -242,12 +254,15 @@ int mb_bf16_gemm(mb_ctx* ctx, mb_stream stream, const void* a_bf16, const void* 
                  size_t n, size_t k, void* out, int out_dtype);
 /* Nvfp4::project(W4a16) / w4a16_linear_launch (src/nn/nvfp4_gemm.rs:93-197, src/models/inkling/w4a16gemm.rs):
  * [m, k] bf16 x [n, k]^T NVFP4 with the weight left four bits in HBM and no 16-bit copy of it anywhere: code
- * bytes arrive in shared memory by TMA, converter warps expand code x block scale to bf16 (exact) into the
- * tensor core's operand tile, tcgen05 kind::f16 accumulates in f32, scale2 is applied once to the accumulator,
- * one cast. codes [n, k/2], scales [n, k/16] ROW-MAJOR (the canonical planes). k % 64 == 0, n % 8 == 0. */
+ * bytes arrive in shared memory by TMA, converter warps expand code x block scale to f16 (exact) into the
+ * tensor core's operand tile, tcgen05 kind::f16 (bf16 A, f16 B) accumulates in f32, scale2 is applied once to
+ * the accumulator, one cast. codes [n, k/2], scales [n, k/16] ROW-MAJOR (the canonical planes). k % 64 == 0,
+ * n % 8 == 0. workspace: optional K-slice planes for products with few output tiles
+ * (mb_nvfp4_gemm_w4a16_workspace bytes, 0 = never split; a null or short workspace runs unsplit). */
+size_t mb_nvfp4_gemm_w4a16_workspace(size_t m, size_t n, size_t k);
 int mb_nvfp4_gemm_w4a16(mb_ctx* ctx, mb_stream stream, const void* x_bf16, const uint8_t* codes,
                         const uint8_t* scales_rowmajor, float scale2, size_t m, size_t n, size_t k, void* out,
-                        int out_dtype);
+                        int out_dtype, void* workspace, size_t workspace_bytes);
 /* The same product when the output has few tiles and K is long (the router projection
  * src/models/k3/router.rs:300-340 `Router::logits`: [tokens, hidden] x [experts, hidden]^T): K slices into f32 planes of
  * `workspace`, summed in slice order. mb_bf16_gemm_splitk_workspace gives the bytes, 0 = not split. */
@@ -477,6 +492,14 @@ int mb_tp_unique_id(mb_ctx* ctx, uint8_t id_out[128]);
 int mb_tp_form(mb_ctx* ctx, const uint8_t id[128], int rank, int world);
 int mb_tp_warm(mb_ctx* ctx, mb_stream stream);
 int mb_tp_all_reduce(mb_ctx* ctx, mb_stream stream, void* buf, size_t count, int dtype);
+/* The two halves of that all-reduce for prompt-sized activations (no counterpart in the reference, which
+ * all-reduces the whole f32 partial, src/models/inkling/tpcomm.rs:1453-1467): SUM reduce-scatter of the f32
+ * partial by rows, so each rank adds the residual, normalises and quantizes only its own rows, then an
+ * all-gather of what the next product reads (NVFP4 planes: 0.5625 bytes per element instead of 4). The sums
+ * are the all-reduce's f32 sums; only who holds which rows in between differs. send holds world x recv_count
+ * floats; mb_tp_all_gather moves raw bytes and works in place when send == recv + rank * send_bytes. */
+int mb_tp_reduce_scatter_f32(mb_ctx* ctx, mb_stream stream, const float* send, float* recv, size_t recv_count);
+int mb_tp_all_gather(mb_ctx* ctx, mb_stream stream, const void* send, void* recv, size_t send_bytes);
 int mb_tp_close(mb_ctx* ctx);
 
 /* Fused row-parallel path over peer memory: tp_reduce (src/models/inkling/tpcomm.rs:1453-1467)

@@ -50,6 +50,8 @@ SIGNATURES = {
     "mb_nvfp4_tile_scales": (_i, [_vp, _vp, _vp, _sz, _sz, _vp]),
     "mb_nvfp4_untile_scales": (_i, [_vp, _vp, _vp, _sz, _sz, _vp]),
     "mb_nvfp4_gemv_w4a16": (_i, [_vp, _vp, _vp, _sz, _vp, _vp, _f, _sz, _sz, _vp, _i]),
+    "mb_nvfp4_gemv_workspace": (_sz, [_sz, _sz]),
+    "mb_nvfp4_gemv_w4a16_ws": (_i, [_vp, _vp, _vp, _sz, _vp, _vp, _f, _sz, _sz, _vp, _i, _vp, _sz]),
     "mb_nvfp4_gemm_w4a4": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _f, _sz, _sz, _sz, _vp, _i, _i]),
     "mb_nvfp4_gemm_splitk_workspace": (_sz, [_sz, _sz, _sz]),
     "mb_nvfp4_gemm_w4a4_splitk": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _f, _sz, _sz, _sz, _vp, _i, _vp, _sz]),
@@ -59,7 +61,8 @@ SIGNATURES = {
     "mb_nvfp4_gemv_w4a4_grouped": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _sz, _sz, _sz, _sz, _vp, _i]),
     "mb_nvfp4_gemm_w4a4_stacked": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _sz, _sz, _sz, _vp, _i, _i, _vp, _vp, _sz]),
     "mb_bf16_gemm": (_i, [_vp, _vp, _vp, _vp, _f, _sz, _sz, _sz, _vp, _i]),
-    "mb_nvfp4_gemm_w4a16": (_i, [_vp, _vp, _vp, _vp, _vp, _f, _sz, _sz, _sz, _vp, _i]),
+    "mb_nvfp4_gemm_w4a16_workspace": (_sz, [_sz, _sz, _sz]),
+    "mb_nvfp4_gemm_w4a16": (_i, [_vp, _vp, _vp, _vp, _vp, _f, _sz, _sz, _sz, _vp, _i, _vp, _sz]),
     "mb_bf16_gemm_splitk_workspace": (_sz, [_sz, _sz, _sz]),
     "mb_bf16_gemm_splitk": (_i, [_vp, _vp, _vp, _vp, _f, _sz, _sz, _sz, _vp, _i, _vp, _sz]),
     "mb_router_topk_softmax": (_i, [_vp, _vp, _vp, _sz, _sz, _sz, _i, _f, _vp, _vp]),
@@ -95,6 +98,8 @@ SIGNATURES = {
     "mb_tp_form": (_i, [_vp, C.POINTER(C.c_uint8), _i, _i]),
     "mb_tp_warm": (_i, [_vp, _vp]),
     "mb_tp_all_reduce": (_i, [_vp, _vp, _vp, _sz, _i]),
+    "mb_tp_reduce_scatter_f32": (_i, [_vp, _vp, _vp, _vp, _sz]),
+    "mb_tp_all_gather": (_i, [_vp, _vp, _vp, _vp, _sz]),
     "mb_tp_close": (_i, [_vp]),
     "mb_tp_symm_bytes": (_sz, [_sz, _sz]),
     "mb_tp_symm_create": (_i, [_vp, _sz, _sz, C.POINTER(C.c_uint8)]),

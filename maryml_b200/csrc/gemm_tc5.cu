@@ -586,8 +586,10 @@ struct Gemm2Params {
 // fastest and the column tile slowest, then the next group starts. The concurrent tiles then cover `group`
 // row pairs x (pairs / group) column tiles, a near-square patch whose operands are a few tens of MB, and
 // the A rows of a group stay in L2 while the group walks every column tile: A comes from DRAM once, B once
-// per group at most. With the row pair fastest over ALL rows (group = m_pairs) a K = 14336 activation
-// (66 MB with its scales) was pulled from DRAM again for every wave of column tiles.
+// per group. With the row pair fastest over ALL rows (group = m_pairs) a K = 14336 activation (66 MB with its
+// scales) was pulled from DRAM again for every wave of column tiles (366 MB read for 99 MB of operands); with
+// small groups the weights are read once per group instead (K = 4096, N = 14336: 143 MB against 52 MB at
+// 8 pairs per group). The host picks the group size from K (see launch).
 __device__ __forceinline__ void pair_tile(uint32_t tile, uint32_t m_pairs, uint32_t n_tiles, uint32_t group,
                                           uint32_t& mp, uint32_t& nt) {
   const uint32_t per_group = group * n_tiles;
@@ -1036,7 +1038,14 @@ int gemm_w4a4_common(mb_ctx* ctx, cudaStream_t stream, const uint8_t* a_codes, c
     pp.m_pairs = (p.m_tiles + 1) / 2;
     // MB_GEMM_RASTER=<row pairs per group> in the environment overrides the group size (measurement runs)
     static const uint32_t raster_env = [] { const char* e = getenv("MB_GEMM_RASTER"); return e ? uint32_t(atoi(e)) : 0u; }();
-    pp.raster_group = std::max<uint32_t>(1u, std::min<uint32_t>(pp.m_pairs, raster_env ? raster_env : 8u));
+    // As many row pairs per group as keep the group's A rows (256 rows of codes and scales per pair) within about
+    // 36 MB of the 126 MB L2, the output stream passing through the same cache; groups of equal size. K = 14336:
+    // 16 pairs (two groups at 8192 rows), K = 4096: all of them (one group, B read once).
+    const double a_pair = 256.0 * double(k) * 0.5625;
+    const uint32_t gmax = std::max<uint32_t>(1u, uint32_t(36.0e6 / a_pair));
+    const uint32_t ngroups = (pp.m_pairs + gmax - 1) / gmax;
+    const uint32_t gauto = (pp.m_pairs + ngroups - 1) / ngroups;
+    pp.raster_group = std::max<uint32_t>(1u, std::min<uint32_t>(pp.m_pairs, raster_env ? raster_env : gauto));
     return launch_pair(ctx, stream, pp);
   }
   return wide ? launch<KIND_NVF4, 256>(ctx, stream, p, tiles) : launch<KIND_NVF4, 128>(ctx, stream, p, tiles);

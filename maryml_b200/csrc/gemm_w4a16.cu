@@ -6,13 +6,19 @@
 //   warp 0      producer: per 64-element K step, the A tile (128 rows of bf16) by TMA into 128B-swizzled shared
 //               memory, and the B tile's CODE bytes (BN rows x 32 bytes) by TMA into a raw ring that runs a few
 //               steps ahead.
-//   warps 6-13  converters: a thread owns one weight row (or half of one) of the step: 32 code bytes and 4
-//               block scales (read from global memory one step ahead) become 64 bf16 values, E2M1[code] *
-//               e4m3(scale) exactly (at most 7 significant bits), written into the swizzled K-major B operand
-//               tile the tensor core reads; fence.proxy.async, then one arrival per warp.
-//   warp 1      MMA issuer: tcgen05.mma kind::f16 (bf16 x bf16 -> f32 in TMEM), two accumulators in turn.
+//   warps 6-21  converters: a thread owns half (or a quarter) of one weight row of the step: its code bytes and
+//               block scales (read from global memory one step ahead) become f16 values, E2M1[code] *
+//               e4m3(scale) exactly (at most 7 significant bits, magnitudes 2^-10 .. 2688), written into the
+//               swizzled K-major B operand tile the tensor core reads; fence.proxy.async, one arrival per warp.
+//               f16 and not bf16: the hardware converts a code pair to f16x2 in one instruction and the scale
+//               multiply is one more, where a bf16 result would cost three further conversions per pair.
+//   warp 1      MMA issuer: tcgen05.mma kind::f16 with a bf16 A operand and an f16 B operand (the instruction
+//               descriptor names the two formats separately), f32 accumulation in TMEM, two accumulators in turn.
 //   warps 2-5   epilogue: tcgen05.ld, times scale2 (applied once to the accumulator, as the reference does),
 //               one cast, coalesced stores through a shared-memory patch.
+//
+// A product with few output tiles and a long K is cut into K slices (more CTAs streaming weights); the slices land
+// in f32 planes of a caller workspace and are summed in slice order.
 //
 // Algorithmic bytes: n * k * 0.5625 (weights, once) + 2 m k + out. Every mbarrier wait is bounded.
 #include "common.cuh"
@@ -26,7 +32,7 @@ using namespace tc5;
 
 constexpr int BM = 128;
 constexpr int BK = 64;                        // K elements per step: one 128-byte row of bf16
-constexpr int CONV_WARPS = 8;
+constexpr int CONV_WARPS = 16;
 constexpr int EPI_WARPS = 4;
 constexpr int THREADS = 32 * (2 + EPI_WARPS + CONV_WARPS);
 // The code-byte stream runs RAW_AHEAD steps ahead of the A stream. Its ring is deeper than that by three, so the
@@ -45,7 +51,7 @@ struct Cfg {
   static constexpr int BAR_BYTES = 256;
   static constexpr int SMEM_BYTES = OP_STAGES * OP_BYTES + RAW_STAGES * RAW_BYTES + 1024 + BAR_BYTES + EPI_WARPS * 512;
   static constexpr int TMEM_COLS = 2 * BN;   // 512 or 256: two accumulators
-  static constexpr int TPR = 256 / BN;       // converter threads per weight row
+  static constexpr int TPR = 32 * CONV_WARPS / BN;   // converter threads per weight row: 2 or 4
 };
 
 struct W4a16Params {
@@ -56,6 +62,10 @@ struct W4a16Params {
   int* flags;
   float alpha;
   uint32_t m, n, k_steps, m_tiles, n_tiles, sc_stride;   // sc_stride = k / 16
+  // split-K (few output tiles, long K): a tile index carries a K slice of ks_per_split steps (k_steps is a multiple
+  // of it); slice sp of the sum lands unscaled in plane sp of an f32 workspace [splits, m, n]
+  uint32_t splits, ks_per_split;
+  float* planes;
   int out_dtype;
 };
 
@@ -64,20 +74,18 @@ __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
   return *reinterpret_cast<uint32_t*>(&v);
 }
 
-// Four codes (two bytes, low nibble first) times their block scale -> two bf16x2 words. The product is exact in
-// f16 and in bf16; the detour through f32 is the conversion path the hardware offers.
+// Four codes (two bytes, low nibble first) times their block scale -> two f16x2 words (exact).
 __device__ __forceinline__ void decode4(uint32_t two_bytes, __half2 s, uint32_t& lo, uint32_t& hi) {
   uint32_t h0, h1;
   asm("{ .reg .b8 b0, b1, b2, b3; mov.b32 {b0, b1, b2, b3}, %2;\n\t"
       "cvt.rn.f16x2.e2m1x2 %0, b0;\n\tcvt.rn.f16x2.e2m1x2 %1, b1; }"
       : "=r"(h0), "=r"(h1) : "r"(two_bytes));
-  const float2 f0 = __half22float2(__hmul2(*reinterpret_cast<__half2*>(&h0), s));
-  const float2 f1 = __half22float2(__hmul2(*reinterpret_cast<__half2*>(&h1), s));
-  lo = pack_bf16x2(f0.x, f0.y);
-  hi = pack_bf16x2(f1.x, f1.y);
+  const __half2 p0 = __hmul2(*reinterpret_cast<__half2*>(&h0), s), p1 = __hmul2(*reinterpret_cast<__half2*>(&h1), s);
+  lo = *reinterpret_cast<const uint32_t*>(&p0);
+  hi = *reinterpret_cast<const uint32_t*>(&p1);
 }
 
-// Sixteen codes (eight bytes) and their scale byte -> two 16-byte chunks of eight bf16 values each.
+// Sixteen codes (eight bytes) and their scale byte -> two 16-byte chunks of eight f16 values each.
 __device__ __forceinline__ void decode_block(uint2 codes, uint32_t scale_byte, uint4& c0, uint4& c1) {
   uint32_t sh;
   asm("cvt.rn.f16x2.e4m3x2 %0, %1;" : "=r"(sh) : "h"(uint16_t(scale_byte)));
@@ -86,6 +94,11 @@ __device__ __forceinline__ void decode_block(uint2 codes, uint32_t scale_byte, u
   decode4(codes.x >> 16, s, c0.z, c0.w);
   decode4(codes.y & 0xFFFFu, s, c1.x, c1.y);
   decode4(codes.y >> 16, s, c1.z, c1.w);
+}
+
+// kind::f16 instruction descriptor with a bf16 A operand and an f16 B operand (M = 128, both K-major, f32 accumulate).
+__host__ __device__ constexpr uint32_t idesc_bf16_f16(uint32_t n) {
+  return (1u << 4) | (1u << 7) | (0u << 10) | ((n >> 3) << 17) | ((128u >> 4) << 24);
 }
 
 // Warp-level transpose through a 512-byte shared-memory patch so that global stores are coalesced: lane l holds
@@ -157,10 +170,21 @@ gemm_w4a16_kernel(const __grid_constant__ W4a16Params p) {
   const uint32_t tmem_base = *tmem_ptr_smem;
   mb_grid_dependency_sync();
 
-  // Tiles: row tile fastest, so that the CTAs running together share a column tile's weights in L2.
-  const uint32_t total_tiles = p.m_tiles * p.n_tiles;
+  // Work items: (K slice, row tile, column tile) with the row tile fastest, so that the CTAs running together share a
+  // column tile's weights in L2; every item has ks_per_split K steps.
+  const uint32_t mn_tiles = p.m_tiles * p.n_tiles;
+  const uint32_t total_tiles = mn_tiles * p.splits;
   const uint32_t my_tiles = blockIdx.x < total_tiles ? (total_tiles - blockIdx.x + gridDim.x - 1) / gridDim.x : 0u;
-  const uint32_t total_steps = my_tiles * p.k_steps;    // this CTA's K steps over all its tiles, in order
+  const uint32_t kps = p.ks_per_split;
+  const uint32_t total_steps = my_tiles * kps;          // this CTA's K steps over all its items, in order
+  // item number -> (row tile, column tile, first K step)
+  auto item = [&](uint32_t it, uint32_t& mt, uint32_t& nt, uint32_t& ks0) {
+    const uint32_t tile = blockIdx.x + it * gridDim.x;
+    const uint32_t sp = tile / mn_tiles, mn = tile - sp * mn_tiles;
+    nt = mn / p.m_tiles;
+    mt = mn - nt * p.m_tiles;
+    ks0 = sp * kps;
+  };
 
   if (warp == 0) {
     // ------------------------------ producer ------------------------------------
@@ -170,8 +194,9 @@ gemm_w4a16_kernel(const __grid_constant__ W4a16Params p) {
     auto issue_raw = [&](uint32_t j) -> bool {
       const uint32_t rs = j % RAW_STAGES, ph = (j / RAW_STAGES) & 1u;
       if (!mbar_wait(raw_empty(rs), ph ^ 1u, abort_smem, tflag, 31)) return false;
-      const uint32_t tile = blockIdx.x + (j / p.k_steps) * gridDim.x, ks = j % p.k_steps;
-      const uint32_t nt = tile / p.m_tiles;
+      uint32_t mt, nt, ks0;
+      item(j / kps, mt, nt, ks0);
+      const uint32_t ks = ks0 + j % kps;
       raw_armed |= 1u << rs;
       raw_par = (raw_par & ~(1u << rs)) | (ph << rs);
       if (elect_one()) {
@@ -185,8 +210,9 @@ gemm_w4a16_kernel(const __grid_constant__ W4a16Params p) {
     for (uint32_t i = 0; ok && i < total_steps; ++i) {
       const uint32_t os = i % C::OP_STAGES, ph = (i / C::OP_STAGES) & 1u;
       if (!mbar_wait(op_empty(os), ph ^ 1u, abort_smem, tflag, 32)) { ok = false; break; }
-      const uint32_t tile = blockIdx.x + (i / p.k_steps) * gridDim.x, ks = i % p.k_steps;
-      const uint32_t mt = tile % p.m_tiles;
+      uint32_t mt, nt, ks0;
+      item(i / kps, mt, nt, ks0);
+      const uint32_t ks = ks0 + i % kps;
       op_armed |= 1u << os;
       op_par = (op_par & ~(1u << os)) | (ph << os);
       if (elect_one()) {
@@ -210,7 +236,7 @@ gemm_w4a16_kernel(const __grid_constant__ W4a16Params p) {
     }
   } else if (warp == 1) {
     // ------------------------------ MMA issuer ----------------------------------
-    const uint32_t idesc = idesc_bf16(BN);
+    const uint32_t idesc = idesc_bf16_f16(BN);
     bool ok = true;
     uint32_t i = 0;
     for (uint32_t it = 0; ok && it < my_tiles; ++it) {
@@ -218,7 +244,7 @@ gemm_w4a16_kernel(const __grid_constant__ W4a16Params p) {
       if (!mbar_wait(acc_empty(buf), ((it >> 1) & 1u) ^ 1u, abort_smem, tflag, 33)) { ok = false; break; }
       fence_after_sync();
       const uint32_t d_tmem = tmem_base + buf * BN;
-      for (uint32_t ks = 0; ks < p.k_steps; ++ks, ++i) {
+      for (uint32_t ks = 0; ks < kps; ++ks, ++i) {
         const uint32_t os = i % C::OP_STAGES, ph = (i / C::OP_STAGES) & 1u;
         if (!mbar_wait(op_full(os), ph, abort_smem, tflag, 34)) { ok = false; break; }
         fence_after_sync();
@@ -228,7 +254,7 @@ gemm_w4a16_kernel(const __grid_constant__ W4a16Params p) {
 #pragma unroll
           for (int j = 0; j < 4; ++j) mma_f16(d_tmem, adesc + 2 * j, bdesc + 2 * j, idesc, (ks | uint32_t(j)) != 0u);
           umma_commit(op_empty(os));
-          if (ks + 1 == p.k_steps) umma_commit(acc_full(buf));
+          if (ks + 1 == kps) umma_commit(acc_full(buf));
         }
         __syncwarp();
       }
@@ -244,8 +270,9 @@ gemm_w4a16_kernel(const __grid_constant__ W4a16Params p) {
     const uint32_t quad = uint32_t(warp) & 3u;
     uint8_t* patch = patches + (uint32_t(warp) - 2u) * 512;
     for (uint32_t it = 0; it < my_tiles; ++it) {
-      const uint32_t tile = blockIdx.x + it * gridDim.x;
-      const uint32_t mt = tile % p.m_tiles, nt = tile / p.m_tiles, buf = it & 1u;
+      uint32_t mt, nt, ks0;
+      item(it, mt, nt, ks0);
+      const uint32_t buf = it & 1u, sp = ks0 / kps;
       if (!mbar_wait(acc_full(buf), (it >> 1) & 1u, abort_smem, tflag, 35)) break;
       fence_after_sync();
       const uint32_t row0 = mt * BM + quad * 32u;
@@ -259,15 +286,17 @@ gemm_w4a16_kernel(const __grid_constant__ W4a16Params p) {
         tmem_ld_x32(t_acc + c * 32, r);
         tmem_ld_wait();
         float v[32];
+        const bool to_plane = p.splits > 1;           // a K slice: the unscaled partial sum, f32, into its plane
 #pragma unroll
-        for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]) * p.alpha;
-        if (p.out_dtype == MB_DT_BF16) {
+        for (int i = 0; i < 32; ++i) v[i] = to_plane ? __uint_as_float(r[i]) : __uint_as_float(r[i]) * p.alpha;
+        uint8_t* obase = to_plane ? reinterpret_cast<uint8_t*>(p.planes + size_t(sp) * p.m * p.n) : static_cast<uint8_t*>(p.out);
+        if (!to_plane && p.out_dtype == MB_DT_BF16) {
           uint4 units[4];
 #pragma unroll
           for (int g = 0; g < 4; ++g)
             units[g] = make_uint4(pack_bf16x2(v[8 * g], v[8 * g + 1]), pack_bf16x2(v[8 * g + 2], v[8 * g + 3]),
                                   pack_bf16x2(v[8 * g + 4], v[8 * g + 5]), pack_bf16x2(v[8 * g + 6], v[8 * g + 7]));
-          uint8_t* g8 = static_cast<uint8_t*>(p.out) + (size_t(row0) * p.n + col0) * 2;
+          uint8_t* g8 = obase + (size_t(row0) * p.n + col0) * 2;
           const uint32_t uv = (p.n - col0) / 8;
           store_rows(patch, lane, units[0], units[1], g8, size_t(p.n) * 2, rows_valid, min(2u, uv));
           if (uv > 2) store_rows(patch, lane, units[2], units[3], g8 + 32, size_t(p.n) * 2, rows_valid, min(2u, uv - 2));
@@ -281,7 +310,7 @@ gemm_w4a16_kernel(const __grid_constant__ W4a16Params p) {
             for (int g = 0; g < 4; ++g)
               units[g] = make_uint4(__float_as_uint(v[16 * hh + 4 * g]), __float_as_uint(v[16 * hh + 4 * g + 1]),
                                     __float_as_uint(v[16 * hh + 4 * g + 2]), __float_as_uint(v[16 * hh + 4 * g + 3]));
-            uint8_t* g8 = static_cast<uint8_t*>(p.out) + (size_t(row0) * p.n + c0) * 4;
+            uint8_t* g8 = obase + (size_t(row0) * p.n + c0) * 4;
             const uint32_t uv = (p.n - c0) / 4;
             store_rows(patch, lane, units[0], units[1], g8, size_t(p.n) * 4, rows_valid, min(2u, uv));
             if (uv > 2) store_rows(patch, lane, units[2], units[3], g8 + 32, size_t(p.n) * 4, rows_valid, min(2u, uv - 2));
@@ -293,14 +322,15 @@ gemm_w4a16_kernel(const __grid_constant__ W4a16Params p) {
     }
   } else {
     // ------------------------------ converters ----------------------------------
-    const uint32_t ct = threadIdx.x - 32u * (2 + EPI_WARPS);          // 0 .. 255
+    const uint32_t ct = threadIdx.x - 32u * (2 + EPI_WARPS);          // 0 .. 511
     const uint32_t r = ct / C::TPR, part = ct % C::TPR;               // weight row of the tile, part of the row
-    constexpr int BLOCKS = 4 / C::TPR;                                // 16-value blocks per thread and step
+    constexpr int BLOCKS = 4 / C::TPR;                                // 16-value blocks per thread and step: 2 or 1
     uint32_t sc_next = 0;
     auto scale_word = [&](uint32_t j) -> uint32_t {
-      const uint32_t tile = blockIdx.x + (j / p.k_steps) * gridDim.x, ks = j % p.k_steps;
-      const uint32_t row = (tile / p.m_tiles) * BN + r;
-      return row < p.n ? __ldg(reinterpret_cast<const uint32_t*>(p.scales + size_t(row) * p.sc_stride) + ks) : 0u;
+      uint32_t mt, nt, ks0;
+      item(j / kps, mt, nt, ks0);
+      const uint32_t row = nt * BN + r;
+      return row < p.n ? __ldg(reinterpret_cast<const uint32_t*>(p.scales + size_t(row) * p.sc_stride) + ks0 + j % kps) : 0u;
     };
     if (total_steps) sc_next = scale_word(0);
     for (uint32_t i = 0; i < total_steps; ++i) {
@@ -313,13 +343,11 @@ gemm_w4a16_kernel(const __grid_constant__ W4a16Params p) {
       const uint8_t* raw = smem_gen + (raw_base - smem_base) + rs * C::RAW_BYTES + r * 32 + part * (32 / C::TPR);
       uint8_t* brow = smem_gen + os * C::OP_BYTES + C::A_BYTES + r * 128;
       uint2 codes[BLOCKS];
-      if (BLOCKS == 4) {
-        const uint4 lo = *reinterpret_cast<const uint4*>(raw), hi = *reinterpret_cast<const uint4*>(raw + 16);
-        codes[0] = make_uint2(lo.x, lo.y); codes[1] = make_uint2(lo.z, lo.w);
-        codes[BLOCKS - 2] = make_uint2(hi.x, hi.y); codes[BLOCKS - 1] = make_uint2(hi.z, hi.w);
-      } else {
+      if (BLOCKS == 2) {
         const uint4 lo = *reinterpret_cast<const uint4*>(raw);
-        codes[0] = make_uint2(lo.x, lo.y); codes[1] = make_uint2(lo.z, lo.w);
+        codes[0] = make_uint2(lo.x, lo.y); codes[BLOCKS - 1] = make_uint2(lo.z, lo.w);
+      } else {
+        codes[0] = *reinterpret_cast<const uint2*>(raw);
       }
 #pragma unroll
       for (int b = 0; b < BLOCKS; ++b) {
@@ -345,6 +373,36 @@ gemm_w4a16_kernel(const __grid_constant__ W4a16Params p) {
     fence_after_sync();
     tmem_dealloc(tmem_base, C::TMEM_COLS);
   }
+}
+
+// Sum of the K-slice planes in slice order (deterministic), times scale2, one cast.
+template <typename O>
+__global__ void __launch_bounds__(256)
+w4a16_splitk_reduce_kernel(const float4* __restrict__ planes, uint32_t splits, size_t plane4, float alpha, O* __restrict__ out) {
+  mb_grid_dependency_sync();
+  const size_t i = size_t(blockIdx.x) * 256 + threadIdx.x;
+  if (i >= plane4) return;
+  float4 acc = planes[i];
+  for (uint32_t s = 1; s < splits; ++s) {
+    const float4 v = planes[size_t(s) * plane4 + i];
+    acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+  }
+  if (sizeof(O) == 4) reinterpret_cast<float4*>(out)[i] = make_float4(acc.x * alpha, acc.y * alpha, acc.z * alpha, acc.w * alpha);
+  else reinterpret_cast<uint2*>(out)[i] = make_uint2(pack_bf16x2(acc.x * alpha, acc.y * alpha), pack_bf16x2(acc.z * alpha, acc.w * alpha));
+}
+
+// K slices for a product whose output tiles would leave most SMs idle while the weights stream: the largest
+// divisor of the K steps that keeps tiles x slices within the SMs and at least eight steps per slice (1 = no split).
+uint32_t w4a16_splits(int sm_count, size_t m, size_t n, size_t k) {
+  if (n % 4 != 0) return 1;
+  const uint32_t tiles = uint32_t((m + BM - 1) / BM) * uint32_t((n + 127) / 128);
+  const uint32_t k_steps = uint32_t(k / BK);
+  if (tiles * 2 > uint32_t(sm_count) || k_steps < 16) return 1;
+  const uint32_t want = std::min<uint32_t>(uint32_t(sm_count) / tiles, k_steps / 8);
+  uint32_t best = 1;
+  for (uint32_t s = 2; s <= want; ++s)
+    if (k_steps % s == 0) best = s;
+  return best;
 }
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
@@ -373,7 +431,7 @@ int launch(mb_ctx* ctx, cudaStream_t stream, const W4a16Params& p) {
     mb_once_done(ctx, bit);
   }
   const int sms = ctx->sm_limit > 0 ? std::min(ctx->sm_limit, ctx->sm_count) : ctx->sm_count;
-  const unsigned grid = std::min<uint32_t>(p.m_tiles * p.n_tiles, uint32_t(sms));
+  const unsigned grid = std::min<uint32_t>(p.m_tiles * p.n_tiles * p.splits, uint32_t(sms));
   MB_CUDA_OK(ctx, mb_launch_pdl(gemm_w4a16_kernel<BN>, dim3(grid), dim3(THREADS), C::SMEM_BYTES, stream, p));
   MB_LAUNCH_OK(ctx);
   return MB_OK;
@@ -381,9 +439,15 @@ int launch(mb_ctx* ctx, cudaStream_t stream, const W4a16Params& p) {
 
 }  // namespace
 
+MB_API size_t mb_nvfp4_gemm_w4a16_workspace(size_t m, size_t n, size_t k) {
+  if (k == 0 || k % 64 != 0) return 0;
+  const uint32_t sp = w4a16_splits(148, m, n, k);
+  return sp > 1 ? size_t(sp) * m * n * sizeof(float) : 0;
+}
+
 MB_API int mb_nvfp4_gemm_w4a16(mb_ctx* ctx, mb_stream stream_, const void* x_bf16, const uint8_t* codes,
                                const uint8_t* scales_rowmajor, float scale2, size_t m, size_t n, size_t k, void* out,
-                               int out_dtype) {
+                               int out_dtype, void* workspace, size_t workspace_bytes) {
   cudaStream_t stream = static_cast<cudaStream_t>(stream_);
   MB_REQUIRE(ctx, ctx && x_bf16 && codes && scales_rowmajor && out, "gemm_w4a16: null argument");
   MB_REQUIRE(ctx, m > 0 && n > 0 && k > 0, "gemm_w4a16: empty extent");
@@ -428,5 +492,25 @@ MB_API int mb_nvfp4_gemm_w4a16(mb_ctx* ctx, mb_stream stream_, const void* x_bf1
   p.m_tiles = uint32_t(m_tiles); p.n_tiles = uint32_t((n + bn - 1) / bn);
   p.sc_stride = uint32_t(k / 16);
   p.out_dtype = out_dtype;
+  p.splits = 1; p.ks_per_split = p.k_steps;
+  const uint32_t sp = wide ? 1u : w4a16_splits(ctx->sm_count, m, n, k);
+  if (sp > 1 && workspace && workspace_bytes >= size_t(sp) * m * n * sizeof(float)) {
+    MB_REQUIRE(ctx, mb_aligned(workspace, 16), "gemm_w4a16: workspace needs 16-byte alignment");
+    p.splits = sp; p.ks_per_split = p.k_steps / sp;
+    p.planes = static_cast<float*>(workspace);
+    rc = launch<128>(ctx, stream, p);
+    if (rc) return rc;
+    const size_t plane4 = m * n / 4;
+    const unsigned grid = unsigned((plane4 + 255) / 256);
+    if (out_dtype == MB_DT_F32)
+      MB_CUDA_OK(ctx, mb_launch_pdl(w4a16_splitk_reduce_kernel<float>, dim3(grid), dim3(256), 0, stream,
+                                    static_cast<const float4*>(workspace), sp, plane4, scale2, static_cast<float*>(out)));
+    else
+      MB_CUDA_OK(ctx, mb_launch_pdl(w4a16_splitk_reduce_kernel<__nv_bfloat16>, dim3(grid), dim3(256), 0, stream,
+                                    static_cast<const float4*>(workspace), sp, plane4, scale2,
+                                    static_cast<__nv_bfloat16*>(out)));
+    MB_LAUNCH_OK(ctx);
+    return MB_OK;
+  }
   return wide ? launch<256>(ctx, stream, p) : launch<128>(ctx, stream, p);
 }

@@ -45,11 +45,33 @@ __device__ __forceinline__ void mma_bf16(float* d, uint32_t a0, uint32_t a1, uin
                : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
-template <typename O>
-__global__ void __launch_bounds__(32 * GEMV_WARPS)
-gemv_w4a16_kernel(const uint4* __restrict__ x, const uint4* __restrict__ codes, const uint8_t* __restrict__ scales,
-                  O* __restrict__ out, uint32_t rows, uint32_t n, uint32_t k, float scale2) {
-  __shared__ float part[GEMV_WARPS][16][8];
+// Four weights (two bytes of codes) times their block scale -> two f16x2 registers (exact, no further conversion).
+__device__ __forceinline__ void decode4_f16(uint32_t two_bytes, __half2 s, uint32_t& lo, uint32_t& hi) {
+  uint32_t h0, h1;
+  asm("{ .reg .b8 b0, b1, b2, b3; mov.b32 {b0, b1, b2, b3}, %2;\n\t"
+      "cvt.rn.f16x2.e2m1x2 %0, b0;\n\tcvt.rn.f16x2.e2m1x2 %1, b1; }"
+      : "=r"(h0), "=r"(h1) : "r"(two_bytes));
+  const __half2 p0 = __hmul2(*reinterpret_cast<__half2*>(&h0), s), p1 = __hmul2(*reinterpret_cast<__half2*>(&h1), s);
+  lo = *reinterpret_cast<const uint32_t*>(&p0);
+  hi = *reinterpret_cast<const uint32_t*>(&p1);
+}
+__device__ __forceinline__ void mma_f16_acc(float* d, uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
+                                            uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, "
+               "{%0, %1, %2, %3};"
+               : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+               : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+// The body of the GEMV for one block of 16 weight rows. F16 = false: activations are the caller's bf16 rows and the
+// decoded weights go f16 -> f32 -> bf16 for the bf16 product. F16 = true: activations are an f16 copy of the rows
+// (exact: the conversion pass refuses values f16 cannot hold), the decoded weights stay f16, and the expansion costs
+// five instructions per four weights instead of eleven, which is what separates an instruction-bound kernel from
+// one that streams weights at the HBM rate.
+template <bool F16, typename O>
+__device__ __forceinline__ void gemv_body(const uint4* __restrict__ x, const uint4* __restrict__ codes,
+                                          const uint8_t* __restrict__ scales, O* __restrict__ out, uint32_t rows, uint32_t n,
+                                          uint32_t k, float scale2, float (*part)[16][8]) {
   const uint32_t lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const uint32_t g = lane >> 2, t = lane & 3;
   const uint32_t row_base = blockIdx.x * 16;
@@ -95,11 +117,17 @@ gemv_w4a16_kernel(const uint4* __restrict__ x, const uint4* __restrict__ codes, 
       for (int i = 0; i < 8; ++i) {                      // instruction i takes values 4 i .. 4 i + 3 of the 32
         const uint32_t ba = (wwa[i >> 1] >> ((i & 1) * 16)) & 0xFFFFu, bb = (wwb[i >> 1] >> ((i & 1) * 16)) & 0xFFFFu;
         uint32_t a0, a1, a2, a3;
-        decode4(ba, i < 4 ? sa_lo : sa_hi, a0, a2);      // row g:     slots (2t, 2t+1) and (2t+8, 2t+9)
-        decode4(bb, i < 4 ? sb_lo : sb_hi, a1, a3);      // row g + 8
         const uint4& xq = xv[i >> 1];
         const uint32_t b0 = (i & 1) ? xq.z : xq.x, b1 = (i & 1) ? xq.w : xq.y;
-        mma_bf16(acc, a0, a1, a2, a3, b0, b1);
+        if (F16) {
+          decode4_f16(ba, i < 4 ? sa_lo : sa_hi, a0, a2);
+          decode4_f16(bb, i < 4 ? sb_lo : sb_hi, a1, a3);
+          mma_f16_acc(acc, a0, a1, a2, a3, b0, b1);
+        } else {
+          decode4(ba, i < 4 ? sa_lo : sa_hi, a0, a2);    // row g:     slots (2t, 2t+1) and (2t+8, 2t+9)
+          decode4(bb, i < 4 ? sb_lo : sb_hi, a1, a3);    // row g + 8
+          mma_bf16(acc, a0, a1, a2, a3, b0, b1);
+        }
       }
     }
   }
@@ -116,6 +144,59 @@ gemv_w4a16_kernel(const uint4* __restrict__ x, const uint4* __restrict__ codes, 
     for (int w = 0; w < GEMV_WARPS; ++w) sum += part[w][wr][ar];
     if (ar < rows && row_base + wr < n) out[size_t(ar) * n + row_base + wr] = O(sum * scale2);
   }
+}
+
+template <typename O>
+__global__ void __launch_bounds__(32 * GEMV_WARPS)
+gemv_w4a16_kernel(const uint4* __restrict__ x, const uint4* __restrict__ codes, const uint8_t* __restrict__ scales,
+                  O* __restrict__ out, uint32_t rows, uint32_t n, uint32_t k, float scale2) {
+  __shared__ float part[GEMV_WARPS][16][8];
+  gemv_body<false, O>(x, codes, scales, out, rows, n, k, scale2, part);
+}
+
+// The same with the f16 copy of the activations when every row converted exactly (flags all zero), else with the
+// caller's bf16 rows; the choice is uniform over the grid.
+template <typename O>
+__global__ void __launch_bounds__(32 * GEMV_WARPS)
+gemv_w4a16_dual_kernel(const uint4* __restrict__ x, const uint4* __restrict__ x_f16, const int* __restrict__ inexact,
+                       const uint4* __restrict__ codes, const uint8_t* __restrict__ scales, O* __restrict__ out,
+                       uint32_t rows, uint32_t n, uint32_t k, float scale2) {
+  __shared__ float part[GEMV_WARPS][16][8];
+  mb_grid_dependency_sync();                 // the conversion pass before this kernel wrote x_f16 and the flags
+  int any = 0;
+  for (uint32_t r = 0; r < rows; ++r) any |= __ldg(inexact + r);
+  if (any) gemv_body<false, O>(x, codes, scales, out, rows, n, k, scale2, part);
+  else gemv_body<true, O>(x_f16, codes, scales, out, rows, n, k, scale2, part);
+}
+
+// One block per activation row: bf16 -> f16, exact when the value is zero, infinite, NaN or a normal f16 (bf16 has
+// 8 significant bits, f16 has 11); a finite value outside f16's normal range raises the row's flag.
+__global__ void __launch_bounds__(256)
+gemv_x_to_f16_kernel(const uint4* __restrict__ x, uint4* __restrict__ x_f16, int* __restrict__ inexact, uint32_t k8) {
+  __shared__ int s_bad;
+  if (threadIdx.x == 0) s_bad = 0;
+  __syncthreads();
+  mb_grid_dependency_sync();                 // the rows come from the kernel before this one
+  const uint32_t row = blockIdx.x;
+  int bad = 0;
+  for (uint32_t i = threadIdx.x; i < k8; i += 256) {
+    const uint4 v = __ldg(x + size_t(row) * k8 + i);
+    const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+    uint32_t h[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float lo = __uint_as_float(w[j] << 16), hi = __uint_as_float(w[j] & 0xFFFF0000u);
+      const float alo = fabsf(lo), ahi = fabsf(hi);
+      bad |= (alo != 0.0f && alo < 6.103515625e-05f) || (alo > 65504.0f && alo < __int_as_float(0x7F800000));
+      bad |= (ahi != 0.0f && ahi < 6.103515625e-05f) || (ahi > 65504.0f && ahi < __int_as_float(0x7F800000));
+      __half2 p = __floats2half2_rn(lo, hi);
+      h[j] = *reinterpret_cast<uint32_t*>(&p);
+    }
+    x_f16[size_t(row) * k8 + i] = make_uint4(h[0], h[1], h[2], h[3]);
+  }
+  if (bad) s_bad = 1;
+  __syncthreads();
+  if (threadIdx.x == 0) inexact[row] = s_bad;
 }
 
 // ---------------------------------------------------------------------------------
@@ -302,6 +383,43 @@ MB_API int mb_nvfp4_gemv_w4a16(mb_ctx* ctx, mb_stream stream_, const void* x_bf1
   else
     return mb_fail(ctx, MB_ERR_INVALID, "gemv: output is bf16 or f32");
   if (rc) return mb_fail(ctx, MB_ERR_INVALID, "gemv: unsupported row count");
+  MB_LAUNCH_OK(ctx);
+  return MB_OK;
+}
+
+MB_API size_t mb_nvfp4_gemv_workspace(size_t rows, size_t k) {
+  if (rows == 0 || rows > MAX_ROWS || k == 0 || k % 32 != 0) return 0;
+  return 256 + rows * k * 2;
+}
+
+MB_API int mb_nvfp4_gemv_w4a16_ws(mb_ctx* ctx, mb_stream stream_, const void* x_bf16, size_t rows, const uint8_t* codes,
+                                  const uint8_t* scales, float scale2, size_t n, size_t k, void* out, int out_dtype,
+                                  void* workspace, size_t workspace_bytes) {
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  if (!workspace || workspace_bytes < mb_nvfp4_gemv_workspace(rows, k) || mb_nvfp4_gemv_workspace(rows, k) == 0)
+    return mb_nvfp4_gemv_w4a16(ctx, stream_, x_bf16, rows, codes, scales, scale2, n, k, out, out_dtype);
+  MB_REQUIRE(ctx, ctx && x_bf16 && codes && scales && out, "gemv: null argument");
+  MB_REQUIRE(ctx, n > 0 && n * k <= 0xFFFFFFFFull, "NVFP4 weight exceeds u32 indexing");
+  MB_REQUIRE(ctx, scale2 == scale2 && scale2 > 0.0f && scale2 <= 3.4e38f,
+             "NVFP4 global scale %g is not a positive finite number", double(scale2));
+  MB_REQUIRE(ctx, mb_aligned(x_bf16, 16) && mb_aligned(workspace, 256), "NVFP4 GEMV needs a 16-byte aligned activation and a 256-byte aligned workspace");
+  MB_REQUIRE(ctx, mb_aligned(codes, 16) && mb_aligned(scales, 2), "NVFP4 GEMV needs 16-byte aligned code rows");
+  MB_REQUIRE(ctx, out_dtype == MB_DT_BF16 || out_dtype == MB_DT_F32, "gemv: output is bf16 or f32");
+  int* flags = static_cast<int*>(workspace);
+  uint4* x16 = reinterpret_cast<uint4*>(static_cast<uint8_t*>(workspace) + 256);
+  MB_CUDA_OK(ctx, mb_launch_pdl(gemv_x_to_f16_kernel, dim3(unsigned(rows)), dim3(256), 0, stream,
+                                static_cast<const uint4*>(x_bf16), x16, flags, uint32_t(k / 8)));
+  const dim3 grid(unsigned((n + 15) / 16)), block(32 * GEMV_WARPS);
+  if (out_dtype == MB_DT_BF16)
+    MB_CUDA_OK(ctx, mb_launch_pdl(gemv_w4a16_dual_kernel<__nv_bfloat16>, grid, block, 0, stream,
+                                  static_cast<const uint4*>(x_bf16), static_cast<const uint4*>(x16), static_cast<const int*>(flags),
+                                  reinterpret_cast<const uint4*>(codes), scales, static_cast<__nv_bfloat16*>(out),
+                                  uint32_t(rows), uint32_t(n), uint32_t(k), scale2));
+  else
+    MB_CUDA_OK(ctx, mb_launch_pdl(gemv_w4a16_dual_kernel<float>, grid, block, 0, stream, static_cast<const uint4*>(x_bf16),
+                                  static_cast<const uint4*>(x16), static_cast<const int*>(flags),
+                                  reinterpret_cast<const uint4*>(codes), scales, static_cast<float*>(out), uint32_t(rows),
+                                  uint32_t(n), uint32_t(k), scale2));
   MB_LAUNCH_OK(ctx);
   return MB_OK;
 }

@@ -30,6 +30,12 @@ __device__ __forceinline__ void mb_markstein8(const float* v, float r, float dne
       "mov.b64 {%0, %1}, q0;\n\tmov.b64 {%2, %3}, q1;\n\tmov.b64 {%4, %5}, q2;\n\tmov.b64 {%6, %7}, q3;\n\t}"
       : "=f"(q[0]), "=f"(q[1]), "=f"(q[2]), "=f"(q[3]), "=f"(q[4]), "=f"(q[5]), "=f"(q[6]), "=f"(q[7])
       : "f"(v[0]), "f"(v[1]), "f"(v[2]), "f"(v[3]), "f"(v[4]), "f"(v[5]), "f"(v[6]), "f"(v[7]), "f"(r), "f"(dneg));
+  // The quotient carries the sign of the dividend (d > 0), also when it is zero: x / d of x = -0.0 is -0.0 and
+  // its code keeps the sign bit (src/nvfp4.rs:117-126), but the refinement's last sum (+0 residual term plus a -0
+  // first estimate) rounds to +0. One bit-select per value puts the dividend's sign back.
+#pragma unroll
+  for (int i = 0; i < 8; ++i)
+    q[i] = __uint_as_float((__float_as_uint(q[i]) & 0x7FFFFFFFu) | (__float_as_uint(v[i]) & 0x80000000u));
 }
 // Eight products v[i] * r the same way.
 __device__ __forceinline__ void mb_mul8(const float* v, float r, float* q) {

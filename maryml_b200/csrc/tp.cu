@@ -12,7 +12,7 @@ namespace {
 
 typedef struct { char internal[128]; } NcclUniqueId;
 typedef void* NcclComm;
-enum { NCCL_SUM = 0, NCCL_FLOAT32 = 7, NCCL_BFLOAT16 = 9 };
+enum { NCCL_SUM = 0, NCCL_UINT8 = 1, NCCL_FLOAT32 = 7, NCCL_BFLOAT16 = 9 };
 
 struct NcclApi {
   int (*GetUniqueId)(NcclUniqueId*);
@@ -20,6 +20,8 @@ struct NcclApi {
   int (*CommDestroy)(NcclComm);
   int (*CommAbort)(NcclComm);
   int (*AllReduce)(const void*, void*, size_t, int, int, NcclComm, cudaStream_t);
+  int (*ReduceScatter)(const void*, void*, size_t, int, int, NcclComm, cudaStream_t);
+  int (*AllGather)(const void*, void*, size_t, int, NcclComm, cudaStream_t);
   const char* (*GetErrorString)(int);
 };
 NcclApi g_nccl;
@@ -37,6 +39,8 @@ int load_nccl(mb_ctx* ctx) {
   SYM(CommDestroy, "ncclCommDestroy")
   SYM(CommAbort, "ncclCommAbort")
   SYM(AllReduce, "ncclAllReduce")
+  SYM(ReduceScatter, "ncclReduceScatter")
+  SYM(AllGather, "ncclAllGather")
   SYM(GetErrorString, "ncclGetErrorString")
 #undef SYM
   ctx->nccl_lib = lib;
@@ -93,6 +97,35 @@ MB_API int mb_tp_all_reduce(mb_ctx* ctx, mb_stream stream, void* buf, size_t cou
   MB_REQUIRE(ctx, ctx->nccl_comm != nullptr, "tp_all_reduce: no group formed");
   MB_NCCL_OK(ctx, g_nccl.AllReduce(buf, buf, count, dtype == MB_DT_F32 ? NCCL_FLOAT32 : NCCL_BFLOAT16, NCCL_SUM,
                                    ctx->nccl_comm, static_cast<cudaStream_t>(stream)));
+  return MB_OK;
+}
+
+// The two halves of the all-reduce, for the prompt path that works on its own rows between them: SUM
+// reduce-scatter of f32 ([world x count] in, this rank's [count] out) and all-gather of raw bytes ([bytes] in
+// at recv + rank * bytes or elsewhere, [world x bytes] out; in place when send == recv + rank * bytes).
+MB_API int mb_tp_reduce_scatter_f32(mb_ctx* ctx, mb_stream stream, const float* send, float* recv, size_t recv_count) {
+  MB_REQUIRE(ctx, ctx && send && recv && recv_count > 0, "tp_reduce_scatter_f32: null or empty argument");
+  if (ctx->tp_world == 1 && !ctx->nccl_comm) {
+    if (send != recv)
+      MB_CUDA_OK(ctx, cudaMemcpyAsync(recv, send, recv_count * sizeof(float), cudaMemcpyDeviceToDevice,
+                                      static_cast<cudaStream_t>(stream)));
+    return MB_OK;
+  }
+  MB_REQUIRE(ctx, ctx->nccl_comm != nullptr, "tp_reduce_scatter_f32: no group formed");
+  MB_NCCL_OK(ctx, g_nccl.ReduceScatter(send, recv, recv_count, NCCL_FLOAT32, NCCL_SUM, ctx->nccl_comm,
+                                       static_cast<cudaStream_t>(stream)));
+  return MB_OK;
+}
+
+MB_API int mb_tp_all_gather(mb_ctx* ctx, mb_stream stream, const void* send, void* recv, size_t send_bytes) {
+  MB_REQUIRE(ctx, ctx && send && recv && send_bytes > 0, "tp_all_gather: null or empty argument");
+  if (ctx->tp_world == 1 && !ctx->nccl_comm) {
+    if (send != recv)
+      MB_CUDA_OK(ctx, cudaMemcpyAsync(recv, send, send_bytes, cudaMemcpyDeviceToDevice, static_cast<cudaStream_t>(stream)));
+    return MB_OK;
+  }
+  MB_REQUIRE(ctx, ctx->nccl_comm != nullptr, "tp_all_gather: no group formed");
+  MB_NCCL_OK(ctx, g_nccl.AllGather(send, recv, send_bytes, NCCL_UINT8, ctx->nccl_comm, static_cast<cudaStream_t>(stream)));
   return MB_OK;
 }
 

@@ -147,6 +147,25 @@ class Group:
         self.ctx.check(lib.mb_tp_all_reduce(self.ctx.handle, _stream(), _p(t), t.numel(), _lib.DT_F32))
         return t
 
+    def reduce_scatter_f32(self, t):
+        """SUM reduce-scatter by rows: t [rows, n] f32 on every rank -> this rank's [rows / world, n] of the sum."""
+        assert t.dtype == torch.float32 and t.is_contiguous() and t.shape[0] % self.tp.world == 0
+        out = torch.empty((t.shape[0] // self.tp.world, t.shape[1]), dtype=torch.float32, device=t.device)
+        self.ctx.check(lib.mb_tp_reduce_scatter_f32(self.ctx.handle, _stream(), _p(t), _p(out), out.numel()))
+        return out
+
+    def all_gather_rows(self, whole):
+        """In-place all-gather of a contiguous buffer cut evenly in rank order: this rank's slice is already in
+        its place, the others' slices arrive."""
+        assert whole.is_contiguous()
+        nbytes = whole.numel() * whole.element_size()
+        assert nbytes % self.tp.world == 0
+        part = nbytes // self.tp.world
+        base = whole.data_ptr()
+        self.ctx.check(lib.mb_tp_all_gather(self.ctx.handle, _stream(), C.c_void_p(base + self.tp.rank * part),
+                                            C.c_void_p(base), part))
+        return whole
+
     def close(self):
         lib.mb_tp_close(self.ctx.handle)
 
@@ -350,9 +369,51 @@ class DecoderLayer:
                 out.copy_(y)
                 return out
             return y
+        if self._rows_shard(rows):
+            return self._forward_rows_sharded(x, batch, past, k_cache, v_cache, out, after_rope, before_rope)
         o_sum = self._all_reduce(self.half_attention(x, batch, past, k_cache, v_cache, after_rope, before_rope))
         residual, down = self.half_mlp(x, o_sum)
         return self.finish(residual, self._all_reduce(down), out=out)
+
+    # Prompts of at least this many rows per rank keep their rows sharded between the two exchanges
+    # (MB_TP_ROW_SHARD=0 in the environment keeps the plain all-reduce, for comparison runs).
+    ROW_SHARD_MIN = 256
+
+    def _rows_shard(self, rows):
+        w = self.tp.world
+        return (self.group is not None and w > 1 and rows % (128 * w) == 0 and rows // w >= self.ROW_SHARD_MIN
+                and self.cfg.hidden % 256 == 0 and os.environ.get("MB_TP_ROW_SHARD", "1") != "0")
+
+    def _forward_rows_sharded(self, x, batch, past, k_cache, v_cache, out=None, after_rope=None, before_rope=None):
+        """The split layer for prompt-sized activations. An f32 all-reduce of [rows, hidden] moves 8 bytes per
+        element and rank over the links, and every rank then repeats the same residual add, norm and quantizer on
+        all rows. Here each exchange is the all-reduce's first half only, a SUM reduce-scatter by rows (the same
+        f32 sums); this rank adds the residual, normalises and quantizes its OWN rows, and what is gathered is what
+        the next product reads: NVFP4 planes at 0.5625 bytes per element. The output rows are gathered as bf16 at
+        the end. Per element the arithmetic is that of the all-reduce path."""
+        cfg, w, r = self.cfg, self.tp.world, self.tp.rank
+        rows, hidden = x.shape
+        local = rows // w
+        lo = r * local
+        dev = x.device
+        ctx = context(dev.index)
+        o_local = self.group.reduce_scatter_f32(
+            self.half_attention(x, batch, past, k_cache, v_cache, after_rope, before_rope))
+        codes = torch.empty((rows, hidden // 2), dtype=torch.uint8, device=dev)
+        sf = torch.empty(nv.sf_bytes(rows, hidden), dtype=torch.uint8, device=dev)
+        sf_part = sf.numel() // w                      # whole 128-row tiles per rank: a contiguous range of the plane
+        resid_local = torch.empty((local, hidden), dtype=torch.bfloat16, device=dev)
+        ctx.check(lib.mb_residual_norm_quantize(ctx.handle, _stream(), _p(x[lo:lo + local]), _p(o_local), _p(self.post_gain),
+                                                local, hidden, float(cfg.eps), _p(resid_local), _p(codes[lo:lo + local]),
+                                                C.c_void_p(sf.data_ptr() + r * sf_part)))
+        self.group.all_gather_rows(codes)
+        self.group.all_gather_rows(sf)
+        act = nv.gemm_w4a4_stacked(codes, sf, self.wgu, rows, epilogue=_lib.EPI_SWIGLU_ROUNDED | _lib.EPI_QUANT_SCALED)
+        d_local = self.group.reduce_scatter_f32(self._project((act[0], act[1], rows), self.wdown, out_dtype=torch.float32))
+        y = out if out is not None else torch.empty((rows, hidden), dtype=torch.bfloat16, device=dev)
+        assert y.is_contiguous()
+        add_f32(resid_local, d_local, out=y[lo:lo + local])
+        return self.group.all_gather_rows(y)
 
     # rows per chunk of the pipelined prompt path, and the SMs left to the all-reduce that runs beside the products
     PROMPT_CHUNK = 2048

@@ -121,11 +121,27 @@ _SPLITK_WS = {}
 
 
 def _splitk_workspace(device, nbytes):
-    """One reusable split-K workspace per device (grown on demand, never shrunk)."""
-    ws = _SPLITK_WS.get(device)
+    """One reusable split-K workspace per device and stream (grown on demand, never shrunk): calls on one stream
+    are ordered and may share it, calls on different streams may overlap and may not."""
+    key = (device, torch.cuda.current_stream(device).cuda_stream)
+    ws = _SPLITK_WS.get(key)
     if ws is None or ws.numel() < nbytes:
         ws = torch.empty(nbytes, dtype=torch.uint8, device=device)
-        _SPLITK_WS[device] = ws
+        _SPLITK_WS[key] = ws
+    return ws
+
+
+_GEMV_WS = {}
+
+
+def _gemv_workspace(device, nbytes):
+    """The GEMV's f16 activation copy: one reusable buffer per device and stream (calls on one stream are ordered,
+    so they may share it)."""
+    key = (device, torch.cuda.current_stream(device).cuda_stream)
+    ws = _GEMV_WS.get(key)
+    if ws is None or ws.numel() < nbytes:
+        ws = torch.empty(max(nbytes, 1 << 20), dtype=torch.uint8, device=device)
+        _GEMV_WS[key] = ws
     return ws
 
 
@@ -226,8 +242,10 @@ def w4a16_gemm(x, codes, scales, scale2, n, k, out_dtype=torch.bfloat16):
     ctx = context(x.device.index)
     m = x.shape[0]
     out = torch.empty((m, n), dtype=out_dtype, device=x.device)
+    need = int(lib.mb_nvfp4_gemm_w4a16_workspace(m, n, k))
+    ws = _splitk_workspace(x.device, need) if need else None
     ctx.check(lib.mb_nvfp4_gemm_w4a16(ctx.handle, _stream(), _p(x), _p(codes), _p(scales), float(scale2), m, n, k, _p(out),
-                                      _lib.DT_BF16 if out_dtype == torch.bfloat16 else _lib.DT_F32))
+                                      _lib.DT_BF16 if out_dtype == torch.bfloat16 else _lib.DT_F32, _p(ws), need))
     return out
 
 
@@ -334,8 +352,10 @@ class Nvfp4:
         assert 1 <= rows <= MAX_ROWS, f"NVFP4 GEMV takes 1..={MAX_ROWS} rows"
         ctx = context(self._device.index)
         out = torch.empty((1, rows, self._n), dtype=self._dtype, device=self._device)
-        ctx.check(lib.mb_nvfp4_gemv_w4a16(ctx.handle, _stream(), _p(x), rows, _p(self.codes), _p(self.scales),
-                                          self.scale2, self._n, self._k, _p(out), _lib.DT_BF16))
+        need = int(lib.mb_nvfp4_gemv_workspace(rows, self._k))
+        ws = _gemv_workspace(self._device, need)
+        ctx.check(lib.mb_nvfp4_gemv_w4a16_ws(ctx.handle, _stream(), _p(x), rows, _p(self.codes), _p(self.scales),
+                                             self.scale2, self._n, self._k, _p(out), _lib.DT_BF16, _p(ws), need))
         return out
 
     # ---- prompt projections ---------------------------------------------------

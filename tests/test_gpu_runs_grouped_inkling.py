@@ -179,7 +179,7 @@ def test_prompt_shapes_take_one_run_in_place_with_f32_in_and_out(mods, orc):
     ref = orc.attention(bf16_bits_to_f32(qb[0]), bf16_bits_to_f32(kb[0, :keys]), bf16_bits_to_f32(vb[0, :keys]), heads, kvh,
                         D, past, 1.0 / math.sqrt(D))
     r, cos = attn_check(out.cpu().numpy().reshape(nq, -1), ref)
-    assert r <= 1e-2 and cos >= 0.9999, (r, cos)
+    assert r <= 1.5e-2 and cos >= 0.9999, (r, cos)          # the prompt-shape bound of the attention tests
     with pytest.raises(_lib.MaryError):          # two live runs under a prompt-shaped block
         att.flash_attention_runs(dev_bf16(qb).view(batch, nq, heads, D), [run, run], q0=past)
     with pytest.raises(_lib.MaryError):          # a live range outside the buffer
@@ -310,6 +310,30 @@ def test_linear_w_lanes_against_the_oracle(mods, orc):
     assert np.abs(got.cpu().numpy() - ref).max() <= 1e-4 * np.abs(ref).max()
     got = ink.linear_w(dev_bf16(xb).view(m, k), ink.ProjW("bf16", dev_bf16(wb).view(n, k)))
     assert np.abs(got.cpu().numpy() - orc.linear_bf16(xb, wb, m, n, k)).max() <= 1e-4 * np.abs(ref).max()
+
+
+def test_calibrated_planes_upload_and_project(mods, orc):
+    """A linear packed by the calibrated packer (src/calibrate.rs:351-434) reaches the device as any stored NVFP4
+    leaf does (payload -> Nvfp4::upload); the consumer applies 1 / s to the activation's columns."""
+    _, _, nv, _ = mods
+    from maryml_b200 import calibrate as cal
+    n, k, m = 64, 128, 24
+    rng = np.random.default_rng(5)
+    w = (rng.standard_normal((n, k)) * 0.02).astype(np.float32)
+    xs = rng.standard_normal((96, k)).astype(np.float32)
+    xs[:, 3 * k // 4:] *= 8.0
+    c = cal.pack_linear(w, k, xs, np.abs(xs).mean(0).astype(np.float32))
+    assert c.error_ratio <= 1.0
+    q = nv.Nvfp4.upload(c.packed.payload(), [n, k], torch.bfloat16, torch.device("cuda", 0))
+    xb = f32_to_bf16_bits((xs[:m] * c.input_scale[None, :]).astype(np.float32))
+    ref = bf16_bits_to_f32(xb).reshape(m, k).astype(np.float64) @ c.packed.decode().astype(np.float64).T
+    for lane in (nv.PromptLane.W4A16,):
+        y = q.project(dev_bf16(xb).view(1, m, k), lane)
+        rel, cos = rel_check(bf16_bits_to_f32(host_bits(y)).reshape(m, n), ref)
+        assert rel <= 1e-2 and cos >= 0.9999, (rel, cos)
+    # and it tracks the unquantized layer better than plain rounding does on the same rows
+    plain = cal.pack_nearest(w, k)
+    assert cal.output_error(w, c.decode(), k, xs) <= cal.output_error(w, plain.decode(), k, xs)
 
 
 def test_swiglu_epilogue_refuses_a_width_it_would_truncate(mods, orc):
