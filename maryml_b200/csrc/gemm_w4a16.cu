@@ -7,13 +7,15 @@
 //               memory, and the B tile's CODE bytes (BN rows x 32 bytes) by TMA into a raw ring that runs a few
 //               steps ahead.
 //   warps 6-21  converters: a thread owns half (or a quarter) of one weight row of the step: its code bytes and
-//               block scales (read from global memory one step ahead) become f16 values, E2M1[code] *
-//               e4m3(scale) exactly (at most 7 significant bits, magnitudes 2^-10 .. 2688), written into the
-//               swizzled K-major B operand tile the tensor core reads; fence.proxy.async, one arrival per warp.
-//               f16 and not bf16: the hardware converts a code pair to f16x2 in one instruction and the scale
-//               multiply is one more, where a bf16 result would cost three further conversions per pair.
-//   warp 1      MMA issuer: tcgen05.mma kind::f16 with a bf16 A operand and an f16 B operand (the instruction
-//               descriptor names the two formats separately), f32 accumulation in TMEM, two accumulators in turn.
+//               block scales (read from global memory one step ahead) become bf16 values, E2M1[code] *
+//               e4m3(scale) exactly (at most 6 significant bits), written into the swizzled K-major B operand
+//               tile the tensor core reads; fence.proxy.async, one arrival per warp. The hardware converts a
+//               code pair to f16x2 in one instruction; the f16 bit pattern of an E2M1 value shifted three places
+//               down IS the bf16 pattern of that value times 2^-112 (zero stays zero), so one packed bf16
+//               multiply by (scale * 2^112) finishes the pair with no trip through f32.
+//   warp 1      MMA issuer: tcgen05.mma kind::f16 on two bf16 operands (one instruction descriptor cannot mix a
+//               bf16 and an f16 operand: the hardware refuses it as an illegal instruction), f32 accumulation
+//               in TMEM, two accumulators in turn.
 //   warps 2-5   epilogue: tcgen05.ld, times scale2 (applied once to the accumulator, as the reference does),
 //               one cast, coalesced stores through a shared-memory patch.
 //
@@ -74,31 +76,34 @@ __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
   return *reinterpret_cast<uint32_t*>(&v);
 }
 
-// Four codes (two bytes, low nibble first) times their block scale -> two f16x2 words (exact).
-__device__ __forceinline__ void decode4(uint32_t two_bytes, __half2 s, uint32_t& lo, uint32_t& hi) {
+// Four codes (two bytes, low nibble first) times their block scale -> two bf16x2 words (exact). `s112` holds the
+// block scale times 2^112 in both halves.
+__device__ __forceinline__ void decode4(uint32_t two_bytes, __nv_bfloat162 s112, uint32_t& lo, uint32_t& hi) {
   uint32_t h0, h1;
   asm("{ .reg .b8 b0, b1, b2, b3; mov.b32 {b0, b1, b2, b3}, %2;\n\t"
       "cvt.rn.f16x2.e2m1x2 %0, b0;\n\tcvt.rn.f16x2.e2m1x2 %1, b1; }"
       : "=r"(h0), "=r"(h1) : "r"(two_bytes));
-  const __half2 p0 = __hmul2(*reinterpret_cast<__half2*>(&h0), s), p1 = __hmul2(*reinterpret_cast<__half2*>(&h1), s);
+  // f16 s.eeeee.mmmmmmmmmm -> bf16 s.000eeeee.mmmmmmm: the value times 2^(15 - 127); the three mantissa bits that
+  // fall off are zero for every E2M1 value
+  uint32_t t0 = ((h0 >> 3) & 0x0FFF0FFFu) | (h0 & 0x80008000u);
+  uint32_t t1 = ((h1 >> 3) & 0x0FFF0FFFu) | (h1 & 0x80008000u);
+  const __nv_bfloat162 p0 = __hmul2(*reinterpret_cast<__nv_bfloat162*>(&t0), s112);
+  const __nv_bfloat162 p1 = __hmul2(*reinterpret_cast<__nv_bfloat162*>(&t1), s112);
   lo = *reinterpret_cast<const uint32_t*>(&p0);
   hi = *reinterpret_cast<const uint32_t*>(&p1);
 }
 
-// Sixteen codes (eight bytes) and their scale byte -> two 16-byte chunks of eight f16 values each.
+// Sixteen codes (eight bytes) and their scale byte -> two 16-byte chunks of eight bf16 values each.
 __device__ __forceinline__ void decode_block(uint2 codes, uint32_t scale_byte, uint4& c0, uint4& c1) {
   uint32_t sh;
   asm("cvt.rn.f16x2.e4m3x2 %0, %1;" : "=r"(sh) : "h"(uint16_t(scale_byte)));
-  const __half2 s = __low2half2(*reinterpret_cast<__half2*>(&sh));
+  // 2^112 * scale <= 2^121 is a bf16 value with the scale's four significant bits
+  const float sf = __half2float(__low2half(*reinterpret_cast<__half2*>(&sh))) * 5192296858534827628530496329220096.0f;
+  const __nv_bfloat162 s = __float2bfloat162_rn(sf);
   decode4(codes.x & 0xFFFFu, s, c0.x, c0.y);
   decode4(codes.x >> 16, s, c0.z, c0.w);
   decode4(codes.y & 0xFFFFu, s, c1.x, c1.y);
   decode4(codes.y >> 16, s, c1.z, c1.w);
-}
-
-// kind::f16 instruction descriptor with a bf16 A operand and an f16 B operand (M = 128, both K-major, f32 accumulate).
-__host__ __device__ constexpr uint32_t idesc_bf16_f16(uint32_t n) {
-  return (1u << 4) | (1u << 7) | (0u << 10) | ((n >> 3) << 17) | ((128u >> 4) << 24);
 }
 
 // Warp-level transpose through a 512-byte shared-memory patch so that global stores are coalesced: lane l holds
@@ -236,7 +241,7 @@ gemm_w4a16_kernel(const __grid_constant__ W4a16Params p) {
     }
   } else if (warp == 1) {
     // ------------------------------ MMA issuer ----------------------------------
-    const uint32_t idesc = idesc_bf16_f16(BN);
+    const uint32_t idesc = idesc_bf16(BN);
     bool ok = true;
     uint32_t i = 0;
     for (uint32_t it = 0; ok && it < my_tiles; ++it) {

@@ -171,15 +171,16 @@ MB_API int mb_tp_close(mb_ctx* ctx) {
 //   D  waits for every peer's slice before it ends, so that the next kernel on the stream
 //      may read the whole output.
 // Plain peer loads/stores only (no multicast). Every wait is bounded; a wait that runs out
-// raises the context's timeout word and the kernel ends. The grid never exceeds the SM
-// count, so CTAs waiting in A or D cannot keep the others from running.
+// raises the context's timeout word and the kernel ends without reducing or publishing anything;
+// the exchange is still counted, so the following exchange finds its counters in order. The grid
+// never exceeds the SM count, so CTAs waiting in A or D cannot keep the others from running.
 // ---------------------------------------------------------------------------------
 namespace {
 
 struct ReduceParams {
   void* const* peer;          // device table of every rank's exchange memory
   const __nv_bfloat16* resid; // [t, n] replicated residual stream
-  int* done_counter;          // two counters, one per step parity
+  int* done_counter;          // two counters, one per step parity, then the exchange counter (word 2)
   int* flags;                 // the context's status words
   unsigned long long wait_ns; // budget of one wait on the peers
   uint32_t t, n, nw, t_max, world, rank;
@@ -215,8 +216,18 @@ __device__ bool wait_flags(volatile int* flags, uint32_t world, int step, int* s
 }
 
 __global__ void __launch_bounds__(256)
-tp_reduce_gather_kernel(const ReduceParams p) {
+tp_reduce_gather_kernel(const ReduceParams p_in) {
   __shared__ int s_ok;
+  // The number of this exchange comes from a counter in device memory (the exchanges completed so far, plus one),
+  // not from the launch parameters, so that a captured graph of the layer can be replayed: every replay then waits
+  // for, and publishes, flag values of its own. The host's number only has to agree in parity (it chose the halves
+  // of the exchange memory by it); a disagreement raises status code 53 and the kernel ends.
+  ReduceParams p = p_in;
+  p.step = p_in.done_counter[2] + 1;
+  if ((p.step ^ p_in.step) & 1) {
+    if (threadIdx.x == 0 && p.flags) atomicCAS(p.flags + MB_FLAG_WAIT_TIMEOUT, 0, 53);
+    return;
+  }
   void* const local = p.peer[p.rank];
   // ---- A: my partials have landed everywhere (the GEMM kernel before this one is complete)
   if (blockIdx.x == 0 && threadIdx.x < p.world) {
@@ -229,7 +240,7 @@ tp_reduce_gather_kernel(const ReduceParams p) {
   if (blockIdx.x == 0 && threadIdx.x == 0) p.done_counter[(p.step + 1) & 1] = 0;
   if (threadIdx.x == 0) s_ok = wait_flags(symm_flags(local), p.world, p.step, p.flags, p.wait_ns, 51) ? 1 : 0;
   __syncthreads();
-  if (!s_ok) return;
+  const bool ok = s_ok != 0;       // a wait that ran out: nothing is reduced or published, but the exchange is still counted
   __threadfence_system();
   // ---- B: reduce my slice, add the residual, store it into every rank's output
   const size_t half_recv = size_t(p.t_max) * p.n;                    // floats per step parity
@@ -239,7 +250,7 @@ tp_reduce_gather_kernel(const ReduceParams p) {
                          size_t(p.step & 1) * size_t(p.t_max) * p.n * 2;
   const uint32_t groups_per_row = p.nw / 8;
   const size_t total = size_t(p.t) * groups_per_row;
-  for (size_t g = size_t(blockIdx.x) * 256 + threadIdx.x; g < total; g += size_t(gridDim.x) * 256) {
+  for (size_t g = size_t(blockIdx.x) * 256 + threadIdx.x; ok && g < total; g += size_t(gridDim.x) * 256) {
     const uint32_t row = uint32_t(g / groups_per_row), c = uint32_t(g % groups_per_row) * 8;
     float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
     for (uint32_t r = 0; r < p.world; ++r) {
@@ -273,14 +284,15 @@ tp_reduce_gather_kernel(const ReduceParams p) {
   if (threadIdx.x == 0) {
     const int done = atomicAdd(p.done_counter + (p.step & 1), 1);
     if (done == int(gridDim.x) - 1) {
+      p.done_counter[2] = p.step;          // every CTA of this exchange has read the counter: the exchange is counted
       __threadfence_system();
-      for (uint32_t r = 0; r < p.world; ++r) {
+      for (uint32_t r = 0; ok && r < p.world; ++r) {
         volatile int* f = symm_flags(p.peer[r]) + 64;
         f[p.rank] = p.step;
       }
     }
     // ---- D: every rank's slice is in my output before this kernel ends
-    wait_flags(symm_flags(local) + 64, p.world, p.step, p.flags, p.wait_ns, 52);
+    if (ok) wait_flags(symm_flags(local) + 64, p.world, p.step, p.flags, p.wait_ns, 52);
     __threadfence_system();
   }
 }
@@ -301,8 +313,8 @@ MB_API int mb_tp_symm_create(mb_ctx* ctx, size_t t_max, size_t n, uint8_t handle
   MB_CUDA_OK(ctx, cudaMalloc(&sy->local, sy->bytes));
   MB_CUDA_OK(ctx, cudaMemset(sy->local, 0, sy->bytes));
   MB_CUDA_OK(ctx, cudaMalloc(&sy->peer_dev, 8 * sizeof(void*)));
-  MB_CUDA_OK(ctx, cudaMalloc(&sy->done_counter, 2 * sizeof(int)));
-  MB_CUDA_OK(ctx, cudaMemset(sy->done_counter, 0, 2 * sizeof(int)));
+  MB_CUDA_OK(ctx, cudaMalloc(&sy->done_counter, 4 * sizeof(int)));
+  MB_CUDA_OK(ctx, cudaMemset(sy->done_counter, 0, 4 * sizeof(int)));
   cudaIpcMemHandle_t h;
   MB_CUDA_OK(ctx, cudaIpcGetMemHandle(&h, sy->local));
   memcpy(handle_out, &h, 64);

@@ -10,6 +10,8 @@ memory and streams; every computation is a call into libmary_b200.so.
 import ctypes as C
 import enum
 
+import os
+
 import numpy as np
 import torch
 
@@ -406,8 +408,8 @@ class Nvfp4:
         # The weight stays four bits in HBM: code x block scale is expanded to bf16 (exact) between shared
         # memory and the tensor core, f32 accumulation, scale2 applied once to the accumulator, as in the
         # reference's W4A16 kernel. k % 64 != 0 (the reference's W4A16 takes k % 32) goes through a decoded
-        # scratch plane and the bf16 product instead.
-        if self._k % KTILE4 == 0 and x2.data_ptr() % 16 == 0:
+        # scratch plane and the bf16 product instead (MB_W4A16_FUSED=0 sends every shape that way, for comparison).
+        if self._k % KTILE4 == 0 and x2.data_ptr() % 16 == 0 and os.environ.get("MB_W4A16_FUSED", "1") != "0":
             return w4a16_gemm(x2, self.codes, self.scales, self.scale2, self._n, self._k, out_dtype=self._dtype)
         w = dequantize(self.codes, self.scales, 1.0, self._n, self._k, dtype=torch.bfloat16)
         return bf16_gemm(x2, w, out_dtype=self._dtype, alpha=self.scale2)

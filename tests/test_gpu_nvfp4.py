@@ -214,7 +214,8 @@ def test_gemv_w4a16_against_f64(mb, orc, rows, n, k):
 
 def test_gemv_takes_the_bf16_form_when_a_value_does_not_fit_f16(mb, orc):
     """The GEMV multiplies an f16 copy of the activation rows when that copy is exact; one value outside f16's normal
-    range (here 3e38, 1e-30 and a bf16 subnormal in different rows) sends the whole call through the bf16 product.
+    range (70000, 1e30, 1e-30 and a bf16 subnormal; 1e30 times a decoded weight still fits the f32 accumulator, which
+    the reference scales by scale2 only at the end) sends the whole call through the bf16 product.
     Both forms stay inside the reference's bound, and with the plain entry point (no workspace) they agree to f32
     summation order."""
     import ctypes as C
@@ -224,7 +225,7 @@ def test_gemv_takes_the_bf16_form_when_a_value_does_not_fit_f16(mb, orc):
     q = mb.Nvfp4.quantize(dev_bf16(wbits).view(n, k))
     codes, scales = q.read_planes()
     dq = np.abs(orc.dequantize(codes, scales, q.scale2).reshape(n, k).astype(np.float64))
-    for poke in (None, 3.0e38, 1.0e-30, 9.2e-41, float("inf")):
+    for poke in (None, 70000.0, 1.0e30, 1.0e-30, 9.2e-41, float("inf")):
         x32 = orc.normal_f32(77, rows * k, 1.0)
         if poke is not None:
             x32[k + 5] = poke

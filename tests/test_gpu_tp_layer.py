@@ -287,9 +287,12 @@ def test_shard_arithmetic_of_worlds_2_4_8_on_one_gpu(world, figures):
     e_d = float((down_sum - st["down"]).abs().max() / st["down"].abs().max())
     y = layer.DecoderLayer.finish(st["residual"], down_sum)
     diff = (y.view(torch.int16) != st["y"].view(torch.int16)).float().mean().item()
-    steps = int((y.view(torch.int16).int() - st["y"].view(torch.int16).int()).abs().max())     # bf16 patterns apart
+    # where the two differ, by one bf16 step of the operands of the last add (residual + bf16(down sum)); the result
+    # itself can be much smaller than its operands, so its own bit patterns may sit several steps apart
+    step = 2.0 ** -7 * torch.maximum(st["residual"].float().abs(), st["down"].abs())
+    steps = float(((y.float() - st["y"].float()).abs() / step.clamp_min(1e-30)).max())
     assert e_o <= 2e-5 and e_d <= 2e-5, (e_o, e_d)            # f32 re-association of 4096- and 14336-term sums
-    assert diff <= 1e-3 and steps <= 1, (diff, steps)          # a rounding boundary straddled here and there
+    assert diff <= 1e-3 and steps <= 3.0, (diff, steps)        # one step of bf16(down) plus the rounding of the sum
     # the layer as it runs, every stage on its own previous output
     down_chain = None
     for L in ranks:
