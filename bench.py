@@ -574,8 +574,13 @@ def build_tp(env, args, decode, setup=None, fused=None):
                            "peak": 4 * peaks["bf16"], "unit": "TFLOP/s", "frac": flop / (ms * 1e-3) / 1e12 / (4 * peaks["bf16"]),
                            "peak_source": "4 x " + peaks["source"] + " bf16 burst", "traffic": None,
                            "note": "projections at the FP4 rate dominate; attention runs at the bf16 rate"}
-    reduce = ("fused: GEMM epilogue scatters to peers, one reduce+residual+gather kernel" if use_fused else
-              ("nccl all-reduce f32 + add" if world > 1 else "none (world 1)"))
+    if use_fused:
+        reduce = "fused: GEMM epilogue scatters to peers, one reduce+residual+gather kernel"
+    elif world > 1 and L_._rows_shard(batch * t):
+        reduce = ("nccl, rows sharded between the exchanges: reduce-scatter f32 by rows, norm + quantizer on the rank's "
+                  "rows, all-gather of NVFP4 planes; reduce-scatter f32 + add, all-gather of bf16 rows")
+    else:
+        reduce = "nccl all-reduce f32 + add" if world > 1 else "none (world 1)"
     w = {
         "step": lambda: L_.forward(x, batch, past, kc, vc), "e2e": e2e, "units": batch * t,
         "metric": f"tp_layer_{'decode' if decode else 'prefill'}_tokens_per_s", "unit": "tokens/s",
@@ -665,12 +670,22 @@ def measure_extra(env, w, steps, warmup, cpu=True, graph=False):
             gr = torch.cuda.CUDAGraph()
             with torch.cuda.graph(gr):
                 w["step"]()
+            if env.world > 1:
+                # two trial replays before the timed ones: a replay whose peer waits run out costs a second each, and
+                # every rank has to agree on whether the timed replays run
+                gr.replay()
+                gr.replay()
+                torch.cuda.synchronize()
+                rc, flags = env.ctx.check_flags(None)
+                (bad,) = env.max_over_ranks([1.0 if (rc != 0 or any(flags)) else 0.0])
+                if bad:
+                    raise RuntimeError(f"trial replay raised device status words {flags}")
             gms, _ = time_steps(env, gr.replay, steps, warmup, sample_clocks=False)
             (gms,) = env.max_over_ranks([gms])
             graph_ms = gms / steps
             del gr
         except Exception as exc:                          # a capture that fails costs the leg, not the line
-            graph_ms = f"capture failed: {type(exc).__name__}"
+            graph_ms = f"capture failed: {type(exc).__name__}: {exc}"[:200]
     env.check_flags()
     if env.rank == 0:
         mult = 1 if w["metric"].startswith("tp_") else env.world
@@ -836,7 +851,7 @@ def run_ours(args, rank, world, local_rank):
                 name = "decode" if decode else "prefill"
                 wl = build_tp(env, args, decode, setup=setup, fused=decode)
                 rec = measure_extra(env, wl, layer_steps if decode else max(50, min(layer_steps, 200)), 5, cpu=(world == 1),
-                                    graph=(decode and world == 1))
+                                    graph=(decode and (world == 1 or setup.fx is not None)))
                 parity = tp_parity(env, setup, wl)
                 if decode and world > 1 and setup.fx is not None:
                     alt = measure_extra(env, build_tp(env, args, True, setup=setup, fused=False), layer_steps, 5, cpu=False)

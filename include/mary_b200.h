@@ -173,8 +173,10 @@ int mb_nvfp4_gemv_w4a16(mb_ctx* ctx, mb_stream stream, const void* x_bf16, size_
  * weights left in f16: five instructions per four weights instead of eleven, the difference between an
  * instruction-bound kernel and one that streams weights at the HBM rate. A row holding a finite value outside
  * f16's normal range raises a flag in the workspace and the whole call takes the bf16 form above; either way
- * every product is exact in f32. A null or short workspace is the call above. */
-size_t mb_nvfp4_gemv_workspace(size_t rows, size_t k);
+ * every product is exact in f32. A weight with few rows and a long K (fewer than four 16-row blocks per SM) is
+ * also cut along K: the ranges' sums meet in the workspace and the block that arrives last adds them in range
+ * order, so the result does not depend on timing. A null or short workspace is the call above. */
+size_t mb_nvfp4_gemv_workspace(size_t rows, size_t n, size_t k);
 int mb_nvfp4_gemv_w4a16_ws(mb_ctx* ctx, mb_stream stream, const void* x_bf16, size_t rows, const uint8_t* codes,
                            const uint8_t* scales_rowmajor, float scale2, size_t n, size_t k, void* out, int out_dtype,
                            void* workspace, size_t workspace_bytes);

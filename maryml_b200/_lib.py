@@ -50,7 +50,7 @@ SIGNATURES = {
     "mb_nvfp4_tile_scales": (_i, [_vp, _vp, _vp, _sz, _sz, _vp]),
     "mb_nvfp4_untile_scales": (_i, [_vp, _vp, _vp, _sz, _sz, _vp]),
     "mb_nvfp4_gemv_w4a16": (_i, [_vp, _vp, _vp, _sz, _vp, _vp, _f, _sz, _sz, _vp, _i]),
-    "mb_nvfp4_gemv_workspace": (_sz, [_sz, _sz]),
+    "mb_nvfp4_gemv_workspace": (_sz, [_sz, _sz, _sz]),
     "mb_nvfp4_gemv_w4a16_ws": (_i, [_vp, _vp, _vp, _sz, _vp, _vp, _f, _sz, _sz, _vp, _i, _vp, _sz]),
     "mb_nvfp4_gemm_w4a4": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _f, _sz, _sz, _sz, _vp, _i, _i]),
     "mb_nvfp4_gemm_splitk_workspace": (_sz, [_sz, _sz, _sz]),

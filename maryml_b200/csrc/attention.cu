@@ -436,7 +436,13 @@ attn_decode_kernel(const __grid_constant__ AttnParams p) {
       const int kabs = int(k_begin + t * BC + key0);       // absolute index of this warp's first key
       float s[2][4];
       if (FP4) fp4_qk(s, qf, raw, lane);
-      else qk_tile<2>(s, qf, s0, key0, lane);
+      else {
+        qk_tile<2>(s, qf, s0, key0, lane);
+        if (t > 0) {
+          __syncwarp();
+          if (lane == 0) mbar_arrive(empty_bar(stage == 0 ? DEC_STAGES - 1 : stage - 1));   // the tile before this one
+        }
+      }
       int vis_lo = int(k_end) - kabs, vis_hi = vis_lo;
       if (p.causal) {
         vis_lo = min(vis_lo, int(qpos_lo) + 1 - kabs);
@@ -478,8 +484,10 @@ attn_decode_kernel(const __grid_constant__ AttnParams p) {
         issue(t + FP4_STAGES);
       } else {
         pv_tile<1>(o, s, s0 + 2 * TILE_HALF_BYTES, key0, lane);
-        __syncwarp();
-        if (lane == 0) mbar_arrive(empty_bar(stage));
+        // This tile's stage goes back to the producer only after the NEXT tile's scores (see the top of the loop):
+        // handing it back right here let the refill overtake the last ldmatrix reads of V on rare occasions, when
+        // the refill was a tile past the end of the keys (zero fill, no trip to memory) and the machine code had
+        // the arrive ahead of those reads. A whole QK^T pass between the last read and the arrive leaves no window.
         if (++stage == DEC_STAGES) { stage = 0; phase ^= 1u; }
       }
     }
@@ -647,9 +655,15 @@ attn_prefill_kernel(const __grid_constant__ AttnParams p) {
       const int kabs = int(t * BC);
       // a warp whose rows all lie before this tile (causal) has nothing to add
       const bool live = !p.causal || kabs <= qpos_lo + 8 + 7 - int(g);   // uniform: uses the warp's last row
+      float s[8][4];
+      if (live) qk_tile<8>(s, qf, s0, 0, lane);
+      // the stage of the tile BEFORE this one goes back to the producer here, a scores pass after its last read
+      // (the decode kernel says why)
+      if (t > 0) {
+        __syncwarp();
+        if (lane == 0) mbar_arrive(empty_bar(stage == 0 ? PRE_STAGES - 1 : stage - 1));
+      }
       if (live) {
-        float s[8][4];
-        qk_tile<8>(s, qf, s0, 0, lane);
         int vis_lo = int(p.keys) - kabs, vis_hi = vis_lo;
         if (p.causal) {
           vis_lo = min(vis_lo, qpos_lo + 1 - kabs);
@@ -658,8 +672,6 @@ attn_prefill_kernel(const __grid_constant__ AttnParams p) {
         softmax_step<8>(s, o, m, l, p.scale_log2, vis_lo, vis_hi, lane);
         pv_tile<4>(o, s, s0 + 2 * TILE_HALF_BYTES, 0, lane);
       }
-      __syncwarp();
-      if (lane == 0) mbar_arrive(empty_bar(stage));
       if (++stage == PRE_STAGES) { stage = 0; phase ^= 1u; }
     }
 #pragma unroll

@@ -37,11 +37,12 @@ constexpr int BK = 64;                        // K elements per step: one 128-by
 constexpr int CONV_WARPS = 16;
 constexpr int EPI_WARPS = 4;
 constexpr int THREADS = 32 * (2 + EPI_WARPS + CONV_WARPS);
-// The code-byte stream runs RAW_AHEAD steps ahead of the A stream. Its ring is deeper than that by three, so the
-// producer's wait for a free raw stage asks for a step the converters finished long ago and never holds back
-// the next A tile.
-constexpr int RAW_STAGES = 6;
-constexpr int RAW_AHEAD = 3;
+// The code bytes are the only operand that comes from HBM (the activation tile is shared by every CTA and stays in
+// L2), so their ring is what has to cover the memory latency: 64 KB per CTA, filled RAW_AHEAD steps ahead of the A
+// stream. The ring is deeper than that by three, so the producer's wait for a free raw stage asks for a step the
+// converters finished long ago and never holds back the next A tile.
+constexpr int RAW_RING_BYTES = 64 * 1024;
+constexpr int SCALE_AHEAD = 4;                // block-scale words a converter thread holds ahead of its step
 
 template <int BN>
 struct Cfg {
@@ -50,7 +51,9 @@ struct Cfg {
   static constexpr int OP_BYTES = A_BYTES + B_BYTES;
   static constexpr int OP_STAGES = BN == 256 ? 3 : 4;
   static constexpr int RAW_BYTES = BN * 32;
-  static constexpr int BAR_BYTES = 256;
+  static constexpr int RAW_STAGES = RAW_RING_BYTES / RAW_BYTES;     // 16 or 8
+  static constexpr int RAW_AHEAD = RAW_STAGES - 3;
+  static constexpr int BAR_BYTES = 512;
   static constexpr int SMEM_BYTES = OP_STAGES * OP_BYTES + RAW_STAGES * RAW_BYTES + 1024 + BAR_BYTES + EPI_WARPS * 512;
   static constexpr int TMEM_COLS = 2 * BN;   // 512 or 256: two accumulators
   static constexpr int TPR = 32 * CONV_WARPS / BN;   // converter threads per weight row: 2 or 4
@@ -132,6 +135,7 @@ template <int BN>
 __global__ void __launch_bounds__(THREADS, 1)
 gemm_w4a16_kernel(const __grid_constant__ W4a16Params p) {
   using C = Cfg<BN>;
+  constexpr int RAW_STAGES = C::RAW_STAGES, RAW_AHEAD = C::RAW_AHEAD;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
@@ -191,41 +195,57 @@ gemm_w4a16_kernel(const __grid_constant__ W4a16Params p) {
     ks0 = sp * kps;
   };
 
+  // A cursor over this CTA's K steps in order: the divisions of item() run once per work item, not per step.
+  struct Cursor {
+    uint32_t it, ks, mt, nt, ks0;     // item number, step inside it, and the item's coordinates
+  };
+  auto cursor_at0 = [&]() {
+    Cursor c{0u, 0u, 0u, 0u, 0u};
+    if (my_tiles) item(0u, c.mt, c.nt, c.ks0);
+    return c;
+  };
+  auto cursor_next = [&](Cursor& c) {
+    if (++c.ks == kps) {
+      c.ks = 0;
+      if (++c.it < my_tiles) item(c.it, c.mt, c.nt, c.ks0);
+    }
+  };
+
   if (warp == 0) {
     // ------------------------------ producer ------------------------------------
     uint32_t op_armed = 0, op_par = 0, raw_armed = 0, raw_par = 0;
     bool ok = true;
     // the code-byte stream: step j of this CTA belongs to tile blockIdx.x + (j / k_steps) * gridDim.x
-    auto issue_raw = [&](uint32_t j) -> bool {
-      const uint32_t rs = j % RAW_STAGES, ph = (j / RAW_STAGES) & 1u;
-      if (!mbar_wait(raw_empty(rs), ph ^ 1u, abort_smem, tflag, 31)) return false;
-      uint32_t mt, nt, ks0;
-      item(j / kps, mt, nt, ks0);
-      const uint32_t ks = ks0 + j % kps;
+    Cursor rc = cursor_at0(), ac = rc;              // the code-byte stream's position and the A stream's
+    uint32_t rj = 0, rs = 0, rph = 0;               // raw steps issued, their ring stage and phase
+    auto issue_raw = [&]() -> bool {
+      if (!mbar_wait(raw_empty(rs), rph ^ 1u, abort_smem, tflag, 31)) return false;
       raw_armed |= 1u << rs;
-      raw_par = (raw_par & ~(1u << rs)) | (ph << rs);
+      raw_par = (raw_par & ~(1u << rs)) | (rph << rs);
       if (elect_one()) {
         mbar_arrive_expect_tx(raw_full(rs), C::RAW_BYTES);
-        tma_load_2d(raw_base + rs * C::RAW_BYTES, &p.tmap_codes, int(ks * 32), int(nt * BN), raw_full(rs));
+        tma_load_2d(raw_base + rs * C::RAW_BYTES, &p.tmap_codes, int((rc.ks0 + rc.ks) * 32), int(rc.nt * BN), raw_full(rs));
       }
       __syncwarp();
+      cursor_next(rc);
+      ++rj;
+      if (++rs == uint32_t(RAW_STAGES)) { rs = 0; rph ^= 1u; }
       return true;
     };
-    for (uint32_t j = 0; ok && j < RAW_AHEAD && j < total_steps; ++j) ok = issue_raw(j);
+    while (ok && rj < uint32_t(RAW_AHEAD) && rj < total_steps) ok = issue_raw();
+    uint32_t os = 0, ph = 0;
     for (uint32_t i = 0; ok && i < total_steps; ++i) {
-      const uint32_t os = i % C::OP_STAGES, ph = (i / C::OP_STAGES) & 1u;
       if (!mbar_wait(op_empty(os), ph ^ 1u, abort_smem, tflag, 32)) { ok = false; break; }
-      uint32_t mt, nt, ks0;
-      item(i / kps, mt, nt, ks0);
-      const uint32_t ks = ks0 + i % kps;
       op_armed |= 1u << os;
       op_par = (op_par & ~(1u << os)) | (ph << os);
       if (elect_one()) {
         mbar_arrive_expect_tx(op_full(os), C::A_BYTES);
-        tma_load_2d(smem_base + os * C::OP_BYTES, &p.tmap_a, int(ks * BK), int(mt * BM), op_full(os));
+        tma_load_2d(smem_base + os * C::OP_BYTES, &p.tmap_a, int((ac.ks0 + ac.ks) * BK), int(ac.mt * BM), op_full(os));
       }
       __syncwarp();
-      if (i + RAW_AHEAD < total_steps && !issue_raw(i + RAW_AHEAD)) { ok = false; break; }
+      cursor_next(ac);
+      if (++os == uint32_t(C::OP_STAGES)) { os = 0; ph ^= 1u; }
+      if (rj < total_steps && !issue_raw()) { ok = false; break; }
     }
     if (!ok) {
       // leave no copy in flight: a bounded wait for every raw stage this warp armed (the operand stages'
@@ -330,19 +350,30 @@ gemm_w4a16_kernel(const __grid_constant__ W4a16Params p) {
     const uint32_t ct = threadIdx.x - 32u * (2 + EPI_WARPS);          // 0 .. 511
     const uint32_t r = ct / C::TPR, part = ct % C::TPR;               // weight row of the tile, part of the row
     constexpr int BLOCKS = 4 / C::TPR;                                // 16-value blocks per thread and step: 2 or 1
-    uint32_t sc_next = 0;
-    auto scale_word = [&](uint32_t j) -> uint32_t {
-      uint32_t mt, nt, ks0;
-      item(j / kps, mt, nt, ks0);
-      const uint32_t row = nt * BN + r;
-      return row < p.n ? __ldg(reinterpret_cast<const uint32_t*>(p.scales + size_t(row) * p.sc_stride) + ks0 + j % kps) : 0u;
+    // the four scale bytes of a step come from global memory (one word per row and step); a short queue in
+    // registers keeps the loads SCALE_AHEAD steps ahead of their use
+    Cursor sc_cur = cursor_at0();
+    uint32_t sc_j = 0;                               // steps whose scale word has been asked for
+    auto scale_word = [&]() -> uint32_t {
+      uint32_t w = 0u;
+      if (sc_j < total_steps) {
+        const uint32_t row = sc_cur.nt * BN + r;
+        if (row < p.n)
+          w = __ldg(reinterpret_cast<const uint32_t*>(p.scales + size_t(row) * p.sc_stride) + sc_cur.ks0 + sc_cur.ks);
+        cursor_next(sc_cur);
+      }
+      ++sc_j;
+      return w;
     };
-    if (total_steps) sc_next = scale_word(0);
+    uint32_t sq[SCALE_AHEAD];
+#pragma unroll
+    for (int j = 0; j < SCALE_AHEAD; ++j) sq[j] = scale_word();
+    uint32_t rs = 0, rph = 0, os = 0, oph = 0;
     for (uint32_t i = 0; i < total_steps; ++i) {
-      const uint32_t sc = sc_next;
-      if (i + 1 < total_steps) sc_next = scale_word(i + 1);            // one step ahead of its use
-      const uint32_t rs = i % RAW_STAGES, rph = (i / RAW_STAGES) & 1u;
-      const uint32_t os = i % C::OP_STAGES, oph = (i / C::OP_STAGES) & 1u;
+      const uint32_t sc = sq[0];
+#pragma unroll
+      for (int j = 0; j + 1 < SCALE_AHEAD; ++j) sq[j] = sq[j + 1];
+      sq[SCALE_AHEAD - 1] = scale_word();
       if (!mbar_wait(raw_full(rs), rph, abort_smem, tflag, 36)) break;
       if (!mbar_wait(op_empty(os), oph ^ 1u, abort_smem, tflag, 37)) break;
       const uint8_t* raw = smem_gen + (raw_base - smem_base) + rs * C::RAW_BYTES + r * 32 + part * (32 / C::TPR);
@@ -368,6 +399,8 @@ gemm_w4a16_kernel(const __grid_constant__ W4a16Params p) {
         mbar_arrive(op_full(os));
         mbar_arrive(raw_empty(rs));
       }
+      if (++rs == uint32_t(RAW_STAGES)) { rs = 0; rph ^= 1u; }
+      if (++os == uint32_t(C::OP_STAGES)) { os = 0; oph ^= 1u; }
     }
   }
 

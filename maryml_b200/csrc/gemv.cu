@@ -68,15 +68,26 @@ __device__ __forceinline__ void mma_f16_acc(float* d, uint32_t a0, uint32_t a1, 
 // (exact: the conversion pass refuses values f16 cannot hold), the decoded weights stay f16, and the expansion costs
 // five instructions per four weights instead of eleven, which is what separates an instruction-bound kernel from
 // one that streams weights at the HBM rate.
+// K slices (128 values each) may be cut into `ksplit` ranges over blockIdx.y, so that a weight with few rows and a
+// long K still puts several blocks on every SM: each range's sums go to `partials` and the block that arrives last
+// at the row block's counter adds them in range order (deterministic) and stores the result.
+struct GemvSplit {
+  uint32_t ksplit;          // 1: no split, the fields below are unused
+  float* partials;          // [ksplit][row blocks][16 weight rows x 8 activation rows]
+  int* counters;            // one per row block, zero between calls
+};
+
 template <bool F16, typename O>
 __device__ __forceinline__ void gemv_body(const uint4* __restrict__ x, const uint4* __restrict__ codes,
                                           const uint8_t* __restrict__ scales, O* __restrict__ out, uint32_t rows, uint32_t n,
-                                          uint32_t k, float scale2, float (*part)[16][8]) {
+                                          uint32_t k, float scale2, float (*part)[16][8], const GemvSplit& sp) {
   const uint32_t lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const uint32_t g = lane >> 2, t = lane & 3;
   const uint32_t row_base = blockIdx.x * 16;
   const uint32_t r0 = min(row_base + g, n - 1), r1 = min(row_base + g + 8, n - 1);   // loads stay inside the planes
-  const uint32_t slices = (k + 127) / 128;
+  const uint32_t all_slices = (k + 127) / 128;
+  const uint32_t per_split = (all_slices + sp.ksplit - 1) / sp.ksplit;
+  const uint32_t sl_begin = blockIdx.y * per_split, slices = min(all_slices, sl_begin + per_split);
   const uint4* c0 = codes + size_t(r0) * (k / 32);
   const uint4* c1 = codes + size_t(r1) * (k / 32);
   const uint16_t* s0p = reinterpret_cast<const uint16_t*>(scales + size_t(r0) * (k / 16));
@@ -85,13 +96,13 @@ __device__ __forceinline__ void gemv_body(const uint4* __restrict__ x, const uin
   const bool x_live = g < rows;
   float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
   constexpr int U = 4;                                   // slices whose weight loads are in flight together
-  for (uint32_t sl0 = warp; sl0 < slices; sl0 += GEMV_WARPS * U) {
+  for (uint32_t sl0 = sl_begin + warp; sl0 < slices; sl0 += GEMV_WARPS * U) {
     uint4 wa[U], wb[U];
     uint32_t sa[U], sb[U];
 #pragma unroll
     for (int u = 0; u < U; ++u) {
       const uint32_t k0 = (sl0 + u * GEMV_WARPS) * 128 + t * 32;    // this lane's 32 values of the slice
-      const bool live = k0 < k;                            // k is a multiple of 32: a group is whole or absent
+      const bool live = sl0 + u * GEMV_WARPS < slices && k0 < k;   // k is a multiple of 32: a group is whole or absent
       wa[u] = live ? __ldg(c0 + k0 / 32) : make_uint4(0u, 0u, 0u, 0u);
       wb[u] = live ? __ldg(c1 + k0 / 32) : make_uint4(0u, 0u, 0u, 0u);
       sa[u] = live ? uint32_t(__ldg(s0p + k0 / 32)) : 0u;
@@ -137,13 +148,28 @@ __device__ __forceinline__ void gemv_body(const uint4* __restrict__ x, const uin
   part[warp][g + 8][2 * t] = acc[2];
   part[warp][g + 8][2 * t + 1] = acc[3];
   __syncthreads();
+  const uint32_t wr = (threadIdx.x >> 3) & 15, ar = threadIdx.x & 7;
+  float sum = 0.0f;
   if (threadIdx.x < 128) {
-    const uint32_t wr = threadIdx.x >> 3, ar = threadIdx.x & 7;
-    float sum = 0.0f;
 #pragma unroll
     for (int w = 0; w < GEMV_WARPS; ++w) sum += part[w][wr][ar];
-    if (ar < rows && row_base + wr < n) out[size_t(ar) * n + row_base + wr] = O(sum * scale2);
   }
+  if (sp.ksplit > 1) {
+    __shared__ int s_last;
+    const size_t stride = size_t(gridDim.x) * 128;
+    if (threadIdx.x < 128) sp.partials[blockIdx.y * stride + size_t(blockIdx.x) * 128 + threadIdx.x] = sum;
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) s_last = atomicAdd(sp.counters + blockIdx.x, 1) == int(sp.ksplit) - 1;
+    __syncthreads();
+    if (!s_last) return;
+    __threadfence();
+    if (threadIdx.x == 0) sp.counters[blockIdx.x] = 0;                 // ready for the next call
+    sum = 0.0f;
+    if (threadIdx.x < 128)
+      for (uint32_t y = 0; y < sp.ksplit; ++y) sum += __ldcg(sp.partials + y * stride + size_t(blockIdx.x) * 128 + threadIdx.x);
+  }
+  if (threadIdx.x < 128 && ar < rows && row_base + wr < n) out[size_t(ar) * n + row_base + wr] = O(sum * scale2);
 }
 
 template <typename O>
@@ -151,7 +177,7 @@ __global__ void __launch_bounds__(32 * GEMV_WARPS)
 gemv_w4a16_kernel(const uint4* __restrict__ x, const uint4* __restrict__ codes, const uint8_t* __restrict__ scales,
                   O* __restrict__ out, uint32_t rows, uint32_t n, uint32_t k, float scale2) {
   __shared__ float part[GEMV_WARPS][16][8];
-  gemv_body<false, O>(x, codes, scales, out, rows, n, k, scale2, part);
+  gemv_body<false, O>(x, codes, scales, out, rows, n, k, scale2, part, GemvSplit{1u, nullptr, nullptr});
 }
 
 // The same with the f16 copy of the activations when every row converted exactly (flags all zero), else with the
@@ -160,24 +186,28 @@ template <typename O>
 __global__ void __launch_bounds__(32 * GEMV_WARPS)
 gemv_w4a16_dual_kernel(const uint4* __restrict__ x, const uint4* __restrict__ x_f16, const int* __restrict__ inexact,
                        const uint4* __restrict__ codes, const uint8_t* __restrict__ scales, O* __restrict__ out,
-                       uint32_t rows, uint32_t n, uint32_t k, float scale2) {
+                       uint32_t rows, uint32_t n, uint32_t k, float scale2, const GemvSplit sp) {
   __shared__ float part[GEMV_WARPS][16][8];
   mb_grid_dependency_sync();                 // the conversion pass before this kernel wrote x_f16 and the flags
   int any = 0;
   for (uint32_t r = 0; r < rows; ++r) any |= __ldg(inexact + r);
-  if (any) gemv_body<false, O>(x, codes, scales, out, rows, n, k, scale2, part);
-  else gemv_body<true, O>(x_f16, codes, scales, out, rows, n, k, scale2, part);
+  if (any) gemv_body<false, O>(x, codes, scales, out, rows, n, k, scale2, part, sp);
+  else gemv_body<true, O>(x_f16, codes, scales, out, rows, n, k, scale2, part, sp);
 }
 
 // One block per activation row: bf16 -> f16, exact when the value is zero, infinite, NaN or a normal f16 (bf16 has
 // 8 significant bits, f16 has 11); a finite value outside f16's normal range raises the row's flag.
 __global__ void __launch_bounds__(256)
-gemv_x_to_f16_kernel(const uint4* __restrict__ x, uint4* __restrict__ x_f16, int* __restrict__ inexact, uint32_t k8) {
+gemv_x_to_f16_kernel(const uint4* __restrict__ x, uint4* __restrict__ x_f16, int* __restrict__ inexact, uint32_t k8,
+                     int* __restrict__ counters, uint32_t n_counters) {
   __shared__ int s_bad;
   if (threadIdx.x == 0) s_bad = 0;
   __syncthreads();
   mb_grid_dependency_sync();                 // the rows come from the kernel before this one
   const uint32_t row = blockIdx.x;
+  // the K-split counters of the product that follows (a workspace arrives with any content)
+  if (row == 0)
+    for (uint32_t i = threadIdx.x; i < n_counters; i += 256) counters[i] = 0;
   int bad = 0;
   for (uint32_t i = threadIdx.x; i < k8; i += 256) {
     const uint4 v = __ldg(x + size_t(row) * k8 + i);
@@ -387,39 +417,74 @@ MB_API int mb_nvfp4_gemv_w4a16(mb_ctx* ctx, mb_stream stream_, const void* x_bf1
   return MB_OK;
 }
 
-MB_API size_t mb_nvfp4_gemv_workspace(size_t rows, size_t k) {
-  if (rows == 0 || rows > MAX_ROWS || k == 0 || k % 32 != 0) return 0;
-  return 256 + rows * k * 2;
+namespace {
+
+// Ranges of K slices per row block: doubled while the grid would leave fewer than four blocks per SM and every
+// warp of a range still has a slice of its own.
+uint32_t gemv_ksplit(size_t n, size_t k) {
+  const size_t blocks = (n + 15) / 16, slices = (k + 127) / 128;
+  uint32_t s = 1;
+  while (blocks * s < 592 && s < 8 && slices / (2 * s) >= size_t(GEMV_WARPS)) s *= 2;
+  return s;
+}
+
+struct GemvWorkspace {
+  size_t counters_off, partials_off, x16_off, bytes;
+  uint32_t ksplit, row_blocks;
+};
+
+GemvWorkspace gemv_workspace_plan(size_t rows, size_t n, size_t k) {
+  GemvWorkspace w;
+  w.ksplit = gemv_ksplit(n, k);
+  w.row_blocks = uint32_t((n + 15) / 16);
+  w.counters_off = 256;                                                     // the rows' flags come first
+  w.partials_off = w.counters_off + ((size_t(w.row_blocks) * 4 + 255) & ~size_t(255));
+  const size_t partials = w.ksplit > 1 ? size_t(w.ksplit) * w.row_blocks * 128 * sizeof(float) : 0;
+  w.x16_off = w.partials_off + ((partials + 255) & ~size_t(255));
+  w.bytes = w.x16_off + rows * k * 2;
+  return w;
+}
+
+}  // namespace
+
+MB_API size_t mb_nvfp4_gemv_workspace(size_t rows, size_t n, size_t k) {
+  if (rows == 0 || rows > MAX_ROWS || n == 0 || k == 0 || k % 32 != 0) return 0;
+  return gemv_workspace_plan(rows, n, k).bytes;
 }
 
 MB_API int mb_nvfp4_gemv_w4a16_ws(mb_ctx* ctx, mb_stream stream_, const void* x_bf16, size_t rows, const uint8_t* codes,
                                   const uint8_t* scales, float scale2, size_t n, size_t k, void* out, int out_dtype,
                                   void* workspace, size_t workspace_bytes) {
   cudaStream_t stream = static_cast<cudaStream_t>(stream_);
-  if (!workspace || workspace_bytes < mb_nvfp4_gemv_workspace(rows, k) || mb_nvfp4_gemv_workspace(rows, k) == 0)
+  const size_t need = mb_nvfp4_gemv_workspace(rows, n, k);
+  if (!workspace || need == 0 || workspace_bytes < need)
     return mb_nvfp4_gemv_w4a16(ctx, stream_, x_bf16, rows, codes, scales, scale2, n, k, out, out_dtype);
   MB_REQUIRE(ctx, ctx && x_bf16 && codes && scales && out, "gemv: null argument");
-  MB_REQUIRE(ctx, n > 0 && n * k <= 0xFFFFFFFFull, "NVFP4 weight exceeds u32 indexing");
+  MB_REQUIRE(ctx, n * k <= 0xFFFFFFFFull, "NVFP4 weight exceeds u32 indexing");
   MB_REQUIRE(ctx, scale2 == scale2 && scale2 > 0.0f && scale2 <= 3.4e38f,
              "NVFP4 global scale %g is not a positive finite number", double(scale2));
   MB_REQUIRE(ctx, mb_aligned(x_bf16, 16) && mb_aligned(workspace, 256), "NVFP4 GEMV needs a 16-byte aligned activation and a 256-byte aligned workspace");
   MB_REQUIRE(ctx, mb_aligned(codes, 16) && mb_aligned(scales, 2), "NVFP4 GEMV needs 16-byte aligned code rows");
   MB_REQUIRE(ctx, out_dtype == MB_DT_BF16 || out_dtype == MB_DT_F32, "gemv: output is bf16 or f32");
-  int* flags = static_cast<int*>(workspace);
-  uint4* x16 = reinterpret_cast<uint4*>(static_cast<uint8_t*>(workspace) + 256);
+  const GemvWorkspace w = gemv_workspace_plan(rows, n, k);
+  uint8_t* base = static_cast<uint8_t*>(workspace);
+  int* flags = reinterpret_cast<int*>(base);
+  int* counters = reinterpret_cast<int*>(base + w.counters_off);
+  uint4* x16 = reinterpret_cast<uint4*>(base + w.x16_off);
+  const GemvSplit sp{w.ksplit, reinterpret_cast<float*>(base + w.partials_off), counters};
   MB_CUDA_OK(ctx, mb_launch_pdl(gemv_x_to_f16_kernel, dim3(unsigned(rows)), dim3(256), 0, stream,
-                                static_cast<const uint4*>(x_bf16), x16, flags, uint32_t(k / 8)));
-  const dim3 grid(unsigned((n + 15) / 16)), block(32 * GEMV_WARPS);
+                                static_cast<const uint4*>(x_bf16), x16, flags, uint32_t(k / 8), counters, w.row_blocks));
+  const dim3 grid(w.row_blocks, w.ksplit), block(32 * GEMV_WARPS);
   if (out_dtype == MB_DT_BF16)
     MB_CUDA_OK(ctx, mb_launch_pdl(gemv_w4a16_dual_kernel<__nv_bfloat16>, grid, block, 0, stream,
                                   static_cast<const uint4*>(x_bf16), static_cast<const uint4*>(x16), static_cast<const int*>(flags),
                                   reinterpret_cast<const uint4*>(codes), scales, static_cast<__nv_bfloat16*>(out),
-                                  uint32_t(rows), uint32_t(n), uint32_t(k), scale2));
+                                  uint32_t(rows), uint32_t(n), uint32_t(k), scale2, sp));
   else
     MB_CUDA_OK(ctx, mb_launch_pdl(gemv_w4a16_dual_kernel<float>, grid, block, 0, stream, static_cast<const uint4*>(x_bf16),
                                   static_cast<const uint4*>(x16), static_cast<const int*>(flags),
                                   reinterpret_cast<const uint4*>(codes), scales, static_cast<float*>(out), uint32_t(rows),
-                                  uint32_t(n), uint32_t(k), scale2));
+                                  uint32_t(n), uint32_t(k), scale2, sp));
   MB_LAUNCH_OK(ctx);
   return MB_OK;
 }

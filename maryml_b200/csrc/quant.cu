@@ -248,11 +248,28 @@ dequantize_kernel(const uint2* __restrict__ codes, const uint8_t* __restrict__ s
   if (blk >= blocks) return;
   uint2 c = codes[blk];
   float unit = __fmul_rn(mb_e4m3_to_f32(scales[blk]), scale2);
-  O* o = out + blk * 16;
+  float v[16];
 #pragma unroll
   for (int i = 0; i < 8; ++i) {
-    o[i] = O(__fmul_rn(mb_e2m1_to_f32(c.x >> (4 * i)), unit));
-    o[8 + i] = O(__fmul_rn(mb_e2m1_to_f32(c.y >> (4 * i)), unit));
+    v[i] = __fmul_rn(mb_e2m1_to_f32(c.x >> (4 * i)), unit);
+    v[8 + i] = __fmul_rn(mb_e2m1_to_f32(c.y >> (4 * i)), unit);
+  }
+  // a block's sixteen values leave as 16-byte stores: consecutive threads write consecutive 32 (bf16) or 64 (f32)
+  // byte pieces of the plane (out + blk * 16 is 32-byte aligned when `out` is)
+  if (sizeof(O) == 2) {
+    uint32_t w[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      __nv_bfloat162 p2 = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
+      w[i] = *reinterpret_cast<uint32_t*>(&p2);
+    }
+    uint4* o = reinterpret_cast<uint4*>(out + blk * 16);
+    o[0] = make_uint4(w[0], w[1], w[2], w[3]);
+    o[1] = make_uint4(w[4], w[5], w[6], w[7]);
+  } else {
+    float4* o = reinterpret_cast<float4*>(out + blk * 16);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) o[i] = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
   }
 }
 
@@ -494,7 +511,7 @@ MB_API int mb_nvfp4_dequantize(mb_ctx* ctx, mb_stream stream_, const uint8_t* co
   cudaStream_t stream = static_cast<cudaStream_t>(stream_);
   MB_REQUIRE(ctx, ctx && codes && scales && out, "dequantize: null argument");
   MB_REQUIRE(ctx, rows > 0 && k > 0 && k % 16 == 0, "dequantize: k must be a positive multiple of 16");
-  MB_REQUIRE(ctx, mb_aligned(codes, 8), "dequantize: codes need 8-byte alignment");
+  MB_REQUIRE(ctx, mb_aligned(codes, 8) && mb_aligned(out, 16), "dequantize: codes need 8-byte and the output 16-byte alignment");
   size_t blocks = rows * k / 16;
   unsigned grid = unsigned((blocks + 255) / 256);
   if (out_dtype == MB_DT_F32)

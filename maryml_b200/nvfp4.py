@@ -20,6 +20,7 @@ from ._lib import lib, context, MaryError
 
 GROUP = 16        # weights per E4M3 block scale (src/nn/nvfp4_gemv.rs:65)
 CHUNK = 32        # weights one GEMV lane takes per step (:67)
+W4A16_FUSED_ROWS = 512
 MAX_ROWS = 8      # activation rows the GEMV takes (:73)
 KTILE4 = 64       # K of the block-scaled instruction (src/nn/nvfp4_gemm.rs:43)
 NTILE = 8
@@ -354,7 +355,7 @@ class Nvfp4:
         assert 1 <= rows <= MAX_ROWS, f"NVFP4 GEMV takes 1..={MAX_ROWS} rows"
         ctx = context(self._device.index)
         out = torch.empty((1, rows, self._n), dtype=self._dtype, device=self._device)
-        need = int(lib.mb_nvfp4_gemv_workspace(rows, self._k))
+        need = int(lib.mb_nvfp4_gemv_workspace(rows, self._n, self._k))
         ws = _gemv_workspace(self._device, need)
         ctx.check(lib.mb_nvfp4_gemv_w4a16_ws(ctx.handle, _stream(), _p(x), rows, _p(self.codes), _p(self.scales),
                                              self.scale2, self._n, self._k, _p(out), _lib.DT_BF16, _p(ws), need))
@@ -408,8 +409,13 @@ class Nvfp4:
         # The weight stays four bits in HBM: code x block scale is expanded to bf16 (exact) between shared
         # memory and the tensor core, f32 accumulation, scale2 applied once to the accumulator, as in the
         # reference's W4A16 kernel. k % 64 != 0 (the reference's W4A16 takes k % 32) goes through a decoded
-        # scratch plane and the bf16 product instead (MB_W4A16_FUSED=0 sends every shape that way, for comparison).
-        if self._k % KTILE4 == 0 and x2.data_ptr() % 16 == 0 and os.environ.get("MB_W4A16_FUSED", "1") != "0":
+        # scratch plane and the bf16 product instead, and so do prompts beyond W4A16_FUSED_ROWS rows: there the
+        # product is bound by the tensor core, the decode of a weight tile would be repeated for every row tile, and
+        # decoding once (the same exact values) costs a few percent of the product. MB_W4A16_FUSED=0 / 1 forces
+        # one way for comparison.
+        fused = os.environ.get("MB_W4A16_FUSED")
+        fused = (t <= W4A16_FUSED_ROWS) if fused is None else fused != "0"
+        if fused and self._k % KTILE4 == 0 and x2.data_ptr() % 16 == 0:
             return w4a16_gemm(x2, self.codes, self.scales, self.scale2, self._n, self._k, out_dtype=self._dtype)
         w = dequantize(self.codes, self.scales, 1.0, self._n, self._k, dtype=torch.bfloat16)
         return bf16_gemm(x2, w, out_dtype=self._dtype, alpha=self.scale2)
