@@ -39,6 +39,7 @@ enum : uint32_t {
   MB_ONCE_ATTN_STATIC = 1u << 7,
   MB_ONCE_GEMM_W4A16_256 = 1u << 8,
   MB_ONCE_GEMM_W4A16_128 = 1u << 9,
+  MB_ONCE_GEMV_RING = 1u << 10,
 };
 
 struct mb_ctx {

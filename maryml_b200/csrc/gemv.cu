@@ -77,6 +77,43 @@ struct GemvSplit {
   int* counters;            // one per row block, zero between calls
 };
 
+// The warps' sums of one row block meet in shared memory; with a K split the ranges' sums meet in the workspace.
+template <typename O>
+__device__ __forceinline__ void gemv_finish(const float* acc, O* __restrict__ out, uint32_t rows, uint32_t n, float scale2,
+                                            float (*part)[16][8], const GemvSplit& sp) {
+  const uint32_t lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const uint32_t g = lane >> 2, t = lane & 3;
+  const uint32_t row_base = blockIdx.x * 16;
+  // acc[0], acc[1]: weight row g, activation rows 2t, 2t+1; acc[2], acc[3]: weight row g + 8
+  part[warp][g][2 * t] = acc[0];
+  part[warp][g][2 * t + 1] = acc[1];
+  part[warp][g + 8][2 * t] = acc[2];
+  part[warp][g + 8][2 * t + 1] = acc[3];
+  __syncthreads();
+  const uint32_t wr = (threadIdx.x >> 3) & 15, ar = threadIdx.x & 7;
+  float sum = 0.0f;
+  if (threadIdx.x < 128) {
+#pragma unroll
+    for (int w = 0; w < GEMV_WARPS; ++w) sum += part[w][wr][ar];
+  }
+  if (sp.ksplit > 1) {
+    __shared__ int s_last;
+    const size_t stride = size_t(gridDim.x) * 128;
+    if (threadIdx.x < 128) sp.partials[blockIdx.y * stride + size_t(blockIdx.x) * 128 + threadIdx.x] = sum;
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) s_last = atomicAdd(sp.counters + blockIdx.x, 1) == int(sp.ksplit) - 1;
+    __syncthreads();
+    if (!s_last) return;
+    __threadfence();
+    if (threadIdx.x == 0) sp.counters[blockIdx.x] = 0;                 // ready for the next call
+    sum = 0.0f;
+    if (threadIdx.x < 128)
+      for (uint32_t y = 0; y < sp.ksplit; ++y) sum += __ldcg(sp.partials + y * stride + size_t(blockIdx.x) * 128 + threadIdx.x);
+  }
+  if (threadIdx.x < 128 && ar < rows && row_base + wr < n) out[size_t(ar) * n + row_base + wr] = O(sum * scale2);
+}
+
 template <bool F16, typename O>
 __device__ __forceinline__ void gemv_body(const uint4* __restrict__ x, const uint4* __restrict__ codes,
                                           const uint8_t* __restrict__ scales, O* __restrict__ out, uint32_t rows, uint32_t n,
@@ -142,34 +179,103 @@ __device__ __forceinline__ void gemv_body(const uint4* __restrict__ x, const uin
       }
     }
   }
-  // acc[0], acc[1]: weight row g, activation rows 2t, 2t+1; acc[2], acc[3]: weight row g + 8
-  part[warp][g][2 * t] = acc[0];
-  part[warp][g][2 * t + 1] = acc[1];
-  part[warp][g + 8][2 * t] = acc[2];
-  part[warp][g + 8][2 * t + 1] = acc[3];
-  __syncthreads();
-  const uint32_t wr = (threadIdx.x >> 3) & 15, ar = threadIdx.x & 7;
-  float sum = 0.0f;
-  if (threadIdx.x < 128) {
+  gemv_finish(acc, out, rows, n, scale2, part, sp);
+}
+
+// The same product with the weight bytes streamed through a ring of cp.async copies per warp (k % 128 == 0).
+// In the body above a warp holds four slices of loads in registers, computes, and only then asks for more; two
+// blocks fit an SM, so about 64 KB per SM are in flight, with gaps. Here every warp keeps GEMV_RING slices (16
+// weight rows x 64 code bytes + 16 x 8 scale bytes each) in flight in shared memory all the time, three blocks fit
+// an SM, and the next slice's activation chunk is loaded while the current one is multiplied. A lane copies the two
+// 16-byte code chunks it will itself read; lanes 0-15 copy one row's eight scale bytes, which other lanes read, so
+// a __syncwarp stands on both sides of a slot's use.
+constexpr int GEMV_RING = 6;
+constexpr int GEMV_SLICE_BYTES = 16 * 64 + 16 * 8;
+constexpr int GEMV_RING_SMEM = GEMV_WARPS * GEMV_RING * GEMV_SLICE_BYTES;
+
+template <bool F16, typename O>
+__device__ __forceinline__ void gemv_body_ring(const uint4* __restrict__ x, const uint4* __restrict__ codes,
+                                               const uint8_t* __restrict__ scales, O* __restrict__ out, uint32_t rows,
+                                               uint32_t n, uint32_t k, float scale2, float (*part)[16][8],
+                                               const GemvSplit& sp, uint8_t* ring_all) {
+  const uint32_t lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const uint32_t g = lane >> 2, t = lane & 3;
+  const uint32_t row_base = blockIdx.x * 16;
+  const uint32_t r0 = min(row_base + g, n - 1), r1 = min(row_base + g + 8, n - 1);   // loads stay inside the planes
+  const uint32_t all_slices = k / 128;
+  const uint32_t per_split = (all_slices + sp.ksplit - 1) / sp.ksplit;
+  const uint32_t sl_begin = blockIdx.y * per_split, sl_end = min(all_slices, sl_begin + per_split);
+  // this warp's slices: sl_begin + warp, + GEMV_WARPS, ...
+  const uint32_t first = sl_begin + warp;
+  const uint32_t mine = first < sl_end ? (sl_end - first + GEMV_WARPS - 1) / GEMV_WARPS : 0u;
+  uint8_t* ring = ring_all + warp * (GEMV_RING * GEMV_SLICE_BYTES);
+  const uint32_t ring_s = uint32_t(__cvta_generic_to_shared(ring));
+  const uint8_t* c0 = reinterpret_cast<const uint8_t*>(codes) + size_t(r0) * (k / 2) + t * 16;
+  const uint8_t* c1 = reinterpret_cast<const uint8_t*>(codes) + size_t(r1) * (k / 2) + t * 16;
+  const uint8_t* sc = scales + size_t(min(row_base + (lane & 15u), n - 1)) * (k / 16);
+  auto issue = [&](uint32_t j) {                       // j-th slice of this warp; an empty group keeps the count uniform
+    if (j < mine) {
+      const uint32_t sl = first + j * GEMV_WARPS;
+      const uint32_t dst = ring_s + (j % GEMV_RING) * GEMV_SLICE_BYTES;
+      asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst + g * 64 + t * 16), "l"(c0 + size_t(sl) * 64) : "memory");
+      asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst + (g + 8) * 64 + t * 16), "l"(c1 + size_t(sl) * 64) : "memory");
+      if (lane < 16)
+        asm volatile("cp.async.ca.shared.global [%0], [%1], 8;" ::"r"(dst + 1024 + lane * 8), "l"(sc + size_t(sl) * 8) : "memory");
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");
+  };
+  const uint4* xr = x + size_t(g) * (k / 8) + t * 4;
+  const bool x_live = g < rows;
+  auto load_x = [&](uint32_t j, uint4* xv) {
+    const bool live = x_live && j < mine;
+    const uint4* src = xr + size_t(first + j * GEMV_WARPS) * 16;
 #pragma unroll
-    for (int w = 0; w < GEMV_WARPS; ++w) sum += part[w][wr][ar];
+    for (int i = 0; i < 4; ++i) xv[i] = live ? __ldg(src + i) : make_uint4(0u, 0u, 0u, 0u);
+  };
+#pragma unroll
+  for (int j = 0; j < GEMV_RING; ++j) issue(uint32_t(j));
+  float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+  uint4 xv[4], xn[4];
+  load_x(0, xv);
+  for (uint32_t j = 0; j < mine; ++j) {
+    load_x(j + 1, xn);
+    asm volatile("cp.async.wait_group %0;" ::"n"(GEMV_RING - 1) : "memory");
+    __syncwarp();
+    const uint8_t* slot = ring + (j % GEMV_RING) * GEMV_SLICE_BYTES;
+    const uint4 wa = *reinterpret_cast<const uint4*>(slot + g * 64 + t * 16);
+    const uint4 wb = *reinterpret_cast<const uint4*>(slot + (g + 8) * 64 + t * 16);
+    const uint32_t sa = *reinterpret_cast<const uint16_t*>(slot + 1024 + g * 8 + t * 2);
+    const uint32_t sb = *reinterpret_cast<const uint16_t*>(slot + 1024 + (g + 8) * 8 + t * 2);
+    __syncwarp();                                        // every lane has taken its bytes: the slot may be refilled
+    issue(j + GEMV_RING);
+    uint32_t sah, sbh;
+    asm("cvt.rn.f16x2.e4m3x2 %0, %1;" : "=r"(sah) : "h"(uint16_t(sa)));
+    asm("cvt.rn.f16x2.e4m3x2 %0, %1;" : "=r"(sbh) : "h"(uint16_t(sb)));
+    const __half2 sa2 = *reinterpret_cast<__half2*>(&sah), sb2 = *reinterpret_cast<__half2*>(&sbh);
+    const __half2 sa_lo = __low2half2(sa2), sa_hi = __high2half2(sa2);
+    const __half2 sb_lo = __low2half2(sb2), sb_hi = __high2half2(sb2);
+    const uint32_t wwa[4] = {wa.x, wa.y, wa.z, wa.w}, wwb[4] = {wb.x, wb.y, wb.z, wb.w};
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {                        // instruction i takes values 4 i .. 4 i + 3 of the lane's 32
+      const uint32_t ba = (wwa[i >> 1] >> ((i & 1) * 16)) & 0xFFFFu, bb = (wwb[i >> 1] >> ((i & 1) * 16)) & 0xFFFFu;
+      uint32_t a0, a1, a2, a3;
+      const uint4& xq = xv[i >> 1];
+      const uint32_t b0 = (i & 1) ? xq.z : xq.x, b1 = (i & 1) ? xq.w : xq.y;
+      if (F16) {
+        decode4_f16(ba, i < 4 ? sa_lo : sa_hi, a0, a2);
+        decode4_f16(bb, i < 4 ? sb_lo : sb_hi, a1, a3);
+        mma_f16_acc(acc, a0, a1, a2, a3, b0, b1);
+      } else {
+        decode4(ba, i < 4 ? sa_lo : sa_hi, a0, a2);
+        decode4(bb, i < 4 ? sb_lo : sb_hi, a1, a3);
+        mma_bf16(acc, a0, a1, a2, a3, b0, b1);
+      }
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i) xv[i] = xn[i];
   }
-  if (sp.ksplit > 1) {
-    __shared__ int s_last;
-    const size_t stride = size_t(gridDim.x) * 128;
-    if (threadIdx.x < 128) sp.partials[blockIdx.y * stride + size_t(blockIdx.x) * 128 + threadIdx.x] = sum;
-    __threadfence();
-    __syncthreads();
-    if (threadIdx.x == 0) s_last = atomicAdd(sp.counters + blockIdx.x, 1) == int(sp.ksplit) - 1;
-    __syncthreads();
-    if (!s_last) return;
-    __threadfence();
-    if (threadIdx.x == 0) sp.counters[blockIdx.x] = 0;                 // ready for the next call
-    sum = 0.0f;
-    if (threadIdx.x < 128)
-      for (uint32_t y = 0; y < sp.ksplit; ++y) sum += __ldcg(sp.partials + y * stride + size_t(blockIdx.x) * 128 + threadIdx.x);
-  }
-  if (threadIdx.x < 128 && ar < rows && row_base + wr < n) out[size_t(ar) * n + row_base + wr] = O(sum * scale2);
+  asm volatile("cp.async.wait_group 0;" ::: "memory");   // nothing of this warp's is in flight when the block ends
+  gemv_finish(acc, out, rows, n, scale2, part, sp);
 }
 
 template <typename O>
@@ -177,22 +283,30 @@ __global__ void __launch_bounds__(32 * GEMV_WARPS)
 gemv_w4a16_kernel(const uint4* __restrict__ x, const uint4* __restrict__ codes, const uint8_t* __restrict__ scales,
                   O* __restrict__ out, uint32_t rows, uint32_t n, uint32_t k, float scale2) {
   __shared__ float part[GEMV_WARPS][16][8];
-  gemv_body<false, O>(x, codes, scales, out, rows, n, k, scale2, part, GemvSplit{1u, nullptr, nullptr});
+  extern __shared__ __align__(16) uint8_t gemv_ring[];      // GEMV_RING_SMEM bytes when k % 128 == 0, else none
+  if (k % 128 == 0) gemv_body_ring<false, O>(x, codes, scales, out, rows, n, k, scale2, part, GemvSplit{1u, nullptr, nullptr}, gemv_ring);
+  else gemv_body<false, O>(x, codes, scales, out, rows, n, k, scale2, part, GemvSplit{1u, nullptr, nullptr});
 }
 
 // The same with the f16 copy of the activations when every row converted exactly (flags all zero), else with the
 // caller's bf16 rows; the choice is uniform over the grid.
 template <typename O>
-__global__ void __launch_bounds__(32 * GEMV_WARPS)
+__global__ void __launch_bounds__(32 * GEMV_WARPS, 3)
 gemv_w4a16_dual_kernel(const uint4* __restrict__ x, const uint4* __restrict__ x_f16, const int* __restrict__ inexact,
                        const uint4* __restrict__ codes, const uint8_t* __restrict__ scales, O* __restrict__ out,
                        uint32_t rows, uint32_t n, uint32_t k, float scale2, const GemvSplit sp) {
   __shared__ float part[GEMV_WARPS][16][8];
   mb_grid_dependency_sync();                 // the conversion pass before this kernel wrote x_f16 and the flags
+  extern __shared__ __align__(16) uint8_t gemv_ring[];      // GEMV_RING_SMEM bytes when k % 128 == 0, else none
   int any = 0;
   for (uint32_t r = 0; r < rows; ++r) any |= __ldg(inexact + r);
-  if (any) gemv_body<false, O>(x, codes, scales, out, rows, n, k, scale2, part, sp);
-  else gemv_body<true, O>(x_f16, codes, scales, out, rows, n, k, scale2, part, sp);
+  if (k % 128 == 0) {
+    if (any) gemv_body_ring<false, O>(x, codes, scales, out, rows, n, k, scale2, part, sp, gemv_ring);
+    else gemv_body_ring<true, O>(x_f16, codes, scales, out, rows, n, k, scale2, part, sp, gemv_ring);
+  } else {
+    if (any) gemv_body<false, O>(x, codes, scales, out, rows, n, k, scale2, part, sp);
+    else gemv_body<true, O>(x_f16, codes, scales, out, rows, n, k, scale2, part, sp);
+  }
 }
 
 // One block per activation row: bf16 -> f16, exact when the value is zero, infinite, NaN or a normal f16 (bf16 has
@@ -383,12 +497,24 @@ gemv_w4a4_grouped_kernel(const uint2* __restrict__ a_codes, const uint8_t* __res
   }
 }
 
+// The ring of the k % 128 == 0 bodies needs more than the default 48 KB of dynamic shared memory.
+int gemv_set_attributes(mb_ctx* ctx) {
+  if (!mb_once(ctx, MB_ONCE_GEMV_RING)) {
+    MB_CUDA_OK(ctx, cudaFuncSetAttribute(gemv_w4a16_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, GEMV_RING_SMEM));
+    MB_CUDA_OK(ctx, cudaFuncSetAttribute(gemv_w4a16_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, GEMV_RING_SMEM));
+    MB_CUDA_OK(ctx, cudaFuncSetAttribute(gemv_w4a16_dual_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, GEMV_RING_SMEM));
+    MB_CUDA_OK(ctx, cudaFuncSetAttribute(gemv_w4a16_dual_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, GEMV_RING_SMEM));
+    mb_once_done(ctx, MB_ONCE_GEMV_RING);
+  }
+  return MB_OK;
+}
+
 template <typename O>
 int launch_rows(cudaStream_t stream, size_t rows, const void* x, const uint8_t* codes, const uint8_t* scales, O* out,
                 uint32_t n, uint32_t k, float scale2) {
   dim3 grid((n + 15) / 16), block(32 * GEMV_WARPS);
-  gemv_w4a16_kernel<O><<<grid, block, 0, stream>>>(static_cast<const uint4*>(x), reinterpret_cast<const uint4*>(codes),
-                                                   scales, out, uint32_t(rows), n, k, scale2);
+  gemv_w4a16_kernel<O><<<grid, block, k % 128 == 0 ? GEMV_RING_SMEM : 0, stream>>>(
+      static_cast<const uint4*>(x), reinterpret_cast<const uint4*>(codes), scales, out, uint32_t(rows), n, k, scale2);
   return 0;
 }
 
@@ -404,8 +530,10 @@ MB_API int mb_nvfp4_gemv_w4a16(mb_ctx* ctx, mb_stream stream_, const void* x_bf1
   MB_REQUIRE(ctx, scale2 == scale2 && scale2 > 0.0f && scale2 <= 3.4e38f,
              "NVFP4 global scale %g is not a positive finite number", double(scale2));
   MB_REQUIRE(ctx, mb_aligned(x_bf16, 16), "NVFP4 GEMV needs a 16-byte aligned activation");
-  MB_REQUIRE(ctx, mb_aligned(codes, 16) && mb_aligned(scales, 2), "NVFP4 GEMV needs 16-byte aligned code rows");
-  int rc;
+  MB_REQUIRE(ctx, mb_aligned(codes, 16) && mb_aligned(scales, k % 128 == 0 ? 8 : 2),
+             "NVFP4 GEMV needs 16-byte aligned code rows (and 8-byte aligned scale rows when k is a multiple of 128)");
+  int rc = gemv_set_attributes(ctx);
+  if (rc) return rc;
   if (out_dtype == MB_DT_BF16)
     rc = launch_rows(stream, rows, x_bf16, codes, scales, static_cast<__nv_bfloat16*>(out), uint32_t(n), uint32_t(k), scale2);
   else if (out_dtype == MB_DT_F32)
@@ -464,8 +592,14 @@ MB_API int mb_nvfp4_gemv_w4a16_ws(mb_ctx* ctx, mb_stream stream_, const void* x_
   MB_REQUIRE(ctx, scale2 == scale2 && scale2 > 0.0f && scale2 <= 3.4e38f,
              "NVFP4 global scale %g is not a positive finite number", double(scale2));
   MB_REQUIRE(ctx, mb_aligned(x_bf16, 16) && mb_aligned(workspace, 256), "NVFP4 GEMV needs a 16-byte aligned activation and a 256-byte aligned workspace");
-  MB_REQUIRE(ctx, mb_aligned(codes, 16) && mb_aligned(scales, 2), "NVFP4 GEMV needs 16-byte aligned code rows");
+  MB_REQUIRE(ctx, mb_aligned(codes, 16) && mb_aligned(scales, k % 128 == 0 ? 8 : 2),
+             "NVFP4 GEMV needs 16-byte aligned code rows (and 8-byte aligned scale rows when k is a multiple of 128)");
   MB_REQUIRE(ctx, out_dtype == MB_DT_BF16 || out_dtype == MB_DT_F32, "gemv: output is bf16 or f32");
+  {
+    int rc = gemv_set_attributes(ctx);
+    if (rc) return rc;
+  }
+  const size_t ring_smem = k % 128 == 0 ? size_t(GEMV_RING_SMEM) : 0;
   const GemvWorkspace w = gemv_workspace_plan(rows, n, k);
   uint8_t* base = static_cast<uint8_t*>(workspace);
   int* flags = reinterpret_cast<int*>(base);
@@ -476,12 +610,12 @@ MB_API int mb_nvfp4_gemv_w4a16_ws(mb_ctx* ctx, mb_stream stream_, const void* x_
                                 static_cast<const uint4*>(x_bf16), x16, flags, uint32_t(k / 8), counters, w.row_blocks));
   const dim3 grid(w.row_blocks, w.ksplit), block(32 * GEMV_WARPS);
   if (out_dtype == MB_DT_BF16)
-    MB_CUDA_OK(ctx, mb_launch_pdl(gemv_w4a16_dual_kernel<__nv_bfloat16>, grid, block, 0, stream,
+    MB_CUDA_OK(ctx, mb_launch_pdl(gemv_w4a16_dual_kernel<__nv_bfloat16>, grid, block, ring_smem, stream,
                                   static_cast<const uint4*>(x_bf16), static_cast<const uint4*>(x16), static_cast<const int*>(flags),
                                   reinterpret_cast<const uint4*>(codes), scales, static_cast<__nv_bfloat16*>(out),
                                   uint32_t(rows), uint32_t(n), uint32_t(k), scale2, sp));
   else
-    MB_CUDA_OK(ctx, mb_launch_pdl(gemv_w4a16_dual_kernel<float>, grid, block, 0, stream, static_cast<const uint4*>(x_bf16),
+    MB_CUDA_OK(ctx, mb_launch_pdl(gemv_w4a16_dual_kernel<float>, grid, block, ring_smem, stream, static_cast<const uint4*>(x_bf16),
                                   static_cast<const uint4*>(x16), static_cast<const int*>(flags),
                                   reinterpret_cast<const uint4*>(codes), scales, static_cast<float*>(out), uint32_t(rows),
                                   uint32_t(n), uint32_t(k), scale2, sp));
