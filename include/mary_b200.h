@@ -354,7 +354,9 @@ int mb_attention_window(mb_ctx* ctx, mb_stream stream, const void* q, const void
  * rows ascending; or NULL, 0): the key in cache row r sits at position r + gap_cums[g] for the last g
  * with gap_rows[g] <= r, at r when there is none; visibility, the window and the bias distance all
  * use positions, and q0 is the position of the first query. All sequences of a call share the gap
- * list. window = 0: none. Decode shapes only (nq * heads / kv_heads <= 16). */
+ * list. window = 0: none. Decode shapes (nq * heads / kv_heads <= 16) run on the split-K decode kernel;
+ * prompt-shaped blocks run on the warp-level (mma.sync) prompt kernel, which masks and biases every score
+ * by position (correct at any nq, at about a fifth of the tcgen05 kernel's rate). */
 int mb_attention_decode_ext(mb_ctx* ctx, mb_stream stream, const void* q, const void* k, const void* v, size_t batch,
                             size_t nq, size_t keys, size_t heads, size_t kv_heads, size_t d, size_t q0, float scale,
                             size_t window, const float* rel, size_t eff, const uint32_t* gap_rows,
@@ -393,8 +395,11 @@ int mb_attention_fp4kv(mb_ctx* ctx, mb_stream stream, const void* q, const uint8
  * eff] f32 or NULL). gap_rows/gap_cums (ngaps <= 64 device words each, or NULL, 0): the eviction gaps of
  * Gaps (flash.rs:1017-1035). Decode shapes (nq * heads / kv_heads <= 16) split every run's visible keys
  * in proportion to its span (key_run_splits, flash.rs:1318-1327) and merge all partials in one pass;
- * prompt shapes take a single non-empty bf16 or f32 run without bias or gaps and run on the tcgen05
- * kernel. At most 64 runs. workspace: mb_attention_runs_workspace bytes, 256-byte aligned. */
+ * prompt shapes take a single non-empty run and run on the tcgen05 kernel (on the warp-level kernel when they
+ * carry a bias or gaps); NVFP4
+ * rows reach it through the dequantizing reader (flash.rs:520-540): the run's live rows are expanded to
+ * bf16 in the workspace, exactly. At most 64 runs. workspace: mb_attention_runs_workspace bytes, 256-byte
+ * aligned. */
 enum { MB_KV_F32 = 0, MB_KV_BF16 = 1, MB_KV_NVFP4 = 2 };
 typedef struct mb_key_run {
   const void* k;

@@ -576,6 +576,10 @@ constexpr int PRE_THREADS = 288;
 constexpr int BR = 128;
 constexpr int PRE_SMEM = PRE_STAGES * KV_STAGE_BYTES + BR * D * 2 + 1024 + 128;
 
+// EXT: the instantiation with the relative bias and the eviction gaps for prompt-shaped blocks (positions instead of
+// rows in the masks, as in the decode kernel's). It is the route of prompt shapes that carry either; the tcgen05
+// kernel serves the rest.
+template <bool EXT>
 __global__ void __launch_bounds__(PRE_THREADS, 1)
 attn_prefill_kernel(const __grid_constant__ AttnParams p) {
   extern __shared__ uint8_t smem_raw[];
@@ -663,7 +667,30 @@ attn_prefill_kernel(const __grid_constant__ AttnParams p) {
         __syncwarp();
         if (lane == 0) mbar_arrive(empty_bar(stage == 0 ? PRE_STAGES - 1 : stage - 1));
       }
-      if (live) {
+      if (live && EXT) {
+        // every score is masked and biased on its own by position, then the step runs unmasked
+        const uint32_t h_abs = h;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const uint32_t qi = q_row0 + warp * 16 + g + 8u * (e >> 1);          // query row of the block
+            const uint32_t krow = uint32_t(kabs) + j * 8 + (lane & 3) * 2 + (e & 1);
+            uint32_t pos = p.pos0 + krow;
+            for (uint32_t gi = 0; gi < p.ngaps; ++gi)
+              if (__ldg(p.gap_rows + gi) <= p.row0 + krow) pos = p.pos0 + krow + __ldg(p.gap_cums + gi);
+            const uint32_t qpos = p.q0_abs + qi;
+            bool vis = qi < p.nq && krow < p.keys && pos <= qpos;
+            if (vis && p.window && qpos - pos >= p.window) vis = false;
+            float val = s[j][e] * p.scale_log2;
+            if (vis && p.rel && qpos - pos < p.eff)
+              val += __ldg(p.rel + ((size_t(b) * p.nq + qi) * p.heads + h_abs) * p.eff + (qpos - pos)) * 1.4426950408889634f;
+            s[j][e] = vis ? val : -INFINITY;
+          }
+        }
+        softmax_step<8>(s, o, m, l, 1.0f, BC, BC, lane);
+        pv_tile<4>(o, s, s0 + 2 * TILE_HALF_BYTES, 0, lane);
+      } else if (live) {
         int vis_lo = int(p.keys) - kabs, vis_hi = vis_lo;
         if (p.causal) {
           vis_lo = min(vis_lo, qpos_lo + 1 - kabs);
@@ -765,6 +792,33 @@ bf16_to_f32_kernel(const __nv_bfloat16* __restrict__ src, float* __restrict__ ds
   const uint2 v = *reinterpret_cast<const uint2*>(src + i * 4);
   *reinterpret_cast<float4*>(dst + i * 4) = make_float4(__uint_as_float(v.x << 16), __uint_as_float(v.x & 0xFFFF0000u),
                                                         __uint_as_float(v.y << 16), __uint_as_float(v.y & 0xFFFF0000u));
+}
+
+// NVFP4 rows -> contiguous bf16 [batch, live rows, elems] (exact: a code times its block scale has six significant
+// bits). One 16-value block per thread; the source keeps `cap` rows per sequence, of which `live` are copied.
+__global__ void __launch_bounds__(256)
+fp4_rows_to_bf16_kernel(const uint2* __restrict__ codes, const uint8_t* __restrict__ scales, uint4* __restrict__ dst,
+                        size_t live_blocks, size_t cap_blocks, size_t total_blocks) {
+  const size_t i = size_t(blockIdx.x) * 256 + threadIdx.x;
+  if (i >= total_blocks) return;
+  const size_t b = i / live_blocks, r = i - b * live_blocks, src = b * cap_blocks + r;
+  const uint2 c = __ldg(codes + src);
+  uint32_t sh;
+  asm("cvt.rn.f16x2.e4m3x2 %0, %1;" : "=r"(sh) : "h"(uint16_t(__ldg(scales + src))));
+  const __half2 sc = __low2half2(*reinterpret_cast<__half2*>(&sh));
+  uint32_t h[8];
+  fp4_decode4(c.x & 0xFFFFu, sc, h[0], h[1]);
+  fp4_decode4(c.x >> 16, sc, h[2], h[3]);
+  fp4_decode4(c.y & 0xFFFFu, sc, h[4], h[5]);
+  fp4_decode4(c.y >> 16, sc, h[6], h[7]);
+  uint32_t w[8];
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    const float2 f = __half22float2(*reinterpret_cast<__half2*>(&h[j]));
+    w[j] = pack2(f.x, f.y);
+  }
+  dst[i * 2] = make_uint4(w[0], w[1], w[2], w[3]);
+  dst[i * 2 + 1] = make_uint4(w[4], w[5], w[6], w[7]);
 }
 
 struct AttnExt {
@@ -880,8 +934,6 @@ int attention_core(mb_ctx* ctx, cudaStream_t stream, const void* q, const float*
     MB_REQUIRE(ctx, decode, "attention: NVFP4 rows are read by the decode kernel only (nq * heads / kv_heads <= 16)");
   if (has_ext) {
     MB_REQUIRE(ctx, causal, "attention: relative bias and eviction gaps belong to causal attention");
-    MB_REQUIRE(ctx, decode,
-               "attention: relative bias and eviction gaps are read by the decode kernel only (nq * heads / kv_heads <= 16)");
     MB_REQUIRE(ctx, !ext->rel || ext->eff > 0, "attention: a relative bias table needs eff > 0");
     MB_REQUIRE(ctx, ext->ngaps <= 64 && (ext->ngaps == 0 || (ext->gap_rows && ext->gap_cums)), "attention: bad gap list");
     MB_REQUIRE(ctx, ext->eff < (1ull << 31), "attention: bad eff");
@@ -973,7 +1025,7 @@ int attention_core(mb_ctx* ctx, cudaStream_t stream, const void* q, const float*
   MB_REQUIRE(ctx, q0 >= one->pos0, "attention: the first query (position %zu) stands before the run's first key (%zu)",
              q0, one->pos0);
   MB_REQUIRE(ctx, one->live < (1ull << 31), "attention: extent overflow");
-  MB_REQUIRE(ctx, window == 0 || one->live >= q0 - one->pos0 + nq,
+  MB_REQUIRE(ctx, window == 0 || gapped || one->live >= q0 - one->pos0 + nq,
              "attention: with a window every query needs its own key in the cache");
   p.keys = uint32_t(one->live);
   p.q0 = uint32_t(q0 - one->pos0);
@@ -982,20 +1034,25 @@ int attention_core(mb_ctx* ctx, cudaStream_t stream, const void* q, const float*
   if (rc) return rc;
   rc = make_tmap_4d(ctx, &p.tmap_v, one->v, batch, one->live, one->cap, kv_heads, BC);
   if (rc) return rc;
-  if (!mb_attention_prefill_legacy()) {
+  if (!has_ext && !mb_attention_prefill_legacy()) {
     rc = make_tmap_4d(ctx, &p.tmap_q, q, batch, nq, nq, heads, 128);
     if (rc) return rc;
     return mb_attention_prefill_tc5(ctx, stream, p);
   }
-  MB_REQUIRE(ctx, window == 0, "attention: the comparison (mma.sync) prefill kernel has no sliding window");
+  // The warp-level (mma.sync) kernel: the route of prompt-shaped blocks with a relative bias or eviction gaps
+  // (its EXT instantiation masks and biases by position, window included), and the comparison arm of the rest.
+  MB_REQUIRE(ctx, has_ext || window == 0, "attention: the comparison (mma.sync) prefill kernel has no sliding window");
+  p.pos0 = uint32_t(one->pos0); p.row0 = uint32_t(one->row0);
   rc = make_tmap_4d(ctx, &p.tmap_q, q, batch, nq, nq, heads, BR);
   if (rc) return rc;
   if (!mb_once(ctx, MB_ONCE_ATTN_PREFILL_LEGACY)) {
-    MB_CUDA_OK(ctx, cudaFuncSetAttribute(attn_prefill_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, PRE_SMEM));
+    MB_CUDA_OK(ctx, cudaFuncSetAttribute(attn_prefill_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, PRE_SMEM));
+    MB_CUDA_OK(ctx, cudaFuncSetAttribute(attn_prefill_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, PRE_SMEM));
     mb_once_done(ctx, MB_ONCE_ATTN_PREFILL_LEGACY);
   }
   dim3 grid(unsigned((nq + BR - 1) / BR), unsigned(heads), unsigned(batch));
-  attn_prefill_kernel<<<grid, PRE_THREADS, PRE_SMEM, stream>>>(p);
+  if (has_ext) attn_prefill_kernel<true><<<grid, PRE_THREADS, PRE_SMEM, stream>>>(p);
+  else attn_prefill_kernel<false><<<grid, PRE_THREADS, PRE_SMEM, stream>>>(p);
   MB_LAUNCH_OK(ctx);
   return MB_OK;
 }
@@ -1069,7 +1126,9 @@ size_t align256(size_t n) { return (n + 255) / 256 * 256; }
 
 // Live-row views of the caller's runs. For an f32 cache `converted` (when given) is where the bf16 copy of the
 // live rows of K then V of each run goes; the views then point there.
-int view_runs(mb_ctx* ctx, const mb_key_run* runs, size_t n_runs, int kv_elem, size_t batch, size_t kv_heads,
+// `expand`: the rows are read through a bf16 copy of the live rows in the workspace (always for f32 rows; for NVFP4
+// rows when the query block is prompt-shaped, which the tensor-core kernel serves from bf16 tiles).
+int view_runs(mb_ctx* ctx, const mb_key_run* runs, size_t n_runs, int kv_elem, bool expand, size_t batch, size_t kv_heads,
               uint8_t* converted, RunView* views, size_t* converted_bytes) {
   const size_t row_bytes = kv_heads * D * (kv_elem == MB_KV_F32 ? 4 : kv_elem == MB_KV_BF16 ? 2 : 0);
   size_t off = 0;
@@ -1083,7 +1142,7 @@ int view_runs(mb_ctx* ctx, const mb_key_run* runs, size_t n_runs, int kv_elem, s
     RunView& v = views[i];
     v = RunView();
     v.live = r.hi - r.lo; v.cap = r.rows; v.pos0 = r.base + r.lo; v.row0 = r.row0 + r.lo;
-    if (kv_elem == MB_KV_NVFP4) {
+    if (kv_elem == MB_KV_NVFP4 && !expand) {
       v.k = static_cast<const uint8_t*>(r.k) + r.lo * kv_heads * (D / 2);
       v.v = static_cast<const uint8_t*>(r.v) + r.lo * kv_heads * (D / 2);
       v.k_scales = static_cast<const uint8_t*>(r.k_scales) + r.lo * kv_heads * (D / 16);
@@ -1112,7 +1171,9 @@ MB_API size_t mb_attention_runs_workspace(const mb_key_run* runs, size_t n_runs,
   if (!runs || n_runs == 0 || n_runs > MAX_RUNS || kv_heads == 0 || heads % kv_heads != 0) return 0;
   RunView views[MAX_RUNS];
   size_t conv = 0;
-  if (view_runs(nullptr, runs, n_runs, kv_elem, batch, kv_heads, nullptr, views, &conv) != MB_OK) return 0;
+  const bool prompt = nq * (heads / kv_heads) > 16;
+  if (view_runs(nullptr, runs, n_runs, kv_elem, kv_elem == MB_KV_F32 || prompt, batch, kv_heads, nullptr, views, &conv) != MB_OK)
+    return 0;
   size_t need = conv;
   if (nq * (heads / kv_heads) <= 16) {
     RunPlan plan[MAX_RUNS];
@@ -1146,8 +1207,32 @@ MB_API int mb_attention_runs(mb_ctx* ctx, mb_stream stream_, const void* q, int 
   uint8_t* ws = static_cast<uint8_t*>(workspace);
   RunView views[MAX_RUNS];
   size_t conv = 0;
-  int rc = view_runs(ctx, runs, n_runs, kv_elem, batch, kv_heads, ws, views, &conv);
+  const bool decode = nq * (heads / kv_heads) <= 16;
+  const bool expand_fp4 = kv_elem == MB_KV_NVFP4 && !decode;
+  int rc = view_runs(ctx, runs, n_runs, kv_elem, kv_elem == MB_KV_F32 || expand_fp4, batch, kv_heads, ws, views, &conv);
   if (rc) return rc;
+  if (expand_fp4) {
+    // prompt-shaped reads of packed rows: the reference's dequantizing reader (src/models/inkling/flash.rs:520-540);
+    // the live rows are expanded to bf16 once (exactly) and the tensor-core kernel reads those
+    for (size_t i = 0; i < n_runs; ++i) {
+      const size_t live = views[i].live;
+      if (!live) continue;
+      MB_REQUIRE(ctx, mb_aligned(runs[i].k, 8) && mb_aligned(runs[i].v, 8), "attention_runs: NVFP4 rows need 8-byte aligned codes");
+      const size_t row_blocks = kv_heads * (D / 16), total = batch * live * row_blocks;
+      const unsigned grid = unsigned((total + 255) / 256);
+      const uint8_t* kc = static_cast<const uint8_t*>(runs[i].k) + runs[i].lo * row_blocks * 8;
+      const uint8_t* vc = static_cast<const uint8_t*>(runs[i].v) + runs[i].lo * row_blocks * 8;
+      const uint8_t* ksc = static_cast<const uint8_t*>(runs[i].k_scales) + runs[i].lo * row_blocks;
+      const uint8_t* vsc = static_cast<const uint8_t*>(runs[i].v_scales) + runs[i].lo * row_blocks;
+      fp4_rows_to_bf16_kernel<<<grid, 256, 0, stream>>>(reinterpret_cast<const uint2*>(kc), ksc,
+                                                        static_cast<uint4*>(const_cast<void*>(views[i].k)), live * row_blocks,
+                                                        runs[i].rows * row_blocks, total);
+      fp4_rows_to_bf16_kernel<<<grid, 256, 0, stream>>>(reinterpret_cast<const uint2*>(vc), vsc,
+                                                        static_cast<uint4*>(const_cast<void*>(views[i].v)), live * row_blocks,
+                                                        runs[i].rows * row_blocks, total);
+      MB_LAUNCH_OK(ctx);
+    }
+  }
   if (kv_elem == MB_KV_F32) {
     // f32 rows go through a bf16 copy of the live rows (both products multiply bf16)
     for (size_t i = 0; i < n_runs; ++i) {
@@ -1168,7 +1253,6 @@ MB_API int mb_attention_runs(mb_ctx* ctx, mb_stream stream_, const void* q, int 
   ws += conv;
   AttnExt ext;
   ext.rel = rel; ext.eff = eff; ext.gap_rows = gap_rows; ext.gap_cums = gap_cums; ext.ngaps = ngaps;
-  const bool decode = nq * (heads / kv_heads) <= 16;
   if (decode) {
     return attention_core(ctx, stream, q_dtype == MB_DT_BF16 ? q : nullptr,
                           q_dtype == MB_DT_F32 ? static_cast<const float*>(q) : nullptr, views, n_runs,

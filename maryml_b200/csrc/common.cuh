@@ -40,6 +40,7 @@ enum : uint32_t {
   MB_ONCE_GEMM_W4A16_256 = 1u << 8,
   MB_ONCE_GEMM_W4A16_128 = 1u << 9,
   MB_ONCE_GEMV_RING = 1u << 10,
+  MB_ONCE_GEMM_BF16_PAIR = 1u << 11,
 };
 
 struct mb_ctx {

@@ -1143,6 +1143,11 @@ static uint32_t bf16_splitk_factor(int sm_count, size_t m, size_t n, size_t k) {
   return (k_steps + per - 1) / per;
 }
 
+// The CTA-pair kernel for prompt-sized products (gemm_bf16_pair.cu).
+bool mb_bf16_pair_takes(size_t m, size_t n, size_t k);
+int mb_bf16_pair_launch(mb_ctx* ctx, cudaStream_t stream, const void* a, const void* b, float alpha, size_t m, size_t n,
+                        size_t k, void* out, int out_dtype);
+
 static int bf16_gemm_common(mb_ctx* ctx, cudaStream_t stream, const void* a, const void* b, float alpha, size_t m,
                             size_t n, size_t k, void* out, int out_dtype, void* workspace, size_t workspace_bytes) {
   MB_REQUIRE(ctx, ctx && a && b && out, "bf16_gemm: null argument");
@@ -1151,6 +1156,11 @@ static int bf16_gemm_common(mb_ctx* ctx, cudaStream_t stream, const void* a, con
   MB_REQUIRE(ctx, out_dtype == MB_DT_BF16 || out_dtype == MB_DT_F32, "bf16_gemm: output is bf16 or f32");
   MB_REQUIRE(ctx, mb_aligned(a, 16) && mb_aligned(b, 16) && mb_aligned(out, 16) && mb_aligned(workspace, 16),
              "bf16_gemm: 16-byte alignment");
+  MB_REQUIRE_DEVICE(ctx, "bf16_gemm");
+  {
+    static const bool pair_off = [] { const char* e = getenv("MB_BF16_PAIR"); return e && e[0] == '0'; }();
+    if (!pair_off && mb_bf16_pair_takes(m, n, k)) return mb_bf16_pair_launch(ctx, stream, a, b, alpha, m, n, k, out, out_dtype);
+  }
   GemmParams p;
   memset(&p, 0, sizeof p);
   const bool wide = (n % 256 == 0);

@@ -149,6 +149,10 @@ def test_decode_attention_over_nvfp4_rows(mods, orc, batch, nq, keys, heads, kvh
     (1, 1, 897, 8, 2, 0, [(17, 5), (853, 19)], 0),      # gaps alone (the reference's gapped case: flash.rs:2040-2044)
     (2, 2, 700, 8, 2, 100, [(3, 2), (650, 40)], 33),    # everything, two queries, two sequences
     (1, 4, 300, 4, 1, 0, [(0, 7)], 300),                # a gap before the first row; bias over every distance
+    # prompt-shaped blocks (more than 16 query rows per KV head) take the warp-level kernel's position path
+    (1, 150, 400, 8, 2, 0, [], 24),                     # bias alone
+    (2, 200, 700, 4, 2, 77, [(5, 3), (450, 21)], 16),   # everything; the block is not a multiple of the 128-row tile
+    (1, 64, 333, 8, 1, 0, [(100, 9)], 0),               # gaps alone
 ])
 def test_decode_attention_with_relative_bias_and_gaps(mods, orc, batch, nq, keys, heads, kvh, window, gaps, eff):
     att, _ = mods
@@ -176,7 +180,7 @@ def test_decode_attention_with_relative_bias_and_gaps(mods, orc, batch, nq, keys
                             1.0 / math.sqrt(D), key_pos=pos if gaps else None, window=window,
                             rel=None if rel is None else rel[b])
         err, cos = attn_check(got[b], ref)
-        assert err <= 1e-2 and cos >= 0.9999, (b, err, cos)
+        assert err <= _attn_bound(nq, heads, kvh) and cos >= 0.9999, (b, err, cos)
     if not gaps and not eff:
         assert torch.equal(out, att.flash_attention(qd, kd, vd, q0=q0, window=window))
 

@@ -397,9 +397,13 @@ def test_w4a4_rows_nan_row_poisons_only_itself(mb, orc):
     assert torch.equal(dirty[0, keep].view(torch.int16), clean[0, keep].view(torch.int16))
 
 
-@pytest.mark.parametrize("m,n,k", [(128, 128, 64), (200, 264, 1032), (512, 1024, 2048), (512, 128, 2048), (100, 128, 1096)])
+@pytest.mark.parametrize("m,n,k", [(128, 128, 64), (200, 264, 1032), (512, 1024, 2048), (512, 128, 2048), (100, 128, 1096),
+                                   (300, 512, 192), (1024, 768, 4096), (2304, 256, 64), (2900, 2048, 128), (5000, 1024, 320)])
 def test_bf16_gemm_against_f64(mb, orc, m, n, k):
-    """The last two shapes have few output tiles and a long K: they run as K slices (split-K)."""
+    """(512, 128, 2048) and (100, 128, 1096) have few output tiles and a long K: they run as K slices (split-K).
+    Shapes with n % 256 == 0, k % 64 == 0 and at least 74 tiles of 256 x 256 run on CTA pairs: (2900, 2048, 128)
+    leaves the last row pair 84 rows (its second CTA none), (5000, 1024, 320) leaves the last pair's second CTA eight
+    rows and has five K steps; (300, 512, 192), (1024, 768, 4096) and (2304, 256, 64) stay on the single-CTA kernel."""
     abits = f32_to_bf16_bits(orc.normal_f32(31, m * k, 1.0))
     bbits = f32_to_bf16_bits(orc.normal_f32(32, n * k, 0.02))
     ref = orc.linear_bf16(abits, bbits, m, n, k)
@@ -408,6 +412,9 @@ def test_bf16_gemm_against_f64(mb, orc, m, n, k):
     assert np.abs(out - ref).max() <= 2e-5 * scale * np.sqrt(k / 64)
     rel, cos = rel_check(out, ref)
     assert rel <= 1e-2 and cos >= 0.9999
+    # the bf16 output is the f32 one rounded once
+    out16 = mb.bf16_gemm(dev_bf16(abits).view(m, k), dev_bf16(bbits).view(n, k), out_dtype=torch.bfloat16)
+    assert torch.equal(out16.cpu().view(torch.int16), torch.from_numpy(out).to(torch.bfloat16).view(torch.int16))
 
 
 def test_project_w4a16_and_linear_dispatch(mb, orc):

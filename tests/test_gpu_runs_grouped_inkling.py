@@ -186,6 +186,34 @@ def test_prompt_shapes_take_one_run_in_place_with_f32_in_and_out(mods, orc):
         att.flash_attention_runs(dev_bf16(qb).view(batch, nq, heads, D), [att.KeyRunView(kd, vd, lo=10, hi=cap + 1)], q0=past)
 
 
+def test_prompt_shaped_block_over_a_packed_page(mods, orc):
+    """A prompt-shaped query block over NVFP4 rows goes through the dequantizing reader
+    (src/models/inkling/flash.rs:520-540): the live rows are expanded to bf16 (exactly) and read by the prompt kernel.
+    Against the CPU rule over the values the page holds; rows past the live ones are garbage on purpose."""
+    att, _, nv, _lib = mods
+    batch, nq, past, cap, heads, kvh, D = 2, 160, 96, 320, 8, 2, 128
+    keys = past + nq
+    qb = _rows(orc, 31, batch, nq, heads * D)
+    kb = _rows(orc, 32, batch, cap, kvh * D)
+    vb = _rows(orc, 33, batch, cap, kvh * D)
+    kd = dev_bf16(kb).view(batch, cap, kvh, D)
+    vd = dev_bf16(vb).view(batch, cap, kvh, D)
+    kc, ksc = att.quantize_kv_rows(kd)
+    vc, vsc = att.quantize_kv_rows(vd)
+    dk = nv.dequantize(kc.view(batch * cap, -1), ksc.view(batch * cap, -1), 1.0, batch * cap, kvh * D).view(batch, cap, -1)
+    dv = nv.dequantize(vc.view(batch * cap, -1), vsc.view(batch * cap, -1), 1.0, batch * cap, kvh * D).view(batch, cap, -1)
+    ksc = ksc.clone()
+    ksc.view(batch, cap, -1)[:, keys:] = 0x7F          # NaN scales beyond the live rows: they must never be read
+    run = att.KeyRunView(kc, vc, ksc, vsc, hi=keys)
+    out = att.flash_attention_runs(dev_bf16(qb).view(batch, nq, heads, D), [run], q0=past)
+    got = bf16_bits_to_f32(host_bits(out)).reshape(batch, nq, -1)
+    for b in range(batch):
+        ref = orc.attention(bf16_bits_to_f32(qb[b]), dk[b, :keys].float().cpu().numpy(), dv[b, :keys].float().cpu().numpy(),
+                            heads, kvh, D, past, 1.0 / math.sqrt(D))
+        r, cos = attn_check(got[b], ref)
+        assert r <= 1.5e-2 and cos >= 0.9999, (b, r, cos)
+
+
 # ------------------------------------------------------------------- decode-time grouped experts
 @pytest.mark.parametrize("groups,experts,n,k,per_group", [(8, 16, 1536, 2048, False), (4, 6, 264, 768, True),
                                                           (1, 3, 2048, 64, True)])
