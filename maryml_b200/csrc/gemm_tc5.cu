@@ -560,20 +560,6 @@ gemm_tc5_kernel(const __grid_constant__ GemmParams p) {
 // 128 + 128 operand rows cross L2 -> shared memory per K step instead of 128 + 256.
 // No load is multicast: every CTA fetches what lands in its own shared memory; only
 // the completion counts (leader's barrier) and tcgen05.commit cross the pair.
-//
-// TMEM holds 512 columns; two 256-column accumulators and the 48 scale columns of a K step
-// need 560, so the two accumulators share 64 columns: tile columns 0..191 live in the
-// buffer's own 192 columns ([0, 192) or [256, 448)), tile columns 192..255 in [192, 256) for
-// both buffers. Every K step is issued as two MMAs, N = 192 and N = 64, and a tile starts its
-// N = 192 MMAs at once: only the N = 64 ones have to wait until the previous tile's epilogue
-// has read the shared columns. Up to four K steps run ahead like that (their ring stages stay
-// held; their N = 64 MMAs follow once the columns are free, after a second copy of the step's
-// scales into TMEM), which covers the microsecond the epilogue needs to get there.
-// For the two MMAs to take whole row ranges of B, a CTA of the pair keeps in shared memory
-// rows [96 r, 96 r + 96) of the tile's 256 weight rows followed by rows [192 + 32 r, + 32)
-// (r = its rank): the N = 192 MMA reads the first 96 rows of both CTAs = tile columns 0..191
-// in order, the N = 64 MMA the last 32 rows of both = columns 192..255, and the scale columns
-// in TMEM keep their natural order (6 + 2 columns per MMA).
 // ---------------------------------------------------------------------------------
 struct Cfg2 {
   static constexpr int BN = 256;
@@ -584,19 +570,15 @@ struct Cfg2 {
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES + SFA_BYTES + SFB_BYTES;   // 38 KB
   static constexpr int STAGES = 5;
   static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + 256 + EPI_WARPS_ * 512;
-  static constexpr int ACC_OWN0 = 0, ACC_SHARED = 192, ACC_OWN1 = 256, SFA_COL = 448, SFB_COL = 464, TMEM_COLS = 512;
-  static constexpr int B_ROWS_A = 96, B_ROWS_B = 32;      // the two row ranges of a CTA's half of the B tile
-  static constexpr int MAX_DEFER = STAGES - 1;
+  static constexpr int ACC0 = 0, ACC1 = 192, SFA_COL = 448, SFB_COL = 464, TMEM_COLS = 512;
 };
 
 struct Gemm2Params {
-  GemmParams g;           // g.tmap_b: B code rows with a box of 96 rows
-  CUtensorMap tmap_b32;   // the same plane with a box of 32 rows
+  GemmParams g;
   CUtensorMap tmap_sfa;   // tiled scale planes as [atoms, 128 x int32], box 4 atoms
   CUtensorMap tmap_sfb;
   uint32_t m_pairs;
   uint32_t raster_group;  // row pairs per group of the tile order (see pair_tile)
-  uint32_t defer;         // K steps whose shared columns may wait for the previous tile's epilogue (0 = none)
 };
 
 // Tile order of the pair kernel. The pairs that run together take consecutive tile numbers, so the order
@@ -631,8 +613,7 @@ gemm_tc5_pair_kernel(const __grid_constant__ Gemm2Params pp) {
   auto acc_full_bar = [&](int b) { return bar_base + 8u * (2 * C::STAGES + b); };
   const uint32_t ovl_free_bar = bar_base + 8u * (2 * C::STAGES + 2);
   const uint32_t drain_bar = bar_base + 8u * (2 * C::STAGES + 3);
-  auto acc_free_bar = [&](int b) { return bar_base + 8u * (2 * C::STAGES + 4 + b); };   // leader's: a buffer read out
-  uint32_t* tmem_ptr_smem = reinterpret_cast<uint32_t*>(smem_gen + C::STAGES * C::STAGE_BYTES + 8 * (2 * C::STAGES + 6));
+  uint32_t* tmem_ptr_smem = reinterpret_cast<uint32_t*>(smem_gen + C::STAGES * C::STAGE_BYTES + 8 * (2 * C::STAGES + 4));
   volatile int* abort_smem = reinterpret_cast<volatile int*>(tmem_ptr_smem + 1);
 
   const int warp = __shfl_sync(0xFFFFFFFFu, int(threadIdx.x >> 5), 0);
@@ -645,13 +626,11 @@ gemm_tc5_pair_kernel(const __grid_constant__ Gemm2Params pp) {
     for (int s = 0; s < C::STAGES; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
     for (int b = 0; b < 2; ++b) mbar_init(acc_full_bar(b), 1);
     mbar_init(ovl_free_bar, 2 * EPI_WARPS);       // one arrival per epilogue warp of both CTAs
-    for (int b = 0; b < 2; ++b) mbar_init(acc_free_bar(b), 2 * EPI_WARPS);
     mbar_init(drain_bar, 1);
     *abort_smem = 0;
     fence_barrier_init();
     tma_prefetch_desc(&p.tmap_a);
     tma_prefetch_desc(&p.tmap_b);
-    tma_prefetch_desc(&pp.tmap_b32);
     tma_prefetch_desc(&pp.tmap_sfa);
     tma_prefetch_desc(&pp.tmap_sfb);
   }
@@ -688,9 +667,7 @@ gemm_tc5_pair_kernel(const __grid_constant__ Gemm2Params pp) {
           const uint32_t fb = map_to_cta(full_bar(stage), 0);
           if (leader) mbar_arrive_expect_tx(full_bar(stage), 2 * C::STAGE_BYTES);
           tma_load_2d_pair(sa, &p.tmap_a, int(ks * 128), int(mt * 128), fb);
-          tma_load_2d_pair(sb, &p.tmap_b, int(ks * 128), int(nt * C::BN + rank * C::B_ROWS_A), fb);
-          tma_load_2d_pair(sb + C::B_ROWS_A * 128, &pp.tmap_b32, int(ks * 128),
-                           int(nt * C::BN + 2 * C::B_ROWS_A + rank * C::B_ROWS_B), fb);
+          tma_load_2d_pair(sb, &p.tmap_b, int(ks * 128), int(nt * C::BN + rank * 128), fb);
           tma_load_2d_pair(ssfa, &pp.tmap_sfa, 0, int(mt * p.sf_kchunks + ks * 4u), fb);
           tma_load_2d_pair(ssfb, &pp.tmap_sfb, 0, int((nt * 2) * p.sf_kchunks + ks * 4u), fb);
           tma_load_2d_pair(ssfb + 2048, &pp.tmap_sfb, 0, int((nt * 2 + 1) * p.sf_kchunks + ks * 4u), fb);
@@ -704,98 +681,39 @@ gemm_tc5_pair_kernel(const __grid_constant__ Gemm2Params pp) {
     if (leader) {
       int stage = 0;
       uint32_t phase = 0;
-      const uint32_t idesc_own = idesc_nvf4(2 * C::B_ROWS_A, 256), idesc_sh = idesc_nvf4(2 * C::B_ROWS_B, 256);
+      const uint32_t idesc = idesc_nvf4(C::BN, 256);
       uint32_t it = 0;
       bool ok = true;
-      // scales of the K step in `st` from shared memory into their TMEM columns
-      auto copy_scales = [&](int st) {
-        const uint32_t ssfa = smem_base + st * C::STAGE_BYTES + C::A_BYTES + C::B_BYTES;
-        const uint32_t ssfb = ssfa + C::SFA_BYTES;
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          utccp_32x128b_warpx4_pair(tmem_base + C::SFA_COL + 4 * j, make_sf_desc(ssfa + 512 * j));
-          utccp_32x128b_warpx4_pair(tmem_base + C::SFB_COL + j * 8, make_sf_desc(ssfb + 512 * j));
-          utccp_32x128b_warpx4_pair(tmem_base + C::SFB_COL + j * 8 + 4, make_sf_desc(ssfb + 2048 + 512 * j));
-        }
-      };
-      // the four MMAs of a K step on the tile's own 192 columns, or on the 64 shared ones
-      auto mma_own = [&](int st, uint32_t d_own, bool first) {
-        const uint32_t sa = smem_base + st * C::STAGE_BYTES;
-        const uint64_t adesc = make_kmajor_sw128_desc(sa), bdesc = make_kmajor_sw128_desc(sa + C::A_BYTES);
-#pragma unroll
-        for (int j = 0; j < 4; ++j)
-          mma_nvf4_pair(d_own, adesc + 2 * j, bdesc + 2 * j, idesc_own, tmem_base + C::SFA_COL + 4 * j,
-                        tmem_base + C::SFB_COL + j * 8, !(first && j == 0));
-      };
-      auto mma_shared = [&](int st, bool first) {
-        const uint32_t sa = smem_base + st * C::STAGE_BYTES;
-        const uint64_t adesc = make_kmajor_sw128_desc(sa);
-        const uint64_t bdesc = make_kmajor_sw128_desc(sa + C::A_BYTES + C::B_ROWS_A * 128);
-#pragma unroll
-        for (int j = 0; j < 4; ++j)
-          mma_nvf4_pair(tmem_base + C::ACC_SHARED, adesc + 2 * j, bdesc + 2 * j, idesc_sh, tmem_base + C::SFA_COL + 4 * j,
-                        tmem_base + C::SFB_COL + j * 8 + 6, !(first && j == 0));
-      };
       for (uint32_t tile = pair; ok && tile < total_tiles; tile += n_pairs, ++it) {
         const uint32_t buf = it & 1u;
-        // this buffer's own columns: the tile before last has been read out of them
-        if (!mbar_wait_cluster(acc_free_bar(buf), ((it >> 1) & 1u) ^ 1u, abort_smem, tflag, 25)) { ok = false; break; }
+        if (it > 0 && !mbar_wait_cluster(ovl_free_bar, (it - 1u) & 1u, abort_smem, tflag, 22)) { ok = false; break; }
         fence_after_sync();
-        const uint32_t d_own = tmem_base + (buf ? C::ACC_OWN1 : C::ACC_OWN0);
-        bool shared_ok = it == 0;             // the shared columns: the previous tile's epilogue has read them
-        uint32_t deferred = 0;                // K steps whose N = 64 part is still to come (their stages are held)
-        int dstage = 0;                       // ring stage of the oldest of them
-        uint32_t dks = 0;                     // and its K step
-        // the N = 64 MMAs of every deferred step, oldest first; each then frees its stage
-        auto catch_up = [&](bool last_of_tile) {
-          fence_after_sync();
-          if (elect_one()) {
-            while (deferred) {
-              copy_scales(dstage);
-              mma_shared(dstage, dks == 0);
-              umma_commit_pair(empty_bar(dstage), 3);
-              if (++dstage == C::STAGES) dstage = 0;
-              ++dks;
-              --deferred;
-            }
-            if (last_of_tile) umma_commit_pair(acc_full_bar(buf), 3);
-          }
-          deferred = 0;
-          __syncwarp();
-        };
+        const uint32_t d_tmem = tmem_base + (buf ? C::ACC1 : C::ACC0);
         for (uint32_t ks = 0; ks < p.k_steps; ++ks) {
           if (!mbar_wait_cluster(full_bar(stage), phase, abort_smem, tflag, 23)) { ok = false; break; }
           fence_after_sync();
-          if (!shared_ok) {
-            if (deferred >= pp.defer) {
-              // no more stages to hold back (or deferral is off): wait for the shared columns here
-              if (!mbar_wait_cluster(ovl_free_bar, (it - 1u) & 1u, abort_smem, tflag, 22)) { ok = false; break; }
-              shared_ok = true;
-            } else if (__all_sync(0xFFFFFFFFu, mbar_try_wait_cluster(ovl_free_bar, (it - 1u) & 1u))) {
-              shared_ok = true;                                     // every lane has seen the phase complete
-            }
-            if (shared_ok) catch_up(false);
-          }
+          const uint32_t sa = smem_base + stage * C::STAGE_BYTES;
+          const uint32_t sb = sa + C::A_BYTES;
+          const uint32_t ssfa = sb + C::B_BYTES;
+          const uint32_t ssfb = ssfa + C::SFA_BYTES;
           if (elect_one()) {
-            copy_scales(stage);
-            mma_own(stage, d_own, ks == 0);
-            if (shared_ok) {
-              mma_shared(stage, ks == 0);
-              umma_commit_pair(empty_bar(stage), 3);                 // frees the stage in both CTAs
-              if (ks + 1 == p.k_steps) umma_commit_pair(acc_full_bar(buf), 3);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              utccp_32x128b_warpx4_pair(tmem_base + C::SFA_COL + 4 * j, make_sf_desc(ssfa + 512 * j));
+              utccp_32x128b_warpx4_pair(tmem_base + C::SFB_COL + j * 8, make_sf_desc(ssfb + 512 * j));
+              utccp_32x128b_warpx4_pair(tmem_base + C::SFB_COL + j * 8 + 4, make_sf_desc(ssfb + 2048 + 512 * j));
             }
+            const uint64_t adesc = make_kmajor_sw128_desc(sa);
+            const uint64_t bdesc = make_kmajor_sw128_desc(sb);
+#pragma unroll
+            for (int j = 0; j < 4; ++j)
+              mma_nvf4_pair(d_tmem, adesc + 2 * j, bdesc + 2 * j, idesc, tmem_base + C::SFA_COL + 4 * j,
+                            tmem_base + C::SFB_COL + j * 8, (ks | uint32_t(j)) != 0u);
+            umma_commit_pair(empty_bar(stage), 3);                 // frees the stage in both CTAs
+            if (ks + 1 == p.k_steps) umma_commit_pair(acc_full_bar(buf), 3);
           }
           __syncwarp();
-          if (!shared_ok) {
-            if (deferred == 0) { dstage = stage; dks = ks; }
-            ++deferred;
-          }
           if (++stage == C::STAGES) { stage = 0; phase ^= 1u; }
-        }
-        if (ok && !shared_ok) {
-          // a tile with fewer K steps than the ring may defer: its shared part all comes now
-          if (!mbar_wait_cluster(ovl_free_bar, (it - 1u) & 1u, abort_smem, tflag, 22)) { ok = false; break; }
-          catch_up(true);
         }
       }
       if (!ok) {
@@ -811,7 +729,6 @@ gemm_tc5_pair_kernel(const __grid_constant__ Gemm2Params pp) {
     const uint32_t ew = uint32_t(warp) - 2u, part = ew >> 2;
     uint8_t* patch = smem_gen + C::STAGES * C::STAGE_BYTES + 256 + ew * 512;
     const uint32_t ovl_remote = map_to_cta(ovl_free_bar, 0);
-    const uint32_t free_remote0 = map_to_cta(acc_free_bar(0), 0), free_remote1 = map_to_cta(acc_free_bar(1), 0);
     uint32_t it = 0;
     bool ok = true;
     for (uint32_t tile = pair; ok && tile < total_tiles; tile += n_pairs, ++it) {
@@ -825,28 +742,21 @@ gemm_tc5_pair_kernel(const __grid_constant__ Gemm2Params pp) {
       if (p.rowscale && row < p.m) scale = p.rowscale[row] * p.alpha;
       if (!mbar_wait_cluster(acc_full_bar(buf), (it >> 1) & 1u, abort_smem, tflag, 24)) { ok = false; break; }
       fence_after_sync();
-      // 32-column chunk c of the tile: chunks 0..5 in the buffer's own columns, 6 and 7 in the shared ones
-      const uint32_t t_lane = tmem_base + ((quad * 32u) << 16);
-      auto chunk_col = [&](int c) {
-        return c < 6 ? uint32_t(buf ? C::ACC_OWN1 : C::ACC_OWN0) + 32u * uint32_t(c) : uint32_t(C::ACC_SHARED) + 32u * uint32_t(c - 6);
-      };
-      // the two warps of a quadrant that own the shared chunks read them first; every warp reports after its first
-      // read, so the barrier completes when nobody needs the shared columns any more
-      const int c0 = part < 2 ? 6 + int(part) : 2 * int(part) - 2;
-      const int c1 = part < 2 ? int(part) : 2 * int(part) - 1;
+      const uint32_t t_acc = tmem_base + ((quad * 32u) << 16) + (buf ? C::ACC1 : C::ACC0);
+      constexpr int CHUNKS = C::BN / 32;
+      const int shared0 = buf == 0 ? CHUNKS - 2 : 0, rest0 = buf == 0 ? 0 : 2;
+      const int c0 = part < 2 ? shared0 + int(part) : rest0 + 2 * int(part) - 2;
+      const int c1 = part < 2 ? rest0 + int(part) : rest0 + 2 * int(part) - 1;
       uint32_t ra[32];
-      tmem_ld_x32(t_lane + chunk_col(c0), ra);
+      tmem_ld_x32(t_acc + c0 * 32, ra);
       tmem_ld_wait();
       fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster(ovl_remote);              // this warp is past the shared columns
       epilogue_chunk(p, ra, nt * C::BN + c0 * 32, row0, rows_valid, scale, patch, lane);
       uint32_t r[32];
-      tmem_ld_x32(t_lane + chunk_col(c1), r);
+      tmem_ld_x32(t_acc + c1 * 32, r);
       tmem_ld_wait();
-      fence_before_sync();
-      __syncwarp();
-      if (lane == 0) mbar_arrive_cluster(buf ? free_remote1 : free_remote0);   // and done with the buffer's own columns
       epilogue_chunk(p, r, nt * C::BN + c1 * 32, row0, rows_valid, scale, patch, lane);
     }
   }
@@ -1119,14 +1029,8 @@ int gemm_w4a4_common(mb_ctx* ctx, cudaStream_t stream, const uint8_t* a_codes, c
     Gemm2Params pp;
     memset(&pp, 0, sizeof pp);
     pp.g = p;
-    // each CTA loads half of the B tile as two row ranges (96 + 32 rows, see the kernel's header)
-    rc = make_tmap(ctx, &pp.g.tmap_b, b_codes, false, n, k / 2, Cfg2::B_ROWS_A);
+    rc = make_tmap(ctx, &pp.g.tmap_b, b_codes, false, n, k / 2, 128);   // each CTA loads half of the B tile
     if (rc) return rc;
-    rc = make_tmap(ctx, &pp.tmap_b32, b_codes, false, n, k / 2, Cfg2::B_ROWS_B);
-    if (rc) return rc;
-    // MB_GEMM_DEFER=<K steps> in the environment bounds (0: switches off) the run-ahead on the unshared columns
-    static const int defer_env = [] { const char* e = getenv("MB_GEMM_DEFER"); return e ? atoi(e) : -1; }();
-    pp.defer = defer_env < 0 ? uint32_t(Cfg2::MAX_DEFER) : std::min<uint32_t>(uint32_t(defer_env), uint32_t(Cfg2::MAX_DEFER));
     rc = make_sf_tmap(ctx, &pp.tmap_sfa, a_sf, uint64_t(p.m_tiles) * p.sf_kchunks);
     if (rc) return rc;
     rc = make_sf_tmap(ctx, &pp.tmap_sfb, b_sf, uint64_t((n + 127) / 128) * p.sf_kchunks);
