@@ -74,6 +74,64 @@ def _worker(rank, world, port, result_path):
     dist.destroy_process_group()
 
 
+def _rows_worker(rank, world, port, result_path):
+    """The prompt path's exchange: SUM reduce-scatter of the f32 partial by rows, residual + norm + quantizer on the
+    rank's own rows, all-gather of the NVFP4 planes, against the all-reduce form (every rank norms and quantizes all
+    rows). Same sums, same per-row arithmetic: the gathered planes and the residual rows must be the same bytes."""
+    sys.path.insert(0, HERE)
+    sys.path.insert(0, os.path.dirname(HERE))
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    from oracle_lib import oracle, f32_to_bf16_bits, bf16_bits_to_f32
+    orc = oracle()
+    orc.set_threads(2)
+    rows, hidden = 8 * world, 256
+    local = rows // world
+    x = f32_to_bf16_bits(orc.normal_f32(11, rows * hidden, 1.0)).reshape(rows, hidden)
+    gain = f32_to_bf16_bits(1.0 + orc.normal_f32(12, hidden, 0.1))
+    partial = orc.normal_f32(100 + rank, rows * hidden, 0.5).reshape(rows, hidden).astype(np.float32)   # this rank's share
+
+    def finish(x_rows, summed, n):
+        """bf16(x + bf16(sum)) -> norm -> W4A4 activation planes, row by row (the layer's second half opens so)."""
+        res = orc.add_bf16(x_rows, f32_to_bf16_bits(summed)).reshape(n, hidden)
+        normed = orc.rmsnorm_breeze(res, gain, n, hidden, 1e-5)
+        codes, scales = orc.quantize_act_scaled(bf16_bits_to_f32(normed), n, hidden, 1.0)
+        return res, np.asarray(codes).reshape(n, hidden // 2), np.asarray(scales).reshape(n, hidden // 16)
+
+    # all-reduce form
+    t = torch.from_numpy(partial.copy())
+    dist.all_reduce(t)
+    res_all, codes_all, scales_all = finish(x, t.numpy(), rows)
+    # rows stay sharded: reduce-scatter, local finish, all-gather of the planes
+    mine = torch.empty(local, hidden)
+    dist.reduce_scatter_tensor(mine, torch.from_numpy(partial.copy()))
+    res_l, codes_l, scales_l = finish(x[rank * local:(rank + 1) * local], mine.numpy(), local)
+    codes_g = torch.empty(rows, hidden // 2, dtype=torch.uint8)
+    scales_g = torch.empty(rows, hidden // 16, dtype=torch.uint8)
+    dist.all_gather_into_tensor(codes_g, torch.from_numpy(codes_l.copy()))
+    dist.all_gather_into_tensor(scales_g, torch.from_numpy(scales_l.copy()))
+    ok = (np.array_equal(codes_g.numpy(), codes_all) and np.array_equal(scales_g.numpy(), scales_all)
+          and np.array_equal(res_l, res_all[rank * local:(rank + 1) * local]))
+    flag = torch.tensor([1.0 if ok else 0.0])
+    dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+    if rank == 0:
+        with open(result_path, "w") as f:
+            f.write(f"{flag.item()}")
+    dist.destroy_process_group()
+
+
+def test_two_rank_rows_sharded_exchange_gathers_the_all_reduce_forms_planes(tmp_path):
+    import socket
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    port = s.getsockname()[1]
+    s.close()
+    result = tmp_path / "rows_result.txt"
+    mp.spawn(_rows_worker, args=(2, port, str(result)), nprocs=2, join=True)
+    assert float(result.read_text()) == 1.0
+
+
 def test_two_rank_row_and_column_parallel_projection(tmp_path):
     import socket
     s = socket.socket()
