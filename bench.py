@@ -485,20 +485,24 @@ class TpLayerSetup:
             qz = mb.Nvfp4.quantize((torch.randn(n, kk, device=dev, generator=gw) * 0.02).to(torch.bfloat16))
             self.full[name] = (qz.codes, qz.scales, qz.scale2)
         self.gain = torch.ones(cfgL.hidden, dtype=torch.bfloat16, device=dev)
-        self.fx = None
+        self.fx = self.bulk = None
+
+        def exchange_all(raw):
+            got = [None] * world
+            dist.all_gather_object(got, raw)
+            return got
         if want_fused and world > 1:
-            def exchange_all(raw):
-                got = [None] * world
-                dist.all_gather_object(got, raw)
-                return got
-            # peer stores of 32-byte segments suit decode-sized messages; an 8192-token prompt's partial moves
-            # faster through NCCL's bulk all-reduce, so the exchange is sized for <= 1024 rows
+            # decode-sized messages: the GEMM epilogue scatters its partial tiles into the peers (32-byte segments)
             self.fx = layer.FusedExchange(self.tp, env.local_rank, 64, cfgL.hidden, exchange_all)
+        if world > 1 and os.environ.get("MB_TP_BULK", "1") != "0":
+            # prompt-sized messages: reduce-scatter and all-gather kernels over a peer-mapped region
+            # (MB_TP_BULK=0 in the environment keeps NCCL for them, for comparison runs)
+            self.bulk = layer.BulkExchange(self.tp, env.local_rank, 8192, cfgL.hidden, exchange_all)
         self.params = sum(n * kk for (n, kk) in self.shapes.values())
 
     def make_layer(self, fused):
         return self.layer.DecoderLayer(self.cfg, self.full, self.gain, self.gain, tp=self.tp, group=self.group,
-                                       device=self.env.dev, fused=self.fx if fused else None)
+                                       device=self.env.dev, fused=self.fx if fused else None, bulk=self.bulk)
 
     def reference_layer(self):
         """The unsharded layer over the same stored planes (rank 0 only: the parity arm)."""
@@ -516,6 +520,8 @@ class TpLayerSetup:
         return batch, t, past, x, kc, vc
 
     def close(self):
+        if self.bulk is not None:
+            self.bulk.close()
         if self.fx is not None:
             self.fx.close()
         if self.group is not None:
@@ -577,7 +583,9 @@ def build_tp(env, args, decode, setup=None, fused=None):
     if use_fused:
         reduce = "fused: GEMM epilogue scatters to peers, one reduce+residual+gather kernel"
     elif world > 1 and L_._rows_shard(batch * t):
-        reduce = ("nccl, rows sharded between the exchanges: reduce-scatter f32 by rows, norm + quantizer on the rank's "
+        how = ("peer-memory kernels (peer stores, flags)" if (L_.bulk is not None and L_.bulk.takes(batch * t, cfgL.hidden))
+               else "nccl")
+        reduce = (f"{how}, rows sharded between the exchanges: reduce-scatter f32 by rows, norm + quantizer on the rank's "
                   "rows, all-gather of NVFP4 planes; reduce-scatter f32 + add, all-gather of bf16 rows")
     else:
         reduce = "nccl all-reduce f32 + add" if world > 1 else "none (world 1)"

@@ -536,6 +536,33 @@ int mb_tp_reduce_residual(mb_ctx* ctx, mb_stream stream, const void* resid_bf16,
                           void** out_dev);
 int mb_tp_symm_destroy(mb_ctx* ctx);
 
+/* The same two halves (reduce-scatter by rows, all-gather) as kernels of this library over peer memory, for
+ * prompt-sized messages: tp_reduce's sums (src/models/inkling/tpcomm.rs:1453-1467) with this rank's rows left
+ * local in between. Each rank creates a region of mb_tp_bulk_header_bytes() + user_bytes (64-byte CUDA IPC
+ * handle out), the handles travel over the host link in rank order, mb_tp_bulk_attach maps them
+ * (mb_tp_bulk_attach_ptrs for ranks of one process); mb_tp_bulk_local gives the region's address and that of
+ * its user part, in which the caller lays out receive areas and gathered buffers by byte offset (256-byte
+ * aligned), the same on every rank.
+ * mb_tp_bulk_reduce_scatter_f32: every rank's partial [rows, n] f32 lies at partial_off in its own region (its
+ * row-parallel product wrote it there), rows % world == 0; a rank reads its own rows out of every rank's partial
+ * with peer loads and this rank's rows of the sum, added in rank order, land in out [rows / world, n] (local).
+ * mb_tp_bulk_all_gather: for up to two buffers at off0 / off1 whose rank-th slice of
+ * part_bytes the caller has already written in its OWN region, the slice is pushed to the same place on every
+ * peer and the call's kernel ends when all slices have arrived (part_bytes1 = 0: one buffer).
+ * `step` counts the calls of each kind from 1, the same on every rank. A partial or a gathered buffer may be
+ * written again two calls of its kind later (alternate between two). Waits on peers are bounded by the context's
+ * wait limit; a wait that runs out leaves status 54 / 55 (mb_check_flags) and the context usable. world <= 8. */
+size_t mb_tp_bulk_header_bytes(void);
+int mb_tp_bulk_create(mb_ctx* ctx, size_t user_bytes, uint8_t handle_out[64]);
+int mb_tp_bulk_attach(mb_ctx* ctx, const uint8_t* handles_world_x64, int rank, int world);
+int mb_tp_bulk_attach_ptrs(mb_ctx* ctx, void* const* peers, int rank, int world);
+int mb_tp_bulk_local(mb_ctx* ctx, void** region_out, void** user_out);
+int mb_tp_bulk_reduce_scatter_f32(mb_ctx* ctx, mb_stream stream, size_t partial_off, size_t rows, size_t n, float* out,
+                                  int step);
+int mb_tp_bulk_all_gather(mb_ctx* ctx, mb_stream stream, size_t off0, size_t part_bytes0, size_t off1,
+                          size_t part_bytes1, int step);
+int mb_tp_bulk_destroy(mb_ctx* ctx);
+
 #ifdef __cplusplus
 }
 #endif

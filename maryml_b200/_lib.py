@@ -109,6 +109,14 @@ SIGNATURES = {
     "mb_nvfp4_gemm_w4a4_scatter": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _f, _sz, _sz, _sz, _i]),
     "mb_tp_reduce_residual": (_i, [_vp, _vp, _vp, _sz, _sz, _i, C.POINTER(_vp)]),
     "mb_tp_symm_destroy": (_i, [_vp]),
+    "mb_tp_bulk_header_bytes": (_sz, []),
+    "mb_tp_bulk_create": (_i, [_vp, _sz, C.POINTER(C.c_uint8)]),
+    "mb_tp_bulk_attach": (_i, [_vp, C.POINTER(C.c_uint8), _i, _i]),
+    "mb_tp_bulk_attach_ptrs": (_i, [_vp, C.POINTER(_vp), _i, _i]),
+    "mb_tp_bulk_local": (_i, [_vp, C.POINTER(_vp), C.POINTER(_vp)]),
+    "mb_tp_bulk_reduce_scatter_f32": (_i, [_vp, _vp, _sz, _sz, _sz, _vp, _i]),
+    "mb_tp_bulk_all_gather": (_i, [_vp, _vp, _sz, _sz, _sz, _sz, _i]),
+    "mb_tp_bulk_destroy": (_i, [_vp]),
 }
 
 for _name, (_res, _args) in SIGNATURES.items():

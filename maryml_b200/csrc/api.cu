@@ -35,6 +35,7 @@ MB_API int mb_ctx_create(int device, mb_ctx** out) {
 MB_API void mb_ctx_destroy(mb_ctx* ctx) {
   if (!ctx) return;
   mb_tp_symm_destroy(ctx);
+  mb_tp_bulk_destroy(ctx);
   mb_tp_close(ctx);
   if (ctx->flags_dev) cudaFree(ctx->flags_dev);
   delete ctx;

@@ -66,6 +66,20 @@ struct mb_ctx {
   int tp_rank = 0, tp_world = 1;
   // Peer-mapped exchange memory of the fused row-parallel path (tp.cu).
   struct mb_symm* symm = nullptr;
+  // Peer-mapped region of the prompt-sized exchanges (tp_bulk.cu).
+  struct mb_bulk* bulk = nullptr;
+};
+
+// A region of device memory every rank of the group maps (CUDA IPC): a 4 KB header of flags, then the callers'
+// receive areas and gathered buffers at offsets of their choosing.
+struct mb_bulk {
+  void* local = nullptr;            // this rank's allocation
+  void* peer[8] = {};               // every rank's allocation as seen from here (peer[rank] == local)
+  void** peer_dev = nullptr;        // the same table in device memory
+  size_t bytes = 0;
+  int world = 0, rank = 0;          // world 0: not attached yet
+  bool ipc = true;
+  int* counters = nullptr;          // device words of the exchange kernels (CTAs that finished pushing)
 };
 
 // Exchange memory of one rank, mapped into every rank of the group (CUDA IPC). Layout:

@@ -199,12 +199,102 @@ class FusedExchange:
 
 
 class _DevBuf:
-    def __init__(self, ptr, shape):
-        self.__cuda_array_interface__ = {"shape": shape, "typestr": "<i2", "data": (ptr, False), "version": 3}
+    def __init__(self, ptr, shape, typestr="<i2"):
+        self.__cuda_array_interface__ = {"shape": shape, "typestr": typestr, "data": (ptr, False), "version": 3}
 
 
 def _wrap_bf16(ptr, rows, cols, device):
     return torch.as_tensor(_DevBuf(ptr, (rows, cols)), device=device).view(torch.bfloat16)
+
+
+def _wrap_bytes(ptr, nbytes, device):
+    return torch.as_tensor(_DevBuf(ptr, (nbytes,), "|u1"), device=device)
+
+
+def _align256(n):
+    return (n + 255) // 256 * 256
+
+
+class BulkExchange:
+    """Peer-mapped region for the prompt path's exchanges (mb_tp_bulk_* in the header): reduce-scatter of the f32
+    partial by rows and all-gather of the next product's NVFP4 planes or of the output rows, as peer stores from
+    kernels of the library instead of NCCL rings. Sized for activations up to [rows_max, hidden]; two of every
+    receive area and gathered buffer, used in turn. `exchange_all` all-gathers one bytes object per rank."""
+
+    def __init__(self, tp, device, rows_max, hidden, exchange_all):
+        self.tp, self.ctx, self.rows_max, self.hidden = tp, context(device), rows_max, hidden
+        self.device = torch.device("cuda", device) if isinstance(device, int) else device
+        recv = _align256(rows_max * hidden * 4)
+        codes = _align256(rows_max * hidden // 2)
+        sf = _align256(nv.sf_bytes(rows_max, hidden))
+        out = _align256(rows_max * hidden * 2)
+        self.off_recv = [0, recv]
+        self.off_codes = [2 * recv, 2 * recv + codes]
+        self.off_sf = [2 * recv + 2 * codes, 2 * recv + 2 * codes + sf]
+        self.off_out = [2 * recv + 2 * codes + 2 * sf, 2 * recv + 2 * codes + 2 * sf + out]
+        total = 2 * (recv + codes + sf + out)
+        h = (C.c_uint8 * 64)()
+        self.ctx.check(lib.mb_tp_bulk_create(self.ctx.handle, total, h))
+        handles = b"".join(exchange_all(bytes(h)))
+        buf = (C.c_uint8 * (64 * tp.world)).from_buffer_copy(handles)
+        self.ctx.check(lib.mb_tp_bulk_attach(self.ctx.handle, buf, tp.rank, tp.world))
+        user = C.c_void_p()
+        self.ctx.check(lib.mb_tp_bulk_local(self.ctx.handle, None, C.byref(user)))
+        self.user = user.value
+        self.n_rs = self.n_ag = 0            # exchanges of each kind so far (the kernels' step numbers)
+        self.n_planes = self.n_rows = 0      # gathers of each buffer kind so far (which of the two buffers is next)
+
+    def takes(self, rows, hidden):
+        return hidden == self.hidden and rows <= self.rows_max
+
+    def partial_buffer(self, rows):
+        """Where the next reduce-scatter's f32 partial [rows, hidden] goes: inside the region, so that the peers can
+        read it (the row-parallel product writes it there directly)."""
+        ptr = self.user + self.off_recv[(self.n_rs + 1) & 1]
+        return torch.as_tensor(_DevBuf(ptr, (rows, self.hidden), "<f4"), device=self.device)
+
+    def reduce_scatter_f32(self, t):
+        """SUM reduce-scatter by rows of the partial in partial_buffer (t is that buffer, or is copied into it):
+        this rank's [rows / world, hidden] of the sum."""
+        assert t.dtype == torch.float32 and t.is_contiguous() and t.shape[0] % self.tp.world == 0
+        buf = self.partial_buffer(t.shape[0])
+        if t.data_ptr() != buf.data_ptr():
+            buf.copy_(t)
+        self.n_rs += 1
+        out = torch.empty((t.shape[0] // self.tp.world, t.shape[1]), dtype=torch.float32, device=t.device)
+        self.ctx.check(lib.mb_tp_bulk_reduce_scatter_f32(self.ctx.handle, _stream(), self.off_recv[self.n_rs & 1], t.shape[0],
+                                                         t.shape[1], _p(out), self.n_rs))
+        return out
+
+    def planes(self, rows):
+        """The next all-gather's activation planes as tensors inside the region: codes [rows, hidden / 2] and the
+        tiled scale plane; the caller writes its own rows' part, all_gather_planes brings the others'."""
+        par = (self.n_planes + 1) & 1
+        codes = _wrap_bytes(self.user + self.off_codes[par], rows * self.hidden // 2, self.device).view(rows, self.hidden // 2)
+        sf = _wrap_bytes(self.user + self.off_sf[par], nv.sf_bytes(rows, self.hidden), self.device)
+        return codes, sf
+
+    def all_gather_planes(self, rows):
+        self.n_ag += 1
+        self.n_planes += 1
+        par = self.n_planes & 1
+        w = self.tp.world
+        self.ctx.check(lib.mb_tp_bulk_all_gather(self.ctx.handle, _stream(), self.off_codes[par], rows * self.hidden // 2 // w,
+                                                 self.off_sf[par], nv.sf_bytes(rows, self.hidden) // w, self.n_ag))
+
+    def rows_buffer(self, rows):
+        """The next all-gather's bf16 rows [rows, hidden] inside the region."""
+        par = (self.n_rows + 1) & 1
+        return _wrap_bf16(self.user + self.off_out[par], rows, self.hidden, self.device)
+
+    def all_gather_rows(self, rows):
+        self.n_ag += 1
+        self.n_rows += 1
+        self.ctx.check(lib.mb_tp_bulk_all_gather(self.ctx.handle, _stream(), self.off_out[self.n_rows & 1],
+                                                 rows * self.hidden * 2 // self.tp.world, 0, 0, self.n_ag))
+
+    def close(self):
+        lib.mb_tp_bulk_destroy(self.ctx.handle)
 
 
 # ---- the layer -----------------------------------------------------------------------
@@ -221,8 +311,10 @@ class DecoderLayer:
     (codes [n, k/2], scales [n, k/16], scale2) quantised BEFORE the cut, so every rank
     holds bytes of the same stored tensor (the reference cuts stored planes)."""
 
-    def __init__(self, cfg, full, input_gain, post_gain, tp=None, group=None, device=None, fused=None, fuse=True):
+    def __init__(self, cfg, full, input_gain, post_gain, tp=None, group=None, device=None, fused=None, fuse=True,
+                 bulk=None):
         self.cfg, self.tp, self.group, self.fused, self.fuse = cfg, tp or Tp(), group, fused, fuse
+        self.bulk = bulk              # BulkExchange: the prompt path's exchanges over peer memory instead of NCCL
         dev = device if device is not None else torch.device("cuda", torch.cuda.current_device())
         D = cfg.head_dim
         qh, kvh = self.tp.q_heads(cfg.heads), self.tp.kv_heads(cfg.kv_heads)
@@ -269,13 +361,13 @@ class DecoderLayer:
         return codes, sf, x.shape[0]
 
     @staticmethod
-    def _project(xq, w, out_dtype=torch.bfloat16):
+    def _project(xq, w, out_dtype=torch.bfloat16, out=None):
         codes, sf, t = xq
-        return nv.gemm_w4a4(codes, sf, w.codes, w.sf_tiled(), w.scale2, t, w.n(), w.k(), out_dtype=out_dtype)
+        return nv.gemm_w4a4(codes, sf, w.codes, w.sf_tiled(), w.scale2, t, w.n(), w.k(), out_dtype=out_dtype, out=out)
 
-    def _linear(self, x, w, out_dtype=torch.bfloat16):
+    def _linear(self, x, w, out_dtype=torch.bfloat16, out=None):
         """W4A4 projection (src/nn/nvfp4_gemm.rs:644-694)."""
-        return self._project(self._quantize(x), w, out_dtype)
+        return self._project(self._quantize(x), w, out_dtype, out=out)
 
     def _reduced_residual(self, resid, x, w):
         """bf16(resid + bf16(all-reduced x . w^T)): NCCL all-reduce of the f32 partial then the add,
@@ -325,11 +417,11 @@ class DecoderLayer:
         return flash_attention(q, k_cache, v_cache, q0=past, scale=1.0 / math.sqrt(D), causal=True,
                                keys=past + t).view(batch * t, self.local_heads * D)
 
-    def half_attention(self, x, batch, past, k_cache, v_cache, after_rope=None, before_rope=None):
+    def half_attention(self, x, batch, past, k_cache, v_cache, after_rope=None, before_rope=None, out=None):
         """The attention half up to the exchange step: this rank's f32 share of the o projection, [rows, hidden].
         The shares of all ranks sum to the whole projection (src/models/inkling/session.rs:2713-2717)."""
         a = self._attention(x, batch, past, k_cache, v_cache, after_rope, before_rope)
-        return self._linear(a, self.wo, out_dtype=torch.float32)
+        return self._linear(a, self.wo, out_dtype=torch.float32, out=out)
 
     def half_mlp(self, x, o_sum):
         """The MLP half between the two exchange steps: given the layer input and the SUMMED o partial, the new
@@ -397,19 +489,38 @@ class DecoderLayer:
         lo = r * local
         dev = x.device
         ctx = context(dev.index)
-        o_local = self.group.reduce_scatter_f32(
-            self.half_attention(x, batch, past, k_cache, v_cache, after_rope, before_rope))
-        codes = torch.empty((rows, hidden // 2), dtype=torch.uint8, device=dev)
-        sf = torch.empty(nv.sf_bytes(rows, hidden), dtype=torch.uint8, device=dev)
+        bulk = self.bulk if (self.bulk is not None and self.bulk.takes(rows, hidden)) else None
+        ex = bulk or self.group                       # peer-memory kernels of this library, or NCCL
+        # with the peer-memory exchange the row-parallel products write their partials where the peers read them
+        part_out = (lambda: bulk.partial_buffer(rows)) if bulk is not None else (lambda: None)
+        o_local = ex.reduce_scatter_f32(self.half_attention(x, batch, past, k_cache, v_cache, after_rope, before_rope,
+                                                            out=part_out()))
+        if bulk is not None:
+            codes, sf = bulk.planes(rows)
+        else:
+            codes = torch.empty((rows, hidden // 2), dtype=torch.uint8, device=dev)
+            sf = torch.empty(nv.sf_bytes(rows, hidden), dtype=torch.uint8, device=dev)
         sf_part = sf.numel() // w                      # whole 128-row tiles per rank: a contiguous range of the plane
         resid_local = torch.empty((local, hidden), dtype=torch.bfloat16, device=dev)
         ctx.check(lib.mb_residual_norm_quantize(ctx.handle, _stream(), _p(x[lo:lo + local]), _p(o_local), _p(self.post_gain),
                                                 local, hidden, float(cfg.eps), _p(resid_local), _p(codes[lo:lo + local]),
                                                 C.c_void_p(sf.data_ptr() + r * sf_part)))
-        self.group.all_gather_rows(codes)
-        self.group.all_gather_rows(sf)
+        if bulk is not None:
+            bulk.all_gather_planes(rows)
+        else:
+            self.group.all_gather_rows(codes)
+            self.group.all_gather_rows(sf)
         act = nv.gemm_w4a4_stacked(codes, sf, self.wgu, rows, epilogue=_lib.EPI_SWIGLU_ROUNDED | _lib.EPI_QUANT_SCALED)
-        d_local = self.group.reduce_scatter_f32(self._project((act[0], act[1], rows), self.wdown, out_dtype=torch.float32))
+        d_local = ex.reduce_scatter_f32(self._project((act[0], act[1], rows), self.wdown, out_dtype=torch.float32,
+                                                      out=part_out()))
+        if bulk is not None:
+            y = bulk.rows_buffer(rows)                 # lives in the region until the exchange after next
+            add_f32(resid_local, d_local, out=y[lo:lo + local])
+            bulk.all_gather_rows(rows)
+            if out is not None:
+                out.copy_(y)
+                return out
+            return y
         y = out if out is not None else torch.empty((rows, hidden), dtype=torch.bfloat16, device=dev)
         assert y.is_contiguous()
         add_f32(resid_local, d_local, out=y[lo:lo + local])

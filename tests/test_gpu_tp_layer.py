@@ -97,6 +97,7 @@ def _worker(rank, world, port, out_path, fused=False):
         rms = a.pow(2).mean().sqrt()
         assert (a - b).abs().max() <= 2e-2 * rms, float((a - b).abs().max() / rms)
         assert torch.equal(pk.view(torch.int16), pk2.view(torch.int16))
+        _bulk_exchange_checks(rank, world, store, layer, cfg, full, g1, g2, tp, group, orc, kv, whole if world == 2 else None)
     if rank == 0:
         np.save(out_path, y.float().cpu().numpy())
     store.set(f"done{rank}", b"1")
@@ -105,6 +106,64 @@ def _worker(rank, world, port, out_path, fused=False):
     if fx is not None:
         fx.close()
     group.close()
+
+
+def _bulk_exchange_checks(rank, world, store, layer, cfg, full, g1, g2, tp, group, orc, kv, whole_512):
+    """The prompt path's exchanges as peer-memory kernels (mb_tp_bulk_*): the reduce-scatter against the sum of every
+    rank's partial in rank order (bit for bit: each rank rebuilds all partials from their seeds), the all-gather
+    against the slices every rank is known to have written, three rounds through both buffers of each kind; then the
+    layer through them against the same layer through NCCL."""
+    dev = torch.device("cuda", rank)
+
+    def exchange_all(raw):
+        key = f"bulk{len(raw)}_{exchange_all.n}"
+        exchange_all.n += 1
+        store.set(f"{key}_{rank}", raw)
+        return [store.get(f"{key}_{r}") for r in range(world)]
+    exchange_all.n = 0
+    rows_max = 256 * world
+    bulk = layer.BulkExchange(tp, rank, rows_max, cfg.hidden, exchange_all)
+    for rnd in range(3):
+        rows = rows_max if rnd != 1 else 128 * world
+        parts = [torch.randn(rows, cfg.hidden, generator=torch.Generator().manual_seed(1000 * rnd + r)) for r in range(world)]
+        got = bulk.reduce_scatter_f32(parts[rank].to(dev))
+        local = rows // world
+        want = parts[0][rank * local:(rank + 1) * local].clone()
+        for r in range(1, world):
+            want += parts[r][rank * local:(rank + 1) * local]
+        assert torch.equal(got.cpu(), want), rnd
+        codes, sf = bulk.planes(rows)
+        sf_part = sf.numel() // world
+        codes[rank * local:(rank + 1) * local] = (rank + 1 + rnd) & 0xFF
+        sf[rank * sf_part:(rank + 1) * sf_part] = (0x40 + rank + rnd) & 0xFF
+        bulk.all_gather_planes(rows)
+        yb = bulk.rows_buffer(rows)
+        yb[rank * local:(rank + 1) * local] = float(rank + 2 + rnd)
+        bulk.all_gather_rows(rows)
+        torch.cuda.synchronize()
+        for r in range(world):
+            assert bool((codes[r * local:(r + 1) * local] == ((r + 1 + rnd) & 0xFF)).all()), (rnd, r)
+            assert bool((sf[r * sf_part:(r + 1) * sf_part] == ((0x40 + r + rnd) & 0xFF)).all()), (rnd, r)
+            assert bool((yb[r * local:(r + 1) * local] == float(r + 2 + rnd)).all()), (rnd, r)
+    # the layer's prompt path through these exchanges and through NCCL
+    Lb = layer.DecoderLayer(cfg, full, g1, g2, tp=tp, group=group, device=dev, bulk=bulk)
+    Ln = layer.DecoderLayer(cfg, full, g1, g2, tp=tp, group=group, device=dev)
+    pt = rows_max
+    assert Lb._rows_shard(pt)
+    px, pk, pv = _inputs(orc, cfg, 1, pt, pt)
+    pk, pv = pk[:, :, kv.start:kv.stop].contiguous().cuda(), pv[:, :, kv.start:kv.stop].contiguous().cuda()
+    a = Lb._forward_fused(px.cuda(), 1, 0, pk.clone(), pv.clone()).clone()
+    b = Ln._forward_fused(px.cuda(), 1, 0, pk.clone(), pv.clone())
+    torch.cuda.synchronize()
+    if world == 2:
+        assert torch.equal(a.view(torch.int16), b.view(torch.int16))       # two partials add in one order only
+    else:
+        rms = b.float().pow(2).mean().sqrt()
+        assert (a.float() - b.float()).abs().max() <= 2e-2 * rms
+    from maryml_b200 import _lib
+    rc, flags = _lib.context(rank).check_flags(None)
+    assert rc == 0, flags
+    bulk.close()
 
 
 @pytest.mark.parametrize("world", [2, 4, 8])
