@@ -425,3 +425,56 @@ def test_wait_on_an_absent_peer_runs_out_and_the_context_stays_usable(mods, orc)
     finally:
         lib.mb_ctx_set_wait_limit_us(ctx.handle, 1000000)
         lib.mb_tp_symm_destroy(ctx.handle)
+
+
+def test_prompt_exchanges_give_up_on_an_absent_peer_and_work_once_it_answers(mods):
+    """The prompt path's reduce-scatter and all-gather kernels (mb_tp_bulk_*) wait on flags their peers write. Rank 0
+    of a world of two is attached to a second LOCAL buffer standing in for a peer that never runs: each kernel gives
+    up after the context's wait limit with its own status code and ends; once the stand-in's flags are written by
+    hand (its partial holds a known pattern) the same calls complete and the sums are exact."""
+    _, _, _, _lib = mods
+    from maryml_b200.layer import _DevBuf
+    lib, ctx = _lib.lib, _lib.context(0)
+    dev = torch.device("cuda", 0)
+    rows, n = 256, 1024
+    user = 2 * rows * n * 4
+    hdr = int(lib.mb_tp_bulk_header_bytes())
+    assert lib.mb_tp_bulk_destroy(ctx.handle) == 0
+    handle = (C.c_uint8 * 64)()
+    ctx.check(lib.mb_tp_bulk_create(ctx.handle, user, handle))
+    try:
+        region, mine = C.c_void_p(), C.c_void_p()
+        ctx.check(lib.mb_tp_bulk_local(ctx.handle, C.byref(region), C.byref(mine)))
+        standin = torch.zeros(hdr + user, dtype=torch.uint8, device=dev)
+        peers = (C.c_void_p * 2)(region, standin.data_ptr())
+        ctx.check(lib.mb_tp_bulk_attach_ptrs(ctx.handle, peers, 0, 2))
+        ctx.check(lib.mb_ctx_set_wait_limit_us(ctx.handle, 2000))
+        stream = C.c_void_p(torch.cuda.current_stream().cuda_stream)
+        my_partial = torch.as_tensor(_DevBuf(mine.value, (rows, n), "<f4"), device=dev)
+        my_partial.copy_(torch.arange(rows * n, dtype=torch.float32, device=dev).view(rows, n) % 1024)
+        peer_partial = standin[hdr:hdr + rows * n * 4].view(torch.float32).view(rows, n)
+        peer_partial.fill_(0.25)
+        out = torch.full((rows // 2, n), -1.0, device=dev)
+        ctx.check(lib.mb_tp_bulk_reduce_scatter_f32(ctx.handle, stream, 0, rows, n, out.data_ptr(), 1))
+        rc, flags = ctx.check_flags(None)
+        assert rc == _lib.ERR_DEVICE_FLAG and flags[0] == 54 and flags[4] == 1, flags
+        assert bool((out == -1.0).all())                                   # nothing was summed
+        ctx.check(lib.mb_tp_bulk_all_gather(ctx.handle, stream, rows * n * 4, 4096, 0, 0, 1))
+        rc, flags = ctx.check_flags(None)
+        assert rc == _lib.ERR_DEVICE_FLAG and flags[0] == 55 and flags[4] == 1, flags
+        # the peer "answers": its flag words of step 2 (reduce-scatter word 1, all-gather word 33) written by hand
+        words = torch.as_tensor(_DevBuf(region.value, (hdr // 4,), "<i4"), device=dev)
+        words[1] = 2
+        words[33] = 2
+        torch.cuda.synchronize()
+        ctx.check(lib.mb_tp_bulk_reduce_scatter_f32(ctx.handle, stream, 0, rows, n, out.data_ptr(), 2))
+        ctx.check(lib.mb_tp_bulk_all_gather(ctx.handle, stream, rows * n * 4, 4096, 0, 0, 2))
+        rc, flags = ctx.check_flags(None)
+        assert rc == 0, flags
+        assert torch.equal(out, my_partial[: rows // 2] + 0.25)            # rank 0's rows: its own partial plus the peer's
+        # the all-gather pushed this rank's slice into the stand-in's copy of the buffer
+        src = torch.as_tensor(_DevBuf(mine.value + rows * n * 4, (4096,), "|u1"), device=dev)
+        assert torch.equal(standin[hdr + rows * n * 4: hdr + rows * n * 4 + 4096], src)
+    finally:
+        lib.mb_ctx_set_wait_limit_us(ctx.handle, 1000000)
+        lib.mb_tp_bulk_destroy(ctx.handle)
