@@ -592,7 +592,10 @@ def build_tp(env, args, decode, setup=None, fused=None):
     w = {
         "step": lambda: L_.forward(x, batch, past, kc, vc), "e2e": e2e, "units": batch * t,
         "metric": f"tp_layer_{'decode' if decode else 'prefill'}_tokens_per_s", "unit": "tokens/s",
-        "launches": tp_launches(setup, L_, batch * t, decode, use_fused), "h2d": x.numel() * 2, "d2h": x.numel() * 2,
+        "launches": tp_launches(setup, L_, batch * t, decode, use_fused) +
+                    (4 if (not use_fused and world > 1 and L_._rows_shard(batch * t) and L_.bulk is not None
+                           and L_.bulk.takes(batch * t, cfgL.hidden)) else 0),      # two reduce-scatters, two all-gathers
+        "h2d": x.numel() * 2, "d2h": x.numel() * 2,
         "roof": roof, "reduce": reduce,
         "config": {"workload": f"tp_{'decode' if decode else 'prefill'}_hidden4096_heads32_kv8_ffn14336_batch{batch}_t{t}_past{past}",
                    "parallelism": f"tp{world}", "reduce": reduce},
