@@ -549,8 +549,9 @@ int mb_tp_symm_destroy(mb_ctx* ctx);
  * mb_tp_bulk_all_gather: for up to two buffers at off0 / off1 whose rank-th slice of
  * part_bytes the caller has already written in its OWN region, the slice is pushed to the same place on every
  * peer and the call's kernel ends when all slices have arrived (part_bytes1 = 0: one buffer).
- * `step` counts the calls of each kind from 1, the same on every rank. A partial or a gathered buffer may be
- * written again two calls of its kind later (alternate between two). Waits on peers are bounded by the context's
+ * `step` counts the calls of each kind from 1, the same on every rank, and the calls of a kind run in that order
+ * (issue them on one stream). A partial or a gathered buffer may be written again two calls of its kind later
+ * (alternate between two). Waits on peers are bounded by the context's
  * wait limit; a wait that runs out leaves status 54 / 55 (mb_check_flags) and the context usable. world <= 8. */
 size_t mb_tp_bulk_header_bytes(void);
 int mb_tp_bulk_create(mb_ctx* ctx, size_t user_bytes, uint8_t handle_out[64]);

@@ -219,7 +219,8 @@ class BulkExchange:
     """Peer-mapped region for the prompt path's exchanges (mb_tp_bulk_* in the header): reduce-scatter of the f32
     partial by rows and all-gather of the next product's NVFP4 planes or of the output rows, as peer stores from
     kernels of the library instead of NCCL rings. Sized for activations up to [rows_max, hidden]; two of every
-    receive area and gathered buffer, used in turn. `exchange_all` all-gathers one bytes object per rank."""
+    partial and gathered buffer, used in turn. All exchanges of one object are issued on one stream (their step
+    numbers are their issue order). `exchange_all` all-gathers one bytes object per rank."""
 
     def __init__(self, tp, device, rows_max, hidden, exchange_all):
         self.tp, self.ctx, self.rows_max, self.hidden = tp, context(device), rows_max, hidden
@@ -315,6 +316,7 @@ class DecoderLayer:
                  bulk=None):
         self.cfg, self.tp, self.group, self.fused, self.fuse = cfg, tp or Tp(), group, fused, fuse
         self.bulk = bulk              # BulkExchange: the prompt path's exchanges over peer memory instead of NCCL
+        self._chunked = False         # inside forward_chunked
         dev = device if device is not None else torch.device("cuda", torch.cuda.current_device())
         D = cfg.head_dim
         qh, kvh = self.tp.q_heads(cfg.heads), self.tp.kv_heads(cfg.kv_heads)
@@ -489,7 +491,9 @@ class DecoderLayer:
         lo = r * local
         dev = x.device
         ctx = context(dev.index)
-        bulk = self.bulk if (self.bulk is not None and self.bulk.takes(rows, hidden)) else None
+        # the peer-memory exchanges count their steps in issue order on ONE stream; the chunked path runs its chunks
+        # on two streams and keeps NCCL
+        bulk = self.bulk if (self.bulk is not None and self.bulk.takes(rows, hidden) and not self._chunked) else None
         ex = bulk or self.group                       # peer-memory kernels of this library, or NCCL
         # with the peer-memory exchange the row-parallel products write their partials where the peers read them
         part_out = (lambda: bulk.partial_buffer(rows)) if bulk is not None else (lambda: None)
@@ -549,6 +553,7 @@ class DecoderLayer:
         if split:
             sms = torch.cuda.get_device_properties(x.device).multi_processor_count
             ctx.check(lib.mb_ctx_set_sm_limit(ctx.handle, sms - self.COLLECTIVE_SMS))
+        self._chunked = True
         try:
             for st in self._side:
                 st.wait_stream(main)
@@ -562,6 +567,7 @@ class DecoderLayer:
             for st in self._side:
                 main.wait_stream(st)
         finally:
+            self._chunked = False
             if split:
                 ctx.check(lib.mb_ctx_set_sm_limit(ctx.handle, 0))
         return out
