@@ -497,7 +497,17 @@ class TpLayerSetup:
         if world > 1 and os.environ.get("MB_TP_BULK", "1") != "0":
             # prompt-sized messages: reduce-scatter and all-gather kernels over a peer-mapped region
             # (MB_TP_BULK=0 in the environment keeps NCCL for them, for comparison runs)
-            self.bulk = layer.BulkExchange(self.tp, env.local_rank, 8192, cfgL.hidden, exchange_all)
+            # every rank has to end up with the same answer: one that cannot map its peers sends all back to NCCL
+            try:
+                self.bulk = layer.BulkExchange(self.tp, env.local_rank, 8192, cfgL.hidden, exchange_all)
+                mine = 1.0
+            except Exception as exc:
+                sys.stderr.write(f"bench.py: rank {rank}: no peer-memory region for the prompt exchanges ({exc}); NCCL instead\n")
+                mine = 0.0
+            (worst,) = env.max_over_ranks([1.0 - mine])
+            if worst > 0.0 and self.bulk is not None:
+                self.bulk.close()
+                self.bulk = None
         self.params = sum(n * kk for (n, kk) in self.shapes.values())
 
     def make_layer(self, fused):
