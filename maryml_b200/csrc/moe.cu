@@ -35,6 +35,7 @@ router_topk_kernel(const float* __restrict__ logits, const float* __restrict__ b
                    uint32_t n_experts, uint32_t k, int renormalize, float scaling, int32_t* __restrict__ idx,
                    float* __restrict__ weight, int* __restrict__ flag) {
   extern __shared__ double s_router[];
+  mb_grid_dependency_sync();
   constexpr uint32_t ROW = 32 * EPL + 1;             // odd stride in doubles: the column walk below meets no bank twice
   double* s_e = s_router;                            // [ROUTER_TOKENS][ROW]
   double* s_sum = s_router + ROUTER_TOKENS * ROW;    // [ROUTER_TOKENS]
@@ -249,6 +250,7 @@ plan_count_kernel(const int32_t* __restrict__ idx, uint32_t tokens, uint32_t k, 
                   uint32_t m_cap, int* __restrict__ flag) {
   extern __shared__ int32_t s_hist[];
   for (uint32_t e = threadIdx.x; e < n_experts; e += PLAN_CHUNK) s_hist[e] = 0;
+  mb_grid_dependency_sync();
   for (uint32_t i = blockIdx.x * PLAN_CHUNK + threadIdx.x; i < m_cap; i += gridDim.x * PLAN_CHUNK) {
     row_tok[i] = -1;
     row_wgt[i] = 0.0f;
@@ -277,6 +279,7 @@ plan_scan_kernel(const int32_t* __restrict__ chunk_counts, int32_t* __restrict__
   __shared__ int32_t s_pad[1024];
   __shared__ int32_t s_off[1024];
   __shared__ int32_t s_total;
+  mb_grid_dependency_sync();
   const uint32_t e = threadIdx.x;
   int32_t c = 0;
   if (e < n_experts) {
@@ -338,6 +341,7 @@ plan_place_kernel(const int32_t* __restrict__ idx, const float* __restrict__ wei
                   int32_t* __restrict__ row_tok, float* __restrict__ row_wgt, int32_t* __restrict__ tok_rows) {
   extern __shared__ uint32_t s_mask[];   // [n_experts][8]
   for (uint32_t i = threadIdx.x; i < n_experts * 8; i += PLAN_CHUNK) s_mask[i] = 0u;
+  mb_grid_dependency_sync();
   __syncthreads();
   const uint32_t t = blockIdx.x * PLAN_CHUNK + threadIdx.x;
   const uint32_t word = threadIdx.x >> 5, bit = threadIdx.x & 31;
@@ -380,6 +384,7 @@ scatter_weighted_kernel(const Y* __restrict__ y, const float* __restrict__ row_w
                         const int32_t* __restrict__ tok_rows, uint32_t tokens, uint32_t k, uint32_t h,
                         float* __restrict__ out) {
   const uint32_t per_tok = h / 8;
+  mb_grid_dependency_sync();
   size_t gid = size_t(blockIdx.x) * 256 + threadIdx.x;
   if (gid >= size_t(tokens) * per_tok) return;
   uint32_t t = uint32_t(gid / per_tok), c = uint32_t(gid % per_tok) * 8;
@@ -419,6 +424,7 @@ plan_place8_kernel(const int32_t* __restrict__ idx, const float* __restrict__ we
                    int32_t* __restrict__ row_tok, float* __restrict__ row_wgt, int32_t* __restrict__ tok_rows) {
   extern __shared__ uint32_t s_mask[];   // [n_experts][8]
   for (uint32_t i = threadIdx.x; i < n_experts * 8; i += PLAN_CHUNK) s_mask[i] = 0u;
+  mb_grid_dependency_sync();
   const uint32_t t = blockIdx.x * PLAN_CHUNK + threadIdx.x;
   const uint32_t word = threadIdx.x >> 5, bit = threadIdx.x & 31;
   const bool live = t < tokens;
@@ -501,8 +507,8 @@ MB_API int mb_router_topk(mb_ctx* ctx, mb_stream stream_, const float* logits, c
     auto kern = router_topk_kernel<EPL, SIG, WARPS>;                                                            \
     if (smem > 48 * 1024)                                                                                       \
       MB_CUDA_OK(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)));      \
-    kern<<<grid, 32 * WARPS, smem, stream>>>(logits, bias, uint32_t(tokens), uint32_t(n_experts), uint32_t(k),  \
-                                             renormalize, scaling, idx, weight, flag);                          \
+    mb_launch_pdl(kern, dim3(grid), dim3(32 * WARPS), smem, stream, logits, bias, uint32_t(tokens),             \
+                  uint32_t(n_experts), uint32_t(k), renormalize, scaling, idx, weight, flag);                   \
   } while (0)
 #define ROUTE(EPL) do { if (sigmoid) ROUTE1(EPL, true); else ROUTE1(EPL, false); } while (0)
   switch (n_experts / 32) {
@@ -589,21 +595,21 @@ MB_API int mb_moe_plan(mb_ctx* ctx, mb_stream stream_, const int32_t* idx, const
   int32_t* chunk_counts = static_cast<int32_t*>(workspace);
   const unsigned chunks = unsigned((tokens + PLAN_CHUNK - 1) / PLAN_CHUNK);
   int* flag = ctx->flags_dev + MB_FLAG_PLAN_FAULT;
-  plan_count_kernel<<<chunks, PLAN_CHUNK, n_experts * sizeof(int32_t), stream>>>(
-      idx, uint32_t(tokens), uint32_t(k), uint32_t(n_experts), chunk_counts, row_tok, row_wgt, uint32_t(m_cap), flag);
+  mb_launch_pdl(plan_count_kernel, dim3(chunks), dim3(PLAN_CHUNK), n_experts * sizeof(int32_t), stream, idx,
+                uint32_t(tokens), uint32_t(k), uint32_t(n_experts), chunk_counts, row_tok, row_wgt, uint32_t(m_cap), flag);
   MB_LAUNCH_OK(ctx);
   int32_t* chunk_base = chunk_counts + size_t(chunks) * n_experts;
-  plan_scan_kernel<<<1, 1024, 0, stream>>>(chunk_counts, chunk_base, chunks, uint32_t(n_experts), expert_rows,
-                                           expert_row0, tile_expert, uint32_t(m_cap / PLAN_PAD), n_tiles);
+  mb_launch_pdl(plan_scan_kernel, dim3(1), dim3(1024), 0, stream, chunk_counts, chunk_base, uint32_t(chunks),
+                uint32_t(n_experts), expert_rows, expert_row0, tile_expert, uint32_t(m_cap / PLAN_PAD), n_tiles);
   MB_LAUNCH_OK(ctx);
   if (k <= 8)
-    plan_place8_kernel<<<chunks, PLAN_CHUNK, n_experts * 32, stream>>>(idx, weight, uint32_t(tokens), uint32_t(k),
-                                                                       uint32_t(n_experts), chunk_base, expert_row0,
-                                                                       row_tok, row_wgt, tok_rows);
+    mb_launch_pdl(plan_place8_kernel, dim3(chunks), dim3(PLAN_CHUNK), n_experts * 32, stream, idx, weight,
+                  uint32_t(tokens), uint32_t(k), uint32_t(n_experts), chunk_base, expert_row0, row_tok, row_wgt,
+                  tok_rows);
   else
-    plan_place_kernel<<<chunks, PLAN_CHUNK, n_experts * 32, stream>>>(idx, weight, uint32_t(tokens), uint32_t(k),
-                                                                      uint32_t(n_experts), chunk_base, expert_row0,
-                                                                      row_tok, row_wgt, tok_rows);
+    mb_launch_pdl(plan_place_kernel, dim3(chunks), dim3(PLAN_CHUNK), n_experts * 32, stream, idx, weight,
+                  uint32_t(tokens), uint32_t(k), uint32_t(n_experts), chunk_base, expert_row0, row_tok, row_wgt,
+                  tok_rows);
   MB_LAUNCH_OK(ctx);
   return MB_OK;
 }
@@ -617,12 +623,11 @@ MB_API int mb_moe_scatter_weighted(mb_ctx* ctx, mb_stream stream_, const void* y
   size_t total = tokens * (h / 8);
   unsigned grid = unsigned((total + 255) / 256);
   if (y_dtype == MB_DT_BF16)
-    scatter_weighted_kernel<__nv_bfloat16><<<grid, 256, 0, stream>>>(static_cast<const __nv_bfloat16*>(y), row_wgt,
-                                                                      tok_rows, uint32_t(tokens), uint32_t(k),
-                                                                      uint32_t(h), out);
+    mb_launch_pdl(scatter_weighted_kernel<__nv_bfloat16>, dim3(grid), dim3(256), 0, stream,
+                  static_cast<const __nv_bfloat16*>(y), row_wgt, tok_rows, uint32_t(tokens), uint32_t(k), uint32_t(h), out);
   else if (y_dtype == MB_DT_F32)
-    scatter_weighted_kernel<float><<<grid, 256, 0, stream>>>(static_cast<const float*>(y), row_wgt, tok_rows,
-                                                             uint32_t(tokens), uint32_t(k), uint32_t(h), out);
+    mb_launch_pdl(scatter_weighted_kernel<float>, dim3(grid), dim3(256), 0, stream, static_cast<const float*>(y),
+                  row_wgt, tok_rows, uint32_t(tokens), uint32_t(k), uint32_t(h), out);
   else
     return mb_fail(ctx, MB_ERR_INVALID, "scatter_weighted: y is bf16 or f32");
   MB_LAUNCH_OK(ctx);

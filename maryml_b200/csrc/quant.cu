@@ -289,8 +289,11 @@ tile_scales_kernel(const uint8_t* __restrict__ in, size_t rows, size_t row_block
 // = 128 rows x 4 scales, one word per row) are written whole, thread by consecutive word, from
 // the scattered words of the source plane. Pad rows and the K padding of the plane get zeros,
 // so the kernel writes every byte of both output planes. A negative source is a zero row.
-constexpr int GATHER_THREADS = 512;
+constexpr int GATHER_THREADS = 128;
+constexpr int GATHER_SPLIT = 4;      // blocks per 128-row tile: 32 code rows and every fourth scale atom each
 
+// Four small blocks per tile rather than one large one: a plan of a few hundred tiles then spreads evenly over
+// the SMs (with one block per tile some SMs held three tiles and others two).
 __global__ void __launch_bounds__(GATHER_THREADS)
 gather_planes_kernel(const uint4* __restrict__ codes, const uint8_t* __restrict__ sf, const int32_t* __restrict__ gather,
                      uint32_t rows, uint32_t src_rows, uint32_t code_vecs, uint32_t sf_words, uint32_t kchunks,
@@ -298,8 +301,9 @@ gather_planes_kernel(const uint4* __restrict__ codes, const uint8_t* __restrict_
   __shared__ int32_t s_src[128];
   mb_grid_dependency_sync();
   const uint32_t lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const uint32_t row0 = blockIdx.x * 128;
-  if (threadIdx.x < 128) {
+  const uint32_t tile = blockIdx.x / GATHER_SPLIT, sub = blockIdx.x % GATHER_SPLIT;
+  const uint32_t row0 = tile * 128;
+  {
     const uint32_t row = row0 + threadIdx.x;
     int32_t src = row < rows ? __ldg(gather + row) : -1;
     if (src >= int32_t(src_rows)) {
@@ -309,10 +313,11 @@ gather_planes_kernel(const uint4* __restrict__ codes, const uint8_t* __restrict_
     s_src[threadIdx.x] = src;
   }
   __syncthreads();
-  // codes: warp w copies rows 8 w .. 8 w + 7 of the tile
+  // codes: warp w copies rows 32 sub + 8 w .. + 7 of the tile
+  const uint32_t r0 = sub * 32 + warp * 8;
   int32_t src[8];
 #pragma unroll
-  for (int r = 0; r < 8; ++r) src[r] = s_src[warp * 8 + r];
+  for (int r = 0; r < 8; ++r) src[r] = s_src[r0 + r];
   for (uint32_t i = lane; i < code_vecs; i += 32) {
     uint4 v[8];
 #pragma unroll
@@ -320,28 +325,27 @@ gather_planes_kernel(const uint4* __restrict__ codes, const uint8_t* __restrict_
       v[r] = src[r] < 0 ? make_uint4(0u, 0u, 0u, 0u) : __ldg(codes + size_t(uint32_t(src[r])) * code_vecs + i);
 #pragma unroll
     for (int r = 0; r < 8; ++r) {
-      const uint32_t row = row0 + warp * 8 + r;
+      const uint32_t row = row0 + r0 + r;
       if (row < rows) out_codes[size_t(row) * code_vecs + i] = v[r];
     }
   }
-  // scales: word t of atom kc belongs to tile row (t >> 2) + 32 (t & 3)
-  uint32_t* dst = reinterpret_cast<uint32_t*>(out_sf + size_t(blockIdx.x) * kchunks * 512);
-  const uint32_t words = kchunks * 128;
-  for (uint32_t j0 = threadIdx.x; j0 < words; j0 += GATHER_THREADS * 8) {
+  // scales: word t of atom kc belongs to tile row (t >> 2) + 32 (t & 3); this block rebuilds atoms sub, sub + 4, ...
+  uint32_t* dst = reinterpret_cast<uint32_t*>(out_sf + size_t(tile) * kchunks * 512);
+  const uint32_t t = threadIdx.x;
+  const int32_t s = s_src[(t >> 2) + 32 * (t & 3)];
+  for (uint32_t kc0 = sub; kc0 < kchunks; kc0 += GATHER_SPLIT * 8) {
     uint32_t v[8];
 #pragma unroll
     for (int u = 0; u < 8; ++u) {
-      const uint32_t j = j0 + u * GATHER_THREADS;
-      const uint32_t kc = j >> 7, t = j & 127;
-      const int32_t s = s_src[(t >> 2) + 32 * (t & 3)];
-      v[u] = (j < words && kc < sf_words && s >= 0)
+      const uint32_t kc = kc0 + u * GATHER_SPLIT;
+      v[u] = (kc < sf_words && s >= 0)
                  ? __ldg(reinterpret_cast<const uint32_t*>(sf + mb_sf_offset(uint32_t(s), 4 * kc, kchunks)))
                  : 0u;
     }
 #pragma unroll
     for (int u = 0; u < 8; ++u) {
-      const uint32_t j = j0 + u * GATHER_THREADS;
-      if (j < words) dst[j] = v[u];
+      const uint32_t kc = kc0 + u * GATHER_SPLIT;
+      if (kc < kchunks) dst[kc * 128 + t] = v[u];
     }
   }
 }
@@ -359,7 +363,7 @@ MB_API int mb_nvfp4_gather_rows(mb_ctx* ctx, mb_stream stream_, const uint8_t* c
              "gather_rows: exceeds u32 block indexing");
   MB_REQUIRE(ctx, mb_aligned(codes, 16) && mb_aligned(out_codes, 16) && mb_aligned(sf_tiled, 4) &&
                       mb_aligned(out_sf_tiled, 4), "gather_rows: planes need 16/4-byte alignment");
-  const unsigned grid = unsigned((rows + 127) / 128);
+  const unsigned grid = unsigned((rows + 127) / 128) * GATHER_SPLIT;
   mb_launch_pdl(gather_planes_kernel, dim3(grid), dim3(GATHER_THREADS), 0, stream,
                 reinterpret_cast<const uint4*>(codes), sf_tiled, gather, uint32_t(rows), uint32_t(src_rows),
                 uint32_t(k / 32), uint32_t(k / 64), uint32_t(mb_sf_kchunks(k)), reinterpret_cast<uint4*>(out_codes),

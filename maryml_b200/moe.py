@@ -8,6 +8,7 @@ algorithm, :3429-3588 for the launch order; routing per src/models/k3/router.rs)
     NVFP4 quantize -> grouped GEMM w2 -> ordered weighted un-permute.
 """
 import ctypes as C
+import os
 
 import numpy as np
 import torch
@@ -155,15 +156,16 @@ def grouped_gemm(a_codes, a_sf, bank, plan, out_dtype=torch.bfloat16, epilogue=_
     return (out, out_sf) if quant else out
 
 
-def moe_experts(x, idx, weight, w13, w2, fuse_swiglu=True, fuse_quant=True):
+def moe_experts(x, idx, weight, w13, w2, fuse_swiglu=True, fuse_quant=True, token_planes=None):
     """grouped_experts_core on the narrow (bf16) lane. x [tokens, h] bf16; w13 bank
-    [E, 2*inter, h] with interleaved gate/up rows; w2 bank [E, h, inter]. Returns [tokens, h] f32."""
+    [E, 2*inter, h] with interleaved gate/up rows; w2 bank [E, h, inter]. Returns [tokens, h] f32.
+    token_planes: the (codes, tiled scales) of quantize_act(x, QUANT_RECIP) when the caller already has them."""
     tokens, h = x.shape
     inter = w2.k
     plan = RowPlan(idx, weight, w13.experts)
     if h % 64 == 0:
         # a row's bytes do not depend on its place in the plan: quantize each token once, copy planes
-        t_codes, t_sf, _ = nv.quantize_act(x, _lib.QUANT_RECIP, tiled=True)
+        t_codes, t_sf = token_planes if token_planes is not None else nv.quantize_act(x, _lib.QUANT_RECIP, tiled=True)[:2]
         a_codes, a_sf = nv.gather_rows(t_codes, t_sf, tokens, h, plan.row_tok)
     else:
         a_codes, a_sf, _ = nv.quantize_act(x, _lib.QUANT_RECIP, tiled=True, gather=plan.row_tok)
@@ -182,9 +184,32 @@ def moe_experts(x, idx, weight, w13, w2, fuse_swiglu=True, fuse_quant=True):
     return scatter_weighted(y, plan, h), plan
 
 
+_side_streams = {}
+
+
+def _side_stream(device):
+    s = _side_streams.get(device.index)
+    if s is None:
+        s = _side_streams[device.index] = torch.cuda.Stream(device=device)
+    return s
+
+
 def moe_layer(x, gate_w, k, w13, w2, renormalize=True, scaling=1.0):
-    """One MoE block of config 2: router projection (bf16 GEMM, f32 logits), softmax top-k, experts."""
+    """One MoE block of config 2: router projection (bf16 GEMM, f32 logits), softmax top-k, experts.
+    The tokens' NVFP4 planes do not depend on the routing: their quantizer runs on a second stream beside the
+    router projection, the selection and the row plan (short, latency-bound kernels), and joins before the planes
+    are copied into plan order. MB_MOE_SIDE_STREAM=0 keeps everything on the caller's stream."""
+    planes = None
+    if x.shape[1] % 64 == 0 and os.environ.get("MB_MOE_SIDE_STREAM", "1") != "0":
+        cur, side = torch.cuda.current_stream(x.device), _side_stream(x.device)
+        side.wait_stream(cur)
+        with torch.cuda.stream(side):
+            planes = nv.quantize_act(x, _lib.QUANT_RECIP, tiled=True)[:2]
+        for t in planes:
+            t.record_stream(cur)
     logits = nv.bf16_gemm(x, gate_w, out_dtype=torch.float32)
     idx, weight = router_topk_softmax(logits, k, renormalize, scaling)
-    out, plan = moe_experts(x, idx, weight, w13, w2)
+    if planes is not None:
+        torch.cuda.current_stream(x.device).wait_stream(_side_stream(x.device))
+    out, plan = moe_experts(x, idx, weight, w13, w2, token_planes=planes)
     return out, (logits, idx, weight, plan)
