@@ -367,7 +367,7 @@ def time_steps(env, step, steps, warmup, sample_clocks=True):
 
 def build_moe(env, args):
     torch = env.torch
-    from maryml_b200 import moe
+    from maryml_b200 import _lib, moe
     dev = env.dev
     g = torch.Generator(device=dev)
     g.manual_seed(99)
@@ -390,7 +390,8 @@ def build_moe(env, args):
     peaks = env.peaks
     return {
         "step": lambda: moe.moe_layer(x, gate, K, b13, b2), "e2e": e2e, "units": T, "metric": "moe_layer_tokens_per_s",
-        "unit": "tokens/s", "launches": 14, "h2d": T * h * 2, "d2h": T * h * 4,
+        "unit": "tokens/s", "launches": 13 + splitk_sum_launches(_lib.context(dev.index), 1, T, E, h),
+        "h2d": T * h * 2, "d2h": T * h * 4,
         "roof": lambda ms: {"bound": "hbm", "kernel": "whole layer", "achieved": byts / (ms * 1e-3) / 1e9,
                             "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": byts / (ms * 1e-3) / 1e9 / peaks["hbm_gbs"],
                             "peak_source": peaks["source"], "traffic": None, "flop_per_step": flop,
@@ -538,6 +539,16 @@ class TpLayerSetup:
             self.group.close()
 
 
+def splitk_sum_launches(ctx, operands, rows, n, k):
+    """1 when a split-K product (operands 0: NVFP4, 1: bf16) needs its second kernel, the sum of f32 planes; 0 when
+    it is not split or its K slices meet inside the product's own kernel (one cluster per output tile)."""
+    import ctypes as C
+    from maryml_b200 import _lib
+    cs, ps = C.c_int(), C.c_int()
+    ctx.check(_lib.lib.mb_gemm_splitk_plan(ctx.handle, operands, rows, n, k, C.byref(cs), C.byref(ps)))
+    return 1 if ps.value > 1 and cs.value == 0 else 0
+
+
 def tp_launches(setup, L_, rows, decode, fused):
     """Kernels of ours per layer step: norm+quantize, q|k|v product, rotation+append, attention, quantize, o product,
     add+norm+quantize, gate/up+SwiGLU+quantize product, down product, add = 10; the decode kernel adds its combine
@@ -545,7 +556,7 @@ def tp_launches(setup, L_, rows, decode, fused):
     reduce+residual kernel and runs the second norm+quantize on its own."""
     from maryml_b200 import _lib
     cfgL = setup.cfg
-    splitk = lambda n, k: 1 if _lib.lib.mb_nvfp4_gemm_splitk_workspace(rows, n, k) else 0
+    splitk = lambda n, k: splitk_sum_launches(_lib.context(setup.env.dev.index), 0, rows, n, k)
     n_qkv = (L_.local_heads + 2 * L_.local_kv_heads) * cfgL.head_dim
     launches = 10 + (1 if decode else 0) + splitk(n_qkv, cfgL.hidden)
     if fused:

@@ -197,6 +197,14 @@ int mb_nvfp4_gemm_w4a4(mb_ctx* ctx, mb_stream stream, const uint8_t* a_codes, co
  * mb_nvfp4_gemm_splitk_workspace returns the bytes to provide, 0 when the shape is not split;
  * with a null or short workspace the call is mb_nvfp4_gemm_w4a4. */
 size_t mb_nvfp4_gemm_splitk_workspace(size_t m, size_t n, size_t k);
+/* How such a product (operands 0: NVFP4 x NVFP4, 1: bf16 x bf16) runs on this context's device. With up to eight
+ * slices the K slices of an output tile are the CTAs of one thread-block cluster and meet in distributed shared
+ * memory inside the product's own kernel: no planes, no second kernel, no workspace needed, also through
+ * mb_nvfp4_gemm_w4a4 / mb_bf16_gemm. *cluster_slices is that slice count (0: the form does not apply: more than
+ * eight slices, or more tiles than clusters the device holds at once), *plane_slices the count of the plane form
+ * (0 or 1: not split). The slices are added in slice order in both forms, so a call gives the same bits every time;
+ * the two forms give the same bits whenever their slice counts agree. */
+int mb_gemm_splitk_plan(mb_ctx* ctx, int operands, size_t m, size_t n, size_t k, int* cluster_slices, int* plane_slices);
 int mb_nvfp4_gemm_w4a4_splitk(mb_ctx* ctx, mb_stream stream, const uint8_t* a_codes, const uint8_t* a_sf_tiled,
                               const uint8_t* b_codes, const uint8_t* b_sf_tiled, const float* rowscale, float alpha,
                               size_t m, size_t n, size_t k, void* out, int out_dtype, void* workspace,

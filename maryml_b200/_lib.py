@@ -64,6 +64,7 @@ SIGNATURES = {
     "mb_nvfp4_gemm_w4a16_workspace": (_sz, [_sz, _sz, _sz]),
     "mb_nvfp4_gemm_w4a16": (_i, [_vp, _vp, _vp, _vp, _vp, _f, _sz, _sz, _sz, _vp, _i, _vp, _sz]),
     "mb_bf16_gemm_splitk_workspace": (_sz, [_sz, _sz, _sz]),
+    "mb_gemm_splitk_plan": (C.c_int, [_vp, C.c_int, _sz, _sz, _sz, C.POINTER(C.c_int), C.POINTER(C.c_int)]),
     "mb_bf16_gemm_splitk": (_i, [_vp, _vp, _vp, _vp, _f, _sz, _sz, _sz, _vp, _i, _vp, _sz]),
     "mb_router_topk_softmax": (_i, [_vp, _vp, _vp, _sz, _sz, _sz, _i, _f, _vp, _vp]),
     "mb_router_topk_sinks": (_i, [_vp, _vp, _vp, _vp, _f, _f, _sz, _sz, _sz, _sz, _vp, _vp, _vp]),

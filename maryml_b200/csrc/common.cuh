@@ -56,6 +56,9 @@ struct mb_ctx {
   // which one-time set-up steps this context has done (a context belongs to one device)
   std::atomic<uint32_t> once{0};
   int pair_clusters = 0;             // CTA pairs of the pair GEMM the device holds at once (0 = not asked yet)
+  // clusters of 2..8 CTAs of the single-CTA GEMM kernels (split-K through distributed shared memory) the device
+  // holds at once, per kernel variant (NVFP4 / bf16 x column width): 0 = not asked yet, -1 = none
+  int splitk_clusters[4][9] = {};
   // budget of the waits on peers in the fused exchange (tp.cu), microseconds of wall time
   uint32_t wait_limit_us = 1000000;
   // Lazily resolved driver entry point for tensor-map encoding.

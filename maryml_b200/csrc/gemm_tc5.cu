@@ -63,6 +63,7 @@ struct GemmParams {
   uint32_t out_sf_kchunks;
   int silu_rounded;           // SwiGLU epilogue: round silu(gate) to bf16 before the product
   int quant;                  // SwiGLU epilogue: 0 bf16 out, 1 NVFP4 (reciprocal recipe), 2 NVFP4 (divide recipe, unit global)
+  int cluster_splitk;         // the `splits` K slices of a tile run as one cluster and meet in distributed shared memory
 };
 
 constexpr int MB_EPI_SCATTER = 2;   // internal: used by mb_nvfp4_gemm_w4a4_scatter only
@@ -490,6 +491,28 @@ gemm_tc5_kernel(const __grid_constant__ GemmParams p) {
       fence_after_sync();
       const uint32_t t_acc = tmem_base + ((quad * 32u) << 16) + (buf ? C::ACC1 : C::ACC0);
       constexpr int CHUNKS = BN / 32;
+      if (p.cluster_splitk) {
+        // This CTA's K slice of the tile: the raw f32 sums are parked in the operand stages (idle now: one tile per
+        // CTA, every MMA has retired) as [128 rows][BN] with the 16-byte units of a row XOR-ed by the row, so that
+        // the 32 rows of a warp store, and the readers of the other CTAs load, without bank conflicts.
+        constexpr int PERW = CHUNKS / (EPI_WARPS / 4);
+        const uint32_t trow = quad * 32u + uint32_t(lane);
+        uint8_t* rowp = smem_gen + trow * (BN * 4);
+#pragma unroll 1
+        for (int ci = 0; ci < PERW; ++ci) {
+          const int c = int(part) * PERW + ci;
+          uint32_t r[32];
+          tmem_ld_x32(t_acc + c * 32, r);
+          tmem_ld_wait();
+#pragma unroll
+          for (int u = 0; u < 8; ++u) {
+            const uint32_t unit = uint32_t(c) * 8u + uint32_t(u);
+            *reinterpret_cast<uint4*>(rowp + ((unit ^ (trow & 7u)) * 16u)) =
+                make_uint4(r[4 * u], r[4 * u + 1], r[4 * u + 2], r[4 * u + 3]);
+          }
+        }
+        continue;
+      }
       // split-K: slice sp of the K sum lands in plane sp of the f32 workspace (p.out, p.m rows per plane)
       const uint32_t row0_store = row0 + sp * p.m;
       auto process = [&](int c, const uint32_t* r) {
@@ -536,6 +559,56 @@ gemm_tc5_kernel(const __grid_constant__ GemmParams p) {
       }
 #endif
     }
+  }
+
+  if (p.cluster_splitk) {
+    // ------------------------------ K slices meet ------------------------------------
+    // Every thread of every CTA of the cluster comes here, also after a wait that ran out (the flag word tells the
+    // host; the sums are then wrong but every load below still finds its shared memory in place). CTA r sums the
+    // 32-column chunks r, r + splits, ... over the slices in slice order, the order of the stand-alone sum of
+    // planes, so both paths give the same bits.
+    cluster_sync_unaligned();
+    if (warp >= 2 && *abort_smem == 0) {
+      const uint32_t ew = uint32_t(warp) - 2u, rank = cluster_ctarank();
+      const uint32_t rest = blockIdx.x / p.splits;
+      const uint32_t mt = p.n_fastest ? rest / p.n_tiles : rest % m_tiles;
+      const uint32_t nt = p.n_fastest ? rest % p.n_tiles : rest / m_tiles;
+      const uint32_t m_valid = min(128u, p.m - mt * 128u);
+      const uint32_t tile_s = smem_u32(smem_gen);
+      for (uint32_t c = rank; c < uint32_t(BN / 32); c += p.splits) {
+        const uint32_t col = nt * BN + c * 32u + (uint32_t(lane) & 7u) * 4u;
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          const uint32_t row = ew * 8u + uint32_t(h) * 4u + (uint32_t(lane) >> 3);
+          if (row >= m_valid || col >= p.n) continue;
+          const uint32_t unit = c * 8u + (uint32_t(lane) & 7u);
+          const uint32_t addr = tile_s + row * (BN * 4) + ((unit ^ (row & 7u)) * 16u);
+          float4 v[8];
+#pragma unroll
+          for (uint32_t sl = 0; sl < 8; ++sl)
+            if (sl < p.splits) v[sl] = ld_cluster_f32x4(map_to_cta(addr, sl));
+          float4 acc = v[0];
+#pragma unroll
+          for (uint32_t sl = 1; sl < 8; ++sl)
+            if (sl < p.splits) { acc.x += v[sl].x; acc.y += v[sl].y; acc.z += v[sl].z; acc.w += v[sl].w; }
+          const size_t grow = size_t(mt) * 128u + row;
+          const float scale = p.rowscale ? p.rowscale[grow] * p.alpha : p.alpha;
+          float4 o;
+          if (p.colscale) {
+            const float4 cs = __ldg(reinterpret_cast<const float4*>(p.colscale + col));
+            o = make_float4(acc.x * scale * cs.x, acc.y * scale * cs.y, acc.z * scale * cs.z, acc.w * scale * cs.w);
+          } else {
+            o = make_float4(acc.x * scale, acc.y * scale, acc.z * scale, acc.w * scale);
+          }
+          if (p.out_dtype == MB_DT_F32)
+            *reinterpret_cast<float4*>(static_cast<float*>(p.out) + grow * p.ldo + col) = o;
+          else
+            *reinterpret_cast<uint2*>(static_cast<__nv_bfloat16*>(p.out) + grow * p.ldo + col) =
+                make_uint2(pack_bf16x2(o.x, o.y), pack_bf16x2(o.z, o.w));
+        }
+      }
+    }
+    cluster_sync_unaligned();          // no CTA leaves while another may still read its sums
   }
 
   // ------------------------------ teardown ----------------------------------------
@@ -869,6 +942,102 @@ int launch(mb_ctx* ctx, cudaStream_t stream, const GemmParams& p, uint32_t max_t
 }
 
 
+// Split-K as clusters: the K slices of an output tile are the CTAs of one cluster (consecutive block indices),
+// one tile per CTA, and meet in distributed shared memory instead of f32 planes in global memory and a second
+// kernel. A cluster must sit inside one GPC, so the device holds fewer CTAs of them than of single CTAs (B200,
+// one CTA per SM: 74 clusters of two, 33 of four, 22 of six, 15 of eight); the slice count is the largest one, up
+// to the count the plane path would use and at most eight, for which all tiles' clusters are resident at once.
+// MB_SPLITK_CLUSTER=0 in the environment switches the form off (comparison runs and tests; read per call).
+template <int KIND, int BN>
+int splitk_clusters_held(mb_ctx* ctx, uint32_t cluster) {
+  using C = Cfg<KIND, BN>;
+  int& held = ctx->splitk_clusters[(KIND == KIND_NVF4 ? 0 : 2) + (BN == 256 ? 0 : 1)][cluster];
+  if (held == 0) {
+    constexpr uint32_t once_bit = KIND == KIND_NVF4 ? (BN == 256 ? MB_ONCE_GEMM_NVF4_256 : MB_ONCE_GEMM_NVF4_128)
+                                                    : (BN == 256 ? MB_ONCE_GEMM_BF16_256 : MB_ONCE_GEMM_BF16_128);
+    auto kern = gemm_tc5_kernel<KIND, BN>;
+    if (!mb_once(ctx, once_bit)) {
+      if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES) != cudaSuccess) {
+        (void)cudaGetLastError();
+        return 0;
+      }
+      mb_once_done(ctx, once_bit);
+    }
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(cluster);
+    cfg.blockDim = dim3(NUM_THREADS);
+    cfg.dynamicSmemBytes = C::SMEM_BYTES;
+    cudaLaunchAttribute attr;
+    attr.id = cudaLaunchAttributeClusterDimension;
+    attr.val.clusterDim.x = cluster; attr.val.clusterDim.y = 1; attr.val.clusterDim.z = 1;
+    cfg.attrs = &attr;
+    cfg.numAttrs = 1;
+    int n = 0;
+    if (cudaOccupancyMaxActiveClusters(&n, kern, &cfg) != cudaSuccess) { (void)cudaGetLastError(); n = 0; }
+    held = n >= 1 ? n : -1;
+  }
+  return held > 0 ? held : 0;
+}
+
+// The cluster form for a product the plane path would cut into `sk` slices: which tile width and how many slices
+// put the most CTAs on the device with every tile's cluster resident at once. A 128-column tile doubles the tiles
+// and so allows smaller clusters, of which the device holds more (a [64, 4096] output: 32 tiles x 4 slices = 128
+// CTAs, where 16 tiles x 8 slices do not fit as clusters). slices = 0: the form does not apply, or would leave more
+// than a third of the plane path's CTAs unused. min_steps: fewest K steps per slice.
+struct SplitkCluster { uint32_t slices; bool wide; };
+
+int splitk_held(mb_ctx* ctx, int kind, bool wide, uint32_t cluster) {
+  if (kind == KIND_NVF4) return wide ? splitk_clusters_held<KIND_NVF4, 256>(ctx, cluster) : splitk_clusters_held<KIND_NVF4, 128>(ctx, cluster);
+  return wide ? splitk_clusters_held<KIND_BF16, 256>(ctx, cluster) : splitk_clusters_held<KIND_BF16, 128>(ctx, cluster);
+}
+
+SplitkCluster splitk_cluster_plan(mb_ctx* ctx, int kind, size_t m, size_t n, uint32_t k_steps, uint32_t sk,
+                                  uint32_t min_steps) {
+  SplitkCluster best = {0u, n % 256 == 0};
+  const char* env = getenv("MB_SPLITK_CLUSTER");
+  if ((env && env[0] == '0') || sk < 2) return best;
+  const uint32_t sms = uint32_t(ctx->sm_limit > 0 ? std::min(ctx->sm_limit, ctx->sm_count) : ctx->sm_count);
+  const uint32_t m_tiles = uint32_t((m + 127) / 128);
+  const uint32_t plane_ctas = m_tiles * uint32_t((n + (best.wide ? 255 : 127)) / (best.wide ? 256 : 128)) * sk;
+  uint32_t best_ctas = 0;
+  for (int w = best.wide ? 1 : 0; w >= 0; --w) {
+    const uint32_t bn = w ? 256u : 128u;
+    const uint32_t tiles = m_tiles * uint32_t((n + bn - 1) / bn);
+    if (tiles == 0 || tiles * 2 > sms) continue;
+    uint32_t want = std::min<uint32_t>(std::min<uint32_t>(8u, sms / tiles), k_steps / std::max(1u, min_steps));
+    for (; want >= 2; --want) {
+      const uint32_t per = (k_steps + want - 1) / want;
+      const uint32_t slices = (k_steps + per - 1) / per;
+      if (slices < 2) break;
+      if (tiles * slices > sms || tiles > uint32_t(splitk_held(ctx, kind, w != 0, slices))) continue;
+      if (tiles * slices > best_ctas) { best_ctas = tiles * slices; best.slices = slices; best.wide = w != 0; }
+      break;
+    }
+  }
+  if (best_ctas * 100 < plane_ctas * 65) best.slices = 0;
+  return best;
+}
+
+template <int KIND, int BN>
+int launch_splitk_cluster(mb_ctx* ctx, cudaStream_t stream, const GemmParams& p, uint32_t tiles) {
+  using C = Cfg<KIND, BN>;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(tiles * p.splits);
+  cfg.blockDim = dim3(NUM_THREADS);
+  cfg.dynamicSmemBytes = C::SMEM_BYTES;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[2];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = p.splits; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[1].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = mb_pdl_enabled() ? 2 : 1;
+  MB_CUDA_OK(ctx, cudaLaunchKernelEx(&cfg, gemm_tc5_kernel<KIND, BN>, p));
+  MB_LAUNCH_OK(ctx);
+  return MB_OK;
+}
+
 // A tiled scale plane seen as [atoms, 512 bytes]: 128 int32 per atom, box of 4 atoms (one K step).
 int make_sf_tmap(mb_ctx* ctx, CUtensorMap* tm, const void* base, uint64_t atoms) {
   EncodeTiledFn enc;
@@ -964,7 +1133,15 @@ int gemm_w4a4_common(mb_ctx* ctx, cudaStream_t stream, const uint8_t* a_codes, c
   if (tile_expert) MB_REQUIRE(ctx, n % 128 == 0 && m % 128 == 0, "grouped gemm: n and the stacked rows are multiples of 128");
   GemmParams p;
   memset(&p, 0, sizeof p);
-  const bool wide = (n % 256 == 0);
+  bool wide = (n % 256 == 0);
+  // decode-sized plain products: the K slices of a tile as one cluster when the device holds enough of them
+  SplitkCluster sc = {0u, wide};
+  uint32_t sk = 1;
+  if (epilogue == MB_EPI_PLAIN && !tile_expert) {
+    sk = splitk_factor(ctx->sm_count, m, n, k);
+    sc = splitk_cluster_plan(ctx, KIND_NVF4, m, n, uint32_t((k + 255) / 256), sk, 2);
+    if (sc.slices) wide = sc.wide;
+  }
   int rc = make_tmap(ctx, &p.tmap_a, a_codes, false, m, k / 2, 128);
   if (rc) return rc;
   rc = make_tmap(ctx, &p.tmap_b, b_codes, false, experts * n, k / 2, wide ? 256 : 128);
@@ -994,9 +1171,17 @@ int gemm_w4a4_common(mb_ctx* ctx, cudaStream_t stream, const uint8_t* a_codes, c
   }
   p.splits = 1; p.ks_per_split = p.k_steps;
   p.n_fastest = tile_expert ? 1u : 0u;
-  if (workspace && epilogue == MB_EPI_PLAIN && !tile_expert) {
-    const uint32_t sk = splitk_factor(ctx->sm_count, m, n, k);
-    if (sk > 1 && workspace_bytes >= size_t(sk) * m * n * sizeof(float)) {
+  if (epilogue == MB_EPI_PLAIN && !tile_expert) {
+    if (sc.slices) {
+      // summed in shared memory: no planes, no second kernel, no workspace
+      GemmParams pc = p;
+      pc.ks_per_split = (p.k_steps + sc.slices - 1) / sc.slices;
+      pc.splits = sc.slices;
+      pc.cluster_splitk = 1;
+      return wide ? launch_splitk_cluster<KIND_NVF4, 256>(ctx, stream, pc, pc.m_tiles * pc.n_tiles)
+                  : launch_splitk_cluster<KIND_NVF4, 128>(ctx, stream, pc, pc.m_tiles * pc.n_tiles);
+    }
+    if (workspace && sk > 1 && workspace_bytes >= size_t(sk) * m * n * sizeof(float)) {
       // K slices into f32 planes of the workspace, then one ordered sum with the epilogue scale
       p.ks_per_split = (p.k_steps + sk - 1) / sk;
       p.splits = (p.k_steps + p.ks_per_split - 1) / p.ks_per_split;
@@ -1163,7 +1348,10 @@ static int bf16_gemm_common(mb_ctx* ctx, cudaStream_t stream, const void* a, con
   }
   GemmParams p;
   memset(&p, 0, sizeof p);
-  const bool wide = (n % 256 == 0);
+  bool wide = (n % 256 == 0);
+  const uint32_t sk = bf16_splitk_factor(ctx->sm_count, m, n, k);
+  const SplitkCluster sc = splitk_cluster_plan(ctx, KIND_BF16, m, n, uint32_t((k + 63) / 64), sk, 4);
+  if (sc.slices) wide = sc.wide;
   int rc = make_tmap(ctx, &p.tmap_a, a, true, m, k * 2, 128);
   if (rc) return rc;
   rc = make_tmap(ctx, &p.tmap_b, b, true, n, k * 2, wide ? 256 : 128);
@@ -1175,8 +1363,16 @@ static int bf16_gemm_common(mb_ctx* ctx, cudaStream_t stream, const void* a, con
   p.ldo = uint32_t(n); p.out_dtype = out_dtype; p.epilogue = MB_EPI_PLAIN;
   p.splits = 1; p.ks_per_split = p.k_steps;
   uint32_t tiles = p.m_tiles * p.n_tiles;
-  const uint32_t sk = workspace ? bf16_splitk_factor(ctx->sm_count, m, n, k) : 1;
-  if (sk > 1 && workspace_bytes >= size_t(sk) * m * n * sizeof(float)) {
+  if (sc.slices) {
+    // the K slices of a tile as one cluster, summed in shared memory
+    GemmParams pc = p;
+    pc.ks_per_split = (p.k_steps + sc.slices - 1) / sc.slices;
+    pc.splits = sc.slices;
+    pc.cluster_splitk = 1;
+    return wide ? launch_splitk_cluster<KIND_BF16, 256>(ctx, stream, pc, tiles)
+                : launch_splitk_cluster<KIND_BF16, 128>(ctx, stream, pc, tiles);
+  }
+  if (workspace && sk > 1 && workspace_bytes >= size_t(sk) * m * n * sizeof(float)) {
     // K slices into f32 planes, then one ordered sum with alpha (deterministic)
     p.ks_per_split = (p.k_steps + sk - 1) / sk;
     p.splits = (p.k_steps + p.ks_per_split - 1) / p.ks_per_split;
@@ -1204,6 +1400,23 @@ static int bf16_gemm_common(mb_ctx* ctx, cudaStream_t stream, const void* a, con
 MB_API int mb_bf16_gemm(mb_ctx* ctx, mb_stream stream, const void* a, const void* b, float alpha, size_t m, size_t n,
                         size_t k, void* out, int out_dtype) {
   return bf16_gemm_common(ctx, static_cast<cudaStream_t>(stream), a, b, alpha, m, n, k, out, out_dtype, nullptr, 0);
+}
+
+MB_API int mb_gemm_splitk_plan(mb_ctx* ctx, int operands, size_t m, size_t n, size_t k, int* cluster_slices,
+                               int* plane_slices) {
+  MB_REQUIRE(ctx, ctx && cluster_slices && plane_slices, "gemm_splitk_plan: null argument");
+  MB_REQUIRE(ctx, (operands == 0 || operands == 1) && m > 0 && n > 0 && k > 0, "gemm_splitk_plan: operands 0 or 1, sizes > 0");
+  uint32_t sk, cs;
+  if (operands == 0) {
+    sk = splitk_factor(ctx->sm_count, m, n, k);
+    cs = splitk_cluster_plan(ctx, KIND_NVF4, m, n, uint32_t((k + 255) / 256), sk, 2).slices;
+  } else {
+    sk = bf16_splitk_factor(ctx->sm_count, m, n, k);
+    cs = splitk_cluster_plan(ctx, KIND_BF16, m, n, uint32_t((k + 63) / 64), sk, 4).slices;
+  }
+  *cluster_slices = int(cs);
+  *plane_slices = int(sk);
+  return MB_OK;
 }
 
 MB_API size_t mb_bf16_gemm_splitk_workspace(size_t m, size_t n, size_t k) {

@@ -24,17 +24,27 @@ namespace {
 constexpr int GEMV_WARPS = 8;
 constexpr int MAX_ROWS = 8;
 
-// Four weights (two bytes of codes) times their block scale -> two bf16x2 registers.
-__device__ __forceinline__ void decode4(uint32_t two_bytes, __half2 s, uint32_t& lo, uint32_t& hi) {
+// A block scale (an E4M3 value held as f16) as the bf16x2 multiplier of decode4: scale * 2^112 in both halves
+// (four significant bits and at most 448 * 2^112: exact and finite in bf16).
+__device__ __forceinline__ __nv_bfloat162 scale_bf16x2(__half2 s_both) {
+  return __float2bfloat162_rn(__low2float(s_both) * 5.192296858534828e33f);
+}
+
+// Four weights (two bytes of codes) times their block scale -> two bf16x2 registers, without leaving 16-bit
+// registers: an E2M1 value as f16 is zero or a normal number, and its f16 pattern shifted three places to the right
+// (sign kept in place) is the bf16 pattern of the value times 2^-112; one packed bf16 multiply by scale * 2^112
+// gives value * scale, exact (at most six significant bits, no intermediate below the normal range).
+__device__ __forceinline__ void decode4(uint32_t two_bytes, __nv_bfloat162 s, uint32_t& lo, uint32_t& hi) {
   uint32_t h0, h1;
   asm("{ .reg .b8 b0, b1, b2, b3; mov.b32 {b0, b1, b2, b3}, %2;\n\t"
       "cvt.rn.f16x2.e2m1x2 %0, b0;\n\tcvt.rn.f16x2.e2m1x2 %1, b1; }"
       : "=r"(h0), "=r"(h1) : "r"(two_bytes));
-  const float2 f0 = __half22float2(__hmul2(*reinterpret_cast<__half2*>(&h0), s));
-  const float2 f1 = __half22float2(__hmul2(*reinterpret_cast<__half2*>(&h1), s));
-  __nv_bfloat162 p0 = __floats2bfloat162_rn(f0.x, f0.y), p1 = __floats2bfloat162_rn(f1.x, f1.y);
-  lo = *reinterpret_cast<uint32_t*>(&p0);
-  hi = *reinterpret_cast<uint32_t*>(&p1);
+  h0 = ((h0 >> 3) & 0x0FFF0FFFu) | (h0 & 0x80008000u);
+  h1 = ((h1 >> 3) & 0x0FFF0FFFu) | (h1 & 0x80008000u);
+  const __nv_bfloat162 p0 = __hmul2(*reinterpret_cast<__nv_bfloat162*>(&h0), s);
+  const __nv_bfloat162 p1 = __hmul2(*reinterpret_cast<__nv_bfloat162*>(&h1), s);
+  lo = *reinterpret_cast<const uint32_t*>(&p0);
+  hi = *reinterpret_cast<const uint32_t*>(&p1);
 }
 
 __device__ __forceinline__ void mma_bf16(float* d, uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
@@ -75,7 +85,20 @@ struct GemvSplit {
   uint32_t ksplit;          // 1: no split, the fields below are unused
   float* partials;          // [ksplit][row blocks][16 weight rows x 8 activation rows]
   int* counters;            // one per row block, zero between calls
+  int cluster;              // the ranges of a row block are the CTAs of one cluster (1, ksplit, 1) and meet in shared memory
 };
+
+// Thread-block cluster primitives of the K-split that needs no workspace.
+__device__ __forceinline__ void gemv_cluster_sync() {
+  asm volatile("barrier.cluster.arrive.release;\n\tbarrier.cluster.wait.acquire;" ::: "memory");
+}
+__device__ __forceinline__ float gemv_ld_cluster(const float* own, uint32_t rank) {
+  uint32_t a = uint32_t(__cvta_generic_to_shared(own)), r;
+  float v;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(rank));
+  asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(r) : "memory");
+  return v;
+}
 
 // The warps' sums of one row block meet in shared memory; with a K split the ranges' sums meet in the workspace.
 template <typename O>
@@ -95,6 +118,19 @@ __device__ __forceinline__ void gemv_finish(const float* acc, O* __restrict__ ou
   if (threadIdx.x < 128) {
 #pragma unroll
     for (int w = 0; w < GEMV_WARPS; ++w) sum += part[w][wr][ar];
+  }
+  if (sp.ksplit > 1 && sp.cluster) {
+    // every CTA of the cluster parks its range's sums; the first one adds them in range order
+    __shared__ float s_range[128];
+    if (threadIdx.x < 128) s_range[threadIdx.x] = sum;
+    gemv_cluster_sync();
+    if (blockIdx.y == 0 && threadIdx.x < 128) {
+      sum = 0.0f;
+      for (uint32_t y = 0; y < sp.ksplit; ++y) sum += gemv_ld_cluster(s_range + threadIdx.x, y);
+      if (ar < rows && row_base + wr < n) out[size_t(ar) * n + row_base + wr] = O(sum * scale2);
+    }
+    gemv_cluster_sync();               // no CTA leaves while the first may still read its sums
+    return;
   }
   if (sp.ksplit > 1) {
     __shared__ int s_last;
@@ -160,6 +196,8 @@ __device__ __forceinline__ void gemv_body(const uint4* __restrict__ x, const uin
       const __half2 sa2 = *reinterpret_cast<__half2*>(&sah), sb2 = *reinterpret_cast<__half2*>(&sbh);
       const __half2 sa_lo = __low2half2(sa2), sa_hi = __high2half2(sa2);
       const __half2 sb_lo = __low2half2(sb2), sb_hi = __high2half2(sb2);
+      __nv_bfloat162 qa_lo, qa_hi, qb_lo, qb_hi;
+      if (!F16) { qa_lo = scale_bf16x2(sa_lo); qa_hi = scale_bf16x2(sa_hi); qb_lo = scale_bf16x2(sb_lo); qb_hi = scale_bf16x2(sb_hi); }
       const uint32_t wwa[4] = {wa[u].x, wa[u].y, wa[u].z, wa[u].w}, wwb[4] = {wb[u].x, wb[u].y, wb[u].z, wb[u].w};
 #pragma unroll
       for (int i = 0; i < 8; ++i) {                      // instruction i takes values 4 i .. 4 i + 3 of the 32
@@ -172,8 +210,8 @@ __device__ __forceinline__ void gemv_body(const uint4* __restrict__ x, const uin
           decode4_f16(bb, i < 4 ? sb_lo : sb_hi, a1, a3);
           mma_f16_acc(acc, a0, a1, a2, a3, b0, b1);
         } else {
-          decode4(ba, i < 4 ? sa_lo : sa_hi, a0, a2);    // row g:     slots (2t, 2t+1) and (2t+8, 2t+9)
-          decode4(bb, i < 4 ? sb_lo : sb_hi, a1, a3);    // row g + 8
+          decode4(ba, i < 4 ? qa_lo : qa_hi, a0, a2);    // row g:     slots (2t, 2t+1) and (2t+8, 2t+9)
+          decode4(bb, i < 4 ? qb_lo : qb_hi, a1, a3);    // row g + 8
           mma_bf16(acc, a0, a1, a2, a3, b0, b1);
         }
       }
@@ -254,6 +292,8 @@ __device__ __forceinline__ void gemv_body_ring(const uint4* __restrict__ x, cons
     const __half2 sa2 = *reinterpret_cast<__half2*>(&sah), sb2 = *reinterpret_cast<__half2*>(&sbh);
     const __half2 sa_lo = __low2half2(sa2), sa_hi = __high2half2(sa2);
     const __half2 sb_lo = __low2half2(sb2), sb_hi = __high2half2(sb2);
+    __nv_bfloat162 qa_lo, qa_hi, qb_lo, qb_hi;
+    if (!F16) { qa_lo = scale_bf16x2(sa_lo); qa_hi = scale_bf16x2(sa_hi); qb_lo = scale_bf16x2(sb_lo); qb_hi = scale_bf16x2(sb_hi); }
     const uint32_t wwa[4] = {wa.x, wa.y, wa.z, wa.w}, wwb[4] = {wb.x, wb.y, wb.z, wb.w};
 #pragma unroll
     for (int i = 0; i < 8; ++i) {                        // instruction i takes values 4 i .. 4 i + 3 of the lane's 32
@@ -266,8 +306,8 @@ __device__ __forceinline__ void gemv_body_ring(const uint4* __restrict__ x, cons
         decode4_f16(bb, i < 4 ? sb_lo : sb_hi, a1, a3);
         mma_f16_acc(acc, a0, a1, a2, a3, b0, b1);
       } else {
-        decode4(ba, i < 4 ? sa_lo : sa_hi, a0, a2);
-        decode4(bb, i < 4 ? sb_lo : sb_hi, a1, a3);
+        decode4(ba, i < 4 ? qa_lo : qa_hi, a0, a2);
+        decode4(bb, i < 4 ? qb_lo : qb_hi, a1, a3);
         mma_bf16(acc, a0, a1, a2, a3, b0, b1);
       }
     }
@@ -279,13 +319,15 @@ __device__ __forceinline__ void gemv_body_ring(const uint4* __restrict__ x, cons
 }
 
 template <typename O>
-__global__ void __launch_bounds__(32 * GEMV_WARPS)
+__global__ void __launch_bounds__(32 * GEMV_WARPS, 3)
 gemv_w4a16_kernel(const uint4* __restrict__ x, const uint4* __restrict__ codes, const uint8_t* __restrict__ scales,
-                  O* __restrict__ out, uint32_t rows, uint32_t n, uint32_t k, float scale2) {
+                  O* __restrict__ out, uint32_t rows, uint32_t n, uint32_t k, float scale2, uint32_t ksplit) {
   __shared__ float part[GEMV_WARPS][16][8];
   extern __shared__ __align__(16) uint8_t gemv_ring[];      // GEMV_RING_SMEM bytes when k % 128 == 0, else none
-  if (k % 128 == 0) gemv_body_ring<false, O>(x, codes, scales, out, rows, n, k, scale2, part, GemvSplit{1u, nullptr, nullptr}, gemv_ring);
-  else gemv_body<false, O>(x, codes, scales, out, rows, n, k, scale2, part, GemvSplit{1u, nullptr, nullptr});
+  mb_grid_dependency_sync();                 // the rows may come from the kernel before this one
+  const GemvSplit sp{ksplit, nullptr, nullptr, 1};
+  if (k % 128 == 0) gemv_body_ring<false, O>(x, codes, scales, out, rows, n, k, scale2, part, sp, gemv_ring);
+  else gemv_body<false, O>(x, codes, scales, out, rows, n, k, scale2, part, sp);
 }
 
 // The same with the f16 copy of the activations when every row converted exactly (flags all zero), else with the
@@ -509,13 +551,41 @@ int gemv_set_attributes(mb_ctx* ctx) {
   return MB_OK;
 }
 
+// Ranges of K slices per row block: doubled while the grid would leave fewer than four blocks per SM and every
+// warp of a range still has a slice of its own.
+uint32_t gemv_ksplit(size_t n, size_t k) {
+  const size_t blocks = (n + 15) / 16, slices = (k + 127) / 128;
+  uint32_t s = 1;
+  while (blocks * s < 592 && s < 8 && slices / (2 * s) >= size_t(GEMV_WARPS)) s *= 2;
+  return s;
+}
+
+// One kernel: the caller's bf16 rows as they are, the K ranges of a row block as one cluster (1, ksplit, 1).
 template <typename O>
-int launch_rows(cudaStream_t stream, size_t rows, const void* x, const uint8_t* codes, const uint8_t* scales, O* out,
-                uint32_t n, uint32_t k, float scale2) {
-  dim3 grid((n + 15) / 16), block(32 * GEMV_WARPS);
-  gemv_w4a16_kernel<O><<<grid, block, k % 128 == 0 ? GEMV_RING_SMEM : 0, stream>>>(
-      static_cast<const uint4*>(x), reinterpret_cast<const uint4*>(codes), scales, out, uint32_t(rows), n, k, scale2);
-  return 0;
+cudaError_t launch_rows(cudaStream_t stream, size_t rows, const void* x, const uint8_t* codes, const uint8_t* scales,
+                        O* out, uint32_t n, uint32_t k, float scale2) {
+  const uint32_t ksplit = gemv_ksplit(n, k);
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((n + 15) / 16, ksplit);
+  cfg.blockDim = dim3(32 * GEMV_WARPS);
+  cfg.dynamicSmemBytes = k % 128 == 0 ? GEMV_RING_SMEM : 0;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[2];
+  unsigned na = 0;
+  if (ksplit > 1) {
+    attr[na].id = cudaLaunchAttributeClusterDimension;
+    attr[na].val.clusterDim.x = 1; attr[na].val.clusterDim.y = ksplit; attr[na].val.clusterDim.z = 1;
+    ++na;
+  }
+  if (mb_pdl_enabled()) {
+    attr[na].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[na].val.programmaticStreamSerializationAllowed = 1;
+    ++na;
+  }
+  cfg.attrs = attr;
+  cfg.numAttrs = na;
+  return cudaLaunchKernelEx(&cfg, gemv_w4a16_kernel<O>, static_cast<const uint4*>(x), reinterpret_cast<const uint4*>(codes),
+                            scales, out, uint32_t(rows), n, k, scale2, ksplit);
 }
 
 }  // namespace
@@ -535,26 +605,16 @@ MB_API int mb_nvfp4_gemv_w4a16(mb_ctx* ctx, mb_stream stream_, const void* x_bf1
   int rc = gemv_set_attributes(ctx);
   if (rc) return rc;
   if (out_dtype == MB_DT_BF16)
-    rc = launch_rows(stream, rows, x_bf16, codes, scales, static_cast<__nv_bfloat16*>(out), uint32_t(n), uint32_t(k), scale2);
+    MB_CUDA_OK(ctx, launch_rows(stream, rows, x_bf16, codes, scales, static_cast<__nv_bfloat16*>(out), uint32_t(n), uint32_t(k), scale2));
   else if (out_dtype == MB_DT_F32)
-    rc = launch_rows(stream, rows, x_bf16, codes, scales, static_cast<float*>(out), uint32_t(n), uint32_t(k), scale2);
+    MB_CUDA_OK(ctx, launch_rows(stream, rows, x_bf16, codes, scales, static_cast<float*>(out), uint32_t(n), uint32_t(k), scale2));
   else
     return mb_fail(ctx, MB_ERR_INVALID, "gemv: output is bf16 or f32");
-  if (rc) return mb_fail(ctx, MB_ERR_INVALID, "gemv: unsupported row count");
   MB_LAUNCH_OK(ctx);
   return MB_OK;
 }
 
 namespace {
-
-// Ranges of K slices per row block: doubled while the grid would leave fewer than four blocks per SM and every
-// warp of a range still has a slice of its own.
-uint32_t gemv_ksplit(size_t n, size_t k) {
-  const size_t blocks = (n + 15) / 16, slices = (k + 127) / 128;
-  uint32_t s = 1;
-  while (blocks * s < 592 && s < 8 && slices / (2 * s) >= size_t(GEMV_WARPS)) s *= 2;
-  return s;
-}
 
 struct GemvWorkspace {
   size_t counters_off, partials_off, x16_off, bytes;
@@ -585,7 +645,10 @@ MB_API int mb_nvfp4_gemv_w4a16_ws(mb_ctx* ctx, mb_stream stream_, const void* x_
                                   void* workspace, size_t workspace_bytes) {
   cudaStream_t stream = static_cast<cudaStream_t>(stream_);
   const size_t need = mb_nvfp4_gemv_workspace(rows, n, k);
-  if (!workspace || need == 0 || workspace_bytes < need)
+  // The one-kernel form (bf16 rows as they are, K ranges meeting inside a cluster) needs no workspace; the form with
+  // an f16 copy of the rows, two kernels and K ranges meeting in the workspace stays for MB_GEMV_TWO_PASS=1.
+  static const bool two_pass = [] { const char* e = getenv("MB_GEMV_TWO_PASS"); return e && e[0] == '1'; }();
+  if (!two_pass || !workspace || need == 0 || workspace_bytes < need)
     return mb_nvfp4_gemv_w4a16(ctx, stream_, x_bf16, rows, codes, scales, scale2, n, k, out, out_dtype);
   MB_REQUIRE(ctx, ctx && x_bf16 && codes && scales && out, "gemv: null argument");
   MB_REQUIRE(ctx, n * k <= 0xFFFFFFFFull, "NVFP4 weight exceeds u32 indexing");
@@ -605,7 +668,7 @@ MB_API int mb_nvfp4_gemv_w4a16_ws(mb_ctx* ctx, mb_stream stream_, const void* x_
   int* flags = reinterpret_cast<int*>(base);
   int* counters = reinterpret_cast<int*>(base + w.counters_off);
   uint4* x16 = reinterpret_cast<uint4*>(base + w.x16_off);
-  const GemvSplit sp{w.ksplit, reinterpret_cast<float*>(base + w.partials_off), counters};
+  const GemvSplit sp{w.ksplit, reinterpret_cast<float*>(base + w.partials_off), counters, 0};
   MB_CUDA_OK(ctx, mb_launch_pdl(gemv_x_to_f16_kernel, dim3(unsigned(rows)), dim3(256), 0, stream,
                                 static_cast<const uint4*>(x_bf16), x16, flags, uint32_t(k / 8), counters, w.row_blocks));
   const dim3 grid(w.row_blocks, w.ksplit), block(32 * GEMV_WARPS);

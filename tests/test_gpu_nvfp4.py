@@ -518,3 +518,75 @@ def test_mxfp4_relabelled_as_nvfp4_decodes_to_the_same_bits(mb, orc):
     bad[[7, 300]] = 0xFF
     with pytest.raises(_lib.MaryError, match=r"scale\[7\] is NaN"):
         nv.mxfp4_to_nvfp4(pd, torch.from_numpy(bad).cuda(), rows, cols)
+
+
+def _splitk_plan(operands, m, n, k):
+    import ctypes as C
+    from maryml_b200 import _lib
+    cs, ps = C.c_int(), C.c_int()
+    ctx = _lib.context(0)
+    ctx.check(_lib.lib.mb_gemm_splitk_plan(ctx.handle, operands, m, n, k, C.byref(cs), C.byref(ps)))
+    return cs.value, ps.value
+
+
+@pytest.mark.parametrize("m,n,k", [(64, 6144, 4096), (64, 4096, 14336), (16, 14336, 4096), (128, 4096, 4096), (1, 1024, 2048),
+                                   (37, 1280, 2048)])
+def test_split_k_in_a_cluster_gives_the_bits_of_the_summed_planes(mb, m, n, k, monkeypatch):
+    """The K slices of a decode-sized product meet either in distributed shared memory (one cluster per output tile)
+    or as f32 planes summed by a second kernel; both add the slices in slice order, so the results are the same
+    bits for ordinary (inexact) operands, for f32 and bf16 outputs, with a row scale and with per-column scales."""
+    from maryml_b200 import _lib
+    g = torch.Generator(device="cuda").manual_seed(m + n + k)
+    w = (torch.randn(n, k, device="cuda", generator=g) * 0.02).to(torch.bfloat16)
+    x = torch.randn(m, k, device="cuda", generator=g).to(torch.bfloat16)
+    q = mb.Nvfp4.quantize(w)
+    ac, asf, _ = mb.quantize_act(x, tiled=True)
+    rowscale = (torch.rand(m, device="cuda", generator=g) + 0.5).float()
+    stacked = mb.Stacked([q, q]) if n <= 6144 else None
+
+    def run():
+        outs = [mb.gemm_w4a4(ac, asf, q.codes, q.sf_tiled(), q.scale2, m, n, k, out_dtype=torch.float32),
+                mb.gemm_w4a4(ac, asf, q.codes, q.sf_tiled(), 0.37, m, n, k, rowscale=rowscale)]
+        if stacked is not None:
+            outs.append(mb.gemm_w4a4_stacked(ac, asf, stacked, m))
+        torch.cuda.synchronize()
+        return outs
+
+    assert int(_lib.lib.mb_nvfp4_gemm_splitk_workspace(m, n, k)) > 0
+    monkeypatch.setenv("MB_SPLITK_CLUSTER", "0")
+    planes = run()
+    monkeypatch.setenv("MB_SPLITK_CLUSTER", "1")
+    cs, ps = _splitk_plan(0, m, n, k)
+    assert ps > 1 and (cs == 0 or 2 <= cs <= 8)
+    cluster = run()
+    again = run()
+    for a, b, c in zip(planes, cluster, again):
+        if cs == ps or cs == 0:      # the same slices in the same order: the same bits
+            assert torch.equal(a.view(torch.int32 if a.dtype == torch.float32 else torch.int16),
+                               b.view(torch.int32 if b.dtype == torch.float32 else torch.int16))
+        else:                        # fewer, longer slices: f32 sums associated differently
+            d = (a.float() - b.float()).abs().max().item()
+            assert d <= 2e-2 * a.float().abs().max().item() * (2.0 ** -7 if a.dtype == torch.bfloat16 else 2.0 ** -12), d
+        assert torch.equal(b, c)
+    assert _lib.context(0).check_flags(None)[0] == 0
+
+
+@pytest.mark.parametrize("m,n,k", [(4096, 128, 2048), (32, 256, 4096), (300, 128, 1024)])
+def test_bf16_split_k_in_a_cluster_gives_the_bits_of_the_summed_planes(mb, m, n, k, monkeypatch):
+    from maryml_b200 import _lib
+    g = torch.Generator(device="cuda").manual_seed(m * 3 + n + k)
+    a = torch.randn(m, k, device="cuda", generator=g).to(torch.bfloat16)
+    b = (torch.randn(n, k, device="cuda", generator=g) * 0.05).to(torch.bfloat16)
+    assert int(_lib.lib.mb_bf16_gemm_splitk_workspace(m, n, k)) > 0
+    monkeypatch.setenv("MB_SPLITK_CLUSTER", "0")
+    planes = [mb.bf16_gemm(a, b, out_dtype=torch.float32), mb.bf16_gemm(a, b, out_dtype=torch.bfloat16, alpha=0.5)]
+    monkeypatch.setenv("MB_SPLITK_CLUSTER", "1")
+    cs, ps = _splitk_plan(1, m, n, k)
+    cluster = [mb.bf16_gemm(a, b, out_dtype=torch.float32), mb.bf16_gemm(a, b, out_dtype=torch.bfloat16, alpha=0.5)]
+    torch.cuda.synchronize()
+    if cs == ps or cs == 0:
+        assert torch.equal(planes[0], cluster[0]) and torch.equal(planes[1], cluster[1])
+    ref = a.float() @ b.float().T
+    assert (planes[0] - ref).abs().max() <= 2e-3 * ref.abs().max()
+    assert (cluster[0] - ref).abs().max() <= 2e-3 * ref.abs().max()
+    assert _lib.context(0).check_flags(None)[0] == 0
