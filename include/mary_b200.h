@@ -167,15 +167,19 @@ int mb_nvfp4_gemv_w4a16(mb_ctx* ctx, mb_stream stream, const void* x_bf16, size_
                         const uint8_t* scales_rowmajor, float scale2, size_t n, size_t k, void* out,
                         int out_dtype);
 
-/* The same GEMV with a workspace (mb_nvfp4_gemv_workspace bytes, 256-byte aligned): a pass of one block per row
- * first makes an f16 copy of the activation rows, which is exact for zero, infinite, NaN and every value in f16's
- * normal range (bf16 carries 8 significant bits, f16 11), and the product then runs f16 x f16 with the decoded
- * weights left in f16: five instructions per four weights instead of eleven, the difference between an
- * instruction-bound kernel and one that streams weights at the HBM rate. A row holding a finite value outside
- * f16's normal range raises a flag in the workspace and the whole call takes the bf16 form above; either way
- * every product is exact in f32. A weight with few rows and a long K (fewer than four 16-row blocks per SM) is
- * also cut along K: the ranges' sums meet in the workspace and the block that arrives last adds them in range
- * order, so the result does not depend on timing. A null or short workspace is the call above. */
+/* mb_nvfp4_gemv_w4a16 is one kernel: the bf16 rows are used as they are (a decoded weight goes from its f16 pattern
+ * to bf16 by a three-bit shift and one packed multiply by scale * 2^112, exact), and a weight with few rows and a
+ * long K is cut along K with the ranges of a 16-row block as the CTAs of one thread-block cluster: their sums meet in
+ * distributed shared memory and are added in range order, so the result does not depend on timing and no workspace
+ * is needed.
+ * mb_nvfp4_gemv_w4a16_ws is the same call for weights of up to four 16-row blocks per SM; for taller ones, which
+ * are bound by instruction issue, and given a workspace (mb_nvfp4_gemv_workspace bytes, 256-byte aligned), it takes
+ * a two-kernel form (MB_GEMV_TWO_PASS=1 / 0 in the environment forces one form or the other): a pass of one
+ * block per row makes an f16 copy of the rows (exact for zero, infinite, NaN and every value in f16's normal range;
+ * a row with a finite value outside it raises a flag in the workspace and the call takes the bf16 form), the product
+ * runs f16 x f16 (five instructions per four weights instead of eight) and K ranges meet in the workspace, the block
+ * that arrives last adding them in range order. Every product is exact in f32 in both forms and the ranges are added
+ * in the same order: the forms differ only where their range counts differ. */
 size_t mb_nvfp4_gemv_workspace(size_t rows, size_t n, size_t k);
 int mb_nvfp4_gemv_w4a16_ws(mb_ctx* ctx, mb_stream stream, const void* x_bf16, size_t rows, const uint8_t* codes,
                            const uint8_t* scales_rowmajor, float scale2, size_t n, size_t k, void* out, int out_dtype,

@@ -227,7 +227,7 @@ __device__ __forceinline__ void gemv_body(const uint4* __restrict__ x, const uin
 // an SM, and the next slice's activation chunk is loaded while the current one is multiplied. A lane copies the two
 // 16-byte code chunks it will itself read; lanes 0-15 copy one row's eight scale bytes, which other lanes read, so
 // a __syncwarp stands on both sides of a slot's use.
-constexpr int GEMV_RING = 6;
+constexpr int GEMV_RING = 5;
 constexpr int GEMV_SLICE_BYTES = 16 * 64 + 16 * 8;
 constexpr int GEMV_RING_SMEM = GEMV_WARPS * GEMV_RING * GEMV_SLICE_BYTES;
 
@@ -319,7 +319,7 @@ __device__ __forceinline__ void gemv_body_ring(const uint4* __restrict__ x, cons
 }
 
 template <typename O>
-__global__ void __launch_bounds__(32 * GEMV_WARPS, 3)
+__global__ void __launch_bounds__(32 * GEMV_WARPS, 4)
 gemv_w4a16_kernel(const uint4* __restrict__ x, const uint4* __restrict__ codes, const uint8_t* __restrict__ scales,
                   O* __restrict__ out, uint32_t rows, uint32_t n, uint32_t k, float scale2, uint32_t ksplit) {
   __shared__ float part[GEMV_WARPS][16][8];
@@ -560,11 +560,20 @@ uint32_t gemv_ksplit(size_t n, size_t k) {
   return s;
 }
 
+// K ranges of the one-kernel form: doubled while the whole grid still fits the device at once (four blocks per
+// SM; a grid a little over one wave costs two) and every warp of a range keeps a slice of its own.
+uint32_t gemv_ksplit_one_wave(int sm_count, size_t n, size_t k) {
+  const size_t blocks = (n + 15) / 16, slices = (k + 127) / 128, slots = size_t(sm_count) * 4;
+  uint32_t s = 1;
+  while (blocks * 2 * s <= slots && s < 8 && slices / (2 * s) >= size_t(GEMV_WARPS)) s *= 2;
+  return s;
+}
+
 // One kernel: the caller's bf16 rows as they are, the K ranges of a row block as one cluster (1, ksplit, 1).
 template <typename O>
-cudaError_t launch_rows(cudaStream_t stream, size_t rows, const void* x, const uint8_t* codes, const uint8_t* scales,
-                        O* out, uint32_t n, uint32_t k, float scale2) {
-  const uint32_t ksplit = gemv_ksplit(n, k);
+cudaError_t launch_rows(int sm_count, cudaStream_t stream, size_t rows, const void* x, const uint8_t* codes,
+                        const uint8_t* scales, O* out, uint32_t n, uint32_t k, float scale2) {
+  const uint32_t ksplit = gemv_ksplit_one_wave(sm_count, n, k);
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3((n + 15) / 16, ksplit);
   cfg.blockDim = dim3(32 * GEMV_WARPS);
@@ -605,9 +614,9 @@ MB_API int mb_nvfp4_gemv_w4a16(mb_ctx* ctx, mb_stream stream_, const void* x_bf1
   int rc = gemv_set_attributes(ctx);
   if (rc) return rc;
   if (out_dtype == MB_DT_BF16)
-    MB_CUDA_OK(ctx, launch_rows(stream, rows, x_bf16, codes, scales, static_cast<__nv_bfloat16*>(out), uint32_t(n), uint32_t(k), scale2));
+    MB_CUDA_OK(ctx, launch_rows(ctx->sm_count, stream, rows, x_bf16, codes, scales, static_cast<__nv_bfloat16*>(out), uint32_t(n), uint32_t(k), scale2));
   else if (out_dtype == MB_DT_F32)
-    MB_CUDA_OK(ctx, launch_rows(stream, rows, x_bf16, codes, scales, static_cast<float*>(out), uint32_t(n), uint32_t(k), scale2));
+    MB_CUDA_OK(ctx, launch_rows(ctx->sm_count, stream, rows, x_bf16, codes, scales, static_cast<float*>(out), uint32_t(n), uint32_t(k), scale2));
   else
     return mb_fail(ctx, MB_ERR_INVALID, "gemv: output is bf16 or f32");
   MB_LAUNCH_OK(ctx);
@@ -645,9 +654,13 @@ MB_API int mb_nvfp4_gemv_w4a16_ws(mb_ctx* ctx, mb_stream stream_, const void* x_
                                   void* workspace, size_t workspace_bytes) {
   cudaStream_t stream = static_cast<cudaStream_t>(stream_);
   const size_t need = mb_nvfp4_gemv_workspace(rows, n, k);
-  // The one-kernel form (bf16 rows as they are, K ranges meeting inside a cluster) needs no workspace; the form with
-  // an f16 copy of the rows, two kernels and K ranges meeting in the workspace stays for MB_GEMV_TWO_PASS=1.
-  static const bool two_pass = [] { const char* e = getenv("MB_GEMV_TWO_PASS"); return e && e[0] == '1'; }();
+  // The one-kernel form (bf16 rows as they are, K ranges meeting inside a cluster) needs no workspace. The form with
+  // an f16 copy of the rows, two kernels and K ranges meeting in the workspace serves tall weights (below);
+  // MB_GEMV_TWO_PASS=1 / 0 in the environment forces one or the other.
+  // Weights of more 16-row blocks than the device holds at once (four per SM) are bound by instruction issue, and
+  // there the f16 form's shorter decode is worth its second launch.
+  static const int forced = [] { const char* e = getenv("MB_GEMV_TWO_PASS"); return !e ? -1 : (e[0] == '1' ? 1 : 0); }();
+  const bool two_pass = forced >= 0 ? forced == 1 : (ctx && (n + 15) / 16 > size_t(ctx->sm_count) * 4);
   if (!two_pass || !workspace || need == 0 || workspace_bytes < need)
     return mb_nvfp4_gemv_w4a16(ctx, stream_, x_bf16, rows, codes, scales, scale2, n, k, out, out_dtype);
   MB_REQUIRE(ctx, ctx && x_bf16 && codes && scales && out, "gemv: null argument");
