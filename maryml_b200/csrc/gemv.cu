@@ -659,7 +659,8 @@ MB_API int mb_nvfp4_gemv_w4a16_ws(mb_ctx* ctx, mb_stream stream_, const void* x_
   // MB_GEMV_TWO_PASS=1 / 0 in the environment forces one or the other.
   // Weights of more 16-row blocks than the device holds at once (four per SM) are bound by instruction issue, and
   // there the f16 form's shorter decode is worth its second launch.
-  static const int forced = [] { const char* e = getenv("MB_GEMV_TWO_PASS"); return !e ? -1 : (e[0] == '1' ? 1 : 0); }();
+  const char* env = getenv("MB_GEMV_TWO_PASS");      // read per call: the tests run both forms in one process
+  const int forced = !env ? -1 : (env[0] == '1' ? 1 : 0);
   const bool two_pass = forced >= 0 ? forced == 1 : (ctx && (n + 15) / 16 > size_t(ctx->sm_count) * 4);
   if (!two_pass || !workspace || need == 0 || workspace_bytes < need)
     return mb_nvfp4_gemv_w4a16(ctx, stream_, x_bf16, rows, codes, scales, scale2, n, k, out, out_dtype);

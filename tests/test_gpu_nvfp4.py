@@ -191,10 +191,13 @@ def test_scale_tiling_is_a_bijection(mb, orc):
 
 
 # --------------------------------------------------------------------------- GEMV
-@pytest.mark.parametrize("n,k", [(512, 4096), (200, 96), (33, 4128)])
+@pytest.mark.parametrize("form", ["one kernel", "two pass"])
+@pytest.mark.parametrize("n,k", [(512, 4096), (200, 96), (33, 4128), (1024, 14336)])
 @pytest.mark.parametrize("rows", [1, 3, 8])
-def test_gemv_w4a16_against_f64(mb, orc, rows, n, k):
-    """(200, 96) and (33, 4128): output rows that do not fill a 16-row block, K that does not fill a 128-value slice."""
+def test_gemv_w4a16_against_f64(mb, orc, rows, n, k, form, monkeypatch):
+    """(200, 96) and (33, 4128): output rows that do not fill a 16-row block, K that does not fill a 128-value slice;
+    (1024, 14336): K ranges (a cluster per 16-row block in the one-kernel form, workspace sums in the two-pass form)."""
+    monkeypatch.setenv("MB_GEMV_TWO_PASS", "1" if form == "two pass" else "0")
     wbits = f32_to_bf16_bits(orc.normal_f32(0x0F16CAFE, n * k, 0.02))
     xbits = f32_to_bf16_bits(orc.normal_f32(21 + rows, rows * k, 1.0))
     q = mb.Nvfp4.quantize(dev_bf16(wbits).view(n, k))
@@ -212,14 +215,15 @@ def test_gemv_w4a16_against_f64(mb, orc, rows, n, k):
     assert np.all(np.abs(got - ref) <= bound)
 
 
-def test_gemv_takes_the_bf16_form_when_a_value_does_not_fit_f16(mb, orc):
-    """The GEMV multiplies an f16 copy of the activation rows when that copy is exact; one value outside f16's normal
+def test_gemv_takes_the_bf16_form_when_a_value_does_not_fit_f16(mb, orc, monkeypatch):
+    """The two-pass GEMV multiplies an f16 copy of the activation rows when that copy is exact; one value outside f16's normal
     range (70000, 1e30, 1e-30 and a bf16 subnormal; 1e30 times a decoded weight still fits the f32 accumulator, which
     the reference scales by scale2 only at the end) sends the whole call through the bf16 product.
     Both forms stay inside the reference's bound, and with the plain entry point (no workspace) they agree to f32
     summation order."""
     import ctypes as C
     from maryml_b200 import _lib
+    monkeypatch.setenv("MB_GEMV_TWO_PASS", "1")
     n, k, rows = 272, 4096, 4
     wbits = f32_to_bf16_bits(orc.normal_f32(0x0F16CAFE, n * k, 0.02))
     q = mb.Nvfp4.quantize(dev_bf16(wbits).view(n, k))
@@ -240,7 +244,7 @@ def test_gemv_takes_the_bf16_form_when_a_value_does_not_fit_f16(mb, orc):
         fin = np.isfinite(ref)
         assert np.all(np.abs(got - ref)[fin] <= bound[fin]), poke
         assert np.array_equal(np.isfinite(got), fin)
-        # the entry point without a workspace is the bf16 form
+        # the entry point without a workspace is the one-kernel form on the bf16 rows
         ctx = _lib.context(0)
         plain = torch.empty_like(y)
         ctx.check(_lib.lib.mb_nvfp4_gemv_w4a16(ctx.handle, None, C.c_void_p(x.data_ptr()), rows, C.c_void_p(q.codes.data_ptr()),
