@@ -59,6 +59,7 @@ struct mb_ctx {
   // clusters of 2..8 CTAs of the single-CTA GEMM kernels (split-K through distributed shared memory) the device
   // holds at once, per kernel variant (NVFP4 / bf16 x column width): 0 = not asked yet, -1 = none
   int splitk_clusters[4][9] = {};
+  int w4a16_clusters[9] = {};        // the same for the W4A16 prompt kernel (128-column tiles)
   // budget of the waits on peers in the fused exchange (tp.cu), microseconds of wall time
   uint32_t wait_limit_us = 1000000;
   // Lazily resolved driver entry point for tensor-map encoding.

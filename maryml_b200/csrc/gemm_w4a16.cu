@@ -72,6 +72,8 @@ struct W4a16Params {
   uint32_t splits, ks_per_split;
   float* planes;
   int out_dtype;
+  int cluster_splitk;        // the `splits` K slices of a tile are the CTAs of one cluster (consecutive blocks, one
+                             // item per CTA) and meet in distributed shared memory: no planes, no second kernel
 };
 
 __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
@@ -189,7 +191,9 @@ gemm_w4a16_kernel(const __grid_constant__ W4a16Params p) {
   // item number -> (row tile, column tile, first K step)
   auto item = [&](uint32_t it, uint32_t& mt, uint32_t& nt, uint32_t& ks0) {
     const uint32_t tile = blockIdx.x + it * gridDim.x;
-    const uint32_t sp = tile / mn_tiles, mn = tile - sp * mn_tiles;
+    uint32_t sp, mn;
+    if (p.cluster_splitk) { mn = tile / p.splits; sp = tile - mn * p.splits; }      // slices of a tile side by side
+    else { sp = tile / mn_tiles; mn = tile - sp * mn_tiles; }
     nt = mn / p.m_tiles;
     mt = mn - nt * p.m_tiles;
     ks0 = sp * kps;
@@ -310,6 +314,19 @@ gemm_w4a16_kernel(const __grid_constant__ W4a16Params p) {
         uint32_t r[32];
         tmem_ld_x32(t_acc + c * 32, r);
         tmem_ld_wait();
+        if (p.cluster_splitk) {
+          // This CTA's K slice: the raw sums are parked in the operand stages (idle: one item per CTA, every MMA has
+          // retired) as [128 rows][BN] f32, the 16-byte units of a row XOR-ed by the row (no bank conflicts for the
+          // 32 rows of a warp here, nor for the readers of the other CTAs below).
+          const uint32_t trow = quad * 32u + lane;
+          uint8_t* rowp = smem_gen + trow * (BN * 4);
+#pragma unroll
+          for (int u = 0; u < 8; ++u) {
+            const uint32_t unit = uint32_t(c) * 8u + uint32_t(u);
+            *reinterpret_cast<uint4*>(rowp + ((unit ^ (trow & 7u)) * 16u)) = make_uint4(r[4 * u], r[4 * u + 1], r[4 * u + 2], r[4 * u + 3]);
+          }
+          continue;
+        }
         float v[32];
         const bool to_plane = p.splits > 1;           // a K slice: the unscaled partial sum, f32, into its plane
 #pragma unroll
@@ -402,6 +419,45 @@ gemm_w4a16_kernel(const __grid_constant__ W4a16Params p) {
       if (++rs == uint32_t(RAW_STAGES)) { rs = 0; rph ^= 1u; }
       if (++os == uint32_t(C::OP_STAGES)) { os = 0; oph ^= 1u; }
     }
+  }
+
+  if (p.cluster_splitk) {
+    // ------------------------------ K slices meet ------------------------------------
+    // Every thread of every CTA of the cluster comes here, also after a wait that ran out. CTA r adds the 32-column
+    // chunks r, r + splits, ... over the slices in slice order (the order of the stand-alone sum of planes: the same
+    // bits), times alpha, one cast.
+    cluster_sync_unaligned();
+    if (warp >= 2 && warp < 2 + EPI_WARPS && *abort_smem == 0 && blockIdx.x < total_tiles) {
+      const uint32_t e = (uint32_t(warp) - 2u) * 32u + lane, rank = cluster_ctarank();
+      uint32_t mt, nt, ks0;
+      item(0u, mt, nt, ks0);
+      const uint32_t m_valid = min(uint32_t(BM), p.m - mt * BM);
+      const uint32_t tile_s = smem_u32(smem_gen);
+      for (uint32_t c = rank; c < uint32_t(BN / 32); c += p.splits) {
+        const uint32_t col = nt * BN + c * 32u + (e & 7u) * 4u;
+        if (col >= p.n) continue;
+        for (uint32_t row = e >> 3; row < m_valid; row += 32u * EPI_WARPS / 8u) {
+          const uint32_t unit = c * 8u + (e & 7u);
+          const uint32_t addr = tile_s + row * (BN * 4) + ((unit ^ (row & 7u)) * 16u);
+          float4 v[8];
+#pragma unroll
+          for (uint32_t sl = 0; sl < 8; ++sl)
+            if (sl < p.splits) v[sl] = ld_cluster_f32x4(map_to_cta(addr, sl));
+          float4 acc = v[0];
+#pragma unroll
+          for (uint32_t sl = 1; sl < 8; ++sl)
+            if (sl < p.splits) { acc.x += v[sl].x; acc.y += v[sl].y; acc.z += v[sl].z; acc.w += v[sl].w; }
+          const size_t o = (size_t(mt) * BM + row) * p.n + col;
+          if (p.out_dtype == MB_DT_F32)
+            *reinterpret_cast<float4*>(static_cast<float*>(p.out) + o) =
+                make_float4(acc.x * p.alpha, acc.y * p.alpha, acc.z * p.alpha, acc.w * p.alpha);
+          else
+            *reinterpret_cast<uint2*>(static_cast<__nv_bfloat16*>(p.out) + o) =
+                make_uint2(pack_bf16x2(acc.x * p.alpha, acc.y * p.alpha), pack_bf16x2(acc.z * p.alpha, acc.w * p.alpha));
+        }
+      }
+    }
+    cluster_sync_unaligned();          // no CTA leaves while another may still read its sums
   }
 
   // ------------------------------ teardown ----------------------------------------
@@ -532,6 +588,44 @@ MB_API int mb_nvfp4_gemm_w4a16(mb_ctx* ctx, mb_stream stream_, const void* x_bf1
   p.out_dtype = out_dtype;
   p.splits = 1; p.ks_per_split = p.k_steps;
   const uint32_t sp = wide ? 1u : w4a16_splits(ctx->sm_count, m, n, k);
+  if (sp > 1 && sp <= 8) {
+    // the K slices of a tile as one cluster, summed in shared memory, when every tile's cluster is resident at once
+    // (MB_SPLITK_CLUSTER=0 in the environment keeps the planes below; read per call)
+    const char* env = getenv("MB_SPLITK_CLUSTER");
+    const uint32_t tiles = p.m_tiles * p.n_tiles;
+    const int sms = ctx->sm_limit > 0 ? std::min(ctx->sm_limit, ctx->sm_count) : ctx->sm_count;
+    if (!(env && env[0] == '0') && tiles * sp <= uint32_t(sms)) {
+      if (!mb_once(ctx, MB_ONCE_GEMM_W4A16_128)) {
+        MB_CUDA_OK(ctx, cudaFuncSetAttribute(gemm_w4a16_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<128>::SMEM_BYTES));
+        mb_once_done(ctx, MB_ONCE_GEMM_W4A16_128);
+      }
+      cudaLaunchConfig_t cfg = {};
+      cfg.gridDim = dim3(tiles * sp);
+      cfg.blockDim = dim3(THREADS);
+      cfg.dynamicSmemBytes = Cfg<128>::SMEM_BYTES;
+      cfg.stream = stream;
+      cudaLaunchAttribute attr[2];
+      attr[0].id = cudaLaunchAttributeClusterDimension;
+      attr[0].val.clusterDim.x = sp; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+      attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+      attr[1].val.programmaticStreamSerializationAllowed = 1;
+      cfg.attrs = attr;
+      int& held = ctx->w4a16_clusters[sp];
+      if (held == 0) {
+        cfg.numAttrs = 1;
+        int nc = 0;
+        if (cudaOccupancyMaxActiveClusters(&nc, gemm_w4a16_kernel<128>, &cfg) != cudaSuccess) { (void)cudaGetLastError(); nc = 0; }
+        held = nc >= 1 ? nc : -1;
+      }
+      if (held > 0 && tiles <= uint32_t(held)) {
+        p.splits = sp; p.ks_per_split = p.k_steps / sp; p.cluster_splitk = 1;
+        cfg.numAttrs = mb_pdl_enabled() ? 2 : 1;
+        MB_CUDA_OK(ctx, cudaLaunchKernelEx(&cfg, gemm_w4a16_kernel<128>, p));
+        MB_LAUNCH_OK(ctx);
+        return MB_OK;
+      }
+    }
+  }
   if (sp > 1 && workspace && workspace_bytes >= size_t(sp) * m * n * sizeof(float)) {
     MB_REQUIRE(ctx, mb_aligned(workspace, 16), "gemm_w4a16: workspace needs 16-byte alignment");
     p.splits = sp; p.ks_per_split = p.k_steps / sp;

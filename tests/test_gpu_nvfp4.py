@@ -534,7 +534,7 @@ def _splitk_plan(operands, m, n, k):
 
 
 @pytest.mark.parametrize("m,n,k", [(64, 6144, 4096), (64, 4096, 14336), (16, 14336, 4096), (128, 4096, 4096), (1, 1024, 2048),
-                                   (37, 1280, 2048)])
+                                   (37, 1280, 2048), (64, 1000, 4096), (5, 2056, 3072)])
 def test_split_k_in_a_cluster_gives_the_bits_of_the_summed_planes(mb, m, n, k, monkeypatch):
     """The K slices of a decode-sized product meet either in distributed shared memory (one cluster per output tile)
     or as f32 planes summed by a second kernel; both add the slices in slice order, so the results are the same
@@ -546,7 +546,7 @@ def test_split_k_in_a_cluster_gives_the_bits_of_the_summed_planes(mb, m, n, k, m
     q = mb.Nvfp4.quantize(w)
     ac, asf, _ = mb.quantize_act(x, tiled=True)
     rowscale = (torch.rand(m, device="cuda", generator=g) + 0.5).float()
-    stacked = mb.Stacked([q, q]) if n <= 6144 else None
+    stacked = mb.Stacked([q, q]) if n <= 6144 and n % 128 == 0 else None
 
     def run():
         outs = [mb.gemm_w4a4(ac, asf, q.codes, q.sf_tiled(), q.scale2, m, n, k, out_dtype=torch.float32),
@@ -593,4 +593,25 @@ def test_bf16_split_k_in_a_cluster_gives_the_bits_of_the_summed_planes(mb, m, n,
     ref = a.float() @ b.float().T
     assert (planes[0] - ref).abs().max() <= 2e-3 * ref.abs().max()
     assert (cluster[0] - ref).abs().max() <= 2e-3 * ref.abs().max()
+    assert _lib.context(0).check_flags(None)[0] == 0
+
+
+@pytest.mark.parametrize("m,n,k", [(16, 4096, 4096), (128, 4096, 14336), (100, 2048, 8192), (64, 1000, 4096)])
+def test_w4a16_split_k_in_a_cluster_gives_the_bits_of_the_summed_planes(mb, m, n, k, monkeypatch):
+    """The W4A16 prompt kernel cuts K the same way; its slices are the same in both forms, so the bits are too."""
+    from maryml_b200 import _lib
+    g = torch.Generator(device="cuda").manual_seed(m + 2 * n + k)
+    w = (torch.randn(n, k, device="cuda", generator=g) * 0.02).to(torch.bfloat16)
+    x = torch.randn(m, k, device="cuda", generator=g).to(torch.bfloat16)
+    q = mb.Nvfp4.quantize(w)
+    assert int(_lib.lib.mb_nvfp4_gemm_w4a16_workspace(m, n, k)) > 0
+    outs = {}
+    for form in ("0", "1"):
+        monkeypatch.setenv("MB_SPLITK_CLUSTER", form)
+        outs[form] = [mb.w4a16_gemm(x, q.codes, q.scales, q.scale2, n, k),
+                      mb.w4a16_gemm(x, q.codes, q.scales, q.scale2, n, k, out_dtype=torch.float32)]
+    torch.cuda.synchronize()
+    assert torch.equal(outs["0"][0], outs["1"][0]) and torch.equal(outs["0"][1], outs["1"][1])
+    ref = x.float() @ mb.dequantize(q.codes, q.scales, q.scale2, n, k).float().T
+    assert (outs["1"][1] - ref).abs().max() <= 2e-3 * ref.abs().max()
     assert _lib.context(0).check_flags(None)[0] == 0
