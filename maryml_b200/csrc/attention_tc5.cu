@@ -51,7 +51,8 @@ constexpr int SMEM = (KSTAGES + VSTAGES) * TILE + Q_BYTES + XCHG_BYTES + 1024 + 
 constexpr int THREADS = 576;                   // producer, issuer, two softmax groups of eight warps
 constexpr int S_COL0 = 0, S_COL1 = 128, PV_COL0 = 256, PV_COL1 = 384, TMEM_COLS = 512;
 
-// Development aid (-DMB_ATTN_PROFILE): cycles per phase, summed over CTAs. Slots: 0 issuer waits K/V, 1 issuer waits
+// Development aid (-DMB_ATTN_PROFILE): cycles per phase, summed over CTAs. Slots: 12 / 13 / 14 issuer waits for the first
+// K tile / a V tile / the next K tile (issuing time in between lands in the slot after it), 1 issuer waits
 // P of tile 0, 2 issuer waits P of tile 1, 3 whole kernel, 4 key tiles; first warp of softmax group 0: 5 waits scores,
 // 6 score load + maximum, 8 exponentials, 9 P store, 10 waits PV, 11 rescales taken.
 #ifdef MB_ATTN_PROFILE
@@ -246,7 +247,7 @@ attn_prefill_tc5_kernel(const __grid_constant__ AttnParams p) {
       mma_where = 33;
       APROF_T0();
       ok = mbar_wait(k_full(0), 0u, abort_smem, tflag, 33);
-      APROF_LAP(0);
+      APROF_LAP(12);
       if (ok) {
         fence_after_sync();
         issue_s(0, 0);
@@ -265,7 +266,7 @@ attn_prefill_tc5_kernel(const __grid_constant__ AttnParams p) {
         if (t == 0) {
           mma_where = 35;
           if (!mbar_wait(v_full(vst), (j / VSTAGES) & 1u, abort_smem, tflag, 35)) { ok = false; break; }
-          APROF_LAP(0);
+          APROF_LAP(13);
         }
         fence_after_sync();
         if (elect_one()) {
@@ -282,7 +283,7 @@ attn_prefill_tc5_kernel(const __grid_constant__ AttnParams p) {
           if (t == 0) {
             mma_where = 33;
             if (!mbar_wait(k_full(int((j + 1) % KSTAGES)), ((j + 1) / KSTAGES) & 1u, abort_smem, tflag, 33)) { ok = false; break; }
-            APROF_LAP(0);
+            APROF_LAP(14);
             fence_after_sync();
           }
           issue_s(t, j + 1);
