@@ -21,9 +21,10 @@
 // the issuer sends PV(t, j) and then S(t, j + 1) as soon as group t publishes P(t, j), and the
 // tensor core works for the other group while group t exponentiates (the two groups alternate).
 //
-// The running maximum a row subtracts is allowed to lag the true one by up to 2^8: O_t in
-// TMEM is rescaled (tcgen05.ld, multiply, tcgen05.st) only when a tile raises a row's maximum
-// by more than that, which after the first tiles is rare; the final O_t / l is exact either way.
+// The running maximum a row subtracts may lag the true one: a probability of 2^40 is as exact in bf16 P and in the
+// f32 sums as one of 1 (P, O_t and l scale together; O_t / l is exact either way). After the first tile no maximum
+// is tracked at all; the sum of a row's probabilities tells when a score has outgrown the subtracted maximum by 2^40
+// or more, and only then are the tile's maxima found and O_t in TMEM rescaled (tcgen05.ld, multiply, tcgen05.st).
 //
 // Warp roles: 0 = TMA producer (Q once, a ring of two K tiles and a ring of two V tiles),
 // 1 = MMA issuer, 2-9 and 10-17 = the two softmax groups (one per query tile). A row of 128 scores is shared by
@@ -347,11 +348,11 @@ attn_prefill_tc5_kernel(const __grid_constant__ AttnParams p) {
       SPROF(5);
       fence_after_sync();
       // One pass in the common case: the probabilities are taken against the maximum the row already
-      // subtracts (it may lag the true one by 2^8, see the header) while the tile's own maximum is
-      // collected on the side; P stays in registers until the pair knows the maximum is within reach.
+      // subtracts (it may lag the true one, see the header); P stays in registers until the pair knows from the
+      // sums that the maximum is within reach.
       uint32_t w[32];
-      float sum = 0.0f, mx = -INFINITY;
-      auto probabilities = [&](bool with_max) {
+      float sum = 0.0f;
+      auto probabilities = [&]() {
         const float neg_m = m == -INFINITY ? -INFINITY : -m;      // a row with nothing visible so far gives p = 0
         const f32x2 c2 = f2_pack(p.scale_log2, p.scale_log2), nm2 = f2_pack(neg_m, neg_m);
         f32x2 acc0 = f2_pack(0.0f, 0.0f), acc1 = acc0;           // two running pairs of partial row sums
@@ -360,7 +361,6 @@ attn_prefill_tc5_kernel(const __grid_constant__ AttnParams p) {
 #pragma unroll
             for (int i = 0; i < 16; ++i) {
               const float s0 = __uint_as_float(s[2 * i]), s1 = __uint_as_float(s[2 * i + 1]);
-              if (with_max) mx = fmaxf(mx, fmaxf(s0, s1));
               float x0, x1;
               f2_unpack(f2_fma(f2_pack(s0, s1), c2, nm2), x0, x1);
               const float p0 = ex2(x0), p1 = ex2(x1);
@@ -373,7 +373,6 @@ attn_prefill_tc5_kernel(const __grid_constant__ AttnParams p) {
               const float s0 = __uint_as_float(s[2 * i]), s1 = __uint_as_float(s[2 * i + 1]);
               const int i0 = q * 32 + 2 * i, i1 = i0 + 1;
               const bool v0 = i0 < vis && i0 >= first, v1 = i1 < vis && i1 >= first;
-              if (with_max) mx = fmaxf(mx, fmaxf(v0 ? s0 : -INFINITY, v1 ? s1 : -INFINITY));
               const float p0 = v0 ? ex2(fmaf(s0, p.scale_log2, neg_m)) : 0.0f;
               const float p1 = v1 ? ex2(fmaf(s1, p.scale_log2, neg_m)) : 0.0f;
               acc0 = f2_add(acc0, f2_pack(p0, p1));
@@ -392,39 +391,51 @@ attn_prefill_tc5_kernel(const __grid_constant__ AttnParams p) {
         f2_unpack(acc1, b0, b1);
         sum = (a0 + a1) + (b0 + b1);
       };
+      auto row_maximum = [&]() -> float {      // over this thread's visible scores of the tile
+        float mx = -INFINITY;
+        uint32_t sa[32], sb[32];
+        tmem_ld_x32(t_s, sa);
+        tmem_ld_x32(t_s + 32, sb);
+        tmem_ld_wait();
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          if (full_tile || (i < vis && i >= first)) mx = fmaxf(mx, __uint_as_float(sa[i]));
+          if (full_tile || (32 + i < vis && 32 + i >= first)) mx = fmaxf(mx, __uint_as_float(sb[i]));
+        }
+        return mx;
+      };
       if (j == 0) {
         // first tile: the row maximum first (this thread's 64 scores, then the partner's), then the probabilities
-        {
-          uint32_t sa[32], sb[32];
-          tmem_ld_x32(t_s, sa);
-          tmem_ld_x32(t_s + 32, sb);
-          tmem_ld_wait();
-#pragma unroll
-          for (int i = 0; i < 32; ++i) {
-            if (full_tile || (i < vis && i >= first)) mx = fmaxf(mx, __uint_as_float(sa[i]));
-            if (full_tile || (32 + i < vis && 32 + i >= first)) mx = fmaxf(mx, __uint_as_float(sb[i]));
-          }
-        }
+        const float mx = row_maximum();
         const float other = swap(mx);
         if (!ok) break;
         m = fmaxf(mx, other) * p.scale_log2;
         SPROF(6);
-        probabilities(false);
+        probabilities();
         // the partner may store its P over columns this thread has just read a second time: one more hand-shake
         (void)swap(0.0f);
         if (!ok) break;
       } else {
-        probabilities(true);
-        const float other = swap(mx);         // also: both threads are past their score loads
+        // No maximum is tracked here: the probabilities are taken against the maximum the row already subtracts,
+        // and their sum tells whether that is still good. A score more than 2^40 above the maximum (in the exponent's
+        // units) makes the pair's sums exceed 2^40, or not a number; such a row, and a row that has seen no key yet,
+        // looks for its maximum in a second pass (rare: after its first tiles a row's maximum hardly moves, and
+        // anything up to 2^40 is as exact in bf16 P and f32 O, l as 1 is, since all three scale together).
+        probabilities();
+        const float other = swap(sum);        // also: both threads are past their score loads
         if (!ok) break;
-        const float mt = fmaxf(mx, other) * p.scale_log2;
-        if (__any_sync(0xFFFFFFFFu, mt > m + 8.0f)) {
+        const bool grown = !(fmaxf(sum, other) <= 1099511627776.0f) || m == -INFINITY;
+        if (__any_sync(0xFFFFFFFFu, grown)) {
 #ifdef MB_ATTN_PROFILE
           if (aprof_on) APROF_COUNT(11);
 #endif
-          // some row of this warp pair outgrew its maximum (both warps see the same maxima and decide alike):
-          // bring this thread's half of O_t, and l, to the new maxima and take the probabilities again
-          // (the scores are still in place: no P has been stored yet)
+          // some row of this warp pair outgrew its maximum (both warps see the same sums and decide alike):
+          // find the tile's maxima, bring this thread's half of O_t, and l, to the new maxima and take the
+          // probabilities again (the scores are still in place: no P has been stored yet)
+          const float mx = row_maximum();
+          const float omx = swap(mx);
+          if (!ok) break;
+          const float mt = fmaxf(mx, omx) * p.scale_log2;
           sm_where = 38;
           if (!mbar_wait(pv_done(t), (j - 1u) & 1u, abort_smem, tflag, 38)) { ok = false; break; }
           pv_waited = true;
@@ -443,7 +454,7 @@ attn_prefill_tc5_kernel(const __grid_constant__ AttnParams p) {
           tmem_st_wait();
           l *= f;
           m = m_new;
-          probabilities(false);
+          probabilities();
           (void)swap(0.0f);                   // both threads are past their second read of the scores
           if (!ok) break;
         }

@@ -222,6 +222,24 @@ def test_prefill_attention_at_benchmark_length(mods, orc, figures, nq, keys, q0,
     figures("prefill_parity", nq=nq, keys=keys, q0=q0, window=window, max_rel=worst)
 
 
+@pytest.mark.parametrize("steep", [False, True])
+def test_prefill_row_maxima_that_keep_growing(mods, orc, steep):
+    """After its first tile the prompt kernel tracks no maximum; a row's sum of probabilities tells when a score has
+    outgrown the subtracted maximum by 2^40 or more. Here every key scores higher than the one before (about 17
+    exponent units per 128-key tile: a rescale every few tiles), or jumps by some 650 units at key 700 (the sum
+    overflows to infinity and the tile is taken again against its own maximum)."""
+    att, _ = mods
+    nq = keys = 1536
+    heads, kvh = 2, 1
+    q, k, v = _qkv(orc, 4242, 1, nq, keys, heads, kvh)
+    qf = 1.0 + 0.2 * bf16_bits_to_f32(q).reshape(nq, heads * 128)
+    ramp = np.where(np.arange(keys) >= 700, 40.0, 0.0) if steep else 12.0 * np.arange(keys) / keys
+    kf = ramp[:, None].astype(np.float32) + 0.2 * bf16_bits_to_f32(k).reshape(keys, kvh * 128)
+    q = f32_to_bf16_bits(qf.astype(np.float32).ravel()).reshape(1, nq, heads * 128)
+    k = f32_to_bf16_bits(kf.astype(np.float32).ravel()).reshape(1, keys, kvh * 128)
+    _check(att, orc, q, k, v, 1, nq, keys, heads, kvh, 0)
+
+
 def test_prefill_with_prefix_and_non_causal(mods, orc):
     att, _ = mods
     batch, nq, keys, heads, kvh = 1, 130, 386, 4, 2
