@@ -196,10 +196,14 @@ int mb_nvfp4_gemm_w4a4(mb_ctx* ctx, mb_stream stream, const uint8_t* a_codes, co
 
 /* The same product for decode-sized activations (m <= 128), where a [m, n] output has too few
  * tiles to keep 148 SMs streaming weights (the reference's own answer at this size is its
- * one-plane-per-tile grid, src/nn/nvfp4_gemm.rs:200-291): K is cut into slices that land in f32
- * planes of `workspace` and are summed in slice order (deterministic) with the epilogue scale.
- * mb_nvfp4_gemm_splitk_workspace returns the bytes to provide, 0 when the shape is not split;
- * with a null or short workspace the call is mb_nvfp4_gemm_w4a4. */
+ * one-plane-per-tile grid, src/nn/nvfp4_gemm.rs:200-291): K is cut into slices whose sums are
+ * added in slice order (deterministic) with the epilogue scale. Where the device holds every
+ * tile's slices as one thread-block cluster (mb_gemm_splitk_plan below), they meet in
+ * distributed shared memory inside the product's kernel and `workspace` is not touched;
+ * otherwise they land in f32 planes of `workspace` and a second kernel adds them.
+ * mb_nvfp4_gemm_splitk_workspace returns the bytes to provide for that case, 0 when the shape
+ * is not split; with a null or short workspace the call is mb_nvfp4_gemm_w4a4 (which takes the
+ * cluster form on its own where it applies). */
 size_t mb_nvfp4_gemm_splitk_workspace(size_t m, size_t n, size_t k);
 /* How such a product (operands 0: NVFP4 x NVFP4, 1: bf16 x bf16) runs on this context's device. With up to eight
  * slices the K slices of an output tile are the CTAs of one thread-block cluster and meet in distributed shared
