@@ -390,7 +390,10 @@ def build_moe(env, args):
     peaks = env.peaks
     return {
         "step": lambda: moe.moe_layer(x, gate, K, b13, b2), "e2e": e2e, "units": T, "metric": "moe_layer_tokens_per_s",
-        "unit": "tokens/s", "launches": 10 + splitk_sum_launches(_lib.context(dev.index), 1, T, E, h),   # the ncu launch list of one layer
+        "unit": "tokens/s", # quantizer, router projection, selection, plan, gather, two products, un-permute (the ncu launch list of a layer);
+        # the plan is one kernel up to 4096 tokens and k <= 8 (its chunks as one cluster), else three
+        "launches": 7 + (1 if T <= 4096 and K <= 8 and os.environ.get("MB_MOE_PLAN_CLUSTER", "1") != "0" else 3)
+        + splitk_sum_launches(_lib.context(dev.index), 1, T, E, h),
         "h2d": T * h * 2, "d2h": T * h * 4,
         "roof": lambda ms: {"bound": "hbm", "kernel": "whole layer", "achieved": byts / (ms * 1e-3) / 1e9,
                             "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": byts / (ms * 1e-3) / 1e9 / peaks["hbm_gbs"],

@@ -41,6 +41,7 @@ enum : uint32_t {
   MB_ONCE_GEMM_W4A16_128 = 1u << 9,
   MB_ONCE_GEMV_RING = 1u << 10,
   MB_ONCE_GEMM_BF16_PAIR = 1u << 11,
+  MB_ONCE_MOE_PLAN_CLUSTER = 1u << 12,
 };
 
 struct mb_ctx {
@@ -60,6 +61,7 @@ struct mb_ctx {
   // holds at once, per kernel variant (NVFP4 / bf16 x column width): 0 = not asked yet, -1 = none
   int splitk_clusters[4][9] = {};
   int w4a16_clusters[9] = {};        // the same for the W4A16 prompt kernel (128-column tiles)
+  int plan_clusters[17] = {};        // whether a cluster of this many CTAs of the MoE plan kernel fits (1 yes, -1 no)
   // budget of the waits on peers in the fused exchange (tp.cu), microseconds of wall time
   uint32_t wait_limit_us = 1000000;
   // Lazily resolved driver entry point for tensor-map encoding.

@@ -484,6 +484,162 @@ plan_place8_kernel(const int32_t* __restrict__ idx, const float* __restrict__ we
     if (j < k) tok_rows[size_t(t) * k + j] = rows[j];
 }
 
+// The three passes as one kernel for plans of up to 16 chunks (4096 tokens) and k <= 8: the chunks' CTAs are one
+// thread-block cluster, a chunk's histogram stays in its CTA's shared memory, and after a cluster barrier every CTA
+// reads the histograms of all chunks through distributed shared memory: the sums over the earlier chunks are its
+// bases, the sums over all chunks give every expert's rows, tiles and first row (each CTA scans them for itself; the
+// first CTA also writes them out). The same values as the three kernels, without their two round trips through
+// global memory and two launches.
+constexpr int PLAN_CLUSTER_MAX = 16;
+
+__device__ __forceinline__ void plan_cluster_sync() {
+  asm volatile("barrier.cluster.arrive.release;\n\tbarrier.cluster.wait.acquire;" ::: "memory");
+}
+__device__ __forceinline__ int32_t plan_ld_cluster(const int32_t* own, uint32_t rank) {
+  uint32_t a = uint32_t(__cvta_generic_to_shared(own)), r;
+  int32_t v;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(rank));
+  asm volatile("ld.shared::cluster.b32 %0, [%1];" : "=r"(v) : "r"(r) : "memory");
+  return v;
+}
+
+__global__ void __launch_bounds__(PLAN_CHUNK)
+plan_cluster8_kernel(const int32_t* __restrict__ idx, const float* __restrict__ weight, uint32_t tokens, uint32_t k,
+                     uint32_t n_experts, int32_t* __restrict__ row_tok, float* __restrict__ row_wgt,
+                     int32_t* __restrict__ tok_rows, int32_t* __restrict__ expert_rows, int32_t* __restrict__ expert_row0,
+                     int32_t* __restrict__ tile_expert, uint32_t tile_cap, int32_t* __restrict__ n_tiles, uint32_t m_cap,
+                     int* __restrict__ flag) {
+  extern __shared__ int32_t s_plan[];          // hist | base | row0 | pad  [n_experts] each, then mask [n_experts][8]
+  int32_t* s_hist = s_plan;
+  int32_t* s_base = s_hist + n_experts;
+  int32_t* s_row0 = s_base + n_experts;
+  int32_t* s_pad = s_row0 + n_experts;
+  uint32_t* s_mask = reinterpret_cast<uint32_t*>(s_pad + n_experts);
+  __shared__ int32_t s_warp[PLAN_CHUNK / 32];
+  __shared__ int32_t s_total;
+  for (uint32_t e = threadIdx.x; e < n_experts; e += PLAN_CHUNK) s_hist[e] = 0;
+  for (uint32_t i = threadIdx.x; i < n_experts * 8; i += PLAN_CHUNK) s_mask[i] = 0u;
+  mb_grid_dependency_sync();
+  for (uint32_t i = blockIdx.x * PLAN_CHUNK + threadIdx.x; i < m_cap; i += gridDim.x * PLAN_CHUNK) {
+    row_tok[i] = -1;
+    row_wgt[i] = 0.0f;
+  }
+  const uint32_t t = blockIdx.x * PLAN_CHUNK + threadIdx.x;
+  const uint32_t word = threadIdx.x >> 5, bit = threadIdx.x & 31, lane = bit;
+  const bool live = t < tokens;
+  int32_t e[8];
+  float w[8];
+#pragma unroll
+  for (uint32_t j = 0; j < 8; ++j) {
+    const bool have = live && j < k;
+    e[j] = have ? __ldg(idx + size_t(t) * k + j) : -1;
+    w[j] = have ? __ldg(weight + size_t(t) * k + j) : 0.0f;
+  }
+  __syncthreads();
+  uint32_t ok_bits = 0;
+#pragma unroll
+  for (uint32_t j = 0; j < 8; ++j) {
+    bool ok = live && j < k && e[j] >= 0 && uint32_t(e[j]) < n_experts;
+#pragma unroll
+    for (uint32_t i = 0; i < j; ++i) ok = ok && e[i] != e[j];
+    if (ok) {
+      ok_bits |= 1u << j;
+      atomicAdd(&s_hist[e[j]], 1);
+      atomicOr(&s_mask[uint32_t(e[j]) * 8 + word], 1u << bit);
+    } else if (live && j < k) {
+      atomicCAS(flag, 0, int(t) + 1);
+    }
+  }
+  __syncthreads();
+  plan_cluster_sync();                         // every chunk's histogram is in place; the rows' empty state is written
+  // this thread's experts: a contiguous run, so that the prefix over the experts is a scan over the threads
+  const uint32_t per = (n_experts + PLAN_CHUNK - 1) / PLAN_CHUNK;       // <= 4
+  const uint32_t e0 = threadIdx.x * per, rank = blockIdx.x, ranks = gridDim.x;
+  int32_t tot[4] = {0, 0, 0, 0}, pads = 0;
+  for (uint32_t i = 0; i < per; ++i) {
+    const uint32_t ex = e0 + i;
+    if (ex >= n_experts) break;
+    int32_t base = 0, total = 0;
+    for (uint32_t r = 0; r < ranks; ++r) {
+      const int32_t c = plan_ld_cluster(s_hist + ex, r);
+      if (r < rank) base += c;
+      total += c;
+    }
+    s_base[ex] = base;
+    tot[i] = total;
+    const int32_t pad = (total + PLAN_PAD - 1) / PLAN_PAD;
+    s_pad[ex] = pad;
+    pads += pad;
+  }
+  int32_t inc = pads;                          // inclusive prefix of the tile counts over the threads
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    const int32_t up = __shfl_up_sync(0xFFFFFFFFu, inc, o);
+    if (lane >= uint32_t(o)) inc += up;
+  }
+  if (lane == 31) s_warp[word] = inc;
+  __syncthreads();
+  if (word == 0) {
+    const int32_t v = lane < PLAN_CHUNK / 32 ? s_warp[lane] : 0;
+    int32_t winc = v;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const int32_t up = __shfl_up_sync(0xFFFFFFFFu, winc, o);
+      if (lane >= uint32_t(o)) winc += up;
+    }
+    if (lane < PLAN_CHUNK / 32) s_warp[lane] = winc - v;
+    if (lane == 31) s_total = winc;
+  }
+  __syncthreads();
+  int32_t off = s_warp[word] + inc - pads;     // tiles before this thread's first expert
+  for (uint32_t i = 0; i < per; ++i) {
+    const uint32_t ex = e0 + i;
+    if (ex >= n_experts) break;
+    s_row0[ex] = off * PLAN_PAD;
+    if (rank == 0) {
+      expert_rows[ex] = tot[i];
+      expert_row0[ex] = off * PLAN_PAD;
+      for (int32_t q = 0; q < s_pad[ex]; ++q)
+        if (uint32_t(off + q) < tile_cap) tile_expert[off + q] = int32_t(ex);
+    }
+    off += s_pad[ex];
+  }
+  if (rank == 0) {
+    if (threadIdx.x == 0) *n_tiles = s_total;
+    for (uint32_t i = uint32_t(s_total) + threadIdx.x; i < tile_cap; i += PLAN_CHUNK) tile_expert[i] = -1;
+  }
+  __syncthreads();
+  plan_cluster_sync();                         // no CTA leaves (or reuses nothing) while another reads its histogram
+  if (!live) return;
+  int32_t rows[8];
+#pragma unroll
+  for (uint32_t j = 0; j < 8; ++j) {
+    int32_t row = j < k ? -1 : 0x7FFFFFFF;          // a pick without a row sorts first, an absent pick last
+    if (ok_bits >> j & 1u) {
+      const uint32_t ex = uint32_t(e[j]);
+      const uint32_t* m = s_mask + ex * 8;
+      int32_t pos = __popc(m[word] & ((1u << bit) - 1u));
+      for (uint32_t ww = 0; ww < word; ++ww) pos += __popc(m[ww]);
+      row = s_row0[ex] + s_base[ex] + pos;
+      row_tok[row] = int32_t(t);
+      row_wgt[row] = w[j];
+    }
+    rows[j] = row;
+  }
+#pragma unroll
+  for (int pass = 0; pass < 8; ++pass) {
+#pragma unroll
+    for (int i = pass & 1; i + 1 < 8; i += 2) {
+      const int32_t lo = min(rows[i], rows[i + 1]), hi = max(rows[i], rows[i + 1]);
+      rows[i] = lo;
+      rows[i + 1] = hi;
+    }
+  }
+#pragma unroll
+  for (uint32_t j = 0; j < 8; ++j)
+    if (j < k) tok_rows[size_t(t) * k + j] = rows[j];
+}
+
 }  // namespace
 
 MB_API int mb_router_topk(mb_ctx* ctx, mb_stream stream_, const float* logits, const float* bias, int activation,
@@ -595,6 +751,42 @@ MB_API int mb_moe_plan(mb_ctx* ctx, mb_stream stream_, const int32_t* idx, const
   int32_t* chunk_counts = static_cast<int32_t*>(workspace);
   const unsigned chunks = unsigned((tokens + PLAN_CHUNK - 1) / PLAN_CHUNK);
   int* flag = ctx->flags_dev + MB_FLAG_PLAN_FAULT;
+  {
+    // one kernel, the chunks as one cluster, where the plan is small enough (MB_MOE_PLAN_CLUSTER=0: the three passes)
+    const char* env = getenv("MB_MOE_PLAN_CLUSTER");
+    const size_t smem = n_experts * (4 * sizeof(int32_t) + 32);
+    if (!(env && env[0] == '0') && k <= 8 && chunks <= unsigned(PLAN_CLUSTER_MAX) && smem <= 48 * 1024) {
+      if (!mb_once(ctx, MB_ONCE_MOE_PLAN_CLUSTER)) {
+        MB_CUDA_OK(ctx, cudaFuncSetAttribute(plan_cluster8_kernel, cudaFuncAttributeNonPortableClusterSizeAllowed, 1));
+        mb_once_done(ctx, MB_ONCE_MOE_PLAN_CLUSTER);
+      }
+      cudaLaunchConfig_t cfg = {};
+      cfg.gridDim = dim3(chunks);
+      cfg.blockDim = dim3(PLAN_CHUNK);
+      cfg.dynamicSmemBytes = smem;
+      cfg.stream = stream;
+      cudaLaunchAttribute attr[2];
+      attr[0].id = cudaLaunchAttributeClusterDimension;
+      attr[0].val.clusterDim.x = chunks; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+      attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+      attr[1].val.programmaticStreamSerializationAllowed = 1;
+      cfg.attrs = attr;
+      cfg.numAttrs = mb_pdl_enabled() ? 2 : 1;
+      int& fits = ctx->plan_clusters[chunks];
+      if (fits == 0) {
+        int held = 0;
+        if (cudaOccupancyMaxActiveClusters(&held, plan_cluster8_kernel, &cfg) != cudaSuccess) { (void)cudaGetLastError(); held = 0; }
+        fits = held >= 1 ? 1 : -1;
+      }
+      if (fits > 0) {
+        MB_CUDA_OK(ctx, cudaLaunchKernelEx(&cfg, plan_cluster8_kernel, idx, weight, uint32_t(tokens), uint32_t(k),
+                                           uint32_t(n_experts), row_tok, row_wgt, tok_rows, expert_rows, expert_row0,
+                                           tile_expert, uint32_t(m_cap / PLAN_PAD), n_tiles, uint32_t(m_cap), flag));
+        MB_LAUNCH_OK(ctx);
+        return MB_OK;
+      }
+    }
+  }
   mb_launch_pdl(plan_count_kernel, dim3(chunks), dim3(PLAN_CHUNK), n_experts * sizeof(int32_t), stream, idx,
                 uint32_t(tokens), uint32_t(k), uint32_t(n_experts), chunk_counts, row_tok, row_wgt, uint32_t(m_cap), flag);
   MB_LAUNCH_OK(ctx);

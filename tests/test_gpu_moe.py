@@ -149,9 +149,13 @@ def test_router_flags_non_finite_logits(moe, orc):
     assert rc == 0
 
 
+@pytest.mark.parametrize("form", ["one kernel", "three passes"])
 @pytest.mark.parametrize("tokens,n_experts,k", [(2, 3, 2), (130, 4, 3), (4096, 128, 8), (5, 128, 8), (300, 64, 12),
-                                               (1000, 32, 1)])
-def test_row_plan_bit_exact(moe, orc, tokens, n_experts, k):
+                                               (1000, 32, 1), (2000, 256, 6), (3000, 1024, 8), (4097, 64, 4)])
+def test_row_plan_bit_exact(moe, orc, tokens, n_experts, k, form, monkeypatch):
+    """Plans of up to 4096 tokens and k <= 8 are built by one kernel whose CTAs (one per 256 tokens) form a cluster
+    and read one another's histograms; larger ones, and MB_MOE_PLAN_CLUSTER=0, by three passes through global memory."""
+    monkeypatch.setenv("MB_MOE_PLAN_CLUSTER", "1" if form == "one kernel" else "0")
     rng = np.random.default_rng(tokens * 7 + k)
     idx = np.stack([rng.permutation(n_experts)[:k] for _ in range(tokens)]).astype(np.int32)
     wgt = rng.random((tokens, k), dtype=np.float32)
@@ -177,8 +181,10 @@ def test_row_plan_bit_exact(moe, orc, tokens, n_experts, k):
         assert sorted(rw[tr[t]].tolist()) == sorted(wgt[t].tolist())
 
 
-def test_plan_fault_flag_on_duplicate_or_out_of_range(moe, orc):
+@pytest.mark.parametrize("form", ["one kernel", "three passes"])
+def test_plan_fault_flag_on_duplicate_or_out_of_range(moe, orc, form, monkeypatch):
     from maryml_b200 import _lib
+    monkeypatch.setenv("MB_MOE_PLAN_CLUSTER", "1" if form == "one kernel" else "0")
     ctx = _lib.context(0)
     ctx.check_flags(None)
     idx = torch.tensor([[0, 1], [2, 2]], dtype=torch.int32, device="cuda")
