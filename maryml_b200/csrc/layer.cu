@@ -197,7 +197,11 @@ residual_norm_quantize_kernel(const uint4* __restrict__ resid, const float4* __r
 // Rotation of the q and k heads of a stacked [tokens, (hq + 2 hkv) d] projection and the
 // cache append in one pass: q goes out contiguous, rotated k and plain v land in the caches
 // [batch, capacity, hkv, d] at position past + i of their sequence. The per-element
-// arithmetic is rope_kernel's. One thread per eight (f, f + d/2) pairs.
+// arithmetic is rope_kernel's. One thread per eight (f, f + d/2) pairs of ROPE_HEADS heads of a token: the sixteen
+// sines and cosines depend on the position and the pair only, so at prompt sizes they are taken once for eight heads
+// (the pass was bound by them: 71 us for 8192 tokens x 48 heads against 31 us of memory traffic); at decode sizes
+// one head per thread keeps the grid wide and the thread's chain short.
+template <uint32_t ROPE_HEADS>
 __global__ void __launch_bounds__(256)
 rope_append_kernel(const uint4* __restrict__ qkv, uint4* __restrict__ q_out, uint4* __restrict__ k_cache,
                    uint4* __restrict__ v_cache, uint32_t batch, uint32_t t, uint32_t hq, uint32_t hkv, uint32_t d,
@@ -205,38 +209,60 @@ rope_append_kernel(const uint4* __restrict__ qkv, uint4* __restrict__ q_out, uin
   mb_grid_dependency_sync();
   const uint32_t groups = d / 16;                      // eight-pair groups per head
   const uint32_t heads = hq + 2 * hkv;
-  const size_t total = size_t(batch) * t * heads * groups;
+  const uint32_t hgroups = (heads + ROPE_HEADS - 1) / ROPE_HEADS;
+  const size_t total = size_t(batch) * t * hgroups * groups;
   const size_t idx = size_t(blockIdx.x) * 256 + threadIdx.x;
   if (idx >= total) return;
   const uint32_t g = uint32_t(idx % groups);
-  const uint32_t head = uint32_t((idx / groups) % heads);
-  const size_t tok = idx / (size_t(groups) * heads);   // b * t + i
+  const uint32_t head0 = uint32_t((idx / groups) % hgroups) * ROPE_HEADS;
+  const size_t tok = idx / (size_t(groups) * hgroups);   // b * t + i
   const uint32_t i = uint32_t(tok % t), b = uint32_t(tok / t);
   const uint32_t d8 = d / 8, half8 = d8 / 2;
-  const uint4* src = qkv + (tok * heads + head) * d8;
-  const uint4 lo_q = __ldg(src + g), hi_q = __ldg(src + half8 + g);
-  uint4* dst;
-  if (head < hq) dst = q_out + (tok * hq + head) * d8;
-  else if (head < hq + hkv) dst = k_cache + ((size_t(b) * capacity + past + i) * hkv + (head - hq)) * d8;
-  else dst = v_cache + ((size_t(b) * capacity + past + i) * hkv + (head - hq - hkv)) * d8;
-  if (head >= hq + hkv) {
-    dst[g] = lo_q;
-    dst[half8 + g] = hi_q;
-    return;
-  }
-  float low[8], high[8], ol[8], oh[8];
-  unpack8(lo_q, low);
-  unpack8(hi_q, high);
-  const float position = float(past + i);
+  const uint32_t n_here = min(ROPE_HEADS, heads - head0);
+  // all loads of this thread's heads first
+  uint4 lo_q[ROPE_HEADS], hi_q[ROPE_HEADS];
 #pragma unroll
-  for (int j = 0; j < 8; ++j) {
-    const float angle = position * inv_freq[g * 8 + j];
-    const float c = bf16r(cosf(angle)), s = bf16r(sinf(angle));
-    ol[j] = bf16r(low[j] * c) - bf16r(high[j] * s);
-    oh[j] = bf16r(high[j] * c) + bf16r(low[j] * s);
+  for (uint32_t hh = 0; hh < ROPE_HEADS; ++hh) {
+    if (hh < n_here) {
+      const uint4* src = qkv + (tok * heads + head0 + hh) * d8;
+      lo_q[hh] = __ldg(src + g);
+      hi_q[hh] = __ldg(src + half8 + g);
+    }
   }
-  dst[g] = pack8(ol);
-  dst[half8 + g] = pack8(oh);
+  float c[8], s[8];
+  if (head0 < hq + hkv) {                              // at least one rotated head among them
+    const float position = float(past + i);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const float angle = position * inv_freq[g * 8 + j];
+      c[j] = bf16r(cosf(angle));
+      s[j] = bf16r(sinf(angle));
+    }
+  }
+#pragma unroll
+  for (uint32_t hh = 0; hh < ROPE_HEADS; ++hh) {
+    if (hh >= n_here) break;
+    const uint32_t head = head0 + hh;
+    uint4* dst;
+    if (head < hq) dst = q_out + (tok * hq + head) * d8;
+    else if (head < hq + hkv) dst = k_cache + ((size_t(b) * capacity + past + i) * hkv + (head - hq)) * d8;
+    else dst = v_cache + ((size_t(b) * capacity + past + i) * hkv + (head - hq - hkv)) * d8;
+    if (head >= hq + hkv) {
+      dst[g] = lo_q[hh];
+      dst[half8 + g] = hi_q[hh];
+      continue;
+    }
+    float low[8], high[8], ol[8], oh[8];
+    unpack8(lo_q[hh], low);
+    unpack8(hi_q[hh], high);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      ol[j] = bf16r(low[j] * c[j]) - bf16r(high[j] * s[j]);
+      oh[j] = bf16r(high[j] * c[j]) + bf16r(low[j] * s[j]);
+    }
+    dst[g] = pack8(ol);
+    dst[half8 + g] = pack8(oh);
+  }
 }
 
 
@@ -460,10 +486,13 @@ MB_API int mb_rope_append(mb_ctx* ctx, mb_stream stream_, const void* qkv, size_
              capacity);
   MB_REQUIRE(ctx, mb_aligned(qkv, 16) && mb_aligned(q_out, 16) && mb_aligned(k_cache, 16) && mb_aligned(v_cache, 16),
              "rope_append: 16-byte alignment");
-  const size_t total = batch * t * (hq + 2 * hkv) * (d / 16);
+  const bool prompt = batch * t >= 1024;           // enough tokens to fill the device with eight heads per thread
+  const size_t hpt = prompt ? 8 : 1;
+  const size_t total = batch * t * ((hq + 2 * hkv + hpt - 1) / hpt) * (d / 16);
   MB_REQUIRE(ctx, total < (1ull << 40) && batch * capacity < (1ull << 32) && past + t < (1ull << 31),
              "rope_append: extent too large");
-  MB_CUDA_OK(ctx, mb_launch_pdl(rope_append_kernel, dim3(unsigned((total + 255) / 256)), dim3(256), 0, stream,
+  auto kern = prompt ? rope_append_kernel<8> : rope_append_kernel<1>;
+  MB_CUDA_OK(ctx, mb_launch_pdl(kern, dim3(unsigned((total + 255) / 256)), dim3(256), 0, stream,
                                 static_cast<const uint4*>(qkv), static_cast<uint4*>(q_out), static_cast<uint4*>(k_cache),
                                 static_cast<uint4*>(v_cache), uint32_t(batch), uint32_t(t), uint32_t(hq), uint32_t(hkv),
                                 uint32_t(d), uint32_t(past), uint32_t(capacity), inv_freq));

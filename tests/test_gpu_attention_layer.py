@@ -422,7 +422,9 @@ def test_residual_norm_quantize_equals_the_three_kernels(mods, orc, rows, width,
     assert match >= 0.999, match       # the f32 sum of squares is ordered differently on the two sides
 
 
-@pytest.mark.parametrize("batch,t,hq,hkv,past,cap", [(3, 1, 4, 2, 21, 22), (2, 40, 4, 1, 0, 64), (1, 5, 8, 8, 7, 12)])
+@pytest.mark.parametrize("batch,t,hq,hkv,past,cap", [(3, 1, 4, 2, 21, 22), (2, 40, 4, 1, 0, 64), (1, 5, 8, 8, 7, 12),
+                                                     # prompt sizes: eight heads per thread share their sines and cosines
+                                                     (1, 1100, 4, 1, 3, 1200), (2, 600, 8, 2, 0, 600), (1, 1024, 32, 8, 0, 1024)])
 def test_rope_append_equals_rope_and_copy(mods, orc, batch, t, hq, hkv, past, cap):
     _, layer = mods
     from maryml_b200 import _lib
