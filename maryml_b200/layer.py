@@ -32,9 +32,10 @@ def rmsnorm(x, gain, eps):
     return out
 
 
-def add(a, b):
+def add(a, b, out=None):
     ctx = context(a.device.index)
-    out = torch.empty_like(a)
+    if out is None:
+        out = torch.empty_like(a)
     ctx.check(lib.mb_add(ctx.handle, _stream(), _p(a), _p(b), a.numel(), _p(out)))
     return out
 
@@ -425,14 +426,15 @@ class DecoderLayer:
         a = self._attention(x, batch, past, k_cache, v_cache, after_rope, before_rope)
         return self._linear(a, self.wo, out_dtype=torch.float32, out=out)
 
-    def half_mlp(self, x, o_sum):
+    def half_mlp(self, x, o_sum, down_dtype=torch.float32):
         """The MLP half between the two exchange steps: given the layer input and the SUMMED o partial, the new
         residual bf16(x + bf16(o_sum)) and this rank's f32 share of the down projection
-        (src/models/inkling/session.rs:2843-2846)."""
+        (src/models/inkling/session.rs:2843-2846). down_dtype = bf16 is for a layer that is not split: the product
+        then rounds its result itself, to the bytes the f32 share would round to in `finish`."""
         residual, nq_ = self._norm_quantize(x, o_sum, self.post_gain)
         act = nv.gemm_w4a4_stacked(nq_[0], nq_[1], self.wgu, nq_[2],
                                    epilogue=_lib.EPI_SWIGLU_ROUNDED | _lib.EPI_QUANT_SCALED)
-        return residual, self._project((act[0], act[1], x.shape[0]), self.wdown, out_dtype=torch.float32)
+        return residual, self._project((act[0], act[1], x.shape[0]), self.wdown, out_dtype=down_dtype)
 
     @staticmethod
     def finish(residual, down_sum, out=None):
@@ -466,6 +468,11 @@ class DecoderLayer:
         if self._rows_shard(rows):
             return self._forward_rows_sharded(x, batch, past, k_cache, v_cache, out, after_rope, before_rope)
         o_sum = self._all_reduce(self.half_attention(x, batch, past, k_cache, v_cache, after_rope, before_rope))
+        if not (self.group is not None and self.tp.is_split()):
+            # nothing to sum across ranks: the down product hands over bf16 (half the bytes written and read back),
+            # bf16(residual + bf16(down)) either way
+            residual, down = self.half_mlp(x, o_sum, down_dtype=torch.bfloat16)
+            return add(residual, down, out=out)
         residual, down = self.half_mlp(x, o_sum)
         return self.finish(residual, self._all_reduce(down), out=out)
 
