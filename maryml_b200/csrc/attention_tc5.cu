@@ -141,8 +141,20 @@ attn_prefill_tc5_kernel(const __grid_constant__ AttnParams p) {
 
   const int warp = __shfl_sync(0xFFFFFFFFu, int(threadIdx.x >> 5), 0);
   const uint32_t lane = threadIdx.x & 31;
-  // heavy (late) query blocks first
+  // Blocks start in the order of their linear index. Within a sequence the heaviest (latest) query blocks of ALL
+  // heads go first and the lightest last, so that the kernel's tail is made of blocks of a tile or two instead of a
+  // late head's 64-tile block; heads run fastest (the four query heads of a KV head side by side), and a sequence's
+  // K and V (33 MB at 8192 keys) stay in L2 while all its heads pass over them. MB_ATTN_ORDER=0: head-major.
+#ifndef MB_ATTN_ORDER
+#define MB_ATTN_ORDER 1
+#endif
+#if MB_ATTN_ORDER
+  const uint32_t lin = blockIdx.x + gridDim.x * (blockIdx.y + gridDim.y * blockIdx.z);
+  const uint32_t per_seq = gridDim.x * gridDim.y, in_seq = lin % per_seq;
+  const uint32_t qb = gridDim.x - 1 - in_seq / gridDim.y, h = in_seq % gridDim.y, b = lin / per_seq;
+#else
   const uint32_t qb = gridDim.x - 1 - blockIdx.x, h = blockIdx.y, b = blockIdx.z;
+#endif
   const uint32_t kvh = h / (p.heads / p.kv_heads);
   const uint32_t q_row0 = qb * 2 * QT;
   const uint32_t q_rows = min(uint32_t(2 * QT), p.nq - q_row0);
