@@ -728,8 +728,15 @@ def measure_extra(env, w, steps, warmup, cpu=True, graph=False):
                "gpu_launches_per_step": w["launches"], "roofline": w["roof"](per), "config": w["config"], "clocks": clocks}
         if "reduce" in w:
             rec["reduce"] = "fused" if w["reduce"].startswith("fused") else ("nccl" if env.world > 1 else "none")
+        rec["launch"] = "host (Python, one C call per kernel)"
         if isinstance(graph_ms, float):
             rec["cuda_graph_replay"] = {"ms": graph_ms, "value": mult * w["units"] / (graph_ms * 1e-3)}
+            if graph_ms < per:
+                # the same kernels replayed as a CUDA graph: what the GPU needs for the step when the host layer
+                # (about 40 us per call on an idle host, several times that on a busy one) is off the clock
+                rec["host_launched"] = {"ms": per, "value": rec["value"]}
+                rec.update(value=mult * w["units"] / (graph_ms * 1e-3), ms=graph_ms, roofline=w["roof"](graph_ms),
+                           launch="cuda graph replay")
         elif graph_ms is not None:
             rec["cuda_graph_replay"] = graph_ms
         if cpu:
